@@ -1,0 +1,321 @@
+"""ctypes front end to the CPU oracle (oracle/eos_oracle.c).
+
+TEST INFRASTRUCTURE ONLY.  Importable from tests/, __graft_entry__.smoke() and the
+cpu-baseline / reference legs of bench.py; the shipped package never imports it.
+Each wrapper takes and returns numpy arrays; see the C file for the Eos source lines every
+function follows.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from typing import Optional, Sequence
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libeos_oracle.so")
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    """Compile libeos_oracle.so next to its source (gcc via oracle/Makefile)."""
+    src = os.path.join(_HERE, "eos_oracle.c")
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "libeos_oracle.so"])
+    return _LIB_PATH
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        _lib = C.CDLL(_LIB_PATH)
+        _lib.eos_oracle_f16_bits_to_f32.restype = C.c_float
+        _lib.eos_oracle_f16_bits_to_f32.argtypes = [C.c_uint16]
+        _lib.eos_oracle_f32_to_f16_bits.restype = C.c_uint16
+        _lib.eos_oracle_f32_to_f16_bits.argtypes = [C.c_float]
+        _lib.eos_oracle_exact_gelu.restype = C.c_float
+        _lib.eos_oracle_exact_gelu.argtypes = [C.c_float]
+        _lib.eos_oracle_tanh_gelu.restype = C.c_float
+        _lib.eos_oracle_tanh_gelu.argtypes = [C.c_float]
+        _lib.eos_oracle_tq_code_bytes.restype = C.c_int64
+        _lib.eos_oracle_dot.restype = C.c_float
+    return _lib
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _p(a: Optional[np.ndarray]):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def default_workers() -> int:
+    return os.cpu_count() or 1
+
+
+# ----------------------------------------------------------------------------- quant grid
+def quantize_symmetric(data, group: int = 0, bits: int = 8, scale_round_f16: bool = False):
+    """Returns (int8 codes shaped like data, float32 scales[n/group])."""
+    d = _f32(data)
+    n = d.size
+    g = n if group <= 0 else group
+    codes = np.empty(d.shape, dtype=np.int8)
+    scales = np.empty((n + g - 1) // g, dtype=np.float32)
+    lib().eos_oracle_quantize_symmetric(_p(d), C.c_int64(n), C.c_int64(g), C.c_int(bits),
+                                        C.c_int(1 if scale_round_f16 else 0), _p(codes), _p(scales))
+    return codes, scales
+
+
+def dequantize(codes, scales, group: int = 0):
+    c = np.ascontiguousarray(codes, dtype=np.int8)
+    s = _f32(scales)
+    out = np.empty(c.shape, dtype=np.float32)
+    lib().eos_oracle_dequantize(_p(c), C.c_int64(c.size), C.c_int64(group if group > 0 else c.size), _p(s), _p(out))
+    return out
+
+
+def f32_to_f16_bits(x: float) -> int:
+    return int(lib().eos_oracle_f32_to_f16_bits(C.c_float(x)))
+
+
+def f16_bits_to_f32(b: int) -> float:
+    return float(lib().eos_oracle_f16_bits_to_f32(C.c_uint16(b)))
+
+
+# ----------------------------------------------------------------------- pipeline tensor ops
+def gather(table, indices):
+    t = _f32(table)
+    idx = _i32(indices)
+    out = np.empty(idx.shape + (t.shape[1],), dtype=np.float32)
+    rc = lib().eos_oracle_gather(_p(t), C.c_int(t.shape[0]), C.c_int(t.shape[1]), _p(idx), C.c_int64(idx.size), _p(out))
+    if rc:
+        raise IndexError("gather index out of range")
+    return out
+
+
+def matmul(lhs, rhs, scale: float = 1.0):
+    a = _f32(lhs)
+    b = _f32(rhs)
+    k = a.shape[-1]
+    rows = a.size // k
+    out = np.empty(a.shape[:-1] + (b.shape[1],), dtype=np.float32)
+    lib().eos_oracle_matmul(_p(a), C.c_int64(rows), C.c_int(k), _p(b), C.c_int(b.shape[1]), C.c_float(scale), _p(out))
+    return out
+
+
+def normalize_rows(x):
+    a = _f32(x)
+    cols = a.shape[-1]
+    out = np.empty_like(a)
+    lib().eos_oracle_normalize_rows(_p(a), C.c_int64(a.size // cols), C.c_int(cols), _p(out))
+    return out
+
+
+def mean_pool_masked(x, mask):
+    a = _f32(x)
+    m = _i32(mask)
+    b, t, c = a.shape
+    out = np.empty((b, c), dtype=np.float32)
+    lib().eos_oracle_mean_pool_masked(_p(a), _p(m), C.c_int(b), C.c_int(t), C.c_int(c), _p(out))
+    return out
+
+
+def embed_pooled(table, projection, tokens, mask, pool_then_l2: bool = False):
+    t = _f32(table)
+    pr = _f32(projection)
+    tok = _i32(tokens)
+    m = _i32(mask)
+    b, tl = tok.shape
+    out = np.empty((b, pr.shape[1]), dtype=np.float32)
+    rc = lib().eos_oracle_embed_pooled(_p(t), C.c_int(t.shape[0]), C.c_int(t.shape[1]), _p(pr), C.c_int(pr.shape[1]),
+                                       _p(tok), _p(m), C.c_int(b), C.c_int(tl), C.c_int(1 if pool_then_l2 else 0),
+                                       _p(out))
+    if rc:
+        raise IndexError("gather index out of range")
+    return out
+
+
+# ------------------------------------------------------------------------------ BERT family
+def bert_embeddings(tok, pos, typ, gamma, beta, input_ids, position_ids, type_ids, eps=1e-12):
+    tok, pos, typ, gamma, beta = map(_f32, (tok, pos, typ, gamma, beta))
+    ids, pids, tids = map(_i32, (input_ids, position_ids, type_ids))
+    dim = tok.shape[1]
+    out = np.empty(ids.shape + (dim,), dtype=np.float32)
+    rc = lib().eos_oracle_bert_embeddings(_p(tok), C.c_int(tok.shape[0]), _p(pos), C.c_int(pos.shape[0]), _p(typ),
+                                          C.c_int(typ.shape[0]), _p(gamma), _p(beta), _p(ids), _p(pids), _p(tids),
+                                          C.c_int64(ids.size), C.c_int(dim), C.c_double(eps), _p(out))
+    if rc:
+        raise IndexError(["", "input_ids", "position_ids", "token_type_ids"][rc] + " value out of range")
+    return out
+
+
+def dense_hf(x, weight, bias, workers: int = 1):
+    a = _f32(x)
+    w = _f32(weight)
+    b = _f32(bias)
+    rows = a.size // a.shape[-1]
+    out = np.empty(a.shape[:-1] + (w.shape[0],), dtype=np.float32)
+    lib().eos_oracle_dense_hf(_p(a), C.c_int64(rows), C.c_int(a.shape[-1]), _p(w), _p(b), C.c_int(w.shape[0]), _p(out),
+                              C.c_int(workers))
+    return out
+
+
+def bert_attention(q, k, v, mask, heads: int, workers: int = 1):
+    q, k, v = map(_f32, (q, k, v))
+    m = _i32(mask)
+    b, t, h = q.shape
+    out = np.empty_like(q)
+    lib().eos_oracle_bert_attention(_p(q), _p(k), _p(v), _p(m), C.c_int(b), C.c_int(t), C.c_int(h), C.c_int(heads),
+                                    _p(out), C.c_int(workers))
+    return out
+
+
+def layernorm_affine(x, gamma, beta, eps=1e-12):
+    a = _f32(x)
+    g = _f32(gamma)
+    bt = _f32(beta)
+    out = np.empty_like(a)
+    lib().eos_oracle_layernorm_affine(_p(a), C.c_int64(a.size // a.shape[-1]), C.c_int(a.shape[-1]), _p(g), _p(bt),
+                                      C.c_double(eps), _p(out))
+    return out
+
+
+def exact_gelu(x):
+    a = _f32(x)
+    f = lib().eos_oracle_exact_gelu
+    return np.array([f(C.c_float(v)) for v in a.ravel()], dtype=np.float32).reshape(a.shape)
+
+
+def _ptr_array(arrays: Sequence[np.ndarray]):
+    arr = (C.c_void_p * len(arrays))()
+    for i, a in enumerate(arrays):
+        arr[i] = a.ctypes.data
+    return arr
+
+
+def bert_layer(hidden_states, mask, weights16: Sequence[np.ndarray], heads: int, eps=1e-12, workers: int = 1):
+    hs = _f32(hidden_states).copy()
+    m = _i32(mask)
+    ws = [_f32(w) for w in weights16]
+    assert len(ws) == 16
+    b, t, h = hs.shape
+    inter = ws[10].shape[0]
+    lib().eos_oracle_bert_layer(_p(hs), _p(m), C.c_int(b), C.c_int(t), C.c_int(h), C.c_int(inter), C.c_int(heads),
+                                _ptr_array(ws), C.c_double(eps), C.c_int(workers))
+    return hs
+
+
+def bert_embedder(input_ids, mask, type_ids, tok, pos, typ, emb_gamma, emb_beta, layer_weights: Sequence[np.ndarray],
+                  heads: int, eps=1e-12, pooling: str = "masked_mean", head_w=None, workers: int = 1):
+    """layer_weights: 16 float32 tensors per layer, dequantised, dense weights in HF [out,in]."""
+    ids, m, tids = map(_i32, (input_ids, mask, type_ids))
+    tok, pos, typ, eg, eb = map(_f32, (tok, pos, typ, emb_gamma, emb_beta))
+    ws = [_f32(w) for w in layer_weights]
+    layers = len(ws) // 16
+    assert layers * 16 == len(ws)
+    b, t = ids.shape
+    hidden = tok.shape[1]
+    inter = ws[10].shape[0]
+    hw = None if head_w is None else _f32(head_w)
+    out_dim = hidden if hw is None else hw.shape[1]
+    out = np.empty((b, out_dim), dtype=np.float32)
+    rc = lib().eos_oracle_bert_embedder(_p(ids), _p(m), _p(tids), C.c_int(b), C.c_int(t), _p(tok), C.c_int(tok.shape[0]),
+                                        _p(pos), C.c_int(pos.shape[0]), _p(typ), C.c_int(typ.shape[0]), _p(eg), _p(eb),
+                                        _ptr_array(ws), C.c_int(layers), C.c_int(hidden), C.c_int(inter),
+                                        C.c_int(heads), C.c_double(eps), C.c_int(1 if pooling == "cls" else 0),
+                                        _p(hw), C.c_int(out_dim), _p(out), C.c_int(workers))
+    if rc:
+        raise IndexError(["", "input_ids", "position_ids", "token_type_ids"][rc] + " value out of range")
+    return out
+
+
+# --------------------------------------------------------------------------------- TurboQuant
+def tq_code_bytes(dim: int, bits: int) -> int:
+    return int(lib().eos_oracle_tq_code_bytes(C.c_int(dim), C.c_int(bits)))
+
+
+def tq_rotate(x, perm, signs1, signs2, prescale: float = 1.0):
+    a = _f32(x)
+    out = np.empty_like(a)
+    lib().eos_oracle_tq_rotate(_p(a), C.c_int(a.size), _p(_i32(perm)), _p(_f32(signs1)), _p(_f32(signs2)),
+                               C.c_float(prescale), _p(out))
+    return out
+
+
+def tq_encode(x, bits, perm, signs1, signs2, boundaries):
+    a = _f32(x)
+    n, dim = a.shape
+    cb = tq_code_bytes(dim, bits)
+    codes = np.empty((n, cb), dtype=np.uint8)
+    norms = np.empty(n, dtype=np.float32)
+    lib().eos_oracle_tq_encode(_p(a), C.c_int64(n), C.c_int(dim), C.c_int(bits), _p(_i32(perm)), _p(_f32(signs1)),
+                               _p(_f32(signs2)), _p(_f32(boundaries)), _p(codes), _p(norms))
+    return codes, norms
+
+
+def tq_decode(codes, norms, dim, bits, perm, signs1, signs2, centroids):
+    c = np.ascontiguousarray(codes, dtype=np.uint8)
+    nr = _f32(norms)
+    out = np.empty((c.shape[0], dim), dtype=np.float32)
+    lib().eos_oracle_tq_decode(_p(c), _p(nr), C.c_int64(c.shape[0]), C.c_int(dim), C.c_int(bits), _p(_i32(perm)),
+                               _p(_f32(signs1)), _p(_f32(signs2)), _p(_f32(centroids)), _p(out))
+    return out
+
+
+def tq_prepare_query(q, perm, signs1, signs2):
+    a = _f32(q)
+    out = np.empty_like(a)
+    lib().eos_oracle_tq_prepare_query(_p(a), C.c_int(a.size), _p(_i32(perm)), _p(_f32(signs1)), _p(_f32(signs2)),
+                                      _p(out))
+    return out
+
+
+def tq_score(codes, norms, dim, bits, centroids, prepared):
+    c = np.ascontiguousarray(codes, dtype=np.uint8)
+    nr = _f32(norms)
+    out = np.empty(c.shape[0], dtype=np.float32)
+    lib().eos_oracle_tq_score(_p(c), _p(nr), C.c_int64(c.shape[0]), C.c_int(dim), C.c_int(bits), _p(_f32(centroids)),
+                              _p(_f32(prepared)), _p(out))
+    return out
+
+
+def topk(scores, k: int, id_base: int = 0):
+    s = _f32(scores)
+    kk = s.size if (k <= 0 or k > s.size) else k
+    ids = np.empty(kk, dtype=np.int64)
+    out = np.empty(kk, dtype=np.float32)
+    r = lib().eos_oracle_topk(_p(s), C.c_int64(s.size), C.c_int64(id_base), C.c_int(k), _p(ids), _p(out))
+    return ids[:r], out[:r]
+
+
+def tq_score_topk(codes, norms, dim, bits, centroids, prepared, k, id_base: int = 0):
+    return topk(tq_score(codes, norms, dim, bits, centroids, prepared), k, id_base)
+
+
+def topk_merge(ids, scores, k: int):
+    i = np.ascontiguousarray(ids, dtype=np.int64).ravel()
+    s = _f32(scores).ravel()
+    kk = s.size if (k <= 0 or k > s.size) else k
+    oi = np.empty(kk, dtype=np.int64)
+    os_ = np.empty(kk, dtype=np.float32)
+    lib().eos_oracle_topk_merge(_p(i), _p(s), C.c_int64(s.size), C.c_int(k), _p(oi), _p(os_))
+    return oi, os_
+
+
+def parent_topk(child_scores, parent_of_child, parents: int, k: int, top_n: int = 1, penalty: float = 0.0):
+    s = _f32(child_scores)
+    p = _i32(parent_of_child)
+    oi = np.empty(parents, dtype=np.int64)
+    os_ = np.empty(parents, dtype=np.float32)
+    r = lib().eos_oracle_parent_topk(_p(s), _p(p), C.c_int64(s.size), C.c_int(parents), C.c_int(top_n),
+                                     C.c_double(penalty), C.c_int(k), _p(oi), _p(os_))
+    return oi[:r], os_[:r]
