@@ -1,0 +1,1409 @@
+// C ABI of libeos_b200.so (declarations and reference citations: include/eos_b200.h).
+// Host-side orchestration only: argument validation, device memory, kernel sequencing.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/eos_b200.h"
+#include "common.cuh"
+#include "encoder_kernels.cuh"
+#include "gemm_tc.cuh"
+#include "turboquant.cuh"
+
+using namespace eosb;
+
+// ------------------------------------------------------------------------------------------------
+// helpers
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+char* dup_cstring(const std::string& s) {
+    char* p = static_cast<char*>(std::malloc(s.size() + 1));
+    if (p != nullptr) std::memcpy(p, s.c_str(), s.size() + 1);
+    return p;
+}
+
+int fail(char** err, const std::string& msg, int code = EOS_B200_ERROR) {
+    if (err != nullptr) *err = dup_cstring(msg);
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                              \
+    do {                                                                                            \
+        cudaError_t e__ = (expr);                                                                   \
+        if (e__ != cudaSuccess) {                                                                   \
+            cudaGetLastError();                                                                     \
+            return fail(err, std::string(#expr) + ": " + cudaGetErrorString(e__));                  \
+        }                                                                                           \
+    } while (0)
+
+template <typename T>
+cudaError_t dev_alloc(T** p, size_t count) {
+    *p = nullptr;
+    if (count == 0) count = 1;
+    return cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T));
+}
+
+template <typename T>
+void dev_free(T*& p) {
+    if (p != nullptr) cudaFree(p);
+    p = nullptr;
+}
+
+std::vector<__half> to_half(const float* src, size_t n) {
+    std::vector<__half> out(n);
+    for (size_t i = 0; i < n; ++i) out[i] = __float2half_rn(src[i]);
+    return out;
+}
+
+cudaStream_t pick_stream(EosB200Runtime* rt, void* stream);
+
+}  // namespace
+
+struct EosB200Runtime {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaDeviceProp prop{};
+    int sm_count = 0;
+    int* d_status = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+};
+
+namespace {
+cudaStream_t pick_stream(EosB200Runtime* rt, void* stream) {
+    return stream != nullptr ? static_cast<cudaStream_t>(stream) : rt->stream;
+}
+
+int read_status(EosB200Runtime* rt, cudaStream_t s, char** err) {
+    int st = 0;
+    CUDA_TRY(cudaMemcpyAsync(&st, rt->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    if (st == kStatusOk) return EOS_B200_OK;
+    const char* what = "unknown device status";
+    if (st == kStatusBadTokenId) what = "input_ids value out of range [0, vocab)";
+    else if (st == kStatusBadTypeId) what = "token_type_ids value out of range";
+    else if (st == kStatusBadPosition) what = "sequence longer than max_positions";
+    else if (st == kStatusPipelineTimeout) what = "a bounded wait inside a kernel ran out (pipeline timeout)";
+    return fail(err, std::string("device status ") + std::to_string(st) + ": " + what, EOS_B200_DEVICE_STATUS);
+}
+}  // namespace
+
+extern "C" {
+
+const char* eos_b200_version(void) { return "eos_b200 0.1 (sm_100a)"; }
+
+void eos_b200_free_cstring(char* s) { std::free(s); }
+
+int eos_b200_runtime_create(int device, EosB200Runtime** out, char** err) {
+    if (out == nullptr) return fail(err, "runtime_create: out is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count <= 0) {
+        cudaGetLastError();
+        return fail(err, std::string("no CUDA device available (no CPU fallback): ") + cudaGetErrorString(e));
+    }
+    if (device < 0 || device >= count) return fail(err, "runtime_create: device index out of range");
+    CUDA_TRY(cudaSetDevice(device));
+    EosB200Runtime* rt = new EosB200Runtime();
+    rt->device = device;
+    e = cudaGetDeviceProperties(&rt->prop, device);
+    if (e != cudaSuccess) {
+        delete rt;
+        return fail(err, std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e));
+    }
+    if (rt->prop.major != 10) {
+        std::string msg = "device '" + std::string(rt->prop.name) + "' is compute capability " +
+                          std::to_string(rt->prop.major) + "." + std::to_string(rt->prop.minor) +
+                          "; this library only contains sm_100a code (no fallback)";
+        delete rt;
+        return fail(err, msg);
+    }
+    rt->sm_count = rt->prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreate(&rt->ev0) != cudaSuccess || cudaEventCreate(&rt->ev1) != cudaSuccess ||
+        dev_alloc(&rt->d_status, 1) != cudaSuccess || cudaMemset(rt->d_status, 0, sizeof(int)) != cudaSuccess) {
+        std::string msg = std::string("runtime_create: ") + cudaGetErrorString(cudaGetLastError());
+        eos_b200_runtime_destroy(rt);
+        return fail(err, msg);
+    }
+    std::string ge = gemm_global_init();
+    if (ge.empty()) {
+        cudaError_t se = tq_scan_init();
+        if (se != cudaSuccess) ge = std::string("tq_scan_init: ") + cudaGetErrorString(se);
+    }
+    if (!ge.empty()) {
+        eos_b200_runtime_destroy(rt);
+        return fail(err, ge);
+    }
+    *out = rt;
+    return EOS_B200_OK;
+}
+
+void eos_b200_runtime_destroy(EosB200Runtime* rt) {
+    if (rt == nullptr) return;
+    cudaSetDevice(rt->device);
+    if (rt->stream) cudaStreamSynchronize(rt->stream);
+    if (rt->ev0) cudaEventDestroy(rt->ev0);
+    if (rt->ev1) cudaEventDestroy(rt->ev1);
+    dev_free(rt->d_status);
+    if (rt->stream) cudaStreamDestroy(rt->stream);
+    delete rt;
+}
+
+int eos_b200_runtime_info(EosB200Runtime* rt, EosB200DeviceInfo* out, char** err) {
+    if (rt == nullptr || out == nullptr) return fail(err, "runtime_info: null argument");
+    std::memset(out, 0, sizeof(*out));
+    out->device = rt->device;
+    out->cc_major = rt->prop.major;
+    out->cc_minor = rt->prop.minor;
+    out->sm_count = rt->sm_count;
+    out->total_memory_bytes = (int64_t)rt->prop.totalGlobalMem;
+    std::strncpy(out->name, rt->prop.name, sizeof(out->name) - 1);
+    return EOS_B200_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// dense weights
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+struct DenseW {
+    void* w = nullptr;      // biased uint8 codes [n, ldw] or f16 [n, ldw]
+    bool int8 = false;
+    int ldw = 0;
+    float* scale = nullptr; // [n] or null
+    float* bias = nullptr;  // [n] or null
+    int n = 0, k = 0;
+};
+
+void free_dense(DenseW& d) {
+    if (d.w) cudaFree(d.w);
+    d.w = nullptr;
+    dev_free(d.scale);
+    dev_free(d.bias);
+}
+
+std::string check_matrix(const EosB200Matrix& m, int rows, int cols, const char* name) {
+    if (m.rows != rows || m.cols != cols)
+        return std::string(name) + " weight shape [" + std::to_string(m.rows) + "," + std::to_string(m.cols) +
+               "] does not match [out,in]=[" + std::to_string(rows) + "," + std::to_string(cols) + "]";
+    if (m.q8_codes != nullptr) {
+        if (m.q8_scales == nullptr) return std::string(name) + ": q8 weight without scales";
+        if (m.n_scales != 1 && m.n_scales != rows)
+            return std::string(name) + ": n_scales must be 1 (per tensor) or rows (per output channel)";
+    } else if (m.dense == nullptr) {
+        return std::string(name) + ": weight has neither q8 codes nor dense values";
+    }
+    return "";
+}
+
+// Uploads the vertical concatenation of `parts` (same cols) as one dense weight.
+std::string upload_dense(const std::vector<const EosB200Matrix*>& parts, const std::vector<const float*>& biases,
+                         int weight_mode, DenseW* out) {
+    const int k = parts[0]->cols;
+    int n = 0;
+    const bool q8 = parts[0]->q8_codes != nullptr;
+    for (auto* p : parts) {
+        if ((p->q8_codes != nullptr) != q8) return "mixed q8 / dense tensors inside one fused projection";
+        if (p->cols != k) return "fused projection parts disagree on the input width";
+        n += p->rows;
+    }
+    if (k % 16 != 0) return "dense input width must be a multiple of 16 (16-byte aligned rows of 8-bit codes)";
+    out->n = n;
+    out->k = k;
+    out->ldw = k;
+    out->int8 = q8 && weight_mode == EOS_B200_WEIGHTS_Q8_SMEM_DEQUANT;
+    std::vector<float> scale;
+    std::vector<float> bias((size_t)n, 0.0f);
+    bool any_bias = false;
+    size_t row0 = 0;
+    if (q8) scale.resize((size_t)n);
+    std::vector<uint8_t> codes8;
+    std::vector<__half> w16;
+    if (out->int8) codes8.resize((size_t)n * k);
+    else w16.resize((size_t)n * k);
+    for (size_t pi = 0; pi < parts.size(); ++pi) {
+        const EosB200Matrix* p = parts[pi];
+        const size_t cnt = (size_t)p->rows * k;
+        if (q8) {
+            for (int r = 0; r < p->rows; ++r) scale[row0 + r] = p->q8_scales[p->n_scales == 1 ? 0 : r];
+            if (out->int8) {
+                for (size_t i = 0; i < cnt; ++i) codes8[row0 * k + i] = (uint8_t)((int)p->q8_codes[i] + 128);
+            } else {
+                for (size_t i = 0; i < cnt; ++i) w16[row0 * k + i] = __float2half_rn((float)p->q8_codes[i]);
+            }
+        } else {
+            for (size_t i = 0; i < cnt; ++i) w16[row0 * k + i] = __float2half_rn(p->dense[i]);
+        }
+        if (biases[pi] != nullptr) {
+            any_bias = true;
+            for (int r = 0; r < p->rows; ++r) bias[row0 + r] = biases[pi][r];
+        }
+        row0 += p->rows;
+    }
+    cudaError_t e;
+    if (out->int8) {
+        e = cudaMalloc(&out->w, codes8.size());
+        if (e == cudaSuccess) e = cudaMemcpy(out->w, codes8.data(), codes8.size(), cudaMemcpyHostToDevice);
+    } else {
+        e = cudaMalloc(&out->w, w16.size() * sizeof(__half));
+        if (e == cudaSuccess) e = cudaMemcpy(out->w, w16.data(), w16.size() * sizeof(__half), cudaMemcpyHostToDevice);
+    }
+    if (e == cudaSuccess && q8) {
+        e = dev_alloc(&out->scale, (size_t)n);
+        if (e == cudaSuccess) e = cudaMemcpy(out->scale, scale.data(), (size_t)n * 4, cudaMemcpyHostToDevice);
+    }
+    if (e == cudaSuccess && any_bias) {
+        e = dev_alloc(&out->bias, (size_t)n);
+        if (e == cudaSuccess) e = cudaMemcpy(out->bias, bias.data(), (size_t)n * 4, cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return std::string("weight upload: ") + cudaGetErrorString(e);
+    }
+    return "";
+}
+
+std::string upload_f32(const float* src, size_t n, float** dst) {
+    cudaError_t e = dev_alloc(dst, n);
+    if (e == cudaSuccess) e = cudaMemcpy(*dst, src, n * 4, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return std::string("vector upload: ") + cudaGetErrorString(e);
+    }
+    return "";
+}
+
+std::string upload_f16(const float* src, size_t n, __half** dst) {
+    std::vector<__half> h = to_half(src, n);
+    cudaError_t e = dev_alloc(dst, n);
+    if (e == cudaSuccess) e = cudaMemcpy(*dst, h.data(), n * sizeof(__half), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return std::string("table upload: ") + cudaGetErrorString(e);
+    }
+    return "";
+}
+
+struct LayerW {
+    DenseW qkv, ao, inter, out;
+    float *g1 = nullptr, *b1 = nullptr, *g2 = nullptr, *b2 = nullptr;
+};
+
+}  // namespace
+
+struct EosB200Encoder {
+    EosB200Runtime* rt = nullptr;
+    int layers = 0, hidden = 0, heads = 0, inter = 0, vocab = 0, max_pos = 0, type_vocab = 0;
+    int activation = 0, pooling = 0, window = 0, head_out = 0;
+    float eps = 1e-12f;
+    __half *tok = nullptr, *pos = nullptr, *typ = nullptr;
+    float *eg = nullptr, *eb = nullptr, *head_w = nullptr;
+    std::vector<LayerW> lw;
+    // workspace
+    int cap_batch = 0;
+    long long cap_elems = 0;
+    int m_alloc = 0;
+    int32_t *d_ids = nullptr, *d_mask = nullptr, *d_types = nullptr;
+    SeqLayout lay{};
+    __half *h0 = nullptr, *h1 = nullptr, *qkv = nullptr, *ctx = nullptr, *pre = nullptr, *ffn = nullptr;
+    float *pooled = nullptr, *d_out = nullptr;
+    std::vector<GemmPlan> plans;  // 4 per layer: qkv, attn-out, inter, out
+};
+
+namespace {
+
+void free_workspace(EosB200Encoder* e) {
+    dev_free(e->d_ids);
+    dev_free(e->d_mask);
+    dev_free(e->d_types);
+    dev_free(e->lay.key_count);
+    dev_free(e->lay.row_count);
+    dev_free(e->lay.cu_rows);
+    dev_free(e->lay.cls_row);
+    dev_free(e->lay.row_src);
+    dev_free(e->lay.total_rows);
+    dev_free(e->h0);
+    dev_free(e->h1);
+    dev_free(e->qkv);
+    dev_free(e->ctx);
+    dev_free(e->pre);
+    dev_free(e->ffn);
+    dev_free(e->pooled);
+    dev_free(e->d_out);
+    e->plans.clear();
+    e->cap_batch = 0;
+    e->cap_elems = 0;
+    e->m_alloc = 0;
+}
+
+int ensure_workspace(EosB200Encoder* e, int batch, int tokens, char** err) {
+    const long long elems = (long long)batch * tokens;
+    if (batch <= e->cap_batch && elems <= e->cap_elems) return EOS_B200_OK;
+    const int nb = batch > e->cap_batch ? batch : e->cap_batch;
+    const long long ne = elems > e->cap_elems ? elems : e->cap_elems;
+    if (ne + nb > 0x7fffffffLL / 4) return fail(err, "encoder: batch*tokens too large for 32-bit row indexing");
+    free_workspace(e);
+    const int m = (int)(ne + nb);
+    const int D = e->hidden, F = e->inter;
+    const int E = e->head_out > 0 ? e->head_out : D;
+    CUDA_TRY(dev_alloc(&e->d_ids, (size_t)ne));
+    CUDA_TRY(dev_alloc(&e->d_mask, (size_t)ne));
+    CUDA_TRY(dev_alloc(&e->d_types, (size_t)ne));
+    CUDA_TRY(dev_alloc(&e->lay.key_count, (size_t)nb));
+    CUDA_TRY(dev_alloc(&e->lay.row_count, (size_t)nb));
+    CUDA_TRY(dev_alloc(&e->lay.cu_rows, (size_t)nb + 1));
+    CUDA_TRY(dev_alloc(&e->lay.cls_row, (size_t)nb));
+    CUDA_TRY(dev_alloc(&e->lay.row_src, (size_t)m));
+    CUDA_TRY(dev_alloc(&e->lay.total_rows, 1));
+    CUDA_TRY(dev_alloc(&e->h0, (size_t)m * D));
+    CUDA_TRY(dev_alloc(&e->h1, (size_t)m * D));
+    CUDA_TRY(dev_alloc(&e->qkv, (size_t)m * 3 * D));
+    CUDA_TRY(dev_alloc(&e->ctx, (size_t)m * D));
+    CUDA_TRY(dev_alloc(&e->pre, (size_t)m * D));
+    CUDA_TRY(dev_alloc(&e->ffn, (size_t)m * F));
+    CUDA_TRY(dev_alloc(&e->pooled, (size_t)nb * D));
+    CUDA_TRY(dev_alloc(&e->d_out, (size_t)nb * E));
+    // activations start as zeros so that rows no kernel writes are finite
+    CUDA_TRY(cudaMemset(e->qkv, 0, (size_t)m * 3 * D * sizeof(__half)));
+    CUDA_TRY(cudaMemset(e->ctx, 0, (size_t)m * D * sizeof(__half)));
+    CUDA_TRY(cudaMemset(e->h0, 0, (size_t)m * D * sizeof(__half)));
+    CUDA_TRY(cudaMemset(e->h1, 0, (size_t)m * D * sizeof(__half)));
+    CUDA_TRY(cudaMemset(e->ffn, 0, (size_t)m * F * sizeof(__half)));
+    e->cap_batch = nb;
+    e->cap_elems = ne;
+    e->m_alloc = m;
+    e->plans.resize((size_t)e->layers * 4);
+    const int act_mode = e->activation == EOS_B200_ACT_GELU_TANH ? kEpiBiasGeluTanh : kEpiBiasGeluErf;
+    for (int l = 0; l < e->layers; ++l) {
+        LayerW& w = e->lw[l];
+        struct Spec {
+            DenseW* d;
+            const __half* a;
+            int lda;
+            __half* out;
+            int ldo;
+            int mode;
+            const __half* res;
+        } specs[4] = {
+            {&w.qkv, e->h0, D, e->qkv, 3 * D, kEpiBias, nullptr},
+            {&w.ao, e->ctx, D, e->pre, D, kEpiBiasResidual, e->h0},
+            {&w.inter, e->h1, D, e->ffn, F, act_mode, nullptr},
+            {&w.out, e->ffn, F, e->pre, D, kEpiBiasResidual, e->h1},
+        };
+        for (int i = 0; i < 4; ++i) {
+            GemmParams p{};
+            p.m_ptr = e->lay.total_rows;
+            p.m_alloc = m;
+            p.n = specs[i].d->n;
+            p.k = specs[i].d->k;
+            p.scale = specs[i].d->scale;
+            p.bias = specs[i].d->bias;
+            p.residual = specs[i].res;
+            p.ldr = D;
+            p.out = specs[i].out;
+            p.ldo = specs[i].ldo;
+            p.mode = specs[i].mode;
+            p.status = e->rt->d_status;
+            std::string ge = gemm_make_plan(&e->plans[(size_t)l * 4 + i], specs[i].a, specs[i].lda, specs[i].d->w,
+                                            specs[i].d->ldw, specs[i].d->int8, p, e->rt->sm_count);
+            if (!ge.empty()) return fail(err, "encoder layer " + std::to_string(l) + ": " + ge);
+        }
+    }
+    return EOS_B200_OK;
+}
+
+// Enqueues the whole forward on `s`; returns the number of kernels launched.
+int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_mask, const int32_t* d_types, int batch,
+                    int tokens, float* d_out, cudaStream_t s) {
+    EosB200Runtime* rt = e->rt;
+    const int D = e->hidden;
+    const int cls = e->pooling == EOS_B200_POOL_CLS ? 1 : 0;
+    int launches = 0;
+    launch_seq_layout(d_mask, batch, tokens, cls, e->lay, s);
+    launches += 3;
+    launch_embed_ln(d_ids, d_types, e->lay, tokens, e->tok, e->vocab, e->pos, e->max_pos, e->typ, e->type_vocab, e->eg,
+                    e->eb, e->eps, D, e->m_alloc, e->h0, rt->d_status, rt->sm_count, s);
+    launches += 1;
+    for (int l = 0; l < e->layers; ++l) {
+        LayerW& w = e->lw[l];
+        gemm_launch(e->plans[(size_t)l * 4 + 0], s);
+        launch_attention(e->qkv, e->lay, batch, tokens, D, e->heads, e->window, e->ctx, s);
+        gemm_launch(e->plans[(size_t)l * 4 + 1], s);
+        launch_layernorm(e->pre, w.g1, w.b1, e->eps, D, e->m_alloc, e->lay.total_rows, e->h1, rt->sm_count, s);
+        gemm_launch(e->plans[(size_t)l * 4 + 2], s);
+        gemm_launch(e->plans[(size_t)l * 4 + 3], s);
+        launch_layernorm(e->pre, w.g2, w.b2, e->eps, D, e->m_alloc, e->lay.total_rows, e->h0, rt->sm_count, s);
+        launches += 7;
+    }
+    launch_pool_head(e->h0, e->lay, batch, D, cls, e->head_w, e->head_out, e->pooled, d_out, s);
+    launches += e->head_w != nullptr ? 2 : 1;
+    return launches;
+}
+
+}  // namespace
+
+extern "C" {
+
+void eos_b200_encoder_destroy(EosB200Encoder* enc) {
+    if (enc == nullptr) return;
+    cudaSetDevice(enc->rt->device);
+    cudaStreamSynchronize(enc->rt->stream);
+    free_workspace(enc);
+    dev_free(enc->tok);
+    dev_free(enc->pos);
+    dev_free(enc->typ);
+    dev_free(enc->eg);
+    dev_free(enc->eb);
+    dev_free(enc->head_w);
+    for (auto& w : enc->lw) {
+        free_dense(w.qkv);
+        free_dense(w.ao);
+        free_dense(w.inter);
+        free_dense(w.out);
+        dev_free(w.g1);
+        dev_free(w.b1);
+        dev_free(w.g2);
+        dev_free(w.b2);
+    }
+    delete enc;
+}
+
+int eos_b200_encoder_bind(EosB200Runtime* rt, const EosB200EncoderDesc* d, EosB200Encoder** out, char** err) {
+    if (rt == nullptr || d == nullptr || out == nullptr) return fail(err, "encoder_bind: null argument");
+    *out = nullptr;
+    if (d->layers <= 0) return fail(err, "bert_embedder num_hidden_layers must be positive");
+    if (d->heads <= 0) return fail(err, "bert_encoder_layer num_attention_heads must be positive");
+    if (d->hidden <= 0 || d->intermediate <= 0 || d->vocab <= 0 || d->max_positions <= 0 || d->type_vocab <= 0)
+        return fail(err, "encoder_bind: dimensions must be positive");
+    if (d->hidden % d->heads != 0) return fail(err, "hidden size must be divisible by num_attention_heads");
+    if (d->hidden % 16 != 0 || d->intermediate % 16 != 0)
+        return fail(err, "hidden and intermediate sizes must be multiples of 16");
+    const int hd = d->hidden / d->heads;
+    if (hd > 64 || hd % 2 != 0) return fail(err, "head dimension must be even and at most 64");
+    if (d->hidden > 2048) return fail(err, "hidden size above 2048 is not supported");
+    if (d->epsilon < 0) return fail(err, "epsilon must be non-negative");
+    if (d->activation != EOS_B200_ACT_GELU_ERF && d->activation != EOS_B200_ACT_GELU_TANH)
+        return fail(err, "unsupported hidden_act; only gelu (erf) and gelu_tanh are supported");
+    if (d->pooling != EOS_B200_POOL_MASKED_MEAN && d->pooling != EOS_B200_POOL_CLS)
+        return fail(err, "unsupported pooling; supported values are masked_mean and cls");
+    if (!d->token_embeddings || !d->position_embeddings || !d->type_embeddings || !d->embedding_ln_gamma ||
+        !d->embedding_ln_beta || !d->layer)
+        return fail(err, "encoder_bind: missing tensor");
+    if (d->head_out < 0 || (d->head_out > 0 && d->head_weights == nullptr))
+        return fail(err, "encoder_bind: projection head without weights");
+    CUDA_TRY(cudaSetDevice(rt->device));
+    EosB200Encoder* e = new EosB200Encoder();
+    e->rt = rt;
+    e->layers = d->layers;
+    e->hidden = d->hidden;
+    e->heads = d->heads;
+    e->inter = d->intermediate;
+    e->vocab = d->vocab;
+    e->max_pos = d->max_positions;
+    e->type_vocab = d->type_vocab;
+    e->activation = d->activation;
+    e->pooling = d->pooling;
+    e->window = d->attention_window;
+    e->head_out = d->head_out;
+    e->eps = (float)d->epsilon;
+    const int D = d->hidden, F = d->intermediate;
+    std::string msg;
+    auto step = [&](const std::string& m) {
+        if (msg.empty() && !m.empty()) msg = m;
+    };
+    step(upload_f16(d->token_embeddings, (size_t)d->vocab * D, &e->tok));
+    step(upload_f16(d->position_embeddings, (size_t)d->max_positions * D, &e->pos));
+    step(upload_f16(d->type_embeddings, (size_t)d->type_vocab * D, &e->typ));
+    step(upload_f32(d->embedding_ln_gamma, D, &e->eg));
+    step(upload_f32(d->embedding_ln_beta, D, &e->eb));
+    if (d->head_out > 0) step(upload_f32(d->head_weights, (size_t)D * d->head_out, &e->head_w));
+    e->lw.resize(d->layers);
+    for (int l = 0; l < d->layers && msg.empty(); ++l) {
+        const EosB200EncoderLayer& s = d->layer[l];
+        const std::string pre = "encoder layer " + std::to_string(l) + " ";
+        step(check_matrix(s.query, D, D, "attention query"));
+        step(check_matrix(s.key, D, D, "attention key"));
+        step(check_matrix(s.value, D, D, "attention value"));
+        step(check_matrix(s.attn_out, D, D, "attention output"));
+        step(check_matrix(s.inter, F, D, "intermediate"));
+        step(check_matrix(s.out, D, F, "output"));
+        if (!s.attn_ln_gamma || !s.attn_ln_beta || !s.out_ln_gamma || !s.out_ln_beta) step("missing LayerNorm tensor");
+        if (!s.query_bias || !s.key_bias || !s.value_bias || !s.attn_out_bias || !s.inter_bias || !s.out_bias)
+            step("dense expects non-nil weight and bias");
+        if (!msg.empty()) {
+            msg = pre + msg;
+            break;
+        }
+        LayerW& w = e->lw[l];
+        step(upload_dense({&s.query, &s.key, &s.value}, {s.query_bias, s.key_bias, s.value_bias}, d->weight_mode,
+                          &w.qkv));
+        step(upload_dense({&s.attn_out}, {s.attn_out_bias}, d->weight_mode, &w.ao));
+        step(upload_dense({&s.inter}, {s.inter_bias}, d->weight_mode, &w.inter));
+        step(upload_dense({&s.out}, {s.out_bias}, d->weight_mode, &w.out));
+        step(upload_f32(s.attn_ln_gamma, D, &w.g1));
+        step(upload_f32(s.attn_ln_beta, D, &w.b1));
+        step(upload_f32(s.out_ln_gamma, D, &w.g2));
+        step(upload_f32(s.out_ln_beta, D, &w.b2));
+        if (!msg.empty()) msg = pre + msg;
+    }
+    if (!msg.empty()) {
+        eos_b200_encoder_destroy(e);
+        return fail(err, msg);
+    }
+    *out = e;
+    return EOS_B200_OK;
+}
+
+int eos_b200_encoder_reserve(EosB200Encoder* enc, int batch, int tokens, char** err) {
+    if (enc == nullptr) return fail(err, "encoder_reserve: null encoder");
+    if (batch <= 0 || tokens <= 0) return fail(err, "encoder_reserve: batch and tokens must be positive");
+    CUDA_TRY(cudaSetDevice(enc->rt->device));
+    return ensure_workspace(enc, batch, tokens, err);
+}
+
+int eos_b200_encoder_run_device(EosB200Encoder* enc, const int32_t* d_ids, const int32_t* d_mask,
+                                const int32_t* d_types, int batch, int tokens, float* d_out, void* stream,
+                                EosB200Stats* stats, char** err) {
+    if (enc == nullptr || d_ids == nullptr || d_mask == nullptr || d_out == nullptr)
+        return fail(err, "bert_embedder expects non-nil input_ids, attention_mask and output");
+    if (batch <= 0 || tokens <= 0) return fail(err, "bert_embedder input_ids must be a non-empty [B,T] tensor");
+    if (tokens > enc->max_pos) return fail(err, "bert_embeddings position_ids value out of range (tokens > max_positions)");
+    CUDA_TRY(cudaSetDevice(enc->rt->device));
+    int rc = ensure_workspace(enc, batch, tokens, err);
+    if (rc != EOS_B200_OK) return rc;
+    cudaStream_t s = pick_stream(enc->rt, stream);
+    CUDA_TRY(cudaMemsetAsync(enc->rt->d_status, 0, sizeof(int), s));
+    const int launches = enqueue_forward(enc, d_ids, d_mask, d_types, batch, tokens, d_out, s);
+    CUDA_TRY(cudaGetLastError());
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+    }
+    return EOS_B200_OK;
+}
+
+int eos_b200_encoder_sync(EosB200Encoder* enc, void* stream, char** err) {
+    if (enc == nullptr) return fail(err, "encoder_sync: null encoder");
+    CUDA_TRY(cudaSetDevice(enc->rt->device));
+    return read_status(enc->rt, pick_stream(enc->rt, stream), err);
+}
+
+int eos_b200_encoder_run(EosB200Encoder* enc, const int32_t* h_ids, const int32_t* h_mask, const int32_t* h_types,
+                         int batch, int tokens, float* h_out, EosB200Stats* stats, char** err) {
+    if (enc == nullptr || h_ids == nullptr || h_mask == nullptr || h_out == nullptr)
+        return fail(err, "bert_embedder expects non-nil input_ids, attention_mask and output");
+    if (batch <= 0 || tokens <= 0) return fail(err, "bert_embedder input_ids must be a non-empty [B,T] tensor");
+    if (tokens > enc->max_pos) return fail(err, "bert_embeddings position_ids value out of range (tokens > max_positions)");
+    EosB200Runtime* rt = enc->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    int rc = ensure_workspace(enc, batch, tokens, err);
+    if (rc != EOS_B200_OK) return rc;
+    cudaStream_t s = rt->stream;
+    const size_t n = (size_t)batch * tokens;
+    const int E = enc->head_out > 0 ? enc->head_out : enc->hidden;
+    CUDA_TRY(cudaEventRecord(rt->ev0, s));
+    CUDA_TRY(cudaMemsetAsync(rt->d_status, 0, sizeof(int), s));
+    CUDA_TRY(cudaMemcpyAsync(enc->d_ids, h_ids, n * 4, cudaMemcpyHostToDevice, s));
+    CUDA_TRY(cudaMemcpyAsync(enc->d_mask, h_mask, n * 4, cudaMemcpyHostToDevice, s));
+    if (h_types != nullptr) CUDA_TRY(cudaMemcpyAsync(enc->d_types, h_types, n * 4, cudaMemcpyHostToDevice, s));
+    const int launches =
+        enqueue_forward(enc, enc->d_ids, enc->d_mask, h_types != nullptr ? enc->d_types : nullptr, batch, tokens,
+                        enc->d_out, s);
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaMemcpyAsync(h_out, enc->d_out, (size_t)batch * E * 4, cudaMemcpyDeviceToHost, s));
+    int rows = 0;
+    CUDA_TRY(cudaMemcpyAsync(&rows, enc->lay.total_rows, 4, cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaEventRecord(rt->ev1, s));
+    rc = read_status(rt, s, err);
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+        stats->uploaded_bytes = (int64_t)n * 4 * (h_types != nullptr ? 3 : 2);
+        stats->downloaded_bytes = (int64_t)batch * E * 4 + 8;
+        stats->valid_tokens = rows;
+        cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+    }
+    return rc;
+}
+
+int eos_b200_linear(EosB200Runtime* rt, const float* h_x, int64_t rows, const EosB200Matrix* w, const float* h_bias,
+                    int epilogue, const float* h_residual, int weight_mode, float* h_y, EosB200Stats* stats,
+                    char** err) {
+    if (rt == nullptr || h_x == nullptr || w == nullptr || h_y == nullptr) return fail(err, "linear: null argument");
+    if (rows <= 0 || rows > 0x7fffffff / 2) return fail(err, "linear: rows must be positive and fit 31 bits");
+    if (epilogue < 0 || epilogue > 3) return fail(err, "linear: unknown epilogue");
+    if (epilogue == kEpiBiasResidual && h_residual == nullptr) return fail(err, "linear: residual epilogue without residual");
+    std::string cm = check_matrix(*w, w->rows, w->cols, "linear");
+    if (!cm.empty()) return fail(err, cm);
+    CUDA_TRY(cudaSetDevice(rt->device));
+    const int n = w->rows, k = w->cols;
+    const int ldo = (n + 7) / 8 * 8;
+    DenseW dw;
+    std::string ue = upload_dense({w}, {h_bias}, weight_mode, &dw);
+    if (!ue.empty()) {
+        free_dense(dw);
+        return fail(err, ue);
+    }
+    __half *d_x = nullptr, *d_y = nullptr, *d_r = nullptr;
+    int rc = EOS_B200_OK;
+    std::string msg;
+    do {
+        std::vector<__half> hx = to_half(h_x, (size_t)rows * k);
+        if (dev_alloc(&d_x, (size_t)rows * k) != cudaSuccess || dev_alloc(&d_y, (size_t)rows * ldo) != cudaSuccess) {
+            msg = "linear: device allocation failed";
+            break;
+        }
+        cudaMemcpyAsync(d_x, hx.data(), hx.size() * 2, cudaMemcpyHostToDevice, rt->stream);
+        if (h_residual != nullptr) {
+            std::vector<__half> hr((size_t)rows * ldo, __float2half_rn(0.f));
+            for (int64_t r = 0; r < rows; ++r)
+                for (int c = 0; c < n; ++c) hr[(size_t)r * ldo + c] = __float2half_rn(h_residual[(size_t)r * n + c]);
+            if (dev_alloc(&d_r, (size_t)rows * ldo) != cudaSuccess) {
+                msg = "linear: device allocation failed";
+                break;
+            }
+            cudaMemcpy(d_r, hr.data(), hr.size() * 2, cudaMemcpyHostToDevice);
+        }
+        GemmParams p{};
+        p.m_ptr = nullptr;
+        p.m_alloc = (int)rows;
+        p.n = n;
+        p.k = k;
+        p.scale = dw.scale;
+        p.bias = dw.bias;
+        p.residual = d_r;
+        p.ldr = ldo;
+        p.out = d_y;
+        p.ldo = ldo;
+        p.mode = epilogue;
+        p.status = rt->d_status;
+        GemmPlan plan;
+        msg = gemm_make_plan(&plan, d_x, k, dw.w, dw.ldw, dw.int8, p, rt->sm_count);
+        if (!msg.empty()) break;
+        cudaMemsetAsync(rt->d_status, 0, sizeof(int), rt->stream);
+        cudaEventRecord(rt->ev0, rt->stream);
+        gemm_launch(plan, rt->stream);
+        cudaEventRecord(rt->ev1, rt->stream);
+        cudaError_t le = cudaGetLastError();
+        if (le != cudaSuccess) {
+            msg = std::string("linear launch: ") + cudaGetErrorString(le);
+            break;
+        }
+        std::vector<__half> hy((size_t)rows * ldo);
+        cudaError_t ce = cudaMemcpyAsync(hy.data(), d_y, hy.size() * 2, cudaMemcpyDeviceToHost, rt->stream);
+        if (ce != cudaSuccess) {
+            msg = std::string("linear download: ") + cudaGetErrorString(ce);
+            break;
+        }
+        rc = read_status(rt, rt->stream, err);
+        if (rc != EOS_B200_OK) break;
+        for (int64_t r = 0; r < rows; ++r)
+            for (int c = 0; c < n; ++c) h_y[(size_t)r * n + c] = __half2float(hy[(size_t)r * ldo + c]);
+        if (stats != nullptr) {
+            std::memset(stats, 0, sizeof(*stats));
+            stats->kernel_launches = 1;
+            stats->uploaded_bytes = (int64_t)rows * k * 2;
+            stats->downloaded_bytes = (int64_t)rows * ldo * 2;
+            cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+        }
+    } while (false);
+    cudaStreamSynchronize(rt->stream);
+    dev_free(d_x);
+    dev_free(d_y);
+    dev_free(d_r);
+    free_dense(dw);
+    if (!msg.empty()) return fail(err, msg);
+    return rc;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// compiled pipeline
+// ------------------------------------------------------------------------------------------------
+struct EosB200EmbedPooled {
+    EosB200Runtime* rt = nullptr;
+    int vocab = 0, dim = 0, out_dim = 0;
+    __half *table = nullptr, *proj = nullptr;
+    int32_t *d_tokens = nullptr, *d_mask = nullptr;
+    float* d_out = nullptr;
+    long long cap_elems = 0;
+    int cap_batch = 0;
+};
+
+extern "C" {
+
+void eos_b200_embed_pooled_destroy(EosB200EmbedPooled* ep) {
+    if (ep == nullptr) return;
+    cudaSetDevice(ep->rt->device);
+    cudaStreamSynchronize(ep->rt->stream);
+    dev_free(ep->table);
+    dev_free(ep->proj);
+    dev_free(ep->d_tokens);
+    dev_free(ep->d_mask);
+    dev_free(ep->d_out);
+    delete ep;
+}
+
+int eos_b200_embed_pooled_bind(EosB200Runtime* rt, const float* h_table, int vocab, int dim,
+                               const float* h_projection, int out_dim, EosB200EmbedPooled** out, char** err) {
+    if (rt == nullptr || h_table == nullptr || h_projection == nullptr || out == nullptr)
+        return fail(err, "embed_pooled_bind: null argument");
+    *out = nullptr;
+    if (vocab <= 0 || dim <= 0 || out_dim <= 0) return fail(err, "embed_pooled_bind: dimensions must be positive");
+    if (out_dim > 1024) return fail(err, "embed_pooled_bind: out_dim above 1024 is not supported");
+    if (dim > 1536) return fail(err, "embed_pooled_bind: dim above 1536 is not supported");
+    CUDA_TRY(cudaSetDevice(rt->device));
+    EosB200EmbedPooled* ep = new EosB200EmbedPooled();
+    ep->rt = rt;
+    ep->vocab = vocab;
+    ep->dim = dim;
+    ep->out_dim = out_dim;
+    std::string msg = upload_f16(h_table, (size_t)vocab * dim, &ep->table);
+    if (msg.empty()) msg = upload_f16(h_projection, (size_t)dim * out_dim, &ep->proj);
+    if (!msg.empty()) {
+        eos_b200_embed_pooled_destroy(ep);
+        return fail(err, msg);
+    }
+    *out = ep;
+    return EOS_B200_OK;
+}
+
+int eos_b200_embed_pooled_run(EosB200EmbedPooled* ep, const int32_t* h_tokens, const int32_t* h_mask, int batch,
+                              int tokens, int pool_then_l2, float* h_out, EosB200Stats* stats, char** err) {
+    if (ep == nullptr || h_tokens == nullptr || h_mask == nullptr || h_out == nullptr)
+        return fail(err, "embed_pooled_run: null argument");
+    if (batch <= 0 || tokens <= 0) return fail(err, "embed_pooled_run: empty token batch");
+    EosB200Runtime* rt = ep->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    const long long n = (long long)batch * tokens;
+    if (n > ep->cap_elems || batch > ep->cap_batch) {
+        dev_free(ep->d_tokens);
+        dev_free(ep->d_mask);
+        dev_free(ep->d_out);
+        CUDA_TRY(dev_alloc(&ep->d_tokens, (size_t)n));
+        CUDA_TRY(dev_alloc(&ep->d_mask, (size_t)n));
+        CUDA_TRY(dev_alloc(&ep->d_out, (size_t)batch * ep->out_dim));
+        ep->cap_elems = n;
+        ep->cap_batch = batch;
+    }
+    cudaStream_t s = rt->stream;
+    CUDA_TRY(cudaEventRecord(rt->ev0, s));
+    CUDA_TRY(cudaMemsetAsync(rt->d_status, 0, sizeof(int), s));
+    CUDA_TRY(cudaMemcpyAsync(ep->d_tokens, h_tokens, (size_t)n * 4, cudaMemcpyHostToDevice, s));
+    CUDA_TRY(cudaMemcpyAsync(ep->d_mask, h_mask, (size_t)n * 4, cudaMemcpyHostToDevice, s));
+    launch_embed_pooled(ep->d_tokens, ep->d_mask, batch, tokens, ep->table, ep->vocab, ep->dim, ep->proj, ep->out_dim,
+                        pool_then_l2 ? 1 : 0, ep->d_out, rt->d_status, s);
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaMemcpyAsync(h_out, ep->d_out, (size_t)batch * ep->out_dim * 4, cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaEventRecord(rt->ev1, s));
+    int rc = read_status(rt, s, err);
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = 1;
+        stats->uploaded_bytes = n * 8;
+        stats->downloaded_bytes = (int64_t)batch * ep->out_dim * 4;
+        cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+    }
+    return rc;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// TurboQuant
+// ------------------------------------------------------------------------------------------------
+struct EosB200Quantizer {
+    EosB200Runtime* rt = nullptr;
+    int dim = 0, bits = 0;
+    int* perm = nullptr;
+    float *signs1 = nullptr, *signs2 = nullptr, *centroids = nullptr, *boundaries = nullptr;
+    uint32_t mag_hi[2] = {0, 0}, mag_lo[2] = {0, 0};
+    TqSpec spec() const { return TqSpec{dim, bits, perm, signs1, signs2, centroids, boundaries}; }
+};
+
+struct EosB200Corpus {
+    EosB200Quantizer* qz = nullptr;
+    int64_t n = 0, id_base = 0;
+    uint8_t* tiles = nullptr;
+    float* norms = nullptr;
+    // scoring workspace
+    int cap_queries = 0;       // padded query capacity
+    float* d_queries = nullptr;
+    uint2* bfrag = nullptr;
+    uint64_t* cand = nullptr;  // [group][grid][kTqMaxK]
+    int* cand_count = nullptr;
+    int64_t* d_ids = nullptr;
+    float* d_scores = nullptr;
+    int grid = 0;
+};
+
+namespace {
+constexpr int kTqGroupQueries = 256;  // queries whose per-CTA candidates are held before one merge launch
+
+__global__ void synth_gaussian_kernel(unsigned long long seed, long long row_offset, long long n, int dim, int normalize,
+                                      float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n; r += warps) {
+        const unsigned long long rowkey = seed * 0x9E3779B97F4A7C15ull + (unsigned long long)(row_offset + r);
+        float sq = 0.f;
+        for (int pass = 0; pass < (normalize ? 2 : 1); ++pass) {
+            float inv = 1.0f;
+            if (pass == 1) {
+                float tot = sq;
+                for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+                inv = tot > 0.f ? rsqrtf(tot) : 1.0f;
+            }
+            for (int p = lane; p < (dim + 1) / 2; p += 32) {
+                unsigned long long z = rowkey * 0xD1342543DE82EF95ull + (unsigned long long)p * 0x9E3779B97F4A7C15ull;
+                z ^= z >> 30;
+                z *= 0xBF58476D1CE4E5B9ull;
+                z ^= z >> 27;
+                z *= 0x94D049BB133111EBull;
+                z ^= z >> 31;
+                const float u1 = ((float)(unsigned)(z >> 40) + 0.5f) * (1.0f / 16777216.0f);
+                const float u2 = ((float)(unsigned)((z >> 8) & 0xffffffu) + 0.5f) * (1.0f / 16777216.0f);
+                const float rad = sqrtf(-2.0f * logf(u1));
+                float s, c;
+                sincosf(6.283185307179586f * u2, &s, &c);
+                const float a = rad * c, b = rad * s;
+                if (normalize && pass == 0) {
+                    sq += a * a;
+                    if (2 * p + 1 < dim) sq += b * b;
+                } else {
+                    out[r * dim + 2 * p] = a * inv;
+                    if (2 * p + 1 < dim) out[r * dim + 2 * p + 1] = b * inv;
+                }
+            }
+        }
+    }
+}
+
+int corpus_finish_bind(EosB200Quantizer* qz, const uint8_t* d_codes, const float* d_norms, int64_t n, int64_t id_base,
+                       EosB200Corpus** out, char** err) {
+    EosB200Corpus* c = new EosB200Corpus();
+    c->qz = qz;
+    c->n = n;
+    c->id_base = id_base;
+    const int64_t n_tiles = (n + kTqDocsPerTile - 1) / kTqDocsPerTile;
+    const size_t tile_bytes = tq_tile_bytes(qz->dim);
+    cudaError_t e = dev_alloc(&c->tiles, (size_t)(n_tiles > 0 ? n_tiles : 1) * tile_bytes);
+    if (e == cudaSuccess) e = dev_alloc(&c->norms, (size_t)(n > 0 ? n : 1));
+    if (e == cudaSuccess && n > 0) {
+        e = cudaMemcpyAsync(c->norms, d_norms, (size_t)n * 4, cudaMemcpyDeviceToDevice, qz->rt->stream);
+        launch_tq_transcode(d_codes, n, qz->dim, qz->bits, c->tiles, qz->rt->stream);
+        if (e == cudaSuccess) e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaStreamSynchronize(qz->rt->stream);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        std::string msg = std::string("corpus_bind: ") + cudaGetErrorString(e);
+        eos_b200_corpus_destroy(c);
+        return fail(err, msg);
+    }
+    int64_t tiles_per_cta = (n_tiles + kTqScanWarps - 1) / kTqScanWarps;
+    c->grid = (int)(tiles_per_cta < qz->rt->sm_count ? (tiles_per_cta > 0 ? tiles_per_cta : 1) : qz->rt->sm_count);
+    *out = c;
+    return EOS_B200_OK;
+}
+
+int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
+    const int q_pad = (q_count + 31) / 32 * 32;
+    if (q_pad <= c->cap_queries) return EOS_B200_OK;
+    dev_free(c->d_queries);
+    dev_free(c->bfrag);
+    dev_free(c->cand);
+    dev_free(c->cand_count);
+    dev_free(c->d_ids);
+    dev_free(c->d_scores);
+    c->cap_queries = 0;
+    const int ksteps = tq_ksteps(c->qz->dim);
+    CUDA_TRY(dev_alloc(&c->d_queries, (size_t)q_pad * c->qz->dim));
+    CUDA_TRY(dev_alloc(&c->bfrag, (size_t)(q_pad / 8) * ksteps * 32));
+    CUDA_TRY(dev_alloc(&c->cand, (size_t)kTqGroupQueries * c->grid * kTqMaxK));
+    CUDA_TRY(dev_alloc(&c->cand_count, (size_t)kTqGroupQueries * c->grid));
+    CUDA_TRY(dev_alloc(&c->d_ids, (size_t)q_pad * kTqMaxK));
+    CUDA_TRY(dev_alloc(&c->d_scores, (size_t)q_pad * kTqMaxK));
+    c->cap_queries = q_pad;
+    return EOS_B200_OK;
+}
+
+// Enqueues prepare + scan passes + merges; returns launches (or -1 with *err set).
+int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, int per_pass, int64_t* d_ids,
+                  float* d_scores, uint64_t* d_keys, cudaStream_t s) {
+    EosB200Quantizer* qz = c->qz;
+    const int ksteps = tq_ksteps(qz->dim);
+    int launches = 0;
+    launch_tq_prepare(d_queries, q_count, (q_count + 31) / 32 * 32, qz->spec(), c->bfrag, nullptr, s);
+    launches++;
+    const int j = per_pass / 8;
+    for (int g0 = 0; g0 < q_count; g0 += kTqGroupQueries) {
+        const int g_queries = (q_count - g0) < kTqGroupQueries ? (q_count - g0) : kTqGroupQueries;
+        const int g_tiles = (g_queries + 7) / 8;
+        for (int t0 = 0; t0 < g_tiles; t0 += j) {
+            TqScanArgs a{};
+            a.tiles = c->tiles;
+            a.norms = c->norms;
+            a.n_docs = c->n;
+            a.id_base = (uint32_t)c->id_base;
+            a.dim = qz->dim;
+            a.bfrag = c->bfrag + (size_t)(g0 / 8 + t0) * ksteps * 32;
+            a.query_tiles = j;
+            a.k = k;
+            a.mag_hi[0] = qz->mag_hi[0];
+            a.mag_hi[1] = qz->mag_hi[1];
+            a.mag_lo[0] = qz->mag_lo[0];
+            a.mag_lo[1] = qz->mag_lo[1];
+            a.cand_keys = c->cand + (size_t)t0 * 8 * c->grid * kTqMaxK;
+            a.cand_count = c->cand_count + (size_t)t0 * 8 * c->grid;
+            a.grid = c->grid;
+            a.all_scores = nullptr;
+            a.all_stride = 0;
+            launch_tq_scan(a, s);
+            launches++;
+        }
+        launch_tq_merge(c->cand, (int64_t)c->grid * kTqMaxK, kTqMaxK, c->grid, kTqMaxK, c->cand_count, g_queries, k,
+                        0, d_ids != nullptr ? d_ids + (size_t)g0 * k : nullptr,
+                        d_scores != nullptr ? d_scores + (size_t)g0 * k : nullptr,
+                        d_keys != nullptr ? d_keys + (size_t)g0 * k : nullptr, s);
+        launches++;
+    }
+    return launches;
+}
+
+std::string check_score_args(const EosB200Corpus* c, int q_count, int k, int per_pass) {
+    if (q_count <= 0) return "score_topk: no queries";
+    if (k <= 0 || k > kTqMaxK) return "score_topk: k must be in [1, 128]";
+    if (per_pass != 8 && per_pass != 16 && per_pass != 32) return "score_topk: queries_per_pass must be 8, 16 or 32";
+    if (c->n + c->id_base > 0xffffffffLL || c->id_base < 0) return "score_topk: document ids must fit 32 bits";
+    return "";
+}
+
+}  // namespace
+
+extern "C" {
+
+void eos_b200_quantizer_destroy(EosB200Quantizer* qz) {
+    if (qz == nullptr) return;
+    cudaSetDevice(qz->rt->device);
+    dev_free(qz->perm);
+    dev_free(qz->signs1);
+    dev_free(qz->signs2);
+    dev_free(qz->centroids);
+    dev_free(qz->boundaries);
+    delete qz;
+}
+
+int eos_b200_quantizer_create(EosB200Runtime* rt, int dim, int bits, const int32_t* perm, const float* signs1,
+                              const float* signs2, const float* centroids, const float* boundaries,
+                              EosB200Quantizer** out, char** err) {
+    if (rt == nullptr || perm == nullptr || signs1 == nullptr || signs2 == nullptr || centroids == nullptr ||
+        boundaries == nullptr || out == nullptr)
+        return fail(err, "quantizer_create: null argument");
+    *out = nullptr;
+    if (dim <= 0 || dim > 8192) return fail(err, "quantizer_create: dim must be in [1, 8192]");
+    if (bits != 2 && bits != 4) return fail(err, "quantizer_create: bits must be 2 or 4");
+    const int levels = 1 << bits;
+    std::vector<char> seen((size_t)dim, 0);
+    for (int i = 0; i < dim; ++i) {
+        if (perm[i] < 0 || perm[i] >= dim || seen[perm[i]]) return fail(err, "quantizer_create: perm is not a permutation");
+        seen[perm[i]] = 1;
+    }
+    for (int i = 0; i + 1 < levels; ++i)
+        if (!(centroids[i] < centroids[i + 1])) return fail(err, "quantizer_create: centroids must be ascending");
+    uint16_t mag[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int m = 0; m < levels / 2; ++m) {
+        const __half pos = __float2half_rn(centroids[levels / 2 + m]);
+        const __half neg = __float2half_rn(centroids[levels / 2 - 1 - m]);
+        const uint16_t pb = *reinterpret_cast<const uint16_t*>(&pos), nb = *reinterpret_cast<const uint16_t*>(&neg);
+        if ((pb ^ 0x8000u) != nb || (pb & 0x8000u))
+            return fail(err, "quantizer_create: the centroid table must be symmetric (c[L-1-i] == -c[i])");
+        mag[m] = pb;
+    }
+    CUDA_TRY(cudaSetDevice(rt->device));
+    EosB200Quantizer* qz = new EosB200Quantizer();
+    qz->rt = rt;
+    qz->dim = dim;
+    qz->bits = bits;
+    for (int m = 0; m < 8; ++m) {
+        qz->mag_hi[m / 4] |= (uint32_t)(mag[m] >> 8) << (8 * (m % 4));
+        qz->mag_lo[m / 4] |= (uint32_t)(mag[m] & 0xff) << (8 * (m % 4));
+    }
+    cudaError_t e = dev_alloc(&qz->perm, (size_t)dim);
+    if (e == cudaSuccess) e = cudaMemcpy(qz->perm, perm, (size_t)dim * 4, cudaMemcpyHostToDevice);
+    std::string msg;
+    if (e != cudaSuccess) msg = std::string("quantizer_create: ") + cudaGetErrorString(e);
+    if (msg.empty()) msg = upload_f32(signs1, dim, &qz->signs1);
+    if (msg.empty()) msg = upload_f32(signs2, dim, &qz->signs2);
+    if (msg.empty()) msg = upload_f32(centroids, levels, &qz->centroids);
+    if (msg.empty()) msg = upload_f32(boundaries, levels - 1, &qz->boundaries);
+    if (!msg.empty()) {
+        eos_b200_quantizer_destroy(qz);
+        return fail(err, msg);
+    }
+    *out = qz;
+    return EOS_B200_OK;
+}
+
+int eos_b200_quantize_device(EosB200Quantizer* qz, const float* d_x, int64_t n, uint8_t* d_codes, float* d_norms,
+                             void* stream, char** err) {
+    if (qz == nullptr || d_x == nullptr || d_codes == nullptr || d_norms == nullptr)
+        return fail(err, "quantize: null argument");
+    if (n < 0) return fail(err, "quantize: negative row count");
+    CUDA_TRY(cudaSetDevice(qz->rt->device));
+    launch_tq_pack(d_x, n, qz->spec(), d_codes, d_norms, pick_stream(qz->rt, stream));
+    CUDA_TRY(cudaGetLastError());
+    return EOS_B200_OK;
+}
+
+int eos_b200_quantize(EosB200Quantizer* qz, const float* h_x, int64_t n, uint8_t* h_codes, float* h_norms,
+                      EosB200Stats* stats, char** err) {
+    if (qz == nullptr || h_x == nullptr || h_codes == nullptr || h_norms == nullptr)
+        return fail(err, "quantize: null argument");
+    if (n <= 0) return fail(err, "quantize: no vectors");
+    EosB200Runtime* rt = qz->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    const size_t cb = ((size_t)qz->dim * qz->bits + 7) / 8;
+    float *d_x = nullptr, *d_norms = nullptr;
+    uint8_t* d_codes = nullptr;
+    cudaError_t e = dev_alloc(&d_x, (size_t)n * qz->dim);
+    if (e == cudaSuccess) e = dev_alloc(&d_codes, (size_t)n * cb);
+    if (e == cudaSuccess) e = dev_alloc(&d_norms, (size_t)n);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev0, rt->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_x, h_x, (size_t)n * qz->dim * 4, cudaMemcpyHostToDevice, rt->stream);
+    if (e == cudaSuccess) {
+        launch_tq_pack(d_x, n, qz->spec(), d_codes, d_norms, rt->stream);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_codes, d_codes, (size_t)n * cb, cudaMemcpyDeviceToHost, rt->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_norms, d_norms, (size_t)n * 4, cudaMemcpyDeviceToHost, rt->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev1, rt->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+    if (e == cudaSuccess && stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = 1;
+        stats->uploaded_bytes = (int64_t)n * qz->dim * 4;
+        stats->downloaded_bytes = (int64_t)n * (cb + 4);
+        cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+    }
+    dev_free(d_x);
+    dev_free(d_codes);
+    dev_free(d_norms);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(err, std::string("quantize: ") + cudaGetErrorString(e));
+    }
+    return EOS_B200_OK;
+}
+
+void eos_b200_corpus_destroy(EosB200Corpus* c) {
+    if (c == nullptr) return;
+    cudaSetDevice(c->qz->rt->device);
+    cudaStreamSynchronize(c->qz->rt->stream);
+    dev_free(c->tiles);
+    dev_free(c->norms);
+    dev_free(c->d_queries);
+    dev_free(c->bfrag);
+    dev_free(c->cand);
+    dev_free(c->cand_count);
+    dev_free(c->d_ids);
+    dev_free(c->d_scores);
+    delete c;
+}
+
+int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* c) {
+    if (c == nullptr) return 0;
+    return ((int64_t)c->qz->dim * c->qz->bits + 7) / 8 + 4;
+}
+
+int eos_b200_corpus_bind_device(EosB200Quantizer* qz, const uint8_t* d_codes, const float* d_norms, int64_t n,
+                                int64_t id_base, EosB200Corpus** out, char** err) {
+    if (qz == nullptr || out == nullptr || (n > 0 && (d_codes == nullptr || d_norms == nullptr)))
+        return fail(err, "corpus_bind: null argument");
+    *out = nullptr;
+    if (n < 0 || id_base < 0 || n + id_base > 0xffffffffLL) return fail(err, "corpus_bind: row ids must fit 32 bits");
+    CUDA_TRY(cudaSetDevice(qz->rt->device));
+    return corpus_finish_bind(qz, d_codes, d_norms, n, id_base, out, err);
+}
+
+int eos_b200_corpus_bind(EosB200Quantizer* qz, const uint8_t* h_codes, const float* h_norms, int64_t n,
+                         int64_t id_base, int allow_zero_norm, EosB200Corpus** out, char** err) {
+    if (qz == nullptr || out == nullptr || (n > 0 && (h_codes == nullptr || h_norms == nullptr)))
+        return fail(err, "corpus_bind: null argument");
+    *out = nullptr;
+    if (n < 0 || id_base < 0 || n + id_base > 0xffffffffLL) return fail(err, "corpus_bind: row ids must fit 32 bits");
+    for (int64_t i = 0; i < n; ++i) {
+        const float v = h_norms[i];
+        if (std::isnan(v) || std::isinf(v) || v < 0 || (v == 0 && !allow_zero_norm))
+            return fail(err, "corpus_bind: quantized vector norm must be positive and finite (row " +
+                                 std::to_string(i) + "); pass allow_zero_norm for confirmed zero vectors");
+    }
+    CUDA_TRY(cudaSetDevice(qz->rt->device));
+    const size_t cb = ((size_t)qz->dim * qz->bits + 7) / 8;
+    uint8_t* d_codes = nullptr;
+    float* d_norms = nullptr;
+    cudaError_t e = dev_alloc(&d_codes, (size_t)n * cb);
+    if (e == cudaSuccess) e = dev_alloc(&d_norms, (size_t)n);
+    if (e == cudaSuccess && n > 0) e = cudaMemcpy(d_codes, h_codes, (size_t)n * cb, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && n > 0) e = cudaMemcpy(d_norms, h_norms, (size_t)n * 4, cudaMemcpyHostToDevice);
+    int rc;
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        rc = fail(err, std::string("corpus_bind: ") + cudaGetErrorString(e));
+    } else {
+        rc = corpus_finish_bind(qz, d_codes, d_norms, n, id_base, out, err);
+    }
+    dev_free(d_codes);
+    dev_free(d_norms);
+    return rc;
+}
+
+int eos_b200_score_topk_device(EosB200Corpus* c, const float* d_queries, int q_count, int k, int per_pass,
+                               int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream, EosB200Stats* stats,
+                               char** err) {
+    if (c == nullptr || d_queries == nullptr) return fail(err, "score_topk: null argument");
+    std::string m = check_score_args(c, q_count, k, per_pass);
+    if (!m.empty()) return fail(err, m);
+    if (c->n == 0) return fail(err, "score_topk: empty corpus");
+    CUDA_TRY(cudaSetDevice(c->qz->rt->device));
+    int rc = ensure_score_workspace(c, q_count, err);
+    if (rc != EOS_B200_OK) return rc;
+    const int launches =
+        enqueue_score(c, d_queries, q_count, k, per_pass, d_ids, d_scores, d_keys, pick_stream(c->qz->rt, stream));
+    CUDA_TRY(cudaGetLastError());
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+    }
+    return EOS_B200_OK;
+}
+
+int eos_b200_score_topk(EosB200Corpus* c, const float* h_queries, int q_count, int k, int per_pass, int64_t* h_ids,
+                        float* h_scores, EosB200Stats* stats, char** err) {
+    if (c == nullptr || h_queries == nullptr || h_ids == nullptr || h_scores == nullptr)
+        return fail(err, "score_topk: null argument");
+    std::string m = check_score_args(c, q_count, k, per_pass);
+    if (!m.empty()) return fail(err, m);
+    if (c->n == 0) {  // topK > len(docs): nothing to return (runtime/retrieval_turboquant.go:1854-1860)
+        for (size_t i = 0; i < (size_t)q_count * k; ++i) {
+            h_ids[i] = -1;
+            h_scores[i] = -INFINITY;
+        }
+        if (stats != nullptr) std::memset(stats, 0, sizeof(*stats));
+        return EOS_B200_OK;
+    }
+    EosB200Runtime* rt = c->qz->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    int rc = ensure_score_workspace(c, q_count, err);
+    if (rc != EOS_B200_OK) return rc;
+    cudaStream_t s = rt->stream;
+    CUDA_TRY(cudaEventRecord(rt->ev0, s));
+    CUDA_TRY(cudaMemcpyAsync(c->d_queries, h_queries, (size_t)q_count * c->qz->dim * 4, cudaMemcpyHostToDevice, s));
+    const int launches = enqueue_score(c, c->d_queries, q_count, k, per_pass, c->d_ids, c->d_scores, nullptr, s);
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaMemcpyAsync(h_ids, c->d_ids, (size_t)q_count * k * 8, cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaMemcpyAsync(h_scores, c->d_scores, (size_t)q_count * k * 4, cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaEventRecord(rt->ev1, s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+        stats->uploaded_bytes = (int64_t)q_count * c->qz->dim * 4;
+        stats->downloaded_bytes = (int64_t)q_count * k * 12;
+        cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+    }
+    return EOS_B200_OK;
+}
+
+int eos_b200_topk_merge_device(EosB200Runtime* rt, const uint64_t* d_keys, int shards, int q_count, int k,
+                               int64_t* d_ids, float* d_scores, void* stream, char** err) {
+    if (rt == nullptr || d_keys == nullptr || d_ids == nullptr || d_scores == nullptr)
+        return fail(err, "topk_merge: null argument");
+    if (shards <= 0 || q_count <= 0 || k <= 0 || k > kTqMaxK) return fail(err, "topk_merge: bad sizes");
+    CUDA_TRY(cudaSetDevice(rt->device));
+    // gathered layout [shards][q_count][k]: a query's segments are q_count*k keys apart
+    launch_tq_merge(d_keys, (int64_t)k, (int64_t)q_count * k, shards, k, nullptr, q_count, k, 0, d_ids, d_scores,
+                    nullptr, pick_stream(rt, stream));
+    CUDA_TRY(cudaGetLastError());
+    return EOS_B200_OK;
+}
+
+int eos_b200_score_all(EosB200Corpus* c, const float* h_queries, int q_count, float* h_scores, char** err) {
+    if (c == nullptr || h_queries == nullptr || h_scores == nullptr) return fail(err, "score_all: null argument");
+    if (q_count <= 0 || c->n <= 0) return fail(err, "score_all: empty input");
+    EosB200Runtime* rt = c->qz->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    int rc = ensure_score_workspace(c, q_count, err);
+    if (rc != EOS_B200_OK) return rc;
+    const int q_pad = (q_count + 7) / 8 * 8;
+    float* d_all = nullptr;
+    CUDA_TRY(dev_alloc(&d_all, (size_t)q_pad * c->n));
+    cudaStream_t s = rt->stream;
+    cudaError_t e = cudaMemcpyAsync(c->d_queries, h_queries, (size_t)q_count * c->qz->dim * 4, cudaMemcpyHostToDevice, s);
+    launch_tq_prepare(c->d_queries, q_count, q_pad, c->qz->spec(), c->bfrag, nullptr, s);
+    const int ksteps = tq_ksteps(c->qz->dim);
+    for (int t = 0; t < q_pad / 8; ++t) {
+        TqScanArgs a{};
+        a.tiles = c->tiles;
+        a.norms = c->norms;
+        a.n_docs = c->n;
+        a.id_base = 0;
+        a.dim = c->qz->dim;
+        a.bfrag = c->bfrag + (size_t)t * ksteps * 32;
+        a.query_tiles = 1;
+        a.k = 1;
+        a.mag_hi[0] = c->qz->mag_hi[0];
+        a.mag_hi[1] = c->qz->mag_hi[1];
+        a.mag_lo[0] = c->qz->mag_lo[0];
+        a.mag_lo[1] = c->qz->mag_lo[1];
+        a.cand_keys = c->cand;
+        a.cand_count = c->cand_count;
+        a.grid = c->grid;
+        a.all_scores = d_all + (size_t)t * 8 * c->n;
+        a.all_stride = c->n;
+        launch_tq_scan(a, s);
+    }
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_scores, d_all, (size_t)q_count * c->n * 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    dev_free(d_all);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(err, std::string("score_all: ") + cudaGetErrorString(e));
+    }
+    return EOS_B200_OK;
+}
+
+int eos_b200_parent_topk(EosB200Corpus* c, const int32_t* h_parent_of_child, int parents, const float* h_queries,
+                         int q_count, int query_group, int top_n, double penalty, int k, int64_t* h_ids,
+                         float* h_scores, EosB200Stats* stats, char** err) {
+    if (c == nullptr || h_parent_of_child == nullptr || h_queries == nullptr || h_ids == nullptr || h_scores == nullptr)
+        return fail(err, "parent_topk: null argument");
+    if (c->n <= 0 || parents <= 0 || q_count <= 0) return fail(err, "parent_topk: empty input");
+    if (k <= 0 || k > kTqMaxK) return fail(err, "parent_topk: k must be in [1, 128]");
+    if (query_group < 1 || query_group > 32 || (query_group & (query_group - 1)) != 0)
+        return fail(err, "parent_topk: query_group must be a power of two in [1, 32]");
+    if (q_count % query_group != 0) return fail(err, "parent_topk: q_count must be a multiple of query_group");
+    if (c->n > 0x7fffffffLL) return fail(err, "parent_topk: too many child vectors");
+    EosB200Runtime* rt = c->qz->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    const int n = (int)c->n;
+    // children grouped by parent (counting sort keeps child order inside a parent)
+    std::vector<int> offsets((size_t)parents + 1, 0), order((size_t)n);
+    for (int i = 0; i < n; ++i) {
+        const int p = h_parent_of_child[i];
+        if (p < 0 || p >= parents) return fail(err, "parent_topk: parent index out of range");
+        offsets[(size_t)p + 1]++;
+    }
+    for (int p = 0; p < parents; ++p) offsets[(size_t)p + 1] += offsets[p];
+    {
+        std::vector<int> cursor(offsets.begin(), offsets.end() - 1);
+        for (int i = 0; i < n; ++i) order[(size_t)cursor[h_parent_of_child[i]]++] = i;
+    }
+    int rc = ensure_score_workspace(c, q_count, err);
+    if (rc != EOS_B200_OK) return rc;
+    const int groups = q_count / query_group;
+    int *d_order = nullptr, *d_offsets = nullptr;
+    float *d_all = nullptr, *d_agg = nullptr, *d_sc = nullptr;
+    uint64_t* d_keys = nullptr;
+    int64_t* d_ids = nullptr;
+    cudaStream_t s = rt->stream;
+    cudaError_t e = dev_alloc(&d_order, (size_t)n);
+    if (e == cudaSuccess) e = dev_alloc(&d_offsets, (size_t)parents + 1);
+    if (e == cudaSuccess) e = dev_alloc(&d_all, (size_t)32 * n);
+    if (e == cudaSuccess) e = dev_alloc(&d_agg, (size_t)query_group * parents);
+    if (e == cudaSuccess) e = dev_alloc(&d_keys, (size_t)groups * parents);
+    if (e == cudaSuccess) e = dev_alloc(&d_ids, (size_t)groups * k);
+    if (e == cudaSuccess) e = dev_alloc(&d_sc, (size_t)groups * k);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_order, order.data(), (size_t)n * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(d_offsets, offsets.data(), ((size_t)parents + 1) * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev0, s);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(c->d_queries, h_queries, (size_t)q_count * c->qz->dim * 4, cudaMemcpyHostToDevice, s);
+    int launches = 0;
+    if (e == cudaSuccess) {
+        const int q_pad = (q_count + 31) / 32 * 32;
+        launch_tq_prepare(c->d_queries, q_count, q_pad, c->qz->spec(), c->bfrag, nullptr, s);
+        launches++;
+        const int ksteps = tq_ksteps(c->qz->dim);
+        for (int r0 = 0; r0 < q_count; r0 += 32) {
+            TqScanArgs a{};
+            a.tiles = c->tiles;
+            a.norms = c->norms;
+            a.n_docs = c->n;
+            a.id_base = 0;
+            a.dim = c->qz->dim;
+            a.bfrag = c->bfrag + (size_t)(r0 / 8) * ksteps * 32;
+            a.query_tiles = 4;
+            a.k = 1;
+            a.mag_hi[0] = c->qz->mag_hi[0];
+            a.mag_hi[1] = c->qz->mag_hi[1];
+            a.mag_lo[0] = c->qz->mag_lo[0];
+            a.mag_lo[1] = c->qz->mag_lo[1];
+            a.cand_keys = c->cand;
+            a.cand_count = c->cand_count;
+            a.grid = c->grid;
+            a.all_scores = d_all;
+            a.all_stride = n;
+            launch_tq_scan(a, s);
+            launches++;
+            const int rows_here = (q_count - r0) < 32 ? (q_count - r0) : 32;
+            for (int r = 0; r < rows_here; r += query_group) {
+                launch_parent_keys(d_all + (size_t)r * n, n, query_group, d_order, d_offsets, parents, top_n, penalty,
+                                   d_agg, d_keys + (size_t)((r0 + r) / query_group) * parents, s);
+                launches += 2;
+            }
+        }
+        launch_tq_merge(d_keys, (int64_t)parents, (int64_t)parents, 1, parents, nullptr, groups, k, 0, d_ids, d_sc,
+                        nullptr, s);
+        launches++;
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_ids, d_ids, (size_t)groups * k * 8, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_scores, d_sc, (size_t)groups * k * 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev1, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess && stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+        stats->uploaded_bytes = (int64_t)q_count * c->qz->dim * 4;
+        stats->downloaded_bytes = (int64_t)groups * k * 12;
+        cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+    }
+    dev_free(d_order);
+    dev_free(d_offsets);
+    dev_free(d_all);
+    dev_free(d_agg);
+    dev_free(d_keys);
+    dev_free(d_ids);
+    dev_free(d_sc);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(err, std::string("parent_topk: ") + cudaGetErrorString(e));
+    }
+    return EOS_B200_OK;
+}
+
+int eos_b200_synth_gaussian_device(EosB200Runtime* rt, uint64_t seed, int64_t row_offset, int64_t n, int dim,
+                                   int normalize, float* d_out, void* stream, char** err) {
+    if (rt == nullptr || d_out == nullptr) return fail(err, "synth_gaussian: null argument");
+    if (n <= 0 || dim <= 0) return fail(err, "synth_gaussian: sizes must be positive");
+    CUDA_TRY(cudaSetDevice(rt->device));
+    synth_gaussian_kernel<<<rt->sm_count * 8, 256, 0, pick_stream(rt, stream)>>>(
+        (unsigned long long)seed, (long long)row_offset, (long long)n, dim, normalize ? 1 : 0, d_out);
+    CUDA_TRY(cudaGetLastError());
+    return EOS_B200_OK;
+}
+
+}  // extern "C"

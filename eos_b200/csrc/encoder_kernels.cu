@@ -1,0 +1,808 @@
+// Bandwidth-bound pieces of the q8 encoder forward and its attention, for sm_100a.
+//
+// Reference semantics restated here (file:line inside the Eos project):
+//   embeddings + LayerNorm   runtime/backend/tensor_ops.go:1451-1512
+//                            (device twin: manta_bert_embedding_affine_layernorm,
+//                             runtime/backends/cuda/native_linux.go:2700-2753)
+//   LayerNorm(x + residual)  runtime/backend/bert_encoder_layer_ops.go:718-740
+//   self-attention           runtime/backend/bert_encoder_layer_ops.go:326-379
+//                            (device twin: manta_bert_attention_context, native_linux.go:2857-2969)
+//   masked mean / CLS + L2   runtime/backend/tensor_ops.go:1680-1705, 1367-1391;
+//                            runtime/backend/bert_embedder_ops.go:174-218
+//   projection head + L2     runtime/pretrained_bert_projection_head.go:84-100
+//   compiled pipeline        examples/embed_masked_pooled.eos:11-16
+//
+// Unlike the reference, rows whose attention_mask is zero are never materialised: they cannot
+// influence a kept row (keys are masked, pooling skips them), so the batch is packed to its
+// valid tokens first and every later kernel works on packed rows.
+#include "encoder_kernels.cuh"
+
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace eosb {
+
+namespace {
+
+// ------------------------------------------------------------------------------------------
+// sequence layout
+// ------------------------------------------------------------------------------------------
+__global__ void seq_count_kernel(const int32_t* __restrict__ mask, int tokens, int cls_pooling, int* key_count,
+                                 int* row_count) {
+    const int b = blockIdx.x;
+    const int32_t* m = mask + (size_t)b * tokens;
+    int local = 0;
+    for (int t = threadIdx.x; t < tokens; t += blockDim.x) local += (m[t] != 0);
+    __shared__ int warp_tot[32];
+    int w = local;
+    for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+    if ((threadIdx.x & 31) == 0) warp_tot[threadIdx.x >> 5] = w;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int i = 0; i < (blockDim.x + 31) / 32; ++i) total += warp_tot[i];
+        key_count[b] = total;
+        row_count[b] = total + ((cls_pooling && m[0] == 0) ? 1 : 0);
+    }
+}
+
+__global__ void seq_scan_kernel(const int* row_count, int batch, int* cu_rows, int* total_rows) {
+    // single block; sequential chunks of blockDim.x with a running carry
+    __shared__ int buf[1024];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < batch; base += blockDim.x) {
+        const int i = base + threadIdx.x;
+        const int v = i < batch ? row_count[i] : 0;
+        buf[threadIdx.x] = v;
+        __syncthreads();
+        for (int o = 1; o < blockDim.x; o <<= 1) {
+            int add = threadIdx.x >= o ? buf[threadIdx.x - o] : 0;
+            __syncthreads();
+            buf[threadIdx.x] += add;
+            __syncthreads();
+        }
+        if (i < batch) cu_rows[i] = carry + buf[threadIdx.x] - v;
+        __syncthreads();
+        if (threadIdx.x == 0) carry += buf[blockDim.x - 1];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        cu_rows[batch] = carry;
+        *total_rows = carry;
+    }
+}
+
+__global__ void seq_fill_kernel(const int32_t* __restrict__ mask, int tokens, int cls_pooling, const int* cu_rows,
+                                const int* key_count, int* row_src, int* cls_row) {
+    const int b = blockIdx.x;
+    const int32_t* m = mask + (size_t)b * tokens;
+    const int row0 = cu_rows[b];
+    __shared__ int warp_off[33];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int base = 0; base < tokens; base += blockDim.x) {
+        const int t = base + threadIdx.x;
+        const int valid = (t < tokens) && (m[t] != 0);
+        const unsigned bal = __ballot_sync(0xffffffffu, valid);
+        if (lane == 0) warp_off[warp] = __popc(bal);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int run = carry;
+            for (int i = 0; i < nwarps; ++i) {
+                int c = warp_off[i];
+                warp_off[i] = run;
+                run += c;
+            }
+            warp_off[32] = run;
+        }
+        __syncthreads();
+        if (valid) row_src[row0 + warp_off[warp] + __popc(bal & ((1u << lane) - 1u))] = b * tokens + t;
+        __syncthreads();
+        if (threadIdx.x == 0) carry = warp_off[32];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        if (cls_pooling && m[0] == 0) {
+            // token 0 is masked: it is still a query (the reference computes every row and CLS
+            // pooling reads row 0), so it gets a query-only row after the sequence's keys.
+            row_src[row0 + key_count[b]] = b * tokens;
+            cls_row[b] = row0 + key_count[b];
+        } else {
+            cls_row[b] = row0;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// row-wise kernels: one warp per row, 8 f16 per 16-byte access, kChunks accesses per lane
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 u;
+    __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]);
+    __half2 h2 = __floats2half2_rn(f[4], f[5]), h3 = __floats2half2_rn(f[6], f[7]);
+    u.x = *reinterpret_cast<uint32_t*>(&h0);
+    u.y = *reinterpret_cast<uint32_t*>(&h1);
+    u.z = *reinterpret_cast<uint32_t*>(&h2);
+    u.w = *reinterpret_cast<uint32_t*>(&h3);
+    return u;
+}
+
+// LayerNorm of one row held as kChunks x 8 values per lane; two-pass (mean, then centred
+// variance) in fp32 like the reference's double-precision two-pass form.
+template <int kChunks>
+__device__ __forceinline__ void row_layernorm_store(float (&v)[kChunks][8], int dim, int lane, const float* gamma,
+                                                    const float* beta, float eps, __half* out_row) {
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < dim) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum += v[c][i];
+        }
+    }
+    const float mean = warp_sum(sum) / (float)dim;
+    float var = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < dim) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float d = v[c][i] - mean;
+                var += d * d;
+            }
+        }
+    }
+    var = warp_sum(var) / (float)dim;
+    const float inv = 1.0f / sqrtf(var + eps);
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < dim) {
+            float o[8];
+            const float4 g0 = *reinterpret_cast<const float4*>(gamma + col);
+            const float4 g1 = *reinterpret_cast<const float4*>(gamma + col + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(beta + col);
+            const float4 b1 = *reinterpret_cast<const float4*>(beta + col + 4);
+            const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = (v[c][i] - mean) * inv * g[i] + bb[i];
+            *reinterpret_cast<uint4*>(out_row + col) = pack8(o);
+        }
+    }
+}
+
+template <int kChunks>
+__global__ void __launch_bounds__(256)
+embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ types, const int* __restrict__ row_src,
+                const int* __restrict__ total_rows, int tokens, const __half* __restrict__ tok, int vocab,
+                const __half* __restrict__ pos, int max_pos, const __half* __restrict__ typ, int type_vocab,
+                const float* __restrict__ gamma, const float* __restrict__ beta, float eps, int dim, int m_alloc,
+                __half* __restrict__ out, int* status) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+    int rows = *total_rows;
+    if (rows > m_alloc) rows = m_alloc;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps_per_grid) {
+        const int src = row_src[r];
+        const int t = src % tokens;
+        const int id = ids[src];
+        const int ty = types != nullptr ? types[src] : 0;
+        int bad = 0;
+        if (id < 0 || id >= vocab) bad = kStatusBadTokenId;
+        else if (ty < 0 || ty >= type_vocab) bad = kStatusBadTypeId;
+        else if (t >= max_pos) bad = kStatusBadPosition;
+        if (bad) {
+            if (lane == 0) atomicCAS(status, 0, bad);
+            continue;  // row left as is; the host reports the status word and discards the result
+        }
+        const __half* a = tok + (size_t)id * dim;
+        const __half* p = pos + (size_t)t * dim;
+        const __half* q = typ + (size_t)ty * dim;
+        float v[kChunks][8];
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            if (col < dim) {
+                float fa[8], fp[8], fq[8];
+                unpack8(*reinterpret_cast<const uint4*>(a + col), fa);
+                unpack8(*reinterpret_cast<const uint4*>(p + col), fp);
+                unpack8(*reinterpret_cast<const uint4*>(q + col), fq);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[c][i] = (fa[i] + fp[i]) + fq[i];
+            }
+        }
+        row_layernorm_store<kChunks>(v, dim, lane, gamma, beta, eps, out + (size_t)r * dim);
+    }
+}
+
+template <int kChunks>
+__global__ void __launch_bounds__(256)
+layernorm_kernel(const __half* __restrict__ in, const float* __restrict__ gamma, const float* __restrict__ beta,
+                 float eps, int dim, int m_alloc, const int* __restrict__ total_rows, __half* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+    int rows = total_rows != nullptr ? *total_rows : m_alloc;
+    if (rows > m_alloc) rows = m_alloc;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps_per_grid) {
+        const __half* x = in + (size_t)r * dim;
+        float v[kChunks][8];
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            if (col < dim) unpack8(*reinterpret_cast<const uint4*>(x + col), v[c]);
+        }
+        row_layernorm_store<kChunks>(v, dim, lane, gamma, beta, eps, out + (size_t)r * dim);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// attention, generic head_dim (<= 64, multiple of 2): one warp per (row, head); lanes split the
+// keys, each keeps an online-softmax partial, partials are merged with shuffles.  fp32 throughout.
+// Used for head dims the tensor-core kernel does not cover and as its cross-check.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+attn_generic_kernel(const __half* __restrict__ qkv, const int* __restrict__ cu_rows, const int* __restrict__ key_count,
+                    const int* __restrict__ row_src, int batch, int tokens, int hidden, int heads, int window,
+                    __half* __restrict__ ctx) {
+    const int hd = hidden / heads;
+    const int lane = threadIdx.x & 31;
+    const int b = blockIdx.z;
+    const int head = blockIdx.y;
+    const int row0 = cu_rows[b];
+    const int nrows = cu_rows[b + 1] - row0;
+    const int nkeys = key_count[b];
+    const int qi = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (qi >= nrows) return;
+    const int ld = 3 * hidden;
+    const __half* qp = qkv + (size_t)(row0 + qi) * ld + head * hd;
+    const float scale = rsqrtf((float)hd);
+    float q[64];
+#pragma unroll
+    for (int d = 0; d < 64; ++d) q[d] = d < hd ? __half2float(qp[d]) * scale : 0.f;
+    const int qpos = row_src[row0 + qi] % tokens;
+    float m = -INFINITY, l = 0.f;
+    float o[64];
+#pragma unroll
+    for (int d = 0; d < 64; ++d) o[d] = 0.f;
+    for (int j = lane; j < nkeys; j += 32) {
+        if (window > 0) {
+            const int kpos = row_src[row0 + j] % tokens;
+            const int dist = qpos > kpos ? qpos - kpos : kpos - qpos;
+            if (2 * dist >= window) continue;
+        }
+        const __half* kp = qkv + (size_t)(row0 + j) * ld + hidden + head * hd;
+        const __half* vp = kp + hidden;
+        float s = 0.f;
+#pragma unroll
+        for (int d = 0; d < 64; d += 2) {
+            if (d < hd) {
+                const float2 kk = __half22float2(*reinterpret_cast<const __half2*>(kp + d));
+                s = fmaf(q[d], kk.x, s);
+                s = fmaf(q[d + 1], kk.y, s);
+            }
+        }
+        const float mn = fmaxf(m, s);
+        const float corr = __expf(m - mn);  // exp(-inf) = 0 on the first key
+        const float pr = __expf(s - mn);
+        l = l * corr + pr;
+#pragma unroll
+        for (int d = 0; d < 64; d += 2) {
+            if (d < hd) {
+                const float2 vv = __half22float2(*reinterpret_cast<const __half2*>(vp + d));
+                o[d] = fmaf(pr, vv.x, o[d] * corr);
+                o[d + 1] = fmaf(pr, vv.y, o[d + 1] * corr);
+            }
+        }
+        m = mn;
+    }
+    const float mall = warp_max(m);
+    const float f = (m == -INFINITY) ? 0.f : __expf(m - mall);
+    const float lall = warp_sum(l * f);
+    __half* op = ctx + (size_t)(row0 + qi) * hidden + head * hd;
+    const float inv = lall > 0.f ? 1.0f / lall : 0.f;  // no visible key: zeros, as the reference
+#pragma unroll
+    for (int d = 0; d < 64; ++d) {
+        if (d < hd) {
+            const float tot = warp_sum(o[d] * f);
+            if (lane == 0) op[d] = __float2half_rn(tot * inv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// attention, head_dim 64, tensor cores (mma.sync m16n8k16 f16 -> f32), flash-style:
+// one CTA = 64 queries of one (sequence, head); 4 warps x 16 query rows; K/V tiles of 64 keys
+// double-buffered in shared memory with cp.async; online softmax in fp32 registers.
+// ------------------------------------------------------------------------------------------
+constexpr int kAttnLd = 72;  // shared row stride in halfs (64 + 8 pad: conflict-free ldmatrix)
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+    const uint32_t d = smem_u32(smem_dst);
+    const int sz = valid ? 16 : 0;  // src-size 0: destination is zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = smem_u32(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = smem_u32(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(128)
+attn_hd64_kernel(const __half* __restrict__ qkv, const int* __restrict__ cu_rows, const int* __restrict__ key_count,
+                 const int* __restrict__ row_src, int tokens, int hidden, int window, __half* __restrict__ ctx) {
+    __shared__ __align__(16) __half sq[64 * kAttnLd];
+    __shared__ __align__(16) __half sk[2][64 * kAttnLd];
+    __shared__ __align__(16) __half sv[2][64 * kAttnLd];
+
+    const int b = blockIdx.z;
+    const int head = blockIdx.y;
+    const int row0 = cu_rows[b];
+    const int nrows = cu_rows[b + 1] - row0;
+    const int q0 = blockIdx.x * 64;
+    if (q0 >= nrows) return;
+    const int nkeys = key_count[b];
+    const int ld = 3 * hidden;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    const __half* qbase = qkv + (size_t)row0 * ld + head * 64;
+    const __half* kbase = qbase + hidden;
+    const __half* vbase = kbase + hidden;
+
+    // key-tile range; with a local window only tiles that can intersect the band are visited
+    int kt_begin = 0, kt_end = (nkeys + 63) / 64;
+    int qpos_lo = 0, qpos_hi = 0;
+    if (window > 0) {
+        const int qlast = min(q0 + 63, nrows - 1);
+        qpos_lo = row_src[row0 + q0] % tokens;
+        qpos_hi = row_src[row0 + qlast] % tokens;
+        if (qpos_hi < qpos_lo) {  // a trailing query-only CLS row (position 0) is in this block
+            qpos_lo = 0;
+        }
+        // positions are increasing along the packed keys, so tiles far outside the band can be
+        // skipped by position of their first / last key
+        while (kt_begin < kt_end) {
+            const int last = min(kt_begin * 64 + 63, nkeys - 1);
+            const int kp = row_src[row0 + last] % tokens;
+            if (2 * (qpos_lo - kp) >= window) ++kt_begin; else break;
+        }
+        while (kt_end > kt_begin) {
+            const int kp = row_src[row0 + (kt_end - 1) * 64] % tokens;
+            if (2 * (kp - qpos_hi) >= window) --kt_end; else break;
+        }
+    }
+
+    auto load_tile = [&](const __half* gbase, int first_row, int limit, __half* dst) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = i * 128 + tid;
+            const int r = c >> 3, ch = c & 7;
+            const bool ok = (first_row + r) < limit;
+            const __half* src = gbase + (size_t)(ok ? first_row + r : 0) * ld + ch * 8;
+            cp_async16(dst + r * kAttnLd + ch * 8, src, ok);
+        }
+    };
+
+    load_tile(qbase, q0, nrows, sq);
+    if (kt_begin < kt_end) {
+        load_tile(kbase, kt_begin * 64, nkeys, sk[0]);
+        load_tile(vbase, kt_begin * 64, nkeys, sv[0]);
+    }
+    cp_async_commit();
+
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+    uint32_t qf[4][4];
+    const float sl2 = 0.125f * 1.4426950408889634f;  // 1/sqrt(64) * log2(e)
+
+    int my_pos[2] = {0, 0};
+    if (window > 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int qi = q0 + warp * 16 + g + h * 8;
+            my_pos[h] = qi < nrows ? row_src[row0 + qi] % tokens : 0;
+        }
+    }
+
+    for (int kt = kt_begin; kt < kt_end; ++kt) {
+        const int buf = (kt - kt_begin) & 1;
+        if (kt + 1 < kt_end) {
+            load_tile(kbase, (kt + 1) * 64, nkeys, sk[buf ^ 1]);
+            load_tile(vbase, (kt + 1) * 64, nkeys, sv[buf ^ 1]);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (kt == kt_begin) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+                ldsm_x4(qf[kk], sq + (warp * 16 + (lane & 15)) * kAttnLd + kk * 16 + (lane >> 4) * 8);
+        }
+        // S = Q K^T
+        float s[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+                uint32_t kf[4];
+                ldsm_x4(kf, sk[buf] + (jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * kAttnLd + kk * 16 +
+                                ((lane >> 3) & 1) * 8);
+                mma16816(s[2 * jp], qf[kk], kf[0], kf[1]);
+                mma16816(s[2 * jp + 1], qf[kk], kf[2], kf[3]);
+            }
+        }
+        // mask + online softmax (rows g and g+8 of this warp's 16)
+        const int key0 = kt * 64;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + j * 8 + t4 * 2 + (e & 1);
+                bool vis = key < nkeys;
+                if (window > 0 && vis) {
+                    const int kp = row_src[row0 + key] % tokens;
+                    const int qp = my_pos[e >> 1];
+                    const int dist = qp > kp ? qp - kp : kp - qp;
+                    vis = 2 * dist < window;
+                }
+                const float x = vis ? s[j][e] * sl2 : -INFINITY;
+                s[j][e] = x;
+                mx[e >> 1] = fmaxf(mx[e >> 1], x);
+            }
+        }
+        float corr[2], mnew[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            mnew[h] = fmaxf(m_run[h], mx[h]);
+            corr[h] = (mnew[h] == -INFINITY) ? 1.f : exp2f(m_run[h] - mnew[h]);
+            m_run[h] = mnew[h];
+        }
+        float ls[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const float pz = (mnew[h] == -INFINITY) ? 0.f : exp2f(s[j][e] - mnew[h]);
+                s[j][e] = pz;
+                ls[h] += pz;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + ls[h];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[0];
+            o[i][2] *= corr[1];
+            o[i][3] *= corr[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            uint32_t pf[4];
+            pf[0] = pack_half2(s[2 * kk][0], s[2 * kk][1]);
+            pf[1] = pack_half2(s[2 * kk][2], s[2 * kk][3]);
+            pf[2] = pack_half2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pf[3] = pack_half2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < 4; ++dp) {
+                uint32_t vf[4];
+                ldsm_x4_t(vf, sv[buf] + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kAttnLd + dp * 16 +
+                                  (lane >> 4) * 8);
+                mma16816(o[2 * dp], pf, vf[0], vf[1]);
+                mma16816(o[2 * dp + 1], pf, vf[2], vf[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int qi = q0 + warp * 16 + g + h * 8;
+        if (qi >= nrows) continue;
+        const float inv = l_run[h] > 0.f ? 1.0f / l_run[h] : 0.f;
+        __half* op = ctx + (size_t)(row0 + qi) * hidden + head * 64 + t4 * 2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            *reinterpret_cast<__half2*>(op + i * 8) =
+                __floats2half2_rn(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// pooling (+ head) + L2
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (blockDim.x + 31) / 32; ++i) tot += red[i];
+    return tot;
+}
+
+__global__ void __launch_bounds__(256)
+pool_l2_kernel(const __half* __restrict__ hs, const int* __restrict__ cu_rows, const int* __restrict__ key_count,
+               const int* __restrict__ cls_row, int dim, int cls_pooling, float* __restrict__ out) {
+    __shared__ float red[32];
+    const int b = blockIdx.x;
+    const int row0 = cu_rows[b];
+    const int n = key_count[b];
+    float sq = 0.f;
+    // each thread owns columns c, c + blockDim, ...; float sum over rows in token order, then
+    // * (1/count): the order of runtime/backend/tensor_ops.go:1680-1705
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        float acc = 0.f;
+        if (cls_pooling) {
+            acc = __half2float(hs[(size_t)cls_row[b] * dim + c]);
+        } else if (n > 0) {
+            for (int r = 0; r < n; ++r) acc += __half2float(hs[(size_t)(row0 + r) * dim + c]);
+            acc *= 1.0f / (float)n;
+        }
+        out[(size_t)b * dim + c] = acc;
+        sq += acc * acc;
+    }
+    const float tot = block_sum(sq, red);
+    const float norm = sqrtf(tot);
+    if (norm != 0.f) {
+        for (int c = threadIdx.x; c < dim; c += blockDim.x) out[(size_t)b * dim + c] /= norm;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+head_l2_kernel(const float* __restrict__ pooled, int dim, const float* __restrict__ w, int out_dim,
+               float* __restrict__ out) {
+    extern __shared__ float vec[];
+    __shared__ float red[32];
+    const int b = blockIdx.x;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) vec[i] = pooled[(size_t)b * dim + i];
+    __syncthreads();
+    float sq = 0.f;
+    for (int j = threadIdx.x; j < out_dim; j += blockDim.x) {
+        float acc = 0.f;
+        for (int i = 0; i < dim; ++i) acc = fmaf(vec[i], w[(size_t)i * out_dim + j], acc);
+        out[(size_t)b * out_dim + j] = acc;
+        sq += acc * acc;
+    }
+    const float tot = block_sum(sq, red);
+    if (tot != 0.f) {
+        const float sc = 1.0f / sqrtf(tot);
+        for (int j = threadIdx.x; j < out_dim; j += blockDim.x) out[(size_t)b * out_dim + j] *= sc;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// compiled pipeline: gather -> matmul -> normalize (per token) -> masked mean_pool, one launch.
+// One CTA per sequence; masked tokens are skipped (they are excluded from the mean).  Tokens are
+// processed 8 at a time: rows gathered to shared memory, every thread owns output columns.
+// ------------------------------------------------------------------------------------------
+constexpr int kEpTok = 8;
+constexpr int kEpMaxColsPerThread = 4;
+
+__global__ void __launch_bounds__(256)
+embed_pooled_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ mask, int tlen,
+                    const __half* __restrict__ table, int vocab, int dim, const __half* __restrict__ proj, int out_dim,
+                    int pool_then_l2, float* __restrict__ out, int* status) {
+    extern __shared__ float xs[];  // [kEpTok][dim]
+    __shared__ float red[32];
+    __shared__ int tok_ids[kEpTok];
+    __shared__ int n_tok;
+    __shared__ int cursor;
+    const int b = blockIdx.x;
+    const int32_t* tk = tokens + (size_t)b * tlen;
+    const int32_t* mk = mask + (size_t)b * tlen;
+    float pooled[kEpMaxColsPerThread];
+#pragma unroll
+    for (int i = 0; i < kEpMaxColsPerThread; ++i) pooled[i] = 0.f;
+    int count = 0;
+    if (threadIdx.x == 0) cursor = 0;
+    __syncthreads();
+    while (true) {
+        if (threadIdx.x == 0) {
+            int n = 0, t = cursor;
+            while (t < tlen && n < kEpTok) {
+                if (mk[t] != 0) tok_ids[n++] = tk[t];
+                ++t;
+            }
+            cursor = t;
+            n_tok = n;
+        }
+        __syncthreads();
+        const int n = n_tok;
+        if (n == 0) break;
+        for (int i = 0; i < n; ++i) {
+            const int id = tok_ids[i];
+            const bool ok = id >= 0 && id < vocab;
+            if (!ok && threadIdx.x == 0) atomicCAS(status, 0, kStatusBadTokenId);
+            for (int k = threadIdx.x; k < dim; k += blockDim.x)
+                xs[i * dim + k] = ok ? __half2float(table[(size_t)id * dim + k]) : 0.f;
+        }
+        __syncthreads();
+        float acc[kEpMaxColsPerThread][kEpTok];
+#pragma unroll
+        for (int c = 0; c < kEpMaxColsPerThread; ++c)
+#pragma unroll
+            for (int i = 0; i < kEpTok; ++i) acc[c][i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < kEpMaxColsPerThread; ++c) {
+            const int j = threadIdx.x + c * blockDim.x;
+            if (j < out_dim) {
+                for (int k = 0; k < dim; ++k) {
+                    const float w = __half2float(proj[(size_t)k * out_dim + j]);
+#pragma unroll
+                    for (int i = 0; i < kEpTok; ++i) acc[c][i] = fmaf(xs[i * dim + k], w, acc[c][i]);
+                }
+            }
+        }
+        for (int i = 0; i < n; ++i) {
+            float inv = 1.0f;
+            if (!pool_then_l2) {
+                float sq = 0.f;
+#pragma unroll
+                for (int c = 0; c < kEpMaxColsPerThread; ++c) sq += acc[c][i] * acc[c][i];
+                const float norm = sqrtf(block_sum(sq, red));
+                inv = norm != 0.f ? 1.0f / norm : 1.0f;
+            }
+#pragma unroll
+            for (int c = 0; c < kEpMaxColsPerThread; ++c)
+                pooled[c] += acc[c][i] * inv;
+        }
+        count += n;
+        __syncthreads();
+    }
+    float scale = count > 0 ? 1.0f / (float)count : 0.f;
+#pragma unroll
+    for (int c = 0; c < kEpMaxColsPerThread; ++c) pooled[c] *= scale;
+    if (pool_then_l2) {
+        float sq = 0.f;
+#pragma unroll
+        for (int c = 0; c < kEpMaxColsPerThread; ++c) sq += pooled[c] * pooled[c];
+        const float norm = sqrtf(block_sum(sq, red));
+        if (norm != 0.f) {
+#pragma unroll
+            for (int c = 0; c < kEpMaxColsPerThread; ++c) pooled[c] /= norm;
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < kEpMaxColsPerThread; ++c) {
+        const int j = threadIdx.x + c * blockDim.x;
+        if (j < out_dim) out[(size_t)b * out_dim + j] = pooled[c];
+    }
+}
+
+template <typename F>
+void dispatch_chunks(int dim, F&& f) {
+    const int chunks = (dim + 255) / 256;
+    if (chunks <= 1) f(std::integral_constant<int, 1>());
+    else if (chunks == 2) f(std::integral_constant<int, 2>());
+    else if (chunks == 3) f(std::integral_constant<int, 3>());
+    else if (chunks == 4) f(std::integral_constant<int, 4>());
+    else f(std::integral_constant<int, 8>());
+}
+
+}  // namespace
+
+void launch_seq_layout(const int32_t* mask, int batch, int tokens, int cls_pooling, const SeqLayout& lay,
+                       cudaStream_t stream) {
+    seq_count_kernel<<<batch, 256, 0, stream>>>(mask, tokens, cls_pooling, lay.key_count, lay.row_count);
+    seq_scan_kernel<<<1, 1024, 0, stream>>>(lay.row_count, batch, lay.cu_rows, lay.total_rows);
+    seq_fill_kernel<<<batch, 256, 0, stream>>>(mask, tokens, cls_pooling, lay.cu_rows, lay.key_count, lay.row_src,
+                                               lay.cls_row);
+}
+
+void launch_embed_ln(const int32_t* ids, const int32_t* types, const SeqLayout& lay, int tokens, const __half* tok,
+                     int vocab, const __half* pos, int max_pos, const __half* typ, int type_vocab, const float* gamma,
+                     const float* beta, float eps, int dim, int m_alloc, __half* out, int* status, int sm_count,
+                     cudaStream_t stream) {
+    dispatch_chunks(dim, [&](auto c) {
+        constexpr int kChunks = decltype(c)::value;
+        embed_ln_kernel<kChunks><<<sm_count * 8, 256, 0, stream>>>(ids, types, lay.row_src, lay.total_rows, tokens,
+                                                                   tok, vocab, pos, max_pos, typ, type_vocab, gamma,
+                                                                   beta, eps, dim, m_alloc, out, status);
+    });
+}
+
+void launch_layernorm(const __half* in, const float* gamma, const float* beta, float eps, int dim, int m_alloc,
+                      const int* total_rows, __half* out, int sm_count, cudaStream_t stream) {
+    dispatch_chunks(dim, [&](auto c) {
+        constexpr int kChunks = decltype(c)::value;
+        layernorm_kernel<kChunks><<<sm_count * 8, 256, 0, stream>>>(in, gamma, beta, eps, dim, m_alloc, total_rows,
+                                                                    out);
+    });
+}
+
+void launch_attention(const __half* qkv, const SeqLayout& lay, int batch, int tokens, int hidden, int heads,
+                      int window, __half* ctx, cudaStream_t stream) {
+    const int hd = hidden / heads;
+    const int max_rows = tokens + 1;
+    if (hd == 64) {
+        dim3 grid((max_rows + 63) / 64, heads, batch);
+        attn_hd64_kernel<<<grid, 128, 0, stream>>>(qkv, lay.cu_rows, lay.key_count, lay.row_src, tokens, hidden,
+                                                   window, ctx);
+    } else {
+        dim3 grid((max_rows + 3) / 4, heads, batch);
+        attn_generic_kernel<<<grid, 128, 0, stream>>>(qkv, lay.cu_rows, lay.key_count, lay.row_src, batch, tokens,
+                                                      hidden, heads, window, ctx);
+    }
+}
+
+void launch_pool_head(const __half* hidden_states, const SeqLayout& lay, int batch, int dim, int cls_pooling,
+                      const float* head_w, int head_out, float* pooled_scratch, float* out, cudaStream_t stream) {
+    float* pooled = head_w != nullptr ? pooled_scratch : out;
+    pool_l2_kernel<<<batch, 256, 0, stream>>>(hidden_states, lay.cu_rows, lay.key_count, lay.cls_row, dim,
+                                              cls_pooling, pooled);
+    if (head_w != nullptr)
+        head_l2_kernel<<<batch, 256, dim * sizeof(float), stream>>>(pooled, dim, head_w, head_out, out);
+}
+
+void launch_embed_pooled(const int32_t* tokens, const int32_t* mask, int batch, int tlen, const __half* table,
+                         int vocab, int dim, const __half* projection, int out_dim, int pool_then_l2, float* out,
+                         int* status, cudaStream_t stream) {
+    embed_pooled_kernel<<<batch, 256, kEpTok * dim * sizeof(float), stream>>>(tokens, mask, tlen, table, vocab, dim,
+                                                                              projection, out_dim, pool_then_l2, out,
+                                                                              status);
+}
+
+}  // namespace eosb

@@ -1,0 +1,50 @@
+// Launchers of the bandwidth-bound encoder kernels and of attention (encoder_kernels.cu).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace eosb {
+
+// Packed-row bookkeeping of one batch: only tokens whose attention_mask is non-zero get a row
+// (padding is skipped, not computed and masked).  All arrays live on the device.
+struct SeqLayout {
+    int* key_count;   // [B]   tokens with mask != 0 (they are the keys and, pooled, the mean's rows)
+    int* row_count;   // [B]   rows of the sequence (= key_count, + 1 query-only CLS row when token 0 is masked)
+    int* cu_rows;     // [B+1] exclusive prefix sum of row_count
+    int* cls_row;     // [B]   packed row that holds token 0
+    int* row_src;     // [M]   flat index b*T + t of every packed row
+    int* total_rows;  // [1]
+};
+
+void launch_seq_layout(const int32_t* mask, int batch, int tokens, int cls_pooling, const SeqLayout& lay,
+                       cudaStream_t stream);
+
+// hidden[r,:] = LayerNorm(tok[id] + pos[t] + typ[type]) * gamma + beta for every packed row.
+void launch_embed_ln(const int32_t* ids, const int32_t* types, const SeqLayout& lay, int tokens, const __half* tok,
+                     int vocab, const __half* pos, int max_pos, const __half* typ, int type_vocab, const float* gamma,
+                     const float* beta, float eps, int dim, int m_alloc, __half* out, int* status, int sm_count,
+                     cudaStream_t stream);
+
+// out[r,:] = LayerNorm(in[r,:]) * gamma + beta, rows < *total_rows.
+void launch_layernorm(const __half* in, const float* gamma, const float* beta, float eps, int dim, int m_alloc,
+                      const int* total_rows, __half* out, int sm_count, cudaStream_t stream);
+
+// Multi-head self-attention over the packed rows.  qkv is [M, 3*hidden] (q | k | v, heads
+// interleaved as head*head_dim + d); ctx is [M, hidden].  Keys of a sequence are its first
+// key_count rows; every row is a query.  window <= 0: full attention; window > 0: key j is
+// visible to query i only if |pos_i - pos_j| < window/2 (local-window extension).
+void launch_attention(const __half* qkv, const SeqLayout& lay, int batch, int tokens, int hidden, int heads,
+                      int window, __half* ctx, cudaStream_t stream);
+
+// pooled -> L2 -> optional head ([hidden, head_out], in-major) -> L2; writes out [B, E] fp32.
+void launch_pool_head(const __half* hidden_states, const SeqLayout& lay, int batch, int dim, int cls_pooling,
+                      const float* head_w, int head_out, float* pooled_scratch, float* out, cudaStream_t stream);
+
+// Compiled pipeline gather -> matmul -> per-token normalize -> masked mean_pool in one launch.
+// table [vocab, dim] f16, projection [dim, out_dim] f16 (in-major), out [B, out_dim] fp32.
+void launch_embed_pooled(const int32_t* tokens, const int32_t* mask, int batch, int tlen, const __half* table,
+                         int vocab, int dim, const __half* projection, int out_dim, int pool_then_l2, float* out,
+                         int* status, cudaStream_t stream);
+
+}  // namespace eosb

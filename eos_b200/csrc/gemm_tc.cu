@@ -1,0 +1,427 @@
+// out[M,N] = epilogue( A[M,K] (f16) x W[N,K]^T ), W stored as 8-bit codes with per-output-channel
+// scales (or as f16), on the 5th-generation tensor cores of sm_100a.
+//
+// This is the dense projection of the q8 encoder: it replaces the reference's
+// cublasSgemm path (runtime/backends/cuda/native_linux.go:1267-1307, called per projection from
+// runBGEFullEncoderHidden :7941-8190) and the host loop denseHFRange
+// (runtime/backend/bert_encoder_layer_ops.go:452-462): y = x W^T + b with W in HF [out,in] layout.
+//
+// Design (one persistent CTA per SM, 384 threads, warp-specialised):
+//   warp 0      TMA producer: A tile 128x64 f16 (128B swizzle) and the W tile 256x64 (8-bit codes,
+//               no swizzle) per k-block into a 4-stage ring, completion on mbarriers.
+//   warps 4-7   dequantisers: expand the 8-bit codes to f16 in shared memory, written directly in
+//               the 128B-swizzled K-major layout the MMA reads (int8 -> f16 is exact; the
+//               per-channel scale is applied in fp32 in the epilogue, which is the same product:
+//               sum_k a_k (s_n q_kn) = s_n sum_k a_k q_kn).
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16, f16 x f16 -> f32)
+//               with the accumulator in tensor memory; tcgen05.commit releases ring stages.
+//   warps 8-11  epilogue: tcgen05.ld the 128x256 fp32 accumulator (thread = row), scale, bias,
+//               GELU or residual add, f16 stores.  Two accumulators (2 x 256 TMEM columns) let the
+//               epilogue of tile i overlap the main loop of tile i+1.
+//   warp 2      allocates / frees tensor memory.
+// Every mbarrier wait is bounded (common.cuh: mbar_wait); on a timeout the kernel raises a
+// CTA-wide abort flag, all roles leave their loops, TMEM is freed and the status word is set.
+#include "gemm_tc.cuh"
+
+#include "common.cuh"
+
+namespace eosb {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int kStagesAB = 4;    // ring depth of the TMA-fed stages
+constexpr int kStagesB16 = 2;   // ring depth of the dequantised W tiles (int8 mode)
+constexpr int kThreads = 384;
+constexpr int kTmemCols = 512;  // two 128x256 fp32 accumulators
+constexpr uint32_t kBytesA = BM * BK * 2;
+constexpr uint32_t kBytesB16 = BN * BK * 2;
+constexpr uint32_t kBytesB8 = BN * BK;
+
+// shared memory map (offsets from a 1024-byte aligned base)
+constexpr uint32_t kOffA = 0;
+constexpr uint32_t kOffB16 = kOffA + kStagesAB * kBytesA;              // 64 KB
+constexpr uint32_t kOffB8 = kOffB16 + kStagesB16 * kBytesB16;          // int8 mode: after 2 f16 stages
+constexpr uint32_t kOffTailInt8 = kOffB8 + kStagesAB * kBytesB8;       // 192 KB
+constexpr uint32_t kOffTailF16 = kOffB16 + kStagesAB * kBytesB16;      // f16 mode: 4 f16 stages, 192 KB
+static_assert(kOffTailInt8 == kOffTailF16, "both modes use the same main footprint");
+constexpr uint32_t kOffScaleBias = kOffTailInt8;                       // 2 x 256 float2
+constexpr uint32_t kOffBars = kOffScaleBias + 2 * BN * 8;
+constexpr uint32_t kNumBars = 2 * kStagesAB + 2 * kStagesB16 + 4;
+constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
+constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;                  // + alignment slack
+
+template <bool kBInt8>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* sm = smem_raw + (base - raw);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const uint32_t bar0 = base + kOffBars;
+    auto full_ab = [&](int s) { return bar0 + 8u * s; };
+    auto empty_ab = [&](int s) { return bar0 + 8u * (kStagesAB + s); };
+    auto full_b16 = [&](int s) { return bar0 + 8u * (2 * kStagesAB + s); };
+    auto empty_b16 = [&](int s) { return bar0 + 8u * (2 * kStagesAB + kStagesB16 + s); };
+    auto acc_full = [&](int s) { return bar0 + 8u * (2 * kStagesAB + 2 * kStagesB16 + s); };
+    auto acc_empty = [&](int s) { return bar0 + 8u * (2 * kStagesAB + 2 * kStagesB16 + 2 + s); };
+
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + kOffMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
+    float2* scale_bias = reinterpret_cast<float2*>(sm + kOffScaleBias);
+
+    int m_rows = p.m_alloc;
+    if (p.m_ptr != nullptr) {
+        int v = *p.m_ptr;
+        m_rows = v < p.m_alloc ? v : p.m_alloc;
+        if (m_rows < 0) m_rows = 0;
+    }
+    const int m_tiles = (m_rows + BM - 1) / BM;
+    const int n_tiles = (p.n + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles;
+    const int num_kb = (p.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < kStagesAB; ++s) {
+            mbar_init(full_ab(s), 1);
+            mbar_init(empty_ab(s), kBInt8 ? 5 : 1);  // MMA commit (+ 4 dequantiser warps)
+        }
+        for (int s = 0; s < kStagesB16; ++s) {
+            mbar_init(full_b16(s), 4);
+            mbar_init(empty_b16(s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(acc_full(s), 1);
+            mbar_init(acc_empty(s), 4);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int m0 = (tile / n_tiles) * BM;
+                const int n0 = (tile % n_tiles) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStagesAB;
+                    const uint32_t ph = (it / kStagesAB) & 1u;
+                    if (!mbar_wait(empty_ab(s), ph ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(full_ab(s), kBytesA + (kBInt8 ? kBytesB8 : kBytesB16));
+                    tma_load_2d(base + kOffA + s * kBytesA, &tm_a, kb * BK, m0, full_ab(s));
+                    if (kBInt8)
+                        tma_load_2d(base + kOffB8 + s * kBytesB8, &tm_b, kb * BK, n0, full_ab(s));
+                    else
+                        tma_load_2d(base + kOffB16 + s * kBytesB16, &tm_b, kb * BK, n0, full_ab(s));
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16(BM, BN);
+            uint32_t it = 0;
+            uint32_t t = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
+                const uint32_t ab = t & 1u;
+                const uint32_t aph = (t >> 1) & 1u;
+                if (!mbar_wait(acc_empty(ab), aph ^ 1u, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + ab * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStagesAB;
+                    const uint32_t ph = (it / kStagesAB) & 1u;
+                    if (!mbar_wait(full_ab(s), ph, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint32_t b_addr;
+                    int c = 0;
+                    if (kBInt8) {
+                        c = it % kStagesB16;
+                        const uint32_t cph = (it / kStagesB16) & 1u;
+                        if (!mbar_wait(full_b16(c), cph, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        b_addr = base + kOffB16 + c * kBytesB16;
+                    } else {
+                        b_addr = base + kOffB16 + s * kBytesB16;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = base + kOffA + s * kBytesA;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        umma_f16(d_tmem, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
+                                 (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_ab(s));
+                    if (kBInt8) umma_commit(empty_b16(c));
+                }
+                if (ok) umma_commit(acc_full(ab));
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 4 && warp < 8) {
+        // ------------------------------------------------------------ dequantisers (int8 mode)
+        if (kBInt8) {
+            const int tid = threadIdx.x - 128;
+            const uint32_t bias1152 = 0x64806480u;  // half2(1152, 1152) = 1024 + 128
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStagesAB;
+                    const uint32_t ph = (it / kStagesAB) & 1u;
+                    const int c = it % kStagesB16;
+                    const uint32_t cph = (it / kStagesB16) & 1u;
+                    if (!mbar_wait(full_ab(s), ph, abort_flag) || !mbar_wait(empty_b16(c), cph ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint8_t* src = sm + kOffB8 + s * kBytesB8;
+                    uint8_t* dst = sm + kOffB16 + c * kBytesB16;
+#pragma unroll
+                    for (int i = 0; i < (BN * BK / 16) / 128; ++i) {
+                        const int q = i * 128 + tid;
+                        const int r = q >> 2;
+                        const int j = q & 3;
+                        const uint4 raw8 = *reinterpret_cast<const uint4*>(src + r * BK + j * 16);
+                        const uint32_t w[4] = {raw8.x, raw8.y, raw8.z, raw8.w};
+                        uint32_t h[8];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            // bytes u = code + 128; 0x6400 | u is the f16 value 1024 + u, so
+                            // (1024 + u) - 1152 = code, exactly.
+                            uint32_t lo = __byte_perm(w[e], 0x64646464u, 0x5140);
+                            uint32_t hi = __byte_perm(w[e], 0x64646464u, 0x7362);
+                            __half2 l2 = __hsub2(*reinterpret_cast<__half2*>(&lo),
+                                                 *reinterpret_cast<const __half2*>(&bias1152));
+                            __half2 h2 = __hsub2(*reinterpret_cast<__half2*>(&hi),
+                                                 *reinterpret_cast<const __half2*>(&bias1152));
+                            h[2 * e] = *reinterpret_cast<uint32_t*>(&l2);
+                            h[2 * e + 1] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                        uint8_t* row = dst + (r >> 3) * 1024 + (r & 7) * 128;
+                        const int x = r & 7;
+                        *reinterpret_cast<uint4*>(row + (((2 * j) ^ x) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4*>(row + (((2 * j + 1) ^ x) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(full_b16(c));
+                        mbar_arrive(empty_ab(s));
+                    }
+                }
+            }
+        }
+    } else if (warp >= 8) {
+        // ------------------------------------------------------------ epilogue
+        const int etid = threadIdx.x - 256;          // 0..127 = accumulator row inside the tile
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32);
+        uint32_t t = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
+            const int m0 = (tile / n_tiles) * BM;
+            const int n0 = (tile % n_tiles) * BN;
+            const uint32_t ab = t & 1u;
+            const uint32_t aph = (t >> 1) & 1u;
+            float2* sb = scale_bias + ab * BN;
+            for (int cidx = etid; cidx < BN; cidx += 128) {
+                const int n = n0 + cidx;
+                float2 v = make_float2(1.0f, 0.0f);
+                if (n < p.n) {
+                    if (p.scale != nullptr) v.x = __ldg(p.scale + n);
+                    if (p.bias != nullptr) v.y = __ldg(p.bias + n);
+                }
+                sb[cidx] = v;
+            }
+            named_bar_sync(1, 128);
+            if (!mbar_wait(acc_full(ab), aph, abort_flag)) break;
+            tc_fence_after();
+            const int m = m0 + etid;
+            const bool row_ok = m < m_rows;
+            const uint32_t taddr = tmem_base + (lane_base << 16) + ab * BN;
+            __half* out_row = p.out + (size_t)m * p.ldo;
+            const __half* res_row = p.residual + (size_t)m * p.ldr;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                const int nc = n0 + ch * 32;
+                if (nc >= p.n) break;
+                uint32_t r[32];
+                __syncwarp();
+                tmem_ld_32x32(taddr + ch * 32, r);
+                tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const float4 f = *reinterpret_cast<const float4*>(&sb[ch * 32 + j]);
+                    v[j] = fmaf(__uint_as_float(r[j]), f.x, f.y);
+                    v[j + 1] = fmaf(__uint_as_float(r[j + 1]), f.z, f.w);
+                }
+                if (p.mode == kEpiBiasGeluErf) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                } else if (p.mode == kEpiBiasGeluTanh) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+                }
+                const bool full_chunk = (nc + 32 <= p.n);
+                if (!row_ok) {
+                    // rows past the end of the activation matrix: nothing to store
+                } else if (full_chunk) {
+                    if (p.mode == kEpiBiasResidual) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 rr = *reinterpret_cast<const uint4*>(res_row + nc + q * 8);
+                            const __half2* h = reinterpret_cast<const __half2*>(&rr);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 f = __half22float2(h[e]);
+                                v[q * 8 + 2 * e] += f.x;
+                                v[q * 8 + 2 * e + 1] += f.y;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint4 o;
+                        __half2 h0 = __floats2half2_rn(v[q * 8 + 0], v[q * 8 + 1]);
+                        __half2 h1 = __floats2half2_rn(v[q * 8 + 2], v[q * 8 + 3]);
+                        __half2 h2 = __floats2half2_rn(v[q * 8 + 4], v[q * 8 + 5]);
+                        __half2 h3 = __floats2half2_rn(v[q * 8 + 6], v[q * 8 + 7]);
+                        o.x = *reinterpret_cast<uint32_t*>(&h0);
+                        o.y = *reinterpret_cast<uint32_t*>(&h1);
+                        o.z = *reinterpret_cast<uint32_t*>(&h2);
+                        o.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(out_row + nc + q * 8) = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (nc + j < p.n) {
+                            float x = v[j];
+                            if (p.mode == kEpiBiasResidual) x += __half2float(res_row[nc + j]);
+                            out_row[nc + j] = __float2half_rn(x);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(ab));
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn(std::string* err) {
+    static EncodeTiledFn fn = nullptr;
+    if (fn != nullptr) return fn;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || sym == nullptr || qres != cudaDriverEntryPointSuccess) {
+        *err = std::string("cuTensorMapEncodeTiled is not available: ") + cudaGetErrorString(e);
+        return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+    return fn;
+}
+
+std::string encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, const void* ptr, uint64_t inner, uint64_t outer,
+                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
+    std::string err;
+    EncodeTiledFn fn = get_encode_fn(&err);
+    if (fn == nullptr) return err;
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return "tensor map base address is not 16-byte aligned";
+    if ((row_stride_bytes & 15u) != 0) return "tensor map row stride is not a multiple of 16 bytes";
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r);
+    return "";
+}
+
+}  // namespace
+
+std::string gemm_global_init() {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return std::string("cudaFuncSetAttribute(gemm_tc_kernel): ") + cudaGetErrorString(e);
+    return "";
+}
+
+std::string gemm_make_plan(GemmPlan* plan, const __half* a, int lda, const void* w, int ldw, bool b_int8,
+                           const GemmParams& params, int sm_count) {
+    if (params.m_alloc <= 0 || params.n <= 0 || params.k <= 0) return "gemm: dimensions must be positive";
+    if (params.ldo % 8 != 0) return "gemm: output row stride must be a multiple of 8 elements";
+    if (params.mode == kEpiBiasResidual && (params.residual == nullptr || params.ldr % 8 != 0))
+        return "gemm: residual epilogue needs a residual pointer with a row stride that is a multiple of 8";
+    std::string err = encode_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)params.k,
+                                (uint64_t)params.m_alloc, (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!err.empty()) return "gemm A: " + err;
+    if (b_int8)
+        err = encode_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, (uint64_t)params.k, (uint64_t)params.n,
+                        (uint64_t)ldw, BK, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
+    else
+        err = encode_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w, (uint64_t)params.k, (uint64_t)params.n,
+                        (uint64_t)ldw * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!err.empty()) return "gemm W: " + err;
+    plan->p = params;
+    plan->b_int8 = b_int8;
+    const int m_tiles = (params.m_alloc + BM - 1) / BM;
+    const int n_tiles = (params.n + BN - 1) / BN;
+    const long long tiles = (long long)m_tiles * n_tiles;
+    plan->grid = (int)(tiles < sm_count ? tiles : sm_count);
+    return "";
+}
+
+void gemm_launch(const GemmPlan& plan, cudaStream_t stream) {
+    if (plan.b_int8)
+        gemm_tc_kernel<true><<<plan.grid, kThreads, kSmemBytes, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+    else
+        gemm_tc_kernel<false><<<plan.grid, kThreads, kSmemBytes, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+}
+
+}  // namespace eosb

@@ -1,0 +1,695 @@
+// TurboQuant (Hadamard/MSE variant) on sm_100a: code packing, scan layout, query preparation,
+// scoring scan with exact per-CTA top-k, and the k-way merge.
+//
+// Reference call sites / semantics (file:line inside the Eos project):
+//   encode structure          runtime/backends/cuda/native_linux.go:1812-1957 (manta_turboq_encode)
+//   corpus quantise loop      runtime/retrieval_turboquant.go:700-711
+//   per-query scoring + heap  runtime/retrieval_turboquant.go:1853-1916
+//   order of results          runtime/retrieval_eval.go:1153-1161 (score desc, then id asc)
+//
+// Scoring: <q, doc> ~= norm * sum_c Rq[c] * centroid[code[c]] with R the quantiser's orthogonal
+// rotation.  The scan streams the packed codes once per pass for a tile of 8/16/32 queries:
+// every warp owns 16 documents, expands their 4-bit codes to f16 in registers with byte
+// permutes (no shared-memory round trip) straight into mma.sync A fragments, and multiplies by
+// the rotated queries held as B fragments.  The codebook of a symmetric density is symmetric,
+// so a code is stored as sign + 3-bit magnitude and the 8 magnitudes fit the two 8-byte pools of
+// a byte permute.
+#include "turboquant.cuh"
+
+#include "common.cuh"
+
+namespace eosb {
+
+namespace {
+
+typedef unsigned long long u64;
+
+// ------------------------------------------------------------------------------------------
+// packing
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ int highest_pow2_le(int v) {
+    int p = 1;
+    while ((p << 1) <= v) p <<= 1;
+    return p;
+}
+
+// In-place blocked normalised FWHT of `work` (shared memory) by one warp.  Butterflies are
+// a+b / a-b in float exactly as the sequential form; their order inside a stage is irrelevant.
+__device__ void warp_fwht_blocks(float* work, int dim, int lane) {
+    int offset = 0, remaining = dim;
+    while (remaining > 0) {
+        const int size = highest_pow2_le(remaining);
+        float* v = work + offset;
+        for (int step = 1; step < size; step <<= 1) {
+            for (int p = lane; p < (size >> 1); p += 32) {
+                const int j = ((p / step) * (step << 1)) + (p % step);
+                const float a = v[j], b = v[j + step];
+                v[j] = __fadd_rn(a, b);
+                v[j + step] = __fsub_rn(a, b);
+            }
+            __syncwarp();
+        }
+        if (size > 1) {
+            const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)size));
+            for (int i = lane; i < size; i += 32) v[i] = __fmul_rn(v[i], scale);
+            __syncwarp();
+        }
+        offset += size;
+        remaining -= size;
+    }
+}
+
+// rotated[perm[i]] = FWHT(x[perm[.]] * prescale * signs1)[i] * signs2[i]; x and the result live in
+// shared memory (work, rot), one warp.
+__device__ void warp_rotate(const float* x, float prescale, const TqSpec& s, float* work, float* rot, int lane) {
+    for (int i = lane; i < s.dim; i += 32) work[i] = __fmul_rn(__fmul_rn(x[s.perm[i]], prescale), s.signs1[i]);
+    __syncwarp();
+    warp_fwht_blocks(work, s.dim, lane);
+    for (int i = lane; i < s.dim; i += 32) rot[s.perm[i]] = __fmul_rn(work[i], s.signs2[i]);
+    __syncwarp();
+}
+
+__global__ void __launch_bounds__(256)
+tq_pack_kernel(const float* __restrict__ x, long long n, TqSpec s, uint8_t* __restrict__ codes,
+               float* __restrict__ norms) {
+    extern __shared__ float sm_f[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warps = blockDim.x >> 5;
+    float* work = sm_f + (size_t)warp * 2 * s.dim;
+    float* rot = work + s.dim;
+    const int levels = 1 << s.bits;
+    const int per_byte = 8 / s.bits;
+    const long long cb = ((long long)s.dim * s.bits + 7) / 8;
+    for (long long v = (long long)blockIdx.x * warps + warp; v < n; v += (long long)gridDim.x * warps) {
+        const float* xv = x + v * s.dim;
+        // sequential float sum of squares (the order the reference's one-thread-per-vector kernel uses)
+        float norm = 0.f;
+        if (lane == 0) {
+            float sq = 0.f;
+            for (int c = 0; c < s.dim; ++c) sq = __fadd_rn(sq, __fmul_rn(xv[c], xv[c]));
+            norm = __fsqrt_rn(sq);
+        }
+        norm = __shfl_sync(0xffffffffu, norm, 0);
+        const float scale = norm > 1.0e-12f ? __fdiv_rn(1.0f, norm) : 1.0f;
+        warp_rotate(xv, scale, s, work, rot, lane);
+        uint8_t* cv = codes + v * cb;
+        for (long long byte = lane; byte < cb; byte += 32) {
+            unsigned out = 0;
+            for (int e = 0; e < per_byte; ++e) {
+                const int c = (int)byte * per_byte + e;
+                if (c < s.dim) {
+                    const float val = rot[c];
+                    int lo = 0, hi = levels - 1;
+                    while (lo < hi) {
+                        const int mid = (lo + hi) >> 1;
+                        if (s.boundaries[mid] > val) hi = mid; else lo = mid + 1;
+                    }
+                    out |= (unsigned)lo << (e * s.bits);
+                }
+            }
+            cv[byte] = (uint8_t)out;
+        }
+        if (lane == 0) norms[v] = norm;
+        __syncwarp();
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// scan layout.  A tile = 16 documents.  For chunk c (128 coordinates = 8 MMA k-steps), lane
+// (g = lane/4, t = lane%4) owns 32 bytes at tile + c*1024 + lane*32: a uint4 for document g and
+// a uint4 for document g+8.  Word i of a uint4 covers k-steps 8c+2i and 8c+2i+1; its element
+// e = 2q+h (q = 0..3, h = 0,1) is coordinate 16*(8c+2i+(q>>1)) + 2t + 8*(q&1) + h, magnitude
+// index in bits [4e, 4e+3), sign (1 = negative) in bit 3 + 4q + 16h.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ int scan_coord(int c, int i, int t, int e) {
+    const int q = e >> 1, h = e & 1;
+    return 16 * (8 * c + 2 * i + (q >> 1)) + 2 * t + 8 * (q & 1) + h;
+}
+
+__global__ void __launch_bounds__(256)
+tq_transcode_kernel(const uint8_t* __restrict__ codes, long long n, int dim, int bits, uint32_t* __restrict__ tiles) {
+    const int chunks = (dim + kTqChunkCoords - 1) / kTqChunkCoords;
+    const long long words_per_tile = (long long)chunks * 32 * 8;  // 8 words per lane per chunk
+    const long long n_tiles = (n + kTqDocsPerTile - 1) / kTqDocsPerTile;
+    const long long total = n_tiles * words_per_tile;
+    const int half_levels = 1 << (bits - 1);
+    const int per_byte = 8 / bits;
+    const int code_mask = (1 << bits) - 1;
+    const long long cb = ((long long)dim * bits + 7) / 8;
+    for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < total;
+         w += (long long)gridDim.x * blockDim.x) {
+        const long long tile = w / words_per_tile;
+        const int r = (int)(w % words_per_tile);
+        const int c = r / 256;
+        const int lane = (r % 256) / 8;
+        const int sub = r % 8;  // 0..3: document g, 4..7: document g+8
+        const int i = sub & 3;
+        const int g = lane >> 2, t = lane & 3;
+        const long long doc = tile * kTqDocsPerTile + g + (sub >> 2) * 8;
+        uint32_t out = 0;
+        if (doc < n) {
+            const uint8_t* cv = codes + doc * cb;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int coord = scan_coord(c, i, t, e);
+                if (coord < dim) {
+                    const int code = (cv[coord / per_byte] >> ((coord % per_byte) * bits)) & code_mask;
+                    const int neg = code < half_levels;
+                    const int mag = neg ? (half_levels - 1 - code) : (code - half_levels);
+                    out |= (uint32_t)mag << (4 * e);
+                    out |= (uint32_t)neg << (3 + 4 * (e >> 1) + 16 * (e & 1));
+                }
+            }
+        }
+        tiles[w] = out;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// query preparation: rotate, round to f16, lay out as mma.sync B fragments.
+// bfrag[(tile*ksteps + s)*32 + lane] = { half2(q[16s+2t], q[16s+2t+1]), half2(q[16s+2t+8], q[16s+2t+9]) }
+// for query tile*8 + g.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+tq_prepare_kernel(const float* __restrict__ queries, int nq, int q_fill, TqSpec s, int ksteps,
+                  uint2* __restrict__ bfrag, float* __restrict__ rotated_out) {
+    extern __shared__ float sm_f[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warps = blockDim.x >> 5;
+    float* xin = sm_f + (size_t)warp * 3 * s.dim;
+    float* work = xin + s.dim;
+    float* rot = work + s.dim;
+    const int q_padded = q_fill;
+    for (int q = blockIdx.x * warps + warp; q < q_padded; q += gridDim.x * warps) {
+        if (q < nq) {
+            for (int i = lane; i < s.dim; i += 32) xin[i] = queries[(size_t)q * s.dim + i];
+            __syncwarp();
+            warp_rotate(xin, 1.0f, s, work, rot, lane);
+            if (rotated_out != nullptr)
+                for (int i = lane; i < s.dim; i += 32) rotated_out[(size_t)q * s.dim + i] = rot[i];
+        } else {
+            for (int i = lane; i < s.dim; i += 32) rot[i] = 0.f;  // padding queries score 0
+            __syncwarp();
+        }
+        const int tile = q >> 3, g = q & 7;
+        for (int idx = lane; idx < ksteps * 4; idx += 32) {
+            const int st = idx >> 2, t = idx & 3;
+            const int c0 = 16 * st + 2 * t;
+            float v[4];
+            const int cc[4] = {c0, c0 + 1, c0 + 8, c0 + 9};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = cc[e] < s.dim ? rot[cc[e]] : 0.f;
+            __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+            uint2 o;
+            o.x = *reinterpret_cast<uint32_t*>(&h0);
+            o.y = *reinterpret_cast<uint32_t*>(&h1);
+            bfrag[((size_t)tile * ksteps + st) * 32 + g * 4 + t] = o;
+        }
+        __syncwarp();
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// keys: (order-preserving score bits << 32) | (0xffffffff - doc index): larger key = better
+// candidate under "score descending, then id ascending"; 0 = empty.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t float_to_ordered(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float ordered_to_float(uint32_t o) {
+    return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
+}
+__device__ __forceinline__ u64 make_key(float score, uint32_t doc) {
+    return ((u64)float_to_ordered(score) << 32) | (u64)(0xffffffffu - doc);
+}
+
+// Radix-select the k-th largest of keys[0..n) (distinct, n > k >= 1) with one warp.
+// hist: 256 counters of shared memory owned by the warp.
+__device__ u64 warp_kth_largest(const u64* keys, int n, int k, unsigned* hist, int lane) {
+    u64 prefix = 0, mask = 0;
+    unsigned want = (unsigned)k;
+    for (int shift = 56; shift >= 0; shift -= 8) {
+        for (int i = lane; i < 256; i += 32) hist[i] = 0;
+        __syncwarp();
+        for (int i = lane; i < n; i += 32) {
+            const u64 key = keys[i];
+            if ((key & mask) == prefix) atomicAdd(&hist[(unsigned)(key >> shift) & 0xffu], 1u);
+        }
+        __syncwarp();
+        unsigned c[8], s = 0;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            c[b] = hist[lane * 8 + b];
+            s += c[b];
+        }
+        unsigned incl = s;  // sum over lanes >= this one (higher lanes own higher digits)
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned tmp = __shfl_down_sync(0xffffffffu, incl, o);
+            if (lane + o < 32) incl += tmp;
+        }
+        const unsigned above = incl - s;
+        const bool mine = (above < want) && (want <= incl);
+        int d = 0;
+        unsigned next_want = 0;
+        if (mine) {
+            unsigned run = above;
+#pragma unroll
+            for (int b = 7; b >= 0; --b) {
+                if (next_want == 0) {
+                    if (run + c[b] >= want) {
+                        d = lane * 8 + b;
+                        next_want = want - run;
+                    } else {
+                        run += c[b];
+                    }
+                }
+            }
+        }
+        const unsigned bal = __ballot_sync(0xffffffffu, mine);
+        const int src = bal ? (__ffs(bal) - 1) : 0;
+        d = __shfl_sync(0xffffffffu, d, src);
+        want = __shfl_sync(0xffffffffu, next_want, src);
+        prefix |= (u64)(unsigned)d << shift;
+        mask |= (u64)0xffu << shift;
+        __syncwarp();
+    }
+    return prefix;
+}
+
+// ------------------------------------------------------------------------------------------
+// the scan
+// ------------------------------------------------------------------------------------------
+constexpr int kScanCap = kTqMaxK + kTqScanWarps * kTqDocsPerTile;  // 384 keys per query buffer
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 8 sign-magnitude nibbles -> 4 half2 (elements 0/1, 2/3, 4/5, 6/7)
+__device__ __forceinline__ void dequant8(uint32_t w, uint32_t hi_a, uint32_t hi_b, uint32_t lo_a, uint32_t lo_b,
+                                         uint32_t (&v)[4]) {
+    const uint32_t m = w & 0x77777777u;
+    const uint32_t mh = m >> 16;
+    const uint32_t h0 = __byte_perm(hi_a, hi_b, m), l0 = __byte_perm(lo_a, lo_b, m);
+    const uint32_t h1 = __byte_perm(hi_a, hi_b, mh), l1 = __byte_perm(lo_a, lo_b, mh);
+    v[0] = __byte_perm(l0, h0, 0x5140) ^ ((w << 12) & 0x80008000u);
+    v[1] = __byte_perm(l0, h0, 0x7362) ^ ((w << 8) & 0x80008000u);
+    v[2] = __byte_perm(l1, h1, 0x5140) ^ ((w << 4) & 0x80008000u);
+    v[3] = __byte_perm(l1, h1, 0x7362) ^ (w & 0x80008000u);
+}
+
+template <int J>
+__global__ void __launch_bounds__(kTqScanWarps * 32, 1) tq_scan_kernel(TqScanArgs a) {
+    extern __shared__ __align__(16) uint8_t sm_raw[];
+    constexpr int QB = 8 * J;
+    const int ksteps = tq_ksteps(a.dim);
+    const int chunks = ksteps / 8;
+    uint2* bfr = reinterpret_cast<uint2*>(sm_raw);                                  // [J][ksteps][32]
+    u64* buf = reinterpret_cast<u64*>(sm_raw + (size_t)J * ksteps * 32 * 8);        // [QB][kScanCap]
+    u64* tau = buf + (size_t)QB * kScanCap;                                          // [QB]
+    int* cnt = reinterpret_cast<int*>(tau + QB);                                     // [QB]
+    unsigned* hist = reinterpret_cast<unsigned*>(cnt + QB);                          // [warps][256]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    for (int i = threadIdx.x; i < J * ksteps * 32; i += blockDim.x) bfr[i] = a.bfrag[i];
+    for (int i = threadIdx.x; i < QB; i += blockDim.x) {
+        tau[i] = 0;
+        cnt[i] = 0;
+    }
+    __syncthreads();
+
+    const long long n_tiles = (a.n_docs + kTqDocsPerTile - 1) / kTqDocsPerTile;
+    const size_t tile_u4 = (size_t)chunks * 64;  // uint4 per tile
+    const uint4* tiles = reinterpret_cast<const uint4*>(a.tiles);
+    const long long stride_tiles = (long long)gridDim.x * kTqScanWarps;
+    const long long iters = (n_tiles + stride_tiles - 1) / stride_tiles;
+    volatile u64* vtau = tau;
+
+    for (long long it = 0; it < iters; ++it) {
+        const long long tile = it * stride_tiles + (long long)blockIdx.x * kTqScanWarps + warp;
+        if (tile < n_tiles) {
+            const uint4* tp = tiles + tile * tile_u4 + lane * 2;
+            float acc[J][4];
+#pragma unroll
+            for (int j = 0; j < J; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+            uint4 da = __ldg(tp), db = __ldg(tp + 1);
+            for (int c = 0; c < chunks; ++c) {
+                const uint4 ca = da, cb = db;
+                if (c + 1 < chunks) {
+                    da = __ldg(tp + (c + 1) * 64);
+                    db = __ldg(tp + (c + 1) * 64 + 1);
+                }
+                const uint32_t wa[4] = {ca.x, ca.y, ca.z, ca.w};
+                const uint32_t wb[4] = {cb.x, cb.y, cb.z, cb.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t va[4], vb[4];
+                    dequant8(wa[i], a.mag_hi[0], a.mag_hi[1], a.mag_lo[0], a.mag_lo[1], va);
+                    dequant8(wb[i], a.mag_hi[0], a.mag_hi[1], a.mag_lo[0], a.mag_lo[1], vb);
+                    const int s0 = c * 8 + 2 * i;
+#pragma unroll
+                    for (int j = 0; j < J; ++j) {
+                        const uint2 b0 = bfr[(j * ksteps + s0) * 32 + lane];
+                        const uint2 b1 = bfr[(j * ksteps + s0 + 1) * 32 + lane];
+                        mma16816(acc[j], va[0], vb[0], va[1], vb[1], b0.x, b0.y);
+                        mma16816(acc[j], va[2], vb[2], va[3], vb[3], b1.x, b1.y);
+                    }
+                }
+            }
+            // epilogue: scale by the document norms, keep candidates that beat the running k-th
+            const long long d0 = tile * kTqDocsPerTile + g;
+            const long long d1 = d0 + 8;
+            const float n0 = d0 < a.n_docs ? __ldg(a.norms + d0) : 0.f;
+            const float n1 = d1 < a.n_docs ? __ldg(a.norms + d1) : 0.f;
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const long long doc = (e & 2) ? d1 : d0;
+                    if (doc < a.n_docs) {
+                        const int q = j * 8 + 2 * t + (e & 1);
+                        const float sc = acc[j][e] * ((e & 2) ? n1 : n0);
+                        if (a.all_scores != nullptr) {
+                            a.all_scores[(long long)q * a.all_stride + doc] = sc;
+                            continue;
+                        }
+                        const u64 key = make_key(sc, a.id_base + (uint32_t)doc);
+                        if (key > vtau[q]) {
+                            const int pos = atomicAdd(&cnt[q], 1);
+                            buf[(size_t)q * kScanCap + pos] = key;  // pos < kScanCap by construction
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        // buffers that could overflow in the next round are cut back to their k best
+        for (int q = warp; q < QB; q += kTqScanWarps) {
+            const int n = cnt[q];
+            if (n > kTqMaxK) {
+                u64* keys = buf + (size_t)q * kScanCap;
+                const u64 thr = warp_kth_largest(keys, n, a.k, hist + warp * 256, lane);
+                u64 mine[kScanCap / 32];
+#pragma unroll
+                for (int r = 0; r < kScanCap / 32; ++r) {
+                    const int i = r * 32 + lane;
+                    mine[r] = i < n ? keys[i] : 0;
+                }
+                __syncwarp();
+                int base = 0;
+#pragma unroll
+                for (int r = 0; r < kScanCap / 32; ++r) {
+                    const bool keep = mine[r] >= thr && mine[r] != 0;
+                    const unsigned bal = __ballot_sync(0xffffffffu, keep);
+                    if (keep) keys[base + __popc(bal & ((1u << lane) - 1u))] = mine[r];
+                    base += __popc(bal);
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    cnt[q] = base;
+                    tau[q] = thr;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (a.all_scores != nullptr) return;
+    // final cut to k and write-out
+    for (int q = warp; q < QB; q += kTqScanWarps) {
+        int n = cnt[q];
+        u64* keys = buf + (size_t)q * kScanCap;
+        u64 thr = 0;
+        if (n > a.k) thr = warp_kth_largest(keys, n, a.k, hist + warp * 256, lane);
+        u64* out = reinterpret_cast<u64*>(a.cand_keys) + ((size_t)q * a.grid + blockIdx.x) * kTqMaxK;
+        int base = 0;
+        for (int r = 0; r < kScanCap / 32; ++r) {
+            const int i = r * 32 + lane;
+            const u64 key = i < n ? keys[i] : 0;
+            const bool keep = key != 0 && key >= thr;
+            const unsigned bal = __ballot_sync(0xffffffffu, keep);
+            if (keep) out[base + __popc(bal & ((1u << lane) - 1u))] = key;
+            base += __popc(bal);
+        }
+        if (lane == 0) a.cand_count[(size_t)q * a.grid + blockIdx.x] = base;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// merge: one CTA per query; block-wide radix select of the k-th largest key over all candidate
+// segments (read from global / L2), gather of the survivors, bitonic sort by one warp.
+// ------------------------------------------------------------------------------------------
+constexpr int kMergeThreads = 512;
+
+__global__ void __launch_bounds__(kMergeThreads)
+tq_merge_kernel(const u64* __restrict__ cand, long long query_stride, long long seg_stride, int n_segs, int seg_len,
+                const int* __restrict__ counts, int k, long long id_base, long long* __restrict__ out_ids,
+                float* __restrict__ out_scores, u64* __restrict__ out_keys) {
+    __shared__ unsigned hist[256];
+    __shared__ u64 s_prefix, s_mask;
+    __shared__ unsigned s_want;
+    __shared__ int s_total, s_fill;
+    __shared__ u64 sel[kTqMaxK];
+    const int qi = blockIdx.x;
+    const u64* base = cand + (long long)qi * query_stride;
+    const int* cnts = counts != nullptr ? counts + (long long)qi * n_segs : nullptr;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long total_slots = (long long)n_segs * seg_len;
+
+    auto key_at = [&](long long slot) -> u64 {
+        const int seg = (int)(slot / seg_len), off = (int)(slot % seg_len);
+        if (cnts != nullptr && off >= cnts[seg]) return 0;
+        return base[(long long)seg * seg_stride + off];
+    };
+
+    // number of non-empty candidates
+    if (threadIdx.x == 0) {
+        s_total = 0;
+        s_fill = 0;
+    }
+    for (int i = threadIdx.x; i < kTqMaxK; i += blockDim.x) sel[i] = 0;
+    __syncthreads();
+    int local = 0;
+    for (long long s = threadIdx.x; s < total_slots; s += blockDim.x) local += key_at(s) != 0;
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+    if (lane == 0 && local) atomicAdd(&s_total, local);
+    __syncthreads();
+    const int total = s_total;
+    const int kk = total < k ? total : k;
+    u64 thr = 1;  // keep every non-empty key
+    if (total > k) {
+        if (threadIdx.x == 0) {
+            s_prefix = 0;
+            s_mask = 0;
+            s_want = (unsigned)k;
+        }
+        for (int shift = 56; shift >= 0; shift -= 8) {
+            for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+            __syncthreads();
+            const u64 prefix = s_prefix, mask = s_mask;
+            for (long long s = threadIdx.x; s < total_slots; s += blockDim.x) {
+                const u64 key = key_at(s);
+                if (key != 0 && (key & mask) == prefix) atomicAdd(&hist[(unsigned)(key >> shift) & 0xffu], 1u);
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                unsigned run = 0, want = s_want;
+                int d = 0;
+                for (int b = 255; b >= 0; --b) {
+                    if (run + hist[b] >= want) {
+                        d = b;
+                        break;
+                    }
+                    run += hist[b];
+                }
+                s_want = want - run;
+                s_prefix = prefix | ((u64)(unsigned)d << shift);
+                s_mask = mask | ((u64)0xffu << shift);
+            }
+            __syncthreads();
+        }
+        thr = s_prefix;
+    }
+    for (long long s = threadIdx.x; s < total_slots; s += blockDim.x) {
+        const u64 key = key_at(s);
+        if (key != 0 && key >= thr) {
+            const int pos = atomicAdd(&s_fill, 1);
+            if (pos < kTqMaxK) sel[pos] = key;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // bitonic sort of 128 keys, descending; empty slots (0) sink to the end
+        for (int size = 2; size <= kTqMaxK; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                for (int tt = lane; tt < kTqMaxK / 2; tt += 32) {
+                    const int i = 2 * tt - (tt & (stride - 1));
+                    const int j = i + stride;
+                    const bool desc = (i & size) == 0;
+                    const u64 x = sel[i], y = sel[j];
+                    if ((x < y) == desc) {
+                        sel[i] = y;
+                        sel[j] = x;
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        for (int i = lane; i < k; i += 32) {
+            const u64 key = i < kk ? sel[i] : 0;
+            if (out_keys != nullptr) out_keys[(long long)qi * k + i] = key;
+            if (out_ids != nullptr) {
+                out_ids[(long long)qi * k + i] =
+                    key != 0 ? id_base + (long long)(0xffffffffu - (uint32_t)(key & 0xffffffffu)) : -1;
+                out_scores[(long long)qi * k + i] = key != 0 ? ordered_to_float((uint32_t)(key >> 32)) : -INFINITY;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// multi-vector parents (runtime/retrieval_multivector_turboquant.go:746-810): per (row, parent)
+// the 5 best child scores in descending order, then the aggregate.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+parent_agg_kernel(const float* __restrict__ scores, long long stride, int rows, const int* __restrict__ child_order,
+                  const int* __restrict__ offsets, int parents, int top_n, double penalty, float* __restrict__ agg) {
+    const long long total = (long long)rows * parents;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / parents), p = (int)(i % parents);
+        const int c0 = offsets[p], c1 = offsets[p + 1];
+        float top[5];
+        int kept = 0;
+        const float* sr = scores + (long long)row * stride;
+        for (int c = c0; c < c1; ++c) {
+            const float sc = sr[child_order[c]];
+            if (kept < 5) {
+                top[kept++] = sc;
+            } else if (sc > top[4]) {
+                top[4] = sc;
+            } else {
+                continue;
+            }
+            for (int j = kept - 1; j > 0 && top[j] > top[j - 1]; --j) {
+                const float t = top[j];
+                top[j] = top[j - 1];
+                top[j - 1] = t;
+            }
+        }
+        float out = 0.f;
+        if (kept > 0) {
+            int avail = top_n <= 0 ? 1 : top_n;
+            if (avail > kept) avail = kept;
+            double sum = 0.0;
+            for (int j = 0; j < avail; ++j) sum += (double)top[j];
+            double sc = sum / (double)avail;
+            if (penalty != 0.0) sc -= penalty * log1p((double)(c1 - c0));
+            out = (float)sc;
+        }
+        agg[i] = out;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+parent_key_kernel(const float* __restrict__ agg, int rows, const int* __restrict__ offsets, int parents,
+                  u64* __restrict__ keys) {
+    for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < parents; p += gridDim.x * blockDim.x) {
+        if (offsets[p + 1] == offsets[p]) {
+            keys[p] = 0;
+            continue;
+        }
+        float sum = agg[p];
+        for (int r = 1; r < rows; ++r) sum += agg[(long long)r * parents + p];
+        keys[p] = make_key(sum, (uint32_t)p);
+    }
+}
+
+}  // namespace
+
+void launch_parent_keys(const float* scores, long long stride, int rows, const int* child_order, const int* offsets,
+                        int parents, int top_n, double penalty, float* agg_scratch, uint64_t* keys,
+                        cudaStream_t stream) {
+    parent_agg_kernel<<<148 * 8, 256, 0, stream>>>(scores, stride, rows, child_order, offsets, parents, top_n, penalty,
+                                                   agg_scratch);
+    parent_key_kernel<<<(parents + 255) / 256, 256, 0, stream>>>(agg_scratch, rows, offsets, parents,
+                                                                 reinterpret_cast<u64*>(keys));
+}
+
+void launch_tq_pack(const float* x, int64_t n, const TqSpec& spec, uint8_t* codes, float* norms,
+                    cudaStream_t stream) {
+    if (n <= 0) return;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * 2 * spec.dim * sizeof(float);
+    long long blocks = (n + warps - 1) / warps;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    tq_pack_kernel<<<(int)blocks, warps * 32, smem, stream>>>(x, (long long)n, spec, codes, norms);
+}
+
+void launch_tq_transcode(const uint8_t* codes, int64_t n, int dim, int bits, uint8_t* tiles, cudaStream_t stream) {
+    if (n <= 0) return;
+    tq_transcode_kernel<<<148 * 8, 256, 0, stream>>>(codes, (long long)n, dim, bits,
+                                                     reinterpret_cast<uint32_t*>(tiles));
+}
+
+void launch_tq_prepare(const float* queries, int q, int q_fill, const TqSpec& spec, uint2* bfrag, float* rotated_out,
+                       cudaStream_t stream) {
+    if (q <= 0) return;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * 3 * spec.dim * sizeof(float);
+    const int q_padded = q_fill;
+    int blocks = (q_padded + warps - 1) / warps;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    tq_prepare_kernel<<<blocks, warps * 32, smem, stream>>>(queries, q, q_fill, spec, tq_ksteps(spec.dim), bfrag,
+                                                            rotated_out);
+}
+
+size_t tq_scan_smem_bytes(int query_tiles, int dim) {
+    if (query_tiles != 1 && query_tiles != 2 && query_tiles != 4) return 0;
+    const int qb = 8 * query_tiles;
+    return (size_t)query_tiles * tq_ksteps(dim) * 32 * 8 + (size_t)qb * kScanCap * 8 + (size_t)qb * 8 +
+           (size_t)qb * 4 + (size_t)kTqScanWarps * 256 * 4;
+}
+
+cudaError_t tq_scan_init() {
+    const int max_smem = 200 * 1024;
+    cudaError_t e = cudaFuncSetAttribute(tq_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tq_scan_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tq_scan_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tq_pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tq_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    return e;
+}
+
+void launch_tq_scan(const TqScanArgs& a, cudaStream_t stream) {
+    const size_t smem = tq_scan_smem_bytes(a.query_tiles, a.dim);
+    const int threads = kTqScanWarps * 32;
+    if (a.query_tiles == 1) tq_scan_kernel<1><<<a.grid, threads, smem, stream>>>(a);
+    else if (a.query_tiles == 2) tq_scan_kernel<2><<<a.grid, threads, smem, stream>>>(a);
+    else tq_scan_kernel<4><<<a.grid, threads, smem, stream>>>(a);
+}
+
+cudaError_t tq_merge_init() { return cudaSuccess; }
+
+void launch_tq_merge(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,
+                     const int* counts, int queries, int k, int64_t id_base, int64_t* out_ids, float* out_scores,
+                     uint64_t* out_keys, cudaStream_t stream) {
+    if (queries <= 0) return;
+    tq_merge_kernel<<<queries, kMergeThreads, 0, stream>>>(
+        reinterpret_cast<const u64*>(cand), (long long)query_stride, (long long)seg_stride, n_segs, seg_len, counts,
+        k, (long long)id_base, reinterpret_cast<long long*>(out_ids), out_scores, reinterpret_cast<u64*>(out_keys));
+}
+
+}  // namespace eosb

@@ -1,0 +1,85 @@
+// Launchers of the TurboQuant kernels (turboquant.cu): Hadamard/MSE code packing, the scan
+// layout, query preparation, the scoring scan with per-CTA exact top-k and the merge.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace eosb {
+
+// Rotation + codebook of one quantiser, device resident.  Same fields the reference's
+// turboquant Spec() exposes (runtime/backends/cuda/native_linux.go:9532-9545).
+struct TqSpec {
+    int dim;
+    int bits;
+    const int* perm;          // [dim]
+    const float* signs1;      // [dim]
+    const float* signs2;      // [dim]
+    const float* centroids;   // [2^bits] ascending
+    const float* boundaries;  // [2^bits - 1]
+};
+
+constexpr int kTqDocsPerTile = 16;   // documents per scan tile (one m16 MMA row block)
+constexpr int kTqChunkCoords = 128;  // coordinates per 16-byte code chunk group (8 k-steps of 16)
+constexpr int kTqMaxK = 128;         // largest k of the fused top-k
+constexpr int kTqScanWarps = 16;
+
+// bytes of one scan tile: 16 documents x padded_dim/2 bytes
+inline size_t tq_tile_bytes(int dim) {
+    const int padded = (dim + kTqChunkCoords - 1) / kTqChunkCoords * kTqChunkCoords;
+    return (size_t)kTqDocsPerTile * padded / 2;
+}
+__host__ __device__ inline int tq_ksteps(int dim) { return (dim + kTqChunkCoords - 1) / kTqChunkCoords * (kTqChunkCoords / 16); }
+
+// x [n, dim] fp32 -> packed codes [n, dim*bits/8] (low bits first) + fp32 norms [n].
+void launch_tq_pack(const float* x, int64_t n, const TqSpec& spec, uint8_t* codes, float* norms,
+                    cudaStream_t stream);
+
+// reference-format codes -> scan tiles (sign-magnitude nibbles in MMA fragment order).
+void launch_tq_transcode(const uint8_t* codes, int64_t n, int dim, int bits, uint8_t* tiles, cudaStream_t stream);
+
+// queries [q, dim] fp32 -> rotated f16 B fragments [ceil(q/8)][ksteps][32 lanes] x 8 bytes;
+// also the rotated fp32 queries when rotated_out != null.
+// Fragments are written for q_fill >= q queries (a multiple of 8); queries past q are zeros.
+void launch_tq_prepare(const float* queries, int q, int q_fill, const TqSpec& spec, uint2* bfrag, float* rotated_out,
+                       cudaStream_t stream);
+
+// keys[p] = sortable key of (sum over `rows` of the per-row parent aggregate, parent id p):
+// per row and parent the mean of the best min(top_n, 5, children) child scores minus
+// penalty * log1p(children); parents without children get key 0.  child_order lists children
+// grouped by parent, offsets [parents + 1]; scores is [rows][stride].
+void launch_parent_keys(const float* scores, long long stride, int rows, const int* child_order, const int* offsets,
+                        int parents, int top_n, double penalty, float* agg_scratch, uint64_t* keys,
+                        cudaStream_t stream);
+
+struct TqScanArgs {
+    const uint8_t* tiles;
+    const float* norms;
+    int64_t n_docs;
+    uint32_t id_base;      // document id of row 0 (ids are carried inside the candidate keys)
+    int dim;
+    const uint2* bfrag;    // fragments of the first query tile of this pass
+    int query_tiles;       // 1, 2 or 4 tiles of 8 queries scored per corpus pass
+    int k;
+    uint32_t mag_hi[2];    // high / low bytes of the f16 magnitude table (8 entries)
+    uint32_t mag_lo[2];
+    uint64_t* cand_keys;   // [query_tiles*8][grid][kTqMaxK]
+    int* cand_count;       // [query_tiles*8][grid]
+    int grid;
+    float* all_scores;     // when non-null: every score is stored at all_scores[q * all_stride + doc]
+    long long all_stride;  // and the top-k bookkeeping is skipped
+};
+// Returns the dynamic shared memory the configuration needs (0 = unsupported).
+size_t tq_scan_smem_bytes(int query_tiles, int dim);
+cudaError_t tq_scan_init();
+void launch_tq_scan(const TqScanArgs& a, cudaStream_t stream);
+
+// For every query: the k best of n_segs x seg_len candidate keys (key 0 = empty), sorted by
+// score descending then id ascending.  cand is [queries][n_segs][seg_len] with the given
+// strides (in keys).  counts, when non-null, is [queries][n_segs] entries in use.
+void launch_tq_merge(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,
+                     const int* counts, int queries, int k, int64_t id_base, int64_t* out_ids, float* out_scores,
+                     uint64_t* out_keys, cudaStream_t stream);
+cudaError_t tq_merge_init();
+
+}  // namespace eosb

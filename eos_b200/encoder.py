@@ -1,0 +1,254 @@
+"""Host-side mirror of the reference's encoder interfaces over the C ABI.
+
+BertEmbedder   <- StepBERTEmbedder / BERTEmbedderReferenceWithPooling
+                  (runtime/backend/bert_embedder_ops.go:101-197): same tensor order
+                  (16 tensors per layer, runtime/pretrained_bert_importer.go:936-951), same attributes
+                  (num_attention_heads, epsilon, pooling), same error behaviour (out-of-range ids are
+                  an error, all-masked sequences give zero vectors).
+EmbedPooledPipeline <- the compiled pipeline examples/embed_masked_pooled.eos.
+linear         <- one dense projection with denseHF semantics
+                  (runtime/backend/bert_encoder_layer_ops.go:452-462).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence, Union
+
+import numpy as np
+
+from . import _lib
+from ._lib import EncoderDesc, EncoderLayer, Matrix, Stats
+
+ACT_GELU_ERF, ACT_GELU_TANH = 0, 1
+WEIGHTS_Q8_SMEM_DEQUANT, WEIGHTS_F16_RESIDENT = 0, 1
+EPILOGUE_NONE, EPILOGUE_GELU_ERF, EPILOGUE_RESIDUAL, EPILOGUE_GELU_TANH = 0, 1, 2, 3
+
+
+@dataclass
+class Q8Weight:
+    """int8 codes [out, in] + fp32 scales (1 = per tensor, out = per output channel); value = code * scale."""
+    codes: np.ndarray
+    scales: np.ndarray
+
+    def dequantized(self) -> np.ndarray:
+        s = np.asarray(self.scales, np.float32).reshape(-1)
+        c = np.asarray(self.codes, np.int8).astype(np.float32)
+        return c * (s[0] if s.size == 1 else s[:, None])
+
+
+Weight = Union[np.ndarray, Q8Weight]
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _ptr(a: Optional[np.ndarray]):
+    return None if a is None else a.ctypes.data
+
+
+class Runtime:
+    """One device + stream (newDeviceRuntime, runtime/backends/cuda/native_linux.go:3127)."""
+
+    def __init__(self, device: int = 0):
+        self.handle = C.c_void_p()
+        _lib.call("eos_b200_runtime_create", int(device), C.byref(self.handle))
+        self.device = int(device)
+
+    def info(self) -> dict:
+        out = _lib.DeviceInfo()
+        _lib.call("eos_b200_runtime_info", self.handle, C.byref(out))
+        return {"device": out.device, "cc": (out.cc_major, out.cc_minor), "sm_count": out.sm_count,
+                "total_memory_bytes": out.total_memory_bytes, "name": out.name.decode()}
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.lib().eos_b200_runtime_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _matrix(w: Weight, keep: list) -> Matrix:
+    m = Matrix()
+    if isinstance(w, Q8Weight):
+        codes = np.ascontiguousarray(w.codes, dtype=np.int8)
+        scales = _f32(w.scales).reshape(-1)
+        keep += [codes, scales]
+        m.rows, m.cols = codes.shape
+        m.q8_codes, m.q8_scales, m.n_scales = codes.ctypes.data, scales.ctypes.data, scales.size
+    else:
+        dense = _f32(w)
+        keep.append(dense)
+        m.rows, m.cols = dense.shape
+        m.dense = dense.ctypes.data
+    return m
+
+
+class BertEmbedder:
+    """q8 / dense BERT-family encoder bound to a device: embeddings -> layers -> pooling -> L2 (-> head -> L2)."""
+
+    def __init__(self, rt: Runtime, token_embeddings, position_embeddings, token_type_embeddings,
+                 embedding_ln_weight, embedding_ln_bias, layer_weights: Sequence[Weight], num_attention_heads: int,
+                 epsilon: float = 1e-12, pooling: str = "masked_mean", hidden_act: str = "gelu",
+                 head_weights=None, weight_mode: int = WEIGHTS_Q8_SMEM_DEQUANT, attention_window: int = 0):
+        if pooling not in ("masked_mean", "cls"):
+            raise ValueError(f"bert_embedder unsupported pooling {pooling!r}; supported values are masked_mean and cls")
+        if hidden_act not in ("gelu", "gelu_tanh"):
+            raise ValueError(f"bert_encoder_layer unsupported hidden_act {hidden_act!r}")
+        if len(layer_weights) == 0 or len(layer_weights) % 16 != 0:
+            raise ValueError(f"bert_embedder expects 16 tensors per encoder layer, got {len(layer_weights)}")
+        self.rt = rt
+        keep: list = []
+        tok, pos, typ = _f32(token_embeddings), _f32(position_embeddings), _f32(token_type_embeddings)
+        eg, eb = _f32(embedding_ln_weight), _f32(embedding_ln_bias)
+        keep += [tok, pos, typ, eg, eb]
+        layers = len(layer_weights) // 16
+        arr = (EncoderLayer * layers)()
+        for l in range(layers):
+            w = layer_weights[l * 16:(l + 1) * 16]
+            L = arr[l]
+            vec = {}
+            for idx, name in ((1, "query_bias"), (3, "key_bias"), (5, "value_bias"), (7, "attn_out_bias"),
+                              (8, "attn_ln_gamma"), (9, "attn_ln_beta"), (11, "inter_bias"), (13, "out_bias"),
+                              (14, "out_ln_gamma"), (15, "out_ln_beta")):
+                v = _f32(w[idx]).reshape(-1)
+                keep.append(v)
+                vec[name] = v
+                setattr(L, name, v.ctypes.data)
+            L.query, L.key, L.value = _matrix(w[0], keep), _matrix(w[2], keep), _matrix(w[4], keep)
+            L.attn_out, L.inter, L.out = _matrix(w[6], keep), _matrix(w[10], keep), _matrix(w[12], keep)
+            for name, mat in (("query_bias", L.query), ("key_bias", L.key), ("value_bias", L.value),
+                              ("attn_out_bias", L.attn_out), ("inter_bias", L.inter), ("out_bias", L.out)):
+                if vec[name].size != mat.rows:
+                    raise ValueError(f"bert_encoder_layer {name} shape {vec[name].shape} does not match [out]=[{mat.rows}]")
+        d = EncoderDesc()
+        d.layers, d.hidden, d.heads = layers, tok.shape[1], int(num_attention_heads)
+        d.intermediate = arr[0].inter.rows
+        d.vocab, d.max_positions, d.type_vocab = tok.shape[0], pos.shape[0], typ.shape[0]
+        d.activation = ACT_GELU_ERF if hidden_act == "gelu" else ACT_GELU_TANH
+        d.pooling = 1 if pooling == "cls" else 0
+        d.weight_mode = int(weight_mode)
+        d.attention_window = int(attention_window)
+        d.epsilon = float(epsilon)
+        d.token_embeddings, d.position_embeddings, d.type_embeddings = tok.ctypes.data, pos.ctypes.data, typ.ctypes.data
+        d.embedding_ln_gamma, d.embedding_ln_beta = eg.ctypes.data, eb.ctypes.data
+        d.layer = arr
+        self.out_dim = tok.shape[1]
+        if head_weights is not None:
+            hw = _f32(head_weights)
+            if hw.ndim != 2 or hw.shape[0] != tok.shape[1]:
+                raise ValueError("projection head input dimension mismatch")
+            keep.append(hw)
+            d.head_out, d.head_weights = hw.shape[1], hw.ctypes.data
+            self.out_dim = hw.shape[1]
+        if pos.shape[1] != tok.shape[1] or typ.shape[1] != tok.shape[1] or eg.size != tok.shape[1] or eb.size != tok.shape[1]:
+            raise ValueError("bert_embeddings tables disagree on the hidden size")
+        self.handle = C.c_void_p()
+        _lib.call("eos_b200_encoder_bind", rt.handle, C.byref(d), C.byref(self.handle))
+        self.hidden, self.layers, self.heads, self.intermediate = d.hidden, layers, d.heads, d.intermediate
+        self.last_stats = Stats()
+
+    def reserve(self, batch: int, tokens: int) -> None:
+        _lib.call("eos_b200_encoder_reserve", self.handle, int(batch), int(tokens))
+
+    def run(self, input_ids, attention_mask, token_type_ids=None) -> np.ndarray:
+        """Host buffers in, host buffer out ([B, E] fp32); copies are part of the call."""
+        ids, mask = _i32(input_ids), _i32(attention_mask)
+        if ids.ndim != 2:
+            raise ValueError(f"bert_embedder input_ids must be rank-2 [B,T], got shape {ids.shape}")
+        if mask.shape != ids.shape:
+            raise ValueError(f"bert_embedder attention_mask shape {mask.shape} does not match input_ids shape {ids.shape}")
+        types = None if token_type_ids is None else _i32(token_type_ids)
+        if types is not None and types.shape != ids.shape:
+            raise ValueError(f"bert_embedder token_type_ids shape {types.shape} does not match input_ids shape {ids.shape}")
+        out = np.empty((ids.shape[0], self.out_dim), dtype=np.float32)
+        _lib.call("eos_b200_encoder_run", self.handle, _ptr(ids), _ptr(mask), _ptr(types), ids.shape[0], ids.shape[1],
+                  _ptr(out), C.byref(self.last_stats))
+        return out
+
+    def run_device(self, d_ids: int, d_mask: int, d_types: Optional[int], batch: int, tokens: int, d_out: int,
+                   stream: Optional[int] = None) -> int:
+        """Device pointers in/out (ints), enqueued on `stream` without synchronising; returns kernels launched."""
+        st = Stats()
+        _lib.call("eos_b200_encoder_run_device", self.handle, d_ids, d_mask, d_types, int(batch), int(tokens), d_out,
+                  stream, C.byref(st))
+        return st.kernel_launches
+
+    def sync(self, stream: Optional[int] = None) -> None:
+        _lib.call("eos_b200_encoder_sync", self.handle, stream)
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.lib().eos_b200_encoder_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class EmbedPooledPipeline:
+    """gather -> matmul -> normalize -> masked mean_pool (examples/embed_masked_pooled.eos:11-16)."""
+
+    def __init__(self, rt: Runtime, token_embedding, projection):
+        table, proj = _f32(token_embedding), _f32(projection)
+        if table.ndim != 2 or proj.ndim != 2 or proj.shape[0] != table.shape[1]:
+            raise ValueError(f"matmul mismatch {table.shape} x {proj.shape}")
+        self.rt = rt
+        self.out_dim = proj.shape[1]
+        self.handle = C.c_void_p()
+        _lib.call("eos_b200_embed_pooled_bind", rt.handle, _ptr(table), table.shape[0], table.shape[1], _ptr(proj),
+                  proj.shape[1], C.byref(self.handle))
+        self.last_stats = Stats()
+
+    def run(self, tokens, attention_mask, pool_then_l2: bool = False) -> np.ndarray:
+        tok, mask = _i32(tokens), _i32(attention_mask)
+        if tok.ndim != 2 or tok.size == 0:
+            raise ValueError("embed_pooled_batch expects a non-empty [B,T] token tensor")
+        if mask.shape != tok.shape:
+            raise ValueError(f"mean_pool mask shape {mask.shape} does not match input {tok.shape}")
+        out = np.empty((tok.shape[0], self.out_dim), dtype=np.float32)
+        _lib.call("eos_b200_embed_pooled_run", self.handle, _ptr(tok), _ptr(mask), tok.shape[0], tok.shape[1],
+                  1 if pool_then_l2 else 0, _ptr(out), C.byref(self.last_stats))
+        return out
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.lib().eos_b200_embed_pooled_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def linear(rt: Runtime, x, weight: Weight, bias=None, epilogue: int = EPILOGUE_NONE, residual=None,
+           weight_mode: int = WEIGHTS_Q8_SMEM_DEQUANT, stats: Optional[Stats] = None) -> np.ndarray:
+    """y = epilogue(x W^T + b) through the tensor-core projection kernel; x, residual and y are f16-rounded."""
+    keep: list = []
+    xa = _f32(x)
+    m = _matrix(weight, keep)
+    if xa.shape[-1] != m.cols:
+        raise ValueError(f"dense weight shape [{m.rows},{m.cols}] does not match input width {xa.shape[-1]}")
+    rows = xa.size // m.cols
+    b = None if bias is None else _f32(bias)
+    r = None if residual is None else _f32(residual)
+    out = np.empty(xa.shape[:-1] + (m.rows,), dtype=np.float32)
+    st = stats if stats is not None else Stats()
+    _lib.call("eos_b200_linear", rt.handle, _ptr(xa), rows, C.byref(m), _ptr(b), int(epilogue), _ptr(r),
+              int(weight_mode), _ptr(out), C.byref(st))
+    return out

@@ -1,0 +1,216 @@
+"""Host-side mirror of the reference's TurboQuant retrieval interfaces over the C ABI.
+
+Quantizer.quantize      <- `for doc: q.Quantize(doc)`        runtime/retrieval_turboquant.go:700-711
+Corpus.score_topk       <- PrepareQuery + topTurboQuantRetrievalScoresWithStats  :1324-1325, 1853-1887
+Corpus.parent_topk      <- topTurboQuantMultiVectorParentScores  runtime/retrieval_multivector_turboquant.go:746-810
+RotationSpec            <- the fields of turboquant Spec() (runtime/backends/cuda/native_linux.go:9532-9545)
+
+The arithmetic of the reference's quantiser lives in the un-vendored module m31labs.dev/turboquant; the
+seeded permutation / sign generator and the Lloyd-Max tables below are this library's own (a Go host that owns
+the real module passes its own Spec instead).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import numpy as np
+
+from . import _lib
+from ._lib import Stats
+from .encoder import Runtime, _f32, _i32, _ptr
+
+DEFAULT_SEED = 0x4D756C7469566563  # runtime/retrieval_multivector_turboquant.go:18
+
+
+@dataclass
+class RotationSpec:
+    dim: int
+    bits: int
+    perm: np.ndarray        # int32 [dim]
+    signs1: np.ndarray      # float32 [dim], +-1
+    signs2: np.ndarray      # float32 [dim], +-1
+    centroids: np.ndarray   # float32 [2^bits], ascending, symmetric
+    boundaries: np.ndarray  # float32 [2^bits - 1]
+
+    @property
+    def code_bytes(self) -> int:
+        return (self.dim * self.bits + 7) // 8
+
+    @property
+    def vector_bytes(self) -> int:
+        """Packed bytes per vector incl. the f32 norm (runtime/turboquant_bytes.go:22-25 accounting)."""
+        return self.code_bytes + 4
+
+
+def _phi(x: float) -> float:
+    return math.exp(-0.5 * x * x) / math.sqrt(2.0 * math.pi)
+
+
+def _cdf(x: float) -> float:
+    return 0.5 * (1.0 + math.erf(x / math.sqrt(2.0)))
+
+
+def lloyd_max_gaussian(levels: int, sigma: float, iters: int = 500) -> Tuple[np.ndarray, np.ndarray]:
+    """Lloyd-Max scalar quantiser for N(0, sigma^2): (centroids[levels], boundaries[levels-1]) as float32.
+
+    Fixed-point iteration of centroid = E[x | cell], boundary = midpoint, in float64 on the unit normal; the
+    result is made exactly symmetric (c[L-1-i] = -c[i]) before rounding to float32.
+    """
+    c = np.array([(i + 0.5) / levels * 6.0 - 3.0 for i in range(levels)], dtype=np.float64)
+    for _ in range(iters):
+        b = (c[:-1] + c[1:]) / 2.0
+        edges = [-math.inf] + list(b) + [math.inf]
+        new = np.empty_like(c)
+        for i in range(levels):
+            lo, hi = edges[i], edges[i + 1]
+            p = _cdf(hi) - _cdf(lo)
+            new[i] = (_phi(lo) - _phi(hi)) / p if p > 0 else c[i]
+        if np.max(np.abs(new - c)) < 1e-14:
+            c = new
+            break
+        c = new
+    c = (c - c[::-1]) / 2.0
+    cf = (c * sigma).astype(np.float32)
+    cf[: levels // 2] = -cf[::-1][: levels // 2]
+    bf = ((cf[:-1].astype(np.float64) + cf[1:].astype(np.float64)) / 2.0).astype(np.float32)
+    return cf, bf
+
+
+def make_rotation_spec(dim: int, bits: int, seed: int = DEFAULT_SEED) -> RotationSpec:
+    """Seeded random-sign Hadamard rotation + Lloyd-Max codebook for N(0, 1/dim)."""
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(dim).astype(np.int32)
+    signs1 = rng.choice(np.array([-1.0, 1.0], dtype=np.float32), size=dim).astype(np.float32)
+    signs2 = rng.choice(np.array([-1.0, 1.0], dtype=np.float32), size=dim).astype(np.float32)
+    cent, bound = lloyd_max_gaussian(1 << bits, 1.0 / math.sqrt(dim))
+    return RotationSpec(dim, bits, perm, signs1, signs2, cent, bound)
+
+
+class Quantizer:
+    def __init__(self, rt: Runtime, spec: RotationSpec):
+        self.rt, self.spec = rt, spec
+        self._keep = [_i32(spec.perm), _f32(spec.signs1), _f32(spec.signs2), _f32(spec.centroids), _f32(spec.boundaries)]
+        if self._keep[0].size != spec.dim or self._keep[3].size != (1 << spec.bits) or \
+                self._keep[4].size != (1 << spec.bits) - 1:
+            raise ValueError("rotation spec arrays do not match dim / bits")
+        self.handle = C.c_void_p()
+        _lib.call("eos_b200_quantizer_create", rt.handle, spec.dim, spec.bits, *[_ptr(a) for a in self._keep],
+                  C.byref(self.handle))
+        self.last_stats = Stats()
+
+    def quantize(self, x) -> Tuple[np.ndarray, np.ndarray]:
+        """[n, dim] fp32 -> (codes uint8 [n, dim*bits/8], norms fp32 [n])."""
+        a = _f32(x)
+        if a.ndim != 2 or a.shape[1] != self.spec.dim or a.shape[0] == 0:
+            raise ValueError(f"quantize expects a non-empty [n, {self.spec.dim}] array, got {a.shape}")
+        codes = np.empty((a.shape[0], self.spec.code_bytes), dtype=np.uint8)
+        norms = np.empty(a.shape[0], dtype=np.float32)
+        _lib.call("eos_b200_quantize", self.handle, _ptr(a), a.shape[0], _ptr(codes), _ptr(norms),
+                  C.byref(self.last_stats))
+        return codes, norms
+
+    def quantize_device(self, d_x: int, n: int, d_codes: int, d_norms: int, stream: Optional[int] = None) -> None:
+        _lib.call("eos_b200_quantize_device", self.handle, d_x, int(n), d_codes, d_norms, stream)
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.lib().eos_b200_quantizer_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Corpus:
+    """Packed vectors resident on one GPU (one shard); row i has document id id_base + i."""
+
+    def __init__(self, quantizer: Quantizer, codes=None, norms=None, id_base: int = 0, allow_zero_norm: bool = False,
+                 device_ptrs: Optional[Tuple[int, int, int]] = None):
+        self.qz = quantizer
+        self.handle = C.c_void_p()
+        self.id_base = int(id_base)
+        if device_ptrs is not None:
+            d_codes, d_norms, n = device_ptrs
+            self.n = int(n)
+            _lib.call("eos_b200_corpus_bind_device", quantizer.handle, d_codes, d_norms, int(n), int(id_base),
+                      C.byref(self.handle))
+        else:
+            c = np.ascontiguousarray(codes, dtype=np.uint8)
+            nr = _f32(norms).reshape(-1)
+            if c.ndim != 2 or c.shape[1] != quantizer.spec.code_bytes or c.shape[0] != nr.size:
+                raise ValueError("corpus codes / norms do not match the quantizer")
+            self.n = c.shape[0]
+            _lib.call("eos_b200_corpus_bind", quantizer.handle, _ptr(c), _ptr(nr), c.shape[0], int(id_base),
+                      1 if allow_zero_norm else 0, C.byref(self.handle))
+        self.last_stats = Stats()
+
+    def score_topk(self, queries, k: int, queries_per_pass: int = 8) -> Tuple[np.ndarray, np.ndarray]:
+        """Exact top-k per query: (ids int64 [Q,k], scores fp32 [Q,k]); score desc, then id asc."""
+        q = _f32(queries)
+        if q.ndim != 2 or q.shape[1] != self.qz.spec.dim or q.shape[0] == 0:
+            raise ValueError(f"score_topk expects non-empty [Q, {self.qz.spec.dim}] queries, got {q.shape}")
+        ids = np.empty((q.shape[0], k), dtype=np.int64)
+        scores = np.empty((q.shape[0], k), dtype=np.float32)
+        _lib.call("eos_b200_score_topk", self.handle, _ptr(q), q.shape[0], int(k), int(queries_per_pass), _ptr(ids),
+                  _ptr(scores), C.byref(self.last_stats))
+        return ids, scores
+
+    def score_topk_device(self, d_queries: int, q_count: int, k: int, queries_per_pass: int, d_ids: Optional[int],
+                          d_scores: Optional[int], d_keys: Optional[int] = None, stream: Optional[int] = None) -> int:
+        st = Stats()
+        _lib.call("eos_b200_score_topk_device", self.handle, d_queries, int(q_count), int(k), int(queries_per_pass),
+                  d_ids, d_scores, d_keys, stream, C.byref(st))
+        return st.kernel_launches
+
+    def score_all(self, queries) -> np.ndarray:
+        q = _f32(queries)
+        out = np.empty((q.shape[0], self.n), dtype=np.float32)
+        _lib.call("eos_b200_score_all", self.handle, _ptr(q), q.shape[0], _ptr(out))
+        return out
+
+    def parent_topk(self, parent_of_child, parents: int, queries, k: int, query_group: int = 1, top_n: int = 1,
+                    penalty: float = 0.0) -> Tuple[np.ndarray, np.ndarray]:
+        p = _i32(parent_of_child).reshape(-1)
+        if p.size != self.n:
+            raise ValueError("parent_of_child must have one entry per corpus row")
+        q = _f32(queries)
+        groups = q.shape[0] // max(1, query_group)
+        ids = np.empty((groups, k), dtype=np.int64)
+        scores = np.empty((groups, k), dtype=np.float32)
+        _lib.call("eos_b200_parent_topk", self.handle, _ptr(p), int(parents), _ptr(q), q.shape[0], int(query_group),
+                  int(top_n), float(penalty), int(k), _ptr(ids), _ptr(scores), C.byref(self.last_stats))
+        return ids, scores
+
+    @property
+    def vector_bytes(self) -> int:
+        return int(_lib.lib().eos_b200_corpus_vector_bytes(self.handle))
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.lib().eos_b200_corpus_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def topk_merge_device(rt: Runtime, d_keys: int, shards: int, q_count: int, k: int, d_ids: int, d_scores: int,
+                      stream: Optional[int] = None) -> None:
+    """Global top-k from all-gathered per-shard key lists [shards, Q, k] (device pointers)."""
+    _lib.call("eos_b200_topk_merge_device", rt.handle, d_keys, int(shards), int(q_count), int(k), d_ids, d_scores,
+              stream)
+
+
+def synth_gaussian_device(rt: Runtime, seed: int, row_offset: int, n: int, dim: int, normalize: bool, d_out: int,
+                          stream: Optional[int] = None) -> None:
+    _lib.call("eos_b200_synth_gaussian_device", rt.handle, C.c_uint64(seed), int(row_offset), int(n), int(dim),
+              1 if normalize else 0, d_out, stream)

@@ -1,0 +1,264 @@
+/*
+ * eos_b200.h -- C ABI of libeos_b200.so: the B200 (sm_100a) implementation of Eos's query-time
+ * embed-and-score path.  Every entry point states which Eos interface it stands in for
+ * (path inside the Eos project : lines).
+ *
+ * Conventions (the ones of Eos's CGo CUDA bridge, runtime/backends/cuda/native_linux.go:1-1616
+ * and eos_cuda_abi.h:22-38):
+ *   - every call returns int: 0 = ok, 1 = failure, 2 = the device status word is non-zero
+ *     (bad token id and the like; native_linux.go:699-705, 8119-8127);
+ *   - on a non-zero return *err (when err != NULL) is a malloc'd, NUL-terminated message owned by
+ *     the caller and released with eos_b200_free_cstring (eosCudaFreeCString, :1378-1382);
+ *   - handles are opaque, C-allocated and explicitly destroyed; no caller pointer is retained
+ *     after a call returns (bind calls copy what they need to the device);
+ *   - every call makes its runtime's device current first, so calls may come from any OS thread
+ *     (the Go runtime migrates goroutines); one call in flight per handle, as the reference's
+ *     mutexes guarantee (runtime/backends/cuda/cuda.go:401-402);
+ *   - pointers named h_* are host memory, d_* device memory of the runtime's device;
+ *   - there is no CPU fallback: without a compute-capability 10.x device every call fails.
+ */
+#ifndef EOS_B200_H
+#define EOS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define EOS_B200_API __attribute__((visibility("default")))
+#else
+#define EOS_B200_API
+#endif
+
+#define EOS_B200_OK 0
+#define EOS_B200_ERROR 1
+#define EOS_B200_DEVICE_STATUS 2
+
+typedef struct EosB200Runtime EosB200Runtime;
+typedef struct EosB200Encoder EosB200Encoder;
+typedef struct EosB200EmbedPooled EosB200EmbedPooled;
+typedef struct EosB200Quantizer EosB200Quantizer;
+typedef struct EosB200Corpus EosB200Corpus;
+
+/* Accounting of one call; mirrors the fields of backend.ExecutionAccounting that the reference
+ * fills per run (runtime/backend/backend.go:1364-1400): launches, bytes moved, device time. */
+typedef struct {
+    int32_t kernel_launches;   /* kernels of this library launched by the call */
+    int32_t reserved;
+    int64_t uploaded_bytes;    /* host -> device */
+    int64_t downloaded_bytes;  /* device -> host */
+    int64_t valid_tokens;      /* encoder: rows actually computed (mask != 0) */
+    float device_ms;           /* CUDA-event time of the call's device work (0 for *_device calls) */
+    float reserved2;
+} EosB200Stats;
+
+typedef struct {
+    int32_t device;
+    int32_t cc_major, cc_minor;
+    int32_t sm_count;
+    int64_t total_memory_bytes;
+    char name[128];
+} EosB200DeviceInfo;
+
+/* ---------------------------------------------------------------------------------------------
+ * runtime
+ * ------------------------------------------------------------------------------------------- */
+
+/* Replaces newDeviceRuntime / eosCudaRuntimeCreate (native_linux.go:150-260, 3127): binds the
+ * device, creates one stream.  Fails unless the device is compute capability 10.x. */
+EOS_B200_API int eos_b200_runtime_create(int device, EosB200Runtime** out, char** err);
+EOS_B200_API void eos_b200_runtime_destroy(EosB200Runtime* rt);
+EOS_B200_API int eos_b200_runtime_info(EosB200Runtime* rt, EosB200DeviceInfo* out, char** err);
+/* eosCudaFreeCString, native_linux.go:1378-1382 */
+EOS_B200_API void eos_b200_free_cstring(char* s);
+EOS_B200_API const char* eos_b200_version(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * weights
+ * ------------------------------------------------------------------------------------------- */
+
+/* A dense weight in HF [out, in] layout (runtime/backend/bert_encoder_layer_ops.go:452-462).
+ * Either q8: int8 codes + scales with the grid of runtime/embedding_trainer.go:11413-11446 /
+ * runtime/weight_file.go:305-356 (value = code * scale; n_scales = 1 for the reference's
+ * per-tensor scale, = rows for per-output-channel scales), or dense fp32 values (rounded to f16
+ * on upload) when q8_codes is NULL. */
+typedef struct {
+    int32_t rows, cols;
+    const int8_t* q8_codes;
+    const float* q8_scales;
+    int32_t n_scales;
+    int32_t reserved;
+    const float* dense;
+} EosB200Matrix;
+
+/* The 16 tensors of one encoder layer in the order of
+ * runtime/pretrained_bert_importer.go:936-951. */
+typedef struct {
+    EosB200Matrix query;      const float* query_bias;
+    EosB200Matrix key;        const float* key_bias;
+    EosB200Matrix value;      const float* value_bias;
+    EosB200Matrix attn_out;   const float* attn_out_bias;
+    const float* attn_ln_gamma; const float* attn_ln_beta;
+    EosB200Matrix inter;      const float* inter_bias;
+    EosB200Matrix out;        const float* out_bias;
+    const float* out_ln_gamma;  const float* out_ln_beta;
+} EosB200EncoderLayer;
+
+#define EOS_B200_ACT_GELU_ERF 0   /* exactGELU, bert_encoder_layer_ops.go:742-744 */
+#define EOS_B200_ACT_GELU_TANH 1  /* geluTensor, runtime/backend/tensor_ops.go:1926-1934 */
+#define EOS_B200_POOL_MASKED_MEAN 0
+#define EOS_B200_POOL_CLS 1
+#define EOS_B200_WEIGHTS_Q8_SMEM_DEQUANT 0 /* 8-bit codes stay 8-bit in HBM; expanded in shared memory */
+#define EOS_B200_WEIGHTS_F16_RESIDENT 1    /* codes expanded to f16 once at bind */
+
+/* What StepBERTEmbedder carries (runtime/backend/tensor_ops.go:102-136; attributes
+ * num_attention_heads, epsilon, pooling per runtime/pretrained_bert_importer.go:920-984).
+ * Embedding tables are fp32 arrays as backend.Tensor holds them (runtime/backend/tensor.go:11-19)
+ * and are stored as f16 on the device. */
+typedef struct {
+    int32_t layers, hidden, heads, intermediate;
+    int32_t vocab, max_positions, type_vocab;
+    int32_t activation;        /* EOS_B200_ACT_* */
+    int32_t pooling;           /* EOS_B200_POOL_* */
+    int32_t weight_mode;       /* EOS_B200_WEIGHTS_* (q8 layers only) */
+    int32_t attention_window;  /* 0 = full attention; > 0: local window (extension, not in Eos) */
+    int32_t head_out;          /* 0 = no projection head */
+    double epsilon;            /* LayerNorm epsilon, default 1e-12 (tensor_ops.go:1434-1447) */
+    const float* token_embeddings;     /* [vocab, hidden] */
+    const float* position_embeddings;  /* [max_positions, hidden] */
+    const float* type_embeddings;      /* [type_vocab, hidden] */
+    const float* embedding_ln_gamma;
+    const float* embedding_ln_beta;
+    const EosB200EncoderLayer* layer;  /* [layers] */
+    const float* head_weights;         /* [hidden, head_out], in-major, no bias
+                                          (runtime/pretrained_bert_projection_head.go:84-100) */
+} EosB200EncoderDesc;
+
+/* ---------------------------------------------------------------------------------------------
+ * q8 encoder forward
+ * ------------------------------------------------------------------------------------------- */
+
+/* Replaces the weight binding of Backend.load / bindBGEFullEncoder (runtime/backends/cuda/
+ * cuda.go:70-112, 174-228): validates shapes, copies every tensor to the device once. */
+EOS_B200_API int eos_b200_encoder_bind(EosB200Runtime* rt, const EosB200EncoderDesc* desc, EosB200Encoder** out, char** err);
+EOS_B200_API void eos_b200_encoder_destroy(EosB200Encoder* enc);
+/* Pre-allocates the activation workspace for batches up to [batch, tokens]. */
+EOS_B200_API int eos_b200_encoder_reserve(EosB200Encoder* enc, int batch, int tokens, char** err);
+
+/* Replaces dispatchStep(StepBERTEmbedder) -> runBGEFullEncoderHidden (cuda.go:394-452,
+ * native_linux.go:7941-8190) and the host path BERTEmbedderReferenceWithPooling
+ * (runtime/backend/bert_embedder_ops.go:101-197) [+ PretrainedBERTProjectionHead.Apply].
+ * h_ids/h_mask/h_types are [batch, tokens] int32 (h_types may be NULL = all zero); h_out is
+ * [batch, E] fp32, E = head_out or hidden.  Out-of-range ids return EOS_B200_DEVICE_STATUS
+ * (tensor_ops.go:1479-1487); an all-masked sequence yields a zero vector. */
+EOS_B200_API int eos_b200_encoder_run(EosB200Encoder* enc, const int32_t* h_ids, const int32_t* h_mask, const int32_t* h_types,
+                         int batch, int tokens, float* h_out, EosB200Stats* stats, char** err);
+/* Same forward with inputs and output resident in device memory; enqueued on `stream`
+ * (a cudaStream_t; NULL = the runtime's stream) without synchronising.  The device status word
+ * is read by eos_b200_encoder_sync. */
+EOS_B200_API int eos_b200_encoder_run_device(EosB200Encoder* enc, const int32_t* d_ids, const int32_t* d_mask,
+                                const int32_t* d_types, int batch, int tokens, float* d_out, void* stream,
+                                EosB200Stats* stats, char** err);
+/* Waits for `stream` and returns EOS_B200_DEVICE_STATUS if a kernel flagged an error. */
+EOS_B200_API int eos_b200_encoder_sync(EosB200Encoder* enc, void* stream, char** err);
+
+/* Replaces MatMulAccelerator / runMatMulWithBoundRight for one dense projection
+ * (runtime/backend/backend.go:785-795, native_linux.go:9286-9372) with denseHF semantics:
+ * h_y[rows, w.rows] = epilogue(h_x[rows, w.cols] x W^T + bias).  epilogue: 0 = none, 1 = erf GELU,
+ * 2 = + h_residual, 3 = tanh GELU.  x and residual are rounded to f16 on upload, y is f16-rounded. */
+EOS_B200_API int eos_b200_linear(EosB200Runtime* rt, const float* h_x, int64_t rows, const EosB200Matrix* w, const float* h_bias,
+                    int epilogue, const float* h_residual, int weight_mode, float* h_y, EosB200Stats* stats,
+                    char** err);
+
+/* ---------------------------------------------------------------------------------------------
+ * compiled pipeline: gather -> matmul -> normalize -> masked mean_pool
+ * (examples/embed_masked_pooled.eos:11-16; steps executed by ExecuteSymbolic,
+ * runtime/backend/symbolic.go:17-172, with gatherTensor / matmulTensor / normalizeRows /
+ * meanPoolMaskedTensor of runtime/backend/tensor_ops.go)
+ * ------------------------------------------------------------------------------------------- */
+EOS_B200_API int eos_b200_embed_pooled_bind(EosB200Runtime* rt, const float* h_table, int vocab, int dim,
+                               const float* h_projection, int out_dim, EosB200EmbedPooled** out, char** err);
+EOS_B200_API void eos_b200_embed_pooled_destroy(EosB200EmbedPooled* ep);
+/* pool_then_l2 = 0: the pipeline's order (normalize each token, then mean);
+ * 1: mean of the projected rows, then one L2 normalisation. h_out [batch, out_dim] fp32. */
+EOS_B200_API int eos_b200_embed_pooled_run(EosB200EmbedPooled* ep, const int32_t* h_tokens, const int32_t* h_mask, int batch,
+                              int tokens, int pool_then_l2, float* h_out, EosB200Stats* stats, char** err);
+
+/* ---------------------------------------------------------------------------------------------
+ * TurboQuant (Hadamard/MSE variant): packing, scoring, top-k
+ * ------------------------------------------------------------------------------------------- */
+
+/* Holds the rotation spec {perm, signs1, signs2, centroids, boundaries} exactly as the
+ * reference's turboquant Spec() exposes it (native_linux.go:9532-9545), so a Go host that owns
+ * the real module can pass its own tables.  bits in {2, 4}; the centroid table must be
+ * symmetric (centroids[L-1-i] == -centroids[i]). */
+EOS_B200_API int eos_b200_quantizer_create(EosB200Runtime* rt, int dim, int bits, const int32_t* perm, const float* signs1,
+                              const float* signs2, const float* centroids, const float* boundaries,
+                              EosB200Quantizer** out, char** err);
+EOS_B200_API void eos_b200_quantizer_destroy(EosB200Quantizer* qz);
+
+/* Replaces the corpus loop `for doc: q.Quantize(doc)` (runtime/retrieval_turboquant.go:700-711):
+ * h_x [n, dim] fp32 -> h_codes [n, dim*bits/8] (codes little-end first inside a byte, the nibble
+ * order of runtime/mll_export.go:950-960) and h_norms [n]. */
+EOS_B200_API int eos_b200_quantize(EosB200Quantizer* qz, const float* h_x, int64_t n, uint8_t* h_codes, float* h_norms,
+                      EosB200Stats* stats, char** err);
+EOS_B200_API int eos_b200_quantize_device(EosB200Quantizer* qz, const float* d_x, int64_t n, uint8_t* d_codes, float* d_norms,
+                             void* stream, char** err);
+
+/* Replaces the qdocs slice built at runtime/retrieval_turboquant.go:702-711: copies the packed
+ * rows to the device once and converts them to the scan layout.  Row i has document id
+ * id_base + i; callers assign rows in ascending id order so that "score descending, then id
+ * ascending" (runtime/retrieval_eval.go:1153-1161) is the order of the results.
+ * Norm rule of runtime/turboquant_quantized_vector.go:25-49: a norm <= 0 or non-finite is rejected
+ * unless allow_zero_norm != 0. */
+EOS_B200_API int eos_b200_corpus_bind(EosB200Quantizer* qz, const uint8_t* h_codes, const float* h_norms, int64_t n,
+                         int64_t id_base, int allow_zero_norm, EosB200Corpus** out, char** err);
+EOS_B200_API int eos_b200_corpus_bind_device(EosB200Quantizer* qz, const uint8_t* d_codes, const float* d_norms, int64_t n,
+                                int64_t id_base, EosB200Corpus** out, char** err);
+EOS_B200_API void eos_b200_corpus_destroy(EosB200Corpus* corpus);
+/* runtime/turboquant_bytes.go:22-25 accounting: packed bytes per vector incl. the f32 norm. */
+EOS_B200_API int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* corpus);
+
+/* Replaces PrepareQuery + topTurboQuantRetrievalScoresWithStats per query
+ * (runtime/retrieval_turboquant.go:1324-1325, 1853-1887): exact top-k of
+ * norm * <R q, centroids[codes]> over the corpus, for q_count queries [q_count, dim] fp32.
+ * queries_per_pass in {8, 16, 32}: queries scored per streaming pass over the codes.
+ * Results [q_count, k]: ids (int64, -1 when the corpus has fewer than k rows) and scores, ordered
+ * score descending then id ascending.  k <= 128. */
+EOS_B200_API int eos_b200_score_topk(EosB200Corpus* corpus, const float* h_queries, int q_count, int k, int queries_per_pass,
+                        int64_t* h_ids, float* h_scores, EosB200Stats* stats, char** err);
+/* Device-resident variant, enqueued on `stream`.  d_keys (nullable, [q_count, k] uint64) receives
+ * the sortable (score, id) keys that eos_b200_topk_merge_device consumes after an all-gather. */
+EOS_B200_API int eos_b200_score_topk_device(EosB200Corpus* corpus, const float* d_queries, int q_count, int k,
+                               int queries_per_pass, int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream,
+                               EosB200Stats* stats, char** err);
+/* Global top-k from `shards` per-shard key lists gathered as d_keys [shards, q_count, k]
+ * (one NCCL all-gather of the per-GPU results).  Keys carry global document ids. */
+EOS_B200_API int eos_b200_topk_merge_device(EosB200Runtime* rt, const uint64_t* d_keys, int shards, int q_count, int k,
+                               int64_t* d_ids, float* d_scores, void* stream, char** err);
+/* Dense scores of a few queries against every row (no top-k), for parity checks and rerank
+ * candidates: h_scores [q_count, n]. */
+EOS_B200_API int eos_b200_score_all(EosB200Corpus* corpus, const float* h_queries, int q_count, float* h_scores, char** err);
+
+/* Multi-vector parents (topTurboQuantMultiVectorParentScores,
+ * runtime/retrieval_multivector_turboquant.go:746-810, 890-907): rows of the corpus are child
+ * vectors, h_parent_of_child [n] maps each to its parent in [0, parents).  Per query vector the
+ * parent score is the mean of its best min(top_n, 5, children) child scores (top_n <= 1: max)
+ * minus penalty * log1p(children); query_group > 1 sums the parent scores of that many
+ * consecutive query vectors (late-interaction MaxSim; extension, not in Eos).
+ * Results [q_count / query_group, k]. */
+EOS_B200_API int eos_b200_parent_topk(EosB200Corpus* corpus, const int32_t* h_parent_of_child, int parents, const float* h_queries,
+                         int q_count, int query_group, int top_n, double penalty, int k, int64_t* h_ids,
+                         float* h_scores, EosB200Stats* stats, char** err);
+
+/* Seeded synthetic data on the device (bench / tests): n rows of dim N(0,1) values, optionally
+ * L2-normalised, row r generated from (seed, row_offset + r) only. */
+EOS_B200_API int eos_b200_synth_gaussian_device(EosB200Runtime* rt, uint64_t seed, int64_t row_offset, int64_t n, int dim,
+                                   int normalize, float* d_out, void* stream, char** err);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EOS_B200_H */
