@@ -1,0 +1,470 @@
+#!/usr/bin/env python3
+"""Benchmark of the embed-and-score hot path.
+
+    python bench.py --gpus N --steps K --warmup W            # this library on N B200s (torchrun for N > 1)
+    python bench.py --impl reference --gpus N --steps K ...  # the CPU restatement of Eos's host path
+
+One JSON line on rank 0.  Primary metric: q8 encoder embeddings/s on the 12-layer / T=512 configuration
+(batch 1024 per GPU, uniform random tokens, lengths uniform 64..512, masked mean-pool + 768->768 head + L2;
+random-init weights, synthetic tokens).  A step is one forward over the batch.  `value` has the inputs resident in
+HBM; `e2e` goes through the host-buffer C-ABI call with the copies inside the timed region.  The TurboQuant
+scoring workload (10M x 768 4-bit corpus, 4096 queries, top-100) is reported under "turboquant" in the same
+line.  The CPU numbers come from oracle/ (the restatement of the reference's host loops), used here only as the
+timed baseline.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ENC = dict(layers=12, hidden=768, heads=12, inter=3072, vocab=30522, max_pos=512, head_out=768)
+ENC_BATCH, ENC_TOKENS, ENC_MIN_LEN = 1024, 512, 64
+TQ = dict(dim=768, bits=4, corpus=10_000_000, queries=4096, k=100)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops_sustained"], "tflops_burst": p["bf16_tflops"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "tflops_burst": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed regions run."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                    power.append(float(f[3]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            # the samples under load are the ones with the highest power draw
+            order = np.argsort(power)[len(power) // 2:]
+            out.update(sm_mhz=float(np.median(np.array(sm)[order])), sm_max_mhz=float(max(mx)),
+                       reasons=sorted(reasons), samples=len(sm), power_w_max=float(max(power)))
+        return out
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ------------------------------------------------------------------------------------------------ reference arm
+def encoder_sample(n_seq: int, seed: int):
+    """The first n_seq sequences of the seeded batch, padded to their own longest length (the reference pads a
+    batch to its longest member, runtime/embedding_model.go:1457-1495)."""
+    from eos_b200 import synth
+    ids, mask, lengths = synth.make_batch(ENC_BATCH, ENC_TOKENS, ENC["vocab"], ENC_MIN_LEN, ENC_TOKENS, seed)
+    t = int(lengths[:n_seq].max())
+    return ids[:n_seq, :t].copy(), mask[:n_seq, :t].copy(), lengths[:n_seq]
+
+
+def oracle_encoder_args(weights):
+    from eos_b200 import synth
+    return dict(tok=weights["token_embeddings"], pos=weights["position_embeddings"],
+                typ=weights["token_type_embeddings"], emb_gamma=weights["embedding_ln_weight"],
+                emb_beta=weights["embedding_ln_bias"],
+                layer_weights=synth.dequantized_layer_weights(weights["layer_weights"]),
+                heads=weights["num_attention_heads"], head_w=weights.get("head_weights"))
+
+
+def time_oracle_encoder(oargs, n_seq: int, workers: int, steps: int, warmup: int, seed: int):
+    from oracle import oracle as O
+    ids, mask, lengths = encoder_sample(n_seq, seed)
+    types = np.zeros_like(ids)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.bert_embedder(ids, mask, types, oargs["tok"], oargs["pos"], oargs["typ"], oargs["emb_gamma"],
+                        oargs["emb_beta"], oargs["layer_weights"], oargs["heads"], 1e-12, "masked_mean",
+                        head_w=oargs["head_w"], workers=workers)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    return n_seq * len(times) / sum(times), float(np.mean(times)), ids.shape[1], lengths
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    from eos_b200 import synth
+    cores = os.cpu_count() or 1
+    weights = synth.make_q8_encoder(seed=301, **ENC)
+    oargs = oracle_encoder_args(weights)
+    # size the per-step sample so that warmup + steps stay within a few minutes
+    rate1, t1, _, _ = time_oracle_encoder(oargs, 1, cores, 1, 0, 303)
+    budget = 150.0 / max(1, args.steps + args.warmup)
+    n_seq = int(max(1, min(16, budget / max(t1, 1e-3))))
+    rate, t_step, t_len, lengths = time_oracle_encoder(oargs, n_seq, cores, args.steps, args.warmup, 303)
+    sample = f"{n_seq} sequence(s) of the seeded batch padded to {t_len} tokens per step, all {cores} host threads"
+    line = {
+        "impl": "reference", "metric": "q8_encoder_embeddings_per_s_T512", "value": rate, "unit": "embeddings/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64-accumulate/f32",
+        "data": "synthetic", "config": workload_config(1),
+        "cpu_baseline": {"value": rate, "unit": "embeddings/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": rate, "unit": "embeddings/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(world: int) -> dict:
+    return {"workload": "12-layer q8 encoder (BERT-base shape) D=768 heads=12 FFN=3072 vocab=30522, int8 per-channel "
+                        "weights, f16 activations, fp32 accumulate; batch 1024 x T=512 per GPU, lengths uniform "
+                        "64..512, masked mean-pool + 768->768 head + L2",
+            "per_gpu_batch": ENC_BATCH, "global_batch": ENC_BATCH * world, "seq_len": ENC_TOKENS,
+            "sharding": f"data-parallel x{world}, no collective on the data path",
+            "l2_policy": "inputs_larger_than_l2 (activations of one step exceed 126 MB many times over)"}
+
+
+# ------------------------------------------------------------------------------------------------ this library
+def run_ours(args, rank: int, world: int, local: int):
+    import torch
+    import torch.distributed as dist
+
+    import eos_b200
+    from eos_b200 import synth
+    from eos_b200 import turboquant as tq
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    peaks = load_peaks()
+    rt = eos_b200.Runtime(local)
+    # an explicit stream: its handle is non-null, so the library launches on exactly the stream the timing
+    # events are recorded on (a null handle would select the runtime's own stream)
+    tstream = torch.cuda.Stream()
+    torch.cuda.set_stream(tstream)
+    stream = tstream.cuda_stream
+    assert stream != 0
+    K, W = args.steps, args.warmup
+
+    # ------------------------------------------------------------------ encoder
+    weights = synth.make_q8_encoder(seed=301, **ENC)
+    enc = eos_b200.BertEmbedder(rt, **weights)
+    ids, mask, lengths = synth.make_batch(ENC_BATCH, ENC_TOKENS, ENC["vocab"], ENC_MIN_LEN, ENC_TOKENS, 303 + rank)
+    enc.reserve(ENC_BATCH, ENC_TOKENS)
+    d_ids, d_mask = torch.from_numpy(ids).cuda(), torch.from_numpy(mask).cuda()
+    d_out = torch.empty((ENC_BATCH, ENC["head_out"]), dtype=torch.float32, device="cuda")
+    flops_total = synth.encoder_flops(lengths, ENC["layers"], ENC["hidden"], ENC["inter"], ENC["head_out"])
+    flops_gemm = synth.gemm_flops(lengths, ENC["layers"], ENC["hidden"], ENC["inter"])
+
+    def forward():
+        return enc.run_device(d_ids.data_ptr(), d_mask.data_ptr(), None, ENC_BATCH, ENC_TOKENS, d_out.data_ptr(), stream)
+
+    for _ in range(W):
+        forward()
+    enc.sync(stream)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    prof_steps = min(K, 4)
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    launches = 0
+    for i in range(K):
+        if i == K - prof_steps:
+            enc.profile_begin(prof_steps)  # event pairs around every launch of the last steps
+        launches += forward()
+    ev1.record()
+    barrier()
+    enc.sync(stream)
+    times = enc.profile_end(stream)
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    ms_step = ms_total / K
+    value = ENC_BATCH * world * K / (ms_total / 1e3)
+
+    # ------------------------------------------------------------------ encoder, end to end (host buffers)
+    h_ids = torch.from_numpy(ids).pin_memory().numpy()
+    h_mask = torch.from_numpy(mask).pin_memory().numpy()
+    enc.run(h_ids, h_mask)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        out_host = enc.run(h_ids, h_mask)
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e_value = ENC_BATCH * world * K / e2e_s
+    clocks = sampler.stop() if rank == 0 else {}
+    e2e_stats = enc.last_stats
+    assert abs(float(np.linalg.norm(out_host[0])) - 1.0) < 1e-3
+
+    gemm_ms_step = times.gemm_ms / max(1, times.steps)
+    roof = {
+        "bound": "tensor", "kernel": "gemm_tc_kernel<int8 weights dequantised in shared memory>",
+        "achieved": flops_gemm / (gemm_ms_step / 1e3) / 1e12 if gemm_ms_step > 0 else None,
+        "peak": peaks["tflops"], "unit": "TFLOP/s", "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)",
+        "traffic": None,
+        "launches_per_step": times.gemm_launches // max(1, times.steps),
+        "avg_launch_ms": times.gemm_ms / max(1, times.gemm_launches),
+        "per_step_ms": {"gemm": gemm_ms_step, "attention": times.attention_ms / max(1, times.steps),
+                        "layernorm": times.layernorm_ms / max(1, times.steps),
+                        "embed": times.embed_ms / max(1, times.steps), "pool": times.pool_ms / max(1, times.steps),
+                        "layout": times.layout_ms / max(1, times.steps)},
+        "whole_step_tflops": flops_total / (ms_step / 1e3) / 1e12,
+        "algorithmic_flops_per_step": flops_total, "gemm_flops_per_step": flops_gemm,
+    }
+    roof["frac"] = roof["achieved"] / roof["peak"] if roof["achieved"] else None
+
+    # ------------------------------------------------------------------ CPU baseline (rank 0, one GPU only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        cores = os.cpu_count() or 1
+        oargs = oracle_encoder_args(weights)
+        _, t1, _, _ = time_oracle_encoder(oargs, 1, cores, 1, 0, 303)
+        n_seq = int(max(1, min(8, 12.0 / max(t1, 1e-3))))
+        rate, _, t_len, _ = time_oracle_encoder(oargs, n_seq, cores, 1, 0, 303)
+        cpu = {"value": rate, "unit": "embeddings/s", "cores": cores, "kind": "port",
+               "sample": f"{n_seq} sequence(s) of the seeded batch padded to {t_len} tokens, all {cores} host threads, "
+                         "one pass"}
+        del oargs
+    enc.close()
+    del d_ids, d_mask, d_out
+    torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------------ TurboQuant scoring
+    tq_out = None
+    if not args.skip_turboquant:
+        tq_out = run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks)
+        launches += tq_out.pop("_launches", 0)
+
+    if rank == 0:
+        line = {
+            "metric": "q8_encoder_embeddings_per_s_T512", "value": value, "unit": "embeddings/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 x int8->f16, fp32 accumulate", "data": "synthetic",
+            "config": workload_config(world),
+            "e2e": {"value": e2e_value, "unit": "embeddings/s", "h2d_bytes_per_step": int(e2e_stats.uploaded_bytes),
+                    "d2h_bytes_per_step": int(e2e_stats.downloaded_bytes)},
+            "gpu_launches": int(launches), "roofline": roof, "clocks": clocks,
+            "valid_tokens_per_step": int(lengths.sum()),
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        if tq_out is not None:
+            line["turboquant"] = tq_out
+        print(json.dumps(line), flush=True)
+    rt.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks):
+    import torch
+    import torch.distributed as dist
+
+    import eos_b200
+    from eos_b200 import turboquant as tq
+
+    dim, bits, k, nq = TQ["dim"], TQ["bits"], TQ["k"], TQ["queries"]
+    n_total = args.tq_corpus
+    per_pass = args.tq_queries_per_pass
+    shard = (n_total + world - 1) // world
+    lo = rank * shard
+    n_local = max(0, min(n_total, lo + shard) - lo)
+    spec = eos_b200.make_rotation_spec(dim, bits, seed=402)
+    qz = eos_b200.Quantizer(rt, spec)
+    codes = torch.empty((n_local, spec.code_bytes), dtype=torch.uint8, device="cuda")
+    norms = torch.empty((n_local,), dtype=torch.float32, device="cuda")
+    chunk = 1_000_000
+    xbuf = torch.empty((min(chunk, n_local), dim), dtype=torch.float32, device="cuda")
+    for c0 in range(0, n_local, chunk):
+        c1 = min(n_local, c0 + chunk)
+        tq.synth_gaussian_device(rt, 401, lo + c0, c1 - c0, dim, True, xbuf.data_ptr(), stream)
+        qz.quantize_device(xbuf.data_ptr(), c1 - c0, codes[c0:].data_ptr(), norms[c0:].data_ptr(), stream)
+    torch.cuda.synchronize()
+    corpus = eos_b200.Corpus(qz, device_ptrs=(codes.data_ptr(), norms.data_ptr(), n_local), id_base=lo)
+    del xbuf, codes
+    torch.cuda.empty_cache()
+    queries = torch.empty((nq, dim), dtype=torch.float32, device="cuda")
+    tq.synth_gaussian_device(rt, 403, 0, nq, dim, True, queries.data_ptr(), stream)
+    queries = queries.half().float().contiguous()  # the configuration's queries are f16
+    ids = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+    scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+    keys = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+    keys_all = torch.empty((world, nq, k), dtype=torch.int64, device="cuda") if world > 1 else None
+    launches = 0
+
+    def step():
+        n = 0
+        if world == 1:
+            n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, ids.data_ptr(), scores.data_ptr(), None,
+                                          stream)
+        else:
+            n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, None, None, keys.data_ptr(), stream)
+            dist.all_gather_into_tensor(keys_all, keys)  # one NCCL all-gather of the per-shard top-k
+            tq.topk_merge_device(rt, keys_all.data_ptr(), world, nq, k, ids.data_ptr(), scores.data_ptr(), stream)
+            n += 1
+        return n
+
+    steps = max(1, min(args.steps, args.tq_steps))
+    warm = max(1, min(args.warmup, 3))
+    for _ in range(warm):
+        step()
+    barrier()
+    passes = (nq + per_pass - 1) // per_pass
+    corpus.profile_begin(passes * steps + 8)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        launches += step()
+    ev1.record()
+    barrier()
+    scan_ms, scan_launches = corpus.profile_end(stream)
+    ms = max_over_ranks(ev0.elapsed_time(ev1)) / steps
+    vec_passes = passes * n_total
+    # end to end: host queries in, host ids/scores out (single GPU); copies inside the timed region
+    e2e = None
+    if world == 1:
+        hq = queries.cpu().pin_memory().numpy()
+        corpus.score_topk(hq[:64], k, per_pass)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            h_ids, h_scores = corpus.score_topk(hq, k, per_pass)
+        dt = (time.perf_counter() - t0) / steps
+        st = corpus.last_stats
+        e2e = {"value": vec_passes / dt, "unit": "vectors/s", "h2d_bytes_per_step": int(st.uploaded_bytes),
+               "d2h_bytes_per_step": int(st.downloaded_bytes), "queries_per_s": nq / dt}
+    bytes_per_vec = spec.vector_bytes
+    scan_avg_ms = scan_ms / max(1, scan_launches)
+    achieved = (n_local * bytes_per_vec) / (scan_avg_ms / 1e3) / 1e9 if scan_avg_ms > 0 else None
+    out = {
+        "metric": "turboquant_vectors_scored_per_s", "value": vec_passes / (ms / 1e3), "unit": "vectors/s",
+        "pair_scores_per_s": float(nq) * n_total / (ms / 1e3), "ms_per_step": ms, "steps": steps, "scaling": "strong",
+        "config": {"workload": f"TurboQuant 4-bit Hadamard/MSE, {n_total} x {dim} unit Gaussian corpus sharded over "
+                               f"{world} GPU(s), {nq} f16 queries, exact top-{k}, {per_pass} queries per corpus pass "
+                               f"({passes} passes)", "bytes_per_vector": bytes_per_vec,
+                   "merge": "none" if world == 1 else "NCCL all-gather of per-shard top-k + merge kernel"},
+        "roofline": {"bound": "hbm", "kernel": f"tq_scan_kernel<{per_pass // 8}>", "achieved": achieved,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"] if achieved else None,
+                     "peak_source": f"{peaks['source']} (copy bandwidth)", "traffic": None,
+                     "avg_launch_ms": scan_avg_ms, "algorithmic_bytes_per_launch": n_local * bytes_per_vec},
+        "_launches": launches,
+    }
+    if e2e is not None:
+        out["e2e"] = e2e
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        out["cpu_baseline"] = time_oracle_scoring(spec, rt, qz)
+    corpus.close()
+    qz.close()
+    return out
+
+
+def time_oracle_scoring(spec, rt, qz):
+    """Per-query scoring loop + heap of the reference (single-threaded, as runtime/retrieval_turboquant.go:1306-1331
+    runs it) on a bounded sample of the workload."""
+    from oracle import oracle as O
+    n, nq = 250_000, 8
+    rng = np.random.default_rng(401)
+    x = rng.standard_normal((n, spec.dim)).astype(np.float32)
+    x /= np.linalg.norm(x, axis=1, keepdims=True)
+    codes, norms = qz.quantize(x)  # packing is not what is timed
+    q = rng.standard_normal((nq, spec.dim)).astype(np.float32)
+    t0 = time.perf_counter()
+    for i in range(nq):
+        prep = O.tq_prepare_query(q[i], spec.perm, spec.signs1, spec.signs2)
+        O.tq_score_topk(codes, norms, spec.dim, spec.bits, spec.centroids, prep, TQ["k"])
+    dt = time.perf_counter() - t0
+    return {"value": n * nq / dt, "unit": "vectors/s", "cores": 1, "kind": "port",
+            "sample": f"{nq} queries x {n} packed vectors, one thread (the reference's scoring loop is serial)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the timed CPU baseline")
+    ap.add_argument("--skip-turboquant", action="store_true", help="encoder only")
+    ap.add_argument("--tq-corpus", type=int, default=TQ["corpus"])
+    ap.add_argument("--tq-queries-per-pass", type=int, default=16)
+    ap.add_argument("--tq-steps", type=int, default=2)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank, world, local = dist_setup(args.gpus)
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_ours(args, rank, world, local)
+
+
+if __name__ == "__main__":
+    main()

@@ -28,6 +28,13 @@ class Stats(C.Structure):
                 ("reserved2", C.c_float)]
 
 
+class EncoderTimes(C.Structure):
+    _fields_ = [("steps", C.c_int32), ("gemm_launches", C.c_int32), ("attention_launches", C.c_int32),
+                ("layernorm_launches", C.c_int32), ("other_launches", C.c_int32), ("gemm_ms", C.c_float),
+                ("attention_ms", C.c_float), ("layernorm_ms", C.c_float), ("embed_ms", C.c_float),
+                ("pool_ms", C.c_float), ("layout_ms", C.c_float)]
+
+
 class DeviceInfo(C.Structure):
     _fields_ = [("device", C.c_int32), ("cc_major", C.c_int32), ("cc_minor", C.c_int32), ("sm_count", C.c_int32),
                 ("total_memory_bytes", C.c_int64), ("name", C.c_char * 128)]
@@ -71,6 +78,10 @@ SYMBOLS = {
     "eos_b200_encoder_run": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_encoder_run_device": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_encoder_sync": (C.c_int, [_P, _P, _ERR]),
+    "eos_b200_encoder_profile_begin": (C.c_int, [_P, C.c_int, _ERR]),
+    "eos_b200_encoder_profile_end": (C.c_int, [_P, _P, C.POINTER(EncoderTimes), _ERR]),
+    "eos_b200_corpus_profile_begin": (C.c_int, [_P, C.c_int, _ERR]),
+    "eos_b200_corpus_profile_end": (C.c_int, [_P, _P, C.POINTER(C.c_float), C.POINTER(C.c_int), _ERR]),
     "eos_b200_linear": (C.c_int, [_P, _P, C.c_int64, C.POINTER(Matrix), _P, C.c_int, _P, C.c_int, _P,
                                   C.POINTER(Stats), _ERR]),
     "eos_b200_embed_pooled_bind": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, C.c_int, C.POINTER(_P), _ERR]),

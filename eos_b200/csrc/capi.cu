@@ -298,6 +298,43 @@ struct LayerW {
     float *g1 = nullptr, *b1 = nullptr, *g2 = nullptr, *b2 = nullptr;
 };
 
+// CUDA-event pairs around individual launches, tagged with a kernel class.
+enum KernelClass : int { kClsLayout = 0, kClsEmbed, kClsGemm, kClsAttention, kClsLayerNorm, kClsPool, kClsScan };
+
+struct Profiler {
+    std::vector<cudaEvent_t> ev;  // 2 per slot
+    std::vector<int> cls;
+    int used = 0;
+    bool on = false;
+
+    void reset() {
+        for (cudaEvent_t e : ev) cudaEventDestroy(e);
+        ev.clear();
+        cls.clear();
+        used = 0;
+        on = false;
+    }
+    bool begin(int slots) {
+        reset();
+        ev.resize((size_t)slots * 2);
+        cls.assign((size_t)slots, 0);
+        for (auto& e : ev)
+            if (cudaEventCreate(&e) != cudaSuccess) return false;
+        on = true;
+        return true;
+    }
+    template <typename F>
+    void launch(int c, cudaStream_t s, F&& f) {
+        const bool rec = on && (size_t)used < cls.size();
+        if (rec) cudaEventRecord(ev[(size_t)used * 2], s);
+        f();
+        if (rec) {
+            cudaEventRecord(ev[(size_t)used * 2 + 1], s);
+            cls[used++] = c;
+        }
+    }
+};
+
 }  // namespace
 
 struct EosB200Encoder {
@@ -317,6 +354,8 @@ struct EosB200Encoder {
     __half *h0 = nullptr, *h1 = nullptr, *qkv = nullptr, *ctx = nullptr, *pre = nullptr, *ffn = nullptr;
     float *pooled = nullptr, *d_out = nullptr;
     std::vector<GemmPlan> plans;  // 4 per layer: qkv, attn-out, inter, out
+    Profiler prof;
+    int launches_per_forward = 0;
 };
 
 namespace {
@@ -428,24 +467,36 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
     const int D = e->hidden;
     const int cls = e->pooling == EOS_B200_POOL_CLS ? 1 : 0;
     int launches = 0;
-    launch_seq_layout(d_mask, batch, tokens, cls, e->lay, s);
+    Profiler& pf = e->prof;
+    pf.launch(kClsLayout, s, [&] { launch_seq_layout(d_mask, batch, tokens, cls, e->lay, s); });
     launches += 3;
-    launch_embed_ln(d_ids, d_types, e->lay, tokens, e->tok, e->vocab, e->pos, e->max_pos, e->typ, e->type_vocab, e->eg,
-                    e->eb, e->eps, D, e->m_alloc, e->h0, rt->d_status, rt->sm_count, s);
+    pf.launch(kClsEmbed, s, [&] {
+        launch_embed_ln(d_ids, d_types, e->lay, tokens, e->tok, e->vocab, e->pos, e->max_pos, e->typ, e->type_vocab,
+                        e->eg, e->eb, e->eps, D, e->m_alloc, e->h0, rt->d_status, rt->sm_count, s);
+    });
     launches += 1;
     for (int l = 0; l < e->layers; ++l) {
         LayerW& w = e->lw[l];
-        gemm_launch(e->plans[(size_t)l * 4 + 0], s);
-        launch_attention(e->qkv, e->lay, batch, tokens, D, e->heads, e->window, e->ctx, s);
-        gemm_launch(e->plans[(size_t)l * 4 + 1], s);
-        launch_layernorm(e->pre, w.g1, w.b1, e->eps, D, e->m_alloc, e->lay.total_rows, e->h1, rt->sm_count, s);
-        gemm_launch(e->plans[(size_t)l * 4 + 2], s);
-        gemm_launch(e->plans[(size_t)l * 4 + 3], s);
-        launch_layernorm(e->pre, w.g2, w.b2, e->eps, D, e->m_alloc, e->lay.total_rows, e->h0, rt->sm_count, s);
+        pf.launch(kClsGemm, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 0], s); });
+        pf.launch(kClsAttention, s, [&] {
+            launch_attention(e->qkv, e->lay, batch, tokens, D, e->heads, e->window, e->ctx, s);
+        });
+        pf.launch(kClsGemm, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 1], s); });
+        pf.launch(kClsLayerNorm, s, [&] {
+            launch_layernorm(e->pre, w.g1, w.b1, e->eps, D, e->m_alloc, e->lay.total_rows, e->h1, rt->sm_count, s);
+        });
+        pf.launch(kClsGemm, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 2], s); });
+        pf.launch(kClsGemm, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 3], s); });
+        pf.launch(kClsLayerNorm, s, [&] {
+            launch_layernorm(e->pre, w.g2, w.b2, e->eps, D, e->m_alloc, e->lay.total_rows, e->h0, rt->sm_count, s);
+        });
         launches += 7;
     }
-    launch_pool_head(e->h0, e->lay, batch, D, cls, e->head_w, e->head_out, e->pooled, d_out, s);
+    pf.launch(kClsPool, s, [&] {
+        launch_pool_head(e->h0, e->lay, batch, D, cls, e->head_w, e->head_out, e->pooled, d_out, s);
+    });
     launches += e->head_w != nullptr ? 2 : 1;
+    e->launches_per_forward = launches;
     return launches;
 }
 
@@ -458,6 +509,7 @@ void eos_b200_encoder_destroy(EosB200Encoder* enc) {
     cudaSetDevice(enc->rt->device);
     cudaStreamSynchronize(enc->rt->stream);
     free_workspace(enc);
+    enc->prof.reset();
     dev_free(enc->tok);
     dev_free(enc->pos);
     dev_free(enc->typ);
@@ -588,6 +640,37 @@ int eos_b200_encoder_run_device(EosB200Encoder* enc, const int32_t* d_ids, const
         std::memset(stats, 0, sizeof(*stats));
         stats->kernel_launches = launches;
     }
+    return EOS_B200_OK;
+}
+
+int eos_b200_encoder_profile_begin(EosB200Encoder* enc, int max_steps, char** err) {
+    if (enc == nullptr || max_steps <= 0) return fail(err, "encoder_profile_begin: bad argument");
+    CUDA_TRY(cudaSetDevice(enc->rt->device));
+    const int per_forward = 3 + enc->layers * 7;  // event pairs per forward (one per launcher call)
+    if (!enc->prof.begin(per_forward * max_steps)) return fail(err, "encoder_profile_begin: cudaEventCreate failed");
+    return EOS_B200_OK;
+}
+
+int eos_b200_encoder_profile_end(EosB200Encoder* enc, void* stream, EosB200EncoderTimes* out, char** err) {
+    if (enc == nullptr || out == nullptr) return fail(err, "encoder_profile_end: null argument");
+    CUDA_TRY(cudaSetDevice(enc->rt->device));
+    CUDA_TRY(cudaStreamSynchronize(pick_stream(enc->rt, stream)));
+    std::memset(out, 0, sizeof(*out));
+    const int per_forward = 3 + enc->layers * 7;
+    out->steps = enc->prof.used / per_forward;
+    for (int i = 0; i < enc->prof.used; ++i) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, enc->prof.ev[(size_t)i * 2], enc->prof.ev[(size_t)i * 2 + 1]);
+        switch (enc->prof.cls[i]) {
+            case kClsGemm: out->gemm_ms += ms; out->gemm_launches++; break;
+            case kClsAttention: out->attention_ms += ms; out->attention_launches++; break;
+            case kClsLayerNorm: out->layernorm_ms += ms; out->layernorm_launches++; break;
+            case kClsEmbed: out->embed_ms += ms; out->other_launches++; break;
+            case kClsPool: out->pool_ms += ms; out->other_launches += enc->head_w != nullptr ? 2 : 1; break;
+            default: out->layout_ms += ms; out->other_launches += 3; break;
+        }
+    }
+    enc->prof.reset();
     return EOS_B200_OK;
 }
 
@@ -845,6 +928,7 @@ struct EosB200Corpus {
     int64_t* d_ids = nullptr;
     float* d_scores = nullptr;
     int grid = 0;
+    Profiler prof;
 };
 
 namespace {
@@ -969,7 +1053,7 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
             a.grid = c->grid;
             a.all_scores = nullptr;
             a.all_stride = 0;
-            launch_tq_scan(a, s);
+            c->prof.launch(kClsScan, s, [&] { launch_tq_scan(a, s); });
             launches++;
         }
         launch_tq_merge(c->cand, (int64_t)c->grid * kTqMaxK, kTqMaxK, c->grid, kTqMaxK, c->cand_count, g_queries, k,
@@ -1118,7 +1202,31 @@ void eos_b200_corpus_destroy(EosB200Corpus* c) {
     dev_free(c->cand_count);
     dev_free(c->d_ids);
     dev_free(c->d_scores);
+    c->prof.reset();
     delete c;
+}
+
+int eos_b200_corpus_profile_begin(EosB200Corpus* c, int max_launches, char** err) {
+    if (c == nullptr || max_launches <= 0) return fail(err, "corpus_profile_begin: bad argument");
+    CUDA_TRY(cudaSetDevice(c->qz->rt->device));
+    if (!c->prof.begin(max_launches)) return fail(err, "corpus_profile_begin: cudaEventCreate failed");
+    return EOS_B200_OK;
+}
+
+int eos_b200_corpus_profile_end(EosB200Corpus* c, void* stream, float* out_ms, int* out_launches, char** err) {
+    if (c == nullptr || out_ms == nullptr || out_launches == nullptr) return fail(err, "corpus_profile_end: null argument");
+    CUDA_TRY(cudaSetDevice(c->qz->rt->device));
+    CUDA_TRY(cudaStreamSynchronize(pick_stream(c->qz->rt, stream)));
+    float total = 0.f;
+    for (int i = 0; i < c->prof.used; ++i) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, c->prof.ev[(size_t)i * 2], c->prof.ev[(size_t)i * 2 + 1]);
+        total += ms;
+    }
+    *out_ms = total;
+    *out_launches = c->prof.used;
+    c->prof.reset();
+    return EOS_B200_OK;
 }
 
 int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* c) {

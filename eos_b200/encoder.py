@@ -12,6 +12,7 @@ linear         <- one dense projection with denseHF semantics
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from dataclasses import dataclass
 from typing import Optional, Sequence, Union
 
@@ -59,6 +60,10 @@ class Runtime:
         self.handle = C.c_void_p()
         _lib.call("eos_b200_runtime_create", int(device), C.byref(self.handle))
         self.device = int(device)
+        self._children = weakref.WeakSet()  # handles bound to this runtime; they must be destroyed first
+
+    def _adopt(self, child) -> None:
+        self._children.add(child)
 
     def info(self) -> dict:
         out = _lib.DeviceInfo()
@@ -68,6 +73,8 @@ class Runtime:
 
     def close(self) -> None:
         if self.handle:
+            for child in list(self._children):
+                child.close()
             _lib.lib().eos_b200_runtime_destroy(self.handle)
             self.handle = C.c_void_p()
 
@@ -155,6 +162,7 @@ class BertEmbedder:
             raise ValueError("bert_embeddings tables disagree on the hidden size")
         self.handle = C.c_void_p()
         _lib.call("eos_b200_encoder_bind", rt.handle, C.byref(d), C.byref(self.handle))
+        rt._adopt(self)
         self.hidden, self.layers, self.heads, self.intermediate = d.hidden, layers, d.heads, d.intermediate
         self.last_stats = Stats()
 
@@ -187,6 +195,15 @@ class BertEmbedder:
     def sync(self, stream: Optional[int] = None) -> None:
         _lib.call("eos_b200_encoder_sync", self.handle, stream)
 
+    def profile_begin(self, max_steps: int) -> None:
+        """Record CUDA events around every kernel launch of the next `max_steps` forwards."""
+        _lib.call("eos_b200_encoder_profile_begin", self.handle, int(max_steps))
+
+    def profile_end(self, stream: Optional[int] = None) -> "_lib.EncoderTimes":
+        out = _lib.EncoderTimes()
+        _lib.call("eos_b200_encoder_profile_end", self.handle, stream, C.byref(out))
+        return out
+
     def close(self) -> None:
         if self.handle:
             _lib.lib().eos_b200_encoder_destroy(self.handle)
@@ -211,6 +228,7 @@ class EmbedPooledPipeline:
         self.handle = C.c_void_p()
         _lib.call("eos_b200_embed_pooled_bind", rt.handle, _ptr(table), table.shape[0], table.shape[1], _ptr(proj),
                   proj.shape[1], C.byref(self.handle))
+        rt._adopt(self)
         self.last_stats = Stats()
 
     def run(self, tokens, attention_mask, pool_then_l2: bool = False) -> np.ndarray:

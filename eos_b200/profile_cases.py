@@ -1,0 +1,82 @@
+"""Small, self-contained launches of single kernels, sized for profiler captures that end by themselves.
+
+    python -m eos_b200.profile_cases gemm        # projection kernel, 32768 x 768 -> 3072, erf-GELU epilogue
+    python -m eos_b200.profile_cases gemm_res    # 32768 x 3072 -> 768 with residual epilogue
+    python -m eos_b200.profile_cases scan        # TurboQuant scan, 1,000,000 x 768 4-bit codes, 16 queries per pass
+    python -m eos_b200.profile_cases attention   # 2-layer encoder forward, 128 x 512 tokens (attention + LN kernels)
+
+Each case touches more than the 126 MB L2 but holds well under a few GB on the device.
+"""
+from __future__ import annotations
+
+import sys
+
+import numpy as np
+
+
+def case_gemm(residual: bool = False) -> None:
+    import eos_b200
+    from eos_b200 import synth
+    rt = eos_b200.Runtime(0)
+    rng = np.random.default_rng(0)
+    rows, k, n = (32768, 3072, 768) if residual else (32768, 768, 3072)
+    x = rng.standard_normal((rows, k), dtype=np.float32)
+    w = synth.quantize_per_channel(rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+    bias = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    res = rng.standard_normal((rows, n), dtype=np.float32) if residual else None
+    for _ in range(3):
+        st = eos_b200.Stats()
+        eos_b200.linear(rt, x, w, bias, epilogue=2 if residual else 1, residual=res, stats=st)
+        print(f"gemm {rows}x{k}->{n}: {st.device_ms:.3f} ms, {2.0 * rows * k * n / st.device_ms / 1e9:.1f} TFLOP/s")
+    rt.close()
+
+
+def case_scan() -> None:
+    import torch
+
+    import eos_b200
+    from eos_b200 import turboquant as tq
+    rt = eos_b200.Runtime(0)
+    spec = eos_b200.make_rotation_spec(768, 4, seed=402)
+    qz = eos_b200.Quantizer(rt, spec)
+    n = 1_000_000
+    x = torch.empty((n, 768), dtype=torch.float32, device="cuda")
+    codes = torch.empty((n, 384), dtype=torch.uint8, device="cuda")
+    norms = torch.empty((n,), dtype=torch.float32, device="cuda")
+    tq.synth_gaussian_device(rt, 401, 0, n, 768, True, x.data_ptr())
+    qz.quantize_device(x.data_ptr(), n, codes.data_ptr(), norms.data_ptr())
+    corpus = eos_b200.Corpus(qz, device_ptrs=(codes.data_ptr(), norms.data_ptr(), n))
+    q = x[:64].cpu().numpy()
+    del x
+    for per_pass in (8, 16, 32):
+        corpus.profile_begin(64)
+        corpus.score_topk(q, 100, queries_per_pass=per_pass)
+        ms, launches = corpus.profile_end()
+        print(f"scan {per_pass} queries/pass: {ms / launches:.3f} ms per pass, "
+              f"{n * spec.vector_bytes / (ms / launches) / 1e6:.0f} GB/s")
+    corpus.close()
+    qz.close()
+    rt.close()
+
+
+def case_attention() -> None:
+    import eos_b200
+    from eos_b200 import synth
+    rt = eos_b200.Runtime(0)
+    args = synth.make_q8_encoder(2, 768, 12, 3072, vocab=30522, max_pos=512, seed=301)
+    ids, mask, lengths = synth.make_batch(128, 512, 30522, 64, 512, seed=303)
+    enc = eos_b200.BertEmbedder(rt, **args)
+    for _ in range(2):
+        enc.run(ids, mask)
+    enc.profile_begin(1)
+    enc.run(ids, mask)
+    t = enc.profile_end()
+    print(f"tokens {int(lengths.sum())}: gemm {t.gemm_ms:.3f} ms, attention {t.attention_ms:.3f} ms, "
+          f"layernorm {t.layernorm_ms:.3f} ms")
+    enc.close()
+    rt.close()
+
+
+if __name__ == "__main__":
+    name = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    {"gemm": case_gemm, "gemm_res": lambda: case_gemm(True), "scan": case_scan, "attention": case_attention}[name]()

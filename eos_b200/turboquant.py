@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import weakref
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -99,6 +100,8 @@ class Quantizer:
         self.handle = C.c_void_p()
         _lib.call("eos_b200_quantizer_create", rt.handle, spec.dim, spec.bits, *[_ptr(a) for a in self._keep],
                   C.byref(self.handle))
+        rt._adopt(self)
+        self._children = weakref.WeakSet()
         self.last_stats = Stats()
 
     def quantize(self, x) -> Tuple[np.ndarray, np.ndarray]:
@@ -117,6 +120,8 @@ class Quantizer:
 
     def close(self) -> None:
         if self.handle:
+            for child in list(self._children):
+                child.close()
             _lib.lib().eos_b200_quantizer_destroy(self.handle)
             self.handle = C.c_void_p()
 
@@ -140,6 +145,7 @@ class Corpus:
             self.n = int(n)
             _lib.call("eos_b200_corpus_bind_device", quantizer.handle, d_codes, d_norms, int(n), int(id_base),
                       C.byref(self.handle))
+            quantizer._children.add(self)
         else:
             c = np.ascontiguousarray(codes, dtype=np.uint8)
             nr = _f32(norms).reshape(-1)
@@ -148,6 +154,7 @@ class Corpus:
             self.n = c.shape[0]
             _lib.call("eos_b200_corpus_bind", quantizer.handle, _ptr(c), _ptr(nr), c.shape[0], int(id_base),
                       1 if allow_zero_norm else 0, C.byref(self.handle))
+            quantizer._children.add(self)
         self.last_stats = Stats()
 
     def score_topk(self, queries, k: int, queries_per_pass: int = 8) -> Tuple[np.ndarray, np.ndarray]:
@@ -167,6 +174,15 @@ class Corpus:
         _lib.call("eos_b200_score_topk_device", self.handle, d_queries, int(q_count), int(k), int(queries_per_pass),
                   d_ids, d_scores, d_keys, stream, C.byref(st))
         return st.kernel_launches
+
+    def profile_begin(self, max_launches: int) -> None:
+        _lib.call("eos_b200_corpus_profile_begin", self.handle, int(max_launches))
+
+    def profile_end(self, stream: Optional[int] = None) -> Tuple[float, int]:
+        """(total milliseconds, launches) of the scan kernel since profile_begin."""
+        ms, n = C.c_float(), C.c_int()
+        _lib.call("eos_b200_corpus_profile_end", self.handle, stream, C.byref(ms), C.byref(n))
+        return float(ms.value), int(n.value)
 
     def score_all(self, queries) -> np.ndarray:
         q = _f32(queries)

@@ -161,6 +161,18 @@ EOS_B200_API int eos_b200_encoder_run(EosB200Encoder* enc, const int32_t* h_ids,
 EOS_B200_API int eos_b200_encoder_run_device(EosB200Encoder* enc, const int32_t* d_ids, const int32_t* d_mask,
                                 const int32_t* d_types, int batch, int tokens, float* d_out, void* stream,
                                 EosB200Stats* stats, char** err);
+/* Per-kernel-class device time of the forwards enqueued between profile_begin and profile_end,
+ * taken with CUDA events recorded around every launch on the launching stream.  The reference
+ * keeps the same kind of evidence as CUDA-event phase pairs (native_linux.go:285-498,
+ * EOS_CUDA_COMPACT_PROFILE_EVENTS).  Times are totals over `steps` forwards. */
+typedef struct {
+    int32_t steps;
+    int32_t gemm_launches, attention_launches, layernorm_launches, other_launches;
+    float gemm_ms, attention_ms, layernorm_ms, embed_ms, pool_ms, layout_ms;
+} EosB200EncoderTimes;
+EOS_B200_API int eos_b200_encoder_profile_begin(EosB200Encoder* enc, int max_steps, char** err);
+EOS_B200_API int eos_b200_encoder_profile_end(EosB200Encoder* enc, void* stream, EosB200EncoderTimes* out, char** err);
+
 /* Waits for `stream` and returns EOS_B200_DEVICE_STATUS if a kernel flagged an error. */
 EOS_B200_API int eos_b200_encoder_sync(EosB200Encoder* enc, void* stream, char** err);
 
@@ -234,6 +246,12 @@ EOS_B200_API int eos_b200_score_topk(EosB200Corpus* corpus, const float* h_queri
 EOS_B200_API int eos_b200_score_topk_device(EosB200Corpus* corpus, const float* d_queries, int q_count, int k,
                                int queries_per_pass, int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream,
                                EosB200Stats* stats, char** err);
+/* Device time of the scan kernel alone (CUDA events around every scan launch between begin and
+ * end): out_ms = total milliseconds, out_launches = scan launches covered. */
+EOS_B200_API int eos_b200_corpus_profile_begin(EosB200Corpus* corpus, int max_launches, char** err);
+EOS_B200_API int eos_b200_corpus_profile_end(EosB200Corpus* corpus, void* stream, float* out_ms, int* out_launches,
+                                             char** err);
+
 /* Global top-k from `shards` per-shard key lists gathered as d_keys [shards, q_count, k]
  * (one NCCL all-gather of the per-GPU results).  Keys carry global document ids. */
 EOS_B200_API int eos_b200_topk_merge_device(EosB200Runtime* rt, const uint64_t* d_keys, int shards, int q_count, int k,

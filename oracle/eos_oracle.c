@@ -351,12 +351,15 @@ EOS_ORACLE_API void eos_oracle_dense_hf(const float *input, int64_t rows, int in
 /* bertSelfAttentionContextRange: runtime/backend/bert_encoder_layer_ops.go:326-379.
  * One job per (batch, query token, head); double logits over unmasked keys only,
  * max-subtracted softmax, context += float(prob * v); no active key -> zeros.
- * Padded query rows are computed like any other. */
+ * Padded query rows are computed like any other.
+ * Extension (NOT in the reference, which has no local attention): with window > 0 key j is
+ * visible to query i only if 2*|i - j| < window; everything else is unchanged. */
 typedef struct {
     const float *q, *k, *v;
     const int32_t *mask;
     float *context;
     int tokens, hidden, heads, head_dim;
+    int window; /* 0 = the reference (full attention); > 0 = local-window extension, see below */
 } attn_ctx;
 
 static void attn_range(void *p, int64_t j0, int64_t j1) {
@@ -368,10 +371,11 @@ static void attn_range(void *p, int64_t j0, int64_t j1) {
         int64_t qi = job / c->heads;
         int64_t batch = qi / c->tokens;
         int64_t qrow = qi;
+        int qt = (int)(qi % c->tokens);
         int active = 0;
         double max_logit = -INFINITY;
         for (int kt = 0; kt < c->tokens; kt++) {
-            if (c->mask[batch * c->tokens + kt] == 0) continue;
+            if (c->mask[batch * c->tokens + kt] == 0 || (c->window > 0 && 2 * abs(qt - kt) >= c->window)) continue;
             active++;
             int64_t krow = batch * c->tokens + kt;
             double dot = 0.0;
@@ -386,13 +390,13 @@ static void attn_range(void *p, int64_t j0, int64_t j1) {
         if (active == 0) continue;
         double sum_exp = 0.0;
         for (int kt = 0; kt < c->tokens; kt++) {
-            if (c->mask[batch * c->tokens + kt] == 0) continue;
+            if (c->mask[batch * c->tokens + kt] == 0 || (c->window > 0 && 2 * abs(qt - kt) >= c->window)) continue;
             double ev = exp(logits[kt] - max_logit);
             logits[kt] = ev;
             sum_exp += ev;
         }
         for (int kt = 0; kt < c->tokens; kt++) {
-            if (c->mask[batch * c->tokens + kt] == 0) continue;
+            if (c->mask[batch * c->tokens + kt] == 0 || (c->window > 0 && 2 * abs(qt - kt) >= c->window)) continue;
             double prob = logits[kt] / sum_exp;
             int64_t vrow = batch * c->tokens + kt;
             for (int d = 0; d < c->head_dim; d++) {
@@ -404,11 +408,19 @@ static void attn_range(void *p, int64_t j0, int64_t j1) {
     free(logits);
 }
 
+EOS_ORACLE_API void eos_oracle_bert_attention_window(const float *q, const float *k, const float *v,
+                                                     const int32_t *mask, int batch, int tokens, int hidden,
+                                                     int heads, int window, float *context, int workers) {
+    memset(context, 0, sizeof(float) * (size_t)batch * tokens * hidden);
+    attn_ctx c = {q, k, v, mask, context, tokens, hidden, heads, hidden / heads, window};
+    parallel_ranges(attn_range, &c, (int64_t)batch * tokens * heads, workers);
+}
+
 EOS_ORACLE_API void eos_oracle_bert_attention(const float *q, const float *k, const float *v, const int32_t *mask,
                                               int batch, int tokens, int hidden, int heads, float *context,
                                               int workers) {
     memset(context, 0, sizeof(float) * (size_t)batch * tokens * hidden);
-    attn_ctx c = {q, k, v, mask, context, tokens, hidden, heads, hidden / heads};
+    attn_ctx c = {q, k, v, mask, context, tokens, hidden, heads, hidden / heads, 0};
     parallel_ranges(attn_range, &c, (int64_t)batch * tokens * heads, workers);
 }
 
@@ -447,8 +459,8 @@ EOS_ORACLE_API float eos_oracle_tanh_gelu(float x) {
  * runtime/backend/bert_encoder_layer_ops.go:186-224.  `w` holds the 16 tensors in the fixed
  * order of runtime/pretrained_bert_importer.go:936-951:
  * qW qB kW kB vW vB aoW aoB aLNg aLNb iW iB oW oB oLNg oLNb. `hidden` is updated in place. */
-EOS_ORACLE_API void eos_oracle_bert_layer(float *hidden_states, const int32_t *mask, int batch, int tokens, int hidden,
-                                          int inter, int heads, const float *const *w, double eps, int workers) {
+static void bert_layer_impl(float *hidden_states, const int32_t *mask, int batch, int tokens, int hidden, int inter,
+                            int heads, const float *const *w, double eps, int window, int workers) {
     int64_t rows = (int64_t)batch * tokens;
     size_t hsz = sizeof(float) * (size_t)(rows * hidden);
     float *q = (float *)malloc(hsz), *k = (float *)malloc(hsz), *v = (float *)malloc(hsz);
@@ -457,7 +469,7 @@ EOS_ORACLE_API void eos_oracle_bert_layer(float *hidden_states, const int32_t *m
     eos_oracle_dense_hf(hidden_states, rows, hidden, w[0], w[1], hidden, q, workers);
     eos_oracle_dense_hf(hidden_states, rows, hidden, w[2], w[3], hidden, k, workers);
     eos_oracle_dense_hf(hidden_states, rows, hidden, w[4], w[5], hidden, v, workers);
-    eos_oracle_bert_attention(q, k, v, mask, batch, tokens, hidden, heads, ctx, workers);
+    eos_oracle_bert_attention_window(q, k, v, mask, batch, tokens, hidden, heads, window, ctx, workers);
     eos_oracle_dense_hf(ctx, rows, hidden, w[6], w[7], hidden, tmp, workers);
     for (int64_t i = 0; i < rows * hidden; i++) tmp[i] = tmp[i] + hidden_states[i];
     eos_oracle_layernorm_affine(tmp, rows, hidden, w[8], w[9], eps, attn_layer);
@@ -475,18 +487,24 @@ EOS_ORACLE_API void eos_oracle_bert_layer(float *hidden_states, const int32_t *m
     free(mid);
 }
 
+EOS_ORACLE_API void eos_oracle_bert_layer(float *hidden_states, const int32_t *mask, int batch, int tokens, int hidden,
+                                          int inter, int heads, const float *const *w, double eps, int workers) {
+    bert_layer_impl(hidden_states, mask, batch, tokens, hidden, inter, heads, w, eps, 0, workers);
+}
+
 /* Whole embedder, BERTEmbedderReferenceWithPooling: runtime/backend/bert_embedder_ops.go:101-197
  * (position ids 0..T-1 per :220-228; pooling 0 = masked_mean, 1 = cls; then normalizeRows),
  * optionally followed by PretrainedBERTProjectionHead.Apply
  * (runtime/pretrained_bert_projection_head.go:84-100: [in,out] weights, no bias, double
  * accumulate) and normalizeRetrievalVector (runtime/retrieval_eval.go:1040-1054).
- * out is [batch, head ? head_out : hidden].  Returns the bert_embeddings error code. */
+ * out is [batch, head ? head_out : hidden].  Returns the bert_embeddings error code.
+ * window = 0 is the reference; window > 0 selects the local-window extension of the attention. */
 EOS_ORACLE_API int eos_oracle_bert_embedder(const int32_t *input_ids, const int32_t *mask, const int32_t *type_ids,
                                             int batch, int tokens, const float *tok, int vocab, const float *pos,
                                             int max_pos, const float *typ, int type_vocab, const float *emb_gamma,
                                             const float *emb_beta, const float *const *layer_weights, int layers,
                                             int hidden, int inter, int heads, double eps, int pooling,
-                                            const float *head_w, int head_out, float *out, int workers) {
+                                            const float *head_w, int head_out, int window, float *out, int workers) {
     int64_t rows = (int64_t)batch * tokens;
     int32_t *pos_ids = (int32_t *)malloc(sizeof(int32_t) * (size_t)rows);
     for (int b = 0; b < batch; b++)
@@ -500,8 +518,8 @@ EOS_ORACLE_API int eos_oracle_bert_embedder(const int32_t *input_ids, const int3
         return rc;
     }
     for (int l = 0; l < layers; l++)
-        eos_oracle_bert_layer(hs, mask, batch, tokens, hidden, inter, heads, layer_weights + (size_t)l * 16, eps,
-                              workers);
+        bert_layer_impl(hs, mask, batch, tokens, hidden, inter, heads, layer_weights + (size_t)l * 16, eps, window,
+                        workers);
     float *pooled = (float *)malloc(sizeof(float) * (size_t)batch * hidden);
     float *normed = (float *)malloc(sizeof(float) * (size_t)batch * hidden);
     if (pooling == 1)

@@ -215,7 +215,8 @@ def bert_layer(hidden_states, mask, weights16: Sequence[np.ndarray], heads: int,
 
 
 def bert_embedder(input_ids, mask, type_ids, tok, pos, typ, emb_gamma, emb_beta, layer_weights: Sequence[np.ndarray],
-                  heads: int, eps=1e-12, pooling: str = "masked_mean", head_w=None, workers: int = 1):
+                  heads: int, eps=1e-12, pooling: str = "masked_mean", head_w=None, workers: int = 1,
+                  window: int = 0):
     """layer_weights: 16 float32 tensors per layer, dequantised, dense weights in HF [out,in]."""
     ids, m, tids = map(_i32, (input_ids, mask, type_ids))
     tok, pos, typ, eg, eb = map(_f32, (tok, pos, typ, emb_gamma, emb_beta))
@@ -232,7 +233,7 @@ def bert_embedder(input_ids, mask, type_ids, tok, pos, typ, emb_gamma, emb_beta,
                                         _p(pos), C.c_int(pos.shape[0]), _p(typ), C.c_int(typ.shape[0]), _p(eg), _p(eb),
                                         _ptr_array(ws), C.c_int(layers), C.c_int(hidden), C.c_int(inter),
                                         C.c_int(heads), C.c_double(eps), C.c_int(1 if pooling == "cls" else 0),
-                                        _p(hw), C.c_int(out_dim), _p(out), C.c_int(workers))
+                                        _p(hw), C.c_int(out_dim), C.c_int(window), _p(out), C.c_int(workers))
     if rc:
         raise IndexError(["", "input_ids", "position_ids", "token_type_ids"][rc] + " value out of range")
     return out
