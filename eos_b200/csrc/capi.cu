@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -1330,6 +1331,100 @@ int eos_b200_score_topk(EosB200Corpus* c, const float* h_queries, int q_count, i
         stats->downloaded_bytes = (int64_t)q_count * k * 12;
         cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
     }
+    return EOS_B200_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// scoring without any allocation: scratch in a file-scope device array
+// ------------------------------------------------------------------------------------------------
+namespace {
+constexpr int kNoAllocMaxQueries = 32;
+constexpr int kNoAllocMaxGrid = 160;
+constexpr int kNoAllocMaxKsteps = 64;  // dim <= 1024
+constexpr size_t kNoAllocBfragBytes = (size_t)(kNoAllocMaxQueries / 8) * kNoAllocMaxKsteps * 32 * sizeof(uint2);
+constexpr size_t kNoAllocCandBytes = (size_t)kNoAllocMaxQueries * kNoAllocMaxGrid * kTqMaxK * sizeof(uint64_t);
+constexpr size_t kNoAllocCountBytes = (size_t)kNoAllocMaxQueries * kNoAllocMaxGrid * sizeof(int);
+constexpr size_t kNoAllocOffCand = (kNoAllocBfragBytes + 255) / 256 * 256;
+constexpr size_t kNoAllocOffCount = kNoAllocOffCand + (kNoAllocCandBytes + 255) / 256 * 256;
+constexpr size_t kNoAllocBytes = kNoAllocOffCount + (kNoAllocCountBytes + 255) / 256 * 256;
+
+// In host code this name is only a handle for the runtime's symbol table, not an address a kernel
+// could use: the device address is fetched once per device with cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_score_scratch[kNoAllocBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mu;
+unsigned char* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+}  // namespace
+
+extern "C" {
+
+int eos_b200_score_topk_noalloc(EosB200Corpus* c, const float* d_queries, int q_count, int k, int per_pass,
+                                int64_t* d_ids, float* d_scores, void* stream, char** err) {
+    if (c == nullptr || d_queries == nullptr || d_ids == nullptr || d_scores == nullptr)
+        return fail(err, "score_topk_noalloc: null argument");
+    std::string m = check_score_args(c, q_count, k, per_pass);
+    if (!m.empty()) return fail(err, m);
+    if (c->n == 0) return fail(err, "score_topk_noalloc: empty corpus");
+    EosB200Quantizer* qz = c->qz;
+    const int ksteps = tq_ksteps(qz->dim);
+    if (q_count > kNoAllocMaxQueries)
+        return fail(err, "score_topk_noalloc: at most 32 queries per call (got " + std::to_string(q_count) + ")");
+    if (ksteps > kNoAllocMaxKsteps) return fail(err, "score_topk_noalloc: dim above 1024 is not supported");
+    if (c->grid > kNoAllocMaxGrid) return fail(err, "score_topk_noalloc: more than 160 SMs are not supported");
+    const int dev = qz->rt->device;
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return fail(err, "score_topk_noalloc: device index above 63");
+    CUDA_TRY(cudaSetDevice(dev));
+    unsigned char* base = nullptr;
+    {
+        // once per device, with that device current: the device address of the static array
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        if (g_noalloc_ptr[dev] == nullptr) {
+            void* p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_score_scratch);
+            if (e != cudaSuccess || p == nullptr) {
+                cudaGetLastError();
+                return fail(err, std::string("score_topk_noalloc: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+            }
+            g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+        }
+        base = g_noalloc_ptr[dev];
+    }
+    uint2* bfrag = reinterpret_cast<uint2*>(base);
+    uint64_t* cand = reinterpret_cast<uint64_t*>(base + kNoAllocOffCand);
+    int* cand_count = reinterpret_cast<int*>(base + kNoAllocOffCount);
+    cudaStream_t s = pick_stream(qz->rt, stream);
+    // the array still holds the previous call's lists: the counts are what a stale read would trust
+    CUDA_TRY(cudaMemsetAsync(cand_count, 0, kNoAllocCountBytes, s));
+    launch_tq_prepare(d_queries, q_count, kNoAllocMaxQueries, qz->spec(), bfrag, nullptr, s);
+    const int j = per_pass / 8;
+    const int g_tiles = (q_count + 7) / 8;
+    for (int t0 = 0; t0 < g_tiles; t0 += j) {
+        TqScanArgs a{};
+        a.tiles = c->tiles;
+        a.norms = c->norms;
+        a.n_docs = c->n;
+        a.id_base = (uint32_t)c->id_base;
+        a.dim = qz->dim;
+        a.bfrag = bfrag + (size_t)t0 * ksteps * 32;
+        a.query_tiles = j;
+        a.k = k;
+        a.mag_hi[0] = qz->mag_hi[0];
+        a.mag_hi[1] = qz->mag_hi[1];
+        a.mag_lo[0] = qz->mag_lo[0];
+        a.mag_lo[1] = qz->mag_lo[1];
+        a.cand_keys = cand + (size_t)t0 * 8 * c->grid * kTqMaxK;
+        a.cand_count = cand_count + (size_t)t0 * 8 * c->grid;
+        a.grid = c->grid;
+        a.all_scores = nullptr;
+        a.all_stride = 0;
+        launch_tq_scan(a, s);
+    }
+    launch_tq_merge(cand, (int64_t)c->grid * kTqMaxK, kTqMaxK, c->grid, kTqMaxK, cand_count, q_count, k, 0, d_ids,
+                    d_scores, nullptr, s);
+    CUDA_TRY(cudaGetLastError());
     return EOS_B200_OK;
 }
 

@@ -175,6 +175,15 @@ class Corpus:
                   d_ids, d_scores, d_keys, stream, C.byref(st))
         return st.kernel_launches
 
+    def score_topk_noalloc(self, d_queries: int, q_count: int, k: int, queries_per_pass: int, d_ids: int,
+                           d_scores: int, stream: Optional[int] = None) -> None:
+        """score_topk_device for callers that may not allocate device memory while serving (a fixed memory
+        arena, allocation locked after start-up, or a latency path where cudaMalloc would stall the device).
+        The scratch is a fixed array inside the library: at most 32 queries per call, dim <= 1024; calls on one
+        device share it, so keep them ordered on one stream.  Make the first call before any stream capture."""
+        _lib.call("eos_b200_score_topk_noalloc", self.handle, d_queries, int(q_count), int(k), int(queries_per_pass),
+                  d_ids, d_scores, stream)
+
     def profile_begin(self, max_launches: int) -> None:
         _lib.call("eos_b200_corpus_profile_begin", self.handle, int(max_launches))
 

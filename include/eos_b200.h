@@ -246,6 +246,25 @@ EOS_B200_API int eos_b200_score_topk(EosB200Corpus* corpus, const float* h_queri
 EOS_B200_API int eos_b200_score_topk_device(EosB200Corpus* corpus, const float* d_queries, int q_count, int k,
                                int queries_per_pass, int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream,
                                EosB200Stats* stats, char** err);
+/* No counterpart in Eos: a scoring call for hosts that must not allocate device memory while they
+ * serve queries -- for example a caller that holds the GPU inside a pre-sized memory arena, runs
+ * with allocation forbidden after start-up, or sits on a latency path where a cudaMalloc (which can
+ * synchronise the whole device) is unacceptable.  Same result as eos_b200_score_topk_device, but
+ * every byte of scratch (query fragments, per-CTA candidate lists and their counts) lives in one
+ * file-scope __device__ array inside the library instead of in memory the corpus handle
+ * allocates on demand.  The call itself performs no cudaMalloc / cudaFree and calls no allocating
+ * routine; the caller passes the device buffers for queries, ids and scores.
+ * Limits: q_count <= 32, dim <= 1024, k <= 128, at most 160 SMs; larger requests are rejected
+ * with an error, nothing is truncated.  The array is about 5.1 MB and is resident on every GPU
+ * that loads the library until the process exits.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call before starting any stream capture.  All calls on a device share the array and
+ * it keeps the previous call's contents: calls whose GPU work overlaps (two streams, two
+ * threads, two corpora) race on it, so keep them ordered on one stream. */
+EOS_B200_API int eos_b200_score_topk_noalloc(EosB200Corpus* corpus, const float* d_queries, int q_count, int k,
+                                             int queries_per_pass, int64_t* d_ids, float* d_scores, void* stream,
+                                             char** err);
+
 /* Device time of the scan kernel alone (CUDA events around every scan launch between begin and
  * end): out_ms = total milliseconds, out_launches = scan launches covered. */
 EOS_B200_API int eos_b200_corpus_profile_begin(EosB200Corpus* corpus, int max_launches, char** err);
