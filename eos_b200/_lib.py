@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libeos_b200.so")
+LIB_PATH = os.environ.get("EOS_B200_LIBRARY") or os.path.join(_HERE, "libeos_b200.so")
 
 OK, ERROR, DEVICE_STATUS = 0, 1, 2
 

@@ -1,0 +1,525 @@
+// Multi-head self-attention, head_dim 64, sequences of up to 512 keys, on the 5th-generation
+// tensor cores (tcgen05) with S and O in tensor memory.
+//
+// Reference semantics: bertSelfAttentionContextRange, runtime/backend/bert_encoder_layer_ops.go:326-379
+// (device twin manta_bert_attention_context, runtime/backends/cuda/native_linux.go:2857-2969):
+// per (query, head): logits q.k/sqrt(hd) over unmasked keys, max-subtracted softmax, sum p.v;
+// no visible key -> zeros.  Masked rows never exist here (packed layout), so "unmasked keys" are the
+// first key_count rows of the sequence.
+//
+// One persistent CTA per SM walks work items (sequence, 128-query tile, head):
+//   warp 0       TMA producer: Q tile, then K tiles and V tiles (128 rows x 64, 128B swizzle) into rings.
+//   warp 1       MMA issuer: S_j = Q K_j^T per key tile j (fp32, 128 TMEM columns each), then
+//                O += P_j V_j (V as an MN-major operand, straight from the row-major tile TMA
+//                delivered), O reusing S_0's columns.  Work is cut into sub-items of at most two key
+//                tiles = half of tensor memory, so the S phase of the next sub-item is issued before
+//                the P V phase of the current one and two sub-items are always in flight.
+//                The row sums l = P 1 come from a third, 16-column MMA against a tile of ones, so they are
+//                the fp32 sums of exactly the f16 probabilities that multiply V.
+//   warps 4-11   softmax (thread = query row, two warps per row split the columns): pass A reads all
+//                S tiles for the row maximum, pass B re-reads them, writes P = exp2(s - m) (packed f16 ex2)
+//                into the 128B-swizzled K-major layout the second MMA consumes; finally O / l -> f16 -> global.
+// All scores of a sub-item are resident in TMEM before any probability is formed, so O is never
+// rescaled in place; a sequence longer than 256 keys is two sub-items whose partial (O, m, l) are
+// merged in registers.  All mbarrier waits are bounded (abort flag + status word).
+#include "attention_tc.cuh"
+
+#include "common.cuh"
+#include "tma_util.cuh"
+
+namespace eosb {
+
+#ifdef EOSB_ATTN_TIMING
+__device__ long long g_attn_timing[16];
+#define TMARK(i) do { if (blockIdx.x == 0 && threadIdx.x == 128) { long long now__ = clock64(); g_attn_timing[i] += now__ - tlast__; tlast__ = now__; } } while (0)
+#else
+#define TMARK(i) do { } while (0)
+#endif
+
+namespace {
+
+constexpr int kAtThreads = 384;
+constexpr int kQStages = 2;
+constexpr int kKvStages = 6;
+constexpr uint32_t kTileBytes = 128 * 64 * 2;   // 16 KB: Q, K_j or V_j
+constexpr uint32_t kPBytes = 128 * 128 * 2;     // 32 KB: one P tile (two 128x64 blocks)
+constexpr uint32_t kOffQ = 0;
+constexpr uint32_t kOffKv = kOffQ + kQStages * kTileBytes;
+constexpr uint32_t kOffP = kOffKv + kKvStages * kTileBytes;
+constexpr uint32_t kOffOnes = kOffP + 2 * kPBytes;              // 16 x 64 f16 of 1.0: B operand of the row-sum MMA
+constexpr uint32_t kOffRed = kOffOnes + 2048;                   // 2 x 128 floats: row max exchange
+constexpr uint32_t kOffBars = kOffRed + 2 * 128 * 4;
+constexpr uint32_t kNumBars = 2 * kQStages + 2 * kKvStages + 4 + 2 + 2 + 2 + 2;
+constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
+constexpr uint32_t kAtSmemBytes = kOffMisc + 16 + 1024;
+
+struct WorkItem {
+    int row0;    // first packed row of the sequence
+    int nrows;   // query rows of the sequence
+    int nkeys;   // key rows of the sequence
+    int q0;      // first query of this tile (relative to row0)
+    int head;
+    int ntiles;  // key tiles of 128
+};
+
+__device__ __forceinline__ WorkItem decode_item(int w, int heads, const int4* __restrict__ qtile_info) {
+    const int4 q = __ldg(qtile_info + w / heads);
+    WorkItem it;
+    it.row0 = q.x;
+    it.nrows = q.y;
+    it.nkeys = q.z > 512 ? 512 : q.z;  // the host only selects this kernel when tokens <= 512
+    it.q0 = q.w;
+    it.head = w % heads;
+    it.ntiles = (it.nkeys + 127) >> 7;
+    return it;
+}
+
+// A work item is processed as one or two sub-items of at most two key tiles (256 keys): a sub-item
+// needs only half of tensor memory, so two of them are in flight per SM; the two partial softmax
+// results of a long sequence are merged in registers (same rule as split-key flash decoding).
+struct Walker {
+    int w, step, total, heads;
+    const int4* info;
+    int sub;
+    unsigned item_no;  // items visited so far
+    WorkItem wi;
+    __device__ __forceinline__ void init(int first, int stride, int tot, int h, const int4* p) {
+        w = first; step = stride; total = tot; heads = h; info = p; sub = 0; item_no = 0;
+        if (w < total) wi = decode_item(w, heads, info);
+    }
+    __device__ __forceinline__ bool valid() const { return w < total; }
+    __device__ __forceinline__ int nsub() const { return wi.ntiles > 2 ? 2 : 1; }
+    __device__ __forceinline__ int tile0() const { return sub * 2; }
+    __device__ __forceinline__ int nt() const { const int r = wi.ntiles - sub * 2; return r > 2 ? 2 : (r < 0 ? 0 : r); }
+    __device__ __forceinline__ bool first_sub() const { return sub == 0; }
+    __device__ __forceinline__ bool last_sub() const { return sub + 1 == nsub(); }
+    __device__ __forceinline__ void next() {
+        if (sub + 1 < nsub()) { ++sub; return; }
+        w += step; sub = 0; ++item_no;
+        if (w < total) wi = decode_item(w, heads, info);
+    }
+};
+
+// MN-major operand tile (row = K index, 64 contiguous MN elements = 128 bytes per row, 128B
+// swizzle): 8-row groups of 1024 bytes along K (stride byte offset), a single 64-wide MN block.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ uint32_t ex2_f16x2(float x0, float x1) {
+    __half2 h = __floats2half2_rn(x0, x1);
+    uint32_t hx = *reinterpret_cast<uint32_t*>(&h), px;
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(px) : "r"(hx));
+    return px;
+}
+
+__global__ void __launch_bounds__(kAtThreads, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict__ cu_qtiles,
+               const int4* __restrict__ qtile_info, int batch, int hidden, int heads, __half* __restrict__ ctx,
+               int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* sm = smem_raw + (base - raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const uint32_t bar0 = base + kOffBars;
+    auto q_full = [&](int s) { return bar0 + 8u * s; };
+    auto q_empty = [&](int s) { return bar0 + 8u * (kQStages + s); };
+    auto kv_full = [&](int s) { return bar0 + 8u * (2 * kQStages + s); };
+    auto kv_empty = [&](int s) { return bar0 + 8u * (2 * kQStages + kKvStages + s); };
+    const uint32_t bar1 = bar0 + 8u * (2 * kQStages + 2 * kKvStages);
+    auto s_full = [&](int h, int t) { return bar1 + 8u * (h * 2 + t); };   // [half][tile]
+    auto p_full = [&](int s) { return bar1 + 8u * (4 + s); };
+    auto p_empty = [&](int s) { return bar1 + 8u * (6 + s); };
+    auto o_full = [&](int h) { return bar1 + 8u * (8 + h); };
+    auto half_free = [&](int h) { return bar1 + 8u * (10 + h); };
+
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + kOffMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
+    float* red = reinterpret_cast<float*>(sm + kOffRed);
+
+    const int total_items = cu_qtiles[batch] * heads;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < kQStages; ++s) {
+            mbar_init(q_full(s), 1);
+            mbar_init(q_empty(s), 1);
+        }
+        for (int s = 0; s < kKvStages; ++s) {
+            mbar_init(kv_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+        }
+        for (int h = 0; h < 2; ++h) {
+            mbar_init(s_full(h, 0), 1);
+            mbar_init(s_full(h, 1), 1);
+            mbar_init(p_full(h), 8);
+            mbar_init(p_empty(h), 1);
+            mbar_init(o_full(h), 1);
+            mbar_init(half_free(h), 8);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&tm_qkv);
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+        tmem_relinquish();
+    }
+    if (warp == 3) {
+        for (int i = lane; i < 2048 / 4; i += 32) reinterpret_cast<uint32_t*>(sm + kOffOnes)[i] = 0x3c003c00u;
+        fence_proxy_async_smem();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        // order of the K/V ring = order of consumption by the MMA warp: K(0); then K(n+1), V(n) for n = 0, 1, ...
+        if (lane == 0) {
+            uint32_t kvc = 0;
+            bool ok = true;
+            auto load_q = [&](const Walker& wk) -> bool {
+                const int qs = wk.item_no % kQStages;
+                if (!mbar_wait(q_empty(qs), ((wk.item_no / kQStages) & 1u) ^ 1u, abort_flag)) return false;
+                mbar_arrive_expect_tx(q_full(qs), kTileBytes);
+                tma_load_2d(base + kOffQ + qs * kTileBytes, &tm_qkv, wk.wi.head * 64, wk.wi.row0 + wk.wi.q0, q_full(qs));
+                return true;
+            };
+            auto load_kv = [&](const Walker& wk, int part) -> bool {  // part 1 = K, 2 = V
+                const int x = part * hidden + wk.wi.head * 64;
+                for (int t = 0; t < wk.nt(); ++t, ++kvc) {
+                    const int s = kvc % kKvStages;
+                    if (!mbar_wait(kv_empty(s), ((kvc / kKvStages) & 1u) ^ 1u, abort_flag)) return false;
+                    mbar_arrive_expect_tx(kv_full(s), kTileBytes);
+                    tma_load_2d(base + kOffKv + s * kTileBytes, &tm_qkv, x, wk.wi.row0 + (wk.tile0() + t) * 128, kv_full(s));
+                }
+                return true;
+            };
+            Walker cur, nxt;
+            cur.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info);
+            nxt = cur;
+            if (cur.valid()) {
+                ok = load_q(cur) && load_kv(cur, 1);
+                nxt.next();
+            }
+            while (ok && cur.valid()) {
+                if (nxt.valid()) {
+                    if (nxt.first_sub()) ok = load_q(nxt);
+                    ok = ok && load_kv(nxt, 1);
+                }
+                ok = ok && load_kv(cur, 2);
+                cur = nxt;
+                if (nxt.valid()) nxt.next();
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc_f16(128, 128);
+            constexpr uint32_t idesc_o = umma_idesc_f16(128, 64) | (1u << 16);  // B (= V) is MN-major
+            constexpr uint32_t idesc_l = umma_idesc_f16(128, 16);               // row sums: P x ones
+            uint32_t kvc = 0, pc = 0;
+            bool ok = true;
+            // S phase of sub-item number n (in tensor-memory half n & 1)
+            auto issue_s = [&](const Walker& wk, uint32_t n) -> bool {
+                const int h = n & 1u;
+                if (n >= 2 && !mbar_wait(half_free(h), ((n >> 1) - 1u) & 1u, abort_flag)) return false;
+                const int qs = wk.item_no % kQStages;
+                if (wk.first_sub() && !mbar_wait(q_full(qs), (wk.item_no / kQStages) & 1u, abort_flag)) return false;
+                tc_fence_after();
+                const uint32_t q_addr = base + kOffQ + qs * kTileBytes;
+                for (int t = 0; t < wk.nt(); ++t, ++kvc) {
+                    const int s = kvc % kKvStages;
+                    if (!mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag)) return false;
+                    tc_fence_after();
+                    const uint32_t k_addr = base + kOffKv + s * kTileBytes;
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_f16(tmem_base + h * 256 + t * 128, umma_desc_sw128(q_addr + kk * 32),
+                                 umma_desc_sw128(k_addr + kk * 32), idesc_s, kk > 0 ? 1u : 0u);
+                    umma_commit(kv_empty(s));
+                    umma_commit(s_full(h, t));
+                }
+                if (wk.last_sub()) {
+                    if (wk.wi.ntiles > 0) umma_commit(q_empty(qs)); else mbar_arrive(q_empty(qs));
+                }
+                return true;
+            };
+            auto issue_pv = [&](const Walker& wk, uint32_t n) -> bool {
+                const int h = n & 1u;
+                for (int t = 0; t < wk.nt(); ++t, ++kvc, ++pc) {
+                    const int s = kvc % kKvStages;
+                    const int pb = pc & 1;
+                    if (!mbar_wait(p_full(pb), (pc >> 1) & 1u, abort_flag) ||
+                        !mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag))
+                        return false;
+                    tc_fence_after();
+                    const uint32_t p_addr = base + kOffP + pb * kPBytes;
+                    const uint32_t v_addr = base + kOffKv + s * kTileBytes;
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint64_t pd = umma_desc_sw128(p_addr + (kk >> 2) * (kPBytes / 2) + (kk & 3) * 32);
+                        umma_f16(tmem_base + h * 256, pd, umma_desc_sw128_mn(v_addr + kk * 2048), idesc_o,
+                                 (t > 0 || kk > 0) ? 1u : 0u);
+                        umma_f16(tmem_base + h * 256 + 64, pd, umma_desc_sw128(base + kOffOnes + (kk & 3) * 32), idesc_l,
+                                 (t > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(kv_empty(s));
+                    umma_commit(p_empty(pb));
+                }
+                if (wk.nt() > 0) umma_commit(o_full(h));
+                return true;
+            };
+            Walker cur, nxt;
+            cur.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info);
+            nxt = cur;
+            uint32_t n = 0;
+            if (cur.valid()) {
+                ok = issue_s(cur, 0);
+                nxt.next();
+            }
+            while (ok && cur.valid()) {
+                if (nxt.valid()) ok = issue_s(nxt, n + 1);
+                ok = ok && issue_pv(cur, n);
+                cur = nxt;
+                if (nxt.valid()) nxt.next();
+                ++n;
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------ softmax + epilogue
+        const int w8 = warp - 4;
+        const int quarter = warp & 3;          // TMEM lane quarter this warp may access
+        const int half = w8 >> 2;              // which 64 columns of every 128-column tile
+        const int r = quarter * 32 + lane;     // query row inside the tile
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const float sl2 = 0.125f * 1.4426950408889634f;  // 1/sqrt(64) * log2(e)
+        uint32_t pc = 0, o_cnt[2] = {0, 0}, s_cnt[2][2] = {{0, 0}, {0, 0}};
+        bool ok = true;
+        float part_o[32], part_m = 0.f, part_l = 0.f;  // first half of a two-part item, kept across sub-items
+
+        // epilogue of sub-item number n (deferred by one sub-item so that its PV MMAs overlap the next
+        // sub-item's softmax): O / l, or the merge of two partial results
+        auto epilogue = [&](const Walker& wk, uint32_t n, float ms_n) -> bool {
+            const int h = n & 1u;
+            const int qrow = wk.wi.q0 + r;
+            __half* out = ctx + (size_t)(wk.wi.row0 + qrow) * hidden + wk.wi.head * 64 + half * 32;
+            float o[32], l = 0.f;
+            if (wk.nt() > 0) {
+                if (!mbar_wait(o_full(h), o_cnt[h] & 1u, abort_flag)) return false;
+                ++o_cnt[h];
+                tc_fence_after();
+                uint32_t v[32], lv[16];
+                __syncwarp();
+                tmem_ld_32x32(tmem_base + lane_addr + h * 256 + half * 32, v);
+                tmem_ld_32x16(tmem_base + lane_addr + h * 256 + 64, lv);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) o[e] = __uint_as_float(v[e]);
+                l = __uint_as_float(lv[0]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) o[e] = 0.f;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(half_free(h));
+            if (wk.nsub() == 2 && wk.first_sub()) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) part_o[e] = o[e];
+                part_m = ms_n;
+                part_l = l;
+                return true;
+            }
+            if (wk.nsub() == 2) {  // second part: merge with the first
+                const float m = fmaxf(part_m, ms_n);
+                const float a = exp2f(part_m - m), b = exp2f(ms_n - m);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) o[e] = part_o[e] * a + o[e] * b;
+                l = part_l * a + l * b;
+            }
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            if (qrow < wk.wi.nrows) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 ov;
+                    uint32_t* ow = reinterpret_cast<uint32_t*>(&ov);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        __half2 hh = __floats2half2_rn(o[q * 8 + 2 * e] * inv, o[q * 8 + 2 * e + 1] * inv);
+                        ow[e] = *reinterpret_cast<uint32_t*>(&hh);
+                    }
+                    *reinterpret_cast<uint4*>(out + q * 8) = ov;
+                }
+            }
+            return true;
+        };
+
+        Walker cur, prev;
+        cur.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info);
+        prev = cur;
+        uint32_t n = 0;
+        float ms_prev = 0.f;
+#ifdef EOSB_ATTN_TIMING
+        long long tlast__ = clock64();
+#endif
+        bool have_prev = false;
+        while (ok && cur.valid()) {
+            const int h = n & 1u;
+            const int nt = cur.nt();
+            const int key0 = cur.tile0() * 128;           // first key of this sub-item
+            const int nkeys = cur.wi.nkeys;
+            float ms = 0.f;
+            if (nt > 0) {
+                // pass A: row maximum over the visible keys of this sub-item
+                float mx = -INFINITY;
+                for (int t = 0; t < nt; ++t) {
+                    if (!mbar_wait(s_full(h, t), s_cnt[h][t] & 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    ++s_cnt[h][t];
+                    tc_fence_after();
+                    TMARK(0);
+                    const int col0 = key0 + t * 128 + half * 64;   // key index of this thread's first column
+                    if (col0 >= nkeys) continue;
+                    uint32_t v0[32], v1[32];
+                    __syncwarp();
+                    tmem_ld_32x32(tmem_base + lane_addr + h * 256 + t * 128 + half * 64, v0);
+                    tmem_ld_32x32(tmem_base + lane_addr + h * 256 + t * 128 + half * 64 + 32, v1);
+                    tmem_ld_wait();
+                    const int lim = nkeys - col0;
+                    if (lim >= 64) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fmaxf(__uint_as_float(v0[e]), __uint_as_float(v1[e])));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            if (e < lim) mx = fmaxf(mx, __uint_as_float(v0[e]));
+                            if (e + 32 < lim) mx = fmaxf(mx, __uint_as_float(v1[e]));
+                        }
+                    }
+                }
+                if (!ok) break;
+                TMARK(1);
+                red[half * 128 + r] = mx;
+                named_bar_sync(2, 256);
+                mx = fmaxf(mx, red[(half ^ 1) * 128 + r]);
+                named_bar_sync(2, 256);
+                ms = mx * sl2;  // every sub-item holds at least one visible key, so mx is finite
+                TMARK(2);
+                // the previous sub-item's epilogue goes here: its P V MMAs have had pass A's time to finish,
+                // and freeing its half of tensor memory now lets the next S phase run under pass B
+                if (have_prev) {
+                    ok = epilogue(prev, n - 1, ms_prev);
+                    have_prev = false;
+                    if (!ok) break;
+                }
+                TMARK(5);
+                // pass B: probabilities, P tiles for the second MMA
+                for (int t = 0; t < nt; ++t, ++pc) {
+                    const int pb = pc & 1;
+                    if (!mbar_wait(p_empty(pb), ((pc >> 1) & 1u) ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    TMARK(3);
+                    uint8_t* prow = sm + kOffP + pb * kPBytes + half * (kPBytes / 2) + (r >> 3) * 1024 + (r & 7) * 128;
+                    const int col0 = key0 + t * 128 + half * 64;
+                    const int lim = nkeys - col0;
+                    uint32_t packed[32];
+                    if (lim > 0) {
+                        uint32_t v0[32], v1[32];
+                        __syncwarp();
+                        tmem_ld_32x32(tmem_base + lane_addr + h * 256 + t * 128 + half * 64, v0);
+                        tmem_ld_32x32(tmem_base + lane_addr + h * 256 + t * 128 + half * 64 + 32, v1);
+                        tmem_ld_wait();
+                        if (lim >= 64) {
+#pragma unroll
+                            for (int e = 0; e < 32; e += 2) {
+                                packed[e >> 1] = ex2_f16x2(fmaf(__uint_as_float(v0[e]), sl2, -ms),
+                                                           fmaf(__uint_as_float(v0[e + 1]), sl2, -ms));
+                                packed[16 + (e >> 1)] = ex2_f16x2(fmaf(__uint_as_float(v1[e]), sl2, -ms),
+                                                                  fmaf(__uint_as_float(v1[e + 1]), sl2, -ms));
+                            }
+                        } else {  // the sequence's last, partial tile: masked keys get exp2(-inf) = 0
+#pragma unroll
+                            for (int e = 0; e < 32; e += 2) {
+                                const float a0 = e < lim ? fmaf(__uint_as_float(v0[e]), sl2, -ms) : -INFINITY;
+                                const float a1 = e + 1 < lim ? fmaf(__uint_as_float(v0[e + 1]), sl2, -ms) : -INFINITY;
+                                const float b0 = e + 32 < lim ? fmaf(__uint_as_float(v1[e]), sl2, -ms) : -INFINITY;
+                                const float b1 = e + 33 < lim ? fmaf(__uint_as_float(v1[e + 1]), sl2, -ms) : -INFINITY;
+                                packed[e >> 1] = ex2_f16x2(a0, a1);
+                                packed[16 + (e >> 1)] = ex2_f16x2(b0, b1);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) packed[e] = 0u;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        *reinterpret_cast<uint4*>(prow + ((q ^ (r & 7)) << 4)) =
+                            make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+                    tc_fence_before();  // S columns of this half are about to be overwritten by O
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(p_full(pb));
+                    TMARK(4);
+                }
+                if (!ok) break;
+            }
+            if (have_prev) ok = epilogue(prev, n - 1, ms_prev);
+            TMARK(5);
+            prev = cur;
+            ms_prev = ms;
+            have_prev = true;
+            cur.next();
+            ++n;
+        }
+        if (ok && have_prev) epilogue(prev, n - 1, ms_prev);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *abort_flag != 0 && status != nullptr) atomicExch(status, kStatusPipelineTimeout);
+}
+
+}  // namespace
+
+#ifdef EOSB_ATTN_TIMING
+extern "C" __attribute__((visibility("default"))) int eos_b200_debug_attn_timing(long long* out16, int reset) {
+    long long zero[16] = {0};
+    if (cudaMemcpyFromSymbol(out16, g_attn_timing, sizeof(zero)) != cudaSuccess) return 1;
+    if (reset && cudaMemcpyToSymbol(g_attn_timing, zero, sizeof(zero)) != cudaSuccess) return 1;
+    return 0;
+}
+#endif
+
+std::string attn_tc_global_init() {
+    cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmemBytes);
+    if (e != cudaSuccess) return std::string("cudaFuncSetAttribute(attn_tc_kernel): ") + cudaGetErrorString(e);
+    return "";
+}
+
+std::string attn_tc_make_plan(AttnTcPlan* plan, const __half* qkv, int m_alloc, int hidden) {
+    return encode_2d(&plan->tm_qkv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, qkv, (uint64_t)3 * hidden, (uint64_t)m_alloc,
+                     (uint64_t)3 * hidden * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+void attn_tc_launch(const AttnTcPlan& plan, const SeqLayout& lay, int batch, int hidden, int heads, __half* ctx,
+                    int* status, int sm_count, cudaStream_t stream) {
+    attn_tc_kernel<<<sm_count, kAtThreads, kAtSmemBytes, stream>>>(plan.tm_qkv, lay.cu_qtiles, lay.qtile_info, batch,
+                                                                    hidden, heads, ctx, status);
+}
+
+}  // namespace eosb

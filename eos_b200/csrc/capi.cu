@@ -12,6 +12,7 @@
 
 #include "../../include/eos_b200.h"
 #include "common.cuh"
+#include "attention_tc.cuh"
 #include "encoder_kernels.cuh"
 #include "gemm_tc.cuh"
 #include "turboquant.cuh"
@@ -134,6 +135,7 @@ int eos_b200_runtime_create(int device, EosB200Runtime** out, char** err) {
         return fail(err, msg);
     }
     std::string ge = gemm_global_init();
+    if (ge.empty()) ge = attn_tc_global_init();
     if (ge.empty()) {
         cudaError_t se = tq_scan_init();
         if (se != cudaSuccess) ge = std::string("tq_scan_init: ") + cudaGetErrorString(se);
@@ -355,6 +357,8 @@ struct EosB200Encoder {
     __half *h0 = nullptr, *h1 = nullptr, *qkv = nullptr, *ctx = nullptr, *pre = nullptr, *ffn = nullptr;
     float *pooled = nullptr, *d_out = nullptr;
     std::vector<GemmPlan> plans;  // 4 per layer: qkv, attn-out, inter, out
+    AttnTcPlan attn_plan{};
+    bool attn_tc = false;        // tensor-memory attention kernel usable (head_dim 64, no window)
     Profiler prof;
     int launches_per_forward = 0;
 };
@@ -371,6 +375,8 @@ void free_workspace(EosB200Encoder* e) {
     dev_free(e->lay.cls_row);
     dev_free(e->lay.row_src);
     dev_free(e->lay.total_rows);
+    dev_free(e->lay.cu_qtiles);
+    dev_free(e->lay.qtile_info);
     dev_free(e->h0);
     dev_free(e->h1);
     dev_free(e->qkv);
@@ -404,6 +410,8 @@ int ensure_workspace(EosB200Encoder* e, int batch, int tokens, char** err) {
     CUDA_TRY(dev_alloc(&e->lay.cls_row, (size_t)nb));
     CUDA_TRY(dev_alloc(&e->lay.row_src, (size_t)m));
     CUDA_TRY(dev_alloc(&e->lay.total_rows, 1));
+    CUDA_TRY(dev_alloc(&e->lay.cu_qtiles, (size_t)nb + 1));
+    CUDA_TRY(dev_alloc(&e->lay.qtile_info, (size_t)(m / 128 + nb + 1)));
     CUDA_TRY(dev_alloc(&e->h0, (size_t)m * D));
     CUDA_TRY(dev_alloc(&e->h1, (size_t)m * D));
     CUDA_TRY(dev_alloc(&e->qkv, (size_t)m * 3 * D));
@@ -421,6 +429,12 @@ int ensure_workspace(EosB200Encoder* e, int batch, int tokens, char** err) {
     e->cap_batch = nb;
     e->cap_elems = ne;
     e->m_alloc = m;
+    e->attn_tc = false;
+    if (e->hidden / e->heads == 64 && e->window <= 0 && std::getenv("EOS_B200_LEGACY_ATTENTION") == nullptr) {
+        std::string ae = attn_tc_make_plan(&e->attn_plan, e->qkv, m, D);
+        if (!ae.empty()) return fail(err, "attention plan: " + ae);
+        e->attn_tc = true;
+    }
     e->plans.resize((size_t)e->layers * 4);
     const int act_mode = e->activation == EOS_B200_ACT_GELU_TANH ? kEpiBiasGeluTanh : kEpiBiasGeluErf;
     for (int l = 0; l < e->layers; ++l) {
@@ -470,7 +484,7 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
     int launches = 0;
     Profiler& pf = e->prof;
     pf.launch(kClsLayout, s, [&] { launch_seq_layout(d_mask, batch, tokens, cls, e->lay, s); });
-    launches += 3;
+    launches += 4;
     pf.launch(kClsEmbed, s, [&] {
         launch_embed_ln(d_ids, d_types, e->lay, tokens, e->tok, e->vocab, e->pos, e->max_pos, e->typ, e->type_vocab,
                         e->eg, e->eb, e->eps, D, e->m_alloc, e->h0, rt->d_status, rt->sm_count, s);
@@ -480,7 +494,10 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
         LayerW& w = e->lw[l];
         pf.launch(kClsGemm, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 0], s); });
         pf.launch(kClsAttention, s, [&] {
-            launch_attention(e->qkv, e->lay, batch, tokens, D, e->heads, e->window, e->ctx, s);
+            if (e->attn_tc && tokens <= 512)
+                attn_tc_launch(e->attn_plan, e->lay, batch, D, e->heads, e->ctx, rt->d_status, rt->sm_count, s);
+            else
+                launch_attention(e->qkv, e->lay, batch, tokens, D, e->heads, e->window, e->ctx, s);
         });
         pf.launch(kClsGemm, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 1], s); });
         pf.launch(kClsLayerNorm, s, [&] {
@@ -668,7 +685,7 @@ int eos_b200_encoder_profile_end(EosB200Encoder* enc, void* stream, EosB200Encod
             case kClsLayerNorm: out->layernorm_ms += ms; out->layernorm_launches++; break;
             case kClsEmbed: out->embed_ms += ms; out->other_launches++; break;
             case kClsPool: out->pool_ms += ms; out->other_launches += enc->head_w != nullptr ? 2 : 1; break;
-            default: out->layout_ms += ms; out->other_launches += 3; break;
+            default: out->layout_ms += ms; out->other_launches += 4; break;
         }
     }
     enc->prof.reset();

@@ -47,15 +47,15 @@ __global__ void seq_count_kernel(const int32_t* __restrict__ mask, int tokens, i
     }
 }
 
-__global__ void seq_scan_kernel(const int* row_count, int batch, int* cu_rows, int* total_rows) {
-    // single block; sequential chunks of blockDim.x with a running carry
+__global__ void seq_scan_kernel(const int* row_count, int batch, int unit, int* cu_rows, int* total_rows) {
+    // single block; sequential chunks of blockDim.x with a running carry; scans ceil(row_count / unit)
     __shared__ int buf[1024];
     __shared__ int carry;
     if (threadIdx.x == 0) carry = 0;
     __syncthreads();
     for (int base = 0; base < batch; base += blockDim.x) {
         const int i = base + threadIdx.x;
-        const int v = i < batch ? row_count[i] : 0;
+        const int v = i < batch ? (row_count[i] + unit - 1) / unit : 0;
         buf[threadIdx.x] = v;
         __syncthreads();
         for (int o = 1; o < blockDim.x; o <<= 1) {
@@ -71,12 +71,13 @@ __global__ void seq_scan_kernel(const int* row_count, int batch, int* cu_rows, i
     }
     if (threadIdx.x == 0) {
         cu_rows[batch] = carry;
-        *total_rows = carry;
+        if (total_rows != nullptr) *total_rows = carry;
     }
 }
 
 __global__ void seq_fill_kernel(const int32_t* __restrict__ mask, int tokens, int cls_pooling, const int* cu_rows,
-                                const int* key_count, int* row_src, int* cls_row) {
+                                const int* key_count, const int* cu_qtiles, int* row_src, int* cls_row,
+                                int4* qtile_info) {
     const int b = blockIdx.x;
     const int32_t* m = mask + (size_t)b * tokens;
     const int row0 = cu_rows[b];
@@ -105,6 +106,12 @@ __global__ void seq_fill_kernel(const int32_t* __restrict__ mask, int tokens, in
         __syncthreads();
         if (threadIdx.x == 0) carry = warp_off[32];
         __syncthreads();
+    }
+    {
+        const int nrows = cu_rows[b + 1] - row0;
+        const int qt0 = cu_qtiles[b];
+        for (int q = threadIdx.x; q < cu_qtiles[b + 1] - qt0; q += blockDim.x)
+            qtile_info[qt0 + q] = make_int4(row0, nrows, key_count[b], q * 128);
     }
     if (threadIdx.x == 0) {
         if (cls_pooling && m[0] == 0) {
@@ -747,9 +754,10 @@ void dispatch_chunks(int dim, F&& f) {
 void launch_seq_layout(const int32_t* mask, int batch, int tokens, int cls_pooling, const SeqLayout& lay,
                        cudaStream_t stream) {
     seq_count_kernel<<<batch, 256, 0, stream>>>(mask, tokens, cls_pooling, lay.key_count, lay.row_count);
-    seq_scan_kernel<<<1, 1024, 0, stream>>>(lay.row_count, batch, lay.cu_rows, lay.total_rows);
-    seq_fill_kernel<<<batch, 256, 0, stream>>>(mask, tokens, cls_pooling, lay.cu_rows, lay.key_count, lay.row_src,
-                                               lay.cls_row);
+    seq_scan_kernel<<<1, 1024, 0, stream>>>(lay.row_count, batch, 1, lay.cu_rows, lay.total_rows);
+    seq_scan_kernel<<<1, 1024, 0, stream>>>(lay.row_count, batch, 128, lay.cu_qtiles, nullptr);
+    seq_fill_kernel<<<batch, 256, 0, stream>>>(mask, tokens, cls_pooling, lay.cu_rows, lay.key_count, lay.cu_qtiles,
+                                               lay.row_src, lay.cls_row, lay.qtile_info);
 }
 
 void launch_embed_ln(const int32_t* ids, const int32_t* types, const SeqLayout& lay, int tokens, const __half* tok,

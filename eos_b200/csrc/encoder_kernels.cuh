@@ -15,6 +15,8 @@ struct SeqLayout {
     int* cls_row;     // [B]   packed row that holds token 0
     int* row_src;     // [M]   flat index b*T + t of every packed row
     int* total_rows;  // [1]
+    int* cu_qtiles;   // [B+1] exclusive prefix sum of ceil(row_count / 128): 128-query tiles per sequence
+    int4* qtile_info; // [sum of q-tiles] per 128-query tile: {first row of the sequence, its rows, its keys, tile's first query}
 };
 
 void launch_seq_layout(const int32_t* mask, int batch, int tokens, int cls_pooling, const SeqLayout& lay,

@@ -6,16 +6,16 @@
 // runBGEFullEncoderHidden :7941-8190) and the host loop denseHFRange
 // (runtime/backend/bert_encoder_layer_ops.go:452-462): y = x W^T + b with W in HF [out,in] layout.
 //
-// Design (one persistent CTA per SM, 384 threads, warp-specialised):
+// Design (one persistent CTA per SM, 640 threads, warp-specialised):
 //   warp 0      TMA producer: A tile 128x64 f16 (128B swizzle) and the W tile 256x64 (8-bit codes,
 //               no swizzle) per k-block into a 4-stage ring, completion on mbarriers.
-//   warps 4-7   dequantisers: expand the 8-bit codes to f16 in shared memory, written directly in
+//   warps 4-11  dequantisers: expand the 8-bit codes to f16 in shared memory, written directly in
 //               the 128B-swizzled K-major layout the MMA reads (int8 -> f16 is exact; the
 //               per-channel scale is applied in fp32 in the epilogue, which is the same product:
 //               sum_k a_k (s_n q_kn) = s_n sum_k a_k q_kn).
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16, f16 x f16 -> f32)
 //               with the accumulator in tensor memory; tcgen05.commit releases ring stages.
-//   warps 8-11  epilogue: tcgen05.ld the 128x256 fp32 accumulator (thread = row), scale, bias,
+//   warps 12-19 epilogue: tcgen05.ld the 128x256 fp32 accumulator (thread = row), scale, bias,
 //               GELU or residual add, f16 stores.  Two accumulators (2 x 256 TMEM columns) let the
 //               epilogue of tile i overlap the main loop of tile i+1.
 //   warp 2      allocates / frees tensor memory.
@@ -24,6 +24,7 @@
 #include "gemm_tc.cuh"
 
 #include "common.cuh"
+#include "tma_util.cuh"
 
 namespace eosb {
 
@@ -34,7 +35,9 @@ constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int kStagesAB = 4;    // ring depth of the TMA-fed stages
 constexpr int kStagesB16 = 2;   // ring depth of the dequantised W tiles (int8 mode)
-constexpr int kThreads = 384;
+constexpr int kDequantWarps = 8;
+constexpr int kEpilogueWarps = 8;  // two per TMEM lane quarter, each owning half of the tile's columns
+constexpr int kThreads = (4 + kDequantWarps + kEpilogueWarps) * 32;
 constexpr int kTmemCols = 512;  // two 128x256 fp32 accumulators
 constexpr uint32_t kBytesA = BM * BK * 2;
 constexpr uint32_t kBytesB16 = BN * BK * 2;
@@ -91,15 +94,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         *abort_flag = 0;
         for (int s = 0; s < kStagesAB; ++s) {
             mbar_init(full_ab(s), 1);
-            mbar_init(empty_ab(s), kBInt8 ? 5 : 1);  // MMA commit (+ 4 dequantiser warps)
+            mbar_init(empty_ab(s), kBInt8 ? 1 + kDequantWarps : 1);  // MMA commit (+ dequantiser warps)
         }
         for (int s = 0; s < kStagesB16; ++s) {
-            mbar_init(full_b16(s), 4);
+            mbar_init(full_b16(s), kDequantWarps);
             mbar_init(empty_b16(s), 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(acc_full(s), 1);
-            mbar_init(acc_empty(s), 4);
+            mbar_init(acc_empty(s), kEpilogueWarps);
         }
         mbar_fence_init();
         tma_prefetch_desc(&tm_a);
@@ -186,10 +189,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
         }
         __syncwarp();
-    } else if (warp >= 4 && warp < 8) {
+    } else if (warp >= 4 && warp < 4 + kDequantWarps) {
         // ------------------------------------------------------------ dequantisers (int8 mode)
         if (kBInt8) {
-            const int tid = threadIdx.x - 128;
+            const int tid = threadIdx.x - 128;  // 0 .. kDequantWarps*32 - 1
             const uint32_t bias1152 = 0x64806480u;  // half2(1152, 1152) = 1024 + 128
             uint32_t it = 0;
             bool ok = true;
@@ -206,8 +209,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     const uint8_t* src = sm + kOffB8 + s * kBytesB8;
                     uint8_t* dst = sm + kOffB16 + c * kBytesB16;
 #pragma unroll
-                    for (int i = 0; i < (BN * BK / 16) / 128; ++i) {
-                        const int q = i * 128 + tid;
+                    for (int i = 0; i < (BN * BK / 16) / (kDequantWarps * 32); ++i) {
+                        const int q = i * (kDequantWarps * 32) + tid;
                         const int r = q >> 2;
                         const int j = q & 3;
                         const uint4 raw8 = *reinterpret_cast<const uint4*>(src + r * BK + j * 16);
@@ -240,9 +243,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
             }
         }
-    } else if (warp >= 8) {
+    } else if (warp >= 4 + kDequantWarps) {
         // ------------------------------------------------------------ epilogue
-        const int etid = threadIdx.x - 256;          // 0..127 = accumulator row inside the tile
+        const int etid = threadIdx.x - (4 + kDequantWarps) * 32;  // 0..255
+        const int erow = ((warp & 3) * 32) + lane;                 // accumulator row inside the tile
+        const int ehalf = (warp - (4 + kDequantWarps)) >> 2;       // which 128 columns of the tile
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32);
         uint32_t t = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
@@ -251,7 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const uint32_t ab = t & 1u;
             const uint32_t aph = (t >> 1) & 1u;
             float2* sb = scale_bias + ab * BN;
-            for (int cidx = etid; cidx < BN; cidx += 128) {
+            for (int cidx = etid; cidx < BN; cidx += kEpilogueWarps * 32) {
                 const int n = n0 + cidx;
                 float2 v = make_float2(1.0f, 0.0f);
                 if (n < p.n) {
@@ -260,43 +265,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
                 sb[cidx] = v;
             }
-            named_bar_sync(1, 128);
+            named_bar_sync(1, kEpilogueWarps * 32);
             if (!mbar_wait(acc_full(ab), aph, abort_flag)) break;
             tc_fence_after();
-            const int m = m0 + etid;
+            const int m = m0 + erow;
             const bool row_ok = m < m_rows;
             const uint32_t taddr = tmem_base + (lane_base << 16) + ab * BN;
             __half* out_row = p.out + (size_t)m * p.ldo;
             const __half* res_row = p.residual + (size_t)m * p.ldr;
 #pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ++ch) {
-                const int nc = n0 + ch * 32;
+            for (int ch = ehalf * (BN / 32); ch < (ehalf + 1) * (BN / 32); ++ch) {
+                const int nc = n0 + ch * 16;
                 if (nc >= p.n) break;
-                uint32_t r[32];
+                uint32_t r[16];
                 __syncwarp();
-                tmem_ld_32x32(taddr + ch * 32, r);
+                tmem_ld_32x16(taddr + ch * 16, r);
                 tmem_ld_wait();
-                float v[32];
+                float v[16];
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const float4 f = *reinterpret_cast<const float4*>(&sb[ch * 32 + j]);
+                for (int j = 0; j < 16; j += 2) {
+                    const float4 f = *reinterpret_cast<const float4*>(&sb[ch * 16 + j]);
                     v[j] = fmaf(__uint_as_float(r[j]), f.x, f.y);
                     v[j + 1] = fmaf(__uint_as_float(r[j + 1]), f.z, f.w);
                 }
                 if (p.mode == kEpiBiasGeluErf) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                    for (int j = 0; j < 16; ++j) v[j] = gelu_erf_fast(v[j]);
                 } else if (p.mode == kEpiBiasGeluTanh) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+                    for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
                 }
-                const bool full_chunk = (nc + 32 <= p.n);
+                const bool full_chunk = (nc + 16 <= p.n);
                 if (!row_ok) {
                     // rows past the end of the activation matrix: nothing to store
                 } else if (full_chunk) {
                     if (p.mode == kEpiBiasResidual) {
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
+                        for (int q = 0; q < 2; ++q) {
                             const uint4 rr = *reinterpret_cast<const uint4*>(res_row + nc + q * 8);
                             const __half2* h = reinterpret_cast<const __half2*>(&rr);
 #pragma unroll
@@ -308,7 +313,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         }
                     }
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
+                    for (int q = 0; q < 2; ++q) {
                         uint4 o;
                         __half2 h0 = __floats2half2_rn(v[q * 8 + 0], v[q * 8 + 1]);
                         __half2 h1 = __floats2half2_rn(v[q * 8 + 2], v[q * 8 + 3]);
@@ -322,7 +327,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
+                    for (int j = 0; j < 16; ++j) {
                         if (nc + j < p.n) {
                             float x = v[j];
                             if (p.mode == kEpiBiasResidual) x += __half2float(res_row[nc + j]);
@@ -345,41 +350,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         tmem_dealloc(tmem_base, kTmemCols);
     }
     if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn(std::string* err) {
-    static EncodeTiledFn fn = nullptr;
-    if (fn != nullptr) return fn;
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
-    if (e != cudaSuccess || sym == nullptr || qres != cudaDriverEntryPointSuccess) {
-        *err = std::string("cuTensorMapEncodeTiled is not available: ") + cudaGetErrorString(e);
-        return nullptr;
-    }
-    fn = reinterpret_cast<EncodeTiledFn>(sym);
-    return fn;
-}
-
-std::string encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, const void* ptr, uint64_t inner, uint64_t outer,
-                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
-    std::string err;
-    EncodeTiledFn fn = get_encode_fn(&err);
-    if (fn == nullptr) return err;
-    if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return "tensor map base address is not 16-byte aligned";
-    if ((row_stride_bytes & 15u) != 0) return "tensor map row stride is not a multiple of 16 bytes";
-    cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {row_stride_bytes};
-    cuuint32_t box[2] = {box_inner, box_outer};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(tm, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r);
-    return "";
 }
 
 }  // namespace

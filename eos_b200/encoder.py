@@ -107,7 +107,13 @@ class BertEmbedder:
     def __init__(self, rt: Runtime, token_embeddings, position_embeddings, token_type_embeddings,
                  embedding_ln_weight, embedding_ln_bias, layer_weights: Sequence[Weight], num_attention_heads: int,
                  epsilon: float = 1e-12, pooling: str = "masked_mean", hidden_act: str = "gelu",
-                 head_weights=None, weight_mode: int = WEIGHTS_Q8_SMEM_DEQUANT, attention_window: int = 0):
+                 head_weights=None, weight_mode: int = WEIGHTS_F16_RESIDENT, attention_window: int = 0):
+        # weight_mode: WEIGHTS_F16_RESIDENT expands the 8-bit codes to f16 once at bind (the code values are
+        # exact in f16, the per-channel scale stays in the fp32 epilogue); WEIGHTS_Q8_SMEM_DEQUANT keeps the
+        # codes 8-bit in HBM and expands them in shared memory inside the projection kernel.  Both feed the
+        # same values to the same tensor-core instruction, so their results are bit-identical; the resident
+        # form is faster when the batch makes the projections compute-bound, the 8-bit form halves weight
+        # bytes when they are not.
         if pooling not in ("masked_mean", "cls"):
             raise ValueError(f"bert_embedder unsupported pooling {pooling!r}; supported values are masked_mean and cls")
         if hidden_act not in ("gelu", "gelu_tanh"):

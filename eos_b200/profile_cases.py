@@ -14,20 +14,20 @@ import sys
 import numpy as np
 
 
-def case_gemm(residual: bool = False) -> None:
+def case_gemm(residual: bool = False, weight_mode: int = 0, rows: int = 32768) -> None:
     import eos_b200
     from eos_b200 import synth
     rt = eos_b200.Runtime(0)
     rng = np.random.default_rng(0)
-    rows, k, n = (32768, 3072, 768) if residual else (32768, 768, 3072)
+    k, n = (3072, 768) if residual else (768, 3072)
     x = rng.standard_normal((rows, k), dtype=np.float32)
     w = synth.quantize_per_channel(rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
     bias = (rng.standard_normal(n) * 0.02).astype(np.float32)
     res = rng.standard_normal((rows, n), dtype=np.float32) if residual else None
     for _ in range(3):
         st = eos_b200.Stats()
-        eos_b200.linear(rt, x, w, bias, epilogue=2 if residual else 1, residual=res, stats=st)
-        print(f"gemm {rows}x{k}->{n}: {st.device_ms:.3f} ms, {2.0 * rows * k * n / st.device_ms / 1e9:.1f} TFLOP/s")
+        eos_b200.linear(rt, x, w, bias, epilogue=2 if residual else 1, residual=res, weight_mode=weight_mode, stats=st)
+        print(f"gemm {rows}x{k}->{n} weight_mode={weight_mode}: {st.device_ms:.3f} ms, {2.0 * rows * k * n / st.device_ms / 1e9:.1f} TFLOP/s")
     rt.close()
 
 
@@ -79,4 +79,8 @@ def case_attention() -> None:
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": case_gemm, "gemm_res": lambda: case_gemm(True), "scan": case_scan, "attention": case_attention}[name]()
+    {"gemm": case_gemm, "gemm_res": lambda: case_gemm(True), "scan": case_scan, "attention": case_attention,
+     "gemm_f16w": lambda: case_gemm(False, 1), "gemm_res_f16w": lambda: case_gemm(True, 1),
+     "gemm_big": lambda: case_gemm(False, 0, 131072), "gemm_res_big": lambda: case_gemm(True, 0, 131072),
+     "gemm_big_f16w": lambda: case_gemm(False, 1, 131072), "gemm_res_big_f16w": lambda: case_gemm(True, 1, 131072),
+     }[name]()

@@ -152,7 +152,7 @@ def test_device_resident_run_matches_host_run(rt):
     stream = ts.cuda_stream  # non-null: the library launches on this stream
     launches = enc.run_device(d_ids.data_ptr(), d_mask.data_ptr(), None, 16, 128, d_out.data_ptr(), stream)
     enc.sync(stream)
-    assert launches == 3 + 1 + 7 * 2 + 1
+    assert launches == 4 + 1 + 7 * 2 + 1
     assert np.array_equal(d_out.cpu().numpy(), ref)
     enc.close()
 
@@ -191,5 +191,6 @@ def test_local_window_attention_extension(rt):
                                   workers=8)
             _check(outs[window], ref)
             enc.close()
-        assert np.abs(outs[0] - outs[1000]).max() <= 1e-6   # a window wider than the sequence is full attention
+        # a window wider than the sequence is full attention (different kernels: tensor-memory vs mma.sync)
+        assert np.abs(outs[0] - outs[1000]).max() <= 1e-4
         assert np.abs(outs[0][:3] - outs[16][:3]).max() > 5e-3  # and a narrow one is a different function
