@@ -277,7 +277,11 @@ def run_ours(args, rank: int, world: int, local: int):
         "per_step_ms": {"gemm": gemm_ms_step, "attention": times.attention_ms / max(1, times.steps),
                         "layernorm": times.layernorm_ms / max(1, times.steps),
                         "embed": times.embed_ms / max(1, times.steps), "pool": times.pool_ms / max(1, times.steps),
-                        "layout": times.layout_ms / max(1, times.steps)},
+                        "layout": times.layout_ms / max(1, times.steps),
+                        "gemm_qkv": times.gemm_kind_ms[0] / max(1, times.steps),
+                        "gemm_attn_out": times.gemm_kind_ms[1] / max(1, times.steps),
+                        "gemm_ffn_up": times.gemm_kind_ms[2] / max(1, times.steps),
+                        "gemm_ffn_down": times.gemm_kind_ms[3] / max(1, times.steps)},
         "whole_step_tflops": flops_total / (ms_step / 1e3) / 1e12,
         "algorithmic_flops_per_step": flops_total, "gemm_flops_per_step": flops_gemm,
     }

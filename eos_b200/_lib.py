@@ -32,7 +32,7 @@ class EncoderTimes(C.Structure):
     _fields_ = [("steps", C.c_int32), ("gemm_launches", C.c_int32), ("attention_launches", C.c_int32),
                 ("layernorm_launches", C.c_int32), ("other_launches", C.c_int32), ("gemm_ms", C.c_float),
                 ("attention_ms", C.c_float), ("layernorm_ms", C.c_float), ("embed_ms", C.c_float),
-                ("pool_ms", C.c_float), ("layout_ms", C.c_float)]
+                ("pool_ms", C.c_float), ("layout_ms", C.c_float), ("gemm_kind_ms", C.c_float * 4)]
 
 
 class DeviceInfo(C.Structure):

@@ -302,7 +302,10 @@ struct LayerW {
 };
 
 // CUDA-event pairs around individual launches, tagged with a kernel class.
-enum KernelClass : int { kClsLayout = 0, kClsEmbed, kClsGemm, kClsAttention, kClsLayerNorm, kClsPool, kClsScan };
+enum KernelClass : int {
+    kClsLayout = 0, kClsEmbed, kClsGemm, kClsAttention, kClsLayerNorm, kClsPool, kClsScan,
+    kClsGemmKind0 = 16  // + 0..3: QKV, attention output, FFN up, FFN down
+};
 
 struct Profiler {
     std::vector<cudaEvent_t> ev;  // 2 per slot
@@ -492,19 +495,19 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
     launches += 1;
     for (int l = 0; l < e->layers; ++l) {
         LayerW& w = e->lw[l];
-        pf.launch(kClsGemm, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 0], s); });
+        pf.launch(kClsGemmKind0 + 0, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 0], s); });
         pf.launch(kClsAttention, s, [&] {
             if (e->attn_tc && tokens <= 512)
                 attn_tc_launch(e->attn_plan, e->lay, batch, D, e->heads, e->ctx, rt->d_status, rt->sm_count, s);
             else
                 launch_attention(e->qkv, e->lay, batch, tokens, D, e->heads, e->window, e->ctx, s);
         });
-        pf.launch(kClsGemm, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 1], s); });
+        pf.launch(kClsGemmKind0 + 1, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 1], s); });
         pf.launch(kClsLayerNorm, s, [&] {
             launch_layernorm(e->pre, w.g1, w.b1, e->eps, D, e->m_alloc, e->lay.total_rows, e->h1, rt->sm_count, s);
         });
-        pf.launch(kClsGemm, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 2], s); });
-        pf.launch(kClsGemm, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 3], s); });
+        pf.launch(kClsGemmKind0 + 2, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 2], s); });
+        pf.launch(kClsGemmKind0 + 3, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 3], s); });
         pf.launch(kClsLayerNorm, s, [&] {
             launch_layernorm(e->pre, w.g2, w.b2, e->eps, D, e->m_alloc, e->lay.total_rows, e->h0, rt->sm_count, s);
         });
@@ -679,7 +682,14 @@ int eos_b200_encoder_profile_end(EosB200Encoder* enc, void* stream, EosB200Encod
     for (int i = 0; i < enc->prof.used; ++i) {
         float ms = 0.f;
         cudaEventElapsedTime(&ms, enc->prof.ev[(size_t)i * 2], enc->prof.ev[(size_t)i * 2 + 1]);
-        switch (enc->prof.cls[i]) {
+        const int cls = enc->prof.cls[i];
+        if (cls >= kClsGemmKind0 && cls < kClsGemmKind0 + 4) {
+            out->gemm_ms += ms;
+            out->gemm_launches++;
+            out->gemm_kind_ms[cls - kClsGemmKind0] += ms;
+            continue;
+        }
+        switch (cls) {
             case kClsGemm: out->gemm_ms += ms; out->gemm_launches++; break;
             case kClsAttention: out->attention_ms += ms; out->attention_launches++; break;
             case kClsLayerNorm: out->layernorm_ms += ms; out->layernorm_launches++; break;
@@ -1070,6 +1080,7 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
             a.cand_count = c->cand_count + (size_t)t0 * 8 * c->grid;
             a.grid = c->grid;
             a.all_scores = nullptr;
+            a.status = nullptr;
             a.all_stride = 0;
             c->prof.launch(kClsScan, s, [&] { launch_tq_scan(a, s); });
             launches++;
@@ -1436,6 +1447,7 @@ int eos_b200_score_topk_noalloc(EosB200Corpus* c, const float* d_queries, int q_
         a.cand_count = cand_count + (size_t)t0 * 8 * c->grid;
         a.grid = c->grid;
         a.all_scores = nullptr;
+            a.status = nullptr;
         a.all_stride = 0;
         launch_tq_scan(a, s);
     }

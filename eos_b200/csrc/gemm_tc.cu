@@ -6,21 +6,24 @@
 // runBGEFullEncoderHidden :7941-8190) and the host loop denseHFRange
 // (runtime/backend/bert_encoder_layer_ops.go:452-462): y = x W^T + b with W in HF [out,in] layout.
 //
-// Design (one persistent CTA per SM, 640 threads, warp-specialised):
-//   warp 0      TMA producer: A tile 128x64 f16 (128B swizzle) and the W tile 256x64 (8-bit codes,
-//               no swizzle) per k-block into a 4-stage ring, completion on mbarriers.
-//   warps 4-11  dequantisers: expand the 8-bit codes to f16 in shared memory, written directly in
-//               the 128B-swizzled K-major layout the MMA reads (int8 -> f16 is exact; the
+// Design (one persistent CTA per SM, warp-specialised):
+//   warp 0      TMA producer: A tile 128x64 f16 (128B swizzle) and the W tile 256x64 (8-bit codes, no
+//               swizzle, or f16 with 128B swizzle) per k-block into a 4-stage ring, completion on mbarriers.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16, f16 x f16 -> f32) with
+//               the accumulator in tensor memory; tcgen05.commit releases ring stages.
+//   warp 2      allocates / frees tensor memory.
+//   warps 4-7   (8-bit weights only) dequantisers: expand the codes to f16 in shared memory, written
+//               directly in the 128B-swizzled K-major layout the MMA reads (int8 -> f16 is exact; the
 //               per-channel scale is applied in fp32 in the epilogue, which is the same product:
 //               sum_k a_k (s_n q_kn) = s_n sum_k a_k q_kn).
-//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16, f16 x f16 -> f32)
-//               with the accumulator in tensor memory; tcgen05.commit releases ring stages.
-//   warps 12-19 epilogue: tcgen05.ld the 128x256 fp32 accumulator (thread = row), scale, bias,
-//               GELU or residual add, f16 stores.  Two accumulators (2 x 256 TMEM columns) let the
-//               epilogue of tile i overlap the main loop of tile i+1.
-//   warp 2      allocates / frees tensor memory.
-// Every mbarrier wait is bounded (common.cuh: mbar_wait); on a timeout the kernel raises a
-// CTA-wide abort flag, all roles leave their loops, TMEM is freed and the status word is set.
+//   last 8      epilogue warps, two per TMEM lane quarter, each owning 128 of the tile's 256 columns:
+//               tcgen05.ld (thread = row, software-pipelined 16 columns at a time), scale, bias, GELU or
+//               residual add, f16.  Output (and the residual) move between registers and global memory
+//               through a per-warp swizzled staging slab of 32 rows x 32 columns, so that every global
+//               access instruction covers 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
+// Two accumulators (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
+// Every mbarrier wait is bounded (common.cuh: mbar_wait); on a timeout the kernel raises a CTA-wide
+// abort flag, all roles leave their loops, TMEM is freed and the status word is set.
 #include "gemm_tc.cuh"
 
 #include "common.cuh"
@@ -34,31 +37,37 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int kStagesAB = 4;    // ring depth of the TMA-fed stages
-constexpr int kStagesB16 = 2;   // ring depth of the dequantised W tiles (int8 mode)
-constexpr int kDequantWarps = 8;
-constexpr int kEpilogueWarps = 8;  // two per TMEM lane quarter, each owning half of the tile's columns
-constexpr int kThreads = (4 + kDequantWarps + kEpilogueWarps) * 32;
+constexpr int kStagesB16 = 2;   // ring depth of the dequantised W tiles (8-bit mode)
+constexpr int kEpilogueWarps = 8;
 constexpr int kTmemCols = 512;  // two 128x256 fp32 accumulators
 constexpr uint32_t kBytesA = BM * BK * 2;
 constexpr uint32_t kBytesB16 = BN * BK * 2;
 constexpr uint32_t kBytesB8 = BN * BK;
-
-// shared memory map (offsets from a 1024-byte aligned base)
-constexpr uint32_t kOffA = 0;
-constexpr uint32_t kOffB16 = kOffA + kStagesAB * kBytesA;              // 64 KB
-constexpr uint32_t kOffB8 = kOffB16 + kStagesB16 * kBytesB16;          // int8 mode: after 2 f16 stages
-constexpr uint32_t kOffTailInt8 = kOffB8 + kStagesAB * kBytesB8;       // 192 KB
-constexpr uint32_t kOffTailF16 = kOffB16 + kStagesAB * kBytesB16;      // f16 mode: 4 f16 stages, 192 KB
-static_assert(kOffTailInt8 == kOffTailF16, "both modes use the same main footprint");
-constexpr uint32_t kOffScaleBias = kOffTailInt8;                       // 2 x 256 float2
-constexpr uint32_t kOffBars = kOffScaleBias + 2 * BN * 8;
-constexpr uint32_t kNumBars = 2 * kStagesAB + 2 * kStagesB16 + 4;
-constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
-constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;                  // + alignment slack
+constexpr int kSlabCols = 32;                  // columns of the staging slab of one epilogue warp
+constexpr uint32_t kSlabBytes = 32 * kSlabCols * 2;
 
 template <bool kBInt8>
-__global__ void __launch_bounds__(kThreads, 1)
+struct Cfg {
+    static constexpr int kDequantWarps = kBInt8 ? 8 : 0;
+    static constexpr int kFirstEpilogueWarp = 4 + kDequantWarps;
+    static constexpr int kThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
+    static constexpr int kBStages = kBInt8 ? kStagesB16 : kStagesAB;  // f16 W tiles ride the TMA ring
+    // shared memory map (offsets from a 1024-byte aligned base)
+    static constexpr uint32_t kOffA = 0;
+    static constexpr uint32_t kOffB16 = kOffA + kStagesAB * kBytesA;
+    static constexpr uint32_t kOffB8 = kOffB16 + kBStages * kBytesB16;
+    static constexpr uint32_t kOffSlab = kOffB8 + (kBInt8 ? kStagesAB * kBytesB8 : 0);
+    static constexpr uint32_t kOffScaleBias = kOffSlab + kEpilogueWarps * kSlabBytes;  // 2 x 256 float2
+    static constexpr uint32_t kOffBars = kOffScaleBias + 2 * BN * 8;
+    static constexpr uint32_t kNumBars = 2 * kStagesAB + 2 * kStagesB16 + 4;
+    static constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
+    static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
+};
+
+template <bool kBInt8>
+__global__ void __launch_bounds__(Cfg<kBInt8>::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, GemmParams p) {
+    using C = Cfg<kBInt8>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -67,7 +76,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    const uint32_t bar0 = base + kOffBars;
+    const uint32_t bar0 = base + C::kOffBars;
     auto full_ab = [&](int s) { return bar0 + 8u * s; };
     auto empty_ab = [&](int s) { return bar0 + 8u * (kStagesAB + s); };
     auto full_b16 = [&](int s) { return bar0 + 8u * (2 * kStagesAB + s); };
@@ -75,9 +84,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     auto acc_full = [&](int s) { return bar0 + 8u * (2 * kStagesAB + 2 * kStagesB16 + s); };
     auto acc_empty = [&](int s) { return bar0 + 8u * (2 * kStagesAB + 2 * kStagesB16 + 2 + s); };
 
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + kOffMisc);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
-    float2* scale_bias = reinterpret_cast<float2*>(sm + kOffScaleBias);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + C::kOffMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + C::kOffMisc + 4);
+    float2* scale_bias = reinterpret_cast<float2*>(sm + C::kOffScaleBias);
 
     int m_rows = p.m_alloc;
     if (p.m_ptr != nullptr) {
@@ -94,10 +103,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         *abort_flag = 0;
         for (int s = 0; s < kStagesAB; ++s) {
             mbar_init(full_ab(s), 1);
-            mbar_init(empty_ab(s), kBInt8 ? 1 + kDequantWarps : 1);  // MMA commit (+ dequantiser warps)
+            mbar_init(empty_ab(s), 1 + C::kDequantWarps);  // MMA commit (+ dequantiser warps)
         }
         for (int s = 0; s < kStagesB16; ++s) {
-            mbar_init(full_b16(s), kDequantWarps);
+            mbar_init(full_b16(s), kBInt8 ? C::kDequantWarps : 1);
             mbar_init(empty_b16(s), 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -133,11 +142,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         break;
                     }
                     mbar_arrive_expect_tx(full_ab(s), kBytesA + (kBInt8 ? kBytesB8 : kBytesB16));
-                    tma_load_2d(base + kOffA + s * kBytesA, &tm_a, kb * BK, m0, full_ab(s));
+                    tma_load_2d(base + C::kOffA + s * kBytesA, &tm_a, kb * BK, m0, full_ab(s));
                     if (kBInt8)
-                        tma_load_2d(base + kOffB8 + s * kBytesB8, &tm_b, kb * BK, n0, full_ab(s));
+                        tma_load_2d(base + C::kOffB8 + s * kBytesB8, &tm_b, kb * BK, n0, full_ab(s));
                     else
-                        tma_load_2d(base + kOffB16 + s * kBytesB16, &tm_b, kb * BK, n0, full_ab(s));
+                        tma_load_2d(base + C::kOffB16 + s * kBytesB16, &tm_b, kb * BK, n0, full_ab(s));
                 }
             }
         }
@@ -171,12 +180,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             ok = false;
                             break;
                         }
-                        b_addr = base + kOffB16 + c * kBytesB16;
+                        b_addr = base + C::kOffB16 + c * kBytesB16;
                     } else {
-                        b_addr = base + kOffB16 + s * kBytesB16;
+                        b_addr = base + C::kOffB16 + s * kBytesB16;
                     }
                     tc_fence_after();
-                    const uint32_t a_addr = base + kOffA + s * kBytesA;
+                    const uint32_t a_addr = base + C::kOffA + s * kBytesA;
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
                         umma_f16(d_tmem, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
@@ -189,66 +198,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
         }
         __syncwarp();
-    } else if (warp >= 4 && warp < 4 + kDequantWarps) {
-        // ------------------------------------------------------------ dequantisers (int8 mode)
-        if (kBInt8) {
-            const int tid = threadIdx.x - 128;  // 0 .. kDequantWarps*32 - 1
-            const uint32_t bias1152 = 0x64806480u;  // half2(1152, 1152) = 1024 + 128
-            uint32_t it = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % kStagesAB;
-                    const uint32_t ph = (it / kStagesAB) & 1u;
-                    const int c = it % kStagesB16;
-                    const uint32_t cph = (it / kStagesB16) & 1u;
-                    if (!mbar_wait(full_ab(s), ph, abort_flag) || !mbar_wait(empty_b16(c), cph ^ 1u, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint8_t* src = sm + kOffB8 + s * kBytesB8;
-                    uint8_t* dst = sm + kOffB16 + c * kBytesB16;
+    } else if (kBInt8 && warp >= 4 && warp < C::kFirstEpilogueWarp) {
+        // ------------------------------------------------------------ dequantisers (8-bit weights)
+        constexpr int kDqThreads = (C::kDequantWarps > 0 ? C::kDequantWarps : 1) * 32;
+        const int tid = threadIdx.x - 128;
+        const uint32_t bias1152 = 0x64806480u;  // half2(1152, 1152) = 1024 + 128
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % kStagesAB;
+                const uint32_t ph = (it / kStagesAB) & 1u;
+                const int c = it % kStagesB16;
+                const uint32_t cph = (it / kStagesB16) & 1u;
+                if (!mbar_wait(full_ab(s), ph, abort_flag) || !mbar_wait(empty_b16(c), cph ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                const uint8_t* src = sm + C::kOffB8 + s * kBytesB8;
+                uint8_t* dst = sm + C::kOffB16 + c * kBytesB16;
 #pragma unroll
-                    for (int i = 0; i < (BN * BK / 16) / (kDequantWarps * 32); ++i) {
-                        const int q = i * (kDequantWarps * 32) + tid;
-                        const int r = q >> 2;
-                        const int j = q & 3;
-                        const uint4 raw8 = *reinterpret_cast<const uint4*>(src + r * BK + j * 16);
-                        const uint32_t w[4] = {raw8.x, raw8.y, raw8.z, raw8.w};
-                        uint32_t h[8];
+                for (int i = 0; i < (BN * BK / 16) / kDqThreads; ++i) {
+                    const int q = i * kDqThreads + tid;
+                    const int r = q >> 2;
+                    const int j = q & 3;
+                    const uint4 raw8 = *reinterpret_cast<const uint4*>(src + r * BK + j * 16);
+                    const uint32_t w[4] = {raw8.x, raw8.y, raw8.z, raw8.w};
+                    uint32_t h[8];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            // bytes u = code + 128; 0x6400 | u is the f16 value 1024 + u, so
-                            // (1024 + u) - 1152 = code, exactly.
-                            uint32_t lo = __byte_perm(w[e], 0x64646464u, 0x5140);
-                            uint32_t hi = __byte_perm(w[e], 0x64646464u, 0x7362);
-                            __half2 l2 = __hsub2(*reinterpret_cast<__half2*>(&lo),
-                                                 *reinterpret_cast<const __half2*>(&bias1152));
-                            __half2 h2 = __hsub2(*reinterpret_cast<__half2*>(&hi),
-                                                 *reinterpret_cast<const __half2*>(&bias1152));
-                            h[2 * e] = *reinterpret_cast<uint32_t*>(&l2);
-                            h[2 * e + 1] = *reinterpret_cast<uint32_t*>(&h2);
-                        }
-                        uint8_t* row = dst + (r >> 3) * 1024 + (r & 7) * 128;
-                        const int x = r & 7;
-                        *reinterpret_cast<uint4*>(row + (((2 * j) ^ x) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-                        *reinterpret_cast<uint4*>(row + (((2 * j + 1) ^ x) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+                    for (int e = 0; e < 4; ++e) {
+                        // bytes u = code + 128; 0x6400 | u is the f16 value 1024 + u, so
+                        // (1024 + u) - 1152 = code, exactly.
+                        uint32_t lo = __byte_perm(w[e], 0x64646464u, 0x5140);
+                        uint32_t hi = __byte_perm(w[e], 0x64646464u, 0x7362);
+                        __half2 l2 = __hsub2(*reinterpret_cast<__half2*>(&lo), *reinterpret_cast<const __half2*>(&bias1152));
+                        __half2 h2 = __hsub2(*reinterpret_cast<__half2*>(&hi), *reinterpret_cast<const __half2*>(&bias1152));
+                        h[2 * e] = *reinterpret_cast<uint32_t*>(&l2);
+                        h[2 * e + 1] = *reinterpret_cast<uint32_t*>(&h2);
                     }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(full_b16(c));
-                        mbar_arrive(empty_ab(s));
-                    }
+                    uint8_t* row = dst + (r >> 3) * 1024 + (r & 7) * 128;
+                    const int x = r & 7;
+                    *reinterpret_cast<uint4*>(row + (((2 * j) ^ x) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(row + (((2 * j + 1) ^ x) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(full_b16(c));
+                    mbar_arrive(empty_ab(s));
                 }
             }
         }
-    } else if (warp >= 4 + kDequantWarps) {
+    } else if (warp >= C::kFirstEpilogueWarp) {
         // ------------------------------------------------------------ epilogue
-        const int etid = threadIdx.x - (4 + kDequantWarps) * 32;  // 0..255
-        const int erow = ((warp & 3) * 32) + lane;                 // accumulator row inside the tile
-        const int ehalf = (warp - (4 + kDequantWarps)) >> 2;       // which 128 columns of the tile
-        const uint32_t lane_base = (uint32_t)((warp & 3) * 32);
+        const int ew = warp - C::kFirstEpilogueWarp;               // 0..7
+        const int etid = threadIdx.x - C::kFirstEpilogueWarp * 32;  // 0..255
+        const int wrow0 = (warp & 3) * 32;                          // this warp's rows inside the tile
+        const int ehalf = ew >> 2;                                  // which 128 columns of the tile
+        const uint32_t lane_base = (uint32_t)wrow0;
+        uint8_t* slab = sm + C::kOffSlab + ew * kSlabBytes;         // [32 rows][8 x 16 B], chunk index ^ (row & 7)
         uint32_t t = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
             const int m0 = (tile / n_tiles) * BM;
@@ -265,75 +273,141 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
                 sb[cidx] = v;
             }
-            named_bar_sync(1, kEpilogueWarps * 32);
-            if (!mbar_wait(acc_full(ab), aph, abort_flag)) break;
-            tc_fence_after();
-            const int m = m0 + erow;
+            const int m = m0 + wrow0 + lane;  // this thread's accumulator row
             const bool row_ok = m < m_rows;
+            const int rows_here = m_rows - (m0 + wrow0);  // rows of this warp's block that exist (may exceed 32)
             const uint32_t taddr = tmem_base + (lane_base << 16) + ab * BN;
             __half* out_row = p.out + (size_t)m * p.ldo;
             const __half* res_row = p.residual + (size_t)m * p.ldr;
+            // coalesced access pattern of the slab copies: instruction i covers rows 8i .. 8i+7, 64 bytes each
+            // slab layout: row pitch 64 B, 16-byte chunk c of row r at position c ^ ((r >> 1) & 3)
+            const int crow = lane >> 2, cchunk = lane & 3;
+            const bool residual = p.mode == kEpiBiasResidual;
+            constexpr int kSlabs = 128 / kSlabCols;
+
+            // residual of the next slab is requested one slab ahead (the first one before the accumulator
+            // is even complete)
+            uint4 res_in[4];
+            auto residual_fetch = [&](int slab_idx) {
+                const int col = n0 + ehalf * 128 + slab_idx * kSlabCols;
+                if (slab_idx >= kSlabs || col + kSlabCols > p.n) return;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int rr = 8 * i + crow;
+                    res_in[i] = make_uint4(0, 0, 0, 0);
+                    if (rr < rows_here)
+                        res_in[i] = *reinterpret_cast<const uint4*>(p.residual + (size_t)(m0 + wrow0 + rr) * p.ldr + col +
+                                                                     cchunk * 8);
+                }
+            };
+            if (residual) residual_fetch(0);
+            named_bar_sync(1, kEpilogueWarps * 32);
+            if (!mbar_wait(acc_full(ab), aph, abort_flag)) break;
+            tc_fence_after();
+
+            uint32_t r_next[16];
+            __syncwarp();
+            tmem_ld_32x16(taddr + ehalf * 128, r_next);
 #pragma unroll 1
-            for (int ch = ehalf * (BN / 32); ch < (ehalf + 1) * (BN / 32); ++ch) {
-                const int nc = n0 + ch * 16;
-                if (nc >= p.n) break;
-                uint32_t r[16];
-                __syncwarp();
-                tmem_ld_32x16(taddr + ch * 16, r);
-                tmem_ld_wait();
-                float v[16];
-#pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                    const float4 f = *reinterpret_cast<const float4*>(&sb[ch * 16 + j]);
-                    v[j] = fmaf(__uint_as_float(r[j]), f.x, f.y);
-                    v[j + 1] = fmaf(__uint_as_float(r[j + 1]), f.z, f.w);
+            for (int sl = 0; sl < kSlabs; ++sl) {
+                const int col0 = ehalf * 128 + sl * kSlabCols;  // first column of the slab inside the tile
+                const int ncol0 = n0 + col0;
+                if (ncol0 >= p.n) {
+                    tmem_ld_wait();
+                    break;
                 }
-                if (p.mode == kEpiBiasGeluErf) {
+                const bool fast = (ncol0 + kSlabCols <= p.n);
+                uint4 res_own[4];
+                if (fast && residual) {
+                    // residual slab: coalesced registers -> staging -> this thread's own row
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = gelu_erf_fast(v[j]);
-                } else if (p.mode == kEpiBiasGeluTanh) {
+                    for (int i = 0; i < 4; ++i) {
+                        const int rr = 8 * i + crow;
+                        *reinterpret_cast<uint4*>(slab + rr * 64 + ((cchunk ^ ((rr >> 1) & 3)) << 4)) = res_in[i];
+                    }
+                    __syncwarp();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
+                    for (int c4 = 0; c4 < 4; ++c4)
+                        res_own[c4] = *reinterpret_cast<const uint4*>(slab + lane * 64 + ((c4 ^ ((lane >> 1) & 3)) << 4));
+                    __syncwarp();
+                    residual_fetch(sl + 1);
                 }
-                const bool full_chunk = (nc + 16 <= p.n);
-                if (!row_ok) {
-                    // rows past the end of the activation matrix: nothing to store
-                } else if (full_chunk) {
-                    if (p.mode == kEpiBiasResidual) {
+#pragma unroll
+                for (int ch = 0; ch < kSlabCols / 16; ++ch) {
+                    uint32_t r[16];
+                    tmem_ld_wait16(r_next);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = r_next[j];
+                    {
+                        const int next_col = col0 + (ch + 1) * 16;  // next chunk, possibly of the next slab
+                        if (next_col < (ehalf + 1) * 128) {
+                            __syncwarp();
+                            tmem_ld_32x16(taddr + next_col, r_next);
+                        }
+                    }
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        const float4 f = *reinterpret_cast<const float4*>(&sb[col0 + ch * 16 + j]);
+                        v[j] = fmaf(__uint_as_float(r[j]), f.x, f.y);
+                        v[j + 1] = fmaf(__uint_as_float(r[j + 1]), f.z, f.w);
+                    }
+                    if (p.mode == kEpiBiasGeluErf) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = gelu_erf_fast(v[j]);
+                    } else if (p.mode == kEpiBiasGeluTanh) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
+                    }
+                    if (fast) {
+                        if (residual) {
+#pragma unroll
+                            for (int q = 0; q < 2; ++q) {
+                                const __half2* h = reinterpret_cast<const __half2*>(&res_own[ch * 2 + q]);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float2 f = __half22float2(h[e]);
+                                    v[q * 8 + 2 * e] += f.x;
+                                    v[q * 8 + 2 * e + 1] += f.y;
+                                }
+                            }
+                        }
 #pragma unroll
                         for (int q = 0; q < 2; ++q) {
-                            const uint4 rr = *reinterpret_cast<const uint4*>(res_row + nc + q * 8);
-                            const __half2* h = reinterpret_cast<const __half2*>(&rr);
+                            uint4 o;
+                            __half2 h0 = __floats2half2_rn(v[q * 8 + 0], v[q * 8 + 1]);
+                            __half2 h1 = __floats2half2_rn(v[q * 8 + 2], v[q * 8 + 3]);
+                            __half2 h2 = __floats2half2_rn(v[q * 8 + 4], v[q * 8 + 5]);
+                            __half2 h3 = __floats2half2_rn(v[q * 8 + 6], v[q * 8 + 7]);
+                            o.x = *reinterpret_cast<uint32_t*>(&h0);
+                            o.y = *reinterpret_cast<uint32_t*>(&h1);
+                            o.z = *reinterpret_cast<uint32_t*>(&h2);
+                            o.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(slab + lane * 64 + (((ch * 2 + q) ^ ((lane >> 1) & 3)) << 4)) = o;
+                        }
+                    } else if (row_ok) {
+                        // ragged right edge of the matrix: element-wise stores
+                        const int nc = ncol0 + ch * 16;
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float2 f = __half22float2(h[e]);
-                                v[q * 8 + 2 * e] += f.x;
-                                v[q * 8 + 2 * e + 1] += f.y;
+                        for (int j = 0; j < 16; ++j) {
+                            if (nc + j < p.n) {
+                                float x = v[j];
+                                if (residual) x += __half2float(res_row[nc + j]);
+                                out_row[nc + j] = __float2half_rn(x);
                             }
                         }
                     }
+                }
+                if (fast) {
+                    __syncwarp();
 #pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        uint4 o;
-                        __half2 h0 = __floats2half2_rn(v[q * 8 + 0], v[q * 8 + 1]);
-                        __half2 h1 = __floats2half2_rn(v[q * 8 + 2], v[q * 8 + 3]);
-                        __half2 h2 = __floats2half2_rn(v[q * 8 + 4], v[q * 8 + 5]);
-                        __half2 h3 = __floats2half2_rn(v[q * 8 + 6], v[q * 8 + 7]);
-                        o.x = *reinterpret_cast<uint32_t*>(&h0);
-                        o.y = *reinterpret_cast<uint32_t*>(&h1);
-                        o.z = *reinterpret_cast<uint32_t*>(&h2);
-                        o.w = *reinterpret_cast<uint32_t*>(&h3);
-                        *reinterpret_cast<uint4*>(out_row + nc + q * 8) = o;
+                    for (int i = 0; i < 4; ++i) {
+                        const int rr = 8 * i + crow;
+                        const uint4 o = *reinterpret_cast<const uint4*>(slab + rr * 64 + ((cchunk ^ ((rr >> 1) & 3)) << 4));
+                        if (rr < rows_here)
+                            *reinterpret_cast<uint4*>(p.out + (size_t)(m0 + wrow0 + rr) * p.ldo + ncol0 + cchunk * 8) = o;
                     }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (nc + j < p.n) {
-                            float x = v[j];
-                            if (p.mode == kEpiBiasResidual) x += __half2float(res_row[nc + j]);
-                            out_row[nc + j] = __float2half_rn(x);
-                        }
-                    }
+                    __syncwarp();
                 }
             }
             tc_fence_before();
@@ -355,9 +429,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 }  // namespace
 
 std::string gemm_global_init() {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::kSmemBytes);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::kSmemBytes);
     if (e != cudaSuccess) return std::string("cudaFuncSetAttribute(gemm_tc_kernel): ") + cudaGetErrorString(e);
     return "";
 }
@@ -389,9 +463,9 @@ std::string gemm_make_plan(GemmPlan* plan, const __half* a, int lda, const void*
 
 void gemm_launch(const GemmPlan& plan, cudaStream_t stream) {
     if (plan.b_int8)
-        gemm_tc_kernel<true><<<plan.grid, kThreads, kSmemBytes, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+        gemm_tc_kernel<true><<<plan.grid, Cfg<true>::kThreads, Cfg<true>::kSmemBytes, stream>>>(plan.tm_a, plan.tm_b, plan.p);
     else
-        gemm_tc_kernel<false><<<plan.grid, kThreads, kSmemBytes, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+        gemm_tc_kernel<false><<<plan.grid, Cfg<false>::kThreads, Cfg<false>::kSmemBytes, stream>>>(plan.tm_a, plan.tm_b, plan.p);
 }
 
 }  // namespace eosb

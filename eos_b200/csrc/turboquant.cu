@@ -444,6 +444,235 @@ __global__ void __launch_bounds__(kTqScanWarps * 32, 1) tq_scan_kernel(TqScanArg
 }
 
 // ------------------------------------------------------------------------------------------
+// the scan, streaming form for 8 queries per pass.  Differences to tq_scan_kernel:
+//   * code tiles arrive by bulk-async copies (cp.async.bulk, completion on an mbarrier) into two
+//     private 1-tile slots per warp, so every warp keeps up to two tiles (12 KB at dim 768) in flight
+//     and never waits for another warp;
+//   * the rotated queries live in registers as MMA B fragments for the whole kernel;
+//   * candidates go to a small per-warp staging area and are folded into the CTA's per-query list
+//     under a per-query lock only when the staging area is half full, so there is no block-wide
+//     barrier inside the scan loop.
+// ------------------------------------------------------------------------------------------
+constexpr int kStreamWarps = 12;
+constexpr int kStreamStage = 32;             // staged keys per (warp, query)
+constexpr int kStreamList = kTqMaxK + kStreamStage;  // CTA list capacity per query
+
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst),
+                 "l"(gsrc), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <int KSTEPS>
+__global__ void __launch_bounds__(kStreamWarps * 32, 1) tq_scan_stream_kernel(TqScanArgs a) {
+    extern __shared__ __align__(128) uint8_t sm_raw[];
+    constexpr int CHUNKS = KSTEPS / 8;
+    constexpr uint32_t TILE_BYTES = CHUNKS * 1024;
+    uint8_t* slots = sm_raw;                                                            // [warps][2][TILE_BYTES]
+    u64* list = reinterpret_cast<u64*>(sm_raw + (size_t)kStreamWarps * 2 * TILE_BYTES); // [8][kStreamList]
+    u64* stage = list + 8 * kStreamList;                                                 // [warps][8][kStreamStage]
+    u64* tau = stage + (size_t)kStreamWarps * 8 * kStreamStage;                          // [8]
+    u64* bars = tau + 8;                                                                 // [warps][2] mbarriers
+    int* lcnt = reinterpret_cast<int*>(bars + kStreamWarps * 2);                         // [8] list counts
+    int* locks = lcnt + 8;                                                               // [8]
+    int* wcnt = locks + 8;                                                               // [warps][8] staged counts
+    unsigned* hist = reinterpret_cast<unsigned*>(wcnt + kStreamWarps * 8);               // [warps][256]
+    __shared__ int abort_flag_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    if (threadIdx.x == 0) abort_flag_s = 0;
+    for (int i = threadIdx.x; i < 8; i += blockDim.x) {
+        tau[i] = 0;
+        lcnt[i] = 0;
+        locks[i] = 0;
+    }
+    for (int i = threadIdx.x; i < kStreamWarps * 8; i += blockDim.x) wcnt[i] = 0;
+    if (lane == 0) {
+        mbar_init(smem_u32(&bars[warp * 2]), 1);
+        mbar_init(smem_u32(&bars[warp * 2 + 1]), 1);
+        mbar_fence_init();
+    }
+    // rotated queries as B fragments, resident in registers
+    uint2 bq[KSTEPS];
+#pragma unroll
+    for (int s = 0; s < KSTEPS; ++s) bq[s] = __ldg(a.bfrag + s * 32 + lane);
+    __syncthreads();
+    volatile int* abort_flag = &abort_flag_s;
+    volatile u64* vtau = tau;
+
+    const long long n_tiles = (a.n_docs + kTqDocsPerTile - 1) / kTqDocsPerTile;
+    const long long stride_tiles = (long long)gridDim.x * kStreamWarps;
+    const long long first = (long long)blockIdx.x * kStreamWarps + warp;
+    const uint8_t* gt = a.tiles;
+    uint8_t* my_slots = slots + (size_t)warp * 2 * TILE_BYTES;
+    const uint32_t bar_addr[2] = {smem_u32(&bars[warp * 2]), smem_u32(&bars[warp * 2 + 1])};
+
+    auto issue = [&](long long tile, int slot) {
+        if (lane == 0 && tile < n_tiles) {
+            mbar_arrive_expect_tx(bar_addr[slot], TILE_BYTES);
+            bulk_load(smem_u32(my_slots + slot * TILE_BYTES), gt + (size_t)tile * TILE_BYTES, TILE_BYTES, bar_addr[slot]);
+        }
+    };
+    // fold this warp's staged keys of query q into the CTA list (lane-parallel, under the query's lock)
+    auto flush = [&](int q) -> bool {
+        const int m = wcnt[warp * 8 + q];
+        if (m == 0) return true;
+        int got = 0;
+        if (lane == 0) {
+            for (int spin = 0; spin < (1 << 24); ++spin) {
+                if (atomicCAS(&locks[q], 0, 1) == 0) {
+                    got = 1;
+                    break;
+                }
+                if (*abort_flag) break;
+            }
+            if (!got) *abort_flag = 1;
+        }
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) return false;
+        __threadfence_block();
+        u64* keys = list + q * kStreamList;
+        int n = *reinterpret_cast<volatile int*>(&lcnt[q]);
+        const u64 cur_tau = vtau[q];
+        const u64* st = stage + ((size_t)warp * 8 + q) * kStreamStage;
+        // staged keys that still beat the (possibly raised) threshold
+        const u64 mine = lane < m ? st[lane] : 0;
+        const bool keep = mine > cur_tau;
+        const unsigned bal = __ballot_sync(0xffffffffu, keep);
+        if (keep) keys[n + __popc(bal & ((1u << lane) - 1u))] = mine;
+        n += __popc(bal);
+        __syncwarp();
+        if (n > kTqMaxK) {
+            const u64 thr = warp_kth_largest(keys, n, a.k, hist + warp * 256, lane);
+            u64 held[kStreamList / 32];
+#pragma unroll
+            for (int r = 0; r < kStreamList / 32; ++r) {
+                const int i = r * 32 + lane;
+                held[r] = i < n ? keys[i] : 0;
+            }
+            __syncwarp();
+            int base = 0;
+#pragma unroll
+            for (int r = 0; r < kStreamList / 32; ++r) {
+                const bool kp = held[r] >= thr && held[r] != 0;
+                const unsigned b2 = __ballot_sync(0xffffffffu, kp);
+                if (kp) keys[base + __popc(b2 & ((1u << lane) - 1u))] = held[r];
+                base += __popc(b2);
+            }
+            n = base;
+            if (lane == 0) tau[q] = thr;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            lcnt[q] = n;
+            wcnt[warp * 8 + q] = 0;
+            __threadfence_block();
+            atomicExch(&locks[q], 0);
+        }
+        __syncwarp();
+        return true;
+    };
+
+    issue(first, 0);
+    issue(first + stride_tiles, 1);
+    bool ok = true;
+    long long k = 0;
+    for (long long tile = first; ok && tile < n_tiles; tile += stride_tiles, ++k) {
+        const int slot = (int)(k & 1);
+        if (!mbar_wait(bar_addr[slot], (uint32_t)((k >> 1) & 1), abort_flag)) {
+            ok = false;
+            break;
+        }
+        const uint4* tp = reinterpret_cast<const uint4*>(my_slots + slot * TILE_BYTES) + lane * 2;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const uint4 ca = tp[c * 64], cb = tp[c * 64 + 1];
+            const uint32_t wa[4] = {ca.x, ca.y, ca.z, ca.w};
+            const uint32_t wb[4] = {cb.x, cb.y, cb.z, cb.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t va[4], vb[4];
+                dequant8(wa[i], a.mag_hi[0], a.mag_hi[1], a.mag_lo[0], a.mag_lo[1], va);
+                dequant8(wb[i], a.mag_hi[0], a.mag_hi[1], a.mag_lo[0], a.mag_lo[1], vb);
+                const int s0 = c * 8 + 2 * i;
+                mma16816(acc, va[0], vb[0], va[1], vb[1], bq[s0].x, bq[s0].y);
+                mma16816(acc, va[2], vb[2], va[3], vb[3], bq[s0 + 1].x, bq[s0 + 1].y);
+            }
+        }
+        // the slot has been read: refill it with the tile after next
+        __syncwarp();
+        if (lane == 0) fence_proxy_async_smem();
+        issue(tile + 2 * stride_tiles, slot);
+        // epilogue: scale by the document norms, stage candidates that beat the running k-th
+        const long long d0 = tile * kTqDocsPerTile + g;
+        const long long d1 = d0 + 8;
+        const float n0 = d0 < a.n_docs ? __ldg(a.norms + d0) : 0.f;
+        const float n1 = d1 < a.n_docs ? __ldg(a.norms + d1) : 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const long long doc = (e & 2) ? d1 : d0;
+            if (doc < a.n_docs) {
+                const int q = 2 * t + (e & 1);
+                const float sc = acc[e] * ((e & 2) ? n1 : n0);
+                if (a.all_scores != nullptr) {
+                    a.all_scores[(long long)q * a.all_stride + doc] = sc;
+                } else {
+                    const u64 key = make_key(sc, a.id_base + (uint32_t)doc);
+                    if (key > vtau[q]) {
+                        const int pos = atomicAdd(&wcnt[warp * 8 + q], 1);
+                        stage[((size_t)warp * 8 + q) * kStreamStage + pos] = key;  // pos < 32: flushed above 16
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (a.all_scores == nullptr) {
+            const int pending = lane < 8 ? wcnt[warp * 8 + lane] : 0;
+            unsigned need = __ballot_sync(0xffffffffu, pending > kStreamStage / 2);
+            while (need && ok) {
+                const int q = __ffs(need) - 1;
+                need &= need - 1;
+                ok = flush(q);
+            }
+        }
+    }
+    if (a.all_scores == nullptr) {
+        for (int q = 0; q < 8 && ok; ++q) ok = flush(q);
+    }
+    __syncthreads();
+    if (a.all_scores != nullptr) return;
+    // final cut to k and write-out: warp q finishes query q
+    if (warp < 8) {
+        const int q = warp;
+        u64* keys = list + q * kStreamList;
+        const int n = lcnt[q];
+        u64 thr = 0;
+        if (n > a.k) thr = warp_kth_largest(keys, n, a.k, hist + warp * 256, lane);
+        u64* out = reinterpret_cast<u64*>(a.cand_keys) + ((size_t)q * a.grid + blockIdx.x) * kTqMaxK;
+        int base = 0;
+        for (int r = 0; r < kStreamList / 32; ++r) {
+            const int i = r * 32 + lane;
+            const u64 key = i < n ? keys[i] : 0;
+            const bool keep = key != 0 && key >= thr;
+            const unsigned bal = __ballot_sync(0xffffffffu, keep);
+            if (keep) out[base + __popc(bal & ((1u << lane) - 1u))] = key;
+            base += __popc(bal);
+        }
+        if (lane == 0) a.cand_count[(size_t)q * a.grid + blockIdx.x] = base;
+    }
+    if (threadIdx.x == 0 && abort_flag_s != 0 && a.status != nullptr) atomicExch(a.status, kStatusPipelineTimeout);
+}
+
+template <int KSTEPS>
+size_t tq_stream_smem() {
+    return (size_t)kStreamWarps * 2 * (KSTEPS / 8) * 1024 + (size_t)8 * kStreamList * 8 +
+           (size_t)kStreamWarps * 8 * kStreamStage * 8 + 8 * 8 + (size_t)kStreamWarps * 2 * 8 + 8 * 4 + 8 * 4 +
+           (size_t)kStreamWarps * 8 * 4 + (size_t)kStreamWarps * 256 * 4 + 128;
+}
+
+// ------------------------------------------------------------------------------------------
 // merge: one CTA per query; block-wide radix select of the k-th largest key over all candidate
 // segments (read from global / L2), gather of the survivors, bitonic sort by one warp.
 // ------------------------------------------------------------------------------------------
@@ -667,6 +896,14 @@ cudaError_t tq_scan_init() {
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(tq_scan_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tq_scan_stream_kernel<48>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tq_scan_stream_kernel<24>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tq_scan_stream_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tq_scan_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
         e = cudaFuncSetAttribute(tq_pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(tq_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
@@ -674,6 +911,14 @@ cudaError_t tq_scan_init() {
 }
 
 void launch_tq_scan(const TqScanArgs& a, cudaStream_t stream) {
+    if (a.query_tiles == 1) {
+        const int ks = tq_ksteps(a.dim);
+        const int threads = kStreamWarps * 32;
+        if (ks == 48) { tq_scan_stream_kernel<48><<<a.grid, threads, tq_stream_smem<48>(), stream>>>(a); return; }
+        if (ks == 24) { tq_scan_stream_kernel<24><<<a.grid, threads, tq_stream_smem<24>(), stream>>>(a); return; }
+        if (ks == 16) { tq_scan_stream_kernel<16><<<a.grid, threads, tq_stream_smem<16>(), stream>>>(a); return; }
+        if (ks == 8) { tq_scan_stream_kernel<8><<<a.grid, threads, tq_stream_smem<8>(), stream>>>(a); return; }
+    }
     const size_t smem = tq_scan_smem_bytes(a.query_tiles, a.dim);
     const int threads = kTqScanWarps * 32;
     if (a.query_tiles == 1) tq_scan_kernel<1><<<a.grid, threads, smem, stream>>>(a);

@@ -66,6 +66,7 @@ struct TqScanArgs {
     uint64_t* cand_keys;   // [query_tiles*8][grid][kTqMaxK]
     int* cand_count;       // [query_tiles*8][grid]
     int grid;
+    int* status;           // device status word (receives kStatusPipelineTimeout if a bounded wait runs out)
     float* all_scores;     // when non-null: every score is stored at all_scores[q * all_stride + doc]
     long long all_stride;  // and the top-k bookkeeping is skipped
 };

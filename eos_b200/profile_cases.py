@@ -14,12 +14,12 @@ import sys
 import numpy as np
 
 
-def case_gemm(residual: bool = False, weight_mode: int = 0, rows: int = 32768) -> None:
+def case_gemm(residual: bool = False, weight_mode: int = 0, rows: int = 32768, kn=None) -> None:
     import eos_b200
     from eos_b200 import synth
     rt = eos_b200.Runtime(0)
     rng = np.random.default_rng(0)
-    k, n = (3072, 768) if residual else (768, 3072)
+    k, n = kn if kn is not None else ((3072, 768) if residual else (768, 3072))
     x = rng.standard_normal((rows, k), dtype=np.float32)
     w = synth.quantize_per_channel(rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
     bias = (rng.standard_normal(n) * 0.02).astype(np.float32)
@@ -82,5 +82,6 @@ if __name__ == "__main__":
     {"gemm": case_gemm, "gemm_res": lambda: case_gemm(True), "scan": case_scan, "attention": case_attention,
      "gemm_f16w": lambda: case_gemm(False, 1), "gemm_res_f16w": lambda: case_gemm(True, 1),
      "gemm_big": lambda: case_gemm(False, 0, 131072), "gemm_res_big": lambda: case_gemm(True, 0, 131072),
-     "gemm_big_f16w": lambda: case_gemm(False, 1, 131072), "gemm_res_big_f16w": lambda: case_gemm(True, 1, 131072),
+     "gemm_big_f16w": lambda: case_gemm(False, 1, 131072),
+     "gemm_attn_out_big_f16w": lambda: case_gemm(True, 1, 131072, (768, 768)), "gemm_res_big_f16w": lambda: case_gemm(True, 1, 131072),
      }[name]()

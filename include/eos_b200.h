@@ -169,6 +169,7 @@ typedef struct {
     int32_t steps;
     int32_t gemm_launches, attention_launches, layernorm_launches, other_launches;
     float gemm_ms, attention_ms, layernorm_ms, embed_ms, pool_ms, layout_ms;
+    float gemm_kind_ms[4];     /* fused QKV, attention output, FFN up, FFN down */
 } EosB200EncoderTimes;
 EOS_B200_API int eos_b200_encoder_profile_begin(EosB200Encoder* enc, int max_steps, char** err);
 EOS_B200_API int eos_b200_encoder_profile_end(EosB200Encoder* enc, void* stream, EosB200EncoderTimes* out, char** err);

@@ -35,7 +35,7 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(_lib.EncoderLayer) == 6 * 40 + 10 * 8
     assert _lib.EncoderDesc.epsilon.offset == 48
     assert C.sizeof(_lib.Stats) == 40
-    assert C.sizeof(_lib.EncoderTimes) == 44
+    assert C.sizeof(_lib.EncoderTimes) == 60
 
 
 def test_no_cpu_fallback_without_a_device():
