@@ -14,8 +14,8 @@
 //                delivered), O reusing S_0's columns.  Work is cut into sub-items of at most two key
 //                tiles = half of tensor memory, so the S phase of the next sub-item is issued before
 //                the P V phase of the current one and two sub-items are always in flight.
-//                The row sums l = P 1 come from a third, 16-column MMA against a tile of ones, so they are
-//                the fp32 sums of exactly the f16 probabilities that multiply V.
+//                The row sums l = P 1 come out of the same MMA: its B operand is [V | ones] (N = 80), so
+//                they are the fp32 sums of exactly the f16 probabilities that multiply V.
 //   warps 4-11   softmax (thread = query row, two warps per row split the columns): pass A reads all
 //                S tiles for the row maximum, pass B re-reads them, writes P = exp2(s - m) (packed f16 ex2)
 //                into the 128B-swizzled K-major layout the second MMA consumes; finally O / l -> f16 -> global.
@@ -31,9 +31,15 @@ namespace eosb {
 
 #ifdef EOSB_ATTN_TIMING
 __device__ long long g_attn_timing[16];
-#define TMARK(i) do { if (blockIdx.x == 0 && threadIdx.x == 128) { long long now__ = clock64(); g_attn_timing[i] += now__ - tlast__; tlast__ = now__; } } while (0)
+__device__ long long g_attn_trace[2][2048];
+#define TMARK(i) do { long long now__ = clock64(); tacc__[i] += now__ - tlast__; tlast__ = now__; if (blockIdx.x == 0 && threadIdx.x == 128 && tcnt__ < 2048) g_attn_trace[0][tcnt__++] = (now__ << 8) | (i); } while (0)
 #else
 #define TMARK(i) do { } while (0)
+#endif
+#ifdef EOSB_ATTN_TIMING
+#define MMARK(i) do { long long now__ = clock64(); macc__[(i) - 8] += now__ - mlast__; mlast__ = now__; if (blockIdx.x == 0 && mcnt__ < 2048) g_attn_trace[1][mcnt__++] = (now__ << 8) | (i); } while (0)
+#else
+#define MMARK(i) do { } while (0)
 #endif
 
 namespace {
@@ -62,14 +68,13 @@ struct WorkItem {
     int ntiles;  // key tiles of 128
 };
 
-__device__ __forceinline__ WorkItem decode_item(int w, int heads, const int4* __restrict__ qtile_info) {
-    const int4 q = __ldg(qtile_info + w / heads);
+__device__ __forceinline__ WorkItem decode_item(const int4 q, int head) {
     WorkItem it;
     it.row0 = q.x;
     it.nrows = q.y;
     it.nkeys = q.z > 512 ? 512 : q.z;  // the host only selects this kernel when tokens <= 512
     it.q0 = q.w;
-    it.head = w % heads;
+    it.head = head;
     it.ntiles = (it.nkeys + 127) >> 7;
     return it;
 }
@@ -77,15 +82,42 @@ __device__ __forceinline__ WorkItem decode_item(int w, int heads, const int4* __
 // A work item is processed as one or two sub-items of at most two key tiles (256 keys): a sub-item
 // needs only half of tensor memory, so two of them are in flight per SM; the two partial softmax
 // results of a long sequence are merged in registers (same rule as split-key flash decoding).
+// The walker keeps the descriptor of the item after the current one in flight (loaded one item
+// ahead), so that stepping to the next item never waits for global memory.
 struct Walker {
-    int w, step, total, heads;
+    int w, total;
+    int qi, head;             // w = qi * heads + head
+    int step_q, step_h, heads;
     const int4* info;
     int sub;
     unsigned item_no;  // items visited so far
     WorkItem wi;
+    int4 pre;          // descriptor of item w + step (valid if that item exists)
+    __device__ __forceinline__ void advance_index() {
+        w += step_q * heads + step_h;
+        qi += step_q;
+        head += step_h;
+        if (head >= heads) { head -= heads; ++qi; }
+    }
+    __device__ __forceinline__ void prefetch() {
+        int q2 = qi + step_q, h2 = head + step_h;
+        if (h2 >= heads) ++q2;
+        if (w + step_q * heads + step_h < total) pre = __ldg(info + q2);
+    }
     __device__ __forceinline__ void init(int first, int stride, int tot, int h, const int4* p) {
-        w = first; step = stride; total = tot; heads = h; info = p; sub = 0; item_no = 0;
-        if (w < total) wi = decode_item(w, heads, info);
+        w = first; total = tot; heads = h; info = p; sub = 0; item_no = 0;
+        qi = first / h; head = first - qi * h;
+        step_q = stride / h; step_h = stride - step_q * h;
+        pre = make_int4(0, 0, 0, 0);
+        if (w < total) {
+            wi = decode_item(__ldg(info + qi), head);
+            prefetch();
+        }
+    }
+    // copy of the position without the in-flight descriptor (touching it would wait for the load)
+    __device__ __forceinline__ void follow(const Walker& o) {
+        w = o.w; total = o.total; qi = o.qi; head = o.head; step_q = o.step_q; step_h = o.step_h; heads = o.heads;
+        info = o.info; sub = o.sub; item_no = o.item_no; wi = o.wi;
     }
     __device__ __forceinline__ bool valid() const { return w < total; }
     __device__ __forceinline__ int nsub() const { return wi.ntiles > 2 ? 2 : 1; }
@@ -95,16 +127,19 @@ struct Walker {
     __device__ __forceinline__ bool last_sub() const { return sub + 1 == nsub(); }
     __device__ __forceinline__ void next() {
         if (sub + 1 < nsub()) { ++sub; return; }
-        w += step; sub = 0; ++item_no;
-        if (w < total) wi = decode_item(w, heads, info);
+        advance_index();
+        sub = 0; ++item_no;
+        if (w < total) {
+            wi = decode_item(pre, head);
+            prefetch();
+        }
     }
 };
 
-// MN-major operand tile (row = K index, 64 contiguous MN elements = 128 bytes per row, 128B
-// swizzle): 8-row groups of 1024 bytes along K (stride byte offset), a single 64-wide MN block.
-__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
+// MN-major operand tile (V; row = K index, 64 contiguous MN elements = 128 bytes per row, 128B
+// swizzle): 8-row groups of 1024 bytes along K (stride byte offset); the leading byte offset is the
+// distance from one 64-wide MN block to the next (used when N > 64).  Its descriptor has the same
+// high half as the K-major one.
 
 __device__ __forceinline__ uint32_t ex2_f16x2(float x0, float x1) {
     __half2 h = __floats2half2_rn(x0, x1);
@@ -211,7 +246,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                     ok = ok && load_kv(nxt, 1);
                 }
                 ok = ok && load_kv(cur, 2);
-                cur = nxt;
+                cur.follow(nxt);
                 if (nxt.valid()) nxt.next();
             }
         }
@@ -220,14 +255,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc_f16(128, 128);
-            constexpr uint32_t idesc_o = umma_idesc_f16(128, 64) | (1u << 16);  // B (= V) is MN-major
-            constexpr uint32_t idesc_l = umma_idesc_f16(128, 16);               // row sums: P x ones
+            // B = [V | ones]: 64 columns of V (MN-major, as TMA delivered it) and, as a second MN block, 16
+            // columns of 1.0, so that columns 64..79 of the accumulator are the row sums of P
+            constexpr uint32_t idesc_o = umma_idesc_f16(128, 80) | (1u << 16);
             uint32_t kvc = 0, pc = 0;
             bool ok = true;
+#ifdef EOSB_ATTN_TIMING
+            long long mlast__ = clock64();
+            long long macc__[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            int mcnt__ = 0;
+#endif
             // S phase of sub-item number n (in tensor-memory half n & 1)
             auto issue_s = [&](const Walker& wk, uint32_t n) -> bool {
                 const int h = n & 1u;
+                MMARK(8);
                 if (n >= 2 && !mbar_wait(half_free(h), ((n >> 1) - 1u) & 1u, abort_flag)) return false;
+                MMARK(9);
                 const int qs = wk.item_no % kQStages;
                 if (wk.first_sub() && !mbar_wait(q_full(qs), (wk.item_no / kQStages) & 1u, abort_flag)) return false;
                 tc_fence_after();
@@ -236,13 +279,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                     const int s = kvc % kKvStages;
                     if (!mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag)) return false;
                     tc_fence_after();
-                    const uint32_t k_addr = base + kOffKv + s * kTileBytes;
+                    MMARK(10);
+                    const uint32_t q_lo = umma_desc_sw128_lo(q_addr);
+                    const uint32_t k_lo = umma_desc_sw128_lo(base + kOffKv + s * kTileBytes);
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma_f16(tmem_base + h * 256 + t * 128, umma_desc_sw128(q_addr + kk * 32),
-                                 umma_desc_sw128(k_addr + kk * 32), idesc_s, kk > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < 4; ++kk)  // 32 bytes along K per step = 2 in descriptor units
+                        umma_f16_split(tmem_base + h * 256 + t * 128, q_lo + kk * 2, kDescSw128Hi, k_lo + kk * 2,
+                                       kDescSw128Hi, idesc_s, kk > 0 ? 1u : 0u);
                     umma_commit(kv_empty(s));
                     umma_commit(s_full(h, t));
+                    MMARK(11);
                 }
                 if (wk.last_sub()) {
                     if (wk.wi.ntiles > 0) umma_commit(q_empty(qs)); else mbar_arrive(q_empty(qs));
@@ -254,22 +300,26 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                 for (int t = 0; t < wk.nt(); ++t, ++kvc, ++pc) {
                     const int s = kvc % kKvStages;
                     const int pb = pc & 1;
-                    if (!mbar_wait(p_full(pb), (pc >> 1) & 1u, abort_flag) ||
-                        !mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag))
-                        return false;
+                    MMARK(8);
+                    if (!mbar_wait(p_full(pb), (pc >> 1) & 1u, abort_flag)) return false;
+                    MMARK(12);
+                    if (!mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag)) return false;
                     tc_fence_after();
+                    MMARK(13);
                     const uint32_t p_addr = base + kOffP + pb * kPBytes;
                     const uint32_t v_addr = base + kOffKv + s * kTileBytes;
+                    const uint32_t p_lo = umma_desc_sw128_lo(p_addr);
+                    // MN-major V: start address and the leading offset (distance to the block of ones) both
+                    // move by one 16-key slab (2048 bytes = 128 units) per step, in opposite directions
+                    const uint32_t v_lo = ((v_addr >> 4) & 0x3fffu) | (((base + kOffOnes - v_addr) >> 4) << 16);
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) {
-                        const uint64_t pd = umma_desc_sw128(p_addr + (kk >> 2) * (kPBytes / 2) + (kk & 3) * 32);
-                        umma_f16(tmem_base + h * 256, pd, umma_desc_sw128_mn(v_addr + kk * 2048), idesc_o,
-                                 (t > 0 || kk > 0) ? 1u : 0u);
-                        umma_f16(tmem_base + h * 256 + 64, pd, umma_desc_sw128(base + kOffOnes + (kk & 3) * 32), idesc_l,
-                                 (t > 0 || kk > 0) ? 1u : 0u);
-                    }
+                    for (int kk = 0; kk < 8; ++kk)
+                        umma_f16_split(tmem_base + h * 256, p_lo + (kk >> 2) * (kPBytes / 2 / 16) + (kk & 3) * 2,
+                                       kDescSw128Hi, v_lo + kk * 128u - ((kk * 128u) << 16), kDescSw128Hi, idesc_o,
+                                       (t > 0 || kk > 0) ? 1u : 0u);
                     umma_commit(kv_empty(s));
                     umma_commit(p_empty(pb));
+                    MMARK(14);
                 }
                 if (wk.nt() > 0) umma_commit(o_full(h));
                 return true;
@@ -285,10 +335,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
             while (ok && cur.valid()) {
                 if (nxt.valid()) ok = issue_s(nxt, n + 1);
                 ok = ok && issue_pv(cur, n);
-                cur = nxt;
+                cur.follow(nxt);
                 if (nxt.valid()) nxt.next();
                 ++n;
             }
+#ifdef EOSB_ATTN_TIMING
+            if (blockIdx.x == 0)
+                for (int i = 0; i < 8; ++i) g_attn_timing[8 + i] += macc__[i];
+#endif
         }
         __syncwarp();
     } else if (warp >= 4) {
@@ -367,6 +421,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         float ms_prev = 0.f;
 #ifdef EOSB_ATTN_TIMING
         long long tlast__ = clock64();
+        long long tacc__[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int tcnt__ = 0;
 #endif
         bool have_prev = false;
         while (ok && cur.valid()) {
@@ -476,13 +532,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
             }
             if (have_prev) ok = epilogue(prev, n - 1, ms_prev);
             TMARK(5);
-            prev = cur;
+            prev.follow(cur);
             ms_prev = ms;
             have_prev = true;
             cur.next();
             ++n;
         }
         if (ok && have_prev) epilogue(prev, n - 1, ms_prev);
+#ifdef EOSB_ATTN_TIMING
+        if (blockIdx.x == 0 && threadIdx.x == 128)
+            for (int i = 0; i < 8; ++i) g_attn_timing[i] += tacc__[i];
+#endif
     }
 
     tc_fence_before();
@@ -502,6 +562,9 @@ extern "C" __attribute__((visibility("default"))) int eos_b200_debug_attn_timing
     if (cudaMemcpyFromSymbol(out16, g_attn_timing, sizeof(zero)) != cudaSuccess) return 1;
     if (reset && cudaMemcpyToSymbol(g_attn_timing, zero, sizeof(zero)) != cudaSuccess) return 1;
     return 0;
+}
+extern "C" __attribute__((visibility("default"))) int eos_b200_debug_attn_trace(long long* out4096) {
+    return cudaMemcpyFromSymbol(out4096, g_attn_trace, sizeof(long long) * 4096) != cudaSuccess;
 }
 #endif
 

@@ -86,6 +86,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tmap,
         : "memory");
 }
 
+// Asks L2 to fetch a tile ahead of the TMA load that will bring it into shared memory.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols)
@@ -122,6 +127,23 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
         " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// Same MMA with the two shared-memory descriptors given as 32-bit halves: the high halves are
+// compile-time constants of a layout and the low halves (start address, leading offset) advance
+// by constants along K, so the issuing thread spends one add per operand between two MMAs.
+__device__ __forceinline__ void umma_f16_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n"
+        " mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Halves of the K-major 128B-swizzle descriptor of umma_desc_sw128.
+constexpr uint32_t kDescSw128Hi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t umma_desc_sw128_lo(uint32_t smem_addr) {
+    return ((smem_addr >> 4) & 0x3fffu) | (1u << 16);
 }
 // Arrive on an mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {

@@ -31,6 +31,13 @@
 
 namespace eosb {
 
+#ifdef EOSB_GEMM_TIMING
+__device__ long long g_gemm_timing[16];
+#define GMARK(i) do { long long now__ = clock64(); g_gemm_timing[i] += now__ - tlast__; tlast__ = now__; } while (0)
+#else
+#define GMARK(i) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int BM = 128;
@@ -158,11 +165,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             uint32_t it = 0;
             uint32_t t = 0;
             bool ok = true;
+#ifdef EOSB_GEMM_TIMING
+            long long tlast__ = clock64();
+            const bool tm__ = blockIdx.x == 0;
+#endif
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
                 const uint32_t ab = t & 1u;
                 const uint32_t aph = (t >> 1) & 1u;
                 if (!mbar_wait(acc_empty(ab), aph ^ 1u, abort_flag)) break;
                 tc_fence_after();
+#ifdef EOSB_GEMM_TIMING
+                if (tm__) GMARK(0);
+#endif
                 const uint32_t d_tmem = tmem_base + ab * BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % kStagesAB;
@@ -185,6 +199,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         b_addr = base + C::kOffB16 + s * kBytesB16;
                     }
                     tc_fence_after();
+#ifdef EOSB_GEMM_TIMING
+                    if (tm__) GMARK(1);
+#endif
                     const uint32_t a_addr = base + C::kOffA + s * kBytesA;
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
@@ -193,6 +210,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                     umma_commit(empty_ab(s));
                     if (kBInt8) umma_commit(empty_b16(c));
+#ifdef EOSB_GEMM_TIMING
+                    if (tm__) GMARK(2);
+#endif
                 }
                 if (ok) umma_commit(acc_full(ab));
             }
@@ -257,6 +277,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int ehalf = ew >> 2;                                  // which 128 columns of the tile
         const uint32_t lane_base = (uint32_t)wrow0;
         uint8_t* slab = sm + C::kOffSlab + ew * kSlabBytes;         // [32 rows][8 x 16 B], chunk index ^ (row & 7)
+#ifdef EOSB_GEMM_TIMING
+        long long tlast__ = clock64();
+        const bool tm__ = blockIdx.x == 0 && etid == 0;
+#endif
         uint32_t t = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
             const int m0 = (tile / n_tiles) * BM;
@@ -302,8 +326,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             };
             if (residual) residual_fetch(0);
             named_bar_sync(1, kEpilogueWarps * 32);
+#ifdef EOSB_GEMM_TIMING
+            if (tm__) GMARK(4);
+#endif
             if (!mbar_wait(acc_full(ab), aph, abort_flag)) break;
             tc_fence_after();
+#ifdef EOSB_GEMM_TIMING
+            if (tm__) GMARK(5);
+#endif
 
             uint32_t r_next[16];
             __syncwarp();
@@ -410,6 +440,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     __syncwarp();
                 }
             }
+#ifdef EOSB_GEMM_TIMING
+            if (tm__) GMARK(6);
+#endif
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty(ab));
@@ -427,6 +460,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 }
 
 }  // namespace
+
+#ifdef EOSB_GEMM_TIMING
+extern "C" __attribute__((visibility("default"))) int eos_b200_debug_gemm_timing(long long* out16, int reset) {
+    long long zero[16] = {0};
+    if (cudaMemcpyFromSymbol(out16, g_gemm_timing, sizeof(zero)) != cudaSuccess) return 1;
+    if (reset && cudaMemcpyToSymbol(g_gemm_timing, zero, sizeof(zero)) != cudaSuccess) return 1;
+    return 0;
+}
+#endif
 
 std::string gemm_global_init() {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::kSmemBytes);

@@ -465,7 +465,7 @@ __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, u
 
 template <int KSTEPS>
 __global__ void __launch_bounds__(kStreamWarps * 32, 1) tq_scan_stream_kernel(TqScanArgs a) {
-    extern __shared__ __align__(128) uint8_t sm_raw[];
+    extern __shared__ __align__(16) uint8_t sm_raw[];
     constexpr int CHUNKS = KSTEPS / 8;
     constexpr uint32_t TILE_BYTES = CHUNKS * 1024;
     uint8_t* slots = sm_raw;                                                            // [warps][2][TILE_BYTES]
@@ -610,19 +610,31 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) tq_scan_stream_kernel(Tq
         const long long d1 = d0 + 8;
         const float n0 = d0 < a.n_docs ? __ldg(a.norms + d0) : 0.f;
         const float n1 = d1 < a.n_docs ? __ldg(a.norms + d1) : 0.f;
+        if (a.all_scores != nullptr) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const long long doc = (e & 2) ? d1 : d0;
-            if (doc < a.n_docs) {
-                const int q = 2 * t + (e & 1);
-                const float sc = acc[e] * ((e & 2) ? n1 : n0);
-                if (a.all_scores != nullptr) {
-                    a.all_scores[(long long)q * a.all_stride + doc] = sc;
-                } else {
-                    const u64 key = make_key(sc, a.id_base + (uint32_t)doc);
-                    if (key > vtau[q]) {
+            for (int e = 0; e < 4; ++e) {
+                const long long doc = (e & 2) ? d1 : d0;
+                if (doc < a.n_docs)
+                    a.all_scores[(long long)(2 * t + (e & 1)) * a.all_stride + doc] = acc[e] * ((e & 2) ? n1 : n0);
+            }
+        } else {
+            // keys of documents past the end are 0 and never beat a threshold
+            u64 key[4];
+            bool any_pass = false;
+            const u64 t0 = vtau[2 * t], t1 = vtau[2 * t + 1];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const long long doc = (e & 2) ? d1 : d0;
+                key[e] = doc < a.n_docs ? make_key(acc[e] * ((e & 2) ? n1 : n0), a.id_base + (uint32_t)doc) : 0;
+                any_pass |= key[e] > ((e & 1) ? t1 : t0);
+            }
+            if (__any_sync(0xffffffffu, any_pass)) {  // rare once the lists have warmed up
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int q = 2 * t + (e & 1);
+                    if (key[e] > ((e & 1) ? t1 : t0)) {
                         const int pos = atomicAdd(&wcnt[warp * 8 + q], 1);
-                        stage[((size_t)warp * 8 + q) * kStreamStage + pos] = key;  // pos < 32: flushed above 16
+                        stage[((size_t)warp * 8 + q) * kStreamStage + pos] = key[e];  // pos < 32: flushed above 16
                     }
                 }
             }

@@ -2,7 +2,7 @@
 
     python -m eos_b200.profile_cases gemm        # projection kernel, 32768 x 768 -> 3072, erf-GELU epilogue
     python -m eos_b200.profile_cases gemm_res    # 32768 x 3072 -> 768 with residual epilogue
-    python -m eos_b200.profile_cases scan        # TurboQuant scan, 1,000,000 x 768 4-bit codes, 16 queries per pass
+    python -m eos_b200.profile_cases scan        # TurboQuant scan, 2,000,000 x 768 4-bit codes (776 MB), 8 / 16 / 32 queries per pass
     python -m eos_b200.profile_cases attention   # 2-layer encoder forward, 128 x 512 tokens (attention + LN kernels)
 
 Each case touches more than the 126 MB L2 but holds well under a few GB on the device.
@@ -31,7 +31,7 @@ def case_gemm(residual: bool = False, weight_mode: int = 0, rows: int = 32768, k
     rt.close()
 
 
-def case_scan() -> None:
+def case_scan(n: int = 2_000_000) -> None:
     import torch
 
     import eos_b200
@@ -39,20 +39,25 @@ def case_scan() -> None:
     rt = eos_b200.Runtime(0)
     spec = eos_b200.make_rotation_spec(768, 4, seed=402)
     qz = eos_b200.Quantizer(rt, spec)
-    n = 1_000_000
-    x = torch.empty((n, 768), dtype=torch.float32, device="cuda")
+    chunk = 500_000
+    x = torch.empty((chunk, 768), dtype=torch.float32, device="cuda")
     codes = torch.empty((n, 384), dtype=torch.uint8, device="cuda")
     norms = torch.empty((n,), dtype=torch.float32, device="cuda")
-    tq.synth_gaussian_device(rt, 401, 0, n, 768, True, x.data_ptr())
-    qz.quantize_device(x.data_ptr(), n, codes.data_ptr(), norms.data_ptr())
+    for c0 in range(0, n, chunk):
+        c1 = min(n, c0 + chunk)
+        tq.synth_gaussian_device(rt, 401, c0, c1 - c0, 768, True, x.data_ptr())
+        qz.quantize_device(x.data_ptr(), c1 - c0, codes[c0:].data_ptr(), norms[c0:].data_ptr())
+    torch.cuda.synchronize()
     corpus = eos_b200.Corpus(qz, device_ptrs=(codes.data_ptr(), norms.data_ptr(), n))
     q = x[:64].cpu().numpy()
-    del x
+    del x, codes
+    torch.cuda.empty_cache()
     for per_pass in (8, 16, 32):
+        corpus.score_topk(q, 100, queries_per_pass=per_pass)
         corpus.profile_begin(64)
         corpus.score_topk(q, 100, queries_per_pass=per_pass)
         ms, launches = corpus.profile_end()
-        print(f"scan {per_pass} queries/pass: {ms / launches:.3f} ms per pass, "
+        print(f"scan {n} rows, {per_pass} queries/pass: {ms / launches:.3f} ms per pass, "
               f"{n * spec.vector_bytes / (ms / launches) / 1e6:.0f} GB/s")
     corpus.close()
     qz.close()
