@@ -86,9 +86,35 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tmap,
         : "memory");
 }
 
-// Asks L2 to fetch a tile ahead of the TMA load that will bring it into shared memory.
-__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+// Same load issued by either CTA of a CTA pair (cta_group::2): the data lands in the issuing CTA's
+// shared memory, the byte count is credited to an mbarrier that may live in the other CTA of the
+// pair (bar is a shared::cluster address, see mapa_shared).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* tmap, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// ---------------------------------------------------------------- thread-block clusters
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Barrier over every thread of every CTA of the cluster (also orders shared-memory accesses).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in the CTA of the given rank.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t smem_addr, uint32_t cta_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
 // ---------------------------------------------------------------- tcgen05 / TMEM
@@ -101,6 +127,18 @@ __device__ __forceinline__ void tmem_relinquish() {
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// CTA-pair variants (cta_group::2): issued by the same warp of both CTAs of the pair.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
 // Shared-memory matrix descriptor for a K-major operand tile stored with the 128-byte
@@ -138,6 +176,26 @@ __device__ __forceinline__ void umma_f16_split(uint32_t d_tmem, uint32_t a_lo, u
         " mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n"
         " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n" ::"r"(d_tmem),
         "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One MMA over a CTA pair (cta_group::2), issued by one thread of the pair's leader CTA: M = 256
+// (128 rows from each CTA's A tile), B = the two CTAs' tiles side by side along N; each CTA's
+// tensor memory receives its own 128 rows of D.  The descriptors are offsets valid in both CTAs.
+__device__ __forceinline__ void umma_f16_pair_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                    uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %6, 0;\n"
+        " mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive, in every CTA of cta_mask, on the mbarrier at this shared-memory offset once every MMA
+// issued so far by this thread (for the CTA pair) has completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+        "h"(cta_mask)
         : "memory");
 }
 // Halves of the K-major 128B-swizzle descriptor of umma_desc_sw128.
@@ -206,6 +264,25 @@ __device__ __forceinline__ float gelu_erf_fast(float x) {
     const float z = x * p;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z));
     return __fdividef(x, 1.0f + e);
+}
+// Two values at once with one reciprocal: 1/a = b/(ab), 1/b = a/(ab), so the pair costs three MUFU
+// ops instead of four (the epilogue that applies it is MUFU-bound).  The exponent is clamped so that
+// the product (1 + e0)(1 + e1) stays finite; beyond the clamp the sigmoid is below 2^-60.
+__device__ __forceinline__ void gelu_erf_fast2(float& x0, float& x1) {
+    const float t0 = fminf(x0 * x0, 18.0f), t1 = fminf(x1 * x1, 18.0f);
+    float p0 = fmaf(t0, 2.33936606e-5f, 7.47459662e-4f), p1 = fmaf(t1, 2.33936606e-5f, 7.47459662e-4f);
+    p0 = fmaf(p0, t0, -1.06012290e-1f);
+    p1 = fmaf(p1, t1, -1.06012290e-1f);
+    p0 = fmaf(p0, t0, -2.30159100e+0f);
+    p1 = fmaf(p1, t1, -2.30159100e+0f);
+    float e0, e1, r;
+    const float z0 = fminf(x0 * p0, 60.0f), z1 = fminf(x1 * p1, 60.0f);
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(z0));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(z1));
+    const float a = 1.0f + e0, b = 1.0f + e1;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a * b));
+    x0 = x0 * (r * b);
+    x1 = x1 * (r * a);
 }
 // tanh-form GELU of the compact encoder profile.
 __device__ __forceinline__ float gelu_tanh(float x) {

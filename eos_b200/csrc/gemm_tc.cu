@@ -22,9 +22,21 @@
 //               through a per-warp swizzled staging slab of 32 rows x 32 columns, so that every global
 //               access instruction covers 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
 // Two accumulators (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// CTA-pair mode (f16 weights): two CTAs of a cluster share one 256x256 output tile.  Each loads its
+// own 128 rows of A and 128 of the 256 W rows (32 KB per k-block instead of 48 KB, 6 ring stages), the
+// leader's MMA thread issues tcgen05.mma.cta_group::2 (M = 256) reading both CTAs' shared memory, and
+// each CTA's epilogue drains its own 128 rows from its own tensor memory.  TMA completions of both
+// CTAs count on the leader's full barrier; the MMA commits release both CTAs' ring stages; both
+// epilogues arrive on the leader's accumulator-empty barrier.  Measured on the encoder's shapes it is
+// not faster than one CTA per tile (both are bound by shared-memory bandwidth and, at K = 768, by the
+// epilogue), so it is opt-in: environment EOS_B200_GEMM_CTA_PAIR=1.
 // Every mbarrier wait is bounded (common.cuh: mbar_wait); on a timeout the kernel raises a CTA-wide
 // abort flag, all roles leave their loops, TMEM is freed and the status word is set.
 #include "gemm_tc.cuh"
+
+#include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "tma_util.cuh"
@@ -33,9 +45,13 @@ namespace eosb {
 
 #ifdef EOSB_GEMM_TIMING
 __device__ long long g_gemm_timing[16];
-#define GMARK(i) do { long long now__ = clock64(); g_gemm_timing[i] += now__ - tlast__; tlast__ = now__; } while (0)
+// timing marks accumulate in registers (a read-modify-write of global memory per mark would itself
+// stall the role being measured) and are flushed once per role
+#define GMARK(i) do { long long now__ = clock64(); gacc__[(i) & 3] += now__ - tlast__; tlast__ = now__; } while (0)
+#define GFLUSH(base) do { if (tm__) for (int i__ = 0; i__ < 4; ++i__) g_gemm_timing[(base) + i__] += gacc__[i__]; } while (0)
 #else
 #define GMARK(i) do { } while (0)
+#define GFLUSH(base) do { } while (0)
 #endif
 
 namespace {
@@ -43,18 +59,22 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int kStagesAB = 4;    // ring depth of the TMA-fed stages
 constexpr int kStagesB16 = 2;   // ring depth of the dequantised W tiles (8-bit mode)
-constexpr int kEpilogueWarps = 8;
 constexpr int kTmemCols = 512;  // two 128x256 fp32 accumulators
 constexpr uint32_t kBytesA = BM * BK * 2;
-constexpr uint32_t kBytesB16 = BN * BK * 2;
 constexpr uint32_t kBytesB8 = BN * BK;
 constexpr int kSlabCols = 32;                  // columns of the staging slab of one epilogue warp
 constexpr uint32_t kSlabBytes = 32 * kSlabCols * 2;
 
-template <bool kBInt8>
+template <bool kBInt8, bool kPair>
 struct Cfg {
+    static_assert(!(kBInt8 && kPair), "CTA-pair mode takes f16 weights");
+    static constexpr int kStagesAB = kPair ? 6 : 4;          // ring depth of the TMA-fed stages
+    static constexpr int kEpilogueWarps = 8;                 // 2 per TMEM lane quarter (a multiple of 4)
+    static constexpr int kWarpCols = BN / (kEpilogueWarps / 4);  // tile columns one epilogue warp owns
+    static constexpr int kBRows = kPair ? BN / 2 : BN;        // W rows this CTA holds per k-block
+    static constexpr uint32_t kBytesB16 = kBRows * BK * 2;
+    static constexpr int kTileM = kPair ? 2 * BM : BM;        // output rows per work item
     static constexpr int kDequantWarps = kBInt8 ? 8 : 0;
     static constexpr int kFirstEpilogueWarp = 4 + kDequantWarps;
     static constexpr int kThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
@@ -71,10 +91,14 @@ struct Cfg {
     static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
 };
 
-template <bool kBInt8>
-__global__ void __launch_bounds__(Cfg<kBInt8>::kThreads, 1)
+template <bool kBInt8, bool kPair>
+__global__ void __launch_bounds__(Cfg<kBInt8, kPair>::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, GemmParams p) {
-    using C = Cfg<kBInt8>;
+    using C = Cfg<kBInt8, kPair>;
+    constexpr int kStagesAB = C::kStagesAB;
+    constexpr int kEpilogueWarps = C::kEpilogueWarps;
+    constexpr int kWarpCols = C::kWarpCols;
+    constexpr uint32_t kBytesB16 = C::kBytesB16;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -101,10 +125,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         m_rows = v < p.m_alloc ? v : p.m_alloc;
         if (m_rows < 0) m_rows = 0;
     }
-    const int m_tiles = (m_rows + BM - 1) / BM;
+    const int m_tiles = (m_rows + C::kTileM - 1) / C::kTileM;
     const int n_tiles = (p.n + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
     const int num_kb = (p.k + BK - 1) / BK;
+    // work distribution: one worker = one CTA, or one CTA pair (cluster of 2: blocks 2i and 2i + 1)
+    const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
+    const int worker = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int num_workers = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int m_off = (int)cta_rank * BM;  // this CTA's rows inside the work item
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -118,18 +147,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(acc_full(s), 1);
-            mbar_init(acc_empty(s), kEpilogueWarps);
+            mbar_init(acc_empty(s), kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
         }
         mbar_fence_init();
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
     }
     if (warp == 2) {
-        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
-        tmem_relinquish();
+        if (kPair) {
+            tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if (kPair) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -138,41 +172,66 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int m0 = (tile / n_tiles) * BM;
+#ifdef EOSB_GEMM_TIMING
+            long long tlast__ = clock64();
+            long long gacc__[4] = {0, 0, 0, 0};
+            const bool tm__ = blockIdx.x == 0;
+#endif
+            for (int tile = worker; ok && tile < total_tiles; tile += num_workers) {
+                const int m0 = (tile / n_tiles) * C::kTileM + m_off;
                 const int n0 = (tile % n_tiles) * BN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % kStagesAB;
                     const uint32_t ph = (it / kStagesAB) & 1u;
+#ifdef EOSB_GEMM_TIMING
+                    if (tm__) GMARK(9);
+#endif
                     if (!mbar_wait(empty_ab(s), ph ^ 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
-                    mbar_arrive_expect_tx(full_ab(s), kBytesA + (kBInt8 ? kBytesB8 : kBytesB16));
-                    tma_load_2d(base + C::kOffA + s * kBytesA, &tm_a, kb * BK, m0, full_ab(s));
-                    if (kBInt8)
-                        tma_load_2d(base + C::kOffB8 + s * kBytesB8, &tm_b, kb * BK, n0, full_ab(s));
-                    else
-                        tma_load_2d(base + C::kOffB16 + s * kBytesB16, &tm_b, kb * BK, n0, full_ab(s));
+#ifdef EOSB_GEMM_TIMING
+                    if (tm__) GMARK(8);
+#endif
+                    if (kPair) {
+                        // both CTAs' bytes are counted on the leader's barrier, which the leader arms
+                        const uint32_t full_leader = mapa_shared(full_ab(s), 0);
+                        if (cta_rank == 0) mbar_arrive_expect_tx(full_ab(s), 2 * (kBytesA + kBytesB16));
+                        tma_load_2d_pair(base + C::kOffA + s * kBytesA, &tm_a, kb * BK, m0, full_leader);
+                        tma_load_2d_pair(base + C::kOffB16 + s * kBytesB16, &tm_b, kb * BK, n0 + (int)cta_rank * C::kBRows,
+                                         full_leader);
+                    } else {
+                        mbar_arrive_expect_tx(full_ab(s), kBytesA + (kBInt8 ? kBytesB8 : kBytesB16));
+                        tma_load_2d(base + C::kOffA + s * kBytesA, &tm_a, kb * BK, m0, full_ab(s));
+                        if (kBInt8)
+                            tma_load_2d(base + C::kOffB8 + s * kBytesB8, &tm_b, kb * BK, n0, full_ab(s));
+                        else
+                            tma_load_2d(base + C::kOffB16 + s * kBytesB16, &tm_b, kb * BK, n0, full_ab(s));
+                    }
                 }
             }
+#ifdef EOSB_GEMM_TIMING
+            GFLUSH(8);
+#endif
         }
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_f16(BM, BN);
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16(C::kTileM, BN);
             uint32_t it = 0;
             uint32_t t = 0;
             bool ok = true;
 #ifdef EOSB_GEMM_TIMING
             long long tlast__ = clock64();
+            long long gacc__[4] = {0, 0, 0, 0};
             const bool tm__ = blockIdx.x == 0;
 #endif
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
+            for (int tile = worker; ok && tile < total_tiles; tile += num_workers, ++t) {
                 const uint32_t ab = t & 1u;
                 const uint32_t aph = (t >> 1) & 1u;
                 if (!mbar_wait(acc_empty(ab), aph ^ 1u, abort_flag)) break;
+                if (kPair) fence_acq_rel_cluster();  // half of the arrivals came from the partner CTA
                 tc_fence_after();
 #ifdef EOSB_GEMM_TIMING
                 if (tm__) GMARK(0);
@@ -202,20 +261,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #ifdef EOSB_GEMM_TIMING
                     if (tm__) GMARK(1);
 #endif
-                    const uint32_t a_addr = base + C::kOffA + s * kBytesA;
+                    const uint32_t a_lo = umma_desc_sw128_lo(base + C::kOffA + s * kBytesA);
+                    const uint32_t b_lo = umma_desc_sw128_lo(b_addr);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        umma_f16(d_tmem, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32), idesc,
-                                 (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; ++k) {  // 32 bytes along K per step = 2 in descriptor units
+                        if (kPair)
+                            umma_f16_pair_split(d_tmem, a_lo + k * 2, kDescSw128Hi, b_lo + k * 2, kDescSw128Hi, idesc,
+                                                (kb > 0 || k > 0) ? 1u : 0u);
+                        else
+                            umma_f16_split(d_tmem, a_lo + k * 2, kDescSw128Hi, b_lo + k * 2, kDescSw128Hi, idesc,
+                                           (kb > 0 || k > 0) ? 1u : 0u);
                     }
-                    umma_commit(empty_ab(s));
+                    if (kPair) umma_commit_pair(empty_ab(s), 3); else umma_commit(empty_ab(s));
                     if (kBInt8) umma_commit(empty_b16(c));
 #ifdef EOSB_GEMM_TIMING
                     if (tm__) GMARK(2);
 #endif
                 }
-                if (ok) umma_commit(acc_full(ab));
+                if (ok) {
+                    if (kPair) umma_commit_pair(acc_full(ab), 3); else umma_commit(acc_full(ab));
+                }
             }
+#ifdef EOSB_GEMM_TIMING
+            GFLUSH(0);
+#endif
         }
         __syncwarp();
     } else if (kBInt8 && warp >= 4 && warp < C::kFirstEpilogueWarp) {
@@ -225,7 +294,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const uint32_t bias1152 = 0x64806480u;  // half2(1152, 1152) = 1024 + 128
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        for (int tile = worker; ok && tile < total_tiles; tile += num_workers) {
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const int s = it % kStagesAB;
                 const uint32_t ph = (it / kStagesAB) & 1u;
@@ -274,29 +343,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int ew = warp - C::kFirstEpilogueWarp;               // 0..7
         const int etid = threadIdx.x - C::kFirstEpilogueWarp * 32;  // 0..255
         const int wrow0 = (warp & 3) * 32;                          // this warp's rows inside the tile
-        const int ehalf = ew >> 2;                                  // which 128 columns of the tile
+        const int epart = ew >> 2;                                  // which kWarpCols columns of the tile
         const uint32_t lane_base = (uint32_t)wrow0;
         uint8_t* slab = sm + C::kOffSlab + ew * kSlabBytes;         // [32 rows][8 x 16 B], chunk index ^ (row & 7)
 #ifdef EOSB_GEMM_TIMING
         long long tlast__ = clock64();
+        long long gacc__[4] = {0, 0, 0, 0};
         const bool tm__ = blockIdx.x == 0 && etid == 0;
 #endif
         uint32_t t = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
-            const int m0 = (tile / n_tiles) * BM;
+        const uint32_t acc_empty_leader0 = kPair ? mapa_shared(acc_empty(0), 0) : acc_empty(0);
+        const uint32_t acc_empty_leader1 = kPair ? mapa_shared(acc_empty(1), 0) : acc_empty(1);
+        // (scale, bias) of output column n; one column of the 256-wide tile per epilogue thread
+        static_assert(kEpilogueWarps * 32 >= BN, "one epilogue thread per tile column");
+        auto fetch_scale_bias = [&](int n) {
+            float2 v = make_float2(1.0f, 0.0f);
+            if (etid < BN && n < p.n) {
+                if (p.scale != nullptr) v.x = __ldg(p.scale + n);
+                if (p.bias != nullptr) v.y = __ldg(p.bias + n);
+            }
+            return v;
+        };
+        float2 sb_next = make_float2(1.0f, 0.0f);
+        if (worker < total_tiles) sb_next = fetch_scale_bias((worker % n_tiles) * BN + etid);
+        for (int tile = worker; tile < total_tiles; tile += num_workers, ++t) {
+            const int m0 = (tile / n_tiles) * C::kTileM + m_off;
             const int n0 = (tile % n_tiles) * BN;
             const uint32_t ab = t & 1u;
             const uint32_t aph = (t >> 1) & 1u;
+            // this tile's column constants were requested one tile ago; request the next tile's now
             float2* sb = scale_bias + ab * BN;
-            for (int cidx = etid; cidx < BN; cidx += kEpilogueWarps * 32) {
-                const int n = n0 + cidx;
-                float2 v = make_float2(1.0f, 0.0f);
-                if (n < p.n) {
-                    if (p.scale != nullptr) v.x = __ldg(p.scale + n);
-                    if (p.bias != nullptr) v.y = __ldg(p.bias + n);
-                }
-                sb[cidx] = v;
-            }
+            if (etid < BN) sb[etid] = sb_next;
+            if (tile + num_workers < total_tiles) sb_next = fetch_scale_bias(((tile + num_workers) % n_tiles) * BN + etid);
             const int m = m0 + wrow0 + lane;  // this thread's accumulator row
             const bool row_ok = m < m_rows;
             const int rows_here = m_rows - (m0 + wrow0);  // rows of this warp's block that exist (may exceed 32)
@@ -307,13 +385,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             // slab layout: row pitch 64 B, 16-byte chunk c of row r at position c ^ ((r >> 1) & 3)
             const int crow = lane >> 2, cchunk = lane & 3;
             const bool residual = p.mode == kEpiBiasResidual;
-            constexpr int kSlabs = 128 / kSlabCols;
+            constexpr int kSlabs = kWarpCols / kSlabCols;
 
             // residual of the next slab is requested one slab ahead (the first one before the accumulator
             // is even complete)
             uint4 res_in[4];
             auto residual_fetch = [&](int slab_idx) {
-                const int col = n0 + ehalf * 128 + slab_idx * kSlabCols;
+                const int col = n0 + epart * kWarpCols + slab_idx * kSlabCols;
                 if (slab_idx >= kSlabs || col + kSlabCols > p.n) return;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -332,15 +410,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (!mbar_wait(acc_full(ab), aph, abort_flag)) break;
             tc_fence_after();
 #ifdef EOSB_GEMM_TIMING
-            if (tm__) GMARK(5);
+            if (tm__) GMARK(4);
 #endif
 
             uint32_t r_next[16];
             __syncwarp();
-            tmem_ld_32x16(taddr + ehalf * 128, r_next);
+            tmem_ld_32x16(taddr + epart * kWarpCols, r_next);
 #pragma unroll 1
             for (int sl = 0; sl < kSlabs; ++sl) {
-                const int col0 = ehalf * 128 + sl * kSlabCols;  // first column of the slab inside the tile
+                const int col0 = epart * kWarpCols + sl * kSlabCols;  // first column of the slab inside the tile
                 const int ncol0 = n0 + col0;
                 if (ncol0 >= p.n) {
                     tmem_ld_wait();
@@ -362,6 +440,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     __syncwarp();
                     residual_fetch(sl + 1);
                 }
+#ifdef EOSB_GEMM_TIMING
+                if (tm__) GMARK(5);
+#endif
 #pragma unroll
                 for (int ch = 0; ch < kSlabCols / 16; ++ch) {
                     uint32_t r[16];
@@ -370,7 +451,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     for (int j = 0; j < 16; ++j) r[j] = r_next[j];
                     {
                         const int next_col = col0 + (ch + 1) * 16;  // next chunk, possibly of the next slab
-                        if (next_col < (ehalf + 1) * 128) {
+                        if (next_col < (epart + 1) * kWarpCols) {
                             __syncwarp();
                             tmem_ld_32x16(taddr + next_col, r_next);
                         }
@@ -384,7 +465,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                     if (p.mode == kEpiBiasGeluErf) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = gelu_erf_fast(v[j]);
+                        for (int j = 0; j < 16; j += 2) gelu_erf_fast2(v[j], v[j + 1]);
                     } else if (p.mode == kEpiBiasGeluTanh) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
@@ -428,6 +509,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         }
                     }
                 }
+#ifdef EOSB_GEMM_TIMING
+                if (tm__) GMARK(6);
+#endif
                 if (fast) {
                     __syncwarp();
 #pragma unroll
@@ -439,22 +523,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                     __syncwarp();
                 }
+#ifdef EOSB_GEMM_TIMING
+                if (tm__) GMARK(7);
+#endif
             }
 #ifdef EOSB_GEMM_TIMING
-            if (tm__) GMARK(6);
+            if (tm__) GMARK(7);
 #endif
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty(ab));
+            if (lane == 0) {
+                if (kPair) mbar_arrive_cluster(ab ? acc_empty_leader1 : acc_empty_leader0); else mbar_arrive(acc_empty(ab));
+            }
         }
+#ifdef EOSB_GEMM_TIMING
+        GFLUSH(4);
+#endif
     }
 
     // ---------------------------------------------------------------- teardown
+    // (pair mode: no CTA may leave while its partner can still read its shared memory, arrive on
+    // its barriers or use its tensor memory)
     tc_fence_before();
-    __syncthreads();
+    if (kPair) cluster_sync_all(); else __syncthreads();
     if (warp == 2) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, kTmemCols);
+        if (kPair) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
     }
     if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, kStatusPipelineTimeout);
 }
@@ -470,11 +564,52 @@ extern "C" __attribute__((visibility("default"))) int eos_b200_debug_gemm_timing
 }
 #endif
 
+namespace {
+int g_pair_clusters = -1;  // CTA pairs that can be resident at once; 0 = pair mode unavailable
+
+cudaLaunchConfig_t pair_launch_config(int grid, cudaStream_t stream, cudaLaunchAttribute* attr) {
+    attr->id = cudaLaunchAttributeClusterDimension;
+    attr->val.clusterDim.x = 2;
+    attr->val.clusterDim.y = 1;
+    attr->val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(Cfg<false, true>::kThreads);
+    cfg.dynamicSmemBytes = Cfg<false, true>::kSmemBytes;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cfg;
+}
+}  // namespace
+
 std::string gemm_global_init() {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<true, false>::kSmemBytes);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::kSmemBytes);
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<false, false>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<false, true>::kSmemBytes);
     if (e != cudaSuccess) return std::string("cudaFuncSetAttribute(gemm_tc_kernel): ") + cudaGetErrorString(e);
+    if (g_pair_clusters < 0) {
+        g_pair_clusters = 0;
+        const char* on = getenv("EOS_B200_GEMM_CTA_PAIR");
+        if (on != nullptr && on[0] != '\0' && on[0] != '0') {
+            int dev = 0, sms = 0, clusters = 0;
+            cudaLaunchAttribute attr;
+            if (cudaGetDevice(&dev) == cudaSuccess &&
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms >= 2) {
+                cudaLaunchConfig_t cfg = pair_launch_config(sms & ~1, nullptr, &attr);
+                if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<false, true>, &cfg) == cudaSuccess)
+                    g_pair_clusters = clusters;
+                else
+                    (void)cudaGetLastError();
+            }
+        }
+        if (getenv("EOS_B200_DEBUG") != nullptr) fprintf(stderr, "eos_b200: resident CTA pairs for the GEMM: %d\n", g_pair_clusters);
+    }
     return "";
 }
 
@@ -484,6 +619,7 @@ std::string gemm_make_plan(GemmPlan* plan, const __half* a, int lda, const void*
     if (params.ldo % 8 != 0) return "gemm: output row stride must be a multiple of 8 elements";
     if (params.mode == kEpiBiasResidual && (params.residual == nullptr || params.ldr % 8 != 0))
         return "gemm: residual epilogue needs a residual pointer with a row stride that is a multiple of 8";
+    const bool pair = !b_int8 && g_pair_clusters > 0;
     std::string err = encode_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)params.k,
                                 (uint64_t)params.m_alloc, (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!err.empty()) return "gemm A: " + err;
@@ -492,22 +628,36 @@ std::string gemm_make_plan(GemmPlan* plan, const __half* a, int lda, const void*
                         (uint64_t)ldw, BK, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
     else
         err = encode_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w, (uint64_t)params.k, (uint64_t)params.n,
-                        (uint64_t)ldw * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+                        (uint64_t)ldw * 2, BK, pair ? BN / 2 : BN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!err.empty()) return "gemm W: " + err;
     plan->p = params;
     plan->b_int8 = b_int8;
-    const int m_tiles = (params.m_alloc + BM - 1) / BM;
+    plan->pair = pair;
+    const int tile_m = pair ? 2 * BM : BM;
+    const int m_tiles = (params.m_alloc + tile_m - 1) / tile_m;
     const int n_tiles = (params.n + BN - 1) / BN;
     const long long tiles = (long long)m_tiles * n_tiles;
-    plan->grid = (int)(tiles < sm_count ? tiles : sm_count);
+    if (pair) {
+        int workers = sm_count / 2 < g_pair_clusters ? sm_count / 2 : g_pair_clusters;
+        plan->grid = 2 * (int)(tiles < workers ? tiles : workers);
+    } else {
+        plan->grid = (int)(tiles < sm_count ? tiles : sm_count);
+    }
     return "";
 }
 
 void gemm_launch(const GemmPlan& plan, cudaStream_t stream) {
-    if (plan.b_int8)
-        gemm_tc_kernel<true><<<plan.grid, Cfg<true>::kThreads, Cfg<true>::kSmemBytes, stream>>>(plan.tm_a, plan.tm_b, plan.p);
-    else
-        gemm_tc_kernel<false><<<plan.grid, Cfg<false>::kThreads, Cfg<false>::kSmemBytes, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+    if (plan.pair) {
+        cudaLaunchAttribute attr;
+        cudaLaunchConfig_t cfg = pair_launch_config(plan.grid, stream, &attr);
+        cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true>, plan.tm_a, plan.tm_b, plan.p);
+    } else if (plan.b_int8) {
+        gemm_tc_kernel<true, false><<<plan.grid, Cfg<true, false>::kThreads, Cfg<true, false>::kSmemBytes, stream>>>(
+            plan.tm_a, plan.tm_b, plan.p);
+    } else {
+        gemm_tc_kernel<false, false><<<plan.grid, Cfg<false, false>::kThreads, Cfg<false, false>::kSmemBytes, stream>>>(
+            plan.tm_a, plan.tm_b, plan.p);
+    }
 }
 
 }  // namespace eosb

@@ -38,6 +38,7 @@ struct GemmPlan {
     GemmParams p;
     int grid;
     bool b_int8;
+    bool pair;  // two CTAs of a cluster per 256x256 tile (f16 weights)
 };
 
 // Builds the TMA descriptors for out[m, n] = A[m, k] (f16, row stride lda elements) x W[n, k]^T.
@@ -49,7 +50,9 @@ std::string gemm_make_plan(GemmPlan* plan, const __half* a, int lda, const void*
 
 void gemm_launch(const GemmPlan& plan, cudaStream_t stream);
 
-// One-time per process: raises the dynamic shared memory limit of the kernels.
+// One-time per process: raises the dynamic shared memory limit of the kernels and asks the driver how
+// many CTA pairs fit on the device when environment EOS_B200_GEMM_CTA_PAIR=1 selects the CTA-pair
+// kernel for f16 weights (default: one CTA per tile).
 std::string gemm_global_init();
 
 }  // namespace eosb
