@@ -16,9 +16,12 @@
 //                the P V phase of the current one and two sub-items are always in flight.
 //                The row sums l = P 1 come out of the same MMA: its B operand is [V | ones] (N = 80), so
 //                they are the fp32 sums of exactly the f16 probabilities that multiply V.
-//   warps 4-11   softmax (thread = query row, two warps per row split the columns): pass A reads all
-//                S tiles for the row maximum, pass B re-reads them, writes P = exp2(s - m) (packed f16 ex2)
-//                into the 128B-swizzled K-major layout the second MMA consumes; finally O / l -> f16 -> global.
+//   warps 4-19   softmax (thread = query row, four warps per row split the columns of every tile): pass A
+//                reads all S tiles for the row maximum (exchanged through shared memory), pass B re-reads
+//                them, writes P = exp2(s - m) (packed f16 ex2) into the 128B-swizzled K-major layout the
+//                second MMA consumes; finally O / l -> f16 -> global, 32 bytes (one sector) per thread.
+//                Warps whose 32 query rows are padding of a sequence's last query tile only keep the
+//                barrier protocol.
 // All scores of a sub-item are resident in TMEM before any probability is formed, so O is never
 // rescaled in place; a sequence longer than 256 keys is two sub-items whose partial (O, m, l) are
 // merged in registers.  All mbarrier waits are bounded (abort flag + status word).
@@ -31,7 +34,7 @@ namespace eosb {
 
 #ifdef EOSB_ATTN_TIMING
 __device__ long long g_attn_timing[16];
-__device__ long long g_attn_trace[2][2048];
+__device__ long long g_attn_trace[3][2048];
 #define TMARK(i) do { long long now__ = clock64(); tacc__[i] += now__ - tlast__; tlast__ = now__; if (blockIdx.x == 0 && threadIdx.x == 128 && tcnt__ < 2048) g_attn_trace[0][tcnt__++] = (now__ << 8) | (i); } while (0)
 #else
 #define TMARK(i) do { } while (0)
@@ -44,7 +47,11 @@ __device__ long long g_attn_trace[2][2048];
 
 namespace {
 
-constexpr int kAtThreads = 384;
+constexpr int kParts = 4;                       // softmax warps per TMEM lane quarter (column parts of a row)
+constexpr int kSoftmaxWarps = 4 * kParts;
+constexpr int kPartCols = 128 / kParts;          // S columns of one tile per softmax thread
+constexpr int kPartOut = 64 / kParts;            // O columns per softmax thread
+constexpr int kAtThreads = (4 + kSoftmaxWarps) * 32;
 constexpr int kQStages = 2;
 constexpr int kKvStages = 6;
 constexpr uint32_t kTileBytes = 128 * 64 * 2;   // 16 KB: Q, K_j or V_j
@@ -53,8 +60,8 @@ constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffKv = kOffQ + kQStages * kTileBytes;
 constexpr uint32_t kOffP = kOffKv + kKvStages * kTileBytes;
 constexpr uint32_t kOffOnes = kOffP + 2 * kPBytes;              // 16 x 64 f16 of 1.0: B operand of the row-sum MMA
-constexpr uint32_t kOffRed = kOffOnes + 2048;                   // 2 x 128 floats: row max exchange
-constexpr uint32_t kOffBars = kOffRed + 2 * 128 * 4;
+constexpr uint32_t kOffRed = kOffOnes + 2048;                   // 2 buffers x kParts x 128 floats: row max exchange
+constexpr uint32_t kOffBars = kOffRed + 2 * kParts * 128 * 4;
 constexpr uint32_t kNumBars = 2 * kQStages + 2 * kKvStages + 4 + 2 + 2 + 2 + 2;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
 constexpr uint32_t kAtSmemBytes = kOffMisc + 16 + 1024;
@@ -141,11 +148,42 @@ struct Walker {
 // distance from one 64-wide MN block to the next (used when N > 64).  Its descriptor has the same
 // high half as the K-major one.
 
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[16]) { tmem_ld_32x16(taddr, v); }
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[32]) { tmem_ld_32x32(taddr, v); }
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[64]) {
+    tmem_ld_32x32(taddr, reinterpret_cast<uint32_t(&)[32]>(v[0]));
+    tmem_ld_32x32(taddr + 32, reinterpret_cast<uint32_t(&)[32]>(v[32]));
+}
+
+// 2^x for x <= 0 on the FMA and integer pipes (no MUFU): round-to-nearest split x = n + f with
+// |f| <= 0.5 by the 1.5 * 2^23 trick, cubic for 2^f (maximum relative error 7.5e-5, a third of
+// half an f16 ulp), n added to the exponent field.  x below -125 (masked keys: -inf) gives 2^-125,
+// which rounds to 0 in f16.
+__device__ __forceinline__ float exp2_fma(float x) {
+    x = fmaxf(x, -125.0f);
+    const float t = x + 12582912.0f;
+    const float f = x - (t - 12582912.0f);
+    float p = fmaf(0.05517132207751274f, f, 0.24261054396629333f);
+    p = fmaf(p, f, 0.6932609677314758f);
+    p = fmaf(p, f, 0.9999281167984009f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+// A pair of probabilities as packed f16.  Every third pair is computed on the FMA pipe instead of the
+// MUFU pipe (16 ex2 per clock per SM): measured 1.4% faster than all-MUFU, every second pair is slower.
+__device__ __forceinline__ uint32_t exp2_pair_fma(float x0, float x1) {
+    __half2 h = __floats2half2_rn(exp2_fma(x0), exp2_fma(x1));
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
 __device__ __forceinline__ uint32_t ex2_f16x2(float x0, float x1) {
     __half2 h = __floats2half2_rn(x0, x1);
     uint32_t hx = *reinterpret_cast<uint32_t*>(&h), px;
     asm("ex2.approx.f16x2 %0, %1;" : "=r"(px) : "r"(hx));
     return px;
+}
+// pair_idx is a compile-time constant after unrolling
+__device__ __forceinline__ uint32_t exp2_pair(int pair_idx, float x0, float x1) {
+    return (pair_idx % 3) == 2 ? exp2_pair_fma(x0, x1) : ex2_f16x2(x0, x1);
 }
 
 __global__ void __launch_bounds__(kAtThreads, 1)
@@ -189,10 +227,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         for (int h = 0; h < 2; ++h) {
             mbar_init(s_full(h, 0), 1);
             mbar_init(s_full(h, 1), 1);
-            mbar_init(p_full(h), 8);
+            mbar_init(p_full(h), kSoftmaxWarps);
             mbar_init(p_empty(h), 1);
             mbar_init(o_full(h), 1);
-            mbar_init(half_free(h), 8);
+            mbar_init(half_free(h), kSoftmaxWarps);
         }
         mbar_fence_init();
         tma_prefetch_desc(&tm_qkv);
@@ -228,19 +266,43 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                 for (int t = 0; t < wk.nt(); ++t, ++kvc) {
                     const int s = kvc % kKvStages;
                     if (!mbar_wait(kv_empty(s), ((kvc / kKvStages) & 1u) ^ 1u, abort_flag)) return false;
+#ifdef EOSB_ATTN_TIMING
+                    if (blockIdx.x == 0 && kvc < 2048) g_attn_trace[2][kvc] = (clock64() << 8) | 20;
+#endif
                     mbar_arrive_expect_tx(kv_full(s), kTileBytes);
                     tma_load_2d(base + kOffKv + s * kTileBytes, &tm_qkv, x, wk.wi.row0 + (wk.tile0() + t) * 128, kv_full(s));
                 }
                 return true;
             };
-            Walker cur, nxt;
+            // K/V tiles mostly come from HBM (one layer's q|k|v rows exceed L2), and the ring only holds about
+            // one and a half sub-items: a third walker runs kL2Ahead sub-items in front of the loads and asks
+            // L2 for those tiles, so that the ring's loads are L2 hits
+            auto prefetch_l2 = [&](const Walker& wk) {
+                if (wk.first_sub()) tma_prefetch_l2_2d(&tm_qkv, wk.wi.head * 64, wk.wi.row0 + wk.wi.q0);
+                for (int t = 0; t < wk.nt(); ++t) {
+                    const int y = wk.wi.row0 + (wk.tile0() + t) * 128;
+                    tma_prefetch_l2_2d(&tm_qkv, hidden + wk.wi.head * 64, y);
+                    tma_prefetch_l2_2d(&tm_qkv, 2 * hidden + wk.wi.head * 64, y);
+                }
+            };
+            constexpr int kL2Ahead = 2;
+            Walker cur, nxt, far;
             cur.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info);
             nxt = cur;
             if (cur.valid()) {
                 ok = load_q(cur) && load_kv(cur, 1);
                 nxt.next();
             }
+            far = nxt;
+            for (int i = 0; i < kL2Ahead && far.valid(); ++i) {
+                prefetch_l2(far);
+                far.next();
+            }
             while (ok && cur.valid()) {
+                if (far.valid()) {
+                    prefetch_l2(far);
+                    far.next();
+                }
                 if (nxt.valid()) {
                     if (nxt.first_sub()) ok = load_q(nxt);
                     ok = ok && load_kv(nxt, 1);
@@ -349,43 +411,52 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         // ------------------------------------------------------------ softmax + epilogue
         const int w8 = warp - 4;
         const int quarter = warp & 3;          // TMEM lane quarter this warp may access
-        const int half = w8 >> 2;              // which 64 columns of every 128-column tile
+        const int part = w8 >> 2;              // which kPartCols columns of every 128-column tile
         const int r = quarter * 32 + lane;     // query row inside the tile
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const float sl2 = 0.125f * 1.4426950408889634f;  // 1/sqrt(64) * log2(e)
-        uint32_t pc = 0, o_cnt[2] = {0, 0}, s_cnt[2][2] = {{0, 0}, {0, 0}};
+        uint32_t pc = 0;
+        uint32_t par = 0;  // expected phase parities: bit h*2+t for s_full(h, t), bit 4+h for o_full(h)
         bool ok = true;
-        float part_o[32], part_m = 0.f, part_l = 0.f;  // first half of a two-part item, kept across sub-items
+        float part_o[kPartOut], part_m = 0.f, part_l = 0.f;  // first half of a two-part item, kept across sub-items
 
+#ifdef EOSB_ATTN_TIMING
+        long long tlast__ = clock64();
+        long long tacc__[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int tcnt__ = 0;
+#endif
         // epilogue of sub-item number n (deferred by one sub-item so that its PV MMAs overlap the next
         // sub-item's softmax): O / l, or the merge of two partial results
         auto epilogue = [&](const Walker& wk, uint32_t n, float ms_n) -> bool {
             const int h = n & 1u;
             const int qrow = wk.wi.q0 + r;
-            __half* out = ctx + (size_t)(wk.wi.row0 + qrow) * hidden + wk.wi.head * 64 + half * 32;
-            float o[32], l = 0.f;
+            __half* out = ctx + (size_t)(wk.wi.row0 + qrow) * hidden + wk.wi.head * 64 + part * kPartOut;
+            float o[kPartOut], l = 0.f;
+#pragma unroll
+            for (int e = 0; e < kPartOut; ++e) o[e] = 0.f;
             if (wk.nt() > 0) {
-                if (!mbar_wait(o_full(h), o_cnt[h] & 1u, abort_flag)) return false;
-                ++o_cnt[h];
+                if (!mbar_wait(o_full(h), (par >> (4 + h)) & 1u, abort_flag)) return false;
+                par ^= 1u << (4 + h);
                 tc_fence_after();
-                uint32_t v[32], lv[16];
-                __syncwarp();
-                tmem_ld_32x32(tmem_base + lane_addr + h * 256 + half * 32, v);
-                tmem_ld_32x16(tmem_base + lane_addr + h * 256 + 64, lv);
-                tmem_ld_wait();
+                TMARK(6);
+                if (wk.wi.q0 + quarter * 32 < wk.wi.nrows) {  // else: a warp of padding rows
+                    uint32_t v[kPartOut], lv[1];
+                    __syncwarp();
+                    tmem_ld_cols(tmem_base + lane_addr + h * 256 + part * kPartOut, v);
+                    tmem_ld_32x1(tmem_base + lane_addr + h * 256 + 64, lv);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int e = 0; e < 32; ++e) o[e] = __uint_as_float(v[e]);
-                l = __uint_as_float(lv[0]);
-            } else {
-#pragma unroll
-                for (int e = 0; e < 32; ++e) o[e] = 0.f;
+                    for (int e = 0; e < kPartOut; ++e) o[e] = __uint_as_float(v[e]);
+                    l = __uint_as_float(lv[0]);
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(half_free(h));
+            TMARK(7);
             if (wk.nsub() == 2 && wk.first_sub()) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) part_o[e] = o[e];
+                for (int e = 0; e < kPartOut; ++e) part_o[e] = o[e];
                 part_m = ms_n;
                 part_l = l;
                 return true;
@@ -394,21 +465,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                 const float m = fmaxf(part_m, ms_n);
                 const float a = exp2f(part_m - m), b = exp2f(ms_n - m);
 #pragma unroll
-                for (int e = 0; e < 32; ++e) o[e] = part_o[e] * a + o[e] * b;
+                for (int e = 0; e < kPartOut; ++e) o[e] = part_o[e] * a + o[e] * b;
                 l = part_l * a + l * b;
             }
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             if (qrow < wk.wi.nrows) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint4 ov;
-                    uint32_t* ow = reinterpret_cast<uint32_t*>(&ov);
+                for (int q = 0; q < kPartOut / 16; ++q) {  // 32 bytes (one sector) per store
+                    uint32_t ow[8];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        __half2 hh = __floats2half2_rn(o[q * 8 + 2 * e] * inv, o[q * 8 + 2 * e + 1] * inv);
+                    for (int e = 0; e < 8; ++e) {
+                        __half2 hh = __floats2half2_rn(o[q * 16 + 2 * e] * inv, o[q * 16 + 2 * e + 1] * inv);
                         ow[e] = *reinterpret_cast<uint32_t*>(&hh);
                     }
-                    *reinterpret_cast<uint4*>(out + q * 8) = ov;
+                    st_global_v8(out + q * 16, ow);
                 }
             }
             return true;
@@ -419,54 +489,54 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         prev = cur;
         uint32_t n = 0;
         float ms_prev = 0.f;
-#ifdef EOSB_ATTN_TIMING
-        long long tlast__ = clock64();
-        long long tacc__[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        int tcnt__ = 0;
-#endif
         bool have_prev = false;
         while (ok && cur.valid()) {
             const int h = n & 1u;
             const int nt = cur.nt();
             const int key0 = cur.tile0() * 128;           // first key of this sub-item
             const int nkeys = cur.wi.nkeys;
+            // a warp whose 32 query rows are all padding of the last query tile keeps the barrier protocol
+            // but computes nothing (its P rows and O rows are never used)
+            const bool live = cur.wi.q0 + quarter * 32 < cur.wi.nrows;
             float ms = 0.f;
             if (nt > 0) {
                 // pass A: row maximum over the visible keys of this sub-item
                 float mx = -INFINITY;
                 for (int t = 0; t < nt; ++t) {
-                    if (!mbar_wait(s_full(h, t), s_cnt[h][t] & 1u, abort_flag)) {
+                    if (!mbar_wait(s_full(h, t), (par >> (h * 2 + t)) & 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
-                    ++s_cnt[h][t];
+                    par ^= 1u << (h * 2 + t);
                     tc_fence_after();
                     TMARK(0);
-                    const int col0 = key0 + t * 128 + half * 64;   // key index of this thread's first column
-                    if (col0 >= nkeys) continue;
-                    uint32_t v0[32], v1[32];
+                    const int col0 = key0 + t * 128 + part * kPartCols;   // key index of this thread's first column
+                    if (col0 >= nkeys || !live) continue;
+                    uint32_t v[kPartCols];
                     __syncwarp();
-                    tmem_ld_32x32(tmem_base + lane_addr + h * 256 + t * 128 + half * 64, v0);
-                    tmem_ld_32x32(tmem_base + lane_addr + h * 256 + t * 128 + half * 64 + 32, v1);
+                    tmem_ld_cols(tmem_base + lane_addr + h * 256 + t * 128 + part * kPartCols, v);
                     tmem_ld_wait();
                     const int lim = nkeys - col0;
-                    if (lim >= 64) {
+                    if (lim >= kPartCols) {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fmaxf(__uint_as_float(v0[e]), __uint_as_float(v1[e])));
+                        for (int e = 0; e < kPartCols; e += 2)
+                            mx = fmaxf(mx, fmaxf(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
                     } else {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            if (e < lim) mx = fmaxf(mx, __uint_as_float(v0[e]));
-                            if (e + 32 < lim) mx = fmaxf(mx, __uint_as_float(v1[e]));
-                        }
+                        for (int e = 0; e < kPartCols; ++e)
+                            if (e < lim) mx = fmaxf(mx, __uint_as_float(v[e]));
                     }
                 }
                 if (!ok) break;
                 TMARK(1);
-                red[half * 128 + r] = mx;
-                named_bar_sync(2, 256);
-                mx = fmaxf(mx, red[(half ^ 1) * 128 + r]);
-                named_bar_sync(2, 256);
+                // exchange with the warps that hold the other columns of this row; the buffer alternates per
+                // sub-item, and nobody can be two sub-items ahead of a warp that has not yet read, because
+                // every sub-item has this barrier
+                float* redn = red + (n & 1u) * (kParts * 128);
+                redn[part * 128 + r] = mx;
+                named_bar_sync(2, kSoftmaxWarps * 32);
+#pragma unroll
+                for (int q = 0; q < kParts; ++q) mx = fmaxf(mx, redn[q * 128 + r]);
                 ms = mx * sl2;  // every sub-item holds at least one visible key, so mx is finite
                 TMARK(2);
                 // the previous sub-item's epilogue goes here: its P V MMAs have had pass A's time to finish,
@@ -485,43 +555,43 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                         break;
                     }
                     TMARK(3);
-                    uint8_t* prow = sm + kOffP + pb * kPBytes + half * (kPBytes / 2) + (r >> 3) * 1024 + (r & 7) * 128;
-                    const int col0 = key0 + t * 128 + half * 64;
+                    // P tile = two 128 x 64 K-major blocks; this thread's keys are kPartCols / 8 16-byte chunks of its row
+                    constexpr int kChunks = kPartCols / 8;
+                    const int key_in_tile = part * kPartCols;
+                    uint8_t* prow = sm + kOffP + pb * kPBytes + (key_in_tile >> 6) * (kPBytes / 2) + (r >> 3) * 1024 + (r & 7) * 128;
+                    const int chunk0 = (key_in_tile & 63) >> 3;
+                    const int col0 = key0 + t * 128 + key_in_tile;
                     const int lim = nkeys - col0;
-                    uint32_t packed[32];
-                    if (lim > 0) {
-                        uint32_t v0[32], v1[32];
+                    uint32_t packed[kPartCols / 2];
+                    if (!live) {
+                        // nothing to write
+                    } else if (lim > 0) {
+                        uint32_t v[kPartCols];
                         __syncwarp();
-                        tmem_ld_32x32(tmem_base + lane_addr + h * 256 + t * 128 + half * 64, v0);
-                        tmem_ld_32x32(tmem_base + lane_addr + h * 256 + t * 128 + half * 64 + 32, v1);
+                        tmem_ld_cols(tmem_base + lane_addr + h * 256 + t * 128 + key_in_tile, v);
                         tmem_ld_wait();
-                        if (lim >= 64) {
+                        if (lim >= kPartCols) {
 #pragma unroll
-                            for (int e = 0; e < 32; e += 2) {
-                                packed[e >> 1] = ex2_f16x2(fmaf(__uint_as_float(v0[e]), sl2, -ms),
-                                                           fmaf(__uint_as_float(v0[e + 1]), sl2, -ms));
-                                packed[16 + (e >> 1)] = ex2_f16x2(fmaf(__uint_as_float(v1[e]), sl2, -ms),
-                                                                  fmaf(__uint_as_float(v1[e + 1]), sl2, -ms));
-                            }
+                            for (int e = 0; e < kPartCols; e += 2)
+                                packed[e >> 1] = exp2_pair(e >> 1, fmaf(__uint_as_float(v[e]), sl2, -ms), fmaf(__uint_as_float(v[e + 1]), sl2, -ms));
                         } else {  // the sequence's last, partial tile: masked keys get exp2(-inf) = 0
 #pragma unroll
-                            for (int e = 0; e < 32; e += 2) {
-                                const float a0 = e < lim ? fmaf(__uint_as_float(v0[e]), sl2, -ms) : -INFINITY;
-                                const float a1 = e + 1 < lim ? fmaf(__uint_as_float(v0[e + 1]), sl2, -ms) : -INFINITY;
-                                const float b0 = e + 32 < lim ? fmaf(__uint_as_float(v1[e]), sl2, -ms) : -INFINITY;
-                                const float b1 = e + 33 < lim ? fmaf(__uint_as_float(v1[e + 1]), sl2, -ms) : -INFINITY;
-                                packed[e >> 1] = ex2_f16x2(a0, a1);
-                                packed[16 + (e >> 1)] = ex2_f16x2(b0, b1);
+                            for (int e = 0; e < kPartCols; e += 2) {
+                                const float a0 = e < lim ? fmaf(__uint_as_float(v[e]), sl2, -ms) : -INFINITY;
+                                const float a1 = e + 1 < lim ? fmaf(__uint_as_float(v[e + 1]), sl2, -ms) : -INFINITY;
+                                packed[e >> 1] = exp2_pair(e >> 1, a0, a1);
                             }
                         }
                     } else {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) packed[e] = 0u;
+                        for (int e = 0; e < kPartCols / 2; ++e) packed[e] = 0u;
                     }
+                    if (live) {
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        *reinterpret_cast<uint4*>(prow + ((q ^ (r & 7)) << 4)) =
-                            make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+                        for (int q = 0; q < kChunks; ++q)
+                            *reinterpret_cast<uint4*>(prow + (((chunk0 + q) ^ (r & 7)) << 4)) =
+                                make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+                    }
                     tc_fence_before();  // S columns of this half are about to be overwritten by O
                     fence_proxy_async_smem();
                     __syncwarp();
@@ -563,8 +633,8 @@ extern "C" __attribute__((visibility("default"))) int eos_b200_debug_attn_timing
     if (reset && cudaMemcpyToSymbol(g_attn_timing, zero, sizeof(zero)) != cudaSuccess) return 1;
     return 0;
 }
-extern "C" __attribute__((visibility("default"))) int eos_b200_debug_attn_trace(long long* out4096) {
-    return cudaMemcpyFromSymbol(out4096, g_attn_trace, sizeof(long long) * 4096) != cudaSuccess;
+extern "C" __attribute__((visibility("default"))) int eos_b200_debug_attn_trace(long long* out6144) {
+    return cudaMemcpyFromSymbol(out6144, g_attn_trace, sizeof(long long) * 6144) != cudaSuccess;
 }
 #endif
 

@@ -86,6 +86,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tmap,
         : "memory");
 }
 
+// Asks L2 to fetch a tile ahead of the TMA load that will bring it into shared memory.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
 // Same load issued by either CTA of a CTA pair (cta_group::2): the data lands in the issuing CTA's
 // shared memory, the byte count is credited to an mbarrier that may live in the other CTA of the
 // pair (bar is a shared::cluster address, see mapa_shared).
@@ -94,6 +98,19 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* 
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_dst), "l"(tmap), "r"(bar), "r"(x), "r"(y)
         : "memory");
+}
+
+// ---------------------------------------------------------------- 256-bit global accesses
+// One thread moves 32 contiguous bytes (a whole L2 sector) per instruction; p must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&v)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ void ld_global_v8(const void* p, uint32_t (&v)[8]) {
+    asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "l"(p));
 }
 
 // ---------------------------------------------------------------- thread-block clusters
@@ -208,6 +225,10 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// One column: thread i of the warp receives column col of TMEM lane (lane_base + i).
+__device__ __forceinline__ void tmem_ld_32x1(uint32_t taddr, uint32_t (&r)[1]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r[0]) : "r"(taddr));
+}
 // 32 lanes x 32 columns of 32-bit accumulators: thread i of the warp receives columns
 // [col, col+32) of TMEM lane (lane_base + i).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
