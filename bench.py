@@ -31,6 +31,11 @@ sys.path.insert(0, ROOT)
 ENC = dict(layers=12, hidden=768, heads=12, inter=3072, vocab=30522, max_pos=512, head_out=768)
 ENC_BATCH, ENC_TOKENS, ENC_MIN_LEN = 1024, 512, 64
 TQ = dict(dim=768, bits=4, corpus=10_000_000, queries=4096, k=100)
+# DRAM traffic measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one launch) on the small
+# cases of eos_b200/profile_cases.py, per row of the launch; the summaries are under profiles/.
+NCU_GEMM_DRAM_BYTES_PER_ROW = {"qkv": 153.05e6 / 32768, "attn_out": 122.30e6 / 32768, "ffn_up": 203.92e6 / 32768,
+                               "ffn_down": 291.71e6 / 32768}
+NCU_SCAN_DRAM_BYTES_PER_ROW = 783.74e6 / 2_000_000
 
 
 def load_peaks():
@@ -180,6 +185,7 @@ def run_ours(args, rank: int, world: int, local: int):
     import torch.distributed as dist
 
     import eos_b200
+    from eos_b200 import encoder as encoder_mod
     from eos_b200 import synth
     from eos_b200 import turboquant as tq
 
@@ -218,7 +224,8 @@ def run_ours(args, rank: int, world: int, local: int):
 
     # ------------------------------------------------------------------ encoder
     weights = synth.make_q8_encoder(seed=301, **ENC)
-    enc = eos_b200.BertEmbedder(rt, **weights)
+    wmode = encoder_mod.WEIGHTS_F16_RESIDENT if args.weight_mode == "f16_resident" else encoder_mod.WEIGHTS_Q8_SMEM_DEQUANT
+    enc = eos_b200.BertEmbedder(rt, weight_mode=wmode, **weights)
     ids, mask, lengths = synth.make_batch(ENC_BATCH, ENC_TOKENS, ENC["vocab"], ENC_MIN_LEN, ENC_TOKENS, 303 + rank)
     enc.reserve(ENC_BATCH, ENC_TOKENS)
     d_ids, d_mask = torch.from_numpy(ids).cuda(), torch.from_numpy(mask).cuda()
@@ -267,12 +274,22 @@ def run_ours(args, rank: int, world: int, local: int):
     assert abs(float(np.linalg.norm(out_host[0])) - 1.0) < 1e-3
 
     gemm_ms_step = times.gemm_ms / max(1, times.steps)
+    rows_step = int(lengths.sum())
+    gemm_launches_step = times.gemm_launches // max(1, times.steps)
+    # DRAM bytes per launch of the projection kernel: the ncu captures of the four projections of a layer
+    # (dram__bytes_read.sum + dram__bytes_write.sum at 32768 rows, profiles/gemm_tc_kernel_*.md) scaled by
+    # rows, averaged over the launches of a step; only quoted for the mode that was captured
+    traffic = None
+    if args.weight_mode == "f16_resident" and gemm_launches_step > 0:
+        traffic = sum(NCU_GEMM_DRAM_BYTES_PER_ROW.values()) * ENC["layers"] * rows_step / gemm_launches_step
     roof = {
-        "bound": "tensor", "kernel": "gemm_tc_kernel<int8 weights dequantised in shared memory>",
+        "bound": "tensor",
+        "kernel": "gemm_tc_kernel (q8 weights expanded to f16 at bind, scales in the fp32 epilogue)"
+                  if args.weight_mode == "f16_resident" else "gemm_tc_kernel (8-bit weights dequantised in shared memory)",
         "achieved": flops_gemm / (gemm_ms_step / 1e3) / 1e12 if gemm_ms_step > 0 else None,
         "peak": peaks["tflops"], "unit": "TFLOP/s", "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)",
-        "traffic": None,
-        "launches_per_step": times.gemm_launches // max(1, times.steps),
+        "traffic": traffic,
+        "launches_per_step": gemm_launches_step,
         "avg_launch_ms": times.gemm_ms / max(1, times.gemm_launches),
         "per_step_ms": {"gemm": gemm_ms_step, "attention": times.attention_ms / max(1, times.steps),
                         "layernorm": times.layernorm_ms / max(1, times.steps),
@@ -300,6 +317,29 @@ def run_ours(args, rank: int, world: int, local: int):
                          "one pass"}
         del oargs
     enc.close()
+    # the other weight mode, timed the same way on fewer steps (reported beside the headline, not as it)
+    other = None
+    if not args.skip_other_mode:
+        omode = (encoder_mod.WEIGHTS_Q8_SMEM_DEQUANT if args.weight_mode == "f16_resident"
+                 else encoder_mod.WEIGHTS_F16_RESIDENT)
+        enc2 = eos_b200.BertEmbedder(rt, weight_mode=omode, **weights)
+        for _ in range(3):
+            enc2.run_device(d_ids.data_ptr(), d_mask.data_ptr(), None, ENC_BATCH, ENC_TOKENS, d_out.data_ptr(), stream)
+        enc2.sync(stream)
+        k2 = min(K, 5)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(k2):
+            launches += enc2.run_device(d_ids.data_ptr(), d_mask.data_ptr(), None, ENC_BATCH, ENC_TOKENS,
+                                        d_out.data_ptr(), stream)
+        e1.record()
+        barrier()
+        enc2.sync(stream)
+        ms2 = max_over_ranks(e0.elapsed_time(e1)) / k2
+        other = {"weight_mode": "q8_smem_dequant" if args.weight_mode == "f16_resident" else "f16_resident",
+                 "value": ENC_BATCH * world / (ms2 / 1e3), "unit": "embeddings/s", "ms_per_step": ms2, "steps": k2}
+        enc2.close()
     del d_ids, d_mask, d_out
     torch.cuda.empty_cache()
 
@@ -314,12 +354,14 @@ def run_ours(args, rank: int, world: int, local: int):
             "metric": "q8_encoder_embeddings_per_s_T512", "value": value, "unit": "embeddings/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16 x int8->f16, fp32 accumulate", "data": "synthetic",
-            "config": workload_config(world),
+            "config": dict(workload_config(world), weight_mode=args.weight_mode),
             "e2e": {"value": e2e_value, "unit": "embeddings/s", "h2d_bytes_per_step": int(e2e_stats.uploaded_bytes),
                     "d2h_bytes_per_step": int(e2e_stats.downloaded_bytes)},
             "gpu_launches": int(launches), "roofline": roof, "clocks": clocks,
             "valid_tokens_per_step": int(lengths.sum()),
         }
+        if other is not None:
+            line["other_weight_mode"] = other
         if cpu is not None:
             line["cpu_baseline"] = cpu
         if tq_out is not None:
@@ -416,9 +458,13 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
                                f"{world} GPU(s), {nq} f16 queries, exact top-{k}, {per_pass} queries per corpus pass "
                                f"({passes} passes)", "bytes_per_vector": bytes_per_vec,
                    "merge": "none" if world == 1 else "NCCL all-gather of per-shard top-k + merge kernel"},
-        "roofline": {"bound": "hbm", "kernel": f"tq_scan_kernel<{per_pass // 8}>", "achieved": achieved,
+        "roofline": {"bound": "hbm",
+                     "kernel": "tq_scan_stream_kernel" if per_pass == 8 else f"tq_scan_kernel<{per_pass // 8}>",
+                     "achieved": achieved,
                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"] if achieved else None,
-                     "peak_source": f"{peaks['source']} (copy bandwidth)", "traffic": None,
+                     "peak_source": f"{peaks['source']} (copy bandwidth)",
+                     # ncu: 783.7 MB of DRAM traffic for a 2,000,000-row launch (profiles/tq_scan_stream_kernel_*.md)
+                     "traffic": n_local * NCU_SCAN_DRAM_BYTES_PER_ROW if per_pass == 8 else None,
                      "avg_launch_ms": scan_avg_ms, "algorithmic_bytes_per_launch": n_local * bytes_per_vec},
         "_launches": launches,
     }
@@ -459,7 +505,10 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="omit the timed CPU baseline")
     ap.add_argument("--skip-turboquant", action="store_true", help="encoder only")
     ap.add_argument("--tq-corpus", type=int, default=TQ["corpus"])
-    ap.add_argument("--tq-queries-per-pass", type=int, default=16)
+    ap.add_argument("--tq-queries-per-pass", type=int, default=8, choices=[8, 16, 32])
+    ap.add_argument("--weight-mode", default="f16_resident", choices=["f16_resident", "q8_smem"],
+                    help="how the projection kernel receives the 8-bit weights (results are bit-identical)")
+    ap.add_argument("--skip-other-mode", action="store_true", help="do not also time the other weight mode")
     ap.add_argument("--tq-steps", type=int, default=2)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -2,6 +2,8 @@
 
     python -m eos_b200.profile_cases gemm        # projection kernel, 32768 x 768 -> 3072, erf-GELU epilogue
     python -m eos_b200.profile_cases gemm_res    # 32768 x 3072 -> 768 with residual epilogue
+    python -m eos_b200.profile_cases gemm_f16w / gemm_res_f16w / gemm_qkv_f16w / gemm_attn_out_f16w
+                                                 # the four projections of a layer, weights resident as f16
     python -m eos_b200.profile_cases scan        # TurboQuant scan, 2,000,000 x 768 4-bit codes (776 MB), 8 / 16 / 32 queries per pass
     python -m eos_b200.profile_cases attention   # 2-layer encoder forward, 128 x 512 tokens (attention + LN kernels)
 
@@ -14,7 +16,7 @@ import sys
 import numpy as np
 
 
-def case_gemm(residual: bool = False, weight_mode: int = 0, rows: int = 32768, kn=None) -> None:
+def case_gemm(residual: bool = False, weight_mode: int = 0, rows: int = 32768, kn=None, epilogue=None) -> None:
     import eos_b200
     from eos_b200 import synth
     rt = eos_b200.Runtime(0)
@@ -26,7 +28,8 @@ def case_gemm(residual: bool = False, weight_mode: int = 0, rows: int = 32768, k
     res = rng.standard_normal((rows, n), dtype=np.float32) if residual else None
     for _ in range(3):
         st = eos_b200.Stats()
-        eos_b200.linear(rt, x, w, bias, epilogue=2 if residual else 1, residual=res, weight_mode=weight_mode, stats=st)
+        epi = epilogue if epilogue is not None else (2 if residual else 1)
+        eos_b200.linear(rt, x, w, bias, epilogue=epi, residual=res, weight_mode=weight_mode, stats=st)
         print(f"gemm {rows}x{k}->{n} weight_mode={weight_mode}: {st.device_ms:.3f} ms, {2.0 * rows * k * n / st.device_ms / 1e9:.1f} TFLOP/s")
     rt.close()
 
@@ -88,5 +91,7 @@ if __name__ == "__main__":
      "gemm_f16w": lambda: case_gemm(False, 1), "gemm_res_f16w": lambda: case_gemm(True, 1),
      "gemm_big": lambda: case_gemm(False, 0, 131072), "gemm_res_big": lambda: case_gemm(True, 0, 131072),
      "gemm_big_f16w": lambda: case_gemm(False, 1, 131072),
+     "gemm_qkv_f16w": lambda: case_gemm(False, 1, 32768, (768, 2304), 0),
+     "gemm_attn_out_f16w": lambda: case_gemm(True, 1, 32768, (768, 768)),
      "gemm_attn_out_big_f16w": lambda: case_gemm(True, 1, 131072, (768, 768)), "gemm_res_big_f16w": lambda: case_gemm(True, 1, 131072),
      }[name]()
