@@ -95,3 +95,42 @@ def test_linear_rejects_bad_arguments(rt):
         eos_b200.linear(rt, x, np.zeros((8, 24), np.float32))  # in width not a multiple of 16
     with pytest.raises(ValueError):
         eos_b200.linear(rt, x, np.zeros((8, 32), np.float32))
+
+
+_PAIR_SCRIPT = r"""
+import numpy as np, sys
+import eos_b200
+from eos_b200 import synth
+rt = eos_b200.Runtime(0)
+worst = 0.0
+for rows, k, n, epi in ((5, 16, 16, 0), (129, 96, 264, 1), (1000, 768, 768, 2), (257, 3072, 272, 0), (4100, 384, 1152, 2),
+                        (70000, 768, 768, 2)):
+    rng = np.random.default_rng(rows + k + n)
+    x = rng.standard_normal((rows, k)).astype(np.float32)
+    w = synth.quantize_per_channel((rng.standard_normal((n, k)) * 0.05).astype(np.float32))
+    bias = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    res = rng.standard_normal((rows, n)).astype(np.float32) if epi == 2 else None
+    y1 = eos_b200.linear(rt, x, w, bias, epilogue=epi, residual=res, weight_mode=1)   # f16 weights: CTA pairs
+    y0 = eos_b200.linear(rt, x, w, bias, epilogue=epi, residual=res, weight_mode=0)   # 8-bit weights: one CTA per tile
+    if not np.array_equal(y0, y1):
+        worst = max(worst, float(np.abs(y0 - y1).max()))
+print("PAIR_RESULT", worst)
+rt.close()
+"""
+
+
+def test_linear_cta_pair_mode_is_bit_identical():
+    """The opt-in CTA-pair kernel (EOS_B200_GEMM_CTA_PAIR=1: two CTAs of a cluster per 256 x 256 tile,
+    tcgen05.mma.cta_group::2) must give exactly the bits of the one-CTA kernel: same products, same fp32
+    accumulation order along K, same epilogue.  Runs in a child process because the mode is read once per process."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, EOS_B200_GEMM_CTA_PAIR="1", EOS_B200_DEBUG="1", PYTHONPATH=root)
+    out = subprocess.run([sys.executable, "-c", _PAIR_SCRIPT], env=env, cwd=root, capture_output=True, text=True,
+                         timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "resident CTA pairs for the GEMM" in out.stderr and "pairs for the GEMM: 0" not in out.stderr, out.stderr[-500:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("PAIR_RESULT")][-1]
+    assert float(line.split()[1]) == 0.0, line
