@@ -286,25 +286,6 @@ __device__ __forceinline__ float gelu_erf_fast(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z));
     return __fdividef(x, 1.0f + e);
 }
-// Two values at once with one reciprocal: 1/a = b/(ab), 1/b = a/(ab), so the pair costs three MUFU
-// ops instead of four (the epilogue that applies it is MUFU-bound).  The exponent is clamped so that
-// the product (1 + e0)(1 + e1) stays finite; beyond the clamp the sigmoid is below 2^-60.
-__device__ __forceinline__ void gelu_erf_fast2(float& x0, float& x1) {
-    const float t0 = fminf(x0 * x0, 18.0f), t1 = fminf(x1 * x1, 18.0f);
-    float p0 = fmaf(t0, 2.33936606e-5f, 7.47459662e-4f), p1 = fmaf(t1, 2.33936606e-5f, 7.47459662e-4f);
-    p0 = fmaf(p0, t0, -1.06012290e-1f);
-    p1 = fmaf(p1, t1, -1.06012290e-1f);
-    p0 = fmaf(p0, t0, -2.30159100e+0f);
-    p1 = fmaf(p1, t1, -2.30159100e+0f);
-    float e0, e1, r;
-    const float z0 = fminf(x0 * p0, 60.0f), z1 = fminf(x1 * p1, 60.0f);
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(z0));
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(z1));
-    const float a = 1.0f + e0, b = 1.0f + e1;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a * b));
-    x0 = x0 * (r * b);
-    x1 = x1 * (r * a);
-}
 // tanh-form GELU of the compact encoder profile.
 __device__ __forceinline__ float gelu_tanh(float x) {
     return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));

@@ -413,9 +413,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (tm__) GMARK(4);
 #endif
 
-            uint32_t r_next[16];
+            // accumulator chunks of 16 columns ping-pong between two register buffers: while one is being
+            // turned into outputs the next tcgen05.ld fills the other
+            uint32_t ra[16], rb[16];
             __syncwarp();
-            tmem_ld_32x16(taddr + epart * kWarpCols, r_next);
+            tmem_ld_32x16(taddr + epart * kWarpCols, ra);
 #pragma unroll 1
             for (int sl = 0; sl < kSlabs; ++sl) {
                 const int col0 = epart * kWarpCols + sl * kSlabCols;  // first column of the slab inside the tile
@@ -443,19 +445,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #ifdef EOSB_GEMM_TIMING
                 if (tm__) GMARK(5);
 #endif
-#pragma unroll
-                for (int ch = 0; ch < kSlabCols / 16; ++ch) {
-                    uint32_t r[16];
-                    tmem_ld_wait16(r_next);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = r_next[j];
-                    {
-                        const int next_col = col0 + (ch + 1) * 16;  // next chunk, possibly of the next slab
-                        if (next_col < (epart + 1) * kWarpCols) {
-                            __syncwarp();
-                            tmem_ld_32x16(taddr + next_col, r_next);
-                        }
-                    }
+                // one chunk: 16 accumulator columns of this thread's row -> scale, bias, activation / residual, f16
+                auto chunk = [&](const uint32_t (&r)[16], const int ch) {
                     float v[16];
 #pragma unroll
                     for (int j = 0; j < 16; j += 2) {
@@ -465,7 +456,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                     if (p.mode == kEpiBiasGeluErf) {
 #pragma unroll
-                        for (int j = 0; j < 16; j += 2) gelu_erf_fast2(v[j], v[j + 1]);
+                        for (int j = 0; j < 16; ++j) v[j] = gelu_erf_fast(v[j]);
                     } else if (p.mode == kEpiBiasGeluTanh) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
@@ -508,7 +499,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             }
                         }
                     }
+                };
+                static_assert(kSlabCols == 32, "a slab is two chunks of 16 columns");
+                tmem_ld_wait16(ra);
+                __syncwarp();
+                tmem_ld_32x16(taddr + col0 + 16, rb);
+                chunk(ra, 0);
+                tmem_ld_wait16(rb);
+                if (sl + 1 < kSlabs) {
+                    __syncwarp();
+                    tmem_ld_32x16(taddr + col0 + 32, ra);
                 }
+                chunk(rb, 1);
 #ifdef EOSB_GEMM_TIMING
                 if (tm__) GMARK(6);
 #endif
