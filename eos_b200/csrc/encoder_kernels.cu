@@ -247,15 +247,31 @@ layernorm_kernel(const __half* __restrict__ in, const float* __restrict__ gamma,
     const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
     int rows = total_rows != nullptr ? *total_rows : m_alloc;
     if (rows > m_alloc) rows = m_alloc;
-    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps_per_grid) {
+    // the next row of this warp is requested before the current one is reduced, so that a warp always has a
+    // row in flight while it computes
+    uint4 raw[kChunks];
+    auto fetch = [&](int r, uint4 (&dst)[kChunks]) {
         const __half* x = in + (size_t)r * dim;
-        float v[kChunks][8];
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
             const int col = (c * 32 + lane) * 8;
-            if (col < dim) unpack8(*reinterpret_cast<const uint4*>(x + col), v[c]);
+            dst[c] = make_uint4(0, 0, 0, 0);
+            if (col < dim) dst[c] = *reinterpret_cast<const uint4*>(x + col);
         }
+    };
+    int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (r < rows) fetch(r, raw);
+    while (r < rows) {
+        const int rn = r + warps_per_grid;
+        uint4 nxt[kChunks];
+        if (rn < rows) fetch(rn, nxt);
+        float v[kChunks][8];
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) unpack8(raw[c], v[c]);
         row_layernorm_store<kChunks>(v, dim, lane, gamma, beta, eps, out + (size_t)r * dim);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) raw[c] = nxt[c];
+        r = rn;
     }
 }
 
@@ -776,8 +792,8 @@ void launch_layernorm(const __half* in, const float* gamma, const float* beta, f
                       const int* total_rows, __half* out, int sm_count, cudaStream_t stream) {
     dispatch_chunks(dim, [&](auto c) {
         constexpr int kChunks = decltype(c)::value;
-        layernorm_kernel<kChunks><<<sm_count * 8, 256, 0, stream>>>(in, gamma, beta, eps, dim, m_alloc, total_rows,
-                                                                    out);
+        layernorm_kernel<kChunks><<<sm_count * 8, 256, 0, stream>>>(in, gamma, beta, eps, dim, m_alloc,
+                                                                                 total_rows, out);
     });
 }
 
