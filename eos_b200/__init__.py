@@ -5,9 +5,9 @@ libeos_b200.so (hand-written CUDA, C ABI in include/eos_b200.h).
 """
 from ._lib import EosB200DeviceStatusError, EosB200Error, Stats
 from .encoder import BertEmbedder, EmbedPooledPipeline, Q8Weight, Runtime, linear
-from .turboquant import Corpus, Quantizer, RotationSpec, lloyd_max_gaussian, make_rotation_spec
+from .turboquant import Corpus, DenseIndex, Quantizer, RotationSpec, lloyd_max_gaussian, make_rotation_spec
 
 __all__ = [
-    "BertEmbedder", "Corpus", "EmbedPooledPipeline", "EosB200DeviceStatusError", "EosB200Error", "Q8Weight",
+    "BertEmbedder", "Corpus", "DenseIndex", "EmbedPooledPipeline", "EosB200DeviceStatusError", "EosB200Error", "Q8Weight",
     "Quantizer", "RotationSpec", "Runtime", "Stats", "linear", "lloyd_max_gaussian", "make_rotation_spec",
 ]

@@ -103,6 +103,10 @@ SYMBOLS = {
     "eos_b200_score_all": (C.c_int, [_P, _P, C.c_int, _P, _ERR]),
     "eos_b200_parent_topk": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, C.c_int, C.c_double, C.c_int, _P, _P,
                                        C.POINTER(Stats), _ERR]),
+    "eos_b200_dense_bind": (C.c_int, [_P, _P, C.c_int64, C.c_int, C.c_int, C.POINTER(_P), _ERR]),
+    "eos_b200_dense_destroy": (None, [_P]),
+    "eos_b200_dense_score_topk": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
+    "eos_b200_dense_rerank": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_synth_gaussian_device": (C.c_int, [_P, C.c_uint64, C.c_int64, C.c_int64, C.c_int, C.c_int, _P, _P,
                                                  _ERR]),
 }

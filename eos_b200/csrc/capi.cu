@@ -1639,3 +1639,178 @@ int eos_b200_synth_gaussian_device(EosB200Runtime* rt, uint64_t seed, int64_t ro
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// dense candidates
+// ------------------------------------------------------------------------------------------------
+struct EosB200DenseIndex {
+    EosB200Runtime* rt = nullptr;
+    int64_t n = 0;
+    int dim = 0;
+    bool f16 = false;
+    void* vectors = nullptr;  // [n, dim] fp32 or f16
+};
+
+namespace {
+__global__ void f32_to_f16_kernel(const float* __restrict__ in, long long count, __half* __restrict__ out) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+        out[i] = __float2half_rn(in[i]);
+}
+
+// shared tail of the two dense entry points: keys [q, cand] -> top-k on the host buffers
+int dense_finish(EosB200DenseIndex* ix, uint64_t* d_keys, int q_count, int64_t cand, int k, int launches,
+                 int64_t uploaded, int64_t* h_ids, float* h_scores, EosB200Stats* stats, const char* what, char** err) {
+    EosB200Runtime* rt = ix->rt;
+    cudaStream_t s = rt->stream;
+    int64_t* d_ids = nullptr;
+    float* d_scores = nullptr;
+    cudaError_t e = dev_alloc(&d_ids, (size_t)q_count * k);
+    if (e == cudaSuccess) e = dev_alloc(&d_scores, (size_t)q_count * k);
+    if (e == cudaSuccess) {
+        launch_tq_merge(d_keys, cand, cand, 1, (int)cand, nullptr, q_count, k, 0, d_ids, d_scores, nullptr, s);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_ids, d_ids, (size_t)q_count * k * 8, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_scores, d_scores, (size_t)q_count * k * 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev1, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    dev_free(d_ids);
+    dev_free(d_scores);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(err, std::string(what) + ": " + cudaGetErrorString(e));
+    }
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches + 1;
+        stats->uploaded_bytes = uploaded;
+        stats->downloaded_bytes = (int64_t)q_count * k * 12;
+        cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+    }
+    return EOS_B200_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int eos_b200_dense_bind(EosB200Runtime* rt, const float* h_vectors, int64_t n, int dim, int store_f16,
+                        EosB200DenseIndex** out, char** err) {
+    if (rt == nullptr || h_vectors == nullptr || out == nullptr) return fail(err, "dense_bind: null argument");
+    if (n <= 0 || dim <= 0) return fail(err, "dense_bind: empty input");
+    if (dim > 1024) return fail(err, "dense_bind: dim must be at most 1024");
+    if (n > 0x7fffffffLL) return fail(err, "dense_bind: too many rows");
+    CUDA_TRY(cudaSetDevice(rt->device));
+    auto* ix = new EosB200DenseIndex();
+    ix->rt = rt;
+    ix->n = n;
+    ix->dim = dim;
+    ix->f16 = store_f16 != 0;
+    const size_t count = (size_t)n * dim;
+    float* d_f32 = nullptr;
+    cudaError_t e = dev_alloc(&d_f32, count);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_f32, h_vectors, count * 4, cudaMemcpyHostToDevice, rt->stream);
+    if (e == cudaSuccess && ix->f16) {
+        __half* d_f16 = nullptr;
+        e = dev_alloc(&d_f16, count);
+        if (e == cudaSuccess) {
+            f32_to_f16_kernel<<<rt->sm_count * 8, 256, 0, rt->stream>>>(d_f32, (long long)count, d_f16);
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+        dev_free(d_f32);
+        d_f32 = nullptr;
+        ix->vectors = d_f16;
+    } else {
+        if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+        ix->vectors = d_f32;
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        dev_free(ix->vectors);
+        delete ix;
+        return fail(err, std::string("dense_bind: ") + cudaGetErrorString(e));
+    }
+    *out = ix;
+    return EOS_B200_OK;
+}
+
+void eos_b200_dense_destroy(EosB200DenseIndex* ix) {
+    if (ix == nullptr) return;
+    cudaSetDevice(ix->rt->device);
+    dev_free(ix->vectors);
+    delete ix;
+}
+
+int eos_b200_dense_score_topk(EosB200DenseIndex* ix, const float* h_queries, int q_count, int metric, int k,
+                              int64_t* h_ids, float* h_scores, EosB200Stats* stats, char** err) {
+    if (ix == nullptr || h_queries == nullptr || h_ids == nullptr || h_scores == nullptr)
+        return fail(err, "dense_score_topk: null argument");
+    if (q_count <= 0) return fail(err, "dense_score_topk: empty input");
+    if (metric != EOS_B200_METRIC_DOT && metric != EOS_B200_METRIC_COSINE) return fail(err, "dense_score_topk: unknown metric");
+    if (k <= 0 || k > kTqMaxK || k > ix->n) return fail(err, "dense_score_topk: k must be in [1, min(128, rows)]");
+    EosB200Runtime* rt = ix->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    cudaStream_t s = rt->stream;
+    float* d_q = nullptr;
+    uint64_t* d_keys = nullptr;
+    cudaError_t e = dev_alloc(&d_q, (size_t)q_count * ix->dim);
+    if (e == cudaSuccess) e = dev_alloc(&d_keys, (size_t)q_count * ix->n);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev0, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_q, h_queries, (size_t)q_count * ix->dim * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) {
+        launch_dense_keys(ix->vectors, ix->f16, ix->n, ix->dim, d_q, q_count, nullptr, ix->n, metric, d_keys, rt->sm_count, s);
+        e = cudaGetLastError();
+    }
+    int rc = EOS_B200_OK;
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        rc = fail(err, std::string("dense_score_topk: ") + cudaGetErrorString(e));
+    } else {
+        rc = dense_finish(ix, d_keys, q_count, ix->n, k, 1, (int64_t)q_count * ix->dim * 4, h_ids, h_scores, stats,
+                          "dense_score_topk", err);
+    }
+    dev_free(d_q);
+    dev_free(d_keys);
+    return rc;
+}
+
+int eos_b200_dense_rerank(EosB200DenseIndex* ix, const float* h_queries, int q_count, const int64_t* h_candidates,
+                          int cand, int k, int64_t* h_ids, float* h_scores, EosB200Stats* stats, char** err) {
+    if (ix == nullptr || h_queries == nullptr || h_candidates == nullptr || h_ids == nullptr || h_scores == nullptr)
+        return fail(err, "dense_rerank: null argument");
+    if (q_count <= 0 || cand <= 0) return fail(err, "dense_rerank: empty input");
+    if (k <= 0 || k > cand) k = cand;  // the reference clamps topK to the candidate count
+    if (k > kTqMaxK) return fail(err, "dense_rerank: k must be at most 128");
+    EosB200Runtime* rt = ix->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    cudaStream_t s = rt->stream;
+    float* d_q = nullptr;
+    int64_t* d_cand = nullptr;
+    uint64_t* d_keys = nullptr;
+    cudaError_t e = dev_alloc(&d_q, (size_t)q_count * ix->dim);
+    if (e == cudaSuccess) e = dev_alloc(&d_cand, (size_t)q_count * cand);
+    if (e == cudaSuccess) e = dev_alloc(&d_keys, (size_t)q_count * cand);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev0, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_q, h_queries, (size_t)q_count * ix->dim * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_cand, h_candidates, (size_t)q_count * cand * 8, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) {
+        launch_dense_keys(ix->vectors, ix->f16, ix->n, ix->dim, d_q, q_count, d_cand, cand, EOS_B200_METRIC_DOT, d_keys,
+                          rt->sm_count, s);
+        e = cudaGetLastError();
+    }
+    int rc = EOS_B200_OK;
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        rc = fail(err, std::string("dense_rerank: ") + cudaGetErrorString(e));
+    } else {
+        rc = dense_finish(ix, d_keys, q_count, cand, k, 1, (int64_t)q_count * (ix->dim * 4 + (int64_t)cand * 8), h_ids,
+                          h_scores, stats, "dense_rerank", err);
+    }
+    dev_free(d_q);
+    dev_free(d_cand);
+    dev_free(d_keys);
+    return rc;
+}
+
+}  // extern "C"

@@ -684,6 +684,74 @@ size_t tq_stream_smem() {
            (size_t)kStreamWarps * 8 * 4 + (size_t)kStreamWarps * 256 * 4 + 128;
 }
 
+
+// ------------------------------------------------------------------------------------------
+// dense candidates: dotRows / cosineRows (runtime/backend/tensor_ops.go:1967-2057, device bodies
+// compiler/compiler.go:837-863) and the rerank loops topDenseRerankScores / topFP16RerankScores
+// (runtime/retrieval_turboquant.go:1610-1662).  One warp per (document row, group of queries): the
+// row is read once into registers (fp32, or f16 widened to fp32 as halfToFloat32 does), every query
+// of the group is dotted against it in fp32, the result becomes a sortable key.  With a candidate
+// list the group is one query and the row is that query's j-th candidate (id < 0 = absent, key 0).
+// ------------------------------------------------------------------------------------------
+constexpr int kDenseMaxPerLane = 32;  // dim <= 1024
+constexpr int kDenseQueryGroup = 4;
+
+template <bool kHalf>
+__global__ void __launch_bounds__(256)
+dense_keys_kernel(const void* __restrict__ docs, long long n_rows, int dim, const float* __restrict__ queries, int nq,
+                  const long long* __restrict__ cand_ids, long long cand, int metric, u64* __restrict__ keys) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const int group = cand_ids != nullptr ? 1 : kDenseQueryGroup;
+    const int qgroups = (nq + group - 1) / group;
+    const long long items = (long long)qgroups * cand;
+    for (long long it = warp; it < items; it += warps) {
+        const int qg = (int)(it / cand);
+        const long long j = it % cand;
+        long long row = j;
+        if (cand_ids != nullptr) row = cand_ids[(long long)qg * cand + j];
+        if (row < 0 || row >= n_rows) {
+            if (lane == 0)
+                for (int qi = qg * group; qi < nq && qi < (qg + 1) * group; ++qi) keys[(long long)qi * cand + j] = 0;
+            continue;
+        }
+        float d[kDenseMaxPerLane];
+        float dn = 0.f;
+#pragma unroll
+        for (int c = 0; c < kDenseMaxPerLane; ++c) {
+            const int col = c * 32 + lane;
+            d[c] = 0.f;
+            if (col < dim) {
+                if (kHalf) d[c] = __half2float(reinterpret_cast<const __half*>(docs)[(size_t)row * dim + col]);
+                else d[c] = reinterpret_cast<const float*>(docs)[(size_t)row * dim + col];
+            }
+            dn = fmaf(d[c], d[c], dn);
+        }
+        if (metric == 1) dn = warp_sum(dn);
+        for (int qi = qg * group; qi < nq && qi < (qg + 1) * group; ++qi) {
+            const float* q = queries + (size_t)qi * dim;
+            float dot = 0.f, qn = 0.f;
+#pragma unroll
+            for (int c = 0; c < kDenseMaxPerLane; ++c) {
+                const int col = c * 32 + lane;
+                const float qv = col < dim ? __ldg(q + col) : 0.f;
+                dot = fmaf(qv, d[c], dot);
+                qn = fmaf(qv, qv, qn);
+            }
+            dot = warp_sum(dot);
+            float score = dot;
+            if (metric == 1) {
+                qn = warp_sum(qn);
+                const float denom = sqrtf(qn) * sqrtf(dn);
+                score = denom == 0.f ? 0.f : dot / denom;
+            }
+            // the id inside the key is the row, so that ties go to the smaller row (topKTensor, retrievalScoreBetter)
+            if (lane == 0) keys[(long long)qi * cand + j] = make_key(score, (uint32_t)row);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // merge: one CTA per query; block-wide radix select of the k-th largest key over all candidate
 // segments (read from global / L2), gather of the survivors, bitonic sort by one warp.
@@ -947,6 +1015,21 @@ void launch_tq_merge(const uint64_t* cand, int64_t query_stride, int64_t seg_str
     tq_merge_kernel<<<queries, kMergeThreads, 0, stream>>>(
         reinterpret_cast<const u64*>(cand), (long long)query_stride, (long long)seg_stride, n_segs, seg_len, counts,
         k, (long long)id_base, reinterpret_cast<long long*>(out_ids), out_scores, reinterpret_cast<u64*>(out_keys));
+}
+
+void launch_dense_keys(const void* docs, bool docs_f16, int64_t n_rows, int dim, const float* queries, int nq,
+                       const int64_t* cand_ids, int64_t cand, int metric, uint64_t* keys, int sm_count,
+                       cudaStream_t stream) {
+    if (nq <= 0 || cand <= 0) return;
+    const int grid = sm_count * 8;
+    if (docs_f16)
+        dense_keys_kernel<true><<<grid, 256, 0, stream>>>(docs, (long long)n_rows, dim, queries, nq,
+                                                          reinterpret_cast<const long long*>(cand_ids), (long long)cand,
+                                                          metric, reinterpret_cast<u64*>(keys));
+    else
+        dense_keys_kernel<false><<<grid, 256, 0, stream>>>(docs, (long long)n_rows, dim, queries, nq,
+                                                           reinterpret_cast<const long long*>(cand_ids), (long long)cand,
+                                                           metric, reinterpret_cast<u64*>(keys));
 }
 
 }  // namespace eosb

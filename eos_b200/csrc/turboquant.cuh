@@ -83,4 +83,12 @@ void launch_tq_merge(const uint64_t* cand, int64_t query_stride, int64_t seg_str
                      uint64_t* out_keys, cudaStream_t stream);
 cudaError_t tq_merge_init();
 
+// keys[q * cand + j] = sortable key (score, row) of query q against document row j (cand_ids == null, cand = n_rows)
+// or against row cand_ids[q * cand + j] (negative or out-of-range id: key 0 = absent).  docs is [n_rows, dim] fp32 or
+// f16; metric 0 = dot product, 1 = cosine (0 when either norm is 0).  dim <= 1024.  Feed the keys to launch_tq_merge
+// with one segment of cand keys per query for the exact top-k (score descending, row ascending).
+void launch_dense_keys(const void* docs, bool docs_f16, int64_t n_rows, int dim, const float* queries, int nq,
+                       const int64_t* cand_ids, int64_t cand, int metric, uint64_t* keys, int sm_count,
+                       cudaStream_t stream);
+
 }  // namespace eosb

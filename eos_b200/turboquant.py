@@ -228,6 +228,65 @@ class Corpus:
             pass
 
 
+METRIC_DOT, METRIC_COSINE = 0, 1
+
+
+class DenseIndex:
+    """Uncompressed document vectors on one GPU: the dense scoring operators (dotRows / cosineRows + topKTensor,
+    runtime/backend/tensor_ops.go:1967-2057, 2124-2193) and the rerank stage after a TurboQuant top-k
+    (topDenseRerankScores / topFP16RerankScores, runtime/retrieval_turboquant.go:1610-1662).  store_f16 keeps the
+    vectors rounded to f16 (the reference's fp16 sidecar)."""
+
+    def __init__(self, runtime, vectors, store_f16: bool = False):
+        v = _f32(vectors)
+        if v.ndim != 2 or v.shape[0] == 0 or v.shape[1] == 0:
+            raise ValueError(f"DenseIndex expects non-empty [n, dim] vectors, got {v.shape}")
+        self.rt = runtime
+        self.n, self.dim = v.shape
+        self.handle = C.c_void_p()
+        _lib.call("eos_b200_dense_bind", runtime.handle, _ptr(v), self.n, self.dim, 1 if store_f16 else 0,
+                  C.byref(self.handle))
+        runtime._adopt(self)
+        self.last_stats = Stats()
+
+    def score_topk(self, queries, k: int, metric: int = METRIC_DOT) -> Tuple[np.ndarray, np.ndarray]:
+        """Every query against every row: (row ids int64 [Q,k], scores fp32 [Q,k]); score desc, then row asc."""
+        q = _f32(queries)
+        if q.ndim != 2 or q.shape[1] != self.dim or q.shape[0] == 0:
+            raise ValueError(f"score_topk expects non-empty [Q, {self.dim}] queries, got {q.shape}")
+        ids = np.empty((q.shape[0], k), dtype=np.int64)
+        scores = np.empty((q.shape[0], k), dtype=np.float32)
+        _lib.call("eos_b200_dense_score_topk", self.handle, _ptr(q), q.shape[0], int(metric), int(k), _ptr(ids),
+                  _ptr(scores), C.byref(self.last_stats))
+        return ids, scores
+
+    def rerank(self, queries, candidates, k: int) -> Tuple[np.ndarray, np.ndarray]:
+        """Exact dot products of each query with its own candidate rows ([Q, C] row indices, negative = no vector),
+        best k by score desc / row asc; unused result slots hold id -1."""
+        q = _f32(queries)
+        c = np.ascontiguousarray(candidates, dtype=np.int64)
+        if q.ndim != 2 or q.shape[1] != self.dim or c.ndim != 2 or c.shape[0] != q.shape[0] or c.shape[1] == 0:
+            raise ValueError("rerank expects [Q, dim] queries and [Q, C] candidates")
+        kk = c.shape[1] if (k <= 0 or k > c.shape[1]) else int(k)
+        ids = np.empty((q.shape[0], kk), dtype=np.int64)
+        scores = np.empty((q.shape[0], kk), dtype=np.float32)
+        _lib.call("eos_b200_dense_rerank", self.handle, _ptr(q), q.shape[0], _ptr(c), c.shape[1], kk, _ptr(ids),
+                  _ptr(scores), C.byref(self.last_stats))
+        return ids, scores
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.lib().eos_b200_dense_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+
 def topk_merge_device(rt: Runtime, d_keys: int, shards: int, q_count: int, k: int, d_ids: int, d_scores: int,
                       stream: Optional[int] = None) -> None:
     """Global top-k from all-gathered per-shard key lists [shards, Q, k] (device pointers)."""

@@ -280,6 +280,29 @@ EOS_B200_API int eos_b200_topk_merge_device(EosB200Runtime* rt, const uint64_t* 
  * candidates: h_scores [q_count, n]. */
 EOS_B200_API int eos_b200_score_all(EosB200Corpus* corpus, const float* h_queries, int q_count, float* h_scores, char** err);
 
+/* ---- dense candidates ------------------------------------------------------------------------
+ * Uncompressed document vectors on the device, for the dense scoring operators and the rerank
+ * stage that follows a TurboQuant top-k.  h_vectors [n, dim] fp32 (dim <= 1024); store_f16 != 0
+ * keeps them rounded to f16 (the fp16 rerank sidecar: topFP16RerankScores reads uint16 halves,
+ * runtime/retrieval_turboquant.go:1637-1662), else as fp32 (topDenseRerankScores, :1610-1635). */
+typedef struct EosB200DenseIndex EosB200DenseIndex;
+EOS_B200_API int eos_b200_dense_bind(EosB200Runtime* rt, const float* h_vectors, int64_t n, int dim, int store_f16,
+                                     EosB200DenseIndex** out, char** err);
+EOS_B200_API void eos_b200_dense_destroy(EosB200DenseIndex* index);
+#define EOS_B200_METRIC_DOT 0    /* dotRows, runtime/backend/tensor_ops.go:1967-1995; kernel body compiler/compiler.go:838-846 */
+#define EOS_B200_METRIC_COSINE 1 /* cosineRows, tensor_ops.go:1997-2057 (0 when a norm is 0); compiler.go:847-862 */
+/* Every query against every row, then topKTensor (tensor_ops.go:2124-2193: score descending,
+ * ties to the lower row).  h_queries [q_count, dim] fp32; results [q_count, k], k <= 128, k <= n. */
+EOS_B200_API int eos_b200_dense_score_topk(EosB200DenseIndex* index, const float* h_queries, int q_count, int metric, int k,
+                                           int64_t* h_ids, float* h_scores, EosB200Stats* stats, char** err);
+/* Rerank: for each query the dot product (fp32 accumulate) with its candidate rows only, then the
+ * k best by score descending / row ascending, as the rerank loops of retrieval_turboquant.go:1610-1662
+ * do with a heap.  h_candidates [q_count, cand] row indices; a negative or out-of-range entry is a
+ * candidate without a vector (skipped, like a missing map entry).  Slots past the number of valid
+ * candidates hold id -1 and score -infinity. */
+EOS_B200_API int eos_b200_dense_rerank(EosB200DenseIndex* index, const float* h_queries, int q_count, const int64_t* h_candidates,
+                                       int cand, int k, int64_t* h_ids, float* h_scores, EosB200Stats* stats, char** err);
+
 /* Multi-vector parents (topTurboQuantMultiVectorParentScores,
  * runtime/retrieval_multivector_turboquant.go:746-810, 890-907): rows of the corpus are child
  * vectors, h_parent_of_child [n] maps each to its parent in [0, parents).  Per query vector the

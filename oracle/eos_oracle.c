@@ -893,3 +893,31 @@ EOS_ORACLE_API float eos_oracle_dot(const float *a, const float *b, int n) {
     for (int i = 0; i < n; i++) sum += a[i] * b[i];
     return sum;
 }
+
+/* dotRows: runtime/backend/tensor_ops.go:1967-1995 (one query against every row, float accumulate in
+ * column order).  out[r] for r in [0, rows). */
+EOS_ORACLE_API void eos_oracle_dot_rows(const float *query, const float *docs, int64_t rows, int cols, float *out) {
+    for (int64_t r = 0; r < rows; r++) {
+        float sum = 0.0f;
+        const float *d = docs + r * (int64_t)cols;
+        for (int c = 0; c < cols; c++) sum += query[c] * d[c];
+        out[r] = sum;
+    }
+}
+
+/* cosineRows: runtime/backend/tensor_ops.go:1997-2057 (double accumulation of the dot product and of
+ * both squared norms; a zero denominator gives 0). */
+EOS_ORACLE_API void eos_oracle_cosine_rows(const float *query, const float *docs, int64_t rows, int cols, float *out) {
+    double qn = 0.0;
+    for (int c = 0; c < cols; c++) qn += (double)query[c] * (double)query[c];
+    for (int64_t r = 0; r < rows; r++) {
+        double dot = 0.0, dn = 0.0;
+        const float *d = docs + r * (int64_t)cols;
+        for (int c = 0; c < cols; c++) {
+            dot += (double)query[c] * (double)d[c];
+            dn += (double)d[c] * (double)d[c];
+        }
+        const double denom = sqrt(qn) * sqrt(dn);
+        out[r] = denom == 0.0 ? 0.0f : (float)(dot / denom);
+    }
+}

@@ -320,3 +320,29 @@ def parent_topk(child_scores, parent_of_child, parents: int, k: int, top_n: int 
     r = lib().eos_oracle_parent_topk(_p(s), _p(p), C.c_int64(s.size), C.c_int(parents), C.c_int(top_n),
                                      C.c_double(penalty), C.c_int(k), _p(oi), _p(os_))
     return oi[:r], os_[:r]
+
+
+def dot_rows(query, docs):
+    q = _f32(query).ravel()
+    d = _f32(docs)
+    out = np.empty(d.shape[0], dtype=np.float32)
+    lib().eos_oracle_dot_rows(_p(q), _p(d), C.c_int64(d.shape[0]), C.c_int(d.shape[1]), _p(out))
+    return out
+
+
+def cosine_rows(query, docs):
+    q = _f32(query).ravel()
+    d = _f32(docs)
+    out = np.empty(d.shape[0], dtype=np.float32)
+    lib().eos_oracle_cosine_rows(_p(q), _p(d), C.c_int64(d.shape[0]), C.c_int(d.shape[1]), _p(out))
+    return out
+
+
+def rerank(query, docs, candidates, k: int):
+    """topDenseRerankScores (runtime/retrieval_turboquant.go:1610-1635): dot product of the query with every
+    candidate that has a vector, best k by score descending then id ascending."""
+    cand = [int(c) for c in np.asarray(candidates).ravel() if 0 <= int(c) < len(docs)]
+    if not cand:
+        return np.empty(0, np.int64), np.empty(0, np.float32)
+    scores = dot_rows(query, _f32(docs)[cand])
+    return topk_merge(np.asarray(cand, np.int64), scores, k)

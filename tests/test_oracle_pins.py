@@ -180,3 +180,18 @@ def test_f16_roundtrip_matches_numpy_off_ties():
         assert O.f16_bits_to_f32(bits) == float(np.uint16(bits).view(np.float16))
     n_equal = sum(O.f32_to_f16_bits(float(x)) == int(np.float16(x).view(np.uint16)) for x in xs[::7])
     assert n_equal >= len(xs[::7]) - 2  # differs from IEEE only on exact ties (round half up)
+
+
+def test_dense_rows_and_rerank_restatement():
+    """dotRows / cosineRows (runtime/backend/tensor_ops.go:1967-2057) on hand-checked values, and the rerank loop's
+    order (retrieval_turboquant.go:1610-1635: score descending, then id ascending; candidates without a vector skipped)."""
+    from oracle import oracle as O
+    docs = np.array([[1, 0, 0], [0, 2, 0], [3, 4, 0], [0, 0, 0], [1, 0, 0]], np.float32)
+    q = np.array([3, 4, 0], np.float32)
+    assert O.dot_rows(q, docs).tolist() == [3.0, 8.0, 25.0, 0.0, 3.0]
+    cos = O.cosine_rows(q, docs)
+    assert np.allclose(cos, [0.6, 0.8, 1.0, 0.0, 0.6], atol=1e-7) and cos[3] == 0.0   # zero row -> 0, not NaN
+    ids, scores = O.rerank(q, docs, [4, 0, 3, -1, 9, 1], 3)
+    assert ids.tolist() == [1, 0, 4] and scores.tolist() == [8.0, 3.0, 3.0]             # tie 0 / 4: smaller id first
+    ids, _ = O.rerank(q, docs, [-1, 17], 3)
+    assert ids.size == 0
