@@ -4,10 +4,10 @@ Host-side mirror of the reference's interfaces for this path; all compute happen
 libeos_b200.so (hand-written CUDA, C ABI in include/eos_b200.h).
 """
 from ._lib import EosB200DeviceStatusError, EosB200Error, Stats
-from .encoder import BertEmbedder, EmbedPooledPipeline, Q8Weight, Runtime, linear
+from .encoder import BertEmbedder, CompactEmbedder, EmbedPooledPipeline, Q8Weight, Q8WeightInOut, Runtime, linear
 from .turboquant import Corpus, DenseIndex, Quantizer, RotationSpec, lloyd_max_gaussian, make_rotation_spec
 
 __all__ = [
-    "BertEmbedder", "Corpus", "DenseIndex", "EmbedPooledPipeline", "EosB200DeviceStatusError", "EosB200Error", "Q8Weight",
+    "BertEmbedder", "CompactEmbedder", "Corpus", "DenseIndex", "EmbedPooledPipeline", "EosB200DeviceStatusError", "EosB200Error", "Q8Weight", "Q8WeightInOut",
     "Quantizer", "RotationSpec", "Runtime", "Stats", "linear", "lloyd_max_gaussian", "make_rotation_spec",
 ]

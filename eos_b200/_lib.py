@@ -63,6 +63,18 @@ class EncoderDesc(C.Structure):
                 ("embedding_ln_beta", C.c_void_p), ("layer", C.POINTER(EncoderLayer)), ("head_weights", C.c_void_p)]
 
 
+class CompactLayer(C.Structure):
+    _fields_ = [("attn_q", Matrix), ("attn_k", Matrix), ("attn_v", Matrix), ("attn_o", Matrix), ("ffn_up", Matrix),
+                ("ffn_down", Matrix)]
+
+
+class CompactEncoderDesc(C.Structure):
+    _fields_ = [("layers", C.c_int32), ("hidden", C.c_int32), ("heads", C.c_int32), ("intermediate", C.c_int32),
+                ("vocab", C.c_int32), ("role_vocab", C.c_int32), ("output_dim", C.c_int32), ("weight_mode", C.c_int32),
+                ("token_embedding", C.c_void_p), ("role_embedding", C.c_void_p), ("layer", C.POINTER(CompactLayer)),
+                ("output_projection", Matrix)]
+
+
 # name -> (restype, argtypes); every symbol include/eos_b200.h declares
 _P = C.c_void_p
 _ERR = C.POINTER(C.c_char_p)
@@ -73,6 +85,7 @@ SYMBOLS = {
     "eos_b200_free_cstring": (None, [_P]),
     "eos_b200_version": (C.c_char_p, []),
     "eos_b200_encoder_bind": (C.c_int, [_P, C.POINTER(EncoderDesc), C.POINTER(_P), _ERR]),
+    "eos_b200_compact_encoder_bind": (C.c_int, [_P, C.POINTER(CompactEncoderDesc), C.POINTER(_P), _ERR]),
     "eos_b200_encoder_destroy": (None, [_P]),
     "eos_b200_encoder_reserve": (C.c_int, [_P, C.c_int, C.c_int, _ERR]),
     "eos_b200_encoder_run": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P, C.POINTER(Stats), _ERR]),

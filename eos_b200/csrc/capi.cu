@@ -364,6 +364,15 @@ struct EosB200Encoder {
     bool attn_tc = false;        // tensor-memory attention kernel usable (head_dim 64, no window)
     Profiler prof;
     int launches_per_forward = 0;
+    // compact profile (models/default_embedding.go:461-505): role table instead of position / type tables,
+    // rotary positions, no biases, non-affine LayerNorm, per-token normalize + masked mean at the end
+    bool compact = false;
+    int role_vocab = 0;
+    __half* role = nullptr;
+    DenseW outp;                 // optional output projection [output_dim, hidden]
+    float2* rope_cs = nullptr;   // [rope_tokens, hidden / 2] (cos, sin), workspace
+    int rope_tokens = 0;
+    GemmPlan outp_plan{};
 };
 
 namespace {
@@ -395,6 +404,23 @@ void free_workspace(EosB200Encoder* e) {
 }
 
 int ensure_workspace(EosB200Encoder* e, int batch, int tokens, char** err) {
+    if (e->compact && tokens > e->rope_tokens) {
+        // rotary table for positions 0 .. tokens-1: the angle in double, cosine and sine rounded to float, as
+        // ropeRows computes them (runtime/backend/tensor_ops.go:1936-1965)
+        const int D = e->hidden;
+        std::vector<float2> cs((size_t)tokens * (D / 2));
+        for (int t = 0; t < tokens; ++t)
+            for (int c = 0; c + 1 < D; c += 2) {
+                const double theta = (double)t / std::pow(10000.0, (double)c / (double)D);
+                cs[(size_t)t * (D / 2) + c / 2] = make_float2((float)std::cos(theta), (float)std::sin(theta));
+            }
+        CUDA_TRY(cudaStreamSynchronize(e->rt->stream));
+        dev_free(e->rope_cs);
+        e->rope_tokens = 0;
+        CUDA_TRY(dev_alloc(&e->rope_cs, cs.size()));
+        CUDA_TRY(cudaMemcpy(e->rope_cs, cs.data(), cs.size() * sizeof(float2), cudaMemcpyHostToDevice));
+        e->rope_tokens = tokens;
+    }
     const long long elems = (long long)batch * tokens;
     if (batch <= e->cap_batch && elems <= e->cap_elems) return EOS_B200_OK;
     const int nb = batch > e->cap_batch ? batch : e->cap_batch;
@@ -475,6 +501,23 @@ int ensure_workspace(EosB200Encoder* e, int batch, int tokens, char** err) {
             if (!ge.empty()) return fail(err, "encoder layer " + std::to_string(l) + ": " + ge);
         }
     }
+    if (e->compact) {
+        if (e->outp.w != nullptr) {
+            GemmParams p{};
+            p.m_ptr = e->lay.total_rows;
+            p.m_alloc = m;
+            p.n = e->outp.n;
+            p.k = e->outp.k;
+            p.scale = e->outp.scale;
+            p.bias = nullptr;
+            p.out = e->qkv;  // free at that point of the forward; row stride = output_dim
+            p.ldo = e->outp.n;
+            p.mode = kEpiBias;
+            p.status = e->rt->d_status;
+            std::string ge = gemm_make_plan(&e->outp_plan, e->h0, D, e->outp.w, e->outp.ldw, e->outp.int8, p, e->rt->sm_count);
+            if (!ge.empty()) return fail(err, "output projection: " + ge);
+        }
+    }
     return EOS_B200_OK;
 }
 
@@ -489,8 +532,12 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
     pf.launch(kClsLayout, s, [&] { launch_seq_layout(d_mask, batch, tokens, cls, e->lay, s); });
     launches += 4;
     pf.launch(kClsEmbed, s, [&] {
-        launch_embed_ln(d_ids, d_types, e->lay, tokens, e->tok, e->vocab, e->pos, e->max_pos, e->typ, e->type_vocab,
-                        e->eg, e->eb, e->eps, D, e->m_alloc, e->h0, rt->d_status, rt->sm_count, s);
+        if (e->compact)
+            launch_embed_rope(d_ids, d_types, e->lay, tokens, e->tok, e->vocab, e->role, e->role_vocab, e->rope_cs,
+                              e->rope_tokens, D, e->m_alloc, e->h0, rt->d_status, rt->sm_count, s);
+        else
+            launch_embed_ln(d_ids, d_types, e->lay, tokens, e->tok, e->vocab, e->pos, e->max_pos, e->typ, e->type_vocab,
+                            e->eg, e->eb, e->eps, D, e->m_alloc, e->h0, rt->d_status, rt->sm_count, s);
     });
     launches += 1;
     for (int l = 0; l < e->layers; ++l) {
@@ -513,10 +560,22 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
         });
         launches += 7;
     }
-    pf.launch(kClsPool, s, [&] {
-        launch_pool_head(e->h0, e->lay, batch, D, cls, e->head_w, e->head_out, e->pooled, d_out, s);
-    });
-    launches += e->head_w != nullptr ? 2 : 1;
+    if (e->compact) {
+        if (e->outp.w != nullptr) {
+            pf.launch(kClsPool, s, [&] { launch_token_normalize(e->h0, e->lay, D, e->m_alloc, rt->sm_count, s); });
+            pf.launch(kClsGemm, s, [&] { gemm_launch(e->outp_plan, s); });
+            pf.launch(kClsPool, s, [&] { launch_compact_pool(e->qkv, e->lay, batch, tokens, e->outp.n, 0, d_out, s); });
+            launches += 3;
+        } else {
+            pf.launch(kClsPool, s, [&] { launch_compact_pool(e->h0, e->lay, batch, tokens, D, 1, d_out, s); });
+            launches += 1;
+        }
+    } else {
+        pf.launch(kClsPool, s, [&] {
+            launch_pool_head(e->h0, e->lay, batch, D, cls, e->head_w, e->head_out, e->pooled, d_out, s);
+        });
+        launches += e->head_w != nullptr ? 2 : 1;
+    }
     e->launches_per_forward = launches;
     return launches;
 }
@@ -537,6 +596,9 @@ void eos_b200_encoder_destroy(EosB200Encoder* enc) {
     dev_free(enc->eg);
     dev_free(enc->eb);
     dev_free(enc->head_w);
+    dev_free(enc->role);
+    dev_free(enc->rope_cs);
+    free_dense(enc->outp);
     for (auto& w : enc->lw) {
         free_dense(w.qkv);
         free_dense(w.ao);
@@ -636,6 +698,116 @@ int eos_b200_encoder_bind(EosB200Runtime* rt, const EosB200EncoderDesc* d, EosB2
     return EOS_B200_OK;
 }
 
+namespace {
+// An Eos [in, out] matrix as the [out, in] EosB200Matrix the uploader takes (storage in `keep`).
+struct TransposedMatrix {
+    std::vector<int8_t> codes;
+    std::vector<float> dense;
+    EosB200Matrix m{};
+};
+std::string transpose_in_out(const EosB200Matrix& src, int in, int out, const char* name, TransposedMatrix* t) {
+    if (src.rows != in || src.cols != out)
+        return std::string(name) + " weight shape [" + std::to_string(src.rows) + "," + std::to_string(src.cols) +
+               "] does not match [in,out]=[" + std::to_string(in) + "," + std::to_string(out) + "]";
+    t->m = src;
+    t->m.rows = out;
+    t->m.cols = in;
+    if (src.q8_codes != nullptr) {
+        if (src.q8_scales == nullptr) return std::string(name) + ": q8 weight without scales";
+        if (src.n_scales != 1 && src.n_scales != out)
+            return std::string(name) + ": n_scales must be 1 (per tensor) or cols (per output channel)";
+        t->codes.resize((size_t)in * out);
+        for (int i = 0; i < in; ++i)
+            for (int o = 0; o < out; ++o) t->codes[(size_t)o * in + i] = src.q8_codes[(size_t)i * out + o];
+        t->m.q8_codes = t->codes.data();
+    } else if (src.dense != nullptr) {
+        t->dense.resize((size_t)in * out);
+        for (int i = 0; i < in; ++i)
+            for (int o = 0; o < out; ++o) t->dense[(size_t)o * in + i] = src.dense[(size_t)i * out + o];
+        t->m.dense = t->dense.data();
+    } else {
+        return std::string(name) + ": weight has neither q8 codes nor dense values";
+    }
+    return "";
+}
+}  // namespace
+
+int eos_b200_compact_encoder_bind(EosB200Runtime* rt, const EosB200CompactEncoderDesc* d, EosB200Encoder** out,
+                                  char** err) {
+    if (rt == nullptr || d == nullptr || out == nullptr) return fail(err, "compact_encoder_bind: null argument");
+    *out = nullptr;
+    if (d->layers <= 0 || d->heads <= 0 || d->hidden <= 0 || d->intermediate <= 0 || d->vocab <= 0 || d->role_vocab <= 0)
+        return fail(err, "compact_encoder_bind: dimensions must be positive");
+    if (d->hidden % d->heads != 0) return fail(err, "hidden size must be divisible by num_attention_heads");
+    if (d->hidden % 16 != 0 || d->intermediate % 16 != 0)
+        return fail(err, "hidden and intermediate sizes must be multiples of 16");
+    const int hd = d->hidden / d->heads;
+    if (hd > 64 || hd % 2 != 0) return fail(err, "head dimension must be even and at most 64");
+    if (d->hidden > 2048) return fail(err, "hidden size above 2048 is not supported");
+    if (!d->token_embedding || !d->role_embedding || !d->layer) return fail(err, "compact_encoder_bind: missing tensor");
+    const bool project = d->output_dim > 0 && d->output_dim != d->hidden;
+    if (d->output_dim < 0 || (project && d->output_dim % 8 != 0))
+        return fail(err, "compact_encoder_bind: output_dim must be a non-negative multiple of 8");
+    CUDA_TRY(cudaSetDevice(rt->device));
+    EosB200Encoder* e = new EosB200Encoder();
+    e->rt = rt;
+    e->compact = true;
+    e->layers = d->layers;
+    e->hidden = d->hidden;
+    e->heads = d->heads;
+    e->inter = d->intermediate;
+    e->vocab = d->vocab;
+    e->role_vocab = d->role_vocab;
+    e->activation = EOS_B200_ACT_GELU_TANH;
+    e->pooling = EOS_B200_POOL_MASKED_MEAN;
+    e->head_out = project ? d->output_dim : 0;  // sizes the output buffer; there is no BERT-style head
+    e->eps = 1e-5f;
+    const int D = d->hidden, F = d->intermediate;
+    std::string msg;
+    auto step = [&](const std::string& m) {
+        if (msg.empty() && !m.empty()) msg = m;
+    };
+    step(upload_f16(d->token_embedding, (size_t)d->vocab * D, &e->tok));
+    step(upload_f16(d->role_embedding, (size_t)d->role_vocab * D, &e->role));
+    const std::vector<float> ones((size_t)D, 1.0f), zeros((size_t)D, 0.0f);
+    e->lw.resize(d->layers);
+    for (int l = 0; l < d->layers && msg.empty(); ++l) {
+        const EosB200CompactLayer& s = d->layer[l];
+        TransposedMatrix q, k, v, o, up, down;
+        step(transpose_in_out(s.attn_q, D, D, "attention query", &q));
+        step(transpose_in_out(s.attn_k, D, D, "attention key", &k));
+        step(transpose_in_out(s.attn_v, D, D, "attention value", &v));
+        step(transpose_in_out(s.attn_o, D, D, "attention output", &o));
+        step(transpose_in_out(s.ffn_up, D, F, "ffn up", &up));
+        step(transpose_in_out(s.ffn_down, F, D, "ffn down", &down));
+        if (!msg.empty()) {
+            msg = "encoder layer " + std::to_string(l) + " " + msg;
+            break;
+        }
+        LayerW& w = e->lw[l];
+        step(upload_dense({&q.m, &k.m, &v.m}, {nullptr, nullptr, nullptr}, d->weight_mode, &w.qkv));
+        step(upload_dense({&o.m}, {nullptr}, d->weight_mode, &w.ao));
+        step(upload_dense({&up.m}, {nullptr}, d->weight_mode, &w.inter));
+        step(upload_dense({&down.m}, {nullptr}, d->weight_mode, &w.out));
+        step(upload_f32(ones.data(), D, &w.g1));
+        step(upload_f32(zeros.data(), D, &w.b1));
+        step(upload_f32(ones.data(), D, &w.g2));
+        step(upload_f32(zeros.data(), D, &w.b2));
+        if (!msg.empty()) msg = "encoder layer " + std::to_string(l) + " " + msg;
+    }
+    if (msg.empty() && project) {
+        TransposedMatrix p;
+        step(transpose_in_out(d->output_projection, D, d->output_dim, "output projection", &p));
+        if (msg.empty()) step(upload_dense({&p.m}, {nullptr}, d->weight_mode, &e->outp));
+    }
+    if (!msg.empty()) {
+        eos_b200_encoder_destroy(e);
+        return fail(err, msg);
+    }
+    *out = e;
+    return EOS_B200_OK;
+}
+
 int eos_b200_encoder_reserve(EosB200Encoder* enc, int batch, int tokens, char** err) {
     if (enc == nullptr) return fail(err, "encoder_reserve: null encoder");
     if (batch <= 0 || tokens <= 0) return fail(err, "encoder_reserve: batch and tokens must be positive");
@@ -649,7 +821,8 @@ int eos_b200_encoder_run_device(EosB200Encoder* enc, const int32_t* d_ids, const
     if (enc == nullptr || d_ids == nullptr || d_mask == nullptr || d_out == nullptr)
         return fail(err, "bert_embedder expects non-nil input_ids, attention_mask and output");
     if (batch <= 0 || tokens <= 0) return fail(err, "bert_embedder input_ids must be a non-empty [B,T] tensor");
-    if (tokens > enc->max_pos) return fail(err, "bert_embeddings position_ids value out of range (tokens > max_positions)");
+    if (!enc->compact && tokens > enc->max_pos)
+        return fail(err, "bert_embeddings position_ids value out of range (tokens > max_positions)");
     CUDA_TRY(cudaSetDevice(enc->rt->device));
     int rc = ensure_workspace(enc, batch, tokens, err);
     if (rc != EOS_B200_OK) return rc;
@@ -713,7 +886,8 @@ int eos_b200_encoder_run(EosB200Encoder* enc, const int32_t* h_ids, const int32_
     if (enc == nullptr || h_ids == nullptr || h_mask == nullptr || h_out == nullptr)
         return fail(err, "bert_embedder expects non-nil input_ids, attention_mask and output");
     if (batch <= 0 || tokens <= 0) return fail(err, "bert_embedder input_ids must be a non-empty [B,T] tensor");
-    if (tokens > enc->max_pos) return fail(err, "bert_embeddings position_ids value out of range (tokens > max_positions)");
+    if (!enc->compact && tokens > enc->max_pos)
+        return fail(err, "bert_embeddings position_ids value out of range (tokens > max_positions)");
     EosB200Runtime* rt = enc->rt;
     CUDA_TRY(cudaSetDevice(rt->device));
     int rc = ensure_workspace(enc, batch, tokens, err);

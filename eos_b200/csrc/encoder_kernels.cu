@@ -657,6 +657,128 @@ head_l2_kernel(const float* __restrict__ pooled, int dim, const float* __restric
 }
 
 // ------------------------------------------------------------------------------------------
+// compact encoder profile (models/default_embedding.go:461-505)
+// ------------------------------------------------------------------------------------------
+// hidden[r,:] = rope(tok[id] + role[rid]) for every packed row: ropeRows,
+// runtime/backend/tensor_ops.go:1936-1965, with the position t of the row inside its sequence.
+// rope_cs[t * dim/2 + c/2] = (cos, sin) of t / 10000^(c/dim), computed in double on the host.
+template <int kChunks>
+__global__ void __launch_bounds__(256)
+embed_rope_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ roles, const int* __restrict__ row_src,
+                  const int* __restrict__ total_rows, int tokens, const __half* __restrict__ tok, int vocab,
+                  const __half* __restrict__ role_tab, int role_vocab, const float2* __restrict__ rope_cs, int rope_tokens,
+                  int dim, int m_alloc, __half* __restrict__ out, int* status) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+    int rows = *total_rows;
+    if (rows > m_alloc) rows = m_alloc;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps_per_grid) {
+        const int src = row_src[r];
+        const int t = src % tokens;
+        const int id = ids[src];
+        const int ro = roles != nullptr ? roles[src] : 0;
+        int bad = 0;
+        if (id < 0 || id >= vocab) bad = kStatusBadTokenId;
+        else if (ro < 0 || ro >= role_vocab) bad = kStatusBadTypeId;
+        else if (t >= rope_tokens) bad = kStatusBadPosition;
+        if (bad) {
+            if (lane == 0) atomicCAS(status, 0, bad);
+            continue;
+        }
+        const __half* a = tok + (size_t)id * dim;
+        const __half* b = role_tab + (size_t)ro * dim;
+        const float2* cs = rope_cs + (size_t)t * (dim / 2);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            if (col < dim) {
+                float fa[8], fb[8], o[8];
+                unpack8(*reinterpret_cast<const uint4*>(a + col), fa);
+                unpack8(*reinterpret_cast<const uint4*>(b + col), fb);
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const float x0 = fa[i] + fb[i], x1 = fa[i + 1] + fb[i + 1];
+                    const float2 k = cs[(col + i) >> 1];
+                    o[i] = x0 * k.x - x1 * k.y;
+                    o[i + 1] = x0 * k.y + x1 * k.x;
+                }
+                *reinterpret_cast<uint4*>(out + (size_t)r * dim + col) = pack8(o);
+            }
+        }
+    }
+}
+
+// In place: every packed row divided by its L2 norm (normalizeRows, tensor_ops.go:1367-1391; a zero
+// row stays as it is).
+template <int kChunks>
+__global__ void __launch_bounds__(256)
+token_normalize_kernel(__half* __restrict__ x, int dim, int m_alloc, const int* __restrict__ total_rows) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+    int rows = *total_rows;
+    if (rows > m_alloc) rows = m_alloc;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps_per_grid) {
+        float v[kChunks][8];
+        float sq = 0.f;
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            if (col < dim) {
+                unpack8(*reinterpret_cast<const uint4*>(x + (size_t)r * dim + col), v[c]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sq = fmaf(v[c][i], v[c][i], sq);
+            }
+        }
+        sq = warp_sum(sq);
+        if (sq == 0.f) continue;
+        const float inv = 1.0f / sqrtf(sq);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            if (col < dim) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[c][i] *= inv;
+                *reinterpret_cast<uint4*>(x + (size_t)r * dim + col) = pack8(v[c]);
+            }
+        }
+    }
+}
+
+// out[b,:] = mean over the valid tokens of sequence b of (normalize ? row / |row| : row); no valid token
+// -> zeros (meanPoolMaskedTensor, tensor_ops.go:1644-1709, after the per-token normalize of the graph).
+// One CTA per sequence; a thread owns columns c, c + blockDim, ...; rows are visited in token order.
+__global__ void __launch_bounds__(256)
+compact_pool_kernel(const __half* __restrict__ hs, const int* __restrict__ cu_rows, const int* __restrict__ key_count,
+                    int dim, int normalize, float* __restrict__ out) {
+    extern __shared__ float inv_norm[];  // [rows of the sequence] when normalising
+    const int b = blockIdx.x;
+    const int row0 = cu_rows[b];
+    const int n = key_count[b];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    if (normalize) {
+        for (int r = warp; r < n; r += warps) {
+            float sq = 0.f;
+            for (int c = lane; c < dim; c += 32) {
+                const float v = __half2float(hs[(size_t)(row0 + r) * dim + c]);
+                sq = fmaf(v, v, sq);
+            }
+            sq = warp_sum(sq);
+            if (lane == 0) inv_norm[r] = sq == 0.f ? 1.0f : 1.0f / sqrtf(sq);
+        }
+        __syncthreads();
+    }
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        float acc = 0.f;
+        for (int r = 0; r < n; ++r) {
+            float v = __half2float(hs[(size_t)(row0 + r) * dim + c]);
+            if (normalize) v *= inv_norm[r];
+            acc += v;
+        }
+        out[(size_t)b * dim + c] = n > 0 ? acc * (1.0f / (float)n) : 0.f;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // compiled pipeline: gather -> matmul -> normalize (per token) -> masked mean_pool, one launch.
 // One CTA per sequence; masked tokens are skipped (they are excluded from the mean).  Tokens are
 // processed 8 at a time: rows gathered to shared memory, every thread owns output columns.
@@ -819,6 +941,30 @@ void launch_pool_head(const __half* hidden_states, const SeqLayout& lay, int bat
                                               cls_pooling, pooled);
     if (head_w != nullptr)
         head_l2_kernel<<<batch, 256, dim * sizeof(float), stream>>>(pooled, dim, head_w, head_out, out);
+}
+
+void launch_embed_rope(const int32_t* ids, const int32_t* roles, const SeqLayout& lay, int tokens, const __half* tok,
+                       int vocab, const __half* role_tab, int role_vocab, const float2* rope_cs, int rope_tokens, int dim,
+                       int m_alloc, __half* out, int* status, int sm_count, cudaStream_t stream) {
+    dispatch_chunks(dim, [&](auto c) {
+        constexpr int kChunks = decltype(c)::value;
+        embed_rope_kernel<kChunks><<<sm_count * 8, 256, 0, stream>>>(ids, roles, lay.row_src, lay.total_rows, tokens, tok,
+                                                                     vocab, role_tab, role_vocab, rope_cs, rope_tokens,
+                                                                     dim, m_alloc, out, status);
+    });
+}
+
+void launch_token_normalize(__half* x, const SeqLayout& lay, int dim, int m_alloc, int sm_count, cudaStream_t stream) {
+    dispatch_chunks(dim, [&](auto c) {
+        constexpr int kChunks = decltype(c)::value;
+        token_normalize_kernel<kChunks><<<sm_count * 8, 256, 0, stream>>>(x, dim, m_alloc, lay.total_rows);
+    });
+}
+
+void launch_compact_pool(const __half* hidden_states, const SeqLayout& lay, int batch, int tokens, int dim, int normalize,
+                         float* out, cudaStream_t stream) {
+    compact_pool_kernel<<<batch, 256, (size_t)(tokens + 1) * sizeof(float), stream>>>(
+        hidden_states, lay.cu_rows, lay.key_count, dim, normalize, out);
 }
 
 void launch_embed_pooled(const int32_t* tokens, const int32_t* mask, int batch, int tlen, const __half* table,

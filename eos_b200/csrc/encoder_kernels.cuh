@@ -43,6 +43,17 @@ void launch_attention(const __half* qkv, const SeqLayout& lay, int batch, int to
 void launch_pool_head(const __half* hidden_states, const SeqLayout& lay, int batch, int dim, int cls_pooling,
                       const float* head_w, int head_out, float* pooled_scratch, float* out, cudaStream_t stream);
 
+// Compact encoder profile (models/default_embedding.go:461-505).
+// hidden[r,:] = rope(tok[id] + role[role id]) for every packed row; rope_cs is [rope_tokens, dim/2] (cos, sin).
+void launch_embed_rope(const int32_t* ids, const int32_t* roles, const SeqLayout& lay, int tokens, const __half* tok,
+                       int vocab, const __half* role_tab, int role_vocab, const float2* rope_cs, int rope_tokens, int dim,
+                       int m_alloc, __half* out, int* status, int sm_count, cudaStream_t stream);
+// In place per-row L2 normalisation of the packed rows (zero rows untouched).
+void launch_token_normalize(__half* x, const SeqLayout& lay, int dim, int m_alloc, int sm_count, cudaStream_t stream);
+// out [B, dim] fp32 = mean over each sequence's valid tokens of the (optionally L2-normalised) rows.
+void launch_compact_pool(const __half* hidden_states, const SeqLayout& lay, int batch, int tokens, int dim, int normalize,
+                         float* out, cudaStream_t stream);
+
 // Compiled pipeline gather -> matmul -> per-token normalize -> masked mean_pool in one launch.
 // table [vocab, dim] f16, projection [dim, out_dim] f16 (in-major), out [B, out_dim] fp32.
 void launch_embed_pooled(const int32_t* tokens, const int32_t* mask, int batch, int tlen, const __half* table,

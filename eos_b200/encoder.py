@@ -38,7 +38,19 @@ class Q8Weight:
         return c * (s[0] if s.size == 1 else s[:, None])
 
 
-Weight = Union[np.ndarray, Q8Weight]
+@dataclass
+class Q8WeightInOut:
+    """int8 codes in Eos's matmul layout [in, out] + fp32 scales (1 = per tensor, out = per output channel)."""
+    codes: np.ndarray
+    scales: np.ndarray
+
+    def dequantized(self) -> np.ndarray:
+        s = np.asarray(self.scales, np.float32).reshape(-1)
+        c = np.asarray(self.codes, np.int8).astype(np.float32)
+        return c * (s[0] if s.size == 1 else s[None, :])
+
+
+Weight = Union[np.ndarray, Q8Weight, Q8WeightInOut]
 
 
 def _f32(a) -> np.ndarray:
@@ -87,7 +99,7 @@ class Runtime:
 
 def _matrix(w: Weight, keep: list) -> Matrix:
     m = Matrix()
-    if isinstance(w, Q8Weight):
+    if isinstance(w, (Q8Weight, Q8WeightInOut)):
         codes = np.ascontiguousarray(w.codes, dtype=np.int8)
         scales = _f32(w.scales).reshape(-1)
         keep += [codes, scales]
@@ -220,6 +232,49 @@ class BertEmbedder:
             self.close()
         except Exception:
             pass
+
+
+class CompactEmbedder(BertEmbedder):
+    """The native compact q8 encoder profile (models/default_embedding.go:461-505): token + role embeddings, rotary
+    positions, bias-free projections in [in, out] layout, non-affine LayerNorm (epsilon 1e-5), tanh-GELU FFN,
+    per-token L2 normalize, optional output projection, masked mean pool.  `layer_weights` holds, per layer,
+    (attn_q, attn_k, attn_v, attn_o, ffn_up, ffn_down); run(tokens, attention_mask, role_ids)."""
+
+    def __init__(self, rt: Runtime, token_embedding, role_embedding, layer_weights: Sequence[Weight],
+                 num_attention_heads: int, output_projection: Optional[Weight] = None,
+                 weight_mode: int = WEIGHTS_F16_RESIDENT):
+        from ._lib import CompactEncoderDesc, CompactLayer
+        if len(layer_weights) == 0 or len(layer_weights) % 6 != 0:
+            raise ValueError(f"compact encoder expects 6 tensors per layer, got {len(layer_weights)}")
+        self.rt = rt
+        keep: list = []
+        tok, role = _f32(token_embedding), _f32(role_embedding)
+        if tok.ndim != 2 or role.ndim != 2 or tok.shape[1] != role.shape[1]:
+            raise ValueError("token and role embedding tables disagree on the hidden size")
+        keep += [tok, role]
+        layers = len(layer_weights) // 6
+        arr = (CompactLayer * layers)()
+        for l in range(layers):
+            w = layer_weights[l * 6:(l + 1) * 6]
+            for name, mat in zip(("attn_q", "attn_k", "attn_v", "attn_o", "ffn_up", "ffn_down"), w):
+                setattr(arr[l], name, _matrix(mat, keep))
+        d = CompactEncoderDesc()
+        d.layers, d.hidden, d.heads = layers, tok.shape[1], int(num_attention_heads)
+        d.intermediate = arr[0].ffn_up.cols
+        d.vocab, d.role_vocab = tok.shape[0], role.shape[0]
+        d.weight_mode = int(weight_mode)
+        d.token_embedding, d.role_embedding = tok.ctypes.data, role.ctypes.data
+        d.layer = arr
+        self.out_dim = tok.shape[1]
+        if output_projection is not None:
+            d.output_projection = _matrix(output_projection, keep)
+            d.output_dim = d.output_projection.cols
+            self.out_dim = int(d.output_dim)
+        self.handle = C.c_void_p()
+        _lib.call("eos_b200_compact_encoder_bind", rt.handle, C.byref(d), C.byref(self.handle))
+        rt._adopt(self)
+        self.hidden, self.layers, self.heads, self.intermediate = d.hidden, layers, d.heads, d.intermediate
+        self.last_stats = Stats()
 
 
 class EmbedPooledPipeline:

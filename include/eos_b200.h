@@ -155,6 +155,38 @@ EOS_B200_API int eos_b200_encoder_reserve(EosB200Encoder* enc, int batch, int to
  * (tensor_ops.go:1479-1487); an all-masked sequence yields a zero vector. */
 EOS_B200_API int eos_b200_encoder_run(EosB200Encoder* enc, const int32_t* h_ids, const int32_t* h_mask, const int32_t* h_types,
                          int batch, int tokens, float* h_out, EosB200Stats* stats, char** err);
+/* ---- compact encoder profile ----------------------------------------------------------------
+ * The native q8 encoder graph of models/default_embedding.go:461-505 (pipeline embed_pooled_batch):
+ * gather(token_embedding) + gather(role_embedding) -> rope (runtime/backend/tensor_ops.go:1936-1965)
+ * -> per layer { q, k, v = h @ W (no bias); multi-head attention over the unmasked keys
+ * (compactMultiheadAttentionTensor, tensor_ops.go:1867-1924); @ Wo; layernorm(attended + h)
+ * (non-affine, epsilon 1e-5, tensor_ops.go:1393-1421); tanh-GELU FFN (tensor_ops.go:1926-1934);
+ * layernorm(projected + attn_hidden) } -> per-token L2 normalize -> optional output projection ->
+ * masked mean pool (the result is not re-normalised).
+ * Weights are in Eos's matmul layout [in, out] (EosB200Matrix.rows = in, .cols = out); a q8 matrix
+ * has n_scales = 1 (the reference's per-tensor scale) or = cols (per output channel).  The bound
+ * handle is an EosB200Encoder: run / run_device / sync / profile / destroy are the entry points
+ * above, with the role ids passed where the token type ids go. */
+typedef struct {
+    EosB200Matrix attn_q, attn_k, attn_v, attn_o;  /* [hidden, hidden] */
+    EosB200Matrix ffn_up;                          /* [hidden, intermediate] */
+    EosB200Matrix ffn_down;                        /* [intermediate, hidden] */
+} EosB200CompactLayer;
+
+typedef struct {
+    int32_t layers, hidden, heads, intermediate;
+    int32_t vocab, role_vocab;
+    int32_t output_dim;            /* 0 or hidden: no output projection */
+    int32_t weight_mode;           /* EOS_B200_WEIGHTS_* */
+    const float* token_embedding;  /* [vocab, hidden], dequantised values */
+    const float* role_embedding;   /* [role_vocab, hidden] */
+    const EosB200CompactLayer* layer;
+    EosB200Matrix output_projection;  /* [hidden, output_dim]; ignored without a projection */
+} EosB200CompactEncoderDesc;
+
+EOS_B200_API int eos_b200_compact_encoder_bind(EosB200Runtime* rt, const EosB200CompactEncoderDesc* desc, EosB200Encoder** out,
+                                               char** err);
+
 /* Same forward with inputs and output resident in device memory; enqueued on `stream`
  * (a cudaStream_t; NULL = the runtime's stream) without synchronising.  The device status word
  * is read by eos_b200_encoder_sync. */

@@ -921,3 +921,48 @@ EOS_ORACLE_API void eos_oracle_cosine_rows(const float *query, const float *docs
         out[r] = denom == 0.0 ? 0.0f : (float)(dot / denom);
     }
 }
+
+/* ropeRows: runtime/backend/tensor_ops.go:1936-1965.  `in` is [rows, cols]; the position of row r is
+ * r % seq_rows (seq_rows = rows for a rank-2 input, = T for a [B, T, cols] input); the angle is computed
+ * in double and its cosine / sine rounded to float before the rotation of each (even, odd) pair. */
+EOS_ORACLE_API void eos_oracle_rope_rows(const float *in, int64_t rows, int seq_rows, int cols, float *out) {
+    memcpy(out, in, sizeof(float) * (size_t)rows * (size_t)cols);
+    for (int64_t r = 0; r < rows; r++) {
+        const int64_t pos = r % seq_rows;
+        for (int c = 0; c + 1 < cols; c += 2) {
+            const double theta = (double)pos / pow(10000.0, (double)c / (double)cols);
+            const float cos_t = (float)cos(theta), sin_t = (float)sin(theta);
+            const float x0 = in[r * cols + c], x1 = in[r * cols + c + 1];
+            out[r * cols + c] = x0 * cos_t - x1 * sin_t;
+            out[r * cols + c + 1] = x0 * sin_t + x1 * cos_t;
+        }
+    }
+}
+
+/* layerNormRows (non-affine, epsilon 1e-5, float statistics): runtime/backend/tensor_ops.go:1393-1421. */
+EOS_ORACLE_API void eos_oracle_layernorm_rows(const float *in, int64_t rows, int cols, float *out) {
+    for (int64_t r = 0; r < rows; r++) {
+        const float *x = in + r * (int64_t)cols;
+        float mean = 0.0f;
+        for (int c = 0; c < cols; c++) mean += x[c];
+        mean /= (float)cols;
+        float variance = 0.0f;
+        for (int c = 0; c < cols; c++) {
+            const float centered = x[c] - mean;
+            variance += centered * centered;
+        }
+        variance /= (float)cols;
+        const float inv_std = (float)(1.0 / sqrt((double)variance + 1e-5));
+        for (int c = 0; c < cols; c++) out[r * (int64_t)cols + c] = (x[c] - mean) * inv_std;
+    }
+}
+
+/* geluTensor with its float intermediates: runtime/backend/tensor_ops.go:1926-1934. */
+EOS_ORACLE_API void eos_oracle_gelu_tanh_rows(const float *in, int64_t n, float *out) {
+    for (int64_t i = 0; i < n; i++) {
+        const float x = in[i];
+        const float cubic = x * x * x;
+        const float inner = 0.7978845608f * (x + 0.044715f * cubic);
+        out[i] = 0.5f * x * (1.0f + (float)tanh((double)inner));
+    }
+}

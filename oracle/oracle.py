@@ -346,3 +346,50 @@ def rerank(query, docs, candidates, k: int):
         return np.empty(0, np.int64), np.empty(0, np.float32)
     scores = dot_rows(query, _f32(docs)[cand])
     return topk_merge(np.asarray(cand, np.int64), scores, k)
+
+
+def rope_rows(x):
+    a = _f32(x)
+    cols = a.shape[-1]
+    rows = a.size // cols
+    seq_rows = a.shape[1] if a.ndim == 3 else rows
+    out = np.empty_like(a)
+    lib().eos_oracle_rope_rows(_p(a), C.c_int64(rows), C.c_int(seq_rows), C.c_int(cols), _p(out))
+    return out
+
+
+def layernorm_rows(x):
+    a = _f32(x)
+    cols = a.shape[-1]
+    out = np.empty_like(a)
+    lib().eos_oracle_layernorm_rows(_p(a), C.c_int64(a.size // cols), C.c_int(cols), _p(out))
+    return out
+
+
+def gelu_tanh(x):
+    a = _f32(x)
+    out = np.empty_like(a)
+    lib().eos_oracle_gelu_tanh_rows(_p(a), C.c_int64(a.size), _p(out))
+    return out
+
+
+def compact_encoder(tokens, mask, role_ids, token_embedding, role_embedding, layers, heads: int,
+                    output_projection=None, workers: int = 1):
+    """The native compact encoder graph, step by step as models/default_embedding.go:461-505 emits it:
+    gather + gather -> add -> rope -> per layer { q, k, v = hidden @ W ([in, out], no bias); multi-head attention
+    over the unmasked keys; @ Wo; layernorm(attended + hidden); tanh-GELU FFN; layernorm(projected + attn_hidden) }
+    -> per-token normalize -> optional output projection -> masked mean pool.  `layers` holds
+    (wq, wk, wv, wo, w_up, w_down) per layer as dequantised fp32 [in, out] matrices."""
+    tokens = _i32(tokens)
+    mask = _i32(mask)
+    hidden = rope_rows(gather(token_embedding, tokens) + gather(role_embedding, _i32(role_ids)))
+    for wq, wk, wv, wo, w_up, w_down in layers:
+        q, k, v = matmul(hidden, wq), matmul(hidden, wk), matmul(hidden, wv)
+        mixed = bert_attention(q, k, v, mask, heads, workers)
+        attn_hidden = layernorm_rows(matmul(mixed, wo) + hidden)
+        activated = gelu_tanh(matmul(attn_hidden, w_up))
+        hidden = layernorm_rows(matmul(activated, w_down) + attn_hidden)
+    normalized = normalize_rows(hidden)
+    if output_projection is not None:
+        normalized = matmul(normalized, output_projection)
+    return mean_pool_masked(normalized, mask)

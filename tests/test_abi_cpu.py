@@ -34,6 +34,8 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(_lib.Matrix) == 40
     assert C.sizeof(_lib.EncoderLayer) == 6 * 40 + 10 * 8
     assert _lib.EncoderDesc.epsilon.offset == 48
+    assert C.sizeof(_lib.CompactLayer) == 6 * 40
+    assert C.sizeof(_lib.CompactEncoderDesc) == 8 * 4 + 3 * 8 + 40
     assert C.sizeof(_lib.Stats) == 40
     assert C.sizeof(_lib.EncoderTimes) == 60
 

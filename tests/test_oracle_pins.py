@@ -195,3 +195,17 @@ def test_dense_rows_and_rerank_restatement():
     assert ids.tolist() == [1, 0, 4] and scores.tolist() == [8.0, 3.0, 3.0]             # tie 0 / 4: smaller id first
     ids, _ = O.rerank(q, docs, [-1, 17], 3)
     assert ids.size == 0
+
+
+def test_compact_path_rows_match_reference_expectations():
+    """Expected values copied from runtime/backend/tensor_ops_test.go: TestLayerNormRows(:465-475),
+    TestLayerNormRowsBatched (:477-491), TestRoPERows (:646-656), TestRoPERowsBatchedResetsPositionPerBatch (:658-672)."""
+    from oracle import oracle as O
+    ln = O.layernorm_rows(np.array([[2, 4], [6, 8]], np.float32))
+    assert np.allclose(ln, [[-0.999995, 0.999995], [-0.999995, 0.999995]], atol=1e-6)
+    ln3 = O.layernorm_rows(np.array([[[2, 4], [6, 8]], [[1, 3], [5, 7]]], np.float32))
+    assert np.allclose(ln3, np.tile([-0.999995, 0.999995], (2, 2, 1)), atol=1e-6)
+    r = O.rope_rows(np.array([[1, 0], [0, 1]], np.float32))
+    assert np.allclose(r, [[1, 0], [-0.84147096, 0.5403023]], atol=1e-7)
+    r3 = O.rope_rows(np.array([[[1, 0], [0, 1]], [[1, 0], [0, 1]]], np.float32))
+    assert np.allclose(r3, np.tile([[1, 0], [-0.84147096, 0.5403023]], (2, 1, 1)), atol=1e-7)
