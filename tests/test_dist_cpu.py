@@ -101,3 +101,41 @@ def test_bounds_and_key_round_trip():
     assert b[1] > b[0]
     e_ids, e_sc = D.decode_keys(D.encode_keys(np.array([-1]), np.array([3.0], np.float32)))
     assert e_ids[0] == -1 and e_sc[0] == -np.inf
+
+
+def test_batching_helpers_follow_the_reference():
+    """buildMaskedTokenInputs (runtime/embedding_model.go:1457-1495), padPretrainedBERTBatchEncodings
+    (pretrained_bert_retrieval_vector_export.go:615-646), buildTokenBatch (inference.go:323-339)."""
+    import pytest
+    from eos_b200 import batching
+    tok, mask = batching.build_masked_token_inputs([[5, 6, 0, 0], [7], [8, 0, 9]], pad_id=0)
+    assert tok.tolist() == [[5, 6, 0, 0], [7, 0, 0, 0], [8, 0, 9, 0]]
+    assert mask.tolist() == [[1, 1, 0, 0], [1, 0, 0, 0], [1, 1, 1, 0]]   # trailing pads masked, inner pad kept
+    with pytest.raises(ValueError):
+        batching.build_masked_token_inputs([], 0)
+    with pytest.raises(ValueError):
+        batching.build_masked_token_inputs([[1], []], 0)
+    ids, m, ty = batching.pad_bert_batch([[101, 7, 102], [101, 102]], [[1, 1, 1], [1, 1]], [[0, 0, 0], [0, 1]], 4, pad_id=9)
+    assert ids.tolist() == [[101, 7, 102, 9], [101, 102, 9, 9]]
+    assert m.tolist() == [[1, 1, 1, 0], [1, 1, 0, 0]] and ty.tolist() == [[0, 0, 0, 0], [0, 1, 0, 0]]
+    with pytest.raises(ValueError):
+        batching.pad_bert_batch([[1, 2, 3]], [[1, 1, 1]], [[0, 0, 0]], 2, 0)
+    with pytest.raises(ValueError):
+        batching.pad_bert_batch([[1, 2]], [[1]], [[0, 0]], 4, 0)
+    assert batching.build_token_batch([[1, 2], [3, 4]]).tolist() == [[1, 2], [3, 4]]
+    with pytest.raises(ValueError):
+        batching.build_token_batch([[1, 2], [3]])
+
+
+def test_split_by_length_balances_valid_tokens():
+    from eos_b200 import batching
+    rng = np.random.default_rng(0)
+    lengths = rng.integers(64, 513, size=1024)
+    for world in (1, 2, 4, 8):
+        parts = batching.split_by_length(lengths, world)
+        assert sorted(np.concatenate(parts).tolist()) == list(range(1024))
+        tokens = [int(lengths[p].sum()) for p in parts]
+        assert max(len(p) for p in parts) - min(len(p) for p in parts) <= 1
+        assert max(tokens) - min(tokens) <= 0.01 * sum(tokens) / world + 512
+        inv = np.argsort(np.concatenate(parts))
+        assert (np.concatenate(parts)[inv] == np.arange(1024)).all()
