@@ -175,7 +175,8 @@ def workload_config(world: int) -> dict:
                         "weights, f16 activations, fp32 accumulate; batch 1024 x T=512 per GPU, lengths uniform "
                         "64..512, masked mean-pool + 768->768 head + L2",
             "per_gpu_batch": ENC_BATCH, "global_batch": ENC_BATCH * world, "seq_len": ENC_TOKENS,
-            "sharding": f"data-parallel x{world}, no collective on the data path",
+            "sharding": f"data-parallel x{world}: length-balanced slices of one seeded global batch, no collective on "
+                        "the data path",
             "l2_policy": "inputs_larger_than_l2 (activations of one step exceed 126 MB many times over)"}
 
 
@@ -185,6 +186,7 @@ def run_ours(args, rank: int, world: int, local: int):
     import torch.distributed as dist
 
     import eos_b200
+    from eos_b200 import batching
     from eos_b200 import encoder as encoder_mod
     from eos_b200 import synth
     from eos_b200 import turboquant as tq
@@ -237,7 +239,12 @@ def run_ours(args, rank: int, world: int, local: int):
     weights = synth.make_q8_encoder(seed=301, **ENC)
     wmode = encoder_mod.WEIGHTS_F16_RESIDENT if args.weight_mode == "f16_resident" else encoder_mod.WEIGHTS_Q8_SMEM_DEQUANT
     enc = eos_b200.BertEmbedder(rt, weight_mode=wmode, **weights)
-    ids, mask, lengths = synth.make_batch(ENC_BATCH, ENC_TOKENS, ENC["vocab"], ENC_MIN_LEN, ENC_TOKENS, 303 + rank)
+    # one seeded global batch of 1024 x world sequences; ranks take length-balanced slices of it (sequences are
+    # independent, so the split needs no collective and every rank sees nearly the same number of valid tokens)
+    g_ids, g_mask, g_lengths = synth.make_batch(ENC_BATCH * world, ENC_TOKENS, ENC["vocab"], ENC_MIN_LEN, ENC_TOKENS, 303)
+    rows = batching.split_by_length(g_lengths, world)[rank]
+    ids, mask, lengths = np.ascontiguousarray(g_ids[rows]), np.ascontiguousarray(g_mask[rows]), g_lengths[rows]
+    del g_ids, g_mask
     enc.reserve(ENC_BATCH, ENC_TOKENS)
     d_ids, d_mask = torch.from_numpy(ids).cuda(), torch.from_numpy(mask).cuda()
     d_out = torch.empty((ENC_BATCH, ENC["head_out"]), dtype=torch.float32, device="cuda")
