@@ -634,25 +634,60 @@ pool_l2_kernel(const __half* __restrict__ hs, const int* __restrict__ cu_rows, c
     }
 }
 
+// Projection head: out[b,:] = l2norm(pooled[b,:] x W), W [dim, out_dim] in-major, fp32 accumulate in input order
+// (PretrainedBERTProjectionHead.Apply, runtime/pretrained_bert_projection_head.go:84-100).  A CTA serves kHeadRows
+// batch rows so that every weight it reads is used kHeadRows times.
+constexpr int kHeadRows = 8;
 __global__ void __launch_bounds__(256)
-head_l2_kernel(const float* __restrict__ pooled, int dim, const float* __restrict__ w, int out_dim,
+head_l2_kernel(const float* __restrict__ pooled, int batch, int dim, const float* __restrict__ w, int out_dim,
                float* __restrict__ out) {
-    extern __shared__ float vec[];
+    extern __shared__ float vec[];  // [kHeadRows][dim]
     __shared__ float red[32];
-    const int b = blockIdx.x;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) vec[i] = pooled[(size_t)b * dim + i];
-    __syncthreads();
-    float sq = 0.f;
-    for (int j = threadIdx.x; j < out_dim; j += blockDim.x) {
-        float acc = 0.f;
-        for (int i = 0; i < dim; ++i) acc = fmaf(vec[i], w[(size_t)i * out_dim + j], acc);
-        out[(size_t)b * out_dim + j] = acc;
-        sq += acc * acc;
+    const int b0 = blockIdx.x * kHeadRows;
+    const int nb = batch - b0 < kHeadRows ? batch - b0 : kHeadRows;
+    for (int i = threadIdx.x; i < kHeadRows * dim; i += blockDim.x) {
+        const int r = i / dim;
+        vec[i] = r < nb ? pooled[(size_t)(b0 + r) * dim + (i - r * dim)] : 0.f;
     }
-    const float tot = block_sum(sq, red);
-    if (tot != 0.f) {
-        const float sc = 1.0f / sqrtf(tot);
-        for (int j = threadIdx.x; j < out_dim; j += blockDim.x) out[(size_t)b * out_dim + j] *= sc;
+    __syncthreads();
+    float sq[kHeadRows];
+#pragma unroll
+    for (int r = 0; r < kHeadRows; ++r) sq[r] = 0.f;
+    for (int j = threadIdx.x; j < out_dim; j += blockDim.x) {
+        float acc[kHeadRows];
+#pragma unroll
+        for (int r = 0; r < kHeadRows; ++r) acc[r] = 0.f;
+        // eight weight loads in flight per thread (the loop is bound by their L2 latency otherwise)
+        int i = 0;
+        for (; i + 8 <= dim; i += 8) {
+            float wv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) wv[u] = __ldg(w + (size_t)(i + u) * out_dim + j);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+#pragma unroll
+                for (int r = 0; r < kHeadRows; ++r) acc[r] = fmaf(vec[r * dim + i + u], wv[u], acc[r]);
+            }
+        }
+        for (; i < dim; ++i) {
+            const float wv = __ldg(w + (size_t)i * out_dim + j);
+#pragma unroll
+            for (int r = 0; r < kHeadRows; ++r) acc[r] = fmaf(vec[r * dim + i], wv, acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < kHeadRows; ++r) {
+            if (r < nb) out[(size_t)(b0 + r) * out_dim + j] = acc[r];
+            sq[r] += acc[r] * acc[r];
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kHeadRows; ++r) {
+        const float tot = block_sum(sq[r], red);
+        __syncthreads();
+        if (r < nb && tot != 0.f) {
+            const float sc = 1.0f / sqrtf(tot);
+            for (int j = threadIdx.x; j < out_dim; j += blockDim.x) out[(size_t)(b0 + r) * out_dim + j] *= sc;
+        }
     }
 }
 
@@ -940,7 +975,8 @@ void launch_pool_head(const __half* hidden_states, const SeqLayout& lay, int bat
     pool_l2_kernel<<<batch, 256, 0, stream>>>(hidden_states, lay.cu_rows, lay.key_count, lay.cls_row, dim,
                                               cls_pooling, pooled);
     if (head_w != nullptr)
-        head_l2_kernel<<<batch, 256, dim * sizeof(float), stream>>>(pooled, dim, head_w, head_out, out);
+        head_l2_kernel<<<(batch + kHeadRows - 1) / kHeadRows, 256, (size_t)kHeadRows * dim * sizeof(float), stream>>>(
+            pooled, batch, dim, head_w, head_out, out);
 }
 
 void launch_embed_rope(const int32_t* ids, const int32_t* roles, const SeqLayout& lay, int tokens, const __half* tok,
