@@ -91,10 +91,13 @@ struct Cfg {
     static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
 };
 
-template <bool kBInt8, bool kPair>
+// kMode >= 0 fixes the epilogue at compile time (the one-CTA f16 kernel, which serves the encoder: the residual
+// registers and the activation code of the other modes disappear); kMode < 0 reads it from the parameters.
+template <bool kBInt8, bool kPair, int kMode>
 __global__ void __launch_bounds__(Cfg<kBInt8, kPair>::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, GemmParams p) {
     using C = Cfg<kBInt8, kPair>;
+    const int mode = kMode >= 0 ? kMode : p.mode;
     constexpr int kStagesAB = C::kStagesAB;
     constexpr int kEpilogueWarps = C::kEpilogueWarps;
     constexpr int kWarpCols = C::kWarpCols;
@@ -384,7 +387,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             // coalesced access pattern of the slab copies: instruction i covers rows 8i .. 8i+7, 64 bytes each
             // slab layout: row pitch 64 B, 16-byte chunk c of row r at position c ^ ((r >> 1) & 3)
             const int crow = lane >> 2, cchunk = lane & 3;
-            const bool residual = p.mode == kEpiBiasResidual;
+            const bool residual = mode == kEpiBiasResidual;
             constexpr int kSlabs = kWarpCols / kSlabCols;
 
             // residual of the next slab is requested one slab ahead (the first one before the accumulator
@@ -454,10 +457,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         v[j] = fmaf(__uint_as_float(r[j]), f.x, f.y);
                         v[j + 1] = fmaf(__uint_as_float(r[j + 1]), f.z, f.w);
                     }
-                    if (p.mode == kEpiBiasGeluErf) {
+                    if (mode == kEpiBiasGeluErf) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = gelu_erf_fast(v[j]);
-                    } else if (p.mode == kEpiBiasGeluTanh) {
+                    } else if (mode == kEpiBiasGeluTanh) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
                     }
@@ -586,13 +589,22 @@ cudaLaunchConfig_t pair_launch_config(int grid, cudaStream_t stream, cudaLaunchA
 }  // namespace
 
 std::string gemm_global_init() {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true, false, -1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg<true, false>::kSmemBytes);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, false, kEpiBias>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg<false, false>::kSmemBytes);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, false, kEpiBiasGeluErf>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<false, false>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, false, kEpiBiasResidual>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<false, false>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, false, kEpiBiasGeluTanh>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<false, false>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, true, -1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg<false, true>::kSmemBytes);
     if (e != cudaSuccess) return std::string("cudaFuncSetAttribute(gemm_tc_kernel): ") + cudaGetErrorString(e);
     if (g_pair_clusters < 0) {
@@ -604,7 +616,7 @@ std::string gemm_global_init() {
             if (cudaGetDevice(&dev) == cudaSuccess &&
                 cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms >= 2) {
                 cudaLaunchConfig_t cfg = pair_launch_config(sms & ~1, nullptr, &attr);
-                if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<false, true>, &cfg) == cudaSuccess)
+                if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<false, true, -1>, &cfg) == cudaSuccess)
                     g_pair_clusters = clusters;
                 else
                     (void)cudaGetLastError();
@@ -652,13 +664,27 @@ void gemm_launch(const GemmPlan& plan, cudaStream_t stream) {
     if (plan.pair) {
         cudaLaunchAttribute attr;
         cudaLaunchConfig_t cfg = pair_launch_config(plan.grid, stream, &attr);
-        cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true>, plan.tm_a, plan.tm_b, plan.p);
+        cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, -1>, plan.tm_a, plan.tm_b, plan.p);
     } else if (plan.b_int8) {
-        gemm_tc_kernel<true, false><<<plan.grid, Cfg<true, false>::kThreads, Cfg<true, false>::kSmemBytes, stream>>>(
+        gemm_tc_kernel<true, false, -1><<<plan.grid, Cfg<true, false>::kThreads, Cfg<true, false>::kSmemBytes, stream>>>(
             plan.tm_a, plan.tm_b, plan.p);
     } else {
-        gemm_tc_kernel<false, false><<<plan.grid, Cfg<false, false>::kThreads, Cfg<false, false>::kSmemBytes, stream>>>(
-            plan.tm_a, plan.tm_b, plan.p);
+        constexpr int kT = Cfg<false, false>::kThreads;
+        constexpr uint32_t kS = Cfg<false, false>::kSmemBytes;
+        switch (plan.p.mode) {
+            case kEpiBiasGeluErf:
+                gemm_tc_kernel<false, false, kEpiBiasGeluErf><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                break;
+            case kEpiBiasResidual:
+                gemm_tc_kernel<false, false, kEpiBiasResidual><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                break;
+            case kEpiBiasGeluTanh:
+                gemm_tc_kernel<false, false, kEpiBiasGeluTanh><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                break;
+            default:
+                gemm_tc_kernel<false, false, kEpiBias><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                break;
+        }
     }
 }
 
