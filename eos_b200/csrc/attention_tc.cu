@@ -11,9 +11,9 @@
 //   warp 0       TMA producer: Q tile, then K tiles and V tiles (128 rows x 64, 128B swizzle) into rings.
 //   warp 1       MMA issuer: S_j = Q K_j^T per key tile j (fp32, 128 TMEM columns each), then
 //                O += P_j V_j (V as an MN-major operand, straight from the row-major tile TMA
-//                delivered), O reusing S_0's columns.  Work is cut into sub-items of at most two key
-//                tiles = half of tensor memory, so the S phase of the next sub-item is issued before
-//                the P V phase of the current one and two sub-items are always in flight.
+//                delivered), O reusing the first 80 of S's columns.  Work is cut into sub-items of one key
+//                tile = a quarter of tensor memory; the S phase runs two sub-items ahead of the P V phase,
+//                so four sub-items are in flight per SM (S ready, in softmax, P V running, being retired).
 //                The row sums l = P 1 come out of the same MMA: its B operand is [V | ones] (N = 80), so
 //                they are the fp32 sums of exactly the f16 probabilities that multiply V.
 //   warps 4-19   softmax (thread = query row, four warps per row split the columns of every tile): pass A
@@ -23,8 +23,8 @@
 //                Warps whose 32 query rows are padding of a sequence's last query tile only keep the
 //                barrier protocol.
 // All scores of a sub-item are resident in TMEM before any probability is formed, so O is never
-// rescaled in place; a sequence longer than 256 keys is two sub-items whose partial (O, m, l) are
-// merged in registers.  All mbarrier waits are bounded (abort flag + status word).
+// rescaled in place; a sequence longer than 128 keys is several sub-items whose partial (O, m, l) are
+// merged in registers when they are retired.  All mbarrier waits are bounded (abort flag + status word).
 #include "attention_tc.cuh"
 
 #include "common.cuh"
@@ -52,7 +52,7 @@ constexpr int kSoftmaxWarps = 4 * kParts;
 constexpr int kPartCols = 128 / kParts;          // S columns of one tile per softmax thread
 constexpr int kPartOut = 64 / kParts;            // O columns per softmax thread
 constexpr int kAtThreads = (4 + kSoftmaxWarps) * 32;
-constexpr int kQStages = 2;
+constexpr int kQStages = 3;
 constexpr int kKvStages = 6;
 constexpr uint32_t kTileBytes = 128 * 64 * 2;   // 16 KB: Q, K_j or V_j
 constexpr uint32_t kPBytes = 128 * 128 * 2;     // 32 KB: one P tile (two 128x64 blocks)
@@ -62,7 +62,7 @@ constexpr uint32_t kOffP = kOffKv + kKvStages * kTileBytes;
 constexpr uint32_t kOffOnes = kOffP + 2 * kPBytes;              // 16 x 64 f16 of 1.0: B operand of the row-sum MMA
 constexpr uint32_t kOffRed = kOffOnes + 2048;                   // 2 buffers x kParts x 128 floats: row max exchange
 constexpr uint32_t kOffBars = kOffRed + 2 * kParts * 128 * 4;
-constexpr uint32_t kNumBars = 2 * kQStages + 2 * kKvStages + 4 + 2 + 2 + 2 + 2;
+constexpr uint32_t kNumBars = 2 * kQStages + 2 * kKvStages + 4 + 4 + 4 + 2 + 2;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
 constexpr uint32_t kAtSmemBytes = kOffMisc + 16 + 1024;
 
@@ -86,9 +86,9 @@ __device__ __forceinline__ WorkItem decode_item(const int4 q, int head) {
     return it;
 }
 
-// A work item is processed as one or two sub-items of at most two key tiles (256 keys): a sub-item
-// needs only half of tensor memory, so two of them are in flight per SM; the two partial softmax
-// results of a long sequence are merged in registers (same rule as split-key flash decoding).
+// A work item is processed as sub-items of one key tile (128 keys) each: a sub-item needs a quarter of
+// tensor memory, so four of them are in flight per SM; the partial softmax results of a sequence with
+// more than 128 keys are merged in registers (same rule as split-key flash decoding).
 // The walker keeps the descriptor of the item after the current one in flight (loaded one item
 // ahead), so that stepping to the next item never waits for global memory.
 struct Walker {
@@ -121,15 +121,10 @@ struct Walker {
             prefetch();
         }
     }
-    // copy of the position without the in-flight descriptor (touching it would wait for the load)
-    __device__ __forceinline__ void follow(const Walker& o) {
-        w = o.w; total = o.total; qi = o.qi; head = o.head; step_q = o.step_q; step_h = o.step_h; heads = o.heads;
-        info = o.info; sub = o.sub; item_no = o.item_no; wi = o.wi;
-    }
     __device__ __forceinline__ bool valid() const { return w < total; }
-    __device__ __forceinline__ int nsub() const { return wi.ntiles > 2 ? 2 : 1; }
-    __device__ __forceinline__ int tile0() const { return sub * 2; }
-    __device__ __forceinline__ int nt() const { const int r = wi.ntiles - sub * 2; return r > 2 ? 2 : (r < 0 ? 0 : r); }
+    __device__ __forceinline__ int nsub() const { return wi.ntiles > 1 ? wi.ntiles : 1; }
+    __device__ __forceinline__ int tile0() const { return sub; }
+    __device__ __forceinline__ int nt() const { return sub < wi.ntiles ? 1 : 0; }  // 0: a sequence without keys
     __device__ __forceinline__ bool first_sub() const { return sub == 0; }
     __device__ __forceinline__ bool last_sub() const { return sub + 1 == nsub(); }
     __device__ __forceinline__ void next() {
@@ -150,10 +145,6 @@ struct Walker {
 
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[16]) { tmem_ld_32x16(taddr, v); }
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[32]) { tmem_ld_32x32(taddr, v); }
-__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[64]) {
-    tmem_ld_32x32(taddr, reinterpret_cast<uint32_t(&)[32]>(v[0]));
-    tmem_ld_32x32(taddr + 32, reinterpret_cast<uint32_t(&)[32]>(v[32]));
-}
 
 // 2^x for x <= 0 on the FMA and integer pipes (no MUFU): round-to-nearest split x = n + f with
 // |f| <= 0.5 by the 1.5 * 2^23 trick, cubic for 2^f (maximum relative error 7.5e-5, a third of
@@ -168,8 +159,8 @@ __device__ __forceinline__ float exp2_fma(float x) {
     p = fmaf(p, f, 0.9999281167984009f);
     return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
-// A pair of probabilities as packed f16.  Every third pair is computed on the FMA pipe instead of the
-// MUFU pipe (16 ex2 per clock per SM): measured 1.4% faster than all-MUFU, every second pair is slower.
+// A pair of probabilities as packed f16.  Every fourth pair is computed on the FMA pipe instead of the
+// MUFU pipe (16 ex2 per clock per SM): measured 4% faster than all-MUFU; every third pair 2%, every second slower.
 __device__ __forceinline__ uint32_t exp2_pair_fma(float x0, float x1) {
     __half2 h = __floats2half2_rn(exp2_fma(x0), exp2_fma(x1));
     return *reinterpret_cast<uint32_t*>(&h);
@@ -183,7 +174,7 @@ __device__ __forceinline__ uint32_t ex2_f16x2(float x0, float x1) {
 }
 // pair_idx is a compile-time constant after unrolling
 __device__ __forceinline__ uint32_t exp2_pair(int pair_idx, float x0, float x1) {
-    return (pair_idx % 3) == 2 ? exp2_pair_fma(x0, x1) : ex2_f16x2(x0, x1);
+    return (pair_idx % 4) == 3 ? exp2_pair_fma(x0, x1) : ex2_f16x2(x0, x1);
 }
 
 __global__ void __launch_bounds__(kAtThreads, 1)
@@ -202,11 +193,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
     auto kv_full = [&](int s) { return bar0 + 8u * (2 * kQStages + s); };
     auto kv_empty = [&](int s) { return bar0 + 8u * (2 * kQStages + kKvStages + s); };
     const uint32_t bar1 = bar0 + 8u * (2 * kQStages + 2 * kKvStages);
-    auto s_full = [&](int h, int t) { return bar1 + 8u * (h * 2 + t); };   // [half][tile]
-    auto p_full = [&](int s) { return bar1 + 8u * (4 + s); };
-    auto p_empty = [&](int s) { return bar1 + 8u * (6 + s); };
-    auto o_full = [&](int h) { return bar1 + 8u * (8 + h); };
-    auto half_free = [&](int h) { return bar1 + 8u * (10 + h); };
+    auto s_full = [&](int slot) { return bar1 + 8u * slot; };             // [slot]: S of the sub-item is in tensor memory
+    auto o_full = [&](int slot) { return bar1 + 8u * (4 + slot); };       // its O is complete
+    auto slot_free = [&](int slot) { return bar1 + 8u * (8 + slot); };    // its O has been read: the slot may be reused
+    auto p_full = [&](int s) { return bar1 + 8u * (12 + s); };
+    auto p_empty = [&](int s) { return bar1 + 8u * (14 + s); };
 
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
@@ -224,13 +215,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
             mbar_init(kv_full(s), 1);
             mbar_init(kv_empty(s), 1);
         }
-        for (int h = 0; h < 2; ++h) {
-            mbar_init(s_full(h, 0), 1);
-            mbar_init(s_full(h, 1), 1);
-            mbar_init(p_full(h), kSoftmaxWarps);
-            mbar_init(p_empty(h), 1);
-            mbar_init(o_full(h), 1);
-            mbar_init(half_free(h), kSoftmaxWarps);
+        for (int slot = 0; slot < 4; ++slot) {
+            mbar_init(s_full(slot), 1);
+            mbar_init(o_full(slot), 1);
+            mbar_init(slot_free(slot), kSoftmaxWarps);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(p_full(b), kSoftmaxWarps);
+            mbar_init(p_empty(b), 1);
         }
         mbar_fence_init();
         tma_prefetch_desc(&tm_qkv);
@@ -250,7 +242,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        // order of the K/V ring = order of consumption by the MMA warp: K(0); then K(n+1), V(n) for n = 0, 1, ...
         if (lane == 0) {
             uint32_t kvc = 0;
             bool ok = true;
@@ -285,31 +276,33 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                     tma_prefetch_l2_2d(&tm_qkv, 2 * hidden + wk.wi.head * 64, y);
                 }
             };
+            // order of the K/V ring = order of consumption by the MMA warp: K(0), K(1); then K(n+2), V(n) for n = 0, 1, ...
             constexpr int kL2Ahead = 2;
-            Walker cur, nxt, far;
-            cur.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info);
-            nxt = cur;
-            if (cur.valid()) {
-                ok = load_q(cur) && load_kv(cur, 1);
-                nxt.next();
-            }
-            far = nxt;
+            Walker vs, ks, far;   // V loads, K loads (two sub-items ahead), L2 requests (kL2Ahead further)
+            vs.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info);
+            ks = vs;
+            auto load_qk = [&](Walker& wk) -> bool {
+                if (!wk.valid()) return true;
+                bool r = true;
+                if (wk.first_sub()) r = load_q(wk);
+                r = r && load_kv(wk, 1);
+                wk.next();
+                return r;
+            };
+            ok = load_qk(ks) && load_qk(ks);
+            far = ks;
             for (int i = 0; i < kL2Ahead && far.valid(); ++i) {
                 prefetch_l2(far);
                 far.next();
             }
-            while (ok && cur.valid()) {
+            while (ok && vs.valid()) {
                 if (far.valid()) {
                     prefetch_l2(far);
                     far.next();
                 }
-                if (nxt.valid()) {
-                    if (nxt.first_sub()) ok = load_q(nxt);
-                    ok = ok && load_kv(nxt, 1);
-                }
-                ok = ok && load_kv(cur, 2);
-                cur.follow(nxt);
-                if (nxt.valid()) nxt.next();
+                ok = load_qk(ks);
+                ok = ok && load_kv(vs, 2);
+                vs.next();
             }
         }
         __syncwarp();
@@ -320,52 +313,55 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
             // B = [V | ones]: 64 columns of V (MN-major, as TMA delivered it) and, as a second MN block, 16
             // columns of 1.0, so that columns 64..79 of the accumulator are the row sums of P
             constexpr uint32_t idesc_o = umma_idesc_f16(128, 80) | (1u << 16);
-            uint32_t kvc = 0, pc = 0;
+            uint32_t kvc = 0;
             bool ok = true;
 #ifdef EOSB_ATTN_TIMING
             long long mlast__ = clock64();
             long long macc__[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             int mcnt__ = 0;
 #endif
-            // S phase of sub-item number n (in tensor-memory half n & 1)
+            // S phase of sub-item number n, into tensor-memory slot n & 3.  Every barrier completes exactly once per
+            // sub-item (a sub-item without keys arrives by hand), so all parities follow from n alone.
             auto issue_s = [&](const Walker& wk, uint32_t n) -> bool {
-                const int h = n & 1u;
+                const int slot = n & 3u;
                 MMARK(8);
-                if (n >= 2 && !mbar_wait(half_free(h), ((n >> 1) - 1u) & 1u, abort_flag)) return false;
+                if (n >= 4 && !mbar_wait(slot_free(slot), ((n >> 2) - 1u) & 1u, abort_flag)) return false;
                 MMARK(9);
                 const int qs = wk.item_no % kQStages;
                 if (wk.first_sub() && !mbar_wait(q_full(qs), (wk.item_no / kQStages) & 1u, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t q_addr = base + kOffQ + qs * kTileBytes;
-                for (int t = 0; t < wk.nt(); ++t, ++kvc) {
+                if (wk.nt() > 0) {
                     const int s = kvc % kKvStages;
                     if (!mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag)) return false;
+                    ++kvc;
                     tc_fence_after();
                     MMARK(10);
-                    const uint32_t q_lo = umma_desc_sw128_lo(q_addr);
+                    const uint32_t q_lo = umma_desc_sw128_lo(base + kOffQ + qs * kTileBytes);
                     const uint32_t k_lo = umma_desc_sw128_lo(base + kOffKv + s * kTileBytes);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)  // 32 bytes along K per step = 2 in descriptor units
-                        umma_f16_split(tmem_base + h * 256 + t * 128, q_lo + kk * 2, kDescSw128Hi, k_lo + kk * 2,
-                                       kDescSw128Hi, idesc_s, kk > 0 ? 1u : 0u);
+                        umma_f16_split(tmem_base + slot * 128, q_lo + kk * 2, kDescSw128Hi, k_lo + kk * 2, kDescSw128Hi,
+                                       idesc_s, kk > 0 ? 1u : 0u);
                     umma_commit(kv_empty(s));
-                    umma_commit(s_full(h, t));
+                    umma_commit(s_full(slot));
                     MMARK(11);
-                }
-                if (wk.last_sub()) {
-                    if (wk.wi.ntiles > 0) umma_commit(q_empty(qs)); else mbar_arrive(q_empty(qs));
+                    if (wk.last_sub()) umma_commit(q_empty(qs));
+                } else {
+                    mbar_arrive(s_full(slot));
+                    if (wk.last_sub()) mbar_arrive(q_empty(qs));
                 }
                 return true;
             };
             auto issue_pv = [&](const Walker& wk, uint32_t n) -> bool {
-                const int h = n & 1u;
-                for (int t = 0; t < wk.nt(); ++t, ++kvc, ++pc) {
+                const int slot = n & 3u;
+                const int pb = n & 1u;
+                MMARK(8);
+                if (!mbar_wait(p_full(pb), (n >> 1) & 1u, abort_flag)) return false;
+                MMARK(12);
+                if (wk.nt() > 0) {
                     const int s = kvc % kKvStages;
-                    const int pb = pc & 1;
-                    MMARK(8);
-                    if (!mbar_wait(p_full(pb), (pc >> 1) & 1u, abort_flag)) return false;
-                    MMARK(12);
                     if (!mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag)) return false;
+                    ++kvc;
                     tc_fence_after();
                     MMARK(13);
                     const uint32_t p_addr = base + kOffP + pb * kPBytes;
@@ -376,30 +372,35 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                     const uint32_t v_lo = ((v_addr >> 4) & 0x3fffu) | (((base + kOffOnes - v_addr) >> 4) << 16);
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)
-                        umma_f16_split(tmem_base + h * 256, p_lo + (kk >> 2) * (kPBytes / 2 / 16) + (kk & 3) * 2,
+                        umma_f16_split(tmem_base + slot * 128, p_lo + (kk >> 2) * (kPBytes / 2 / 16) + (kk & 3) * 2,
                                        kDescSw128Hi, v_lo + kk * 128u - ((kk * 128u) << 16), kDescSw128Hi, idesc_o,
-                                       (t > 0 || kk > 0) ? 1u : 0u);
+                                       kk > 0 ? 1u : 0u);
                     umma_commit(kv_empty(s));
                     umma_commit(p_empty(pb));
+                    umma_commit(o_full(slot));
                     MMARK(14);
+                } else {
+                    mbar_arrive(p_empty(pb));
+                    mbar_arrive(o_full(slot));
                 }
-                if (wk.nt() > 0) umma_commit(o_full(h));
                 return true;
             };
-            Walker cur, nxt;
-            cur.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info);
-            nxt = cur;
-            uint32_t n = 0;
-            if (cur.valid()) {
-                ok = issue_s(cur, 0);
-                nxt.next();
+            // S runs two sub-items ahead of P V: S(0), S(1); then S(n + 2), PV(n) for n = 0, 1, ...
+            Walker ws, wp;
+            wp.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info);
+            ws = wp;
+            uint32_t ns = 0, np = 0;
+            for (int i = 0; i < 2 && ok && ws.valid(); ++i) {
+                ok = issue_s(ws, ns++);
+                ws.next();
             }
-            while (ok && cur.valid()) {
-                if (nxt.valid()) ok = issue_s(nxt, n + 1);
-                ok = ok && issue_pv(cur, n);
-                cur.follow(nxt);
-                if (nxt.valid()) nxt.next();
-                ++n;
+            while (ok && wp.valid()) {
+                if (ws.valid()) {
+                    ok = issue_s(ws, ns++);
+                    ws.next();
+                }
+                ok = ok && issue_pv(wp, np++);
+                wp.next();
             }
 #ifdef EOSB_ATTN_TIMING
             if (blockIdx.x == 0)
@@ -411,71 +412,72 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         // ------------------------------------------------------------ softmax + epilogue
         const int w8 = warp - 4;
         const int quarter = warp & 3;          // TMEM lane quarter this warp may access
-        const int part = w8 >> 2;              // which kPartCols columns of every 128-column tile
+        const int part = w8 >> 2;              // which kPartCols columns of the tile
         const int r = quarter * 32 + lane;     // query row inside the tile
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const float sl2 = 0.125f * 1.4426950408889634f;  // 1/sqrt(64) * log2(e)
-        uint32_t pc = 0;
-        uint32_t par = 0;  // expected phase parities: bit h*2+t for s_full(h, t), bit 4+h for o_full(h)
         bool ok = true;
-        float part_o[kPartOut], part_m = 0.f, part_l = 0.f;  // first half of a two-part item, kept across sub-items
+        // running result of the item whose sub-items are being retired: O columns of this thread, maximum, row sum
+        float acc_o[kPartOut], acc_m = 0.f, acc_l = 0.f;
+#pragma unroll
+        for (int e = 0; e < kPartOut; ++e) acc_o[e] = 0.f;
 
 #ifdef EOSB_ATTN_TIMING
         long long tlast__ = clock64();
         long long tacc__[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         int tcnt__ = 0;
 #endif
-        // epilogue of sub-item number n (deferred by one sub-item so that its PV MMAs overlap the next
-        // sub-item's softmax): O / l, or the merge of two partial results
-        auto epilogue = [&](const Walker& wk, uint32_t n, float ms_n) -> bool {
-            const int h = n & 1u;
-            const int qrow = wk.wi.q0 + r;
-            __half* out = ctx + (size_t)(wk.wi.row0 + qrow) * hidden + wk.wi.head * 64 + part * kPartOut;
+        // retire sub-item number n (two sub-items after its softmax, so that its P V MMAs are long done): fold its
+        // partial (O, m, l) into the item's running result; after the item's last sub-item, O / l -> f16 -> global
+        // What retiring a sub-item needs to know about it, two registers per thread: the offset of this thread's
+        // output (row, head, column part) and flags.
+        constexpr int kFirst = 1, kLast = 2, kHasKeys = 4, kRowsLive = 8, kRowValid = 16;
+        auto epilogue = [&](int out_off, int fl, uint32_t n, float ms_n) -> bool {
+            const int slot = n & 3u;
             float o[kPartOut], l = 0.f;
 #pragma unroll
             for (int e = 0; e < kPartOut; ++e) o[e] = 0.f;
-            if (wk.nt() > 0) {
-                if (!mbar_wait(o_full(h), (par >> (4 + h)) & 1u, abort_flag)) return false;
-                par ^= 1u << (4 + h);
-                tc_fence_after();
-                TMARK(6);
-                if (wk.wi.q0 + quarter * 32 < wk.wi.nrows) {  // else: a warp of padding rows
-                    uint32_t v[kPartOut], lv[1];
-                    __syncwarp();
-                    tmem_ld_cols(tmem_base + lane_addr + h * 256 + part * kPartOut, v);
-                    tmem_ld_32x1(tmem_base + lane_addr + h * 256 + 64, lv);
-                    tmem_ld_wait();
+            if (!mbar_wait(o_full(slot), (n >> 2) & 1u, abort_flag)) return false;
+            tc_fence_after();
+            TMARK(6);
+            if ((fl & (kHasKeys | kRowsLive)) == (kHasKeys | kRowsLive)) {
+                uint32_t v[kPartOut], lv[1];
+                __syncwarp();
+                tmem_ld_cols(tmem_base + lane_addr + slot * 128 + part * kPartOut, v);
+                tmem_ld_32x1(tmem_base + lane_addr + slot * 128 + 64, lv);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int e = 0; e < kPartOut; ++e) o[e] = __uint_as_float(v[e]);
-                    l = __uint_as_float(lv[0]);
-                }
+                for (int e = 0; e < kPartOut; ++e) o[e] = __uint_as_float(v[e]);
+                l = __uint_as_float(lv[0]);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(half_free(h));
+            if (lane == 0) mbar_arrive(slot_free(slot));
             TMARK(7);
-            if (wk.nsub() == 2 && wk.first_sub()) {
+            if (fl & kFirst) {
 #pragma unroll
-                for (int e = 0; e < kPartOut; ++e) part_o[e] = o[e];
-                part_m = ms_n;
-                part_l = l;
-                return true;
-            }
-            if (wk.nsub() == 2) {  // second part: merge with the first
-                const float m = fmaxf(part_m, ms_n);
-                const float a = exp2f(part_m - m), b = exp2f(ms_n - m);
+                for (int e = 0; e < kPartOut; ++e) acc_o[e] = o[e];
+                acc_m = ms_n;
+                acc_l = l;
+            } else {
+                const float m = fmaxf(acc_m, ms_n);
+                float a, b;  // both exponents are <= 0
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(a) : "f"(acc_m - m));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(ms_n - m));
 #pragma unroll
-                for (int e = 0; e < kPartOut; ++e) o[e] = part_o[e] * a + o[e] * b;
-                l = part_l * a + l * b;
+                for (int e = 0; e < kPartOut; ++e) acc_o[e] = acc_o[e] * a + o[e] * b;
+                acc_l = acc_l * a + l * b;
+                acc_m = m;
             }
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
-            if (qrow < wk.wi.nrows) {
+            if ((fl & (kLast | kRowValid)) == (kLast | kRowValid)) {
+                const float inv = acc_l > 0.f ? __frcp_rn(acc_l) : 0.f;
+                __half* out = ctx + (size_t)out_off;
 #pragma unroll
                 for (int q = 0; q < kPartOut / 16; ++q) {  // 32 bytes (one sector) per store
                     uint32_t ow[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
-                        __half2 hh = __floats2half2_rn(o[q * 16 + 2 * e] * inv, o[q * 16 + 2 * e + 1] * inv);
+                        __half2 hh = __floats2half2_rn(acc_o[q * 16 + 2 * e] * inv, acc_o[q * 16 + 2 * e + 1] * inv);
                         ow[e] = *reinterpret_cast<uint32_t*>(&hh);
                     }
                     st_global_v8(out + q * 16, ow);
@@ -484,14 +486,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
             return true;
         };
 
-        Walker cur, prev;
+        Walker cur;
         cur.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info);
-        prev = cur;
+        int off_prev1 = 0, off_prev2 = 0, fl_prev1 = 0, fl_prev2 = 0;   // sub-items n - 1 and n - 2
         uint32_t n = 0;
-        float ms_prev = 0.f;
-        bool have_prev = false;
+        float ms_prev1 = 0.f, ms_prev2 = 0.f;
         while (ok && cur.valid()) {
-            const int h = n & 1u;
+            const int slot = n & 3u;
+            const int pb = n & 1u;
             const int nt = cur.nt();
             const int key0 = cur.tile0() * 128;           // first key of this sub-item
             const int nkeys = cur.wi.nkeys;
@@ -499,116 +501,106 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
             // but computes nothing (its P rows and O rows are never used)
             const bool live = cur.wi.q0 + quarter * 32 < cur.wi.nrows;
             float ms = 0.f;
-            if (nt > 0) {
-                // pass A: row maximum over the visible keys of this sub-item
-                float mx = -INFINITY;
-                for (int t = 0; t < nt; ++t) {
-                    if (!mbar_wait(s_full(h, t), (par >> (h * 2 + t)) & 1u, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                    par ^= 1u << (h * 2 + t);
-                    tc_fence_after();
-                    TMARK(0);
-                    const int col0 = key0 + t * 128 + part * kPartCols;   // key index of this thread's first column
-                    if (col0 >= nkeys || !live) continue;
+            if (!mbar_wait(s_full(slot), (n >> 2) & 1u, abort_flag)) break;
+            tc_fence_after();
+            TMARK(0);
+            const int key_in_tile = part * kPartCols;
+            const int col0 = key0 + key_in_tile;          // key index of this thread's first column
+            const int lim = nkeys - col0;
+            // pass A: row maximum over the visible keys of this sub-item
+            float mx = -INFINITY;
+            if (nt > 0 && live && lim > 0) {
+                uint32_t v[kPartCols];
+                __syncwarp();
+                tmem_ld_cols(tmem_base + lane_addr + slot * 128 + key_in_tile, v);
+                tmem_ld_wait();
+                if (lim >= kPartCols) {
+#pragma unroll
+                    for (int e = 0; e < kPartCols; e += 2)
+                        mx = fmaxf(mx, fmaxf(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < kPartCols; ++e)
+                        if (e < lim) mx = fmaxf(mx, __uint_as_float(v[e]));
+                }
+            }
+            TMARK(1);
+            // exchange with the warps that hold the other columns of these rows (one named barrier per group of
+            // 32 rows); the buffer alternates per sub-item, and nobody can be two sub-items ahead of a warp that
+            // has not yet read, because every sub-item passes this barrier
+            {
+                float* redn = red + (n & 1u) * (kParts * 128);
+                redn[part * 128 + r] = mx;
+                named_bar_sync(2 + quarter, kParts * 32);
+#pragma unroll
+                for (int q = 0; q < kParts; ++q) mx = fmaxf(mx, redn[q * 128 + r]);
+            }
+            // a sub-item with keys holds at least one visible key, so mx is finite for live rows
+            if (nt > 0) ms = mx * sl2;
+            TMARK(2);
+            // the sub-item before last is retired here: its P V MMAs have had a whole sub-item to finish, and freeing
+            // its slot lets the S phase two sub-items ahead start under pass B
+            if (n >= 2) {
+                ok = epilogue(off_prev2, fl_prev2, n - 2, ms_prev2);
+                if (!ok) break;
+            }
+            TMARK(5);
+            if (!mbar_wait(p_empty(pb), ((n >> 1) & 1u) ^ 1u, abort_flag)) break;
+            TMARK(3);
+            if (nt > 0 && live) {
+                // pass B: probabilities, the P tile for the second MMA
+                // P tile = two 128 x 64 K-major blocks; this thread's keys are kPartCols / 8 16-byte chunks of its row
+                constexpr int kChunks = kPartCols / 8;
+                uint8_t* prow = sm + kOffP + pb * kPBytes + (key_in_tile >> 6) * (kPBytes / 2) + (r >> 3) * 1024 + (r & 7) * 128;
+                const int chunk0 = (key_in_tile & 63) >> 3;
+                uint32_t packed[kPartCols / 2];
+                if (lim > 0) {
                     uint32_t v[kPartCols];
                     __syncwarp();
-                    tmem_ld_cols(tmem_base + lane_addr + h * 256 + t * 128 + part * kPartCols, v);
+                    tmem_ld_cols(tmem_base + lane_addr + slot * 128 + key_in_tile, v);
                     tmem_ld_wait();
-                    const int lim = nkeys - col0;
                     if (lim >= kPartCols) {
 #pragma unroll
                         for (int e = 0; e < kPartCols; e += 2)
-                            mx = fmaxf(mx, fmaxf(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
-                    } else {
+                            packed[e >> 1] = exp2_pair(e >> 1, fmaf(__uint_as_float(v[e]), sl2, -ms), fmaf(__uint_as_float(v[e + 1]), sl2, -ms));
+                    } else {  // the sequence's last, partial tile: masked keys get exp2(-inf) = 0
 #pragma unroll
-                        for (int e = 0; e < kPartCols; ++e)
-                            if (e < lim) mx = fmaxf(mx, __uint_as_float(v[e]));
-                    }
-                }
-                if (!ok) break;
-                TMARK(1);
-                // exchange with the warps that hold the other columns of this row; the buffer alternates per
-                // sub-item, and nobody can be two sub-items ahead of a warp that has not yet read, because
-                // every sub-item has this barrier
-                float* redn = red + (n & 1u) * (kParts * 128);
-                redn[part * 128 + r] = mx;
-                named_bar_sync(2, kSoftmaxWarps * 32);
-#pragma unroll
-                for (int q = 0; q < kParts; ++q) mx = fmaxf(mx, redn[q * 128 + r]);
-                ms = mx * sl2;  // every sub-item holds at least one visible key, so mx is finite
-                TMARK(2);
-                // the previous sub-item's epilogue goes here: its P V MMAs have had pass A's time to finish,
-                // and freeing its half of tensor memory now lets the next S phase run under pass B
-                if (have_prev) {
-                    ok = epilogue(prev, n - 1, ms_prev);
-                    have_prev = false;
-                    if (!ok) break;
-                }
-                TMARK(5);
-                // pass B: probabilities, P tiles for the second MMA
-                for (int t = 0; t < nt; ++t, ++pc) {
-                    const int pb = pc & 1;
-                    if (!mbar_wait(p_empty(pb), ((pc >> 1) & 1u) ^ 1u, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                    TMARK(3);
-                    // P tile = two 128 x 64 K-major blocks; this thread's keys are kPartCols / 8 16-byte chunks of its row
-                    constexpr int kChunks = kPartCols / 8;
-                    const int key_in_tile = part * kPartCols;
-                    uint8_t* prow = sm + kOffP + pb * kPBytes + (key_in_tile >> 6) * (kPBytes / 2) + (r >> 3) * 1024 + (r & 7) * 128;
-                    const int chunk0 = (key_in_tile & 63) >> 3;
-                    const int col0 = key0 + t * 128 + key_in_tile;
-                    const int lim = nkeys - col0;
-                    uint32_t packed[kPartCols / 2];
-                    if (!live) {
-                        // nothing to write
-                    } else if (lim > 0) {
-                        uint32_t v[kPartCols];
-                        __syncwarp();
-                        tmem_ld_cols(tmem_base + lane_addr + h * 256 + t * 128 + key_in_tile, v);
-                        tmem_ld_wait();
-                        if (lim >= kPartCols) {
-#pragma unroll
-                            for (int e = 0; e < kPartCols; e += 2)
-                                packed[e >> 1] = exp2_pair(e >> 1, fmaf(__uint_as_float(v[e]), sl2, -ms), fmaf(__uint_as_float(v[e + 1]), sl2, -ms));
-                        } else {  // the sequence's last, partial tile: masked keys get exp2(-inf) = 0
-#pragma unroll
-                            for (int e = 0; e < kPartCols; e += 2) {
-                                const float a0 = e < lim ? fmaf(__uint_as_float(v[e]), sl2, -ms) : -INFINITY;
-                                const float a1 = e + 1 < lim ? fmaf(__uint_as_float(v[e + 1]), sl2, -ms) : -INFINITY;
-                                packed[e >> 1] = exp2_pair(e >> 1, a0, a1);
-                            }
+                        for (int e = 0; e < kPartCols; e += 2) {
+                            const float a0 = e < lim ? fmaf(__uint_as_float(v[e]), sl2, -ms) : -INFINITY;
+                            const float a1 = e + 1 < lim ? fmaf(__uint_as_float(v[e + 1]), sl2, -ms) : -INFINITY;
+                            packed[e >> 1] = exp2_pair(e >> 1, a0, a1);
                         }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < kPartCols / 2; ++e) packed[e] = 0u;
                     }
-                    if (live) {
+                } else {
 #pragma unroll
-                        for (int q = 0; q < kChunks; ++q)
-                            *reinterpret_cast<uint4*>(prow + (((chunk0 + q) ^ (r & 7)) << 4)) =
-                                make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
-                    }
-                    tc_fence_before();  // S columns of this half are about to be overwritten by O
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(p_full(pb));
-                    TMARK(4);
+                    for (int e = 0; e < kPartCols / 2; ++e) packed[e] = 0u;
                 }
-                if (!ok) break;
+#pragma unroll
+                for (int q = 0; q < kChunks; ++q)
+                    *reinterpret_cast<uint4*>(prow + (((chunk0 + q) ^ (r & 7)) << 4)) =
+                        make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
             }
-            if (have_prev) ok = epilogue(prev, n - 1, ms_prev);
-            TMARK(5);
-            prev.follow(cur);
-            ms_prev = ms;
-            have_prev = true;
+            tc_fence_before();  // the S columns of this slot are about to be overwritten by O
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(pb));
+            TMARK(4);
+            off_prev2 = off_prev1;
+            fl_prev2 = fl_prev1;
+            ms_prev2 = ms_prev1;
+            {
+                const int qrow = cur.wi.q0 + r;
+                off_prev1 = (cur.wi.row0 + qrow) * hidden + cur.wi.head * 64 + part * kPartOut;
+                fl_prev1 = (cur.first_sub() ? kFirst : 0) | (cur.last_sub() ? kLast : 0) | (nt > 0 ? kHasKeys : 0) |
+                           (live ? kRowsLive : 0) | (qrow < cur.wi.nrows ? kRowValid : 0);
+            }
+            ms_prev1 = ms;
             cur.next();
             ++n;
         }
-        if (ok && have_prev) epilogue(prev, n - 1, ms_prev);
+        // retire the last two sub-items
+        if (ok && n >= 2) ok = epilogue(off_prev2, fl_prev2, n - 2, ms_prev2);
+        if (ok && n >= 1) ok = epilogue(off_prev1, fl_prev1, n - 1, ms_prev1);
 #ifdef EOSB_ATTN_TIMING
         if (blockIdx.x == 0 && threadIdx.x == 128)
             for (int i = 0; i < 8; ++i) g_attn_timing[i] += tacc__[i];
