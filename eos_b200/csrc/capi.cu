@@ -1127,6 +1127,7 @@ struct EosB200Corpus {
     uint2* bfrag = nullptr;
     uint64_t* cand = nullptr;  // [group][grid][kTqMaxK]
     int* cand_count = nullptr;
+    unsigned long long* shared_tau = nullptr;  // [cap_queries] pruning thresholds shared by the CTAs of a pass
     int64_t* d_ids = nullptr;
     float* d_scores = nullptr;
     int grid = 0;
@@ -1210,6 +1211,7 @@ int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
     dev_free(c->bfrag);
     dev_free(c->cand);
     dev_free(c->cand_count);
+    dev_free(c->shared_tau);
     dev_free(c->d_ids);
     dev_free(c->d_scores);
     c->cap_queries = 0;
@@ -1218,6 +1220,7 @@ int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
     CUDA_TRY(dev_alloc(&c->bfrag, (size_t)(q_pad / 8) * ksteps * 32));
     CUDA_TRY(dev_alloc(&c->cand, (size_t)kTqGroupQueries * c->grid * kTqMaxK));
     CUDA_TRY(dev_alloc(&c->cand_count, (size_t)kTqGroupQueries * c->grid));
+    CUDA_TRY(dev_alloc(&c->shared_tau, (size_t)q_pad));
     CUDA_TRY(dev_alloc(&c->d_ids, (size_t)q_pad * kTqMaxK));
     CUDA_TRY(dev_alloc(&c->d_scores, (size_t)q_pad * kTqMaxK));
     c->cap_queries = q_pad;
@@ -1232,6 +1235,8 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
     int launches = 0;
     launch_tq_prepare(d_queries, q_count, (q_count + 31) / 32 * 32, qz->spec(), c->bfrag, nullptr, s);
     launches++;
+    // one threshold per query, shared by the CTAs of the pass that scores it (streaming kernel only)
+    cudaMemsetAsync(c->shared_tau, 0, (size_t)((q_count + 31) / 32 * 32) * sizeof(unsigned long long), s);
     const int j = per_pass / 8;
     for (int g0 = 0; g0 < q_count; g0 += kTqGroupQueries) {
         const int g_queries = (q_count - g0) < kTqGroupQueries ? (q_count - g0) : kTqGroupQueries;
@@ -1253,6 +1258,7 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
             a.cand_keys = c->cand + (size_t)t0 * 8 * c->grid * kTqMaxK;
             a.cand_count = c->cand_count + (size_t)t0 * 8 * c->grid;
             a.grid = c->grid;
+            a.shared_tau = j == 1 ? c->shared_tau + (size_t)g0 + (size_t)t0 * 8 : nullptr;
             a.all_scores = nullptr;
             a.status = nullptr;
             a.all_stride = 0;
@@ -1403,6 +1409,7 @@ void eos_b200_corpus_destroy(EosB200Corpus* c) {
     dev_free(c->bfrag);
     dev_free(c->cand);
     dev_free(c->cand_count);
+    dev_free(c->shared_tau);
     dev_free(c->d_ids);
     dev_free(c->d_scores);
     c->prof.reset();

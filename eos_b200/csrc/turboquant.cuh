@@ -67,6 +67,8 @@ struct TqScanArgs {
     int* cand_count;       // [query_tiles*8][grid]
     int grid;
     int* status;           // device status word (receives kStatusPipelineTimeout if a bounded wait runs out)
+    unsigned long long* shared_tau;  // when non-null: [query_tiles*8] keys, zero before the pass; the CTAs publish the
+                                     // k-th best key they hold, and every CTA prunes with the largest one published
     float* all_scores;     // when non-null: every score is stored at all_scores[q * all_stride + doc]
     long long all_stride;  // and the top-k bookkeeping is skipped
 };
