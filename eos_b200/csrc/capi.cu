@@ -1128,6 +1128,7 @@ struct EosB200Corpus {
     uint64_t* cand = nullptr;  // [group][grid][kTqMaxK]
     int* cand_count = nullptr;
     unsigned long long* shared_tau = nullptr;  // [cap_queries] pruning thresholds shared by the CTAs of a pass
+    uint64_t* seed_keys = nullptr;             // [cap_queries][kTqMaxK] top-k keys of the sample that seeds them
     int64_t* d_ids = nullptr;
     float* d_scores = nullptr;
     int grid = 0;
@@ -1212,6 +1213,7 @@ int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
     dev_free(c->cand);
     dev_free(c->cand_count);
     dev_free(c->shared_tau);
+    dev_free(c->seed_keys);
     dev_free(c->d_ids);
     dev_free(c->d_scores);
     c->cap_queries = 0;
@@ -1221,22 +1223,28 @@ int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
     CUDA_TRY(dev_alloc(&c->cand, (size_t)kTqGroupQueries * c->grid * kTqMaxK));
     CUDA_TRY(dev_alloc(&c->cand_count, (size_t)kTqGroupQueries * c->grid));
     CUDA_TRY(dev_alloc(&c->shared_tau, (size_t)q_pad));
+    CUDA_TRY(dev_alloc(&c->seed_keys, (size_t)q_pad * kTqMaxK));
     CUDA_TRY(dev_alloc(&c->d_ids, (size_t)q_pad * kTqMaxK));
     CUDA_TRY(dev_alloc(&c->d_scores, (size_t)q_pad * kTqMaxK));
     c->cap_queries = q_pad;
     return EOS_B200_OK;
 }
 
-// Enqueues prepare + scan passes + merges; returns launches (or -1 with *err set).
-int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, int per_pass, int64_t* d_ids,
-                  float* d_scores, uint64_t* d_keys, cudaStream_t s) {
+// shared_tau[q] = (k-th best key of the sample) - 1, so that the sample's own k-th document still passes; 0 when the
+// sample holds fewer than k documents.
+__global__ void seed_tau_kernel(const uint64_t* __restrict__ keys, int q_count, int k, unsigned long long* __restrict__ tau) {
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= q_count) return;
+    const uint64_t kth = keys[(size_t)q * k + (k - 1)];
+    tau[q] = kth != 0 ? kth - 1 : 0;
+}
+
+// Scan passes of `per_pass` queries over the first n_docs rows + one merge per group of queries.
+int enqueue_scan_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, int per_pass, bool use_shared_tau,
+                        bool profile, int64_t* d_ids, float* d_scores, uint64_t* d_keys, cudaStream_t s) {
     EosB200Quantizer* qz = c->qz;
     const int ksteps = tq_ksteps(qz->dim);
     int launches = 0;
-    launch_tq_prepare(d_queries, q_count, (q_count + 31) / 32 * 32, qz->spec(), c->bfrag, nullptr, s);
-    launches++;
-    // one threshold per query, shared by the CTAs of the pass that scores it (streaming kernel only)
-    cudaMemsetAsync(c->shared_tau, 0, (size_t)((q_count + 31) / 32 * 32) * sizeof(unsigned long long), s);
     const int j = per_pass / 8;
     for (int g0 = 0; g0 < q_count; g0 += kTqGroupQueries) {
         const int g_queries = (q_count - g0) < kTqGroupQueries ? (q_count - g0) : kTqGroupQueries;
@@ -1245,7 +1253,7 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
             TqScanArgs a{};
             a.tiles = c->tiles;
             a.norms = c->norms;
-            a.n_docs = c->n;
+            a.n_docs = n_docs;
             a.id_base = (uint32_t)c->id_base;
             a.dim = qz->dim;
             a.bfrag = c->bfrag + (size_t)(g0 / 8 + t0) * ksteps * 32;
@@ -1258,11 +1266,12 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
             a.cand_keys = c->cand + (size_t)t0 * 8 * c->grid * kTqMaxK;
             a.cand_count = c->cand_count + (size_t)t0 * 8 * c->grid;
             a.grid = c->grid;
-            a.shared_tau = j == 1 ? c->shared_tau + (size_t)g0 + (size_t)t0 * 8 : nullptr;
+            a.shared_tau = (use_shared_tau && j == 1) ? c->shared_tau + (size_t)g0 + (size_t)t0 * 8 : nullptr;
             a.all_scores = nullptr;
             a.status = nullptr;
             a.all_stride = 0;
-            c->prof.launch(kClsScan, s, [&] { launch_tq_scan(a, s); });
+            if (profile) c->prof.launch(kClsScan, s, [&] { launch_tq_scan(a, s); });
+            else launch_tq_scan(a, s);
             launches++;
         }
         launch_tq_merge(c->cand, (int64_t)c->grid * kTqMaxK, kTqMaxK, c->grid, kTqMaxK, c->cand_count, g_queries, k,
@@ -1271,6 +1280,30 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
                         d_keys != nullptr ? d_keys + (size_t)g0 * k : nullptr, s);
         launches++;
     }
+    return launches;
+}
+
+// Enqueues prepare + scan passes + merges; returns launches (or -1 with *err set).
+int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, int per_pass, int64_t* d_ids,
+                  float* d_scores, uint64_t* d_keys, cudaStream_t s) {
+    EosB200Quantizer* qz = c->qz;
+    int launches = 0;
+    launch_tq_prepare(d_queries, q_count, (q_count + 31) / 32 * 32, qz->spec(), c->bfrag, nullptr, s);
+    launches++;
+    // One pruning threshold per query, shared by the CTAs of the pass that scores it (streaming kernel, 8 queries per
+    // pass).  It starts from a sample: the k-th best key among the first kSeedDocs rows is a lower bound of the k-th best
+    // key of the whole shard, costs a fraction of a percent of the scan (32 queries per pass over 6 MB of codes), and
+    // spares every CTA of every pass the phase in which nearly every document is still a candidate.
+    constexpr int64_t kSeedDocs = 16384;
+    const bool seeded = per_pass == 8 && c->n >= 8 * kSeedDocs && k <= kSeedDocs;
+    if (per_pass == 8 && !seeded)
+        cudaMemsetAsync(c->shared_tau, 0, (size_t)((q_count + 31) / 32 * 32) * sizeof(unsigned long long), s);
+    if (seeded) {
+        launches += enqueue_scan_passes(c, kSeedDocs, q_count, k, 32, false, false, nullptr, nullptr, c->seed_keys, s);
+        seed_tau_kernel<<<(q_count + 255) / 256, 256, 0, s>>>(c->seed_keys, q_count, k, c->shared_tau);
+        launches++;
+    }
+    launches += enqueue_scan_passes(c, c->n, q_count, k, per_pass, true, true, d_ids, d_scores, d_keys, s);
     return launches;
 }
 
@@ -1410,6 +1443,7 @@ void eos_b200_corpus_destroy(EosB200Corpus* c) {
     dev_free(c->cand);
     dev_free(c->cand_count);
     dev_free(c->shared_tau);
+    dev_free(c->seed_keys);
     dev_free(c->d_ids);
     dev_free(c->d_scores);
     c->prof.reset();

@@ -515,7 +515,7 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) tq_scan_stream_kernel(Tq
     const int g = lane >> 2, t = lane & 3;
     if (threadIdx.x == 0) abort_flag_s = 0;
     for (int i = threadIdx.x; i < 8; i += blockDim.x) {
-        tau[i] = 0;
+        tau[i] = a.shared_tau != nullptr ? a.shared_tau[i] : 0;  // seeded by the host from a sample, or 0
         lcnt[i] = 0;
         locks[i] = 0;
     }

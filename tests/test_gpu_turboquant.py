@@ -91,6 +91,7 @@ def _check_topk(ids, scores, ref_scores, k, id_base, tol):
 
 @pytest.mark.parametrize("dim,bits,n,nq,k,per_pass", [
     (768, 4, 5000, 11, 100, 8), (768, 4, 2051, 40, 100, 32), (128, 2, 3000, 16, 10, 16), (96, 4, 50, 3, 100, 8),
+    (96, 4, 140000, 9, 100, 8),   # large enough for the thresholds to be seeded from a sample of the first rows
 ])
 def test_scores_and_topk_match_oracle(rt, dim, bits, n, nq, k, per_pass):
     import eos_b200
