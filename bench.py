@@ -469,6 +469,25 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
     bytes_per_vec = spec.vector_bytes
     scan_avg_ms = scan_ms / max(1, scan_launches)
     achieved = (n_local * bytes_per_vec) / (scan_avg_ms / 1e3) / 1e9 if scan_avg_ms > 0 else None
+    if per_pass == 128:
+        # the batch kernel is a contraction on the tensor cores: 2 x 128 queries x rows x padded dim flops per launch
+        dimp = (dim + 127) // 128 * 128
+        flops = 2.0 * 128 * n_local * dimp
+        tf = flops / (scan_avg_ms / 1e3) / 1e12 if scan_avg_ms > 0 else None
+        roofline = {"bound": "tensor", "kernel": "tq_score_tc_kernel", "achieved": tf, "peak": peaks["tflops"],
+                    "unit": "TFLOP/s", "frac": tf / peaks["tflops"] if tf else None,
+                    "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained)", "traffic": None,
+                    "avg_launch_ms": scan_avg_ms, "algorithmic_flops_per_launch": flops,
+                    "hbm_gbs": achieved}
+    else:
+        roofline = {"bound": "hbm",
+                    "kernel": "tq_scan_stream_kernel" if per_pass == 8 else f"tq_scan_kernel<{per_pass // 8}>",
+                    "achieved": achieved,
+                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"] if achieved else None,
+                    "peak_source": f"{peaks['source']} (copy bandwidth)",
+                    # ncu: 783.7 MB of DRAM traffic for a 2,000,000-row launch (profiles/tq_scan_stream_kernel_*.md)
+                    "traffic": n_local * NCU_SCAN_DRAM_BYTES_PER_ROW if per_pass == 8 else None,
+                    "avg_launch_ms": scan_avg_ms, "algorithmic_bytes_per_launch": n_local * bytes_per_vec}
     out = {
         "metric": "turboquant_vectors_scored_per_s", "value": vec_passes / (ms / 1e3), "unit": "vectors/s",
         "pair_scores_per_s": float(nq) * n_total / (ms / 1e3), "ms_per_step": ms, "steps": steps, "scaling": "strong",
@@ -476,14 +495,7 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
                                f"{world} GPU(s), {nq} f16 queries, exact top-{k}, {per_pass} queries per corpus pass "
                                f"({passes} passes)", "bytes_per_vector": bytes_per_vec,
                    "merge": "none" if world == 1 else "NCCL all-gather of per-shard top-k + merge kernel"},
-        "roofline": {"bound": "hbm",
-                     "kernel": "tq_scan_stream_kernel" if per_pass == 8 else f"tq_scan_kernel<{per_pass // 8}>",
-                     "achieved": achieved,
-                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"] if achieved else None,
-                     "peak_source": f"{peaks['source']} (copy bandwidth)",
-                     # ncu: 783.7 MB of DRAM traffic for a 2,000,000-row launch (profiles/tq_scan_stream_kernel_*.md)
-                     "traffic": n_local * NCU_SCAN_DRAM_BYTES_PER_ROW if per_pass == 8 else None,
-                     "avg_launch_ms": scan_avg_ms, "algorithmic_bytes_per_launch": n_local * bytes_per_vec},
+        "roofline": roofline,
         "_launches": launches,
     }
     if e2e is not None:
@@ -523,7 +535,7 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="omit the timed CPU baseline")
     ap.add_argument("--skip-turboquant", action="store_true", help="encoder only")
     ap.add_argument("--tq-corpus", type=int, default=TQ["corpus"])
-    ap.add_argument("--tq-queries-per-pass", type=int, default=8, choices=[8, 16, 32])
+    ap.add_argument("--tq-queries-per-pass", type=int, default=8, choices=[8, 16, 32, 128])
     ap.add_argument("--weight-mode", default="f16_resident", choices=["f16_resident", "q8_smem"],
                     help="how the projection kernel receives the 8-bit weights (results are bit-identical)")
     ap.add_argument("--skip-other-mode", action="store_true", help="do not also time the other weight mode")

@@ -139,6 +139,7 @@ int eos_b200_runtime_create(int device, EosB200Runtime** out, char** err) {
     if (ge.empty()) {
         cudaError_t se = tq_scan_init();
         if (se != cudaSuccess) ge = std::string("tq_scan_init: ") + cudaGetErrorString(se);
+        if (se == cudaSuccess && (se = tq_tc_init()) != cudaSuccess) ge = std::string("tq_tc_init: ") + cudaGetErrorString(se);
     }
     if (!ge.empty()) {
         eos_b200_runtime_destroy(rt);
@@ -1132,6 +1133,13 @@ struct EosB200Corpus {
     int64_t* d_ids = nullptr;
     float* d_scores = nullptr;
     int grid = 0;
+    // tensor-core batch path (128 queries per launch), allocated on first use
+    int tc_grid = 0;
+    int tc_cap_queries = 0;
+    __half* qperm = nullptr;        // [tc_cap_queries][padded dim] rotated queries, coordinates in code-word order
+    uint64_t* tc_cand = nullptr;    // [128][2 * tc_grid][kTqTcSegLen]
+    int* tc_count = nullptr;        // [128][2 * tc_grid]
+    CUtensorMap tm_q;
     Profiler prof;
 };
 
@@ -1206,7 +1214,7 @@ int corpus_finish_bind(EosB200Quantizer* qz, const uint8_t* d_codes, const float
 }
 
 int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
-    const int q_pad = (q_count + 31) / 32 * 32;
+    const int q_pad = (q_count + kTqTcQueries - 1) / kTqTcQueries * kTqTcQueries;
     if (q_pad <= c->cap_queries) return EOS_B200_OK;
     dev_free(c->d_queries);
     dev_free(c->bfrag);
@@ -1216,6 +1224,8 @@ int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
     dev_free(c->seed_keys);
     dev_free(c->d_ids);
     dev_free(c->d_scores);
+    dev_free(c->qperm);
+    c->tc_cap_queries = 0;
     c->cap_queries = 0;
     const int ksteps = tq_ksteps(c->qz->dim);
     CUDA_TRY(dev_alloc(&c->d_queries, (size_t)q_pad * c->qz->dim));
@@ -1227,6 +1237,25 @@ int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
     CUDA_TRY(dev_alloc(&c->d_ids, (size_t)q_pad * kTqMaxK));
     CUDA_TRY(dev_alloc(&c->d_scores, (size_t)q_pad * kTqMaxK));
     c->cap_queries = q_pad;
+    return EOS_B200_OK;
+}
+
+// Buffers of the tensor-core batch path; the query capacity follows ensure_score_workspace.
+int ensure_tc_workspace(EosB200Corpus* c, char** err) {
+    if (c->tc_cap_queries == c->cap_queries && c->qperm != nullptr) return EOS_B200_OK;
+    const int dimp = tq_ksteps(c->qz->dim) * 16;
+    const int64_t tiles = (c->n + kTqTcDocs - 1) / kTqTcDocs;
+    c->tc_grid = (int)(tiles < c->qz->rt->sm_count ? (tiles > 0 ? tiles : 1) : c->qz->rt->sm_count);
+    dev_free(c->qperm);
+    c->tc_cap_queries = 0;
+    CUDA_TRY(dev_alloc(&c->qperm, (size_t)c->cap_queries * dimp));
+    if (c->tc_cand == nullptr) {
+        CUDA_TRY(dev_alloc(&c->tc_cand, (size_t)kTqTcQueries * 2 * c->tc_grid * kTqTcSegLen));
+        CUDA_TRY(dev_alloc(&c->tc_count, (size_t)kTqTcQueries * 2 * c->tc_grid));
+    }
+    const std::string m = tq_tc_make_query_map(&c->tm_q, c->qperm, dimp, c->cap_queries);
+    if (!m.empty()) return fail(err, "score_topk: " + m);
+    c->tc_cap_queries = c->cap_queries;
     return EOS_B200_OK;
 }
 
@@ -1283,12 +1312,69 @@ int enqueue_scan_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, in
     return launches;
 }
 
+// Tensor-core launches of kTqTcQueries queries over the first n_docs rows, one merge after each.
+int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool profile, int64_t* d_ids, float* d_scores,
+                      uint64_t* d_keys, cudaStream_t s) {
+    EosB200Quantizer* qz = c->qz;
+    const int64_t tiles = (n_docs + kTqTcDocs - 1) / kTqTcDocs;
+    const int grid = (int)(tiles < c->tc_grid ? tiles : c->tc_grid);
+    const int n_segs = 2 * grid;
+    int launches = 0;
+    for (int q0 = 0; q0 < q_count; q0 += kTqTcQueries) {
+        const int q_here = (q_count - q0) < kTqTcQueries ? (q_count - q0) : kTqTcQueries;
+        TqTcArgs a{};
+        a.tiles = c->tiles;
+        a.norms = c->norms;
+        a.n_docs = n_docs;
+        a.id_base = (uint32_t)c->id_base;
+        a.dim = qz->dim;
+        a.q_row0 = q0;
+        a.q_valid = q_here;
+        a.k = k;
+        a.mag_hi[0] = qz->mag_hi[0];
+        a.mag_hi[1] = qz->mag_hi[1];
+        a.mag_lo[0] = qz->mag_lo[0];
+        a.mag_lo[1] = qz->mag_lo[1];
+        a.cand_keys = c->tc_cand;
+        a.cand_count = c->tc_count;
+        a.shared_tau = c->shared_tau + q0;
+        a.status = qz->rt->d_status;
+        if (profile) c->prof.launch(kClsScan, s, [&] { launch_tq_score_tc(c->tm_q, a, grid, s); });
+        else launch_tq_score_tc(c->tm_q, a, grid, s);
+        launch_tq_merge(c->tc_cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, c->tc_count, q_here, k,
+                        0, d_ids != nullptr ? d_ids + (size_t)q0 * k : nullptr,
+                        d_scores != nullptr ? d_scores + (size_t)q0 * k : nullptr,
+                        d_keys != nullptr ? d_keys + (size_t)q0 * k : nullptr, s);
+        launches += 2;
+    }
+    return launches;
+}
+
+// The batch path: thresholds seeded from the first tc_grid * 256 rows (one tile per CTA, so no list is cut while
+// every document still passes), then the whole shard.
+int enqueue_score_tc(EosB200Corpus* c, const float* d_queries, int q_count, int k, int64_t* d_ids, float* d_scores,
+                     uint64_t* d_keys, cudaStream_t s) {
+    const int q_pad = (q_count + kTqTcQueries - 1) / kTqTcQueries * kTqTcQueries;
+    int launches = 1;
+    launch_tq_prepare(d_queries, q_count, q_pad, c->qz->spec(), nullptr, nullptr, c->qperm, s);
+    cudaMemsetAsync(c->shared_tau, 0, (size_t)q_pad * sizeof(unsigned long long), s);
+    const int64_t seed_docs = (int64_t)c->tc_grid * kTqTcDocs;
+    if (c->n >= 8 * seed_docs && k <= seed_docs) {
+        launches += enqueue_tc_passes(c, seed_docs, q_count, k, false, nullptr, nullptr, c->seed_keys, s);
+        seed_tau_kernel<<<(q_count + 255) / 256, 256, 0, s>>>(c->seed_keys, q_count, k, c->shared_tau);
+        launches++;
+    }
+    launches += enqueue_tc_passes(c, c->n, q_count, k, true, d_ids, d_scores, d_keys, s);
+    return launches;
+}
+
 // Enqueues prepare + scan passes + merges; returns launches (or -1 with *err set).
 int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, int per_pass, int64_t* d_ids,
                   float* d_scores, uint64_t* d_keys, cudaStream_t s) {
     EosB200Quantizer* qz = c->qz;
+    if (per_pass == kTqTcQueries) return enqueue_score_tc(c, d_queries, q_count, k, d_ids, d_scores, d_keys, s);
     int launches = 0;
-    launch_tq_prepare(d_queries, q_count, (q_count + 31) / 32 * 32, qz->spec(), c->bfrag, nullptr, s);
+    launch_tq_prepare(d_queries, q_count, (q_count + 31) / 32 * 32, qz->spec(), c->bfrag, nullptr, nullptr, s);
     launches++;
     // One pruning threshold per query, shared by the CTAs of the pass that scores it (streaming kernel, 8 queries per
     // pass).  It starts from a sample: the k-th best key among the first kSeedDocs rows is a lower bound of the k-th best
@@ -1310,7 +1396,8 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
 std::string check_score_args(const EosB200Corpus* c, int q_count, int k, int per_pass) {
     if (q_count <= 0) return "score_topk: no queries";
     if (k <= 0 || k > kTqMaxK) return "score_topk: k must be in [1, 128]";
-    if (per_pass != 8 && per_pass != 16 && per_pass != 32) return "score_topk: queries_per_pass must be 8, 16 or 32";
+    if (per_pass != 8 && per_pass != 16 && per_pass != 32 && per_pass != kTqTcQueries)
+        return "score_topk: queries_per_pass must be 8, 16, 32 or 128";
     if (c->n + c->id_base > 0xffffffffLL || c->id_base < 0) return "score_topk: document ids must fit 32 bits";
     return "";
 }
@@ -1446,6 +1533,9 @@ void eos_b200_corpus_destroy(EosB200Corpus* c) {
     dev_free(c->seed_keys);
     dev_free(c->d_ids);
     dev_free(c->d_scores);
+    dev_free(c->qperm);
+    dev_free(c->tc_cand);
+    dev_free(c->tc_count);
     c->prof.reset();
     delete c;
 }
@@ -1529,6 +1619,7 @@ int eos_b200_score_topk_device(EosB200Corpus* c, const float* d_queries, int q_c
     if (c->n == 0) return fail(err, "score_topk: empty corpus");
     CUDA_TRY(cudaSetDevice(c->qz->rt->device));
     int rc = ensure_score_workspace(c, q_count, err);
+    if (rc == EOS_B200_OK && per_pass == kTqTcQueries) rc = ensure_tc_workspace(c, err);
     if (rc != EOS_B200_OK) return rc;
     const int launches =
         enqueue_score(c, d_queries, q_count, k, per_pass, d_ids, d_scores, d_keys, pick_stream(c->qz->rt, stream));
@@ -1557,6 +1648,7 @@ int eos_b200_score_topk(EosB200Corpus* c, const float* h_queries, int q_count, i
     EosB200Runtime* rt = c->qz->rt;
     CUDA_TRY(cudaSetDevice(rt->device));
     int rc = ensure_score_workspace(c, q_count, err);
+    if (rc == EOS_B200_OK && per_pass == kTqTcQueries) rc = ensure_tc_workspace(c, err);
     if (rc != EOS_B200_OK) return rc;
     cudaStream_t s = rt->stream;
     CUDA_TRY(cudaEventRecord(rt->ev0, s));
@@ -1641,7 +1733,7 @@ int eos_b200_score_topk_noalloc(EosB200Corpus* c, const float* d_queries, int q_
     cudaStream_t s = pick_stream(qz->rt, stream);
     // the array still holds the previous call's lists: the counts are what a stale read would trust
     CUDA_TRY(cudaMemsetAsync(cand_count, 0, kNoAllocCountBytes, s));
-    launch_tq_prepare(d_queries, q_count, kNoAllocMaxQueries, qz->spec(), bfrag, nullptr, s);
+    launch_tq_prepare(d_queries, q_count, kNoAllocMaxQueries, qz->spec(), bfrag, nullptr, nullptr, s);
     const int j = per_pass / 8;
     const int g_tiles = (q_count + 7) / 8;
     for (int t0 = 0; t0 < g_tiles; t0 += j) {
@@ -1697,7 +1789,7 @@ int eos_b200_score_all(EosB200Corpus* c, const float* h_queries, int q_count, fl
     CUDA_TRY(dev_alloc(&d_all, (size_t)q_pad * c->n));
     cudaStream_t s = rt->stream;
     cudaError_t e = cudaMemcpyAsync(c->d_queries, h_queries, (size_t)q_count * c->qz->dim * 4, cudaMemcpyHostToDevice, s);
-    launch_tq_prepare(c->d_queries, q_count, q_pad, c->qz->spec(), c->bfrag, nullptr, s);
+    launch_tq_prepare(c->d_queries, q_count, q_pad, c->qz->spec(), c->bfrag, nullptr, nullptr, s);
     const int ksteps = tq_ksteps(c->qz->dim);
     for (int t = 0; t < q_pad / 8; ++t) {
         TqScanArgs a{};
@@ -1781,7 +1873,7 @@ int eos_b200_parent_topk(EosB200Corpus* c, const int32_t* h_parent_of_child, int
     int launches = 0;
     if (e == cudaSuccess) {
         const int q_pad = (q_count + 31) / 32 * 32;
-        launch_tq_prepare(c->d_queries, q_count, q_pad, c->qz->spec(), c->bfrag, nullptr, s);
+        launch_tq_prepare(c->d_queries, q_count, q_pad, c->qz->spec(), c->bfrag, nullptr, nullptr, s);
         launches++;
         const int ksteps = tq_ksteps(c->qz->dim);
         for (int r0 = 0; r0 < q_count; r0 += 32) {

@@ -17,12 +17,12 @@
 #include "turboquant.cuh"
 
 #include "common.cuh"
+#include "turboquant_dev.cuh"
 
 namespace eosb {
 
 namespace {
 
-typedef unsigned long long u64;
 
 // ------------------------------------------------------------------------------------------
 // packing
@@ -114,18 +114,6 @@ tq_pack_kernel(const float* __restrict__ x, long long n, TqSpec s, uint8_t* __re
     }
 }
 
-// ------------------------------------------------------------------------------------------
-// scan layout.  A tile = 16 documents.  For chunk c (128 coordinates = 8 MMA k-steps), lane
-// (g = lane/4, t = lane%4) owns 32 bytes at tile + c*1024 + lane*32: a uint4 for document g and
-// a uint4 for document g+8.  Word i of a uint4 covers k-steps 8c+2i and 8c+2i+1; its element
-// e = 2q+h (q = 0..3, h = 0,1) is coordinate 16*(8c+2i+(q>>1)) + 2t + 8*(q&1) + h, magnitude
-// index in bits [4e, 4e+3), sign (1 = negative) in bit 3 + 4q + 16h.
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ int scan_coord(int c, int i, int t, int e) {
-    const int q = e >> 1, h = e & 1;
-    return 16 * (8 * c + 2 * i + (q >> 1)) + 2 * t + 8 * (q & 1) + h;
-}
-
 __global__ void __launch_bounds__(256)
 tq_transcode_kernel(const uint8_t* __restrict__ codes, long long n, int dim, int bits, uint32_t* __restrict__ tiles) {
     const int chunks = (dim + kTqChunkCoords - 1) / kTqChunkCoords;
@@ -157,7 +145,7 @@ tq_transcode_kernel(const uint8_t* __restrict__ codes, long long n, int dim, int
                     const int neg = code < half_levels;
                     const int mag = neg ? (half_levels - 1 - code) : (code - half_levels);
                     out |= (uint32_t)mag << (4 * e);
-                    out |= (uint32_t)neg << (3 + 4 * (e >> 1) + 16 * (e & 1));
+                    out |= (uint32_t)neg << (e < 4 ? 8 * e + 7 : 8 * (e - 4) + 3);
                 }
             }
         }
@@ -172,7 +160,7 @@ tq_transcode_kernel(const uint8_t* __restrict__ codes, long long n, int dim, int
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
 tq_prepare_kernel(const float* __restrict__ queries, int nq, int q_fill, TqSpec s, int ksteps,
-                  uint2* __restrict__ bfrag, float* __restrict__ rotated_out) {
+                  uint2* __restrict__ bfrag, float* __restrict__ rotated_out, __half* __restrict__ qperm) {
     extern __shared__ float sm_f[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warps = blockDim.x >> 5;
@@ -191,8 +179,18 @@ tq_prepare_kernel(const float* __restrict__ queries, int nq, int q_fill, TqSpec 
             for (int i = lane; i < s.dim; i += 32) rot[i] = 0.f;  // padding queries score 0
             __syncwarp();
         }
+        if (qperm != nullptr) {
+            // row-major f16 copy for the tensor-core kernel: inside every block of 64 coordinates, 16-byte piece j
+            // holds the 8 coordinates of code word (2 (kb & 1) + (j >> 2), column j & 3) of the scan layout
+            const int dimp = ksteps * 16;
+            for (int idx = lane; idx < dimp; idx += 32) {
+                const int kb = idx >> 6, j = (idx >> 3) & 7, e = idx & 7;
+                const int coord = scan_coord(kb >> 1, 2 * (kb & 1) + (j >> 2), j & 3, e);
+                qperm[(size_t)q * dimp + idx] = __float2half_rn(coord < s.dim ? rot[coord] : 0.f);
+            }
+        }
         const int tile = q >> 3, g = q & 7;
-        for (int idx = lane; idx < ksteps * 4; idx += 32) {
+        for (int idx = lane; bfrag != nullptr && idx < ksteps * 4; idx += 32) {
             const int st = idx >> 2, t = idx & 3;
             const int c0 = 16 * st + 2 * t;
             float v[4];
@@ -210,100 +208,6 @@ tq_prepare_kernel(const float* __restrict__ queries, int nq, int q_fill, TqSpec 
 }
 
 // ------------------------------------------------------------------------------------------
-// keys: (order-preserving score bits << 32) | (0xffffffff - doc index): larger key = better
-// candidate under "score descending, then id ascending"; 0 = empty.
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t float_to_ordered(float f) {
-    const uint32_t u = __float_as_uint(f);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-__device__ __forceinline__ float ordered_to_float(uint32_t o) {
-    return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o);
-}
-__device__ __forceinline__ u64 make_key(float score, uint32_t doc) {
-    return ((u64)float_to_ordered(score) << 32) | (u64)(0xffffffffu - doc);
-}
-
-// Radix-select the k-th largest of keys[0..n) (distinct, n > k >= 1) with one warp.
-// hist: 256 counters of shared memory owned by the warp.
-__device__ u64 warp_kth_largest(const u64* keys, int n, int k, unsigned* hist, int lane) {
-    u64 prefix = 0, mask = 0;
-    unsigned want = (unsigned)k;
-    for (int shift = 56; shift >= 0; shift -= 8) {
-        for (int i = lane; i < 256; i += 32) hist[i] = 0;
-        __syncwarp();
-        for (int i = lane; i < n; i += 32) {
-            const u64 key = keys[i];
-            if ((key & mask) == prefix) atomicAdd(&hist[(unsigned)(key >> shift) & 0xffu], 1u);
-        }
-        __syncwarp();
-        unsigned c[8], s = 0;
-#pragma unroll
-        for (int b = 0; b < 8; ++b) {
-            c[b] = hist[lane * 8 + b];
-            s += c[b];
-        }
-        unsigned incl = s;  // sum over lanes >= this one (higher lanes own higher digits)
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const unsigned tmp = __shfl_down_sync(0xffffffffu, incl, o);
-            if (lane + o < 32) incl += tmp;
-        }
-        const unsigned above = incl - s;
-        const bool mine = (above < want) && (want <= incl);
-        int d = 0;
-        unsigned next_want = 0;
-        if (mine) {
-            unsigned run = above;
-#pragma unroll
-            for (int b = 7; b >= 0; --b) {
-                if (next_want == 0) {
-                    if (run + c[b] >= want) {
-                        d = lane * 8 + b;
-                        next_want = want - run;
-                    } else {
-                        run += c[b];
-                    }
-                }
-            }
-        }
-        const unsigned bal = __ballot_sync(0xffffffffu, mine);
-        const int src = bal ? (__ffs(bal) - 1) : 0;
-        d = __shfl_sync(0xffffffffu, d, src);
-        want = __shfl_sync(0xffffffffu, next_want, src);
-        prefix |= (u64)(unsigned)d << shift;
-        mask |= (u64)0xffu << shift;
-        __syncwarp();
-    }
-    return prefix;
-}
-
-// Bitonic sort of the kSortCap = 256 slots of a list in shared memory by one warp, descending; slots from n on are
-// cleared first (empty = 0 sinks to the end).  Measured faster here than the 8-pass radix select for a few hundred
-// keys, and faster than the same network held in registers (whose unrolled code is long and rarely executed).
-constexpr int kSortCap = 256;
-__device__ __forceinline__ void warp_sort_desc(u64* keys, int n, int lane) {
-    for (int i = n + lane; i < kSortCap; i += 32) keys[i] = 0;
-    __syncwarp();
-    for (int size = 2; size <= kSortCap; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-#pragma unroll
-            for (int tt = lane; tt < kSortCap / 2; tt += 32) {
-                const int i = 2 * tt - (tt & (stride - 1));
-                const int j = i + stride;
-                const bool desc = (i & size) == 0;
-                const u64 x = keys[i], y = keys[j];
-                if ((x < y) == desc) {
-                    keys[i] = y;
-                    keys[j] = x;
-                }
-            }
-            __syncwarp();
-        }
-    }
-}
-
-// ------------------------------------------------------------------------------------------
 // the scan
 // ------------------------------------------------------------------------------------------
 constexpr int kScanCap = kTqMaxK + kTqScanWarps * kTqDocsPerTile;  // 384 keys per query buffer
@@ -314,19 +218,6 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// 8 sign-magnitude nibbles -> 4 half2 (elements 0/1, 2/3, 4/5, 6/7)
-__device__ __forceinline__ void dequant8(uint32_t w, uint32_t hi_a, uint32_t hi_b, uint32_t lo_a, uint32_t lo_b,
-                                         uint32_t (&v)[4]) {
-    const uint32_t m = w & 0x77777777u;
-    const uint32_t mh = m >> 16;
-    const uint32_t h0 = __byte_perm(hi_a, hi_b, m), l0 = __byte_perm(lo_a, lo_b, m);
-    const uint32_t h1 = __byte_perm(hi_a, hi_b, mh), l1 = __byte_perm(lo_a, lo_b, mh);
-    v[0] = __byte_perm(l0, h0, 0x5140) ^ ((w << 12) & 0x80008000u);
-    v[1] = __byte_perm(l0, h0, 0x7362) ^ ((w << 8) & 0x80008000u);
-    v[2] = __byte_perm(l1, h1, 0x5140) ^ ((w << 4) & 0x80008000u);
-    v[3] = __byte_perm(l1, h1, 0x7362) ^ (w & 0x80008000u);
 }
 
 template <int J>
@@ -993,7 +884,7 @@ void launch_tq_transcode(const uint8_t* codes, int64_t n, int dim, int bits, uin
 }
 
 void launch_tq_prepare(const float* queries, int q, int q_fill, const TqSpec& spec, uint2* bfrag, float* rotated_out,
-                       cudaStream_t stream) {
+                       __half* qperm, cudaStream_t stream) {
     if (q <= 0) return;
     const int warps = 4;
     const size_t smem = (size_t)warps * 3 * spec.dim * sizeof(float);
@@ -1001,7 +892,7 @@ void launch_tq_prepare(const float* queries, int q, int q_fill, const TqSpec& sp
     int blocks = (q_padded + warps - 1) / warps;
     if (blocks > 148 * 4) blocks = 148 * 4;
     tq_prepare_kernel<<<blocks, warps * 32, smem, stream>>>(queries, q, q_fill, spec, tq_ksteps(spec.dim), bfrag,
-                                                            rotated_out);
+                                                            rotated_out, qperm);
 }
 
 size_t tq_scan_smem_bytes(int query_tiles, int dim) {

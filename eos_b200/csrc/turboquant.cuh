@@ -1,9 +1,12 @@
 // Launchers of the TurboQuant kernels (turboquant.cu): Hadamard/MSE code packing, the scan
 // layout, query preparation, the scoring scan with per-CTA exact top-k and the merge.
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <string>
 
 namespace eosb {
 
@@ -41,8 +44,10 @@ void launch_tq_transcode(const uint8_t* codes, int64_t n, int dim, int bits, uin
 // queries [q, dim] fp32 -> rotated f16 B fragments [ceil(q/8)][ksteps][32 lanes] x 8 bytes;
 // also the rotated fp32 queries when rotated_out != null.
 // Fragments are written for q_fill >= q queries (a multiple of 8); queries past q are zeros.
+// qperm, when non-null, receives the rotated queries as f16 rows [q_fill][padded dim] with the coordinates of every
+// 64-block in the order of the scan layout's code words (the A operand of the tensor-core kernel); bfrag may be null.
 void launch_tq_prepare(const float* queries, int q, int q_fill, const TqSpec& spec, uint2* bfrag, float* rotated_out,
-                       cudaStream_t stream);
+                       __half* qperm, cudaStream_t stream);
 
 // keys[p] = sortable key of (sum over `rows` of the per-row parent aggregate, parent id p):
 // per row and parent the mean of the best min(top_n, 5, children) child scores minus
@@ -76,6 +81,32 @@ struct TqScanArgs {
 size_t tq_scan_smem_bytes(int query_tiles, int dim);
 cudaError_t tq_scan_init();
 void launch_tq_scan(const TqScanArgs& a, cudaStream_t stream);
+
+// Batched scoring on the tensor cores (turboquant_tc.cu): one launch = kTqTcQueries queries x the whole shard.
+constexpr int kTqTcQueries = 128;  // queries per launch
+constexpr int kTqTcDocs = 256;     // documents per tile
+constexpr int kTqTcSegLen = 256;   // slots of one candidate list; a launch of `grid` CTAs fills 2 * grid lists per query
+struct TqTcArgs {
+    const uint8_t* tiles;
+    const float* norms;
+    int64_t n_docs;
+    uint32_t id_base;
+    int dim;
+    int q_row0;            // first row of this launch's queries in the permuted f16 query matrix
+    int q_valid;           // queries of this launch that exist (the rest are padding and collect nothing)
+    int k;                 // <= kTqMaxK
+    uint32_t mag_hi[2];
+    uint32_t mag_lo[2];
+    uint64_t* cand_keys;   // [kTqTcQueries][2 * grid][kTqTcSegLen]
+    int* cand_count;       // [kTqTcQueries][2 * grid]
+    unsigned long long* shared_tau;  // [kTqTcQueries] pruning thresholds: seeded by the caller (0 = none), raised by
+                                     // every CTA that cuts a list
+    int* status;
+};
+cudaError_t tq_tc_init();
+// Tensor map of the permuted query matrix [rows][padded_dim] f16 (rows a multiple of kTqTcQueries).
+std::string tq_tc_make_query_map(CUtensorMap* tm, const __half* qperm, int padded_dim, int rows);
+void launch_tq_score_tc(const CUtensorMap& tm_q, const TqTcArgs& a, int grid, cudaStream_t stream);
 
 // For every query: the k best of n_segs x seg_len candidate keys (key 0 = empty), sorted by
 // score descending then id ascending.  cand is [queries][n_segs][seg_len] with the given

@@ -92,6 +92,10 @@ def _check_topk(ids, scores, ref_scores, k, id_base, tol):
 @pytest.mark.parametrize("dim,bits,n,nq,k,per_pass", [
     (768, 4, 5000, 11, 100, 8), (768, 4, 2051, 40, 100, 32), (128, 2, 3000, 16, 10, 16), (96, 4, 50, 3, 100, 8),
     (96, 4, 140000, 9, 100, 8),   # large enough for the thresholds to be seeded from a sample of the first rows
+    # 128 queries per launch: the tensor-core batch kernel
+    (768, 4, 5000, 11, 100, 128), (768, 4, 2051, 140, 100, 128), (128, 2, 3000, 16, 10, 128), (96, 4, 50, 3, 100, 128),
+    (96, 4, 140000, 9, 100, 128),  # unseeded, several tiles per CTA: every list is cut
+    (96, 4, 310000, 9, 100, 128),  # thresholds seeded from the first 148 x 256 rows
 ])
 def test_scores_and_topk_match_oracle(rt, dim, bits, n, nq, k, per_pass):
     import eos_b200
@@ -110,13 +114,14 @@ def test_scores_and_topk_match_oracle(rt, dim, bits, n, nq, k, per_pass):
     qz.close()
 
 
-def test_ties_resolve_to_lower_id(rt):
+@pytest.mark.parametrize("per_pass", [8, 128])
+def test_ties_resolve_to_lower_id(rt, per_pass):
     import eos_b200
     spec, qz, codes, norms, q = _setup(rt, 768, 4, 640, 4)
     codes = np.tile(codes[:64], (10, 1))   # every vector appears 10 times: exact score ties
     norms = np.tile(norms[:64], 10)
     corpus = eos_b200.Corpus(qz, codes, norms)
-    ids, scores = corpus.score_topk(q, 100)
+    ids, scores = corpus.score_topk(q, 100, queries_per_pass=per_pass)
     for i in range(4):
         groups = ids[i].reshape(10, 10)
         assert (np.diff(scores[i].reshape(10, 10), axis=1) == 0).all()
