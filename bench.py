@@ -36,6 +36,7 @@ TQ = dict(dim=768, bits=4, corpus=10_000_000, queries=4096, k=100)
 NCU_GEMM_DRAM_BYTES_PER_ROW = {"qkv": 152.35e6 / 32768, "attn_out": 124.88e6 / 32768, "ffn_up": 207.08e6 / 32768,
                                "ffn_down": 291.77e6 / 32768}
 NCU_SCAN_DRAM_BYTES_PER_ROW = 783.74e6 / 2_000_000
+NCU_TC_DRAM_BYTES_PER_ROW = None  # DRAM bytes per row of one tq_score_tc_kernel launch, from an ncu capture
 
 
 def load_peaks():
@@ -424,82 +425,94 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
     scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
     keys = torch.empty((nq, k), dtype=torch.int64, device="cuda")
     keys_all = torch.empty((world, nq, k), dtype=torch.int64, device="cuda") if world > 1 else None
-    launches = 0
+    def measure(per_pass, steps, with_e2e):
+        launches = 0
 
-    def step():
-        n = 0
-        if world == 1:
-            n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, ids.data_ptr(), scores.data_ptr(), None,
-                                          stream)
+        def step():
+            n = 0
+            if world == 1:
+                n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, ids.data_ptr(), scores.data_ptr(), None,
+                                              stream)
+            else:
+                n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, None, None, keys.data_ptr(), stream)
+                dist.all_gather_into_tensor(keys_all, keys)  # one NCCL all-gather of the per-shard top-k
+                tq.topk_merge_device(rt, keys_all.data_ptr(), world, nq, k, ids.data_ptr(), scores.data_ptr(), stream)
+                n += 1
+            return n
+
+        warm = max(1, min(args.warmup, 3))
+        for _ in range(warm):
+            step()
+        barrier()
+        passes = (nq + per_pass - 1) // per_pass
+        corpus.profile_begin(passes * steps + 8)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            launches += step()
+        ev1.record()
+        barrier()
+        scan_ms, scan_launches = corpus.profile_end(stream)
+        ms = max_over_ranks(ev0.elapsed_time(ev1)) / steps
+        scored = float(nq) * n_total  # one vector scored = one (query, vector) inner product, as in the reference's loop
+        # end to end: host queries in, host ids/scores out (single GPU); copies inside the timed region
+        e2e = None
+        if world == 1 and with_e2e:
+            hq = queries.cpu().pin_memory().numpy()
+            corpus.score_topk(hq[:64], k, per_pass)
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                h_ids, h_scores = corpus.score_topk(hq, k, per_pass)
+            dt = (time.perf_counter() - t0) / steps
+            st = corpus.last_stats
+            e2e = {"value": scored / dt, "unit": "vectors/s", "h2d_bytes_per_step": int(st.uploaded_bytes),
+                   "d2h_bytes_per_step": int(st.downloaded_bytes), "queries_per_s": nq / dt}
+        bytes_per_vec = spec.vector_bytes
+        scan_avg_ms = scan_ms / max(1, scan_launches)
+        achieved = (n_local * bytes_per_vec) / (scan_avg_ms / 1e3) / 1e9 if scan_avg_ms > 0 else None
+        if per_pass == 128:
+            # the batch kernel is a contraction on the tensor cores: 2 x 128 queries x rows x padded dim flops per launch
+            dimp = (dim + 127) // 128 * 128
+            flops = 2.0 * 128 * n_local * dimp
+            tf = flops / (scan_avg_ms / 1e3) / 1e12 if scan_avg_ms > 0 else None
+            roofline = {"bound": "tensor", "kernel": "tq_score_tc_kernel", "achieved": tf, "peak": peaks["tflops"],
+                        "unit": "TFLOP/s", "frac": tf / peaks["tflops"] if tf else None,
+                        "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained)",
+                        "traffic": n_local * NCU_TC_DRAM_BYTES_PER_ROW if NCU_TC_DRAM_BYTES_PER_ROW else None,
+                        "avg_launch_ms": scan_avg_ms, "algorithmic_flops_per_launch": flops,
+                        "code_read_gbs": achieved}
         else:
-            n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, None, None, keys.data_ptr(), stream)
-            dist.all_gather_into_tensor(keys_all, keys)  # one NCCL all-gather of the per-shard top-k
-            tq.topk_merge_device(rt, keys_all.data_ptr(), world, nq, k, ids.data_ptr(), scores.data_ptr(), stream)
-            n += 1
-        return n
+            roofline = {"bound": "hbm",
+                        "kernel": "tq_scan_stream_kernel" if per_pass == 8 else f"tq_scan_kernel<{per_pass // 8}>",
+                        "achieved": achieved,
+                        "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"] if achieved else None,
+                        "peak_source": f"{peaks['source']} (copy bandwidth)",
+                        # ncu DRAM traffic of one launch, scaled by rows (profiles/tq_scan_stream_kernel_*.md)
+                        "traffic": n_local * NCU_SCAN_DRAM_BYTES_PER_ROW if per_pass == 8 else None,
+                        "avg_launch_ms": scan_avg_ms, "algorithmic_bytes_per_launch": n_local * bytes_per_vec}
+        res = {
+            "metric": "turboquant_vectors_scored_per_s", "value": scored / (ms / 1e3), "unit": "vectors/s",
+            "corpus_rows_streamed_per_s": float(passes) * n_total / (ms / 1e3), "ms_per_step": ms, "steps": steps,
+            "scaling": "strong",
+            "config": {"workload": f"TurboQuant 4-bit Hadamard/MSE, {n_total} x {dim} unit Gaussian corpus sharded over "
+                                   f"{world} GPU(s), {nq} f16 queries, exact top-{k}, {per_pass} queries per corpus pass "
+                                   f"({passes} passes); one vector scored = one (query, vector) inner product",
+                       "bytes_per_vector": bytes_per_vec,
+                       "merge": "none" if world == 1 else "NCCL all-gather of per-shard top-k + merge kernel"},
+            "roofline": roofline,
+            "_launches": launches,
+        }
+        if e2e is not None:
+            res["e2e"] = e2e
+        return res
 
     steps = max(1, min(args.steps, args.tq_steps))
-    warm = max(1, min(args.warmup, 3))
-    for _ in range(warm):
-        step()
-    barrier()
-    passes = (nq + per_pass - 1) // per_pass
-    corpus.profile_begin(passes * steps + 8)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(steps):
-        launches += step()
-    ev1.record()
-    barrier()
-    scan_ms, scan_launches = corpus.profile_end(stream)
-    ms = max_over_ranks(ev0.elapsed_time(ev1)) / steps
-    vec_passes = passes * n_total
-    # end to end: host queries in, host ids/scores out (single GPU); copies inside the timed region
-    e2e = None
-    if world == 1:
-        hq = queries.cpu().pin_memory().numpy()
-        corpus.score_topk(hq[:64], k, per_pass)
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            h_ids, h_scores = corpus.score_topk(hq, k, per_pass)
-        dt = (time.perf_counter() - t0) / steps
-        st = corpus.last_stats
-        e2e = {"value": vec_passes / dt, "unit": "vectors/s", "h2d_bytes_per_step": int(st.uploaded_bytes),
-               "d2h_bytes_per_step": int(st.downloaded_bytes), "queries_per_s": nq / dt}
-    bytes_per_vec = spec.vector_bytes
-    scan_avg_ms = scan_ms / max(1, scan_launches)
-    achieved = (n_local * bytes_per_vec) / (scan_avg_ms / 1e3) / 1e9 if scan_avg_ms > 0 else None
-    if per_pass == 128:
-        # the batch kernel is a contraction on the tensor cores: 2 x 128 queries x rows x padded dim flops per launch
-        dimp = (dim + 127) // 128 * 128
-        flops = 2.0 * 128 * n_local * dimp
-        tf = flops / (scan_avg_ms / 1e3) / 1e12 if scan_avg_ms > 0 else None
-        roofline = {"bound": "tensor", "kernel": "tq_score_tc_kernel", "achieved": tf, "peak": peaks["tflops"],
-                    "unit": "TFLOP/s", "frac": tf / peaks["tflops"] if tf else None,
-                    "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained)", "traffic": None,
-                    "avg_launch_ms": scan_avg_ms, "algorithmic_flops_per_launch": flops,
-                    "hbm_gbs": achieved}
-    else:
-        roofline = {"bound": "hbm",
-                    "kernel": "tq_scan_stream_kernel" if per_pass == 8 else f"tq_scan_kernel<{per_pass // 8}>",
-                    "achieved": achieved,
-                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"] if achieved else None,
-                    "peak_source": f"{peaks['source']} (copy bandwidth)",
-                    # ncu: 783.7 MB of DRAM traffic for a 2,000,000-row launch (profiles/tq_scan_stream_kernel_*.md)
-                    "traffic": n_local * NCU_SCAN_DRAM_BYTES_PER_ROW if per_pass == 8 else None,
-                    "avg_launch_ms": scan_avg_ms, "algorithmic_bytes_per_launch": n_local * bytes_per_vec}
-    out = {
-        "metric": "turboquant_vectors_scored_per_s", "value": vec_passes / (ms / 1e3), "unit": "vectors/s",
-        "pair_scores_per_s": float(nq) * n_total / (ms / 1e3), "ms_per_step": ms, "steps": steps, "scaling": "strong",
-        "config": {"workload": f"TurboQuant 4-bit Hadamard/MSE, {n_total} x {dim} unit Gaussian corpus sharded over "
-                               f"{world} GPU(s), {nq} f16 queries, exact top-{k}, {per_pass} queries per corpus pass "
-                               f"({passes} passes)", "bytes_per_vector": bytes_per_vec,
-                   "merge": "none" if world == 1 else "NCCL all-gather of per-shard top-k + merge kernel"},
-        "roofline": roofline,
-        "_launches": launches,
-    }
-    if e2e is not None:
-        out["e2e"] = e2e
+    out = measure(per_pass, steps, True)
+    if per_pass != 8 and not args.tq_skip_stream:
+        # the 8-queries-per-pass streaming scan (the kernel small batches use) on the same shard: its HBM roofline
+        st = measure(8, 1, False)
+        out["stream_scan"] = {key: st[key] for key in ("value", "corpus_rows_streamed_per_s", "ms_per_step", "roofline")}
+        out["_launches"] += st["_launches"]
     if rank == 0 and world == 1 and not args.skip_cpu:
         out["cpu_baseline"] = time_oracle_scoring(spec, rt, qz)
     corpus.close()
@@ -535,7 +548,9 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="omit the timed CPU baseline")
     ap.add_argument("--skip-turboquant", action="store_true", help="encoder only")
     ap.add_argument("--tq-corpus", type=int, default=TQ["corpus"])
-    ap.add_argument("--tq-queries-per-pass", type=int, default=8, choices=[8, 16, 32, 128])
+    ap.add_argument("--tq-queries-per-pass", type=int, default=128, choices=[8, 16, 32, 128],
+                    help="128 = tensor-core batch kernel; 8 = streaming scan; 16 / 32 = the earlier register-blocked scan")
+    ap.add_argument("--tq-skip-stream", action="store_true", help="do not also time the 8-queries-per-pass scan")
     ap.add_argument("--weight-mode", default="f16_resident", choices=["f16_resident", "q8_smem"],
                     help="how the projection kernel receives the 8-bit weights (results are bit-identical)")
     ap.add_argument("--skip-other-mode", action="store_true", help="do not also time the other weight mode")

@@ -140,6 +140,7 @@ int eos_b200_runtime_create(int device, EosB200Runtime** out, char** err) {
         cudaError_t se = tq_scan_init();
         if (se != cudaSuccess) ge = std::string("tq_scan_init: ") + cudaGetErrorString(se);
         if (se == cudaSuccess && (se = tq_tc_init()) != cudaSuccess) ge = std::string("tq_tc_init: ") + cudaGetErrorString(se);
+        if (se == cudaSuccess && (se = tq_merge_init()) != cudaSuccess) ge = std::string("tq_merge_init: ") + cudaGetErrorString(se);
     }
     if (!ge.empty()) {
         eos_b200_runtime_destroy(rt);
@@ -1312,8 +1313,9 @@ int enqueue_scan_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, in
     return launches;
 }
 
-// Tensor-core launches of kTqTcQueries queries over the first n_docs rows, one merge after each.
-int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool profile, int64_t* d_ids, float* d_scores,
+// Tensor-core launches of kTqTcQueries queries over the first n_docs rows.  seed = true: the lists of each launch
+// become the pruning thresholds of its queries (shared_tau); otherwise they are merged into the top-k outputs.
+int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool seed, int64_t* d_ids, float* d_scores,
                       uint64_t* d_keys, cudaStream_t s) {
     EosB200Quantizer* qz = c->qz;
     const int64_t tiles = (n_docs + kTqTcDocs - 1) / kTqTcDocs;
@@ -1339,12 +1341,16 @@ int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool
         a.cand_count = c->tc_count;
         a.shared_tau = c->shared_tau + q0;
         a.status = qz->rt->d_status;
-        if (profile) c->prof.launch(kClsScan, s, [&] { launch_tq_score_tc(c->tm_q, a, grid, s); });
+        if (!seed) c->prof.launch(kClsScan, s, [&] { launch_tq_score_tc(c->tm_q, a, grid, s); });
         else launch_tq_score_tc(c->tm_q, a, grid, s);
-        launch_tq_merge(c->tc_cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, c->tc_count, q_here, k,
-                        0, d_ids != nullptr ? d_ids + (size_t)q0 * k : nullptr,
-                        d_scores != nullptr ? d_scores + (size_t)q0 * k : nullptr,
-                        d_keys != nullptr ? d_keys + (size_t)q0 * k : nullptr, s);
+        if (seed)
+            launch_tq_seed_tau_lists(c->tc_cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, c->tc_count,
+                                     q_here, k, c->shared_tau + q0, s);
+        else
+            launch_tq_merge_lists(c->tc_cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, c->tc_count,
+                                  q_here, k, d_ids != nullptr ? d_ids + (size_t)q0 * k : nullptr,
+                                  d_scores != nullptr ? d_scores + (size_t)q0 * k : nullptr,
+                                  d_keys != nullptr ? d_keys + (size_t)q0 * k : nullptr, s);
         launches += 2;
     }
     return launches;
@@ -1359,12 +1365,9 @@ int enqueue_score_tc(EosB200Corpus* c, const float* d_queries, int q_count, int 
     launch_tq_prepare(d_queries, q_count, q_pad, c->qz->spec(), nullptr, nullptr, c->qperm, s);
     cudaMemsetAsync(c->shared_tau, 0, (size_t)q_pad * sizeof(unsigned long long), s);
     const int64_t seed_docs = (int64_t)c->tc_grid * kTqTcDocs;
-    if (c->n >= 8 * seed_docs && k <= seed_docs) {
-        launches += enqueue_tc_passes(c, seed_docs, q_count, k, false, nullptr, nullptr, c->seed_keys, s);
-        seed_tau_kernel<<<(q_count + 255) / 256, 256, 0, s>>>(c->seed_keys, q_count, k, c->shared_tau);
-        launches++;
-    }
-    launches += enqueue_tc_passes(c, c->n, q_count, k, true, d_ids, d_scores, d_keys, s);
+    if (c->n >= 8 * seed_docs && k <= seed_docs && 2 * c->tc_grid <= 1024)
+        launches += enqueue_tc_passes(c, seed_docs, q_count, k, true, nullptr, nullptr, nullptr, s);
+    launches += enqueue_tc_passes(c, c->n, q_count, k, false, d_ids, d_scores, d_keys, s);
     return launches;
 }
 

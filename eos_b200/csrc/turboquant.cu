@@ -687,6 +687,265 @@ dense_keys_kernel(const void* __restrict__ docs, long long n_rows, int dim, cons
 }
 
 // ------------------------------------------------------------------------------------------
+// merge of counted candidate lists (the tensor-core batch kernel's output: n_segs lists of up to seg_len keys
+// per query, cnts entries in use).  One CTA per query.  The counts are prefix-summed in shared memory, the
+// keys are gathered once from global memory (independent, unrolled loads: the lists are short and scattered,
+// so a pass over them is latency-bound) into shared memory, and the radix select, the gather of the k best
+// and the sort run there.  A query with more candidates than the buffer holds selects from global memory.
+// ------------------------------------------------------------------------------------------
+// Radix-select step by one warp: hist[256] counts keys by digit; picks the digit d that holds the want-th largest key
+// (digits descending) and the rank wanted inside it.  Lane l owns digits 8l .. 8l+7.  All 32 lanes call it.
+__device__ __forceinline__ void warp_pick_digit(const unsigned* hist, unsigned want, int lane, int* d_out,
+                                                unsigned* want_out) {
+    unsigned c[8], s = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        c[j] = hist[lane * 8 + j];
+        s += c[j];
+    }
+    unsigned incl = s;  // sum over lanes >= this one (higher lanes own higher digits)
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned t = __shfl_down_sync(0xffffffffu, incl, o);
+        if (lane + o < 32) incl += t;
+    }
+    const unsigned above = incl - s;
+    const bool mine = above < want && want <= incl;
+    int d = 0;
+    unsigned nw = 0;
+    if (mine) {
+        unsigned run = above;
+#pragma unroll
+        for (int j = 7; j >= 0; --j) {
+            if (nw == 0) {
+                if (run + c[j] >= want) {
+                    d = lane * 8 + j;
+                    nw = want - run;
+                } else {
+                    run += c[j];
+                }
+            }
+        }
+    }
+    const unsigned bal = __ballot_sync(0xffffffffu, mine);
+    const int src = bal != 0 ? __ffs(bal) - 1 : 0;
+    *d_out = __shfl_sync(0xffffffffu, d, src);
+    *want_out = __shfl_sync(0xffffffffu, nw, src);
+}
+
+constexpr int kListThreads = 512;
+constexpr int kListMaxSegs = 1024;
+constexpr int kListCapKeys = 16384;   // 128 KB of keys
+constexpr int kSeedCapScores = 49152; // 192 KB of 32-bit scores
+
+// prefix[0] = 0, prefix[i + 1] = sum of min(cnts[j], seg_len) for j <= i; returns the total.  Whole block.
+__device__ int list_prefix(const int* __restrict__ cnts, int n_segs, int seg_len, int* prefix) {
+    for (int i = threadIdx.x; i < n_segs; i += blockDim.x) prefix[i + 1] = min(max(cnts[i], 0), seg_len);
+    if (threadIdx.x == 0) prefix[0] = 0;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        int carry = 0;
+        for (int b = 0; b < n_segs; b += 32) {
+            int v = b + lane < n_segs ? prefix[b + lane + 1] : 0;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += t;
+            }
+            if (b + lane < n_segs) prefix[b + lane + 1] = v + carry;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+    return prefix[n_segs];
+}
+// list that holds flat entry i: the largest seg with prefix[seg] <= i
+__device__ __forceinline__ int list_find(const int* prefix, int n_segs, int i) {
+    int lo = 0, hi = n_segs;  // invariant: prefix[lo] <= i < prefix[hi]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (prefix[mid] <= i) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__global__ void __launch_bounds__(kListThreads)
+tq_merge_lists_kernel(const u64* __restrict__ cand, long long query_stride, long long seg_stride, int n_segs, int seg_len,
+                      const int* __restrict__ counts, int k, long long* __restrict__ out_ids,
+                      float* __restrict__ out_scores, u64* __restrict__ out_keys) {
+    extern __shared__ __align__(16) uint8_t lsm[];
+    u64* buf = reinterpret_cast<u64*>(lsm);                       // [kListCapKeys]
+    int* prefix = reinterpret_cast<int*>(buf + kListCapKeys);      // [n_segs + 1]
+    __shared__ unsigned hist[256];
+    __shared__ u64 s_prefix, s_mask;
+    __shared__ unsigned s_want;
+    __shared__ int s_fill;
+    __shared__ u64 sel[kTqMaxK];
+    const int qi = blockIdx.x;
+    const u64* base = cand + (long long)qi * query_stride;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int total = list_prefix(counts + (long long)qi * n_segs, n_segs, seg_len, prefix);
+    const bool in_smem = total <= kListCapKeys;
+    auto global_key = [&](int i) {
+        const int seg = list_find(prefix, n_segs, i);
+        return base[(long long)seg * seg_stride + (i - prefix[seg])];
+    };
+    if (in_smem) {
+        for (int i0 = threadIdx.x; i0 < total; i0 += 4 * kListThreads) {
+            u64 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * kListThreads;
+                v[u] = i < total ? global_key(i) : 0;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * kListThreads;
+                if (i < total) buf[i] = v[u];
+            }
+        }
+    }
+    if (threadIdx.x == 0) s_fill = 0;
+    for (int i = threadIdx.x; i < kTqMaxK; i += blockDim.x) sel[i] = 0;
+    __syncthreads();
+    auto key_at = [&](int i) { return in_smem ? buf[i] : global_key(i); };
+    const int kk = total < k ? total : k;
+    u64 thr = 1;  // keep every key
+    if (total > k) {
+        if (threadIdx.x == 0) {
+            s_prefix = 0;
+            s_mask = 0;
+            s_want = (unsigned)k;
+        }
+        for (int shift = 56; shift >= 0; shift -= 8) {
+            for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+            __syncthreads();
+            const u64 pre = s_prefix, mask = s_mask;
+            for (int i = threadIdx.x; i < total; i += blockDim.x) {
+                const u64 key = key_at(i);
+                if ((key & mask) == pre) atomicAdd(&hist[(unsigned)(key >> shift) & 0xffu], 1u);
+            }
+            __syncthreads();
+            if (threadIdx.x < 32) {
+                int d;
+                unsigned nw;
+                warp_pick_digit(hist, s_want, lane, &d, &nw);
+                __syncwarp();
+                if (lane == 0) {
+                    s_want = nw;
+                    s_prefix = pre | ((u64)(unsigned)d << shift);
+                    s_mask = mask | ((u64)0xffu << shift);
+                }
+            }
+            __syncthreads();
+        }
+        thr = s_prefix;
+    }
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const u64 key = key_at(i);
+        if (key >= thr) {
+            const int pos = atomicAdd(&s_fill, 1);
+            if (pos < kTqMaxK) sel[pos] = key;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        for (int size = 2; size <= kTqMaxK; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                for (int tt = lane; tt < kTqMaxK / 2; tt += 32) {
+                    const int i = 2 * tt - (tt & (stride - 1));
+                    const int j = i + stride;
+                    const bool desc = (i & size) == 0;
+                    const u64 x = sel[i], y = sel[j];
+                    if ((x < y) == desc) {
+                        sel[i] = y;
+                        sel[j] = x;
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        for (int i = lane; i < k; i += 32) {
+            const u64 key = i < kk ? sel[i] : 0;
+            if (out_keys != nullptr) out_keys[(long long)qi * k + i] = key;
+            if (out_ids != nullptr) {
+                out_ids[(long long)qi * k + i] = key != 0 ? (long long)(0xffffffffu - (uint32_t)(key & 0xffffffffu)) : -1;
+                out_scores[(long long)qi * k + i] = key != 0 ? ordered_to_float((uint32_t)(key >> 32)) : -INFINITY;
+            }
+        }
+    }
+}
+
+// Pruning thresholds from the lists of a sample: tau[q] = (k-th best score among the first kSeedCapScores keys of
+// query q's lists, as a key with id bits 0) - 1, so that every document scoring at least that much still passes;
+// 0 when the sample holds fewer than k keys.  Only the 32 score bits of a key are kept, which lets a sample of
+// tens of thousands of documents sit in shared memory.  Any subset's k-th best is a valid lower bound.
+__global__ void __launch_bounds__(kListThreads)
+tq_seed_tau_lists_kernel(const u64* __restrict__ cand, long long query_stride, long long seg_stride, int n_segs,
+                         int seg_len, const int* __restrict__ counts, int k, unsigned long long* __restrict__ tau) {
+    extern __shared__ __align__(16) uint8_t lsm[];
+    uint32_t* buf = reinterpret_cast<uint32_t*>(lsm);              // [kSeedCapScores]
+    int* prefix = reinterpret_cast<int*>(buf + kSeedCapScores);    // [n_segs + 1]
+    __shared__ unsigned hist[256];
+    __shared__ uint32_t s_prefix, s_mask;
+    __shared__ unsigned s_want;
+    const int qi = blockIdx.x;
+    const u64* base = cand + (long long)qi * query_stride;
+    int total = list_prefix(counts + (long long)qi * n_segs, n_segs, seg_len, prefix);
+    if (total > kSeedCapScores) total = kSeedCapScores;
+    for (int i0 = threadIdx.x; i0 < total; i0 += 8 * kListThreads) {
+        u64 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * kListThreads;
+            v[u] = 0;
+            if (i < total) {
+                const int seg = list_find(prefix, n_segs, i);
+                v[u] = base[(long long)seg * seg_stride + (i - prefix[seg])];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * kListThreads;
+            if (i < total) buf[i] = (uint32_t)(v[u] >> 32);
+        }
+    }
+    if (threadIdx.x == 0) {
+        s_prefix = 0;
+        s_mask = 0;
+        s_want = (unsigned)k;
+    }
+    __syncthreads();
+    if (total < k) {
+        if (threadIdx.x == 0) tau[qi] = 0;
+        return;
+    }
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        const uint32_t pre = s_prefix, mask = s_mask;
+        for (int i = threadIdx.x; i < total; i += blockDim.x) {
+            const uint32_t key = buf[i];
+            if ((key & mask) == pre) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            int d;
+            unsigned nw;
+            warp_pick_digit(hist, s_want, (int)threadIdx.x, &d, &nw);
+            __syncwarp();
+            if (threadIdx.x == 0) {
+                s_want = nw;
+                s_prefix = pre | ((uint32_t)d << shift);
+                s_mask = mask | (0xffu << shift);
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) tau[qi] = s_prefix != 0 ? ((u64)s_prefix << 32) - 1 : 0;
+}
+
+// ------------------------------------------------------------------------------------------
 // merge: one CTA per query; block-wide radix select of the k-th largest key over all candidate
 // segments (read from global / L2), gather of the survivors, bitonic sort by one warp.
 // ------------------------------------------------------------------------------------------
@@ -705,12 +964,15 @@ tq_merge_kernel(const u64* __restrict__ cand, long long query_stride, long long 
     const u64* base = cand + (long long)qi * query_stride;
     const int* cnts = counts != nullptr ? counts + (long long)qi * n_segs : nullptr;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long total_slots = (long long)n_segs * seg_len;
-
-    auto key_at = [&](long long slot) -> u64 {
-        const int seg = (int)(slot / seg_len), off = (int)(slot % seg_len);
-        if (cnts != nullptr && off >= cnts[seg]) return 0;
-        return base[(long long)seg * seg_stride + off];
+    const int nwarps = blockDim.x >> 5;
+    // visits every stored key: a warp per segment, a lane per entry (only the entries in use when counts are given);
+    // the whole warp calls f together (key 0 for the lanes past the end), so f may use full-warp primitives
+    auto for_each_key = [&](auto&& f) {
+        for (int seg = warp; seg < n_segs; seg += nwarps) {
+            const int c = cnts != nullptr ? min(cnts[seg], seg_len) : seg_len;
+            const u64* sp = base + (long long)seg * seg_stride;
+            for (int off0 = 0; off0 < c; off0 += 32) f(off0 + lane < c ? sp[off0 + lane] : 0ull);
+        }
     };
 
     // number of non-empty candidates
@@ -721,7 +983,7 @@ tq_merge_kernel(const u64* __restrict__ cand, long long query_stride, long long 
     for (int i = threadIdx.x; i < kTqMaxK; i += blockDim.x) sel[i] = 0;
     __syncthreads();
     int local = 0;
-    for (long long s = threadIdx.x; s < total_slots; s += blockDim.x) local += key_at(s) != 0;
+    for_each_key([&](u64 key) { local += key != 0; });
     for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
     if (lane == 0 && local) atomicAdd(&s_total, local);
     __syncthreads();
@@ -738,36 +1000,31 @@ tq_merge_kernel(const u64* __restrict__ cand, long long query_stride, long long 
             for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
             __syncthreads();
             const u64 prefix = s_prefix, mask = s_mask;
-            for (long long s = threadIdx.x; s < total_slots; s += blockDim.x) {
-                const u64 key = key_at(s);
+            for_each_key([&](u64 key) {
                 if (key != 0 && (key & mask) == prefix) atomicAdd(&hist[(unsigned)(key >> shift) & 0xffu], 1u);
-            }
+            });
             __syncthreads();
-            if (threadIdx.x == 0) {
-                unsigned run = 0, want = s_want;
-                int d = 0;
-                for (int b = 255; b >= 0; --b) {
-                    if (run + hist[b] >= want) {
-                        d = b;
-                        break;
-                    }
-                    run += hist[b];
+            if (threadIdx.x < 32) {
+                int d;
+                unsigned nw;
+                warp_pick_digit(hist, s_want, lane, &d, &nw);
+                __syncwarp();
+                if (lane == 0) {
+                    s_want = nw;
+                    s_prefix = prefix | ((u64)(unsigned)d << shift);
+                    s_mask = mask | ((u64)0xffu << shift);
                 }
-                s_want = want - run;
-                s_prefix = prefix | ((u64)(unsigned)d << shift);
-                s_mask = mask | ((u64)0xffu << shift);
             }
             __syncthreads();
         }
         thr = s_prefix;
     }
-    for (long long s = threadIdx.x; s < total_slots; s += blockDim.x) {
-        const u64 key = key_at(s);
+    for_each_key([&](u64 key) {
         if (key != 0 && key >= thr) {
             const int pos = atomicAdd(&s_fill, 1);
             if (pos < kTqMaxK) sel[pos] = key;
         }
-    }
+    });
     __syncthreads();
     if (warp == 0) {
         // bitonic sort of 128 keys, descending; empty slots (0) sink to the end
@@ -940,7 +1197,37 @@ void launch_tq_scan(const TqScanArgs& a, cudaStream_t stream) {
     else tq_scan_kernel<4><<<a.grid, threads, smem, stream>>>(a);
 }
 
-cudaError_t tq_merge_init() { return cudaSuccess; }
+cudaError_t tq_merge_init() {
+    cudaError_t e = cudaFuncSetAttribute(tq_merge_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kListCapKeys * 8 + (kListMaxSegs + 1) * 4);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tq_seed_tau_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSeedCapScores * 4 + (kListMaxSegs + 1) * 4);
+    return e;
+}
+
+void launch_tq_merge_lists(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,
+                           const int* counts, int queries, int k, int64_t* out_ids, float* out_scores, uint64_t* out_keys,
+                           cudaStream_t stream) {
+    if (queries <= 0) return;
+    if (n_segs > kListMaxSegs) {  // more lists than the prefix table holds: the general merge
+        launch_tq_merge(cand, query_stride, seg_stride, n_segs, seg_len, counts, queries, k, 0, out_ids, out_scores,
+                        out_keys, stream);
+        return;
+    }
+    tq_merge_lists_kernel<<<queries, kListThreads, kListCapKeys * 8 + (n_segs + 1) * 4, stream>>>(
+        reinterpret_cast<const u64*>(cand), (long long)query_stride, (long long)seg_stride, n_segs, seg_len, counts, k,
+        reinterpret_cast<long long*>(out_ids), out_scores, reinterpret_cast<u64*>(out_keys));
+}
+
+bool launch_tq_seed_tau_lists(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,
+                              const int* counts, int queries, int k, unsigned long long* tau, cudaStream_t stream) {
+    if (queries <= 0 || n_segs > kListMaxSegs) return false;
+    tq_seed_tau_lists_kernel<<<queries, kListThreads, kSeedCapScores * 4 + (n_segs + 1) * 4, stream>>>(
+        reinterpret_cast<const u64*>(cand), (long long)query_stride, (long long)seg_stride, n_segs, seg_len, counts, k,
+        tau);
+    return true;
+}
 
 void launch_tq_merge(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,
                      const int* counts, int queries, int k, int64_t id_base, int64_t* out_ids, float* out_scores,

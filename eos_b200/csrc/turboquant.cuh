@@ -115,6 +115,15 @@ void launch_tq_merge(const uint64_t* cand, int64_t query_stride, int64_t seg_str
                      const int* counts, int queries, int k, int64_t id_base, int64_t* out_ids, float* out_scores,
                      uint64_t* out_keys, cudaStream_t stream);
 cudaError_t tq_merge_init();
+// The same merge for counted lists (counts != null, at most 1024 lists per query), with the keys gathered once into
+// shared memory; keys carry the document ids (no id_base).  Falls back to launch_tq_merge above 1024 lists.
+void launch_tq_merge_lists(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,
+                           const int* counts, int queries, int k, int64_t* out_ids, float* out_scores, uint64_t* out_keys,
+                           cudaStream_t stream);
+// tau[q] = largest key that every document scoring at least the k-th best score of query q's lists still beats
+// (0 when the lists hold fewer than k keys).  Returns false (nothing launched) above 1024 lists.
+bool launch_tq_seed_tau_lists(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,
+                              const int* counts, int queries, int k, unsigned long long* tau, cudaStream_t stream);
 
 // keys[q * cand + j] = sortable key (score, row) of query q against document row j (cand_ids == null, cand = n_rows)
 // or against row cand_ids[q * cand + j] (negative or out-of-range id: key 0 = absent).  docs is [n_rows, dim] fp32 or

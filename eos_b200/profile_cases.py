@@ -5,6 +5,7 @@
     python -m eos_b200.profile_cases gemm_f16w / gemm_res_f16w / gemm_qkv_f16w / gemm_attn_out_f16w
                                                  # the four projections of a layer, weights resident as f16
     python -m eos_b200.profile_cases scan        # TurboQuant scan, 2,000,000 x 768 4-bit codes (776 MB), 8 / 16 / 32 queries per pass
+    python -m eos_b200.profile_cases score_tc    # TurboQuant tensor-core batch scoring, 1,250,000 x 768 4-bit codes (485 MB), 512 queries
     python -m eos_b200.profile_cases attention   # 2-layer encoder forward, 128 x 512 tokens (attention + LN kernels)
 
 Each case touches more than the 126 MB L2 but holds well under a few GB on the device.
@@ -67,6 +68,49 @@ def case_scan(n: int = 2_000_000) -> None:
     rt.close()
 
 
+def case_score_tc(n: int = 1_250_000, nq: int = 512) -> None:
+    import torch
+
+    import eos_b200
+    from eos_b200 import turboquant as tq
+    rt = eos_b200.Runtime(0)
+    spec = eos_b200.make_rotation_spec(768, 4, seed=402)
+    qz = eos_b200.Quantizer(rt, spec)
+    chunk = 250_000
+    x = torch.empty((chunk, 768), dtype=torch.float32, device="cuda")
+    codes = torch.empty((n, 384), dtype=torch.uint8, device="cuda")
+    norms = torch.empty((n,), dtype=torch.float32, device="cuda")
+    for c0 in range(0, n, chunk):
+        c1 = min(n, c0 + chunk)
+        tq.synth_gaussian_device(rt, 401, c0, c1 - c0, 768, True, x.data_ptr())
+        qz.quantize_device(x.data_ptr(), c1 - c0, codes[c0:].data_ptr(), norms[c0:].data_ptr())
+    torch.cuda.synchronize()
+    corpus = eos_b200.Corpus(qz, device_ptrs=(codes.data_ptr(), norms.data_ptr(), n))
+    queries = torch.empty((nq, 768), dtype=torch.float32, device="cuda")
+    tq.synth_gaussian_device(rt, 403, 0, nq, 768, True, queries.data_ptr())
+    ids = torch.empty((nq, 100), dtype=torch.int64, device="cuda")
+    scores = torch.empty((nq, 100), dtype=torch.float32, device="cuda")
+    del x, codes
+    torch.cuda.empty_cache()
+    ts = torch.cuda.Stream()
+    stream = ts.cuda_stream
+    for _ in range(2):
+        corpus.score_topk_device(queries.data_ptr(), nq, 100, 128, ids.data_ptr(), scores.data_ptr(), None, stream)
+    torch.cuda.synchronize()
+    corpus.profile_begin(64)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ts)
+    corpus.score_topk_device(queries.data_ptr(), nq, 100, 128, ids.data_ptr(), scores.data_ptr(), None, stream)
+    e1.record(ts)
+    torch.cuda.synchronize()
+    ms, launches = corpus.profile_end(stream)
+    print(f"score_tc {n} rows x {nq} queries: {e0.elapsed_time(e1):.3f} ms in all, {ms / launches:.3f} ms per main launch "
+          f"({launches} launches), {2.0 * 128 * n * 768 / (ms / launches) / 1e9:.0f} TFLOP/s")
+    corpus.close()
+    qz.close()
+    rt.close()
+
+
 def case_attention() -> None:
     import eos_b200
     from eos_b200 import synth
@@ -87,7 +131,7 @@ def case_attention() -> None:
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": case_gemm, "gemm_res": lambda: case_gemm(True), "scan": case_scan, "attention": case_attention,
+    {"gemm": case_gemm, "gemm_res": lambda: case_gemm(True), "scan": case_scan, "score_tc": case_score_tc, "attention": case_attention,
      "gemm_f16w": lambda: case_gemm(False, 1), "gemm_res_f16w": lambda: case_gemm(True, 1),
      "gemm_big": lambda: case_gemm(False, 0, 131072), "gemm_res_big": lambda: case_gemm(True, 0, 131072),
      "gemm_big_f16w": lambda: case_gemm(False, 1, 131072),
