@@ -1140,6 +1140,7 @@ struct EosB200Corpus {
     __half* qperm = nullptr;        // [tc_cap_queries][padded dim] rotated queries, coordinates in code-word order
     uint64_t* tc_cand = nullptr;    // [128][2 * tc_grid][kTqTcSegLen]
     int* tc_count = nullptr;        // [128][2 * tc_grid]
+    float* tc_seed_scores = nullptr;  // [128][2 * tc_grid][128] scores of the sample that seeds the thresholds
     CUtensorMap tm_q;
     Profiler prof;
 };
@@ -1253,6 +1254,7 @@ int ensure_tc_workspace(EosB200Corpus* c, char** err) {
     if (c->tc_cand == nullptr) {
         CUDA_TRY(dev_alloc(&c->tc_cand, (size_t)kTqTcQueries * 2 * c->tc_grid * kTqTcSegLen));
         CUDA_TRY(dev_alloc(&c->tc_count, (size_t)kTqTcQueries * 2 * c->tc_grid));
+        CUDA_TRY(dev_alloc(&c->tc_seed_scores, (size_t)kTqTcQueries * 2 * c->tc_grid * (kTqTcDocs / 2)));
     }
     const std::string m = tq_tc_make_query_map(&c->tm_q, c->qperm, dimp, c->cap_queries);
     if (!m.empty()) return fail(err, "score_topk: " + m);
@@ -1266,7 +1268,8 @@ __global__ void seed_tau_kernel(const uint64_t* __restrict__ keys, int q_count, 
     const int q = blockIdx.x * blockDim.x + threadIdx.x;
     if (q >= q_count) return;
     const uint64_t kth = keys[(size_t)q * k + (k - 1)];
-    tau[q] = kth != 0 ? kth - 1 : 0;
+    const unsigned long long t = kth != 0 ? kth - 1 : 0;
+    if (t > tau[q]) tau[q] = t;  // never below a threshold that is already there
 }
 
 // Scan passes of `per_pass` queries over the first n_docs rows + one merge per group of queries.
@@ -1315,8 +1318,8 @@ int enqueue_scan_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, in
 
 // Tensor-core launches of kTqTcQueries queries over the first n_docs rows.  seed = true: the lists of each launch
 // become the pruning thresholds of its queries (shared_tau); otherwise they are merged into the top-k outputs.
-int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool seed, int64_t* d_ids, float* d_scores,
-                      uint64_t* d_keys, cudaStream_t s) {
+int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool seed, bool profile, int64_t* d_ids,
+                      float* d_scores, uint64_t* d_keys, cudaStream_t s) {
     EosB200Quantizer* qz = c->qz;
     const int64_t tiles = (n_docs + kTqTcDocs - 1) / kTqTcDocs;
     const int grid = (int)(tiles < c->tc_grid ? tiles : c->tc_grid);
@@ -1340,12 +1343,13 @@ int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool
         a.cand_keys = c->tc_cand;
         a.cand_count = c->tc_count;
         a.shared_tau = c->shared_tau + q0;
+        a.seed_scores = seed ? c->tc_seed_scores : nullptr;
         a.status = qz->rt->d_status;
-        if (!seed) c->prof.launch(kClsScan, s, [&] { launch_tq_score_tc(c->tm_q, a, grid, s); });
+        if (profile) c->prof.launch(kClsScan, s, [&] { launch_tq_score_tc(c->tm_q, a, grid, s); });
         else launch_tq_score_tc(c->tm_q, a, grid, s);
-        if (seed)
-            launch_tq_seed_tau_lists(c->tc_cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, c->tc_count,
-                                     q_here, k, c->shared_tau + q0, s);
+        if (seed)  // n_docs = grid * 256 here: the rows of a query are n_segs * 128 contiguous scores
+            launch_tq_seed_tau_scores(c->tc_seed_scores, (int64_t)n_segs * (kTqTcDocs / 2), (int)n_docs, q_here, k,
+                                      c->shared_tau + q0, s);
         else
             launch_tq_merge_lists(c->tc_cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, c->tc_count,
                                   q_here, k, d_ids != nullptr ? d_ids + (size_t)q0 * k : nullptr,
@@ -1356,8 +1360,10 @@ int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool
     return launches;
 }
 
-// The batch path: thresholds seeded from the first tc_grid * 256 rows (one tile per CTA, so no list is cut while
-// every document still passes), then the whole shard.
+// The batch path.  Thresholds are seeded from the first tc_grid * 256 rows (one tile per CTA, every score written out,
+// k-th best per query); on a large shard a second sample of 1/32 of the rows, scored with those thresholds and merged
+// like the real pass, tightens them further, so that the lists of the full pass stay short (no list is cut, and the
+// merge gathers a few thousand keys per query).  Then the whole shard.
 int enqueue_score_tc(EosB200Corpus* c, const float* d_queries, int q_count, int k, int64_t* d_ids, float* d_scores,
                      uint64_t* d_keys, cudaStream_t s) {
     const int q_pad = (q_count + kTqTcQueries - 1) / kTqTcQueries * kTqTcQueries;
@@ -1365,9 +1371,16 @@ int enqueue_score_tc(EosB200Corpus* c, const float* d_queries, int q_count, int 
     launch_tq_prepare(d_queries, q_count, q_pad, c->qz->spec(), nullptr, nullptr, c->qperm, s);
     cudaMemsetAsync(c->shared_tau, 0, (size_t)q_pad * sizeof(unsigned long long), s);
     const int64_t seed_docs = (int64_t)c->tc_grid * kTqTcDocs;
-    if (c->n >= 8 * seed_docs && k <= seed_docs && 2 * c->tc_grid <= 1024)
-        launches += enqueue_tc_passes(c, seed_docs, q_count, k, true, nullptr, nullptr, nullptr, s);
-    launches += enqueue_tc_passes(c, c->n, q_count, k, false, d_ids, d_scores, d_keys, s);
+    if (c->n >= 8 * seed_docs && k <= seed_docs) {
+        launches += enqueue_tc_passes(c, seed_docs, q_count, k, true, false, nullptr, nullptr, nullptr, s);
+        if (c->n >= 64 * seed_docs) {
+            const int64_t second = c->n / 32 / kTqTcDocs * kTqTcDocs;
+            launches += enqueue_tc_passes(c, second, q_count, k, false, false, nullptr, nullptr, c->seed_keys, s);
+            seed_tau_kernel<<<(q_count + 255) / 256, 256, 0, s>>>(c->seed_keys, q_count, k, c->shared_tau);
+            launches++;
+        }
+    }
+    launches += enqueue_tc_passes(c, c->n, q_count, k, false, true, d_ids, d_scores, d_keys, s);
     return launches;
 }
 
@@ -1385,7 +1398,7 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
     // spares every CTA of every pass the phase in which nearly every document is still a candidate.
     constexpr int64_t kSeedDocs = 16384;
     const bool seeded = per_pass == 8 && c->n >= 8 * kSeedDocs && k <= kSeedDocs;
-    if (per_pass == 8 && !seeded)
+    if (per_pass == 8)
         cudaMemsetAsync(c->shared_tau, 0, (size_t)((q_count + 31) / 32 * 32) * sizeof(unsigned long long), s);
     if (seeded) {
         launches += enqueue_scan_passes(c, kSeedDocs, q_count, k, 32, false, false, nullptr, nullptr, c->seed_keys, s);
@@ -1539,6 +1552,7 @@ void eos_b200_corpus_destroy(EosB200Corpus* c) {
     dev_free(c->qperm);
     dev_free(c->tc_cand);
     dev_free(c->tc_count);
+    dev_free(c->tc_seed_scores);
     c->prof.reset();
     delete c;
 }

@@ -876,39 +876,45 @@ tq_merge_lists_kernel(const u64* __restrict__ cand, long long query_stride, long
     }
 }
 
-// Pruning thresholds from the lists of a sample: tau[q] = (k-th best score among the first kSeedCapScores keys of
-// query q's lists, as a key with id bits 0) - 1, so that every document scoring at least that much still passes;
-// 0 when the sample holds fewer than k keys.  Only the 32 score bits of a key are kept, which lets a sample of
-// tens of thousands of documents sit in shared memory.  Any subset's k-th best is a valid lower bound.
+// Pruning thresholds from the scores of a sample: scores is [queries][total] fp32 (every sample document's score,
+// written by the batch kernel in its seed mode).  tau[q] = (k-th best score, as a key with id bits 0) - 1, so that
+// every document scoring at least that much still passes; 0 when the sample holds fewer than k documents.  The
+// order-preserving 32 score bits of up to kSeedCapScores documents sit in shared memory; the radix select counts
+// into one histogram per warp (the scores of a query share their leading digits, and a single histogram would
+// serialise every warp on one counter).
 __global__ void __launch_bounds__(kListThreads)
-tq_seed_tau_lists_kernel(const u64* __restrict__ cand, long long query_stride, long long seg_stride, int n_segs,
-                         int seg_len, const int* __restrict__ counts, int k, unsigned long long* __restrict__ tau) {
+tq_seed_tau_scores_kernel(const float* __restrict__ scores, long long query_stride, int total, int k,
+                          unsigned long long* __restrict__ tau) {
     extern __shared__ __align__(16) uint8_t lsm[];
-    uint32_t* buf = reinterpret_cast<uint32_t*>(lsm);              // [kSeedCapScores]
-    int* prefix = reinterpret_cast<int*>(buf + kSeedCapScores);    // [n_segs + 1]
+    uint32_t* buf = reinterpret_cast<uint32_t*>(lsm);                 // [kSeedCapScores]
+    unsigned* whist = reinterpret_cast<unsigned*>(buf + kSeedCapScores);  // [warps][256]
     __shared__ unsigned hist[256];
     __shared__ uint32_t s_prefix, s_mask;
     __shared__ unsigned s_want;
     const int qi = blockIdx.x;
-    const u64* base = cand + (long long)qi * query_stride;
-    int total = list_prefix(counts + (long long)qi * n_segs, n_segs, seg_len, prefix);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const float* src = scores + (long long)qi * query_stride;
     if (total > kSeedCapScores) total = kSeedCapScores;
-    for (int i0 = threadIdx.x; i0 < total; i0 += 8 * kListThreads) {
-        u64 v[8];
+    auto ordered = [](float v) { return v == v ? float_to_ordered(v) : 0u; };  // NaN (no document) sorts last
+    if ((query_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(scores) & 15u) == 0) {
+        const float4* src4 = reinterpret_cast<const float4*>(src);
+        const int n4 = total >> 2;
+        for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * kListThreads) {  // four independent 16-byte loads in flight
+            float4 v[4];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * kListThreads;
-            v[u] = 0;
-            if (i < total) {
-                const int seg = list_find(prefix, n_segs, i);
-                v[u] = base[(long long)seg * seg_stride + (i - prefix[seg])];
+            for (int u = 0; u < 4; ++u)
+                if (i0 + u * kListThreads < n4) v[u] = src4[i0 + u * kListThreads];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * kListThreads;
+                if (i < n4)
+                    reinterpret_cast<uint4*>(buf)[i] =
+                        make_uint4(ordered(v[u].x), ordered(v[u].y), ordered(v[u].z), ordered(v[u].w));
             }
         }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * kListThreads;
-            if (i < total) buf[i] = (uint32_t)(v[u] >> 32);
-        }
+        for (int i = (n4 << 2) + threadIdx.x; i < total; i += blockDim.x) buf[i] = ordered(src[i]);
+    } else {
+        for (int i = threadIdx.x; i < total; i += blockDim.x) buf[i] = ordered(src[i]);
     }
     if (threadIdx.x == 0) {
         s_prefix = 0;
@@ -921,20 +927,26 @@ tq_seed_tau_lists_kernel(const u64* __restrict__ cand, long long query_stride, l
         return;
     }
     for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
-        __syncthreads();
+        for (int i = lane; i < 256; i += 32) whist[warp * 256 + i] = 0;
+        __syncwarp();
         const uint32_t pre = s_prefix, mask = s_mask;
         for (int i = threadIdx.x; i < total; i += blockDim.x) {
             const uint32_t key = buf[i];
-            if ((key & mask) == pre) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
+            if ((key & mask) == pre) atomicAdd(&whist[warp * 256 + ((key >> shift) & 0xffu)], 1u);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+            unsigned sum = 0;
+            for (int w = 0; w < nwarps; ++w) sum += whist[w * 256 + i];
+            hist[i] = sum;
         }
         __syncthreads();
         if (threadIdx.x < 32) {
             int d;
             unsigned nw;
-            warp_pick_digit(hist, s_want, (int)threadIdx.x, &d, &nw);
+            warp_pick_digit(hist, s_want, lane, &d, &nw);
             __syncwarp();
-            if (threadIdx.x == 0) {
+            if (lane == 0) {
                 s_want = nw;
                 s_prefix = pre | ((uint32_t)d << shift);
                 s_mask = mask | (0xffu << shift);
@@ -1201,8 +1213,8 @@ cudaError_t tq_merge_init() {
     cudaError_t e = cudaFuncSetAttribute(tq_merge_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kListCapKeys * 8 + (kListMaxSegs + 1) * 4);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(tq_seed_tau_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kSeedCapScores * 4 + (kListMaxSegs + 1) * 4);
+        e = cudaFuncSetAttribute(tq_seed_tau_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSeedCapScores * 4 + (kListThreads / 32) * 256 * 4);
     return e;
 }
 
@@ -1220,13 +1232,11 @@ void launch_tq_merge_lists(const uint64_t* cand, int64_t query_stride, int64_t s
         reinterpret_cast<long long*>(out_ids), out_scores, reinterpret_cast<u64*>(out_keys));
 }
 
-bool launch_tq_seed_tau_lists(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,
-                              const int* counts, int queries, int k, unsigned long long* tau, cudaStream_t stream) {
-    if (queries <= 0 || n_segs > kListMaxSegs) return false;
-    tq_seed_tau_lists_kernel<<<queries, kListThreads, kSeedCapScores * 4 + (n_segs + 1) * 4, stream>>>(
-        reinterpret_cast<const u64*>(cand), (long long)query_stride, (long long)seg_stride, n_segs, seg_len, counts, k,
-        tau);
-    return true;
+void launch_tq_seed_tau_scores(const float* scores, int64_t query_stride, int total, int queries, int k,
+                               unsigned long long* tau, cudaStream_t stream) {
+    if (queries <= 0) return;
+    tq_seed_tau_scores_kernel<<<queries, kListThreads, kSeedCapScores * 4 + (kListThreads / 32) * 256 * 4, stream>>>(
+        scores, (long long)query_stride, total, k, tau);
 }
 
 void launch_tq_merge(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,

@@ -101,6 +101,8 @@ struct TqTcArgs {
     int* cand_count;       // [kTqTcQueries][2 * grid]
     unsigned long long* shared_tau;  // [kTqTcQueries] pruning thresholds: seeded by the caller (0 = none), raised by
                                      // every CTA that cuts a list
+    float* seed_scores;    // seed mode when non-null (at most one tile per CTA): every score goes to
+                           // seed_scores[query][2 * grid][128] and no list is kept
     int* status;
 };
 cudaError_t tq_tc_init();
@@ -120,10 +122,10 @@ cudaError_t tq_merge_init();
 void launch_tq_merge_lists(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,
                            const int* counts, int queries, int k, int64_t* out_ids, float* out_scores, uint64_t* out_keys,
                            cudaStream_t stream);
-// tau[q] = largest key that every document scoring at least the k-th best score of query q's lists still beats
-// (0 when the lists hold fewer than k keys).  Returns false (nothing launched) above 1024 lists.
-bool launch_tq_seed_tau_lists(const uint64_t* cand, int64_t query_stride, int64_t seg_stride, int n_segs, int seg_len,
-                              const int* counts, int queries, int k, unsigned long long* tau, cudaStream_t stream);
+// tau[q] = largest key that every document scoring at least the k-th best of scores[q][0..total) still beats (0 when
+// total < k); scores is [queries][query_stride] fp32, NaN = no document.  At most 49152 scores per query are used.
+void launch_tq_seed_tau_scores(const float* scores, int64_t query_stride, int total, int queries, int k,
+                               unsigned long long* tau, cudaStream_t stream);
 
 // keys[q * cand + j] = sortable key (score, row) of query q against document row j (cand_ids == null, cand = n_rows)
 // or against row cand_ids[q * cand + j] (negative or out-of-range id: key 0 = absent).  docs is [n_rows, dim] fp32 or

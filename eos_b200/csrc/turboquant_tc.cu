@@ -25,8 +25,9 @@
 //               (no atomics).  A list that could overflow during the next tile is cut to its k best by the
 //               whole warp (bitonic sort in shared memory) and the k-th key is published with atomicMax as
 //               the query's threshold for every CTA.
-// Thresholds start from a sample (the caller runs this kernel over the first rows of the shard first), so
-// in the steady state a few documents per thousand reach a list.
+// Thresholds start from a sample: the caller first runs this kernel in its seed mode over the first rows of
+// the shard (one tile per CTA; the epilogue writes every score, 32 bytes per store, instead of keeping lists)
+// and takes each query's k-th best sample score, so in the steady state a few documents per thousand reach a list.
 // Every mbarrier wait is bounded (common.cuh: mbar_wait): on a timeout all roles leave their loops,
 // tensor memory is freed and the status word is set.
 #include "common.cuh"
@@ -292,6 +293,8 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * TD + epart * (TD / 2);
             const uint32_t doc0 = a.id_base + (uint32_t)(tile * TD) + (uint32_t)(epart * (TD / 2));
             const float* nrm_w = nrm + epart * (TD / 2);
+            float* seed_row = a.seed_scores != nullptr
+                                  ? a.seed_scores + ((size_t)qrow * n_segs + seg) * (TD / 2) : nullptr;
             auto chunk = [&](const uint32_t (&r)[16], const int c0) {
                 float sc[16];
                 bool any = false;
@@ -304,7 +307,17 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
                     sc[j + 3] = __uint_as_float(r[j + 3]) * nv.w;
                     any |= (sc[j] >= tau_f) | (sc[j + 1] >= tau_f) | (sc[j + 2] >= tau_f) | (sc[j + 3] >= tau_f);
                 }
-                if (any) {
+                if (seed_row != nullptr) {
+                    // seed mode: the thread's 16 scores are 64 contiguous bytes of its query's row
+                    uint32_t lo8[8], hi8[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        lo8[j] = __float_as_uint(sc[j]);
+                        hi8[j] = __float_as_uint(sc[8 + j]);
+                    }
+                    st_global_v8(seed_row + c0, lo8);
+                    st_global_v8(seed_row + c0 + 8, hi8);
+                } else if (any) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         if (sc[j] >= tau_f) {
