@@ -35,8 +35,8 @@ TQ = dict(dim=768, bits=4, corpus=10_000_000, queries=4096, k=100)
 # cases of eos_b200/profile_cases.py, per row of the launch; the summaries are under profiles/.
 NCU_GEMM_DRAM_BYTES_PER_ROW = {"qkv": 152.35e6 / 32768, "attn_out": 124.88e6 / 32768, "ffn_up": 207.08e6 / 32768,
                                "ffn_down": 291.77e6 / 32768}
-NCU_SCAN_DRAM_BYTES_PER_ROW = 783.74e6 / 2_000_000
-NCU_TC_DRAM_BYTES_PER_ROW = None  # DRAM bytes per row of one tq_score_tc_kernel launch, from an ncu capture
+NCU_SCAN_DRAM_BYTES_PER_ROW = 780.13e6 / 2_000_000
+NCU_TC_DRAM_BYTES_PER_ROW = 493.16e6 / 1_250_000  # profiles/tq_score_tc_kernel_*.md
 
 
 def load_peaks():
