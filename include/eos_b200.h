@@ -269,7 +269,12 @@ EOS_B200_API int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* corpus);
 /* Replaces PrepareQuery + topTurboQuantRetrievalScoresWithStats per query
  * (runtime/retrieval_turboquant.go:1324-1325, 1853-1887): exact top-k of
  * norm * <R q, centroids[codes]> over the corpus, for q_count queries [q_count, dim] fp32.
- * queries_per_pass in {8, 16, 32}: queries scored per streaming pass over the codes.
+ * queries_per_pass selects how many queries share one pass over the codes, and with it the kernel:
+ *   8        streaming scan (codes expanded in registers, mma.sync): the choice for a few queries;
+ *   16, 32   the same scan with more query fragments per pass;
+ *   128      batch kernel on the tensor cores (codes expanded once per 128 queries into a tcgen05
+ *            operand tile): the choice for hundreds of queries; q_count need not be a multiple of 128.
+ * The result is the same exact top-k for every value.
  * Results [q_count, k]: ids (int64, -1 when the corpus has fewer than k rows) and scores, ordered
  * score descending then id ascending.  k <= 128. */
 EOS_B200_API int eos_b200_score_topk(EosB200Corpus* corpus, const float* h_queries, int q_count, int k, int queries_per_pass,
@@ -279,6 +284,7 @@ EOS_B200_API int eos_b200_score_topk(EosB200Corpus* corpus, const float* h_queri
 EOS_B200_API int eos_b200_score_topk_device(EosB200Corpus* corpus, const float* d_queries, int q_count, int k,
                                int queries_per_pass, int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream,
                                EosB200Stats* stats, char** err);
+/* (eos_b200_score_topk_noalloc below takes queries_per_pass in {8, 16, 32} only.) */
 /* No counterpart in Eos: a scoring call for hosts that must not allocate device memory while they
  * serve queries -- for example a caller that holds the GPU inside a pre-sized memory arena, runs
  * with allocation forbidden after start-up, or sits on a latency path where a cudaMalloc (which can
