@@ -1136,6 +1136,8 @@ struct EosB200Corpus {
     int grid = 0;
     // tensor-core batch path (128 queries per launch), allocated on first use
     int tc_grid = 0;
+    int tc_tile_docs = 0;           // 128 with the queries resident in tensor memory (tc_q_in_tmem), else 256
+    bool tc_q_in_tmem = false;
     int tc_cap_queries = 0;
     __half* qperm = nullptr;        // [tc_cap_queries][padded dim] rotated queries, coordinates in code-word order
     uint64_t* tc_cand = nullptr;    // [128][2 * tc_grid][kTqTcSegLen]
@@ -1246,7 +1248,13 @@ int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
 int ensure_tc_workspace(EosB200Corpus* c, char** err) {
     if (c->tc_cap_queries == c->cap_queries && c->qperm != nullptr) return EOS_B200_OK;
     const int dimp = tq_ksteps(c->qz->dim) * 16;
-    const int64_t tiles = (c->n + kTqTcDocs - 1) / kTqTcDocs;
+    // The variant with the queries resident in tensor memory is correct but measured slower (0.42 ms against 0.26 ms per
+    // launch over 1.25 M rows: its 128-document tiles double the hand-offs per document and its single accumulator
+    // serialises epilogue and MMA), so it is opt-in.
+    const char* in_tmem = getenv("EOS_B200_TQ_QUERIES_IN_TMEM");
+    c->tc_q_in_tmem = tq_tc_queries_fit_tmem(c->qz->dim) && in_tmem != nullptr && in_tmem[0] != '\0' && in_tmem[0] != '0';
+    c->tc_tile_docs = c->tc_q_in_tmem ? kTqTcDocsQ : kTqTcDocs;
+    const int64_t tiles = (c->n + c->tc_tile_docs - 1) / c->tc_tile_docs;
     c->tc_grid = (int)(tiles < c->qz->rt->sm_count ? (tiles > 0 ? tiles : 1) : c->qz->rt->sm_count);
     dev_free(c->qperm);
     c->tc_cap_queries = 0;
@@ -1254,7 +1262,7 @@ int ensure_tc_workspace(EosB200Corpus* c, char** err) {
     if (c->tc_cand == nullptr) {
         CUDA_TRY(dev_alloc(&c->tc_cand, (size_t)kTqTcQueries * 2 * c->tc_grid * kTqTcSegLen));
         CUDA_TRY(dev_alloc(&c->tc_count, (size_t)kTqTcQueries * 2 * c->tc_grid));
-        CUDA_TRY(dev_alloc(&c->tc_seed_scores, (size_t)kTqTcQueries * 2 * c->tc_grid * (kTqTcDocs / 2)));
+        CUDA_TRY(dev_alloc(&c->tc_seed_scores, (size_t)kTqTcQueries * c->tc_grid * kTqTcDocs));
     }
     const std::string m = tq_tc_make_query_map(&c->tm_q, c->qperm, dimp, c->cap_queries);
     if (!m.empty()) return fail(err, "score_topk: " + m);
@@ -1321,7 +1329,7 @@ int enqueue_scan_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, in
 int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool seed, bool profile, int64_t* d_ids,
                       float* d_scores, uint64_t* d_keys, cudaStream_t s) {
     EosB200Quantizer* qz = c->qz;
-    const int64_t tiles = (n_docs + kTqTcDocs - 1) / kTqTcDocs;
+    const int64_t tiles = (n_docs + c->tc_tile_docs - 1) / c->tc_tile_docs;
     const int grid = (int)(tiles < c->tc_grid ? tiles : c->tc_grid);
     const int n_segs = 2 * grid;
     int launches = 0;
@@ -1344,12 +1352,13 @@ int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool
         a.cand_count = c->tc_count;
         a.shared_tau = c->shared_tau + q0;
         a.seed_scores = seed ? c->tc_seed_scores : nullptr;
+        a.seed_stride = n_docs;  // seed mode: n_docs = tc_grid * 256 scores per query, a multiple of the tile
+        a.qperm = c->qperm;
         a.status = qz->rt->d_status;
-        if (profile) c->prof.launch(kClsScan, s, [&] { launch_tq_score_tc(c->tm_q, a, grid, s); });
-        else launch_tq_score_tc(c->tm_q, a, grid, s);
-        if (seed)  // n_docs = grid * 256 here: the rows of a query are n_segs * 128 contiguous scores
-            launch_tq_seed_tau_scores(c->tc_seed_scores, (int64_t)n_segs * (kTqTcDocs / 2), (int)n_docs, q_here, k,
-                                      c->shared_tau + q0, s);
+        if (profile) c->prof.launch(kClsScan, s, [&] { launch_tq_score_tc(c->tm_q, a, c->tc_q_in_tmem, grid, s); });
+        else launch_tq_score_tc(c->tm_q, a, c->tc_q_in_tmem, grid, s);
+        if (seed)
+            launch_tq_seed_tau_scores(c->tc_seed_scores, n_docs, (int)n_docs, q_here, k, c->shared_tau + q0, s);
         else
             launch_tq_merge_lists(c->tc_cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, c->tc_count,
                                   q_here, k, d_ids != nullptr ? d_ids + (size_t)q0 * k : nullptr,

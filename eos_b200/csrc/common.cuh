@@ -87,6 +87,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tmap,
 }
 
 // Asks L2 to fetch a tile ahead of the TMA load that will bring it into shared memory.
+// Asks the L2 for `bytes` (a multiple of 16) of global memory starting at a 16-byte aligned address; no data reaches
+// the SM and nothing has to be waited for.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gptr), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int x, int y) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
 }
@@ -195,6 +200,31 @@ __device__ __forceinline__ void umma_f16_split(uint32_t d_tmem, uint32_t a_lo, u
         "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same MMA with the A operand in tensor memory (lanes = the 128 rows of A, one 32-bit column per two consecutive
+// f16 elements along K: a K = 16 step reads 8 columns) and B through its shared-memory descriptor.
+__device__ __forceinline__ void umma_f16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                                uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n .reg .b64 db;\n setp.ne.b32 p, %5, 0;\n"
+        " mov.b64 db, {%2, %3};\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 columns written from registers: thread i of the warp writes columns [col, col+32) of TMEM lane
+// (lane_base + i).  tmem_st_wait makes the stores of this thread visible before a following fence + barrier.
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // One MMA over a CTA pair (cta_group::2), issued by one thread of the pair's leader CTA: M = 256
 // (128 rows from each CTA's A tile), B = the two CTAs' tiles side by side along N; each CTA's
 // tensor memory receives its own 128 rows of D.  The descriptors are offsets valid in both CTAs.

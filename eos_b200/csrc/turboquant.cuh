@@ -84,7 +84,8 @@ void launch_tq_scan(const TqScanArgs& a, cudaStream_t stream);
 
 // Batched scoring on the tensor cores (turboquant_tc.cu): one launch = kTqTcQueries queries x the whole shard.
 constexpr int kTqTcQueries = 128;  // queries per launch
-constexpr int kTqTcDocs = 256;     // documents per tile
+constexpr int kTqTcDocs = 256;     // documents per tile, queries staged through shared memory
+constexpr int kTqTcDocsQ = 128;    // documents per tile, queries resident in tensor memory (padded dim <= 768)
 constexpr int kTqTcSegLen = 256;   // slots of one candidate list; a launch of `grid` CTAs fills 2 * grid lists per query
 struct TqTcArgs {
     const uint8_t* tiles;
@@ -101,14 +102,19 @@ struct TqTcArgs {
     int* cand_count;       // [kTqTcQueries][2 * grid]
     unsigned long long* shared_tau;  // [kTqTcQueries] pruning thresholds: seeded by the caller (0 = none), raised by
                                      // every CTA that cuts a list
-    float* seed_scores;    // seed mode when non-null (at most one tile per CTA): every score goes to
-                           // seed_scores[query][2 * grid][128] and no list is kept
+    float* seed_scores;    // seed mode when non-null: every score goes to seed_scores[query * seed_stride + row] and
+    int64_t seed_stride;   // no list is kept
+    const __half* qperm;   // the permuted f16 query matrix itself (variant with the queries in tensor memory)
     int* status;
 };
 cudaError_t tq_tc_init();
 // Tensor map of the permuted query matrix [rows][padded_dim] f16 (rows a multiple of kTqTcQueries).
 std::string tq_tc_make_query_map(CUtensorMap* tm, const __half* qperm, int padded_dim, int rows);
-void launch_tq_score_tc(const CUtensorMap& tm_q, const TqTcArgs& a, int grid, cudaStream_t stream);
+// True when the rotated queries of a launch fit tensor memory beside one accumulator (padded dim <= 768).
+bool tq_tc_queries_fit_tmem(int dim);
+// q_in_tmem selects the variant: tiles of kTqTcDocsQ documents with the queries resident in tensor memory, or tiles
+// of kTqTcDocs documents with the queries staged through shared memory by TMA (tm_q).
+void launch_tq_score_tc(const CUtensorMap& tm_q, const TqTcArgs& a, bool q_in_tmem, int grid, cudaStream_t stream);
 
 // For every query: the k best of n_segs x seg_len candidate keys (key 0 = empty), sorted by
 // score descending then id ascending.  cand is [queries][n_segs][seg_len] with the given

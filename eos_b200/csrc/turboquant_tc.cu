@@ -28,6 +28,15 @@
 // Thresholds start from a sample: the caller first runs this kernel in its seed mode over the first rows of
 // the shard (one tile per CTA; the epilogue writes every score, 32 bytes per store, instead of keeping lists)
 // and takes each query's k-th best sample score, so in the steady state a few documents per thousand reach a list.
+//
+// Two variants of the same kernel.  kQInTmem = false is the one described above and the one used.  kQInTmem = true
+// (padded dimension <= 768, opt-in) keeps the 128 queries in tensor memory for the whole launch (dim / 2 columns,
+// written once with tcgen05.st) and issues tcgen05.mma with A from tensor memory, so that no query tile crosses
+// shared memory.  Tensor memory then has room for one 128-column accumulator: a tile is 128 documents, its epilogue
+// does not overlap the next tile's MMAs and every document costs twice the ring hand-offs; measured 0.42 ms per
+// launch over 1.25 M rows against 0.26 ms, which shows that the expanders and the hand-offs, not the shared-memory
+// bandwidth, set the pace.  The expanders ask the L2 for their codes a tile ahead (no measurable effect: the stream
+// is not latency-bound either).
 // Every mbarrier wait is bounded (common.cuh: mbar_wait): on a timeout all roles leave their loops,
 // tensor memory is freed and the status word is set.
 #include "common.cuh"
@@ -39,34 +48,48 @@ namespace eosb {
 
 namespace {
 
-constexpr int TD = kTqTcDocs;       // documents per tile (MMA N)
 constexpr int TQ = kTqTcQueries;    // queries per launch (MMA M)
 constexpr int TK = 64;              // coordinates per k-block
-constexpr int kStQ = 4;             // query ring
-constexpr int kStD = 4;             // expanded-document ring
+constexpr int kStQ = 4;             // query ring (shared-memory variant)
 constexpr uint32_t kBytesQ = TQ * TK * 2;
-constexpr uint32_t kBytesD = TD * TK * 2;
 constexpr int kExpWarps = 8;
 constexpr int kEpiWarps = 8;
 constexpr int kFirstExp = 4;
 constexpr int kFirstEpi = kFirstExp + kExpWarps;
 constexpr int kThreads = (kFirstEpi + kEpiWarps) * 32;
 constexpr int kTmemCols = 512;
-constexpr int kCutAbove = TD / 2;   // a list longer than this is cut before the next tile (which adds <= 128)
+constexpr int kCutAbove = 128;      // a list longer than this is cut before the next tile (which adds <= 128)
+constexpr int kQTmemCol = 128;      // first tensor-memory column of the resident queries (after the accumulator)
 
-constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffD = kOffQ + kStQ * kBytesQ;
-constexpr uint32_t kOffNorm = kOffD + kStD * kBytesD;            // 2 x 256 floats
-constexpr uint32_t kOffSort = kOffNorm + 2 * TD * 4;             // 8 warps x 256 keys
-constexpr uint32_t kOffBars = kOffSort + kEpiWarps * kSortCap * 8;
-constexpr uint32_t kNumBars = 2 * kStQ + 2 * kStD + 4;
-constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
-constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+template <bool kQInTmem>
+struct Cfg {
+    static constexpr int TD = kQInTmem ? kTqTcDocsQ : kTqTcDocs;   // documents per tile (MMA N)
+    static constexpr int kAccBufs = kQInTmem ? 1 : 2;
+    static constexpr int kStD = kQInTmem ? 8 : 4;                  // expanded-document ring
+    static constexpr uint32_t kBytesD = TD * TK * 2;
+    static constexpr int kGroups = TD / kTqDocsPerTile / kExpWarps;  // 16-document groups per expander warp
+    static constexpr uint32_t kOffQ = 0;
+    static constexpr uint32_t kOffD = kOffQ + (kQInTmem ? 0 : kStQ * kBytesQ);
+    static constexpr uint32_t kOffNorm = kOffD + kStD * kBytesD;            // 2 x TD floats
+    static constexpr uint32_t kOffSort = kOffNorm + 2 * TD * 4;             // 8 warps x 256 keys
+    static constexpr uint32_t kOffBars = kOffSort + kEpiWarps * kSortCap * 8;
+    static constexpr uint32_t kNumBars = 2 * kStQ + 2 * kStD + 4;
+    static constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
+    static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+    static_assert(kGroups >= 1 && TD / 2 <= 128 && kTqTcSegLen >= kCutAbove + TD / 2, "tile shape / list capacity");
+};
 
-static_assert(kTqTcSegLen == kSortCap && kTqTcSegLen >= kCutAbove + TD / 2, "list capacity");
+static_assert(kTqTcSegLen == kSortCap, "a list is sorted in one piece");
 static_assert(kTqMaxK <= kCutAbove, "a cut keeps k <= 128 keys");
 
+template <bool kQInTmem>
 __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_constant__ CUtensorMap tm_q, TqTcArgs a) {
+    using C = Cfg<kQInTmem>;
+    constexpr int TD = C::TD;
+    constexpr int kStD = C::kStD;
+    constexpr uint32_t kBytesD = C::kBytesD;
+    constexpr uint32_t kOffQ = C::kOffQ, kOffD = C::kOffD, kOffNorm = C::kOffNorm, kOffSort = C::kOffSort;
+    constexpr uint32_t kOffBars = C::kOffBars, kOffMisc = C::kOffMisc;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -104,7 +127,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
             mbar_init(acc_empty(s), kEpiWarps);
         }
         mbar_fence_init();
-        tma_prefetch_desc(&tm_q);
+        if (!kQInTmem) tma_prefetch_desc(&tm_q);
     }
     if (warp == 2) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
@@ -115,9 +138,34 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    if (kQInTmem) {
+        // the launch's 128 queries move into tensor memory once: lane = query, column kQTmemCol + w = the w-th
+        // 32-bit word (two consecutive f16 coordinates) of its permuted row
+        if (warp >= kFirstEpi && warp < kFirstEpi + 4) {
+            const int quarter = warp & 3;
+            const uint4* src = reinterpret_cast<const uint4*>(a.qperm + (size_t)(a.q_row0 + quarter * 32 + lane) * (num_kb * TK));
+            for (int kb = 0; kb < num_kb; ++kb) {
+                uint32_t r[32];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 v = __ldg(src + kb * 8 + i);
+                    r[4 * i] = v.x;
+                    r[4 * i + 1] = v.y;
+                    r[4 * i + 2] = v.z;
+                    r[4 * i + 3] = v.w;
+                }
+                tmem_st_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + kQTmemCol + kb * 32, r);
+            }
+            tmem_st_wait();
+        }
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+    }
+
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer (queries)
-        if (lane == 0) {
+        // ------------------------------------------------------------ TMA producer (queries; shared-memory variant)
+        if (!kQInTmem && lane == 0) {
             uint32_t it = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
@@ -141,15 +189,15 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
             uint32_t it = 0, t = 0;
             bool ok = true;
             for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++t) {
-                const uint32_t ab = t & 1u;
-                const uint32_t aph = (t >> 1) & 1u;
+                const uint32_t ab = t % C::kAccBufs;
+                const uint32_t aph = (t / C::kAccBufs) & 1u;
                 if (!mbar_wait(acc_empty(ab), aph ^ 1u, abort_flag)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * TD;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % kStQ;
                     const int c = it % kStD;
-                    if (!mbar_wait(full_q(s), (it / kStQ) & 1u, abort_flag) ||
+                    if ((!kQInTmem && !mbar_wait(full_q(s), (it / kStQ) & 1u, abort_flag)) ||
                         !mbar_wait(full_d(c), (it / kStD) & 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -158,10 +206,15 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
                     const uint32_t q_lo = umma_desc_sw128_lo(base + kOffQ + s * kBytesQ);
                     const uint32_t d_lo = umma_desc_sw128_lo(base + kOffD + c * kBytesD);
 #pragma unroll
-                    for (int k = 0; k < TK / 16; ++k)
-                        umma_f16_split(d_tmem, q_lo + k * 2, kDescSw128Hi, d_lo + k * 2, kDescSw128Hi, idesc,
-                                       (kb > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(empty_q(s));
+                    for (int k = 0; k < TK / 16; ++k) {
+                        if (kQInTmem)
+                            umma_f16_tmem_a(d_tmem, tmem_base + kQTmemCol + kb * 32 + k * 8, d_lo + k * 2, kDescSw128Hi, idesc,
+                                            (kb > 0 || k > 0) ? 1u : 0u);
+                        else
+                            umma_f16_split(d_tmem, q_lo + k * 2, kDescSw128Hi, d_lo + k * 2, kDescSw128Hi, idesc,
+                                           (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    if (!kQInTmem) umma_commit(empty_q(s));
                     umma_commit(empty_d(c));
                 }
                 if (ok) umma_commit(acc_full(ab));
@@ -170,16 +223,17 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
         __syncwarp();
     } else if (warp >= kFirstExp && warp < kFirstEpi) {
         // ------------------------------------------------------------ expanders (4-bit codes -> f16 operand tile)
-        const int ew = warp - kFirstExp;          // owns the 16-document groups 2 ew, 2 ew + 1 of the tile
+        constexpr int G = C::kGroups;              // 16-document groups per warp
+        const int ew = warp - kFirstExp;          // owns the groups G ew .. G ew + G - 1 of the tile
         const int g = lane & 7, t = lane >> 3;    // document g / g + 8 of the group, code-word column t
         const uint8_t* tiles = a.tiles;
         const size_t group_bytes = (size_t)chunks * 1024;
         const uint32_t lane_off = (uint32_t)(g * 4 + t) * 32;
-        uint32_t cur[2][8], nxt[2][8];
-        auto fetch = [&](long long tile, int c, uint32_t (&dst)[2][8]) {
+        uint32_t cur[G][8], nxt[G][8];
+        auto fetch = [&](long long tile, int c, uint32_t (&dst)[G][8]) {
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const long long grp = tile * (TD / kTqDocsPerTile) + ew * 2 + u;
+            for (int u = 0; u < G; ++u) {
+                const long long grp = tile * (TD / kTqDocsPerTile) + ew * G + u;
                 if (tile < n_tiles && grp < n_tiles16) {
                     ld_global_v8(tiles + (size_t)grp * group_bytes + (size_t)c * 1024 + lane_off, dst[u]);
                 } else {
@@ -188,10 +242,21 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
                 }
             }
         };
+        // the codes of this warp's groups of a later tile are requested into L2 a whole tile ahead (DRAM latency
+        // times the bytes a warp can keep in flight in registers would otherwise cap the stream)
+        auto l2_ahead = [&](long long tile) {
+            const long long grp = tile * (TD / kTqDocsPerTile) + ew * G;
+            if (lane == 0 && tile < n_tiles && grp < n_tiles16) {
+                const long long last = grp + G <= n_tiles16 ? grp + G : n_tiles16;
+                bulk_prefetch_l2(tiles + (size_t)grp * group_bytes, (uint32_t)((last - grp) * group_bytes));
+            }
+        };
         uint32_t it = 0;
         bool ok = true;
+        l2_ahead((long long)blockIdx.x + gridDim.x);
         if ((long long)blockIdx.x < n_tiles) fetch(blockIdx.x, 0, cur);
         for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+            l2_ahead(tile + 2 * (long long)gridDim.x);
             for (int c = 0; ok && c < chunks; ++c) {
                 if (c + 1 < chunks) fetch(tile, c + 1, nxt);
                 else fetch(tile + gridDim.x, 0, nxt);
@@ -204,11 +269,11 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
                     }
                     uint8_t* dst = sm + kOffD + s * kBytesD;
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
+                    for (int u = 0; u < G; ++u) {
 #pragma unroll
                         for (int dh = 0; dh < 2; ++dh) {
                             // tile row of the document; row & 7 == g for both halves
-                            uint8_t* row = dst + ((ew * 2 + u) * 2 + dh) * 1024 + g * 128;
+                            uint8_t* row = dst + ((ew * G + u) * 2 + dh) * 1024 + g * 128;
 #pragma unroll
                             for (int wi = 0; wi < 2; ++wi) {
                                 uint32_t v[4];
@@ -224,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
                     if (lane == 0) mbar_arrive(full_d(s));
                 }
 #pragma unroll
-                for (int u = 0; u < 2; ++u)
+                for (int u = 0; u < G; ++u)
 #pragma unroll
                     for (int i = 0; i < 8; ++i) cur[u][i] = nxt[u][i];
             }
@@ -256,15 +321,15 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
         const float kNoDoc = __int_as_float(0x7fc00000);  // NaN: a missing document never passes a comparison
         auto fetch_norm = [&](long long tile) {
             const long long doc = tile * TD + etid;
-            return (tile < n_tiles && doc < a.n_docs) ? __ldg(a.norms + doc) : kNoDoc;
+            return (etid < TD && tile < n_tiles && doc < a.n_docs) ? __ldg(a.norms + doc) : kNoDoc;
         };
         float norm_next = fetch_norm(blockIdx.x);
         uint32_t t = 0;
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
-            const uint32_t ab = t & 1u;
-            const uint32_t aph = (t >> 1) & 1u;
-            float* nrm = norm_s + ab * TD;
-            nrm[etid] = norm_next;
+            const uint32_t ab = t % C::kAccBufs;
+            const uint32_t aph = (t / C::kAccBufs) & 1u;
+            float* nrm = norm_s + (t & 1u) * TD;
+            if (etid < TD) nrm[etid] = norm_next;
             norm_next = fetch_norm(tile + gridDim.x);
             named_bar_sync(1, kEpiWarps * 32);
             // thresholds other CTAs published; lists that the coming tile could overflow are cut to their k best
@@ -294,7 +359,8 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
             const uint32_t doc0 = a.id_base + (uint32_t)(tile * TD) + (uint32_t)(epart * (TD / 2));
             const float* nrm_w = nrm + epart * (TD / 2);
             float* seed_row = a.seed_scores != nullptr
-                                  ? a.seed_scores + ((size_t)qrow * n_segs + seg) * (TD / 2) : nullptr;
+                                  ? a.seed_scores + (size_t)qrow * a.seed_stride + (size_t)tile * TD + epart * (TD / 2)
+                                  : nullptr;
             auto chunk = [&](const uint32_t (&r)[16], const int c0) {
                 float sc[16];
                 bool any = false;
@@ -322,7 +388,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
                     for (int j = 0; j < 16; ++j) {
                         if (sc[j] >= tau_f) {
                             const u64 key = make_key(sc[j], doc0 + (uint32_t)(c0 + j));
-                            if (key > tau_key) my_list[cnt++] = key;  // cnt <= 128 before the tile, <= 256 after
+                            if (key > tau_key) my_list[cnt++] = key;  // cnt <= 128 before the tile, <= 128 + TD / 2 after
                         }
                     }
                 }
@@ -363,7 +429,12 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
 }  // namespace
 
 cudaError_t tq_tc_init() {
-    return cudaFuncSetAttribute(tq_score_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(tq_score_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<false>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(tq_score_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<true>::kSmemBytes);
+    return e;
 }
 
 std::string tq_tc_make_query_map(CUtensorMap* tm, const __half* qperm, int padded_dim, int rows) {
@@ -371,8 +442,14 @@ std::string tq_tc_make_query_map(CUtensorMap* tm, const __half* qperm, int padde
                      (uint64_t)padded_dim * 2, TK, TQ, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-void launch_tq_score_tc(const CUtensorMap& tm_q, const TqTcArgs& a, int grid, cudaStream_t stream) {
-    tq_score_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tm_q, a);
+bool tq_tc_queries_fit_tmem(int dim) {
+    const int padded = (dim + kTqChunkCoords - 1) / kTqChunkCoords * kTqChunkCoords;
+    return kQTmemCol + padded / 2 <= kTmemCols;
+}
+
+void launch_tq_score_tc(const CUtensorMap& tm_q, const TqTcArgs& a, bool q_in_tmem, int grid, cudaStream_t stream) {
+    if (q_in_tmem) tq_score_tc_kernel<true><<<grid, kThreads, Cfg<true>::kSmemBytes, stream>>>(tm_q, a);
+    else tq_score_tc_kernel<false><<<grid, kThreads, Cfg<false>::kSmemBytes, stream>>>(tm_q, a);
 }
 
 }  // namespace eosb

@@ -249,3 +249,62 @@ def test_argument_validation(rt):
     with pytest.raises(eos_b200.EosB200Error):
         eos_b200.Quantizer(rt, asym)
     qz.close()
+
+
+def test_batch_kernel_ascending_scores(rt):
+    """Worst case for the candidate lists of the batch kernel: every vector is the same code row with a norm that
+    grows with its index, so every document beats the running threshold and every list is cut before every tile.
+    The result must still be the exact top-k (the last k rows for queries with a positive score)."""
+    import eos_b200
+    spec, qz, codes, norms, q = _setup(rt, 96, 4, 64, 5)
+    n = 60000
+    codes = np.tile(codes[:1], (n, 1))
+    norms = np.linspace(0.5, 2.0, n, dtype=np.float32)
+    corpus = eos_b200.Corpus(qz, codes, norms)
+    ref = _oracle_scores(spec, codes[:1], np.ones(1, np.float32), q)[:, 0:1] * norms[None, :]
+    ids8, sc8 = corpus.score_topk(q, 100, queries_per_pass=8)
+    ids, sc = corpus.score_topk(q, 100, queries_per_pass=128)
+    tol = 1e-3 * float(np.abs(ref).max())
+    for i in range(q.shape[0]):
+        _check_topk(ids[i], sc[i], ref[i], 100, 0, tol)
+        assert np.array_equal(ids[i], ids8[i])
+    corpus.close()
+    qz.close()
+
+
+_TMEM_SCRIPT = r"""
+import numpy as np, sys
+sys.path.insert(0, "tests")
+import eos_b200
+import test_gpu_turboquant as T
+rt = eos_b200.Runtime(0)
+bad = 0
+for dim, bits, n, nq, k in ((768, 4, 5000, 11, 100), (768, 4, 2051, 140, 100), (128, 2, 3000, 16, 10), (96, 4, 50, 3, 100),
+                            (96, 4, 140000, 9, 100), (96, 4, 310000, 9, 100)):
+    spec, qz, codes, norms, q = T._setup(rt, dim, bits, n, nq)
+    corpus = eos_b200.Corpus(qz, codes, norms, id_base=1000)
+    ref = T._oracle_scores(spec, codes, norms, q)
+    tol = 1e-3 * float(np.abs(ref).max())
+    ids, scores = corpus.score_topk(q, k, queries_per_pass=128)
+    for i in range(nq):
+        T._check_topk(ids[i], scores[i], ref[i], k, 1000, tol)
+    corpus.close()
+    qz.close()
+print("TMEM_RESULT ok")
+rt.close()
+"""
+
+
+def test_batch_kernel_with_queries_in_tensor_memory():
+    """The opt-in variant of the batch kernel (EOS_B200_TQ_QUERIES_IN_TMEM=1: queries written once to tensor memory,
+    tcgen05.mma with A from tensor memory, 128-document tiles) against the oracle.  Child process: the switch is read
+    when a corpus first allocates its batch workspace."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, EOS_B200_TQ_QUERIES_IN_TMEM="1", PYTHONPATH=root)
+    out = subprocess.run([sys.executable, "-c", _TMEM_SCRIPT], env=env, cwd=root, capture_output=True, text=True,
+                         timeout=900)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "TMEM_RESULT ok" in out.stdout
