@@ -35,8 +35,7 @@
 // shared memory.  Tensor memory then has room for one 128-column accumulator: a tile is 128 documents, its epilogue
 // does not overlap the next tile's MMAs and every document costs twice the ring hand-offs; measured 0.42 ms per
 // launch over 1.25 M rows against 0.26 ms, which shows that the expanders and the hand-offs, not the shared-memory
-// bandwidth, set the pace.  The expanders ask the L2 for their codes a tile ahead (no measurable effect: the stream
-// is not latency-bound either).
+// bandwidth, set the pace.
 // Every mbarrier wait is bounded (common.cuh: mbar_wait): on a timeout all roles leave their loops,
 // tensor memory is freed and the status word is set.
 #include "common.cuh"
@@ -52,11 +51,8 @@ constexpr int TQ = kTqTcQueries;    // queries per launch (MMA M)
 constexpr int TK = 64;              // coordinates per k-block
 constexpr int kStQ = 4;             // query ring (shared-memory variant)
 constexpr uint32_t kBytesQ = TQ * TK * 2;
-constexpr int kExpWarps = 8;
 constexpr int kEpiWarps = 8;
 constexpr int kFirstExp = 4;
-constexpr int kFirstEpi = kFirstExp + kExpWarps;
-constexpr int kThreads = (kFirstEpi + kEpiWarps) * 32;
 constexpr int kTmemCols = 512;
 constexpr int kCutAbove = 128;      // a list longer than this is cut before the next tile (which adds <= 128)
 constexpr int kQTmemCol = 128;      // first tensor-memory column of the resident queries (after the accumulator)
@@ -67,6 +63,9 @@ struct Cfg {
     static constexpr int kAccBufs = kQInTmem ? 1 : 2;
     static constexpr int kStD = kQInTmem ? 8 : 4;                  // expanded-document ring
     static constexpr uint32_t kBytesD = TD * TK * 2;
+    static constexpr int kExpWarps = 8;
+    static constexpr int kFirstEpi = kFirstExp + kExpWarps;
+    static constexpr int kThreads = (kFirstEpi + kEpiWarps) * 32;
     static constexpr int kGroups = TD / kTqDocsPerTile / kExpWarps;  // 16-document groups per expander warp
     static constexpr uint32_t kOffQ = 0;
     static constexpr uint32_t kOffD = kOffQ + (kQInTmem ? 0 : kStQ * kBytesQ);
@@ -83,10 +82,11 @@ static_assert(kTqTcSegLen == kSortCap, "a list is sorted in one piece");
 static_assert(kTqMaxK <= kCutAbove, "a cut keeps k <= 128 keys");
 
 template <bool kQInTmem>
-__global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_constant__ CUtensorMap tm_q, TqTcArgs a) {
+__global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel(const __grid_constant__ CUtensorMap tm_q, TqTcArgs a) {
     using C = Cfg<kQInTmem>;
     constexpr int TD = C::TD;
     constexpr int kStD = C::kStD;
+    constexpr int kExpWarps = C::kExpWarps, kFirstEpi = C::kFirstEpi;
     constexpr uint32_t kBytesD = C::kBytesD;
     constexpr uint32_t kOffQ = C::kOffQ, kOffD = C::kOffD, kOffNorm = C::kOffNorm, kOffSort = C::kOffSort;
     constexpr uint32_t kOffBars = C::kOffBars, kOffMisc = C::kOffMisc;
@@ -242,21 +242,10 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc_kernel(const __grid_c
                 }
             }
         };
-        // the codes of this warp's groups of a later tile are requested into L2 a whole tile ahead (DRAM latency
-        // times the bytes a warp can keep in flight in registers would otherwise cap the stream)
-        auto l2_ahead = [&](long long tile) {
-            const long long grp = tile * (TD / kTqDocsPerTile) + ew * G;
-            if (lane == 0 && tile < n_tiles && grp < n_tiles16) {
-                const long long last = grp + G <= n_tiles16 ? grp + G : n_tiles16;
-                bulk_prefetch_l2(tiles + (size_t)grp * group_bytes, (uint32_t)((last - grp) * group_bytes));
-            }
-        };
         uint32_t it = 0;
         bool ok = true;
-        l2_ahead((long long)blockIdx.x + gridDim.x);
         if ((long long)blockIdx.x < n_tiles) fetch(blockIdx.x, 0, cur);
         for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            l2_ahead(tile + 2 * (long long)gridDim.x);
             for (int c = 0; ok && c < chunks; ++c) {
                 if (c + 1 < chunks) fetch(tile, c + 1, nxt);
                 else fetch(tile + gridDim.x, 0, nxt);
@@ -448,8 +437,8 @@ bool tq_tc_queries_fit_tmem(int dim) {
 }
 
 void launch_tq_score_tc(const CUtensorMap& tm_q, const TqTcArgs& a, bool q_in_tmem, int grid, cudaStream_t stream) {
-    if (q_in_tmem) tq_score_tc_kernel<true><<<grid, kThreads, Cfg<true>::kSmemBytes, stream>>>(tm_q, a);
-    else tq_score_tc_kernel<false><<<grid, kThreads, Cfg<false>::kSmemBytes, stream>>>(tm_q, a);
+    if (q_in_tmem) tq_score_tc_kernel<true><<<grid, Cfg<true>::kThreads, Cfg<true>::kSmemBytes, stream>>>(tm_q, a);
+    else tq_score_tc_kernel<false><<<grid, Cfg<false>::kThreads, Cfg<false>::kSmemBytes, stream>>>(tm_q, a);
 }
 
 }  // namespace eosb
