@@ -151,6 +151,36 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // LayerNorm of one row held as kChunks x 8 values per lane; two-pass (mean, then centred
 // variance) in fp32 like the reference's double-precision two-pass form.
 template <int kChunks>
+__device__ __forceinline__ void row_mean_inv(const float (&v)[kChunks][8], int dim, int lane, float eps, float* mean_out,
+                                             float* inv_out) {
+    float sum = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < dim) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum += v[c][i];
+        }
+    }
+    const float mean = warp_sum(sum) / (float)dim;
+    float var = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < dim) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float d = v[c][i] - mean;
+                var += d * d;
+            }
+        }
+    }
+    var = warp_sum(var) / (float)dim;
+    *mean_out = mean;
+    *inv_out = 1.0f / sqrtf(var + eps);
+}
+
+template <int kChunks>
 __device__ __forceinline__ void row_layernorm_store(float (&v)[kChunks][8], int dim, int lane, const float* gamma,
                                                     const float* beta, float eps, __half* out_row) {
     float sum = 0.f;
@@ -261,6 +291,21 @@ layernorm_kernel(const __half* __restrict__ in, const float* __restrict__ gamma,
     };
     int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (r < rows) fetch(r, raw);
+    // up to 768 columns the lane's scale and shift stay in registers for all its rows (read per row they are four
+    // times the bytes of the row itself through L1)
+    constexpr bool kAffineInRegs = kChunks <= 3;
+    float greg[kAffineInRegs ? kChunks : 1][8], breg[kAffineInRegs ? kChunks : 1][8];
+    if (kAffineInRegs) {
+#pragma unroll
+        for (int c = 0; c < (kAffineInRegs ? kChunks : 1); ++c) {
+            const int col = (c * 32 + lane) * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                greg[c][i] = col < dim ? gamma[col + i] : 0.f;
+                breg[c][i] = col < dim ? beta[col + i] : 0.f;
+            }
+        }
+    }
     while (r < rows) {
         const int rn = r + warps_per_grid;
         uint4 nxt[kChunks];
@@ -268,6 +313,20 @@ layernorm_kernel(const __half* __restrict__ in, const float* __restrict__ gamma,
         float v[kChunks][8];
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) unpack8(raw[c], v[c]);
+        if constexpr (kAffineInRegs) {
+            float mean, inv;
+            row_mean_inv<kChunks>(v, dim, lane, eps, &mean, &inv);
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+                const int col = (c * 32 + lane) * 8;
+                if (col < dim) {
+                    float o[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[i] = (v[c][i] - mean) * inv * greg[c][i] + breg[c][i];
+                    *reinterpret_cast<uint4*>(out + (size_t)r * dim + col) = pack8(o);
+                }
+            }
+        } else
         row_layernorm_store<kChunks>(v, dim, lane, gamma, beta, eps, out + (size_t)r * dim);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) raw[c] = nxt[c];
@@ -949,7 +1008,8 @@ void launch_layernorm(const __half* in, const float* gamma, const float* beta, f
                       const int* total_rows, __half* out, int sm_count, cudaStream_t stream) {
     dispatch_chunks(dim, [&](auto c) {
         constexpr int kChunks = decltype(c)::value;
-        layernorm_kernel<kChunks><<<sm_count * 8, 256, 0, stream>>>(in, gamma, beta, eps, dim, m_alloc,
+        // with the scale and shift in registers (109 registers, two CTAs per SM) every warp keeps its rows to the end
+        layernorm_kernel<kChunks><<<sm_count * (kChunks <= 3 ? 2 : 8), 256, 0, stream>>>(in, gamma, beta, eps, dim, m_alloc,
                                                                                  total_rows, out);
     });
 }
