@@ -470,12 +470,12 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
         bytes_per_vec = spec.vector_bytes
         scan_avg_ms = scan_ms / max(1, scan_launches)
         achieved = (n_local * bytes_per_vec) / (scan_avg_ms / 1e3) / 1e9 if scan_avg_ms > 0 else None
-        if per_pass == 128:
-            # the batch kernel is a contraction on the tensor cores: 2 x 128 queries x rows x padded dim flops per launch
+        if per_pass >= 128:
+            # the batch kernels are contractions on the tensor cores: 2 x queries x rows x padded dim flops per launch
             dimp = (dim + 127) // 128 * 128
-            flops = 2.0 * 128 * n_local * dimp
+            flops = 2.0 * per_pass * n_local * dimp
             tf = flops / (scan_avg_ms / 1e3) / 1e12 if scan_avg_ms > 0 else None
-            roofline = {"bound": "tensor", "kernel": "tq_score_tc_kernel", "achieved": tf, "peak": peaks["tflops"],
+            roofline = {"bound": "tensor", "kernel": "tq_score_tc_kernel" if per_pass == 128 else "tq_score_tc256_kernel", "achieved": tf, "peak": peaks["tflops"],
                         "unit": "TFLOP/s", "frac": tf / peaks["tflops"] if tf else None,
                         "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained)",
                         "traffic": n_local * NCU_TC_DRAM_BYTES_PER_ROW if NCU_TC_DRAM_BYTES_PER_ROW else None,
@@ -548,7 +548,7 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true", help="omit the timed CPU baseline")
     ap.add_argument("--skip-turboquant", action="store_true", help="encoder only")
     ap.add_argument("--tq-corpus", type=int, default=TQ["corpus"])
-    ap.add_argument("--tq-queries-per-pass", type=int, default=128, choices=[8, 16, 32, 128],
+    ap.add_argument("--tq-queries-per-pass", type=int, default=256, choices=[8, 16, 32, 128, 256],
                     help="128 = tensor-core batch kernel; 8 = streaming scan; 16 / 32 = the earlier register-blocked scan")
     ap.add_argument("--tq-skip-stream", action="store_true", help="do not also time the 8-queries-per-pass scan")
     ap.add_argument("--weight-mode", default="f16_resident", choices=["f16_resident", "q8_smem"],

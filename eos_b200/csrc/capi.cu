@@ -140,6 +140,7 @@ int eos_b200_runtime_create(int device, EosB200Runtime** out, char** err) {
         cudaError_t se = tq_scan_init();
         if (se != cudaSuccess) ge = std::string("tq_scan_init: ") + cudaGetErrorString(se);
         if (se == cudaSuccess && (se = tq_tc_init()) != cudaSuccess) ge = std::string("tq_tc_init: ") + cudaGetErrorString(se);
+        if (se == cudaSuccess && (se = tq_tc256_init()) != cudaSuccess) ge = std::string("tq_tc256_init: ") + cudaGetErrorString(se);
         if (se == cudaSuccess && (se = tq_merge_init()) != cudaSuccess) ge = std::string("tq_merge_init: ") + cudaGetErrorString(se);
     }
     if (!ge.empty()) {
@@ -1134,16 +1135,22 @@ struct EosB200Corpus {
     int64_t* d_ids = nullptr;
     float* d_scores = nullptr;
     int grid = 0;
-    // tensor-core batch path (128 queries per launch), allocated on first use
-    int tc_grid = 0;
-    int tc_tile_docs = 0;           // 128 with the queries resident in tensor memory (tc_q_in_tmem), else 256
-    bool tc_q_in_tmem = false;
-    int tc_cap_queries = 0;
-    __half* qperm = nullptr;        // [tc_cap_queries][padded dim] rotated queries, coordinates in code-word order
-    uint64_t* tc_cand = nullptr;    // [128][2 * tc_grid][kTqTcSegLen]
-    int* tc_count = nullptr;        // [128][2 * tc_grid]
-    float* tc_seed_scores = nullptr;  // [128][2 * tc_grid][128] scores of the sample that seeds the thresholds
-    CUtensorMap tm_q;
+    // tensor-core batch paths, allocated on first use: plan 0 = 128 queries per launch (queries are the MMA rows),
+    // plan 1 = 256 queries per launch (128-document tiles are the MMA rows)
+    struct TcPlan {
+        int queries = 0;          // queries per launch
+        int tile_docs = 0;        // documents per tile
+        int segs_per_cta = 0;     // candidate lists a CTA keeps per query
+        int grid = 0;
+        bool q_in_tmem = false;   // plan 0 only: opt-in variant with the queries resident in tensor memory
+        int map_queries = 0;      // query rows the tensor map covers (0 = not built)
+        uint64_t* cand = nullptr;     // [queries][segs_per_cta * grid][kTqTcSegLen]
+        int* count = nullptr;         // [queries][segs_per_cta * grid]
+        float* seed_scores = nullptr; // [queries][grid * 256] scores of the sample that seeds the thresholds
+        CUtensorMap tm;
+    } tcp[2];
+    int qperm_queries = 0;
+    __half* qperm = nullptr;        // [qperm_queries][padded dim] rotated queries, coordinates in code-word order
     Profiler prof;
 };
 
@@ -1218,7 +1225,7 @@ int corpus_finish_bind(EosB200Quantizer* qz, const uint8_t* d_codes, const float
 }
 
 int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
-    const int q_pad = (q_count + kTqTcQueries - 1) / kTqTcQueries * kTqTcQueries;
+    const int q_pad = (q_count + kTqTc256Queries - 1) / kTqTc256Queries * kTqTc256Queries;
     if (q_pad <= c->cap_queries) return EOS_B200_OK;
     dev_free(c->d_queries);
     dev_free(c->bfrag);
@@ -1229,7 +1236,7 @@ int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
     dev_free(c->d_ids);
     dev_free(c->d_scores);
     dev_free(c->qperm);
-    c->tc_cap_queries = 0;
+    c->qperm_queries = 0;
     c->cap_queries = 0;
     const int ksteps = tq_ksteps(c->qz->dim);
     CUDA_TRY(dev_alloc(&c->d_queries, (size_t)q_pad * c->qz->dim));
@@ -1244,29 +1251,39 @@ int ensure_score_workspace(EosB200Corpus* c, int q_count, char** err) {
     return EOS_B200_OK;
 }
 
-// Buffers of the tensor-core batch path; the query capacity follows ensure_score_workspace.
-int ensure_tc_workspace(EosB200Corpus* c, char** err) {
-    if (c->tc_cap_queries == c->cap_queries && c->qperm != nullptr) return EOS_B200_OK;
+// Buffers of a tensor-core batch plan; the query capacity follows ensure_score_workspace.
+int ensure_tc_workspace(EosB200Corpus* c, int plan, char** err) {
+    EosB200Corpus::TcPlan& p = c->tcp[plan];
     const int dimp = tq_ksteps(c->qz->dim) * 16;
-    // The variant with the queries resident in tensor memory is correct but measured slower (0.42 ms against 0.26 ms per
-    // launch over 1.25 M rows: its 128-document tiles double the hand-offs per document and its single accumulator
-    // serialises epilogue and MMA), so it is opt-in.
-    const char* in_tmem = getenv("EOS_B200_TQ_QUERIES_IN_TMEM");
-    c->tc_q_in_tmem = tq_tc_queries_fit_tmem(c->qz->dim) && in_tmem != nullptr && in_tmem[0] != '\0' && in_tmem[0] != '0';
-    c->tc_tile_docs = c->tc_q_in_tmem ? kTqTcDocsQ : kTqTcDocs;
-    const int64_t tiles = (c->n + c->tc_tile_docs - 1) / c->tc_tile_docs;
-    c->tc_grid = (int)(tiles < c->qz->rt->sm_count ? (tiles > 0 ? tiles : 1) : c->qz->rt->sm_count);
-    dev_free(c->qperm);
-    c->tc_cap_queries = 0;
-    CUDA_TRY(dev_alloc(&c->qperm, (size_t)c->cap_queries * dimp));
-    if (c->tc_cand == nullptr) {
-        CUDA_TRY(dev_alloc(&c->tc_cand, (size_t)kTqTcQueries * 2 * c->tc_grid * kTqTcSegLen));
-        CUDA_TRY(dev_alloc(&c->tc_count, (size_t)kTqTcQueries * 2 * c->tc_grid));
-        CUDA_TRY(dev_alloc(&c->tc_seed_scores, (size_t)kTqTcQueries * c->tc_grid * kTqTcDocs));
+    if (c->qperm_queries != c->cap_queries || c->qperm == nullptr) {
+        dev_free(c->qperm);
+        c->qperm_queries = 0;
+        CUDA_TRY(dev_alloc(&c->qperm, (size_t)c->cap_queries * dimp));
+        c->qperm_queries = c->cap_queries;
+        c->tcp[0].map_queries = c->tcp[1].map_queries = 0;
     }
-    const std::string m = tq_tc_make_query_map(&c->tm_q, c->qperm, dimp, c->cap_queries);
-    if (!m.empty()) return fail(err, "score_topk: " + m);
-    c->tc_cap_queries = c->cap_queries;
+    if (p.grid == 0) {
+        p.queries = plan == 1 ? kTqTc256Queries : kTqTcQueries;
+        // The variant of plan 0 with the queries resident in tensor memory is correct but measured slower (0.42 ms against
+        // 0.26 ms per launch over 1.25 M rows), so it is opt-in.
+        const char* in_tmem = getenv("EOS_B200_TQ_QUERIES_IN_TMEM");
+        p.q_in_tmem = plan == 0 && tq_tc_queries_fit_tmem(c->qz->dim) && in_tmem != nullptr && in_tmem[0] != '\0' &&
+                      in_tmem[0] != '0';
+        p.tile_docs = plan == 1 ? kTqTc256Docs : (p.q_in_tmem ? kTqTcDocsQ : kTqTcDocs);
+        p.segs_per_cta = plan == 1 ? 1 : 2;
+        const int64_t tiles = (c->n + p.tile_docs - 1) / p.tile_docs;
+        const int grid = (int)(tiles < c->qz->rt->sm_count ? (tiles > 0 ? tiles : 1) : c->qz->rt->sm_count);
+        CUDA_TRY(dev_alloc(&p.cand, (size_t)p.queries * p.segs_per_cta * grid * kTqTcSegLen));
+        CUDA_TRY(dev_alloc(&p.count, (size_t)p.queries * p.segs_per_cta * grid));
+        CUDA_TRY(dev_alloc(&p.seed_scores, (size_t)p.queries * grid * 256));
+        p.grid = grid;
+    }
+    if (p.map_queries != c->cap_queries) {
+        const std::string m = plan == 1 ? tq_tc256_make_query_map(&p.tm, c->qperm, dimp, c->cap_queries)
+                                        : tq_tc_make_query_map(&p.tm, c->qperm, dimp, c->cap_queries);
+        if (!m.empty()) return fail(err, "score_topk: " + m);
+        p.map_queries = c->cap_queries;
+    }
     return EOS_B200_OK;
 }
 
@@ -1324,17 +1341,18 @@ int enqueue_scan_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, in
     return launches;
 }
 
-// Tensor-core launches of kTqTcQueries queries over the first n_docs rows.  seed = true: the lists of each launch
-// become the pruning thresholds of its queries (shared_tau); otherwise they are merged into the top-k outputs.
-int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool seed, bool profile, int64_t* d_ids,
-                      float* d_scores, uint64_t* d_keys, cudaStream_t s) {
+// Tensor-core launches of one plan over the first n_docs rows.  seed = true: the scores of each launch become the
+// pruning thresholds of its queries (shared_tau); otherwise the lists are merged into the top-k outputs.
+int enqueue_tc_passes(EosB200Corpus* c, int plan, int64_t n_docs, int q_count, int k, bool seed, bool profile,
+                      int64_t* d_ids, float* d_scores, uint64_t* d_keys, cudaStream_t s) {
     EosB200Quantizer* qz = c->qz;
-    const int64_t tiles = (n_docs + c->tc_tile_docs - 1) / c->tc_tile_docs;
-    const int grid = (int)(tiles < c->tc_grid ? tiles : c->tc_grid);
-    const int n_segs = 2 * grid;
+    EosB200Corpus::TcPlan& p = c->tcp[plan];
+    const int64_t tiles = (n_docs + p.tile_docs - 1) / p.tile_docs;
+    const int grid = (int)(tiles < p.grid ? tiles : p.grid);
+    const int n_segs = p.segs_per_cta * grid;
     int launches = 0;
-    for (int q0 = 0; q0 < q_count; q0 += kTqTcQueries) {
-        const int q_here = (q_count - q0) < kTqTcQueries ? (q_count - q0) : kTqTcQueries;
+    for (int q0 = 0; q0 < q_count; q0 += p.queries) {
+        const int q_here = (q_count - q0) < p.queries ? (q_count - q0) : p.queries;
         TqTcArgs a{};
         a.tiles = c->tiles;
         a.norms = c->norms;
@@ -1348,20 +1366,24 @@ int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool
         a.mag_hi[1] = qz->mag_hi[1];
         a.mag_lo[0] = qz->mag_lo[0];
         a.mag_lo[1] = qz->mag_lo[1];
-        a.cand_keys = c->tc_cand;
-        a.cand_count = c->tc_count;
+        a.cand_keys = p.cand;
+        a.cand_count = p.count;
         a.shared_tau = c->shared_tau + q0;
-        a.seed_scores = seed ? c->tc_seed_scores : nullptr;
-        a.seed_stride = n_docs;  // seed mode: n_docs = tc_grid * 256 scores per query, a multiple of the tile
+        a.seed_scores = seed ? p.seed_scores : nullptr;
+        a.seed_stride = n_docs;  // seed mode: n_docs = grid * 256 scores per query, a multiple of the tile
         a.qperm = c->qperm;
         a.status = qz->rt->d_status;
-        if (profile) c->prof.launch(kClsScan, s, [&] { launch_tq_score_tc(c->tm_q, a, c->tc_q_in_tmem, grid, s); });
-        else launch_tq_score_tc(c->tm_q, a, c->tc_q_in_tmem, grid, s);
+        auto launch = [&] {
+            if (plan == 1) launch_tq_score_tc256(p.tm, a, grid, s);
+            else launch_tq_score_tc(p.tm, a, p.q_in_tmem, grid, s);
+        };
+        if (profile) c->prof.launch(kClsScan, s, launch);
+        else launch();
         if (seed)
-            launch_tq_seed_tau_scores(c->tc_seed_scores, n_docs, (int)n_docs, q_here, k, c->shared_tau + q0, s);
+            launch_tq_seed_tau_scores(p.seed_scores, n_docs, (int)n_docs, q_here, k, c->shared_tau + q0, s);
         else
-            launch_tq_merge_lists(c->tc_cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, c->tc_count,
-                                  q_here, k, d_ids != nullptr ? d_ids + (size_t)q0 * k : nullptr,
+            launch_tq_merge_lists(p.cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, p.count, q_here, k,
+                                  d_ids != nullptr ? d_ids + (size_t)q0 * k : nullptr,
                                   d_scores != nullptr ? d_scores + (size_t)q0 * k : nullptr,
                                   d_keys != nullptr ? d_keys + (size_t)q0 * k : nullptr, s);
         launches += 2;
@@ -1369,27 +1391,28 @@ int enqueue_tc_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, bool
     return launches;
 }
 
-// The batch path.  Thresholds are seeded from the first tc_grid * 256 rows (one tile per CTA, every score written out,
-// k-th best per query); on a large shard a second sample of 1/32 of the rows, scored with those thresholds and merged
-// like the real pass, tightens them further, so that the lists of the full pass stay short (no list is cut, and the
-// merge gathers a few thousand keys per query).  Then the whole shard.
-int enqueue_score_tc(EosB200Corpus* c, const float* d_queries, int q_count, int k, int64_t* d_ids, float* d_scores,
-                     uint64_t* d_keys, cudaStream_t s) {
-    const int q_pad = (q_count + kTqTcQueries - 1) / kTqTcQueries * kTqTcQueries;
+// The batch paths.  Thresholds are seeded from the first grid * 256 rows (every score written out, k-th best per
+// query); on a large shard a second sample of 1/32 of the rows, scored with those thresholds and merged like the real
+// pass, tightens them further, so that the lists of the full pass stay short (no list is cut, and the merge gathers a
+// few thousand keys per query).  Then the whole shard.
+int enqueue_score_tc(EosB200Corpus* c, int plan, const float* d_queries, int q_count, int k, int64_t* d_ids,
+                     float* d_scores, uint64_t* d_keys, cudaStream_t s) {
+    const EosB200Corpus::TcPlan& p = c->tcp[plan];
+    const int q_pad = (q_count + p.queries - 1) / p.queries * p.queries;
     int launches = 1;
     launch_tq_prepare(d_queries, q_count, q_pad, c->qz->spec(), nullptr, nullptr, c->qperm, s);
     cudaMemsetAsync(c->shared_tau, 0, (size_t)q_pad * sizeof(unsigned long long), s);
-    const int64_t seed_docs = (int64_t)c->tc_grid * kTqTcDocs;
+    const int64_t seed_docs = (int64_t)p.grid * 256;
     if (c->n >= 8 * seed_docs && k <= seed_docs) {
-        launches += enqueue_tc_passes(c, seed_docs, q_count, k, true, false, nullptr, nullptr, nullptr, s);
+        launches += enqueue_tc_passes(c, plan, seed_docs, q_count, k, true, false, nullptr, nullptr, nullptr, s);
         if (c->n >= 64 * seed_docs) {
-            const int64_t second = c->n / 32 / kTqTcDocs * kTqTcDocs;
-            launches += enqueue_tc_passes(c, second, q_count, k, false, false, nullptr, nullptr, c->seed_keys, s);
+            const int64_t second = c->n / 32 / 256 * 256;
+            launches += enqueue_tc_passes(c, plan, second, q_count, k, false, false, nullptr, nullptr, c->seed_keys, s);
             seed_tau_kernel<<<(q_count + 255) / 256, 256, 0, s>>>(c->seed_keys, q_count, k, c->shared_tau);
             launches++;
         }
     }
-    launches += enqueue_tc_passes(c, c->n, q_count, k, false, true, d_ids, d_scores, d_keys, s);
+    launches += enqueue_tc_passes(c, plan, c->n, q_count, k, false, true, d_ids, d_scores, d_keys, s);
     return launches;
 }
 
@@ -1397,7 +1420,8 @@ int enqueue_score_tc(EosB200Corpus* c, const float* d_queries, int q_count, int 
 int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, int per_pass, int64_t* d_ids,
                   float* d_scores, uint64_t* d_keys, cudaStream_t s) {
     EosB200Quantizer* qz = c->qz;
-    if (per_pass == kTqTcQueries) return enqueue_score_tc(c, d_queries, q_count, k, d_ids, d_scores, d_keys, s);
+    if (per_pass == kTqTcQueries || per_pass == kTqTc256Queries)
+        return enqueue_score_tc(c, per_pass == kTqTc256Queries ? 1 : 0, d_queries, q_count, k, d_ids, d_scores, d_keys, s);
     int launches = 0;
     launch_tq_prepare(d_queries, q_count, (q_count + 31) / 32 * 32, qz->spec(), c->bfrag, nullptr, nullptr, s);
     launches++;
@@ -1421,8 +1445,8 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
 std::string check_score_args(const EosB200Corpus* c, int q_count, int k, int per_pass) {
     if (q_count <= 0) return "score_topk: no queries";
     if (k <= 0 || k > kTqMaxK) return "score_topk: k must be in [1, 128]";
-    if (per_pass != 8 && per_pass != 16 && per_pass != 32 && per_pass != kTqTcQueries)
-        return "score_topk: queries_per_pass must be 8, 16, 32 or 128";
+    if (per_pass != 8 && per_pass != 16 && per_pass != 32 && per_pass != kTqTcQueries && per_pass != kTqTc256Queries)
+        return "score_topk: queries_per_pass must be 8, 16, 32, 128 or 256";
     if (c->n + c->id_base > 0xffffffffLL || c->id_base < 0) return "score_topk: document ids must fit 32 bits";
     return "";
 }
@@ -1559,9 +1583,11 @@ void eos_b200_corpus_destroy(EosB200Corpus* c) {
     dev_free(c->d_ids);
     dev_free(c->d_scores);
     dev_free(c->qperm);
-    dev_free(c->tc_cand);
-    dev_free(c->tc_count);
-    dev_free(c->tc_seed_scores);
+    for (auto& p : c->tcp) {
+        dev_free(p.cand);
+        dev_free(p.count);
+        dev_free(p.seed_scores);
+    }
     c->prof.reset();
     delete c;
 }
@@ -1645,7 +1671,8 @@ int eos_b200_score_topk_device(EosB200Corpus* c, const float* d_queries, int q_c
     if (c->n == 0) return fail(err, "score_topk: empty corpus");
     CUDA_TRY(cudaSetDevice(c->qz->rt->device));
     int rc = ensure_score_workspace(c, q_count, err);
-    if (rc == EOS_B200_OK && per_pass == kTqTcQueries) rc = ensure_tc_workspace(c, err);
+    if (rc == EOS_B200_OK && (per_pass == kTqTcQueries || per_pass == kTqTc256Queries))
+        rc = ensure_tc_workspace(c, per_pass == kTqTc256Queries ? 1 : 0, err);
     if (rc != EOS_B200_OK) return rc;
     const int launches =
         enqueue_score(c, d_queries, q_count, k, per_pass, d_ids, d_scores, d_keys, pick_stream(c->qz->rt, stream));
@@ -1674,7 +1701,8 @@ int eos_b200_score_topk(EosB200Corpus* c, const float* h_queries, int q_count, i
     EosB200Runtime* rt = c->qz->rt;
     CUDA_TRY(cudaSetDevice(rt->device));
     int rc = ensure_score_workspace(c, q_count, err);
-    if (rc == EOS_B200_OK && per_pass == kTqTcQueries) rc = ensure_tc_workspace(c, err);
+    if (rc == EOS_B200_OK && (per_pass == kTqTcQueries || per_pass == kTqTc256Queries))
+        rc = ensure_tc_workspace(c, per_pass == kTqTc256Queries ? 1 : 0, err);
     if (rc != EOS_B200_OK) return rc;
     cudaStream_t s = rt->stream;
     CUDA_TRY(cudaEventRecord(rt->ev0, s));
@@ -1728,6 +1756,7 @@ int eos_b200_score_topk_noalloc(EosB200Corpus* c, const float* d_queries, int q_
         return fail(err, "score_topk_noalloc: null argument");
     std::string m = check_score_args(c, q_count, k, per_pass);
     if (!m.empty()) return fail(err, m);
+    if (per_pass > 32) return fail(err, "score_topk_noalloc: queries_per_pass must be 8, 16 or 32");
     if (c->n == 0) return fail(err, "score_topk_noalloc: empty corpus");
     EosB200Quantizer* qz = c->qz;
     const int ksteps = tq_ksteps(qz->dim);

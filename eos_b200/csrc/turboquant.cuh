@@ -116,6 +116,15 @@ bool tq_tc_queries_fit_tmem(int dim);
 // of kTqTcDocs documents with the queries staged through shared memory by TMA (tm_q).
 void launch_tq_score_tc(const CUtensorMap& tm_q, const TqTcArgs& a, bool q_in_tmem, int grid, cudaStream_t stream);
 
+// The same batch scoring with the operand roles swapped (turboquant_tc256.cu): one launch = kTqTc256Queries queries,
+// tiles of kTqTc256Docs documents as the MMA's M rows; one candidate list per CTA and query
+// (cand_keys [256][grid][kTqTcSegLen], cand_count [256][grid], shared_tau [256]); seed mode as above.
+constexpr int kTqTc256Queries = 256;
+constexpr int kTqTc256Docs = 128;
+cudaError_t tq_tc256_init();
+std::string tq_tc256_make_query_map(CUtensorMap* tm, const __half* qperm, int padded_dim, int rows);
+void launch_tq_score_tc256(const CUtensorMap& tm_q, const TqTcArgs& a, int grid, cudaStream_t stream);
+
 // For every query: the k best of n_segs x seg_len candidate keys (key 0 = empty), sorted by
 // score descending then id ascending.  cand is [queries][n_segs][seg_len] with the given
 // strides (in keys).  counts, when non-null, is [queries][n_segs] entries in use.

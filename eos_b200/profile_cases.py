@@ -68,7 +68,7 @@ def case_scan(n: int = 2_000_000) -> None:
     rt.close()
 
 
-def case_score_tc(n: int = 1_250_000, nq: int = 512) -> None:
+def case_score_tc(n: int = 1_250_000, nq: int = 512, per_pass: int = 128) -> None:
     import torch
 
     import eos_b200
@@ -95,17 +95,17 @@ def case_score_tc(n: int = 1_250_000, nq: int = 512) -> None:
     ts = torch.cuda.Stream()
     stream = ts.cuda_stream
     for _ in range(2):
-        corpus.score_topk_device(queries.data_ptr(), nq, 100, 128, ids.data_ptr(), scores.data_ptr(), None, stream)
+        corpus.score_topk_device(queries.data_ptr(), nq, 100, per_pass, ids.data_ptr(), scores.data_ptr(), None, stream)
     torch.cuda.synchronize()
     corpus.profile_begin(64)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(ts)
-    corpus.score_topk_device(queries.data_ptr(), nq, 100, 128, ids.data_ptr(), scores.data_ptr(), None, stream)
+    corpus.score_topk_device(queries.data_ptr(), nq, 100, per_pass, ids.data_ptr(), scores.data_ptr(), None, stream)
     e1.record(ts)
     torch.cuda.synchronize()
     ms, launches = corpus.profile_end(stream)
     print(f"score_tc {n} rows x {nq} queries: {e0.elapsed_time(e1):.3f} ms in all, {ms / launches:.3f} ms per main launch "
-          f"({launches} launches), {2.0 * 128 * n * 768 / (ms / launches) / 1e9:.0f} TFLOP/s")
+          f"({launches} launches of {per_pass} queries), {2.0 * per_pass * n * 768 / (ms / launches) / 1e9:.0f} TFLOP/s")
     corpus.close()
     qz.close()
     rt.close()
@@ -131,7 +131,7 @@ def case_attention() -> None:
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": case_gemm, "gemm_res": lambda: case_gemm(True), "scan": case_scan, "score_tc": case_score_tc, "attention": case_attention,
+    {"gemm": case_gemm, "gemm_res": lambda: case_gemm(True), "scan": case_scan, "score_tc": case_score_tc, "score_tc256": lambda: case_score_tc(per_pass=256), "attention": case_attention,
      "gemm_f16w": lambda: case_gemm(False, 1), "gemm_res_f16w": lambda: case_gemm(True, 1),
      "gemm_big": lambda: case_gemm(False, 0, 131072), "gemm_res_big": lambda: case_gemm(True, 0, 131072),
      "gemm_big_f16w": lambda: case_gemm(False, 1, 131072),

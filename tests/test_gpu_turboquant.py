@@ -96,6 +96,9 @@ def _check_topk(ids, scores, ref_scores, k, id_base, tol):
     (768, 4, 5000, 11, 100, 128), (768, 4, 2051, 140, 100, 128), (128, 2, 3000, 16, 10, 128), (96, 4, 50, 3, 100, 128),
     (96, 4, 140000, 9, 100, 128),  # unseeded, several tiles per CTA: every list is cut
     (96, 4, 310000, 9, 100, 128),  # thresholds seeded from the first 148 x 256 rows
+    # 256 queries per launch: documents as the MMA rows
+    (768, 4, 5000, 11, 100, 256), (768, 4, 2051, 300, 100, 256), (128, 2, 3000, 16, 10, 256), (96, 4, 50, 3, 100, 256),
+    (96, 4, 140000, 9, 100, 256), (96, 4, 310000, 9, 100, 256),
 ])
 def test_scores_and_topk_match_oracle(rt, dim, bits, n, nq, k, per_pass):
     import eos_b200
@@ -114,7 +117,7 @@ def test_scores_and_topk_match_oracle(rt, dim, bits, n, nq, k, per_pass):
     qz.close()
 
 
-@pytest.mark.parametrize("per_pass", [8, 128])
+@pytest.mark.parametrize("per_pass", [8, 128, 256])
 def test_ties_resolve_to_lower_id(rt, per_pass):
     import eos_b200
     spec, qz, codes, norms, q = _setup(rt, 768, 4, 640, 4)
@@ -263,11 +266,12 @@ def test_batch_kernel_ascending_scores(rt):
     corpus = eos_b200.Corpus(qz, codes, norms)
     ref = _oracle_scores(spec, codes[:1], np.ones(1, np.float32), q)[:, 0:1] * norms[None, :]
     ids8, sc8 = corpus.score_topk(q, 100, queries_per_pass=8)
-    ids, sc = corpus.score_topk(q, 100, queries_per_pass=128)
     tol = 1e-3 * float(np.abs(ref).max())
-    for i in range(q.shape[0]):
-        _check_topk(ids[i], sc[i], ref[i], 100, 0, tol)
-        assert np.array_equal(ids[i], ids8[i])
+    for per_pass in (128, 256):
+        ids, sc = corpus.score_topk(q, 100, queries_per_pass=per_pass)
+        for i in range(q.shape[0]):
+            _check_topk(ids[i], sc[i], ref[i], 100, 0, tol)
+            assert np.array_equal(ids[i], ids8[i])
     corpus.close()
     qz.close()
 
