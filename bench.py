@@ -36,7 +36,7 @@ TQ = dict(dim=768, bits=4, corpus=10_000_000, queries=4096, k=100)
 NCU_GEMM_DRAM_BYTES_PER_ROW = {"qkv": 152.35e6 / 32768, "attn_out": 124.88e6 / 32768, "ffn_up": 207.08e6 / 32768,
                                "ffn_down": 291.77e6 / 32768}
 NCU_SCAN_DRAM_BYTES_PER_ROW = 780.13e6 / 2_000_000
-NCU_TC_DRAM_BYTES_PER_ROW = 493.16e6 / 1_250_000  # profiles/tq_score_tc_kernel_*.md
+NCU_TC_DRAM_BYTES_PER_ROW = {128: 493.16e6 / 1_250_000, 256: 494.45e6 / 1_250_000}  # profiles/tq_score_tc*_kernel_*.md
 
 
 def load_peaks():
@@ -478,7 +478,7 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
             roofline = {"bound": "tensor", "kernel": "tq_score_tc_kernel" if per_pass == 128 else "tq_score_tc256_kernel", "achieved": tf, "peak": peaks["tflops"],
                         "unit": "TFLOP/s", "frac": tf / peaks["tflops"] if tf else None,
                         "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained)",
-                        "traffic": n_local * NCU_TC_DRAM_BYTES_PER_ROW if NCU_TC_DRAM_BYTES_PER_ROW else None,
+                        "traffic": n_local * NCU_TC_DRAM_BYTES_PER_ROW[per_pass],
                         "avg_launch_ms": scan_avg_ms, "algorithmic_flops_per_launch": flops,
                         "code_read_gbs": achieved}
         else:

@@ -272,8 +272,9 @@ EOS_B200_API int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* corpus);
  * queries_per_pass selects how many queries share one pass over the codes, and with it the kernel:
  *   8        streaming scan (codes expanded in registers, mma.sync): the choice for a few queries;
  *   16, 32   the same scan with more query fragments per pass;
- *   128      batch kernel on the tensor cores (codes expanded once per 128 queries into a tcgen05
- *            operand tile): the choice for hundreds of queries; q_count need not be a multiple of 128.
+ *   128, 256 batch kernels on the tensor cores (codes expanded once per 128 / 256 queries into a
+ *            tcgen05 operand tile): the choice for hundreds of queries (256 is the faster one once
+ *            q_count exceeds 128); q_count need not be a multiple.
  * The result is the same exact top-k for every value.
  * Results [q_count, k]: ids (int64, -1 when the corpus has fewer than k rows) and scores, ordered
  * score descending then id ascending.  k <= 128. */
