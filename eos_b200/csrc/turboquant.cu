@@ -735,8 +735,8 @@ __device__ __forceinline__ void warp_pick_digit(const unsigned* hist, unsigned w
 
 constexpr int kListThreads = 512;
 constexpr int kListMaxSegs = 1024;
-constexpr int kListCapKeys = 16384;   // 128 KB of keys
-constexpr int kSeedCapScores = 49152; // 192 KB of 32-bit scores
+constexpr int kListCapKeys = 8192;    // 64 KB of keys: three CTAs per SM, a launch of 256 queries is one wave
+constexpr int kSeedCapScores = 40960; // 80 KB of 16-bit scores: two CTAs per SM
 
 // prefix[0] = 0, prefix[i + 1] = sum of min(cnts[j], seg_len) for j <= i; returns the total.  Whole block.
 __device__ int list_prefix(const int* __restrict__ cnts, int n_segs, int seg_len, int* prefix) {
@@ -877,16 +877,18 @@ tq_merge_lists_kernel(const u64* __restrict__ cand, long long query_stride, long
 }
 
 // Pruning thresholds from the scores of a sample: scores is [queries][total] fp32 (every sample document's score,
-// written by the batch kernel in its seed mode).  tau[q] = (k-th best score, as a key with id bits 0) - 1, so that
-// every document scoring at least that much still passes; 0 when the sample holds fewer than k documents.  The
-// order-preserving 32 score bits of up to kSeedCapScores documents sit in shared memory; the radix select counts
-// into one histogram per warp (the scores of a query share their leading digits, and a single histogram would
-// serialise every warp on one counter).
+// written by the batch kernels in their seed mode).  Only the upper 16 of the 32 order-preserving score bits are
+// kept (rounded down, so that up to kSeedCapScores documents take 80 KB of shared memory and two radix passes
+// select): tau[q] = (k-th best truncated score, as a key whose other bits are 0) - 1.  At least k documents of
+// the sample have a key above it, so the k-th best key of the whole shard does too; the truncation (2^-7 of
+// the score) only lets a few more candidates pass.  0 when the sample holds fewer than k documents.  The radix
+// select counts into one histogram per warp (the scores of a query share their leading digits, and a single
+// histogram would serialise every warp on one counter).
 __global__ void __launch_bounds__(kListThreads)
 tq_seed_tau_scores_kernel(const float* __restrict__ scores, long long query_stride, int total, int k,
                           unsigned long long* __restrict__ tau) {
     extern __shared__ __align__(16) uint8_t lsm[];
-    uint32_t* buf = reinterpret_cast<uint32_t*>(lsm);                 // [kSeedCapScores]
+    uint16_t* buf = reinterpret_cast<uint16_t*>(lsm);                     // [kSeedCapScores]
     unsigned* whist = reinterpret_cast<unsigned*>(buf + kSeedCapScores);  // [warps][256]
     __shared__ unsigned hist[256];
     __shared__ uint32_t s_prefix, s_mask;
@@ -895,7 +897,7 @@ tq_seed_tau_scores_kernel(const float* __restrict__ scores, long long query_stri
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const float* src = scores + (long long)qi * query_stride;
     if (total > kSeedCapScores) total = kSeedCapScores;
-    auto ordered = [](float v) { return v == v ? float_to_ordered(v) : 0u; };  // NaN (no document) sorts last
+    auto ordered = [](float v) { return v == v ? float_to_ordered(v) >> 16 : 0u; };  // NaN (no document) sorts last
     if ((query_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(scores) & 15u) == 0) {
         const float4* src4 = reinterpret_cast<const float4*>(src);
         const int n4 = total >> 2;
@@ -908,13 +910,13 @@ tq_seed_tau_scores_kernel(const float* __restrict__ scores, long long query_stri
             for (int u = 0; u < 4; ++u) {
                 const int i = i0 + u * kListThreads;
                 if (i < n4)
-                    reinterpret_cast<uint4*>(buf)[i] =
-                        make_uint4(ordered(v[u].x), ordered(v[u].y), ordered(v[u].z), ordered(v[u].w));
+                    reinterpret_cast<uint2*>(buf)[i] = make_uint2(ordered(v[u].x) | (ordered(v[u].y) << 16),
+                                                                  ordered(v[u].z) | (ordered(v[u].w) << 16));
             }
         }
-        for (int i = (n4 << 2) + threadIdx.x; i < total; i += blockDim.x) buf[i] = ordered(src[i]);
+        for (int i = (n4 << 2) + threadIdx.x; i < total; i += blockDim.x) buf[i] = (uint16_t)ordered(src[i]);
     } else {
-        for (int i = threadIdx.x; i < total; i += blockDim.x) buf[i] = ordered(src[i]);
+        for (int i = threadIdx.x; i < total; i += blockDim.x) buf[i] = (uint16_t)ordered(src[i]);
     }
     if (threadIdx.x == 0) {
         s_prefix = 0;
@@ -926,7 +928,7 @@ tq_seed_tau_scores_kernel(const float* __restrict__ scores, long long query_stri
         if (threadIdx.x == 0) tau[qi] = 0;
         return;
     }
-    for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int shift = 8; shift >= 0; shift -= 8) {
         for (int i = lane; i < 256; i += 32) whist[warp * 256 + i] = 0;
         __syncwarp();
         const uint32_t pre = s_prefix, mask = s_mask;
@@ -954,7 +956,7 @@ tq_seed_tau_scores_kernel(const float* __restrict__ scores, long long query_stri
         }
         __syncthreads();
     }
-    if (threadIdx.x == 0) tau[qi] = s_prefix != 0 ? ((u64)s_prefix << 32) - 1 : 0;
+    if (threadIdx.x == 0) tau[qi] = s_prefix != 0 ? ((u64)s_prefix << 48) - 1 : 0;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1214,7 +1216,7 @@ cudaError_t tq_merge_init() {
                                          kListCapKeys * 8 + (kListMaxSegs + 1) * 4);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(tq_seed_tau_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kSeedCapScores * 4 + (kListThreads / 32) * 256 * 4);
+                                 kSeedCapScores * 2 + (kListThreads / 32) * 256 * 4);
     return e;
 }
 
@@ -1235,7 +1237,7 @@ void launch_tq_merge_lists(const uint64_t* cand, int64_t query_stride, int64_t s
 void launch_tq_seed_tau_scores(const float* scores, int64_t query_stride, int total, int queries, int k,
                                unsigned long long* tau, cudaStream_t stream) {
     if (queries <= 0) return;
-    tq_seed_tau_scores_kernel<<<queries, kListThreads, kSeedCapScores * 4 + (kListThreads / 32) * 256 * 4, stream>>>(
+    tq_seed_tau_scores_kernel<<<queries, kListThreads, kSeedCapScores * 2 + (kListThreads / 32) * 256 * 4, stream>>>(
         scores, (long long)query_stride, total, k, tau);
 }
 

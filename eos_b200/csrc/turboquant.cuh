@@ -138,7 +138,8 @@ void launch_tq_merge_lists(const uint64_t* cand, int64_t query_stride, int64_t s
                            const int* counts, int queries, int k, int64_t* out_ids, float* out_scores, uint64_t* out_keys,
                            cudaStream_t stream);
 // tau[q] = largest key that every document scoring at least the k-th best of scores[q][0..total) still beats (0 when
-// total < k); scores is [queries][query_stride] fp32, NaN = no document.  At most 49152 scores per query are used.
+// total < k; the scores are compared on their upper 16 bits, rounded down); scores is [queries][query_stride] fp32,
+// NaN = no document.  At most 40960 scores per query are used.
 void launch_tq_seed_tau_scores(const float* scores, int64_t query_stride, int total, int queries, int k,
                                unsigned long long* tau, cudaStream_t stream);
 
