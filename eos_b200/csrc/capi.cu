@@ -1442,11 +1442,18 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
     return launches;
 }
 
+// queries_per_pass = 0 lets the library choose: the streaming scan for a handful of queries, the batch kernels above.
+int resolve_per_pass(int per_pass, int q_count) {
+    if (per_pass != 0) return per_pass;
+    if (q_count <= 16) return 8;
+    return q_count <= kTqTcQueries ? kTqTcQueries : kTqTc256Queries;
+}
+
 std::string check_score_args(const EosB200Corpus* c, int q_count, int k, int per_pass) {
     if (q_count <= 0) return "score_topk: no queries";
     if (k <= 0 || k > kTqMaxK) return "score_topk: k must be in [1, 128]";
     if (per_pass != 8 && per_pass != 16 && per_pass != 32 && per_pass != kTqTcQueries && per_pass != kTqTc256Queries)
-        return "score_topk: queries_per_pass must be 8, 16, 32, 128 or 256";
+        return "score_topk: queries_per_pass must be 0 (automatic), 8, 16, 32, 128 or 256";
     if (c->n + c->id_base > 0xffffffffLL || c->id_base < 0) return "score_topk: document ids must fit 32 bits";
     return "";
 }
@@ -1666,6 +1673,7 @@ int eos_b200_score_topk_device(EosB200Corpus* c, const float* d_queries, int q_c
                                int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream, EosB200Stats* stats,
                                char** err) {
     if (c == nullptr || d_queries == nullptr) return fail(err, "score_topk: null argument");
+    per_pass = resolve_per_pass(per_pass, q_count);
     std::string m = check_score_args(c, q_count, k, per_pass);
     if (!m.empty()) return fail(err, m);
     if (c->n == 0) return fail(err, "score_topk: empty corpus");
@@ -1688,6 +1696,7 @@ int eos_b200_score_topk(EosB200Corpus* c, const float* h_queries, int q_count, i
                         float* h_scores, EosB200Stats* stats, char** err) {
     if (c == nullptr || h_queries == nullptr || h_ids == nullptr || h_scores == nullptr)
         return fail(err, "score_topk: null argument");
+    per_pass = resolve_per_pass(per_pass, q_count);
     std::string m = check_score_args(c, q_count, k, per_pass);
     if (!m.empty()) return fail(err, m);
     if (c->n == 0) {  // topK > len(docs): nothing to return (runtime/retrieval_turboquant.go:1854-1860)

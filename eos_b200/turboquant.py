@@ -157,8 +157,10 @@ class Corpus:
             quantizer._children.add(self)
         self.last_stats = Stats()
 
-    def score_topk(self, queries, k: int, queries_per_pass: int = 8) -> Tuple[np.ndarray, np.ndarray]:
-        """Exact top-k per query: (ids int64 [Q,k], scores fp32 [Q,k]); score desc, then id asc."""
+    def score_topk(self, queries, k: int, queries_per_pass: int = 0) -> Tuple[np.ndarray, np.ndarray]:
+        """Exact top-k per query: (ids int64 [Q,k], scores fp32 [Q,k]); score desc, then id asc.
+        queries_per_pass: 0 = automatic (streaming scan up to 16 queries, tensor-core batch kernels above),
+        or 8 / 16 / 32 (streaming scan), 128 / 256 (batch kernels)."""
         q = _f32(queries)
         if q.ndim != 2 or q.shape[1] != self.qz.spec.dim or q.shape[0] == 0:
             raise ValueError(f"score_topk expects non-empty [Q, {self.qz.spec.dim}] queries, got {q.shape}")

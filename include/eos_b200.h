@@ -270,6 +270,7 @@ EOS_B200_API int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* corpus);
  * (runtime/retrieval_turboquant.go:1324-1325, 1853-1887): exact top-k of
  * norm * <R q, centroids[codes]> over the corpus, for q_count queries [q_count, dim] fp32.
  * queries_per_pass selects how many queries share one pass over the codes, and with it the kernel:
+ *   0        automatic: 8 up to 16 queries, 128 up to 128 queries, 256 above;
  *   8        streaming scan (codes expanded in registers, mma.sync): the choice for a few queries;
  *   16, 32   the same scan with more query fragments per pass;
  *   128, 256 batch kernels on the tensor cores (codes expanded once per 128 / 256 queries into a

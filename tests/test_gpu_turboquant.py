@@ -312,3 +312,28 @@ def test_batch_kernel_with_queries_in_tensor_memory():
                          timeout=900)
     assert out.returncode == 0, out.stderr[-2000:]
     assert "TMEM_RESULT ok" in out.stdout
+
+
+def test_automatic_queries_per_pass_and_argument_errors(rt):
+    """queries_per_pass = 0 picks the kernel from the batch size; every choice returns the same exact top-k.
+    Values outside {0, 8, 16, 32, 128, 256} are rejected, and the allocation-free entry takes the scan only."""
+    import torch
+    import eos_b200
+    spec, qz, codes, norms, q = _setup(rt, 128, 4, 6000, 300)
+    corpus = eos_b200.Corpus(qz, codes, norms)
+    ref_ids, ref_sc = corpus.score_topk(q, 20, queries_per_pass=8)
+    for nq in (5, 40, 300):
+        ids, sc = corpus.score_topk(q[:nq], 20)            # 8, 128 and 256 queries per pass respectively
+        scale = float(np.abs(ref_sc).max())
+        assert np.abs(sc - ref_sc[:nq]).max() <= 1e-5 * scale          # same f16 operands, fp32 accumulation
+        differ = ids != ref_ids[:nq]                                     # only exact-to-rounding ties may swap
+        assert differ.mean() < 0.01
+    with pytest.raises(Exception, match="queries_per_pass"):
+        corpus.score_topk(q[:4], 20, queries_per_pass=64)
+    dq = torch.from_numpy(q[:8]).cuda()
+    d_ids = torch.empty((8, 20), dtype=torch.int64, device="cuda")
+    d_sc = torch.empty((8, 20), dtype=torch.float32, device="cuda")
+    with pytest.raises(Exception, match="queries_per_pass"):
+        corpus.score_topk_noalloc(dq.data_ptr(), 8, 20, 128, d_ids.data_ptr(), d_sc.data_ptr())
+    corpus.close()
+    qz.close()
