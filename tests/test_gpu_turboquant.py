@@ -337,3 +337,20 @@ def test_automatic_queries_per_pass_and_argument_errors(rt):
         corpus.score_topk_noalloc(dq.data_ptr(), 8, 20, 128, d_ids.data_ptr(), d_sc.data_ptr())
     corpus.close()
     qz.close()
+
+
+@pytest.mark.parametrize("per_pass", [8, 128, 256])
+@pytest.mark.parametrize("dim,n,nq,k", [(1024, 3000, 20, 128), (64, 2000, 7, 1), (768, 40000, 130, 128)])
+def test_extreme_k_and_dims(rt, dim, n, nq, k, per_pass):
+    """Largest and smallest k, the widest supported dimension (1024: 16 k-blocks, queries cannot stay in tensor
+    memory) and a narrow one (64: half a code chunk is padding), for every scoring kernel."""
+    import eos_b200
+    spec, qz, codes, norms, q = _setup(rt, dim, 4, n, nq)
+    corpus = eos_b200.Corpus(qz, codes, norms, id_base=7)
+    ref = _oracle_scores(spec, codes, norms, q)
+    tol = 1e-3 * float(np.abs(ref).max())
+    ids, scores = corpus.score_topk(q, k, queries_per_pass=per_pass)
+    for i in range(nq):
+        _check_topk(ids[i], scores[i], ref[i], k, 7, tol)
+    corpus.close()
+    qz.close()
