@@ -469,16 +469,19 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
                    "d2h_bytes_per_step": int(st.downloaded_bytes), "queries_per_s": nq / dt}
         bytes_per_vec = spec.vector_bytes
         scan_avg_ms = scan_ms / max(1, scan_launches)
-        achieved = (n_local * bytes_per_vec) / (scan_avg_ms / 1e3) / 1e9 if scan_avg_ms > 0 else None
+        # a launch of the 256-query kernel walks the shard once per group of 256 queries (up to 4 groups per launch)
+        passes_per_launch = passes * steps / max(1, scan_launches)
+        achieved = (passes_per_launch * n_local * bytes_per_vec) / (scan_avg_ms / 1e3) / 1e9 if scan_avg_ms > 0 else None
         if per_pass >= 128:
             # the batch kernels are contractions on the tensor cores: 2 x queries x rows x padded dim flops per launch
             dimp = (dim + 127) // 128 * 128
-            flops = 2.0 * per_pass * n_local * dimp
+            flops = 2.0 * per_pass * n_local * dimp * passes_per_launch
             tf = flops / (scan_avg_ms / 1e3) / 1e12 if scan_avg_ms > 0 else None
             roofline = {"bound": "tensor", "kernel": "tq_score_tc_kernel" if per_pass == 128 else "tq_score_tc256_kernel", "achieved": tf, "peak": peaks["tflops"],
                         "unit": "TFLOP/s", "frac": tf / peaks["tflops"] if tf else None,
                         "peak_source": f"{peaks['source']} (cuBLAS bf16, sustained)",
-                        "traffic": n_local * NCU_TC_DRAM_BYTES_PER_ROW[per_pass],
+                        "traffic": n_local * NCU_TC_DRAM_BYTES_PER_ROW[per_pass] * passes_per_launch,
+                        "shard_passes_per_launch": passes_per_launch,
                         "avg_launch_ms": scan_avg_ms, "algorithmic_flops_per_launch": flops,
                         "code_read_gbs": achieved}
         else:
