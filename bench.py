@@ -425,6 +425,10 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
     scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
     keys = torch.empty((nq, k), dtype=torch.int64, device="cuda")
     keys_all = torch.empty((world, nq, k), dtype=torch.int64, device="cuda") if world > 1 else None
+    # thresholds seeded cooperatively: slices of the queries, a multiple of 256 each
+    tau_slice = ((nq + world - 1) // world + 255) // 256 * 256 if world > 1 and not args.tq_local_seeds else 0
+    tau_local = torch.zeros((max(1, tau_slice),), dtype=torch.int64, device="cuda")
+    tau_all = torch.zeros((max(1, tau_slice) * world,), dtype=torch.int64, device="cuda")
     def measure(per_pass, steps, with_e2e):
         launches = 0
 
@@ -433,6 +437,19 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
             if world == 1:
                 n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, ids.data_ptr(), scores.data_ptr(), None,
                                               stream)
+            elif per_pass >= 128 and tau_slice > 0:
+                # every rank seeds the thresholds of its slice of the queries from its own shard (a threshold from any
+                # shard bounds the k-th best score of the whole corpus), one small all-gather shares them
+                q_lo = min(nq, rank * tau_slice)
+                q_n = min(nq, q_lo + tau_slice) - q_lo
+                tau_local.zero_()
+                if q_n > 0:
+                    corpus.score_seed_device(queries[q_lo:].data_ptr(), q_n, k, tau_local.data_ptr(), stream)
+                    n += 2 * ((q_n + 255) // 256) + 1
+                dist.all_gather_into_tensor(tau_all, tau_local)
+                n += corpus.score_topk_seeded_device(queries.data_ptr(), nq, k, tau_all.data_ptr(), None, None,
+                                                     keys.data_ptr(), stream)
+                dist.all_gather_into_tensor(keys_all, keys)  # one NCCL all-gather of the per-shard candidates
             else:
                 n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, None, None, keys.data_ptr(), stream)
                 dist.all_gather_into_tensor(keys_all, keys)  # one NCCL all-gather of the per-shard top-k
@@ -501,7 +518,9 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
                                    f"{world} GPU(s), {nq} f16 queries, exact top-{k}, {per_pass} queries per corpus pass "
                                    f"({passes} passes); one vector scored = one (query, vector) inner product",
                        "bytes_per_vector": bytes_per_vec,
-                       "merge": "none" if world == 1 else "NCCL all-gather of per-shard top-k + merge kernel"},
+                       "merge": "none" if world == 1 else "NCCL all-gather of per-shard top-k + merge kernel",
+                       "thresholds": "seeded per shard" if world == 1 or tau_slice == 0 or per_pass < 128 else
+                                     f"each rank seeds {tau_slice} queries, NCCL all-gather of {nq} thresholds"},
             "roofline": roofline,
             "_launches": launches,
         }
@@ -554,6 +573,8 @@ def main():
     ap.add_argument("--tq-queries-per-pass", type=int, default=256, choices=[8, 16, 32, 128, 256],
                     help="128 = tensor-core batch kernel; 8 = streaming scan; 16 / 32 = the earlier register-blocked scan")
     ap.add_argument("--tq-skip-stream", action="store_true", help="do not also time the 8-queries-per-pass scan")
+    ap.add_argument("--tq-local-seeds", action="store_true",
+                    help="multi-GPU: every rank seeds the thresholds of all queries itself instead of a slice each")
     ap.add_argument("--weight-mode", default="f16_resident", choices=["f16_resident", "q8_smem"],
                     help="how the projection kernel receives the 8-bit weights (results are bit-identical)")
     ap.add_argument("--skip-other-mode", action="store_true", help="do not also time the other weight mode")

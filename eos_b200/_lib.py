@@ -111,6 +111,9 @@ SYMBOLS = {
     "eos_b200_score_topk": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_score_topk_device": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, C.POINTER(Stats),
                                              _ERR]),
+    "eos_b200_score_seed_device": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _ERR]),
+    "eos_b200_score_topk_seeded_device": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, _P, _P, C.POINTER(Stats),
+                                                    _ERR]),
     "eos_b200_score_topk_noalloc": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _ERR]),
     "eos_b200_topk_merge_device": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _ERR]),
     "eos_b200_score_all": (C.c_int, [_P, _P, C.c_int, _P, _ERR]),

@@ -1395,15 +1395,20 @@ int enqueue_tc_passes(EosB200Corpus* c, int plan, int64_t n_docs, int q_count, i
 // query); on a large shard a second sample of 1/32 of the rows, scored with those thresholds and merged like the real
 // pass, tightens them further, so that the lists of the full pass stay short (no list is cut, and the merge gathers a
 // few thousand keys per query).  Then the whole shard.
+// d_tau_in, when non-null, holds one threshold per query supplied by the caller (for instance seeded on other shards
+// and gathered): it replaces the seeding passes.  With thresholds that are lower bounds of the k-th best key of the
+// whole sharded corpus, the result is the shard's part of the global top-k rather than the shard's own top-k.
 int enqueue_score_tc(EosB200Corpus* c, int plan, const float* d_queries, int q_count, int k, int64_t* d_ids,
-                     float* d_scores, uint64_t* d_keys, cudaStream_t s) {
+                     float* d_scores, uint64_t* d_keys, const uint64_t* d_tau_in, cudaStream_t s) {
     const EosB200Corpus::TcPlan& p = c->tcp[plan];
     const int q_pad = (q_count + p.queries - 1) / p.queries * p.queries;
     int launches = 1;
     launch_tq_prepare(d_queries, q_count, q_pad, c->qz->spec(), nullptr, nullptr, c->qperm, s);
     cudaMemsetAsync(c->shared_tau, 0, (size_t)q_pad * sizeof(unsigned long long), s);
     const int64_t seed_docs = (int64_t)p.grid * 256;
-    if (c->n >= 8 * seed_docs && k <= seed_docs) {
+    if (d_tau_in != nullptr) {
+        cudaMemcpyAsync(c->shared_tau, d_tau_in, (size_t)q_count * sizeof(unsigned long long), cudaMemcpyDeviceToDevice, s);
+    } else if (c->n >= 8 * seed_docs && k <= seed_docs) {
         launches += enqueue_tc_passes(c, plan, seed_docs, q_count, k, true, false, nullptr, nullptr, nullptr, s);
         if (c->n >= 64 * seed_docs) {
             const int64_t second = c->n / 32 / 256 * 256;
@@ -1421,7 +1426,8 @@ int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, 
                   float* d_scores, uint64_t* d_keys, cudaStream_t s) {
     EosB200Quantizer* qz = c->qz;
     if (per_pass == kTqTcQueries || per_pass == kTqTc256Queries)
-        return enqueue_score_tc(c, per_pass == kTqTc256Queries ? 1 : 0, d_queries, q_count, k, d_ids, d_scores, d_keys, s);
+        return enqueue_score_tc(c, per_pass == kTqTc256Queries ? 1 : 0, d_queries, q_count, k, d_ids, d_scores, d_keys,
+                                nullptr, s);
     int launches = 0;
     launch_tq_prepare(d_queries, q_count, (q_count + 31) / 32 * 32, qz->spec(), c->bfrag, nullptr, nullptr, s);
     launches++;
@@ -1684,6 +1690,55 @@ int eos_b200_score_topk_device(EosB200Corpus* c, const float* d_queries, int q_c
     if (rc != EOS_B200_OK) return rc;
     const int launches =
         enqueue_score(c, d_queries, q_count, k, per_pass, d_ids, d_scores, d_keys, pick_stream(c->qz->rt, stream));
+    CUDA_TRY(cudaGetLastError());
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+    }
+    return EOS_B200_OK;
+}
+
+int eos_b200_score_seed_device(EosB200Corpus* c, const float* d_queries, int q_count, int k, uint64_t* d_tau_out,
+                               void* stream, char** err) {
+    if (c == nullptr || d_queries == nullptr || d_tau_out == nullptr) return fail(err, "score_seed: null argument");
+    std::string m = check_score_args(c, q_count, k, kTqTc256Queries);
+    if (!m.empty()) return fail(err, m);
+    CUDA_TRY(cudaSetDevice(c->qz->rt->device));
+    cudaStream_t s = pick_stream(c->qz->rt, stream);
+    if (c->n == 0) {
+        CUDA_TRY(cudaMemsetAsync(d_tau_out, 0, (size_t)q_count * sizeof(uint64_t), s));
+        return EOS_B200_OK;
+    }
+    int rc = ensure_score_workspace(c, q_count, err);
+    if (rc == EOS_B200_OK) rc = ensure_tc_workspace(c, 1, err);
+    if (rc != EOS_B200_OK) return rc;
+    const EosB200Corpus::TcPlan& p = c->tcp[1];
+    const int q_pad = (q_count + p.queries - 1) / p.queries * p.queries;
+    launch_tq_prepare(d_queries, q_count, q_pad, c->qz->spec(), nullptr, nullptr, c->qperm, s);
+    CUDA_TRY(cudaMemsetAsync(c->shared_tau, 0, (size_t)q_pad * sizeof(unsigned long long), s));
+    const int64_t seed_docs = (int64_t)p.grid * 256;
+    if (c->n >= seed_docs && k <= seed_docs)
+        enqueue_tc_passes(c, 1, seed_docs, q_count, k, true, false, nullptr, nullptr, nullptr, s);
+    CUDA_TRY(cudaMemcpyAsync(d_tau_out, c->shared_tau, (size_t)q_count * sizeof(uint64_t), cudaMemcpyDeviceToDevice, s));
+    CUDA_TRY(cudaGetLastError());
+    return EOS_B200_OK;
+}
+
+int eos_b200_score_topk_seeded_device(EosB200Corpus* c, const float* d_queries, int q_count, int k, const uint64_t* d_tau,
+                                      int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream,
+                                      EosB200Stats* stats, char** err) {
+    if (c == nullptr || d_queries == nullptr || d_tau == nullptr) return fail(err, "score_topk_seeded: null argument");
+    const int per_pass = q_count <= kTqTcQueries ? kTqTcQueries : kTqTc256Queries;
+    std::string m = check_score_args(c, q_count, k, per_pass);
+    if (!m.empty()) return fail(err, m);
+    if (c->n == 0) return fail(err, "score_topk_seeded: empty corpus");
+    CUDA_TRY(cudaSetDevice(c->qz->rt->device));
+    const int plan = per_pass == kTqTc256Queries ? 1 : 0;
+    int rc = ensure_score_workspace(c, q_count, err);
+    if (rc == EOS_B200_OK) rc = ensure_tc_workspace(c, plan, err);
+    if (rc != EOS_B200_OK) return rc;
+    const int launches =
+        enqueue_score_tc(c, plan, d_queries, q_count, k, d_ids, d_scores, d_keys, d_tau, pick_stream(c->qz->rt, stream));
     CUDA_TRY(cudaGetLastError());
     if (stats != nullptr) {
         std::memset(stats, 0, sizeof(*stats));

@@ -177,6 +177,23 @@ class Corpus:
                   d_ids, d_scores, d_keys, stream, C.byref(st))
         return st.kernel_launches
 
+    def score_seed_device(self, d_queries: int, q_count: int, k: int, d_tau_out: int,
+                          stream: Optional[int] = None) -> None:
+        """Pruning thresholds (uint64 keys, [q_count]) of these queries from a sample of this shard.  With a corpus
+        sharded over several GPUs each rank seeds a slice of the batch and the slices are all-gathered: a threshold
+        from any shard is a lower bound of the k-th best score of the whole corpus."""
+        _lib.call("eos_b200_score_seed_device", self.handle, d_queries, int(q_count), int(k), d_tau_out, stream)
+
+    def score_topk_seeded_device(self, d_queries: int, q_count: int, k: int, d_tau: int, d_ids: Optional[int],
+                                 d_scores: Optional[int], d_keys: Optional[int] = None,
+                                 stream: Optional[int] = None) -> int:
+        """Batch scoring with caller-supplied thresholds ([q_count] uint64 keys, 0 = none): this shard's part of the
+        top-k of the whole sharded corpus (empty slots: id -1 / key 0)."""
+        st = Stats()
+        _lib.call("eos_b200_score_topk_seeded_device", self.handle, d_queries, int(q_count), int(k), d_tau, d_ids,
+                  d_scores, d_keys, stream, C.byref(st))
+        return st.kernel_launches
+
     def score_topk_noalloc(self, d_queries: int, q_count: int, k: int, queries_per_pass: int, d_ids: int,
                            d_scores: int, stream: Optional[int] = None) -> None:
         """score_topk_device for callers that may not allocate device memory while serving (a fixed memory

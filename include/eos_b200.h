@@ -286,6 +286,18 @@ EOS_B200_API int eos_b200_score_topk(EosB200Corpus* corpus, const float* h_queri
 EOS_B200_API int eos_b200_score_topk_device(EosB200Corpus* corpus, const float* d_queries, int q_count, int k,
                                int queries_per_pass, int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream,
                                EosB200Stats* stats, char** err);
+/* No counterpart in Eos (its scoring is per process): the two halves of the batch scoring call, for a corpus
+ * sharded over several GPUs.  A threshold seeded on ANY shard (the k-th best score of a sample of that shard) is a
+ * lower bound of the k-th best score of the whole corpus, so the ranks may split the work of seeding -- rank r calls
+ * eos_b200_score_seed_device for its slice of the queries, the slices are all-gathered (8 bytes per query) -- and
+ * every rank then scores with all thresholds.  The per-shard result is that shard's part of the global top-k (it
+ * may hold fewer than k entries; the rest are empty keys), which is what eos_b200_topk_merge_device needs.
+ * d_tau_out / d_tau: [q_count] uint64 keys, 0 = no threshold. */
+EOS_B200_API int eos_b200_score_seed_device(EosB200Corpus* corpus, const float* d_queries, int q_count, int k,
+                               uint64_t* d_tau_out, void* stream, char** err);
+EOS_B200_API int eos_b200_score_topk_seeded_device(EosB200Corpus* corpus, const float* d_queries, int q_count, int k,
+                                      const uint64_t* d_tau, int64_t* d_ids, float* d_scores, uint64_t* d_keys,
+                                      void* stream, EosB200Stats* stats, char** err);
 /* (eos_b200_score_topk_noalloc below takes queries_per_pass in {8, 16, 32} only.) */
 /* No counterpart in Eos: a scoring call for hosts that must not allocate device memory while they
  * serve queries -- for example a caller that holds the GPU inside a pre-sized memory arena, runs

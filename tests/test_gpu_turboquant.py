@@ -354,3 +354,39 @@ def test_extreme_k_and_dims(rt, dim, n, nq, k, per_pass):
         _check_topk(ids[i], scores[i], ref[i], k, 7, tol)
     corpus.close()
     qz.close()
+
+
+def test_thresholds_seeded_on_other_shards(rt):
+    """Two shards of one corpus on one GPU, as two ranks would hold them: each seeds the thresholds of half of the
+    queries from its own sample, the halves are concatenated (the all-gather), both shards score with all
+    thresholds, and the merge of the two partial lists is the exact top-k of the whole corpus."""
+    import torch
+    import eos_b200
+    from eos_b200 import turboquant as tq
+    dim, n, nq, k = 96, 640000, 300, 100
+    spec, qz, codes, norms, q = _setup(rt, dim, 4, n, nq)
+    half = n // 2
+    shards = [eos_b200.Corpus(qz, codes[:half], norms[:half], id_base=0),
+              eos_b200.Corpus(qz, codes[half:], norms[half:], id_base=half)]
+    whole = eos_b200.Corpus(qz, codes, norms)
+    ref_ids, ref_sc = whole.score_topk(q, k, queries_per_pass=256)
+    dq = torch.from_numpy(q).cuda()
+    tau = torch.zeros((nq,), dtype=torch.int64, device="cuda")
+    cut = 150
+    keys = torch.zeros((2, nq, k), dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()                                # the library works on its own stream
+    shards[0].score_seed_device(dq.data_ptr(), cut, k, tau.data_ptr())
+    shards[1].score_seed_device(dq[cut:].data_ptr(), nq - cut, k, tau[cut:].data_ptr())
+    torch.cuda.synchronize()
+    assert int((tau != 0).sum()) == nq                      # both shards are large enough to seed
+    for r in range(2):
+        shards[r].score_topk_seeded_device(dq.data_ptr(), nq, k, tau.data_ptr(), None, None, keys[r].data_ptr())
+    ids = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+    sc = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+    tq.topk_merge_device(rt, keys.data_ptr(), 2, nq, k, ids.data_ptr(), sc.data_ptr())
+    torch.cuda.synchronize()
+    assert np.array_equal(ids.cpu().numpy(), ref_ids)
+    assert np.array_equal(sc.cpu().numpy(), ref_sc)
+    for c in shards + [whole]:
+        c.close()
+    qz.close()
