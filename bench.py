@@ -155,8 +155,8 @@ def run_reference(args, rank: int):
     oargs = oracle_encoder_args(weights)
     # size the per-step sample so that warmup + steps stay within a few minutes
     rate1, t1, _, _ = time_oracle_encoder(oargs, 1, cores, 1, 0, 303)
-    budget = 150.0 / max(1, args.steps + args.warmup)
-    n_seq = int(max(1, min(16, budget / max(t1, 1e-3))))
+    seconds_per_step = 150.0 / max(1, args.steps + args.warmup)
+    n_seq = int(max(1, min(16, seconds_per_step / max(t1, 1e-3))))
     rate, t_step, t_len, lengths = time_oracle_encoder(oargs, n_seq, cores, args.steps, args.warmup, 303)
     sample = f"{n_seq} sequence(s) of the seeded batch padded to {t_len} tokens per step, all {cores} host threads"
     line = {
