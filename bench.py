@@ -529,7 +529,12 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
         return res
 
     steps = max(1, min(args.steps, args.tq_steps))
+    sampler = ClockSampler(torch.cuda.current_device())
+    if rank == 0:
+        sampler.start()
     out = measure(per_pass, steps, True)
+    if rank == 0:
+        out["clocks"] = sampler.stop()  # warm-up, timed steps and the end-to-end calls of the batch kernel
     if per_pass != 8 and not args.tq_skip_stream:
         # the 8-queries-per-pass streaming scan (the kernel small batches use) on the same shard: its HBM roofline
         st = measure(8, 1, False)
