@@ -137,9 +137,9 @@ def time_oracle_encoder(oargs, n_seq: int, workers: int, steps: int, warmup: int
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        O.bert_embedder(ids, mask, types, oargs["tok"], oargs["pos"], oargs["typ"], oargs["emb_gamma"],
-                        oargs["emb_beta"], oargs["layer_weights"], oargs["heads"], 1e-12, "masked_mean",
-                        head_w=oargs["head_w"], workers=workers)
+        time_oracle_encoder.last_output = O.bert_embedder(
+            ids, mask, types, oargs["tok"], oargs["pos"], oargs["typ"], oargs["emb_gamma"], oargs["emb_beta"],
+            oargs["layer_weights"], oargs["heads"], 1e-12, "masked_mean", head_w=oargs["head_w"], workers=workers)
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
@@ -163,7 +163,7 @@ def run_reference(args, rank: int):
         "impl": "reference", "metric": "q8_encoder_embeddings_per_s_T512", "value": rate, "unit": "embeddings/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64-accumulate/f32",
-        "data": "synthetic", "config": workload_config(1),
+        "data": "synthetic", "config": dict(workload_config(args.gpus), weight_mode=args.weight_mode),
         "cpu_baseline": {"value": rate, "unit": "embeddings/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": rate, "unit": "embeddings/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -331,9 +331,15 @@ def run_ours(args, rank: int, world: int, local: int):
         _, t1, _, _ = time_oracle_encoder(oargs, 1, cores, 1, 0, 303)
         n_seq = int(max(1, min(8, 12.0 / max(t1, 1e-3))))
         rate, _, t_len, _ = time_oracle_encoder(oargs, n_seq, cores, 1, 0, 303)
+        # outside every timed region: the GPU's embeddings of those same sequences against the CPU port's
+        s_ids, s_mask, _ = encoder_sample(n_seq, 303)
+        gpu_sample = enc.run(s_ids, s_mask)
+        check_err = float(np.abs(gpu_sample - time_oracle_encoder.last_output).max())
+        assert check_err <= 2e-3, f"encoder output differs from the CPU port by {check_err}"
         cpu = {"value": rate, "unit": "embeddings/s", "cores": cores, "kind": "port",
                "sample": f"{n_seq} sequence(s) of the seeded batch padded to {t_len} tokens, all {cores} host threads, "
-                         "one pass"}
+                         "one pass",
+               "gpu_vs_port_max_abs": check_err}
         del oargs
     enc.close()
     # the other weight mode, timed the same way on fewer steps (reported beside the headline, not as it)
@@ -450,6 +456,8 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
                 n += corpus.score_topk_seeded_device(queries.data_ptr(), nq, k, tau_all.data_ptr(), None, None,
                                                      keys.data_ptr(), stream)
                 dist.all_gather_into_tensor(keys_all, keys)  # one NCCL all-gather of the per-shard candidates
+                tq.topk_merge_device(rt, keys_all.data_ptr(), world, nq, k, ids.data_ptr(), scores.data_ptr(), stream)
+                n += 1
             else:
                 n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, None, None, keys.data_ptr(), stream)
                 dist.all_gather_into_tensor(keys_all, keys)  # one NCCL all-gather of the per-shard top-k
@@ -535,6 +543,26 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
     out = measure(per_pass, steps, True)
     if rank == 0:
         out["clocks"] = sampler.stop()  # warm-up, timed steps and the end-to-end calls of the batch kernel
+    # outside the timed region: the job's result for the first 16 queries (ids / scores hold the last step's output,
+    # merged over all shards) against the streaming scan of the same shards, merged the same way
+    chk_q = 16
+    batch_ids, batch_sc = ids[:chk_q].clone(), scores[:chk_q].clone()
+    c_ids = torch.empty((chk_q, k), dtype=torch.int64, device="cuda")
+    c_sc = torch.empty((chk_q, k), dtype=torch.float32, device="cuda")
+    if world == 1:
+        corpus.score_topk_device(queries.data_ptr(), chk_q, k, 8, c_ids.data_ptr(), c_sc.data_ptr(), None, stream)
+    else:
+        c_keys = torch.empty((chk_q, k), dtype=torch.int64, device="cuda")
+        c_all = torch.empty((world, chk_q, k), dtype=torch.int64, device="cuda")
+        corpus.score_topk_device(queries.data_ptr(), chk_q, k, 8, None, None, c_keys.data_ptr(), stream)
+        dist.all_gather_into_tensor(c_all, c_keys)
+        tq.topk_merge_device(rt, c_all.data_ptr(), world, chk_q, k, c_ids.data_ptr(), c_sc.data_ptr(), stream)
+    corpus.sync(stream)
+    same = float((batch_ids == c_ids).float().mean().item())
+    sc_err = float(((batch_sc - c_sc).abs().max() / c_sc.abs().max()).item())
+    assert same >= 0.99 and sc_err <= 1e-4, f"batch kernel and streaming scan disagree: ids {same}, scores {sc_err}"
+    out["self_check"] = {"queries": chk_q, "ids_equal_fraction": same, "max_rel_score_diff": sc_err,
+                         "against": "8-queries-per-pass streaming scan over the same shards"}
     if per_pass != 8 and not args.tq_skip_stream:
         # the 8-queries-per-pass streaming scan (the kernel small batches use) on the same shard: its HBM roofline
         st = measure(8, 1, False)
@@ -583,7 +611,7 @@ def main():
     ap.add_argument("--weight-mode", default="f16_resident", choices=["f16_resident", "q8_smem"],
                     help="how the projection kernel receives the 8-bit weights (results are bit-identical)")
     ap.add_argument("--skip-other-mode", action="store_true", help="do not also time the other weight mode")
-    ap.add_argument("--tq-steps", type=int, default=2)
+    ap.add_argument("--tq-steps", type=int, default=10)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world, local = dist_setup(args.gpus)

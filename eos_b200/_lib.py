@@ -82,6 +82,7 @@ SYMBOLS = {
     "eos_b200_runtime_create": (C.c_int, [C.c_int, C.POINTER(_P), _ERR]),
     "eos_b200_runtime_destroy": (None, [_P]),
     "eos_b200_runtime_info": (C.c_int, [_P, C.POINTER(DeviceInfo), _ERR]),
+    "eos_b200_selftest_bounded_wait": (C.c_int, [_P, C.c_int64, _ERR]),
     "eos_b200_free_cstring": (None, [_P]),
     "eos_b200_version": (C.c_char_p, []),
     "eos_b200_encoder_bind": (C.c_int, [_P, C.POINTER(EncoderDesc), C.POINTER(_P), _ERR]),
@@ -114,6 +115,7 @@ SYMBOLS = {
     "eos_b200_score_seed_device": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _ERR]),
     "eos_b200_score_topk_seeded_device": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, _P, _P, C.POINTER(Stats),
                                                     _ERR]),
+    "eos_b200_corpus_sync": (C.c_int, [_P, _P, _ERR]),
     "eos_b200_score_topk_noalloc": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _ERR]),
     "eos_b200_topk_merge_device": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _ERR]),
     "eos_b200_score_all": (C.c_int, [_P, _P, C.c_int, _P, _ERR]),

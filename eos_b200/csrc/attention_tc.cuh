@@ -14,10 +14,10 @@ struct AttnTcPlan {
     CUtensorMap tm_qkv;  // [M, 3*hidden] f16, box 64 x 128, 128B swizzle
 };
 
-// Usable when head_dim == 64, no local window, and no sequence has more than 512 keys.
+// Usable when head_dim == 64; any sequence length; window <= 0 means full attention.
 std::string attn_tc_make_plan(AttnTcPlan* plan, const __half* qkv, int m_alloc, int hidden);
-void attn_tc_launch(const AttnTcPlan& plan, const SeqLayout& lay, int batch, int hidden, int heads, __half* ctx,
-                    int* status, int sm_count, cudaStream_t stream);
+void attn_tc_launch(const AttnTcPlan& plan, const SeqLayout& lay, int batch, int tokens, int hidden, int heads,
+                    int window, __half* ctx, int* status, int sm_count, cudaStream_t stream);
 std::string attn_tc_global_init();
 
 }  // namespace eosb

@@ -81,11 +81,28 @@ cudaStream_t pick_stream(EosB200Runtime* rt, void* stream) {
     return stream != nullptr ? static_cast<cudaStream_t>(stream) : rt->stream;
 }
 
+// One warp waits on an mbarrier nobody ever arrives on, with the given limit; the wait gives up, and the kernel
+// reports it through the status word exactly as the pipelines do.
+__global__ void bounded_wait_probe_kernel(long long limit_cycles, int* status) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    const bool ok = mbar_wait_limit(smem_u32(&bar), 0, &abort_flag, limit_cycles);
+    __syncwarp();
+    if (threadIdx.x == 0 && (!ok || abort_flag != 0)) atomicExch(status, kStatusPipelineTimeout);
+}
+
 int read_status(EosB200Runtime* rt, cudaStream_t s, char** err) {
     int st = 0;
     CUDA_TRY(cudaMemcpyAsync(&st, rt->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
     CUDA_TRY(cudaStreamSynchronize(s));
     if (st == kStatusOk) return EOS_B200_OK;
+    cudaMemsetAsync(rt->d_status, 0, sizeof(int), s);  // reported once
     const char* what = "unknown device status";
     if (st == kStatusBadTokenId) what = "input_ids value out of range [0, vocab)";
     else if (st == kStatusBadTypeId) what = "token_type_ids value out of range";
@@ -160,6 +177,17 @@ void eos_b200_runtime_destroy(EosB200Runtime* rt) {
     dev_free(rt->d_status);
     if (rt->stream) cudaStreamDestroy(rt->stream);
     delete rt;
+}
+
+int eos_b200_selftest_bounded_wait(EosB200Runtime* rt, int64_t limit_cycles, char** err) {
+    if (rt == nullptr) return fail(err, "selftest_bounded_wait: null runtime");
+    if (limit_cycles <= 0 || limit_cycles > 200000000LL)
+        return fail(err, "selftest_bounded_wait: limit_cycles must be in [1, 2e8] (about 0.1 s)");
+    CUDA_TRY(cudaSetDevice(rt->device));
+    CUDA_TRY(cudaMemsetAsync(rt->d_status, 0, sizeof(int), rt->stream));
+    bounded_wait_probe_kernel<<<1, 32, 0, rt->stream>>>(limit_cycles, rt->d_status);
+    CUDA_TRY(cudaGetLastError());
+    return read_status(rt, rt->stream, err);
 }
 
 int eos_b200_runtime_info(EosB200Runtime* rt, EosB200DeviceInfo* out, char** err) {
@@ -364,7 +392,7 @@ struct EosB200Encoder {
     float *pooled = nullptr, *d_out = nullptr;
     std::vector<GemmPlan> plans;  // 4 per layer: qkv, attn-out, inter, out
     AttnTcPlan attn_plan{};
-    bool attn_tc = false;        // tensor-memory attention kernel usable (head_dim 64, no window)
+    bool attn_tc = false;        // tensor-memory attention kernel usable (head_dim 64)
     Profiler prof;
     int launches_per_forward = 0;
     // compact profile (models/default_embedding.go:461-505): role table instead of position / type tables,
@@ -392,6 +420,7 @@ void free_workspace(EosB200Encoder* e) {
     dev_free(e->lay.total_rows);
     dev_free(e->lay.cu_qtiles);
     dev_free(e->lay.qtile_info);
+    dev_free(e->lay.qtile_win);
     dev_free(e->h0);
     dev_free(e->h1);
     dev_free(e->qkv);
@@ -444,6 +473,7 @@ int ensure_workspace(EosB200Encoder* e, int batch, int tokens, char** err) {
     CUDA_TRY(dev_alloc(&e->lay.total_rows, 1));
     CUDA_TRY(dev_alloc(&e->lay.cu_qtiles, (size_t)nb + 1));
     CUDA_TRY(dev_alloc(&e->lay.qtile_info, (size_t)(m / 128 + nb + 1)));
+    CUDA_TRY(dev_alloc(&e->lay.qtile_win, (size_t)(m / 128 + nb + 1)));
     CUDA_TRY(dev_alloc(&e->h0, (size_t)m * D));
     CUDA_TRY(dev_alloc(&e->h1, (size_t)m * D));
     CUDA_TRY(dev_alloc(&e->qkv, (size_t)m * 3 * D));
@@ -462,7 +492,7 @@ int ensure_workspace(EosB200Encoder* e, int batch, int tokens, char** err) {
     e->cap_elems = ne;
     e->m_alloc = m;
     e->attn_tc = false;
-    if (e->hidden / e->heads == 64 && e->window <= 0 && std::getenv("EOS_B200_LEGACY_ATTENTION") == nullptr) {
+    if (e->hidden / e->heads == 64 && std::getenv("EOS_B200_LEGACY_ATTENTION") == nullptr) {
         std::string ae = attn_tc_make_plan(&e->attn_plan, e->qkv, m, D);
         if (!ae.empty()) return fail(err, "attention plan: " + ae);
         e->attn_tc = true;
@@ -532,7 +562,7 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
     const int cls = e->pooling == EOS_B200_POOL_CLS ? 1 : 0;
     int launches = 0;
     Profiler& pf = e->prof;
-    pf.launch(kClsLayout, s, [&] { launch_seq_layout(d_mask, batch, tokens, cls, e->lay, s); });
+    pf.launch(kClsLayout, s, [&] { launch_seq_layout(d_mask, batch, tokens, cls, e->window, e->lay, s); });
     launches += 4;
     pf.launch(kClsEmbed, s, [&] {
         if (e->compact)
@@ -547,8 +577,9 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
         LayerW& w = e->lw[l];
         pf.launch(kClsGemmKind0 + 0, s, [&] { gemm_launch(e->plans[(size_t)l * 4 + 0], s); });
         pf.launch(kClsAttention, s, [&] {
-            if (e->attn_tc && tokens <= 512)
-                attn_tc_launch(e->attn_plan, e->lay, batch, D, e->heads, e->ctx, rt->d_status, rt->sm_count, s);
+            if (e->attn_tc)
+                attn_tc_launch(e->attn_plan, e->lay, batch, tokens, D, e->heads, e->window, e->ctx, rt->d_status,
+                               rt->sm_count, s);
             else
                 launch_attention(e->qkv, e->lay, batch, tokens, D, e->heads, e->window, e->ctx, s);
         });
@@ -1326,7 +1357,7 @@ int enqueue_scan_passes(EosB200Corpus* c, int64_t n_docs, int q_count, int k, in
             a.grid = c->grid;
             a.shared_tau = (use_shared_tau && j == 1) ? c->shared_tau + (size_t)g0 + (size_t)t0 * 8 : nullptr;
             a.all_scores = nullptr;
-            a.status = nullptr;
+            a.status = qz->rt->d_status;
             a.all_stride = 0;
             if (profile) c->prof.launch(kClsScan, s, [&] { launch_tq_scan(a, s); });
             else launch_tq_scan(a, s);
@@ -1679,6 +1710,9 @@ int eos_b200_score_topk_device(EosB200Corpus* c, const float* d_queries, int q_c
                                int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream, EosB200Stats* stats,
                                char** err) {
     if (c == nullptr || d_queries == nullptr) return fail(err, "score_topk: null argument");
+    if ((d_ids == nullptr) != (d_scores == nullptr))
+        return fail(err, "score_topk: d_ids and d_scores must be given together or both be null");
+    if (d_ids == nullptr && d_keys == nullptr) return fail(err, "score_topk: no output requested");
     per_pass = resolve_per_pass(per_pass, q_count);
     std::string m = check_score_args(c, q_count, k, per_pass);
     if (!m.empty()) return fail(err, m);
@@ -1728,6 +1762,9 @@ int eos_b200_score_topk_seeded_device(EosB200Corpus* c, const float* d_queries, 
                                       int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream,
                                       EosB200Stats* stats, char** err) {
     if (c == nullptr || d_queries == nullptr || d_tau == nullptr) return fail(err, "score_topk_seeded: null argument");
+    if ((d_ids == nullptr) != (d_scores == nullptr))
+        return fail(err, "score_topk_seeded: d_ids and d_scores must be given together or both be null");
+    if (d_ids == nullptr && d_keys == nullptr) return fail(err, "score_topk_seeded: no output requested");
     const int per_pass = q_count <= kTqTcQueries ? kTqTcQueries : kTqTc256Queries;
     std::string m = check_score_args(c, q_count, k, per_pass);
     if (!m.empty()) return fail(err, m);
@@ -1770,13 +1807,14 @@ int eos_b200_score_topk(EosB200Corpus* c, const float* h_queries, int q_count, i
     if (rc != EOS_B200_OK) return rc;
     cudaStream_t s = rt->stream;
     CUDA_TRY(cudaEventRecord(rt->ev0, s));
+    CUDA_TRY(cudaMemsetAsync(rt->d_status, 0, sizeof(int), s));
     CUDA_TRY(cudaMemcpyAsync(c->d_queries, h_queries, (size_t)q_count * c->qz->dim * 4, cudaMemcpyHostToDevice, s));
     const int launches = enqueue_score(c, c->d_queries, q_count, k, per_pass, c->d_ids, c->d_scores, nullptr, s);
     CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaMemcpyAsync(h_ids, c->d_ids, (size_t)q_count * k * 8, cudaMemcpyDeviceToHost, s));
     CUDA_TRY(cudaMemcpyAsync(h_scores, c->d_scores, (size_t)q_count * k * 4, cudaMemcpyDeviceToHost, s));
     CUDA_TRY(cudaEventRecord(rt->ev1, s));
-    CUDA_TRY(cudaStreamSynchronize(s));
+    rc = read_status(rt, s, err);   // synchronises; a bounded wait that ran out inside a kernel is an error, not a result
     if (stats != nullptr) {
         std::memset(stats, 0, sizeof(*stats));
         stats->kernel_launches = launches;
@@ -1784,7 +1822,13 @@ int eos_b200_score_topk(EosB200Corpus* c, const float* h_queries, int q_count, i
         stats->downloaded_bytes = (int64_t)q_count * k * 12;
         cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
     }
-    return EOS_B200_OK;
+    return rc;
+}
+
+int eos_b200_corpus_sync(EosB200Corpus* c, void* stream, char** err) {
+    if (c == nullptr) return fail(err, "corpus_sync: null corpus");
+    CUDA_TRY(cudaSetDevice(c->qz->rt->device));
+    return read_status(c->qz->rt, pick_stream(c->qz->rt, stream), err);
 }
 
 }  // extern "C"
@@ -1873,7 +1917,7 @@ int eos_b200_score_topk_noalloc(EosB200Corpus* c, const float* d_queries, int q_
         a.cand_count = cand_count + (size_t)t0 * 8 * c->grid;
         a.grid = c->grid;
         a.all_scores = nullptr;
-            a.status = nullptr;
+        a.status = qz->rt->d_status;
         a.all_stride = 0;
         launch_tq_scan(a, s);
     }
@@ -1907,7 +1951,9 @@ int eos_b200_score_all(EosB200Corpus* c, const float* h_queries, int q_count, fl
     float* d_all = nullptr;
     CUDA_TRY(dev_alloc(&d_all, (size_t)q_pad * c->n));
     cudaStream_t s = rt->stream;
-    cudaError_t e = cudaMemcpyAsync(c->d_queries, h_queries, (size_t)q_count * c->qz->dim * 4, cudaMemcpyHostToDevice, s);
+    cudaError_t e = cudaMemsetAsync(rt->d_status, 0, sizeof(int), s);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(c->d_queries, h_queries, (size_t)q_count * c->qz->dim * 4, cudaMemcpyHostToDevice, s);
     launch_tq_prepare(c->d_queries, q_count, q_pad, c->qz->spec(), c->bfrag, nullptr, nullptr, s);
     const int ksteps = tq_ksteps(c->qz->dim);
     for (int t = 0; t < q_pad / 8; ++t) {
@@ -1929,6 +1975,7 @@ int eos_b200_score_all(EosB200Corpus* c, const float* h_queries, int q_count, fl
         a.grid = c->grid;
         a.all_scores = d_all + (size_t)t * 8 * c->n;
         a.all_stride = c->n;
+        a.status = rt->d_status;
         launch_tq_scan(a, s);
     }
     if (e == cudaSuccess) e = cudaGetLastError();
@@ -1939,7 +1986,7 @@ int eos_b200_score_all(EosB200Corpus* c, const float* h_queries, int q_count, fl
         cudaGetLastError();
         return fail(err, std::string("score_all: ") + cudaGetErrorString(e));
     }
-    return EOS_B200_OK;
+    return read_status(rt, s, err);
 }
 
 int eos_b200_parent_topk(EosB200Corpus* c, const int32_t* h_parent_of_child, int parents, const float* h_queries,
@@ -1977,6 +2024,7 @@ int eos_b200_parent_topk(EosB200Corpus* c, const int32_t* h_parent_of_child, int
     int64_t* d_ids = nullptr;
     cudaStream_t s = rt->stream;
     cudaError_t e = dev_alloc(&d_order, (size_t)n);
+    if (e == cudaSuccess) e = cudaMemsetAsync(rt->d_status, 0, sizeof(int), s);
     if (e == cudaSuccess) e = dev_alloc(&d_offsets, (size_t)parents + 1);
     if (e == cudaSuccess) e = dev_alloc(&d_all, (size_t)32 * n);
     if (e == cudaSuccess) e = dev_alloc(&d_agg, (size_t)query_group * parents);
@@ -2014,6 +2062,7 @@ int eos_b200_parent_topk(EosB200Corpus* c, const int32_t* h_parent_of_child, int
             a.grid = c->grid;
             a.all_scores = d_all;
             a.all_stride = n;
+            a.status = rt->d_status;
             launch_tq_scan(a, s);
             launches++;
             const int rows_here = (q_count - r0) < 32 ? (q_count - r0) : 32;
@@ -2050,7 +2099,7 @@ int eos_b200_parent_topk(EosB200Corpus* c, const int32_t* h_parent_of_child, int
         cudaGetLastError();
         return fail(err, std::string("parent_topk: ") + cudaGetErrorString(e));
     }
-    return EOS_B200_OK;
+    return read_status(rt, s, err);
 }
 
 int eos_b200_synth_gaussian_device(EosB200Runtime* rt, uint64_t seed, int64_t row_offset, int64_t n, int dim,

@@ -52,7 +52,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // the elapsed cycle count.  Returns false (and raises the abort flag) when the limit is hit,
 // so that no role of a warp-specialised kernel can spin forever.
 constexpr long long kWaitLimitCycles = 4000000000LL;  // about two seconds of SM clock
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                long long limit_cycles) {
     if (mbar_try_wait(bar, parity)) return true;
     long long start = clock64();
     uint32_t polls = 0;
@@ -60,12 +61,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((++polls & 0xffu) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - start > kWaitLimitCycles) {
+            if (clock64() - start > limit_cycles) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_limit(bar, parity, abort_flag, kWaitLimitCycles);
 }
 
 // ---------------------------------------------------------------- fences
@@ -224,6 +228,18 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// 32 lanes x 16 columns and 32 lanes x 1 column written from registers (same addressing as tmem_st_32x32).
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x1(uint32_t taddr, uint32_t r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(r) : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // One MMA over a CTA pair (cta_group::2), issued by one thread of the pair's leader CTA: M = 256
 // (128 rows from each CTA's A tile), B = the two CTAs' tiles side by side along N; each CTA's
@@ -291,6 +307,19 @@ __device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
                    "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
                  :
                  : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait32(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]),
+                   "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
+                   "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait1(uint32_t (&r)[1]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(r[0]) : : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 

@@ -76,8 +76,8 @@ __global__ void seq_scan_kernel(const int* row_count, int batch, int unit, int* 
 }
 
 __global__ void seq_fill_kernel(const int32_t* __restrict__ mask, int tokens, int cls_pooling, const int* cu_rows,
-                                const int* key_count, const int* cu_qtiles, int* row_src, int* cls_row,
-                                int4* qtile_info) {
+                                const int* key_count, const int* cu_qtiles, int window, int* row_src, int* cls_row,
+                                int4* qtile_info, int4* qtile_win) {
     const int b = blockIdx.x;
     const int32_t* m = mask + (size_t)b * tokens;
     const int row0 = cu_rows[b];
@@ -107,12 +107,6 @@ __global__ void seq_fill_kernel(const int32_t* __restrict__ mask, int tokens, in
         if (threadIdx.x == 0) carry = warp_off[32];
         __syncthreads();
     }
-    {
-        const int nrows = cu_rows[b + 1] - row0;
-        const int qt0 = cu_qtiles[b];
-        for (int q = threadIdx.x; q < cu_qtiles[b + 1] - qt0; q += blockDim.x)
-            qtile_info[qt0 + q] = make_int4(row0, nrows, key_count[b], q * 128);
-    }
     if (threadIdx.x == 0) {
         if (cls_pooling && m[0] == 0) {
             // token 0 is masked: it is still a query (the reference computes every row and CLS
@@ -121,6 +115,41 @@ __global__ void seq_fill_kernel(const int32_t* __restrict__ mask, int tokens, in
             cls_row[b] = row0 + key_count[b];
         } else {
             cls_row[b] = row0;
+        }
+    }
+    __syncthreads();  // row_src of this sequence is complete (written by this block only)
+    {
+        const int nrows = cu_rows[b + 1] - row0;
+        const int nkeys = key_count[b];
+        const int ntiles = (nkeys + 127) >> 7;
+        const int qt0 = cu_qtiles[b];
+        for (int q = threadIdx.x; q < cu_qtiles[b + 1] - qt0; q += blockDim.x) {
+            qtile_info[qt0 + q] = make_int4(row0, nrows, nkeys, q * 128);
+            // key tiles (of 128 keys) the tile's queries can see, and among them the ones every query sees in
+            // full; positions grow along the packed keys, so both are contiguous ranges
+            int kb = 0, ke = ntiles, fb = 0, fe = ntiles;
+            if (window > 0 && nkeys > 0) {
+                const int q0 = q * 128;
+                const int qlast = min(q0 + 127, nrows - 1);
+                int qlo = row_src[row0 + q0], qhi = row_src[row0 + qlast];
+                const bool has_cls_row = nrows > nkeys && qlast == nrows - 1;  // query-only row at position 0
+                if (has_cls_row) {
+                    qlo = b * tokens;
+                    qhi = q0 < nkeys ? row_src[row0 + nkeys - 1] : b * tokens;
+                }
+                auto first_pos = [&](int t) { return row_src[row0 + t * 128]; };
+                auto last_pos = [&](int t) { return row_src[row0 + min(t * 128 + 127, nkeys - 1)]; };
+                while (kb < ke && 2 * (qlo - last_pos(kb)) >= window) ++kb;
+                while (ke > kb && 2 * (first_pos(ke - 1) - qhi) >= window) --ke;
+                auto full = [&](int t) {
+                    return !has_cls_row && 2 * (qhi - first_pos(t)) < window && 2 * (last_pos(t) - qlo) < window;
+                };
+                fb = kb;
+                while (fb < ke && !full(fb)) ++fb;
+                fe = fb;
+                while (fe < ke && full(fe)) ++fe;
+            }
+            qtile_win[qt0 + q] = make_int4(kb, ke, fb, fe);
         }
     }
 }
@@ -983,13 +1012,13 @@ void dispatch_chunks(int dim, F&& f) {
 
 }  // namespace
 
-void launch_seq_layout(const int32_t* mask, int batch, int tokens, int cls_pooling, const SeqLayout& lay,
+void launch_seq_layout(const int32_t* mask, int batch, int tokens, int cls_pooling, int window, const SeqLayout& lay,
                        cudaStream_t stream) {
     seq_count_kernel<<<batch, 256, 0, stream>>>(mask, tokens, cls_pooling, lay.key_count, lay.row_count);
     seq_scan_kernel<<<1, 1024, 0, stream>>>(lay.row_count, batch, 1, lay.cu_rows, lay.total_rows);
     seq_scan_kernel<<<1, 1024, 0, stream>>>(lay.row_count, batch, 128, lay.cu_qtiles, nullptr);
     seq_fill_kernel<<<batch, 256, 0, stream>>>(mask, tokens, cls_pooling, lay.cu_rows, lay.key_count, lay.cu_qtiles,
-                                               lay.row_src, lay.cls_row, lay.qtile_info);
+                                               window, lay.row_src, lay.cls_row, lay.qtile_info, lay.qtile_win);
 }
 
 void launch_embed_ln(const int32_t* ids, const int32_t* types, const SeqLayout& lay, int tokens, const __half* tok,

@@ -17,9 +17,11 @@ struct SeqLayout {
     int* total_rows;  // [1]
     int* cu_qtiles;   // [B+1] exclusive prefix sum of ceil(row_count / 128): 128-query tiles per sequence
     int4* qtile_info; // [sum of q-tiles] per 128-query tile: {first row of the sequence, its rows, its keys, tile's first query}
+    int4* qtile_win;  // [sum of q-tiles] key tiles of 128 the tile attends to: {first, end, first fully visible, end of those}
 };
 
-void launch_seq_layout(const int32_t* mask, int batch, int tokens, int cls_pooling, const SeqLayout& lay,
+// window: local attention window of the model (<= 0: none); it only shapes qtile_win.
+void launch_seq_layout(const int32_t* mask, int batch, int tokens, int cls_pooling, int window, const SeqLayout& lay,
                        cudaStream_t stream);
 
 // hidden[r,:] = LayerNorm(tok[id] + pos[t] + typ[type]) * gamma + beta for every packed row.

@@ -120,6 +120,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + C::kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + C::kOffMisc + 4);
+    // set by an epilogue warp whose wait ran out, read by all epilogue warps right after their next common
+    // barrier: they leave the tile loop together, so the named barrier is never left waiting for warps that have gone
+    volatile int* epi_stop = reinterpret_cast<volatile int*>(sm + C::kOffMisc + 8);
     float2* scale_bias = reinterpret_cast<float2*>(sm + C::kOffScaleBias);
 
     int m_rows = p.m_alloc;
@@ -140,6 +143,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
+        *epi_stop = 0;
         for (int s = 0; s < kStagesAB; ++s) {
             mbar_init(full_ab(s), 1);
             mbar_init(empty_ab(s), 1 + C::kDequantWarps);  // MMA commit (+ dequantiser warps)
@@ -407,10 +411,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             };
             if (residual) residual_fetch(0);
             named_bar_sync(1, kEpilogueWarps * 32);
+            if (*epi_stop != 0) break;
 #ifdef EOSB_GEMM_TIMING
             if (tm__) GMARK(4);
 #endif
-            if (!mbar_wait(acc_full(ab), aph, abort_flag)) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(acc_full(ab), aph, abort_flag))) {
+                *epi_stop = 1;
+                continue;   // to the next common barrier, where every epilogue warp sees the flag
+            }
             tc_fence_after();
 #ifdef EOSB_GEMM_TIMING
             if (tm__) GMARK(4);

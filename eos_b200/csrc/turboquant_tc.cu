@@ -106,6 +106,9 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
     auto acc_empty = [&](int s) { return bar0 + 8u * (2 * kStQ + 2 * kStD + 2 + s); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
+    // set by an epilogue warp whose wait ran out, read by all epilogue warps right after their next common
+    // barrier: they leave the tile loop together, so the named barrier is never left waiting for warps that have gone
+    volatile int* epi_stop = reinterpret_cast<volatile int*>(sm + kOffMisc + 8);
 
     const int chunks = (a.dim + kTqChunkCoords - 1) / kTqChunkCoords;
     const int num_kb = chunks * 2;
@@ -114,6 +117,7 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
+        *epi_stop = 0;
         for (int s = 0; s < kStQ; ++s) {
             mbar_init(full_q(s), 1);
             mbar_init(empty_q(s), 1);
@@ -321,6 +325,7 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
             if (etid < TD) nrm[etid] = norm_next;
             norm_next = fetch_norm(tile + gridDim.x);
             named_bar_sync(1, kEpiWarps * 32);
+            if (*epi_stop != 0) break;
             // thresholds other CTAs published; lists that the coming tile could overflow are cut to their k best
             if (q_live) raise_tau(shared_tau[qrow]);
             unsigned need = __ballot_sync(0xffffffffu, cnt > kCutAbove);
@@ -341,7 +346,10 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
                     atomicMax(const_cast<u64*>(a.shared_tau) + qrow, kth);
                 }
             }
-            if (!mbar_wait(acc_full(ab), aph, abort_flag)) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(acc_full(ab), aph, abort_flag))) {
+                *epi_stop = 1;
+                continue;   // to the next common barrier, where every epilogue warp sees the flag
+            }
             tc_fence_after();
 
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * TD + epart * (TD / 2);

@@ -76,6 +76,9 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc256_kernel(const __gri
     auto acc_empty = [&](int s) { return bar0 + 8u * (2 * kStQ + 2 * kStD + 2 + s); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
+    // set by an epilogue warp whose wait ran out, read by all epilogue warps right after their next common
+    // barrier: they leave the tile loop together, so no named barrier is left waiting for warps that have gone
+    volatile int* epi_stop = reinterpret_cast<volatile int*>(sm + kOffMisc + 8);
 
     const int chunks = (a.dim + kTqChunkCoords - 1) / kTqChunkCoords;
     const int num_kb = chunks * 2;
@@ -84,6 +87,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc256_kernel(const __gri
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
+        *epi_stop = 0;
         for (int s = 0; s < kStQ; ++s) {
             mbar_init(full_q(s), 1);
             mbar_init(empty_q(s), 1);
@@ -237,6 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc256_kernel(const __gri
         };
         float norm_next = fetch_norm(blockIdx.x);
         uint32_t t = 0;
+        bool stopped = false;
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
             const uint32_t ab = t & 1u;
             const uint32_t aph = (t >> 1) & 1u;
@@ -244,6 +249,10 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc256_kernel(const __gri
             norm_next = fetch_norm(tile + gridDim.x);
             // every append of the previous tile is done (and the initial values above are written)
             named_bar_sync(1, kEpiWarps * 32);
+            if (*epi_stop != 0) {
+                stopped = true;
+                break;
+            }
             // this thread's query: thresholds other CTAs published; a list the coming tile could overflow is cut
             if (q_live) {
                 const u64 pub = shared_tau[etid];
@@ -275,7 +284,10 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc256_kernel(const __gri
                 }
             }
             named_bar_sync(2, kEpiWarps * 32);  // thresholds and counters of all 256 queries are in place
-            if (!mbar_wait(acc_full(ab), aph, abort_flag)) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(acc_full(ab), aph, abort_flag))) {
+                *epi_stop = 1;
+                continue;   // to the next common barrier, where every epilogue warp sees the flag
+            }
             tc_fence_after();
 
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * TQ + epart * (TQ / 2);
@@ -338,7 +350,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc256_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty(ab));
         }
-        named_bar_sync(1, kEpiWarps * 32);
+        if (!stopped) named_bar_sync(1, kEpiWarps * 32);
         a.cand_count[(size_t)etid * n_segs + blockIdx.x] = cnt_s[etid];
     }
 

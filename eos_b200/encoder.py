@@ -83,6 +83,10 @@ class Runtime:
         return {"device": out.device, "cc": (out.cc_major, out.cc_minor), "sm_count": out.sm_count,
                 "total_memory_bytes": out.total_memory_bytes, "name": out.name.decode()}
 
+    def selftest_bounded_wait(self, limit_cycles: int = 1_000_000) -> None:
+        """Runs the bounded-wait self-test: raises EosB200DeviceStatusError when the wait ran out as designed."""
+        _lib.call("eos_b200_selftest_bounded_wait", self.handle, int(limit_cycles))
+
     def close(self) -> None:
         if self.handle:
             for child in list(self._children):

@@ -203,6 +203,11 @@ class Corpus:
         _lib.call("eos_b200_score_topk_noalloc", self.handle, d_queries, int(q_count), int(k), int(queries_per_pass),
                   d_ids, d_scores, stream)
 
+    def sync(self, stream: Optional[int] = None) -> None:
+        """Waits for the stream of the *_device / _noalloc calls; raises EosB200DeviceStatusError if one of their
+        kernels gave up on a bounded wait (the results are then incomplete)."""
+        _lib.call("eos_b200_corpus_sync", self.handle, stream)
+
     def profile_begin(self, max_launches: int) -> None:
         _lib.call("eos_b200_corpus_profile_begin", self.handle, int(max_launches))
 

@@ -71,6 +71,12 @@ typedef struct {
 EOS_B200_API int eos_b200_runtime_create(int device, EosB200Runtime** out, char** err);
 EOS_B200_API void eos_b200_runtime_destroy(EosB200Runtime* rt);
 EOS_B200_API int eos_b200_runtime_info(EosB200Runtime* rt, EosB200DeviceInfo* out, char** err);
+/* No counterpart in Eos.  Every wait inside this library's pipelined kernels is bounded: when it runs out the
+ * kernel leaves, sets the runtime's device status word, and the host call that reads it returns
+ * EOS_B200_DEVICE_STATUS ("pipeline timeout") instead of a result.  This self-test exercises exactly that path
+ * without touching any data: one warp waits, with a limit of limit_cycles SM clocks (at most 2e8, about 0.1 s),
+ * on a barrier nothing ever completes.  Expected return: EOS_B200_DEVICE_STATUS; the runtime stays usable. */
+EOS_B200_API int eos_b200_selftest_bounded_wait(EosB200Runtime* rt, int64_t limit_cycles, char** err);
 /* eosCudaFreeCString, native_linux.go:1378-1382 */
 EOS_B200_API void eos_b200_free_cstring(char* s);
 EOS_B200_API const char* eos_b200_version(void);
@@ -267,8 +273,10 @@ EOS_B200_API void eos_b200_corpus_destroy(EosB200Corpus* corpus);
 EOS_B200_API int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* corpus);
 
 /* Replaces PrepareQuery + topTurboQuantRetrievalScoresWithStats per query
- * (runtime/retrieval_turboquant.go:1324-1325, 1853-1887): exact top-k of
- * norm * <R q, centroids[codes]> over the corpus, for q_count queries [q_count, dim] fp32.
+ * (runtime/retrieval_turboquant.go:1324-1325, 1853-1887) for the Hadamard/MSE stage of the quantiser only:
+ * exact top-k of norm * <R q, centroids[codes]> over the corpus, for q_count queries [q_count, dim] fp32.
+ * The reference's IPQuantizer adds a QJL sign stage (Signs, ResNorm) on top of the MSE codes; those two
+ * operands are not accepted here, so for bit widths where the reference uses that stage its rankings differ.
  * queries_per_pass selects how many queries share one pass over the codes, and with it the kernel:
  *   0        automatic: 8 up to 16 queries, 128 up to 128 queries, 256 above;
  *   8        streaming scan (codes expanded in registers, mma.sync): the choice for a few queries;
@@ -282,7 +290,10 @@ EOS_B200_API int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* corpus);
 EOS_B200_API int eos_b200_score_topk(EosB200Corpus* corpus, const float* h_queries, int q_count, int k, int queries_per_pass,
                         int64_t* h_ids, float* h_scores, EosB200Stats* stats, char** err);
 /* Device-resident variant, enqueued on `stream`.  d_keys (nullable, [q_count, k] uint64) receives
- * the sortable (score, id) keys that eos_b200_topk_merge_device consumes after an all-gather. */
+ * the sortable (score, id) keys that eos_b200_topk_merge_device consumes after an all-gather.
+ * d_ids and d_scores are given together or are both null (keys only); at least one output is required.
+ * The call returns after enqueueing; eos_b200_corpus_sync waits for the stream and reports a kernel-side
+ * timeout. */
 EOS_B200_API int eos_b200_score_topk_device(EosB200Corpus* corpus, const float* d_queries, int q_count, int k,
                                int queries_per_pass, int64_t* d_ids, float* d_scores, uint64_t* d_keys, void* stream,
                                EosB200Stats* stats, char** err);
@@ -298,6 +309,9 @@ EOS_B200_API int eos_b200_score_seed_device(EosB200Corpus* corpus, const float* 
 EOS_B200_API int eos_b200_score_topk_seeded_device(EosB200Corpus* corpus, const float* d_queries, int q_count, int k,
                                       const uint64_t* d_tau, int64_t* d_ids, float* d_scores, uint64_t* d_keys,
                                       void* stream, EosB200Stats* stats, char** err);
+/* Waits for `stream` (null: the runtime's stream) and returns EOS_B200_DEVICE_STATUS if a kernel enqueued by
+ * one of the *_device / _noalloc scoring calls gave up on a bounded wait; counterpart of eos_b200_encoder_sync. */
+EOS_B200_API int eos_b200_corpus_sync(EosB200Corpus* corpus, void* stream, char** err);
 /* (eos_b200_score_topk_noalloc below takes queries_per_pass in {8, 16, 32} only.) */
 /* No counterpart in Eos: a scoring call for hosts that must not allocate device memory while they
  * serve queries -- for example a caller that holds the GPU inside a pre-sized memory arena, runs

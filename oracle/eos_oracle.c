@@ -13,11 +13,15 @@
  *     runtime/testdata/pretrained_bert_golden/golden.json (max_abs <= 2e-3,
  *     min_cosine >= 0.9999, runtime/pretrained_bert_golden_parity_test.go:99-103) and
  *     against the hand-computed expectations in runtime/backend (tensor_ops_test.go, bert_encoder_layer_ops_test.go).
- *   - TurboQuant functions: PARITY UNPINNED.  The arithmetic lives in the third-party
- *     Go module m31labs.dev/turboquant v0.2.1 (go.mod:9) whose source is not part of
- *     the Eos tree; what is restated here is the Hadamard/MSE variant exactly as Eos's
- *     own CUDA restatement spells it (runtime/backends/cuda/native_linux.go:1812-2003),
- *     with the rotation spec (perm, signs, centroids, boundaries) supplied by the caller.
+ *   - TurboQuant functions: the arithmetic lives in the third-party Go module
+ *     m31labs.dev/turboquant v0.2.1 (go.mod:9) whose source is not part of the Eos tree; what is
+ *     restated here is the Hadamard/MSE variant exactly as Eos's own CUDA restatement spells it
+ *     (runtime/backends/cuda/native_linux.go:1812-2003), with the rotation spec (perm, signs,
+ *     centroids, boundaries) supplied by the caller.  Encode (rotation + code assignment + 8-bit
+ *     norm code) and decode are PINNED bit for bit against that reference code compiled for the
+ *     host (oracle/build_ref.py -> oracle/_ref, tests/test_oracle_pins.py).  UNPINNED: the seed ->
+ *     spec generator and the scoring of the module's IP variant (QJL signs, ResNorm), which the
+ *     Eos tree does not contain.
  *
  * Build: see oracle/Makefile (gcc -O2 -ffp-contract=off, no -march flags, so that float
  * expressions are evaluated without fused multiply-add exactly as written).
@@ -649,6 +653,30 @@ EOS_ORACLE_API void eos_oracle_tq_encode(const float *x, int64_t n, int dim, int
         norms[v] = norm;
     }
     free(rot);
+}
+
+/* The reference's encode stores the norm as an 8-bit code on a log scale:
+ * code = round(255 * (ln(norm) + 16) / 32) clamped to [0, 255]; 0 for norm <= 0 or NaN, 255 for +inf;
+ * value = exp(-16 + 32 * code / 255).  native_linux.go:1879-1904. */
+EOS_ORACLE_API void eos_oracle_tq_norm_code(const float *norms, int64_t n, uint8_t *codes) {
+    for (int64_t i = 0; i < n; i++) {
+        float norm = norms[i];
+        int code;
+        if (norm <= 0.0f || isnan(norm)) {
+            code = 0;
+        } else if (isinf(norm)) {
+            code = 255;
+        } else {
+            float t = (logf(norm) + 16.0f) / 32.0f;
+            if (t <= 0.0f) code = 0;
+            else if (t >= 1.0f) code = 255;
+            else code = (int)roundf(t * 255.0f);
+        }
+        codes[i] = (uint8_t)code;
+    }
+}
+EOS_ORACLE_API void eos_oracle_tq_norm_value(const uint8_t *codes, int64_t n, float *norms) {
+    for (int64_t i = 0; i < n; i++) norms[i] = expf(-16.0f + ((float)codes[i] / 255.0f) * 32.0f);
 }
 
 EOS_ORACLE_API void eos_oracle_tq_unpack(const uint8_t *codes, int dim, int bits, int32_t *idx) {

@@ -272,6 +272,22 @@ def tq_decode(codes, norms, dim, bits, perm, signs1, signs2, centroids):
     return out
 
 
+def tq_norm_code(norms):
+    """f32 norms -> the reference's 8-bit log-scale norm codes (native_linux.go:1879-1893)."""
+    a = _f32(norms).reshape(-1)
+    out = np.empty(a.size, dtype=np.uint8)
+    lib().eos_oracle_tq_norm_code(_p(a), C.c_int64(a.size), _p(out))
+    return out
+
+
+def tq_norm_value(codes):
+    """8-bit norm codes -> f32 norms (native_linux.go:1895-1904)."""
+    c = np.ascontiguousarray(codes, dtype=np.uint8).reshape(-1)
+    out = np.empty(c.size, dtype=np.float32)
+    lib().eos_oracle_tq_norm_value(_p(c), C.c_int64(c.size), _p(out))
+    return out
+
+
 def tq_prepare_query(q, perm, signs1, signs2):
     a = _f32(q)
     out = np.empty_like(a)

@@ -73,6 +73,10 @@ def _check_topk(ids, scores, ref_scores, k, id_base, tol):
     got = ids[:kk] - id_base
     assert len(set(got.tolist())) == kk and got.min() >= 0 and got.max() < n
     assert np.abs(scores[:kk] - ref_scores[got]).max() <= tol        # reported score = that row's score
+    # per score, not only against the score scale: 1e-3 relative for every returned score that is not itself tiny
+    big = np.abs(ref_scores[got]) >= 100 * tol                       # >= a tenth of the scale
+    if big.any():
+        assert (np.abs(scores[:kk] - ref_scores[got])[big] / np.abs(ref_scores[got])[big]).max() <= 1e-3
     assert np.abs(scores[:kk] - ref_top).max() <= tol                # rank-wise agreement with the oracle
     assert (np.diff(scores[:kk]) <= 0).all()                         # descending
     same = np.diff(scores[:kk]) == 0
@@ -335,6 +339,15 @@ def test_automatic_queries_per_pass_and_argument_errors(rt):
     d_sc = torch.empty((8, 20), dtype=torch.float32, device="cuda")
     with pytest.raises(Exception, match="queries_per_pass"):
         corpus.score_topk_noalloc(dq.data_ptr(), 8, 20, 128, d_ids.data_ptr(), d_sc.data_ptr())
+    # ids and scores come together or not at all (a lone pointer would make the merge store through null)
+    with pytest.raises(Exception, match="together"):
+        corpus.score_topk_device(dq.data_ptr(), 8, 20, 8, d_ids.data_ptr(), None)
+    with pytest.raises(Exception, match="no output"):
+        corpus.score_topk_device(dq.data_ptr(), 8, 20, 8, None, None)
+    keys = torch.zeros((8, 20), dtype=torch.int64, device="cuda")
+    corpus.score_topk_device(dq.data_ptr(), 8, 20, 8, None, None, keys.data_ptr())   # keys only is fine
+    corpus.sync()
+    assert int((keys != 0).sum()) == 8 * 20
     corpus.close()
     qz.close()
 

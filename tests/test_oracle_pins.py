@@ -209,3 +209,62 @@ def test_compact_path_rows_match_reference_expectations():
     assert np.allclose(r, [[1, 0], [-0.84147096, 0.5403023]], atol=1e-7)
     r3 = O.rope_rows(np.array([[[1, 0], [0, 1]], [[1, 0], [0, 1]]], np.float32))
     assert np.allclose(r3, np.tile([[1, 0], [-0.84147096, 0.5403023]], (2, 1, 1)), atol=1e-7)
+
+
+# ---- TurboQuant: the restatement against the reference's own device code compiled for the host ---------------------
+def _turboq_ref():
+    """oracle/_ref/libturboq_ref.so: the reference's turboQKernelSource string
+    (runtime/backends/cuda/native_linux.go:1812-2003) compiled as C++ by oracle/build_ref.py."""
+    import ctypes as C
+    from oracle import build_ref
+    path = build_ref.build()
+    if path is None:
+        pytest.skip("neither the reference tree nor a prebuilt oracle/_ref is present")
+    return C.CDLL(path)
+
+
+@pytest.mark.parametrize("dim,bits,n", [(768, 4, 400), (128, 2, 300), (96, 4, 65), (384, 4, 33), (40, 8, 20)])
+def test_tq_encode_decode_match_the_reference_device_code(dim, bits, n):
+    """Codes of eos_oracle_tq_encode == codes of manta_turboq_encode, and the decoded vectors agree, for a caller
+    supplied rotation spec (the seed -> spec generator of the third-party module stays unpinned).  dim 96 / 40:
+    several Hadamard blocks (64 + 32, 32 + 8)."""
+    import ctypes as C
+    import eos_b200
+    ref = _turboq_ref()
+    spec = eos_b200.make_rotation_spec(dim, bits, seed=402)
+    rng = np.random.default_rng(dim * 7 + bits)
+    x = rng.standard_normal((n, dim)).astype(np.float32)
+    x /= np.linalg.norm(x, axis=1, keepdims=True).astype(np.float32)
+    x *= np.linspace(0.25, 4.0, n, dtype=np.float32)[:, None]
+    x[n // 3] = 0   # zero vector: scale stays 1, codes of the all-zero rotation
+    levels = 1 << bits
+
+    def fp(a):
+        return np.ascontiguousarray(a, np.float32).ctypes.data_as(C.c_void_p)
+
+    coords = np.zeros((n, dim), np.float32)
+    norm_codes = np.zeros(n, np.float32)
+    permf = spec.perm.astype(np.float32)
+    ref.ref_turboq_encode(fp(x), fp(coords), fp(norm_codes), fp(permf), fp(spec.signs1), fp(spec.signs2),
+                          fp(spec.centroids), fp(spec.boundaries), C.c_int(n), C.c_int(dim), C.c_int(levels))
+    codes, norms = O.tq_encode(x, bits, spec.perm, spec.signs1, spec.signs2, spec.boundaries)
+    per_byte = 8 // bits
+    idx = np.zeros((n, dim), np.int32)
+    for c in range(dim):
+        idx[:, c] = (codes[:, c // per_byte] >> ((c % per_byte) * bits)) & (levels - 1)
+    assert np.array_equal(idx, coords.astype(np.int32))          # bit-exact code assignment
+    # the reference stores the norm as an 8-bit log code; the restatement keeps the f32 norm (stated deviation):
+    # the f32 norm must map to exactly the reference's code
+    ref.ref_turboq_norm_code.restype = C.c_int
+    ref.ref_turboq_norm_value.restype = C.c_float
+    got_codes = np.array([ref.ref_turboq_norm_code(C.c_float(float(v))) for v in norms], np.float32)
+    assert np.array_equal(got_codes, norm_codes)
+    assert np.array_equal(O.tq_norm_code(norms), norm_codes.astype(np.uint8))
+    # decode: same centroids -> signs2 -> FWHT -> signs1, times the norm the reference would use (its 8-bit one)
+    out_ref = np.zeros((n, dim), np.float32)
+    ref.ref_turboq_decode(fp(coords), fp(norm_codes), fp(out_ref), fp(permf), fp(spec.signs1), fp(spec.signs2),
+                          fp(spec.centroids), C.c_int(n), C.c_int(dim), C.c_int(levels))
+    norm8 = np.array([ref.ref_turboq_norm_value(C.c_int(int(c))) for c in norm_codes], np.float32)
+    assert np.array_equal(O.tq_norm_value(norm_codes.astype(np.uint8)), norm8)
+    out = O.tq_decode(codes, norm8, dim, bits, spec.perm, spec.signs1, spec.signs2, spec.centroids)
+    assert np.array_equal(out.view(np.uint32), out_ref.view(np.uint32))   # bit-exact reconstruction
