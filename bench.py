@@ -429,41 +429,26 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
     queries = queries.half().float().contiguous()  # the configuration's queries are f16
     ids = torch.empty((nq, k), dtype=torch.int64, device="cuda")
     scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
-    keys = torch.empty((nq, k), dtype=torch.int64, device="cuda")
-    keys_all = torch.empty((world, nq, k), dtype=torch.int64, device="cuda") if world > 1 else None
-    # thresholds seeded cooperatively: slices of the queries, a multiple of 256 each
-    tau_slice = ((nq + world - 1) // world + 255) // 256 * 256 if world > 1 and not args.tq_local_seeds else 0
-    tau_local = torch.zeros((max(1, tau_slice),), dtype=torch.int64, device="cuda")
-    tau_all = torch.zeros((max(1, tau_slice) * world,), dtype=torch.int64, device="cuda")
+    # N > 1: the library's own communicator (NCCL inside the C ABI); torch.distributed only carries the 128-byte id
+    comm = None
+    if world > 1:
+        from eos_b200 import dist as edist
+        id_t = torch.zeros((edist.NCCL_ID_BYTES,), dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            id_t.copy_(torch.frombuffer(bytearray(edist.new_comm_id()), dtype=torch.uint8))
+        dist.broadcast(id_t, src=0)
+        comm = edist.Comm(rt, rank, world, bytes(id_t.cpu().numpy().tobytes()))
+
     def measure(per_pass, steps, with_e2e):
         launches = 0
 
         def step():
-            n = 0
             if world == 1:
-                n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, ids.data_ptr(), scores.data_ptr(), None,
-                                              stream)
-            elif per_pass >= 128 and tau_slice > 0:
-                # every rank seeds the thresholds of its slice of the queries from its own shard (a threshold from any
-                # shard bounds the k-th best score of the whole corpus), one small all-gather shares them
-                q_lo = min(nq, rank * tau_slice)
-                q_n = min(nq, q_lo + tau_slice) - q_lo
-                tau_local.zero_()
-                if q_n > 0:
-                    corpus.score_seed_device(queries[q_lo:].data_ptr(), q_n, k, tau_local.data_ptr(), stream)
-                    n += 2 * ((q_n + 255) // 256) + 1
-                dist.all_gather_into_tensor(tau_all, tau_local)
-                n += corpus.score_topk_seeded_device(queries.data_ptr(), nq, k, tau_all.data_ptr(), None, None,
-                                                     keys.data_ptr(), stream)
-                dist.all_gather_into_tensor(keys_all, keys)  # one NCCL all-gather of the per-shard candidates
-                tq.topk_merge_device(rt, keys_all.data_ptr(), world, nq, k, ids.data_ptr(), scores.data_ptr(), stream)
-                n += 1
-            else:
-                n += corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, None, None, keys.data_ptr(), stream)
-                dist.all_gather_into_tensor(keys_all, keys)  # one NCCL all-gather of the per-shard top-k
-                tq.topk_merge_device(rt, keys_all.data_ptr(), world, nq, k, ids.data_ptr(), scores.data_ptr(), stream)
-                n += 1
-            return n
+                return corpus.score_topk_device(queries.data_ptr(), nq, k, per_pass, ids.data_ptr(), scores.data_ptr(), None,
+                                                stream)
+            # one C-ABI call per rank: seed slice -> all-gather of thresholds -> score -> all-gather of keys -> merge
+            return corpus.score_topk_sharded(comm, queries.data_ptr(), nq, k, per_pass, ids.data_ptr(), scores.data_ptr(),
+                                             stream)
 
         warm = max(1, min(args.warmup, 3))
         for _ in range(warm):
@@ -527,8 +512,9 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
                                    f"({passes} passes); one vector scored = one (query, vector) inner product",
                        "bytes_per_vector": bytes_per_vec,
                        "merge": "none" if world == 1 else "NCCL all-gather of per-shard top-k + merge kernel",
-                       "thresholds": "seeded per shard" if world == 1 or tau_slice == 0 or per_pass < 128 else
-                                     f"each rank seeds {tau_slice} queries, NCCL all-gather of {nq} thresholds"},
+                       "thresholds": "seeded per shard" if world == 1 or per_pass < 128 else
+                                     f"each rank seeds its slice of the queries, NCCL all-gather of {nq} thresholds "
+                                     "(eos_b200_score_topk_sharded)"},
             "roofline": roofline,
             "_launches": launches,
         }
@@ -552,11 +538,7 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
     if world == 1:
         corpus.score_topk_device(queries.data_ptr(), chk_q, k, 8, c_ids.data_ptr(), c_sc.data_ptr(), None, stream)
     else:
-        c_keys = torch.empty((chk_q, k), dtype=torch.int64, device="cuda")
-        c_all = torch.empty((world, chk_q, k), dtype=torch.int64, device="cuda")
-        corpus.score_topk_device(queries.data_ptr(), chk_q, k, 8, None, None, c_keys.data_ptr(), stream)
-        dist.all_gather_into_tensor(c_all, c_keys)
-        tq.topk_merge_device(rt, c_all.data_ptr(), world, chk_q, k, c_ids.data_ptr(), c_sc.data_ptr(), stream)
+        corpus.score_topk_sharded(comm, queries.data_ptr(), chk_q, k, 8, c_ids.data_ptr(), c_sc.data_ptr(), stream)
     corpus.sync(stream)
     same = float((batch_ids == c_ids).float().mean().item())
     sc_err = float(((batch_sc - c_sc).abs().max() / c_sc.abs().max()).item())
@@ -570,6 +552,8 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
         out["_launches"] += st["_launches"]
     if rank == 0 and world == 1 and not args.skip_cpu:
         out["cpu_baseline"] = time_oracle_scoring(spec, rt, qz)
+    if comm is not None:
+        comm.close()
     corpus.close()
     qz.close()
     return out
@@ -606,8 +590,6 @@ def main():
     ap.add_argument("--tq-queries-per-pass", type=int, default=256, choices=[8, 16, 32, 128, 256],
                     help="128 = tensor-core batch kernel; 8 = streaming scan; 16 / 32 = the earlier register-blocked scan")
     ap.add_argument("--tq-skip-stream", action="store_true", help="do not also time the 8-queries-per-pass scan")
-    ap.add_argument("--tq-local-seeds", action="store_true",
-                    help="multi-GPU: every rank seeds the thresholds of all queries itself instead of a slice each")
     ap.add_argument("--weight-mode", default="f16_resident", choices=["f16_resident", "q8_smem"],
                     help="how the projection kernel receives the 8-bit weights (results are bit-identical)")
     ap.add_argument("--skip-other-mode", action="store_true", help="do not also time the other weight mode")

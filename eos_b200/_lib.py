@@ -118,6 +118,11 @@ SYMBOLS = {
     "eos_b200_corpus_sync": (C.c_int, [_P, _P, _ERR]),
     "eos_b200_score_topk_noalloc": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _ERR]),
     "eos_b200_topk_merge_device": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, _ERR]),
+    "eos_b200_comm_unique_id": (C.c_int, [_P, _ERR]),
+    "eos_b200_comm_init": (C.c_int, [_P, C.c_int, C.c_int, _P, C.POINTER(_P), _ERR]),
+    "eos_b200_comm_destroy": (None, [_P]),
+    "eos_b200_score_topk_sharded": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, C.POINTER(Stats),
+                                              _ERR]),
     "eos_b200_score_all": (C.c_int, [_P, _P, C.c_int, _P, _ERR]),
     "eos_b200_parent_topk": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, C.c_int, C.c_double, C.c_int, _P, _P,
                                        C.POINTER(Stats), _ERR]),

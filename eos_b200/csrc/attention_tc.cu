@@ -35,12 +35,6 @@
 namespace eosb {
 
 #ifdef EOSB_ATTN_TIMING
-__device__ int g_attn_skip;   // debug: bit 0 skip the loads of S, bit 1 skip the maximum, bit 2 skip the exponentials, bit 3 skip P stores
-#define SKIP(b) ((skip__ >> (b)) & 1)
-#else
-#define SKIP(b) 0
-#endif
-#ifdef EOSB_ATTN_TIMING
 // Cycle counts per role phase of CTA 0 (debug builds only): [0..7] softmax thread 0, [8..15] MMA thread,
 // [16..19] producer thread.
 __device__ long long g_attn_timing[24];
@@ -352,9 +346,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         wk.init(vcta, vgrid, total_items, heads, qtile_info, qtile_win);
         uint32_t sn = 0, on = 0;
         bool ok = true;
-#ifdef EOSB_ATTN_TIMING
-        const int skip__ = g_attn_skip;
-#endif
         TDECL;
         for (; ok && wk.valid(); wk.next()) {
             const Item& it = wk.it;
@@ -390,7 +381,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                     uint32_t v[4][32];
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
-                        if (c < nch && !SKIP(0)) tmem_ld_32x32(t_s + c * 32, v[c]);
+                        if (c < nch) tmem_ld_32x32(t_s + c * 32, v[c]);
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
                         if (c < nch) tmem_ld_wait32(v[c]);
@@ -428,7 +419,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                         float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
                         for (int c = 0; c < 4; ++c)
-                            if (c < nch && !SKIP(1)) {
+                            if (c < nch) {
 #pragma unroll
                                 for (int e = 0; e < 32; e += 8) {
                                     m0 = max3(m0, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]));
@@ -476,14 +467,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
 #pragma unroll
                             for (int e = 0; e < 32; e += 2) {
                                 float x0, x1;
-                                if (SKIP(2)) {
-                                    p[e >> 1] = v[c][e] ^ v[c][e + 1];
-                                } else {
-                                    ffma2(x0, x1, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]), sl2, neg_m);
-                                    p[e >> 1] = ex2_f16x2(x0, x1);
-                                }
+                                ffma2(x0, x1, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]), sl2, neg_m);
+                                p[e >> 1] = ex2_f16x2(x0, x1);
                             }
-                            if (!SKIP(3)) tmem_st_32x16(t_s + c * 16, p);
+                            tmem_st_32x16(t_s + c * 16, p);
                         }
                     TMARK(4);
                     tmem_st_wait();
@@ -543,9 +530,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
 }  // namespace
 
 #ifdef EOSB_ATTN_TIMING
-extern "C" __attribute__((visibility("default"))) int eos_b200_debug_attn_skip(int mask) {
-    return cudaMemcpyToSymbol(g_attn_skip, &mask, sizeof(int)) != cudaSuccess;
-}
 extern "C" __attribute__((visibility("default"))) int eos_b200_debug_attn_timing(long long* out24, int reset) {
     long long zero[24] = {0};
     if (cudaMemcpyFromSymbol(out24, g_attn_timing, sizeof(zero)) != cudaSuccess) return 1;

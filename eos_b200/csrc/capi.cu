@@ -6,6 +6,9 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <dlfcn.h>
+
+#include <algorithm>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -1751,8 +1754,15 @@ int eos_b200_score_seed_device(EosB200Corpus* c, const float* d_queries, int q_c
     launch_tq_prepare(d_queries, q_count, q_pad, c->qz->spec(), nullptr, nullptr, c->qperm, s);
     CUDA_TRY(cudaMemsetAsync(c->shared_tau, 0, (size_t)q_pad * sizeof(unsigned long long), s));
     const int64_t seed_docs = (int64_t)p.grid * 256;
-    if (c->n >= seed_docs && k <= seed_docs)
+    if (c->n >= seed_docs && k <= seed_docs) {
         enqueue_tc_passes(c, 1, seed_docs, q_count, k, true, false, nullptr, nullptr, nullptr, s);
+        if (c->n >= 64 * seed_docs) {
+            // a large shard: tighten the thresholds with a second sample of 1/32 of the rows, as the unsharded call does
+            const int64_t second = c->n / 32 / 256 * 256;
+            enqueue_tc_passes(c, 1, second, q_count, k, false, false, nullptr, nullptr, c->seed_keys, s);
+            seed_tau_kernel<<<(q_count + 255) / 256, 256, 0, s>>>(c->seed_keys, q_count, k, c->shared_tau);
+        }
+    }
     CUDA_TRY(cudaMemcpyAsync(d_tau_out, c->shared_tau, (size_t)q_count * sizeof(uint64_t), cudaMemcpyDeviceToDevice, s));
     CUDA_TRY(cudaGetLastError());
     return EOS_B200_OK;
@@ -1829,6 +1839,181 @@ int eos_b200_corpus_sync(EosB200Corpus* c, void* stream, char** err) {
     if (c == nullptr) return fail(err, "corpus_sync: null corpus");
     CUDA_TRY(cudaSetDevice(c->qz->rt->device));
     return read_status(c->qz->rt, pick_stream(c->qz->rt, stream), err);
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// multi-GPU scoring: one process per GPU, NCCL between them
+// ------------------------------------------------------------------------------------------------
+namespace {
+// NCCL is resolved at run time (dlopen) so that the library loads, and everything single-GPU works, on a machine
+// without it.  Only the handful of entry points the sharded call needs.
+struct NcclApi {
+    void* handle = nullptr;
+    int (*GetUniqueId)(void*) = nullptr;
+    int (*CommInitRank)(void**, int, EosB200NcclId, int) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    std::string error;
+};
+NcclApi* nccl_api() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        const char* names[] = {"libnccl.so.2", "libnccl.so"};
+        for (const char* n : names) {
+            api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+            if (api.handle != nullptr) break;
+        }
+        if (api.handle == nullptr) {
+            api.error = "NCCL library (libnccl.so.2) not found";
+            return;
+        }
+        api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.handle, "ncclGetUniqueId"));
+        api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
+        api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
+        api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(api.handle, "ncclAllGather"));
+        api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
+        if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.AllGather || !api.GetErrorString)
+            api.error = "NCCL library lacks a required entry point";
+    });
+    return &api;
+}
+constexpr int kNcclChar = 0;  // ncclInt8 / ncclChar: all transfers are counted in bytes
+}  // namespace
+
+struct EosB200Comm {
+    EosB200Runtime* rt = nullptr;
+    void* comm = nullptr;
+    int rank = 0, world = 1;
+    // buffers of the sharded scoring call, grown on demand
+    int cap_queries = 0, cap_k = 0;
+    uint64_t *tau_local = nullptr, *tau_all = nullptr, *keys = nullptr, *keys_all = nullptr;
+};
+
+extern "C" {
+
+int eos_b200_comm_unique_id(EosB200NcclId* out, char** err) {
+    if (out == nullptr) return fail(err, "comm_unique_id: null argument");
+    NcclApi* api = nccl_api();
+    if (!api->error.empty()) return fail(err, "comm_unique_id: " + api->error);
+    const int r = api->GetUniqueId(out);
+    if (r != 0) return fail(err, std::string("ncclGetUniqueId: ") + api->GetErrorString(r));
+    return EOS_B200_OK;
+}
+
+int eos_b200_comm_init(EosB200Runtime* rt, int rank, int world, const EosB200NcclId* id, EosB200Comm** out, char** err) {
+    if (rt == nullptr || id == nullptr || out == nullptr) return fail(err, "comm_init: null argument");
+    *out = nullptr;
+    if (world <= 0 || rank < 0 || rank >= world) return fail(err, "comm_init: rank must be in [0, world)");
+    NcclApi* api = nccl_api();
+    if (!api->error.empty()) return fail(err, "comm_init: " + api->error);
+    CUDA_TRY(cudaSetDevice(rt->device));
+    EosB200Comm* c = new EosB200Comm();
+    c->rt = rt;
+    c->rank = rank;
+    c->world = world;
+    const int r = api->CommInitRank(&c->comm, world, *id, rank);
+    if (r != 0) {
+        delete c;
+        return fail(err, std::string("ncclCommInitRank: ") + api->GetErrorString(r));
+    }
+    *out = c;
+    return EOS_B200_OK;
+}
+
+void eos_b200_comm_destroy(EosB200Comm* c) {
+    if (c == nullptr) return;
+    cudaSetDevice(c->rt->device);
+    cudaStreamSynchronize(c->rt->stream);
+    dev_free(c->tau_local);
+    dev_free(c->tau_all);
+    dev_free(c->keys);
+    dev_free(c->keys_all);
+    if (c->comm != nullptr) nccl_api()->CommDestroy(c->comm);
+    delete c;
+}
+
+int eos_b200_score_topk_sharded(EosB200Corpus* c, EosB200Comm* comm, const float* d_queries, int q_count, int k,
+                                int queries_per_pass, int64_t* d_ids, float* d_scores, void* stream, EosB200Stats* stats,
+                                char** err) {
+    if (c == nullptr || comm == nullptr || d_queries == nullptr || d_ids == nullptr || d_scores == nullptr)
+        return fail(err, "score_topk_sharded: null argument");
+    if (comm->rt != c->qz->rt) return fail(err, "score_topk_sharded: corpus and communicator belong to different runtimes");
+    const int per_pass = resolve_per_pass(queries_per_pass, q_count);
+    std::string m = check_score_args(c, q_count, k, per_pass);
+    if (!m.empty()) return fail(err, m);
+    EosB200Runtime* rt = c->qz->rt;
+    NcclApi* api = nccl_api();
+    CUDA_TRY(cudaSetDevice(rt->device));
+    cudaStream_t s = pick_stream(rt, stream);
+    const int world = comm->world;
+    // thresholds are seeded cooperatively (batch kernels only): slices of the queries, a multiple of 256 each
+    const int slice = ((q_count + world - 1) / world + kTqTc256Queries - 1) / kTqTc256Queries * kTqTc256Queries;
+    if (q_count > comm->cap_queries || k > comm->cap_k) {
+        const int qcap = q_count > comm->cap_queries ? q_count : comm->cap_queries;
+        const int kcap = k > comm->cap_k ? k : comm->cap_k;
+        CUDA_TRY(cudaStreamSynchronize(s));
+        dev_free(comm->tau_local);
+        dev_free(comm->tau_all);
+        dev_free(comm->keys);
+        dev_free(comm->keys_all);
+        comm->cap_queries = comm->cap_k = 0;
+        const size_t slice_cap = (size_t)((qcap + kTqTc256Queries - 1) / kTqTc256Queries * kTqTc256Queries + kTqTc256Queries);
+        CUDA_TRY(dev_alloc(&comm->tau_local, slice_cap));
+        CUDA_TRY(dev_alloc(&comm->tau_all, slice_cap * world));
+        CUDA_TRY(dev_alloc(&comm->keys, (size_t)qcap * kcap));
+        CUDA_TRY(dev_alloc(&comm->keys_all, (size_t)qcap * kcap * world));
+        comm->cap_queries = qcap;
+        comm->cap_k = kcap;
+    }
+    int launches = 0;
+    int rc = EOS_B200_OK;
+    auto nccl_try = [&](int r, const char* what) {
+        if (r != 0 && rc == EOS_B200_OK) rc = fail(err, std::string(what) + ": " + api->GetErrorString(r));
+    };
+    // an empty shard contributes empty key lists (and no thresholds)
+    if (c->n == 0) CUDA_TRY(cudaMemsetAsync(comm->keys, 0, (size_t)q_count * k * sizeof(uint64_t), s));
+    if (per_pass >= kTqTcQueries) {
+        // every rank takes part in the threshold exchange, whatever its shard holds
+        const int q_lo = std::min(q_count, comm->rank * slice);
+        const int q_n = std::min(q_count, q_lo + slice) - q_lo;
+        CUDA_TRY(cudaMemsetAsync(comm->tau_local, 0, (size_t)slice * sizeof(uint64_t), s));
+        if (q_n > 0 && c->n > 0) {
+            rc = eos_b200_score_seed_device(c, d_queries + (size_t)q_lo * c->qz->dim, q_n, k, comm->tau_local, s, err);
+            if (rc != EOS_B200_OK) return rc;
+            launches += 2 * ((q_n + kTqTc256Queries - 1) / kTqTc256Queries) + 1;
+        }
+        nccl_try(api->AllGather(comm->tau_local, comm->tau_all, (size_t)slice * sizeof(uint64_t), kNcclChar, comm->comm, s),
+                 "ncclAllGather(thresholds)");
+        if (rc != EOS_B200_OK) return rc;
+        if (c->n > 0) {
+            EosB200Stats st{};
+            // tau_all is [world][slice]: query q's threshold sits at (q / slice) * slice + q % slice = q
+            rc = eos_b200_score_topk_seeded_device(c, d_queries, q_count, k, comm->tau_all, nullptr, nullptr, comm->keys, s,
+                                                   &st, err);
+            if (rc != EOS_B200_OK) return rc;
+            launches += st.kernel_launches;
+        }
+    } else if (c->n > 0) {
+        EosB200Stats st{};
+        rc = eos_b200_score_topk_device(c, d_queries, q_count, k, per_pass, nullptr, nullptr, comm->keys, s, &st, err);
+        if (rc != EOS_B200_OK) return rc;
+        launches += st.kernel_launches;
+    }
+    nccl_try(api->AllGather(comm->keys, comm->keys_all, (size_t)q_count * k * sizeof(uint64_t), kNcclChar, comm->comm, s),
+             "ncclAllGather(keys)");
+    if (rc != EOS_B200_OK) return rc;
+    rc = eos_b200_topk_merge_device(rt, comm->keys_all, world, q_count, k, d_ids, d_scores, s, err);
+    if (rc != EOS_B200_OK) return rc;
+    launches += 1;
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+    }
+    return EOS_B200_OK;
 }
 
 }  // extern "C"

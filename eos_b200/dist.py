@@ -7,9 +7,12 @@ is ordered by score descending, then id ascending (runtime/retrieval_eval.go:115
 """
 from __future__ import annotations
 
-from typing import Tuple
+import ctypes as C
+from typing import Optional, Tuple
 
 import numpy as np
+
+from . import _lib
 
 
 def shard_bounds(n_total: int, world: int, rank: int) -> Tuple[int, int]:
@@ -48,3 +51,38 @@ def decode_keys(keys: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
     ids[empty] = -1
     scores[empty] = -np.inf
     return ids, scores
+
+
+NCCL_ID_BYTES = 128
+
+
+def new_comm_id() -> bytes:
+    """The 128-byte NCCL id (rank 0 makes it and hands it to every other rank by whatever channel the host has)."""
+    buf = C.create_string_buffer(NCCL_ID_BYTES)
+    _lib.call("eos_b200_comm_unique_id", buf)
+    return buf.raw
+
+
+class Comm:
+    """The library's own communicator over the GPUs of a sharded corpus (one process per GPU): the collectives of
+    Corpus.score_topk_sharded are issued by the library through it, so the host needs no collective library."""
+
+    def __init__(self, runtime, rank: int, world: int, comm_id: bytes):
+        if len(comm_id) != NCCL_ID_BYTES:
+            raise ValueError("comm_id must be the 128 bytes of new_comm_id()")
+        self.rt, self.rank, self.world = runtime, int(rank), int(world)
+        self.handle = C.c_void_p()
+        buf = C.create_string_buffer(comm_id, NCCL_ID_BYTES)
+        _lib.call("eos_b200_comm_init", runtime.handle, self.rank, self.world, buf, C.byref(self.handle))
+        runtime._adopt(self)
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.lib().eos_b200_comm_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -194,6 +194,16 @@ class Corpus:
                   d_scores, d_keys, stream, C.byref(st))
         return st.kernel_launches
 
+    def score_topk_sharded(self, comm, d_queries: int, q_count: int, k: int, queries_per_pass: int, d_ids: int,
+                           d_scores: int, stream: Optional[int] = None) -> int:
+        """Collective over the ranks of `comm` (eos_b200.dist.Comm): this rank's shard is scored and every rank
+        receives the exact top-k of the whole corpus; thresholds and key lists travel by NCCL all-gathers issued
+        inside the library.  Returns the kernel launches of this rank."""
+        st = Stats()
+        _lib.call("eos_b200_score_topk_sharded", self.handle, comm.handle, d_queries, int(q_count), int(k),
+                  int(queries_per_pass), d_ids, d_scores, stream, C.byref(st))
+        return st.kernel_launches
+
     def score_topk_noalloc(self, d_queries: int, q_count: int, k: int, queries_per_pass: int, d_ids: int,
                            d_scores: int, stream: Optional[int] = None) -> None:
         """score_topk_device for callers that may not allocate device memory while serving (a fixed memory

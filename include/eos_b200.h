@@ -342,6 +342,29 @@ EOS_B200_API int eos_b200_corpus_profile_end(EosB200Corpus* corpus, void* stream
  * (one NCCL all-gather of the per-GPU results).  Keys carry global document ids. */
 EOS_B200_API int eos_b200_topk_merge_device(EosB200Runtime* rt, const uint64_t* d_keys, int shards, int q_count, int k,
                                int64_t* d_ids, float* d_scores, void* stream, char** err);
+/* ---- corpus sharded over several GPUs (one process per GPU) ------------------------------------
+ * No counterpart in Eos (its scoring runs in one process).  The exchange steps -- thresholds, then per-shard
+ * candidate lists -- are NCCL all-gathers issued by the library itself, so a host without any collective
+ * library of its own (the Go host) only has to hand the 128-byte NCCL id from rank 0 to the other ranks.
+ * NCCL (libnccl.so.2) is loaded when the first of these calls is made; everything else works without it. */
+typedef struct { char internal[128]; } EosB200NcclId;   /* layout of ncclUniqueId */
+typedef struct EosB200Comm EosB200Comm;
+/* Rank 0 calls this once and distributes the id (a file, a socket, an environment of the launcher). */
+EOS_B200_API int eos_b200_comm_unique_id(EosB200NcclId* out, char** err);
+/* Collective over all `world` ranks (ncclCommInitRank); the runtime's device is the rank's GPU. */
+EOS_B200_API int eos_b200_comm_init(EosB200Runtime* rt, int rank, int world, const EosB200NcclId* id, EosB200Comm** out,
+                                    char** err);
+EOS_B200_API void eos_b200_comm_destroy(EosB200Comm* comm);
+/* Collective: every rank calls it with its own shard (rows in ascending global id order across ranks, id_base
+ * = the shard's first id; an empty shard is allowed) and the same queries; every rank receives the exact global
+ * top-k.  Sequence, all on `stream`: each rank seeds the pruning thresholds of its slice of the queries from its
+ * own shard -> all-gather of the thresholds (8 bytes per query) -> batch scoring of the shard with all
+ * thresholds -> all-gather of the per-shard key lists (q_count * k * 8 bytes per rank) -> merge kernel.
+ * queries_per_pass as in eos_b200_score_topk (8 / 16 / 32: the streaming scan, without the threshold exchange).
+ * Enqueues only; eos_b200_corpus_sync reports kernel-side timeouts.  No peer-memory loads, no multicast. */
+EOS_B200_API int eos_b200_score_topk_sharded(EosB200Corpus* corpus, EosB200Comm* comm, const float* d_queries, int q_count,
+                                             int k, int queries_per_pass, int64_t* d_ids, float* d_scores, void* stream,
+                                             EosB200Stats* stats, char** err);
 /* Dense scores of a few queries against every row (no top-k), for parity checks and rerank
  * candidates: h_scores [q_count, n]. */
 EOS_B200_API int eos_b200_score_all(EosB200Corpus* corpus, const float* h_queries, int q_count, float* h_scores, char** err);

@@ -404,3 +404,29 @@ def test_thresholds_seeded_on_other_shards(rt):
     for c in shards + [whole]:
         c.close()
     qz.close()
+
+
+@pytest.mark.parametrize("per_pass", [8, 256])
+def test_sharded_call_through_the_library_communicator(rt, per_pass):
+    """eos_b200_score_topk_sharded on a one-rank communicator (NCCL inside the library, world = 1): the same exact
+    top-k as the unsharded call.  Ranks > 1 run the same code; bench.py checks them against the streaming scan."""
+    import torch
+    import eos_b200
+    from eos_b200 import dist as edist
+    spec, qz, codes, norms, q = _setup(rt, 96, 4, 400000, 300)
+    corpus = eos_b200.Corpus(qz, codes, norms, id_base=5)
+    ref_ids, ref_sc = corpus.score_topk(q, 50, queries_per_pass=per_pass)
+    comm = edist.Comm(rt, 0, 1, edist.new_comm_id())
+    dq = torch.from_numpy(q).cuda()
+    ids = torch.empty((300, 50), dtype=torch.int64, device="cuda")
+    sc = torch.empty((300, 50), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    for _ in range(2):   # the second call reuses the communicator's buffers
+        launches = corpus.score_topk_sharded(comm, dq.data_ptr(), 300, 50, per_pass, ids.data_ptr(), sc.data_ptr())
+        corpus.sync()
+        assert launches > 0
+        assert np.array_equal(ids.cpu().numpy(), ref_ids)
+        assert np.array_equal(sc.cpu().numpy(), ref_sc)
+    comm.close()
+    corpus.close()
+    qz.close()
