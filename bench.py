@@ -341,7 +341,37 @@ def run_ours(args, rank: int, world: int, local: int):
                          "one pass",
                "gpu_vs_port_max_abs": check_err}
         del oargs
+    # ------------------------------------------------------------------ the same encoder under strong scaling
+    # configuration 3 words it as "batch 1024 ... sharded across 1/2/4/8 GPUs": one global batch of 1024 sequences,
+    # 1024 / N per rank (length-balanced slices, no collective); reported beside the weak-scaling headline
+    strong = None
+    if world > 1:
+        s_ids, s_mask, s_len = synth.make_batch(ENC_BATCH, ENC_TOKENS, ENC["vocab"], ENC_MIN_LEN, ENC_TOKENS, 303)
+        rows_s = batching.split_by_length(s_len, world)[rank]
+        nb = len(rows_s)
+        ds_ids = torch.from_numpy(np.ascontiguousarray(s_ids[rows_s])).cuda()
+        ds_mask = torch.from_numpy(np.ascontiguousarray(s_mask[rows_s])).cuda()
+        for _ in range(3):
+            enc.run_device(ds_ids.data_ptr(), ds_mask.data_ptr(), None, nb, ENC_TOKENS, d_out.data_ptr(), stream)
+        enc.sync(stream)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            launches += enc.run_device(ds_ids.data_ptr(), ds_mask.data_ptr(), None, nb, ENC_TOKENS, d_out.data_ptr(), stream)
+        e1.record()
+        barrier()
+        enc.sync(stream)
+        ms_s = max_over_ranks(e0.elapsed_time(e1)) / K
+        strong = {"scaling": "strong", "global_batch": ENC_BATCH, "per_gpu_batch": nb, "value": ENC_BATCH / (ms_s / 1e3),
+                  "unit": "embeddings/s", "ms_per_step": ms_s, "steps": K}
+        del ds_ids, ds_mask
     enc.close()
+    # ------------------------------------------------------------------ configurations 1 and 2 (one GPU, rank 0's device)
+    small = None
+    if not args.skip_small_configs:
+        small = run_small_configs(rt, stream, peaks, K)
+        launches += small.pop("_launches", 0)
     # the other weight mode, timed the same way on fewer steps (reported beside the headline, not as it)
     other = None
     if not args.skip_other_mode:
@@ -387,6 +417,10 @@ def run_ours(args, rank: int, world: int, local: int):
         }
         if other is not None:
             line["other_weight_mode"] = other
+        if strong is not None:
+            line["encoder_strong_scaling"] = strong
+        if small is not None:
+            line["small_configs"] = small
         if cpu is not None:
             line["cpu_baseline"] = cpu
         if tq_out is not None:
@@ -395,6 +429,68 @@ def run_ours(args, rank: int, world: int, local: int):
     rt.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_small_configs(rt, stream, peaks, steps):
+    """Configurations 1 and 2 of the benchmark list, per GPU (every rank runs them; rank 0's numbers are printed).
+    C1: masked mean-pooled embed pipeline, table [30522, 384], batch 32 x 128, lengths 16..128: microseconds per batch
+    through the host-buffer call (its device time from the call's own events beside it).
+    C2: 4-layer q8 encoder D=384 / 6 heads / FFN 1536, batch 128 x 256, lengths 32..256: embeddings/s and TFLOP/s on
+    valid tokens, inputs resident on the device."""
+    import torch
+
+    import eos_b200
+    from eos_b200 import synth
+    out = {}
+    launches = 0
+    rng = np.random.default_rng(101)
+    table = synth.f16_round(rng.standard_normal((30522, 384), dtype=np.float32) * np.float32(0.02))
+    proj = synth.f16_round(rng.standard_normal((384, 384), dtype=np.float32) * np.float32(0.05))
+    tokens, mask, _ = synth.make_batch(32, 128, 30522, 16, 128, seed=102)
+    pipe = eos_b200.EmbedPooledPipeline(rt, table, proj)
+    for _ in range(5):
+        pipe.run(tokens, mask)
+    reps = max(20, steps * 5)
+    dev_ms = 0.0
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        pipe.run(tokens, mask)
+        dev_ms += pipe.last_stats.device_ms
+    wall_us = (time.perf_counter() - t0) / reps * 1e6
+    launches += reps
+    st = pipe.last_stats
+    out["c1_embed_pooled"] = {
+        "workload": "gather [30522,384] f16 -> projection [384,384] -> per-token L2 -> masked mean, batch 32 x 128",
+        "us_per_batch_e2e": wall_us, "us_per_batch_device": dev_ms / reps * 1e3, "batches_per_s": 1e6 / wall_us,
+        "h2d_bytes_per_step": int(st.uploaded_bytes), "d2h_bytes_per_step": int(st.downloaded_bytes),
+        "kernel_launches_per_batch": int(st.kernel_launches), "reps": reps}
+    pipe.close()
+    c2 = dict(layers=4, hidden=384, heads=6, inter=1536, vocab=30522, max_pos=512)
+    w2 = synth.make_q8_encoder(seed=201, **c2)
+    enc2 = eos_b200.BertEmbedder(rt, **w2)
+    ids2, mask2, len2 = synth.make_batch(128, 256, 30522, 32, 256, seed=202)
+    d_ids2, d_mask2 = torch.from_numpy(ids2).cuda(), torch.from_numpy(mask2).cuda()
+    d_out2 = torch.empty((128, 384), dtype=torch.float32, device="cuda")
+    for _ in range(5):
+        enc2.run_device(d_ids2.data_ptr(), d_mask2.data_ptr(), None, 128, 256, d_out2.data_ptr(), stream)
+    enc2.sync(stream)
+    reps2 = max(20, steps * 5)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps2):
+        launches += enc2.run_device(d_ids2.data_ptr(), d_mask2.data_ptr(), None, 128, 256, d_out2.data_ptr(), stream)
+    e1.record()
+    enc2.sync(stream)
+    ms2 = e0.elapsed_time(e1) / reps2
+    fl2 = synth.encoder_flops(len2, 4, 384, 1536)
+    out["c2_encoder_4layer"] = {
+        "workload": "4-layer q8 encoder D=384 heads=6 FFN=1536, batch 128 x T=256, lengths 32..256, masked mean + L2",
+        "ms_per_batch": ms2, "embeddings_per_s": 128 / (ms2 / 1e3), "tflops_valid_tokens": fl2 / (ms2 / 1e3) / 1e12,
+        "frac_of_sustained_tensor_peak": fl2 / (ms2 / 1e3) / 1e12 / peaks["tflops"], "valid_tokens": int(len2.sum()),
+        "reps": reps2, "note": "3.2 GFLOP per batch: launch- and latency-bound (35 launches per forward), not tensor-bound"}
+    enc2.close()
+    out["_launches"] = launches
+    return out
 
 
 def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks):
@@ -421,6 +517,23 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
         tq.synth_gaussian_device(rt, 401, lo + c0, c1 - c0, dim, True, xbuf.data_ptr(), stream)
         qz.quantize_device(xbuf.data_ptr(), c1 - c0, codes[c0:].data_ptr(), norms[c0:].data_ptr(), stream)
     torch.cuda.synchronize()
+    # the packer on its own: rows already on the device, one chunk re-packed (same bytes) under CUDA events
+    pack_rows = min(chunk, n_local)
+    pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    tq.synth_gaussian_device(rt, 401, lo, pack_rows, dim, True, xbuf.data_ptr(), stream)
+    qz.quantize_device(xbuf.data_ptr(), pack_rows, codes.data_ptr(), norms.data_ptr(), stream)
+    pe0.record()
+    for _ in range(3):
+        qz.quantize_device(xbuf.data_ptr(), pack_rows, codes.data_ptr(), norms.data_ptr(), stream)
+    pe1.record()
+    torch.cuda.synchronize()
+    pack_ms = pe0.elapsed_time(pe1) / 3
+    pack_bytes = dim * 4 + spec.vector_bytes
+    pack = {"kernel": "tq_pack_kernel", "rows": pack_rows, "ms": pack_ms, "docs_per_s": pack_rows / (pack_ms / 1e3),
+            "bound": "hbm", "algorithmic_bytes_per_vector": pack_bytes,
+            "achieved_gbs": pack_rows * pack_bytes / (pack_ms / 1e3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
+            "frac": pack_rows * pack_bytes / (pack_ms / 1e3) / 1e9 / peaks["hbm_gbs"],
+            "reference": "per-document q.Quantize loop, runtime/retrieval_turboquant.go:702-711 (host, one goroutine)"}
     corpus = eos_b200.Corpus(qz, device_ptrs=(codes.data_ptr(), norms.data_ptr(), n_local), id_base=lo)
     del xbuf, codes
     torch.cuda.empty_cache()
@@ -527,6 +640,7 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
     if rank == 0:
         sampler.start()
     out = measure(per_pass, steps, True)
+    out["pack"] = pack
     if rank == 0:
         out["clocks"] = sampler.stop()  # warm-up, timed steps and the end-to-end calls of the batch kernel
     # outside the timed region: the job's result for the first 16 queries (ids / scores hold the last step's output,
@@ -593,6 +707,7 @@ def main():
     ap.add_argument("--weight-mode", default="f16_resident", choices=["f16_resident", "q8_smem"],
                     help="how the projection kernel receives the 8-bit weights (results are bit-identical)")
     ap.add_argument("--skip-other-mode", action="store_true", help="do not also time the other weight mode")
+    ap.add_argument("--skip-small-configs", action="store_true", help="do not also time configurations 1 and 2")
     ap.add_argument("--tq-steps", type=int, default=10)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -1058,6 +1058,8 @@ struct EosB200EmbedPooled {
     __half *table = nullptr, *proj = nullptr;
     int32_t *d_tokens = nullptr, *d_mask = nullptr;
     float* d_out = nullptr;
+    float* d_partial = nullptr;   // [batch][ceil(tokens / 8)][out_dim] group sums
+    int* d_counts = nullptr;      // [batch] valid tokens
     long long cap_elems = 0;
     int cap_batch = 0;
 };
@@ -1073,6 +1075,8 @@ void eos_b200_embed_pooled_destroy(EosB200EmbedPooled* ep) {
     dev_free(ep->d_tokens);
     dev_free(ep->d_mask);
     dev_free(ep->d_out);
+    dev_free(ep->d_partial);
+    dev_free(ep->d_counts);
     delete ep;
 }
 
@@ -1112,9 +1116,13 @@ int eos_b200_embed_pooled_run(EosB200EmbedPooled* ep, const int32_t* h_tokens, c
         dev_free(ep->d_tokens);
         dev_free(ep->d_mask);
         dev_free(ep->d_out);
+        dev_free(ep->d_partial);
+        dev_free(ep->d_counts);
         CUDA_TRY(dev_alloc(&ep->d_tokens, (size_t)n));
         CUDA_TRY(dev_alloc(&ep->d_mask, (size_t)n));
         CUDA_TRY(dev_alloc(&ep->d_out, (size_t)batch * ep->out_dim));
+        CUDA_TRY(dev_alloc(&ep->d_partial, (size_t)(n / 8 + batch) * ep->out_dim));
+        CUDA_TRY(dev_alloc(&ep->d_counts, (size_t)batch));
         ep->cap_elems = n;
         ep->cap_batch = batch;
     }
@@ -1124,14 +1132,14 @@ int eos_b200_embed_pooled_run(EosB200EmbedPooled* ep, const int32_t* h_tokens, c
     CUDA_TRY(cudaMemcpyAsync(ep->d_tokens, h_tokens, (size_t)n * 4, cudaMemcpyHostToDevice, s));
     CUDA_TRY(cudaMemcpyAsync(ep->d_mask, h_mask, (size_t)n * 4, cudaMemcpyHostToDevice, s));
     launch_embed_pooled(ep->d_tokens, ep->d_mask, batch, tokens, ep->table, ep->vocab, ep->dim, ep->proj, ep->out_dim,
-                        pool_then_l2 ? 1 : 0, ep->d_out, rt->d_status, s);
+                        pool_then_l2 ? 1 : 0, ep->d_partial, ep->d_counts, ep->d_out, rt->d_status, s);
     CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaMemcpyAsync(h_out, ep->d_out, (size_t)batch * ep->out_dim * 4, cudaMemcpyDeviceToHost, s));
     CUDA_TRY(cudaEventRecord(rt->ev1, s));
     int rc = read_status(rt, s, err);
     if (stats != nullptr) {
         std::memset(stats, 0, sizeof(*stats));
-        stats->kernel_launches = 1;
+        stats->kernel_launches = 2;
         stats->uploaded_bytes = n * 8;
         stats->downloaded_bytes = (int64_t)batch * ep->out_dim * 4;
         cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
@@ -1520,7 +1528,11 @@ int eos_b200_quantizer_create(EosB200Runtime* rt, int dim, int bits, const int32
         boundaries == nullptr || out == nullptr)
         return fail(err, "quantizer_create: null argument");
     *out = nullptr;
-    if (dim <= 0 || dim > 8192) return fail(err, "quantizer_create: dim must be in [1, 8192]");
+    if (dim <= 0) return fail(err, "quantizer_create: dim must be positive");
+    {
+        const std::string why = tq_check_dim(dim);
+        if (!why.empty()) return fail(err, "quantizer_create: " + why);
+    }
     if (bits != 2 && bits != 4) return fail(err, "quantizer_create: bits must be 2 or 4");
     const int levels = 1 << bits;
     std::vector<char> seen((size_t)dim, 0);

@@ -909,80 +909,109 @@ compact_pool_kernel(const __half* __restrict__ hs, const int* __restrict__ cu_ro
 constexpr int kEpTok = 8;
 constexpr int kEpMaxColsPerThread = 4;
 
+// One CTA per (sequence, group of kEpTok valid tokens): gathers the group's table rows, projects them
+// (fp32 accumulate in k order), L2-normalises each token's row (unless the pooling comes first) and writes
+// the group's sum to partial[b][g][:].  Groups are cut over the VALID tokens, so padding costs nothing.
 __global__ void __launch_bounds__(256)
-embed_pooled_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ mask, int tlen,
-                    const __half* __restrict__ table, int vocab, int dim, const __half* __restrict__ proj, int out_dim,
-                    int pool_then_l2, float* __restrict__ out, int* status) {
+embed_pooled_group_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ mask, int tlen, int groups,
+                          const __half* __restrict__ table, int vocab, int dim, const __half* __restrict__ proj,
+                          int out_dim, int pool_then_l2, float* __restrict__ partial, int* __restrict__ counts,
+                          int* status) {
     extern __shared__ float xs[];  // [kEpTok][dim]
     __shared__ float red[32];
     __shared__ int tok_ids[kEpTok];
     __shared__ int n_tok;
-    __shared__ int cursor;
-    const int b = blockIdx.x;
+    const int b = blockIdx.y, g = blockIdx.x;
     const int32_t* tk = tokens + (size_t)b * tlen;
     const int32_t* mk = mask + (size_t)b * tlen;
+    // warp 0 finds the valid tokens number [g * kEpTok, (g + 1) * kEpTok) of the sequence
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const int first = g * kEpTok;
+        int seen = 0, n = 0;
+        for (int t0 = 0; t0 < tlen; t0 += 32) {
+            const int t = t0 + lane;
+            const bool valid = t < tlen && mk[t] != 0;
+            const unsigned bal = __ballot_sync(0xffffffffu, valid);
+            const int rank = seen + __popc(bal & ((1u << lane) - 1u));
+            if (valid && rank >= first && rank < first + kEpTok) tok_ids[rank - first] = tk[t];
+            seen += __popc(bal);
+        }
+        n = seen - first;
+        n = n < 0 ? 0 : (n > kEpTok ? kEpTok : n);
+        if (lane == 0) {
+            n_tok = n;
+            if (g == 0) counts[b] = seen;
+        }
+    }
+    __syncthreads();
+    const int n = n_tok;
+    if (n == 0) return;
+    for (int i = 0; i < n; ++i) {
+        const int id = tok_ids[i];
+        const bool ok = id >= 0 && id < vocab;
+        if (!ok && threadIdx.x == 0) atomicCAS(status, 0, kStatusBadTokenId);
+        for (int k = threadIdx.x; k < dim; k += blockDim.x)
+            xs[i * dim + k] = ok ? __half2float(table[(size_t)id * dim + k]) : 0.f;
+    }
+    for (int i = n; i < kEpTok; ++i)
+        for (int k = threadIdx.x; k < dim; k += blockDim.x) xs[i * dim + k] = 0.f;
+    __syncthreads();
+    float acc[kEpMaxColsPerThread][kEpTok];
+#pragma unroll
+    for (int c = 0; c < kEpMaxColsPerThread; ++c)
+#pragma unroll
+        for (int i = 0; i < kEpTok; ++i) acc[c][i] = 0.f;
+#pragma unroll
+    for (int c = 0; c < kEpMaxColsPerThread; ++c) {
+        const int j = threadIdx.x + c * blockDim.x;
+        if (j < out_dim) {
+            for (int k = 0; k < dim; ++k) {
+                const float w = __half2float(proj[(size_t)k * out_dim + j]);
+#pragma unroll
+                for (int i = 0; i < kEpTok; ++i) acc[c][i] = fmaf(xs[i * dim + k], w, acc[c][i]);
+            }
+        }
+    }
     float pooled[kEpMaxColsPerThread];
 #pragma unroll
-    for (int i = 0; i < kEpMaxColsPerThread; ++i) pooled[i] = 0.f;
-    int count = 0;
-    if (threadIdx.x == 0) cursor = 0;
-    __syncthreads();
-    while (true) {
-        if (threadIdx.x == 0) {
-            int n = 0, t = cursor;
-            while (t < tlen && n < kEpTok) {
-                if (mk[t] != 0) tok_ids[n++] = tk[t];
-                ++t;
-            }
-            cursor = t;
-            n_tok = n;
+    for (int c = 0; c < kEpMaxColsPerThread; ++c) pooled[c] = 0.f;
+    for (int i = 0; i < n; ++i) {
+        float inv = 1.0f;
+        if (!pool_then_l2) {
+            float sq = 0.f;
+#pragma unroll
+            for (int c = 0; c < kEpMaxColsPerThread; ++c) sq += acc[c][i] * acc[c][i];
+            const float norm = sqrtf(block_sum(sq, red));
+            inv = norm != 0.f ? 1.0f / norm : 1.0f;
         }
-        __syncthreads();
-        const int n = n_tok;
-        if (n == 0) break;
-        for (int i = 0; i < n; ++i) {
-            const int id = tok_ids[i];
-            const bool ok = id >= 0 && id < vocab;
-            if (!ok && threadIdx.x == 0) atomicCAS(status, 0, kStatusBadTokenId);
-            for (int k = threadIdx.x; k < dim; k += blockDim.x)
-                xs[i * dim + k] = ok ? __half2float(table[(size_t)id * dim + k]) : 0.f;
-        }
-        __syncthreads();
-        float acc[kEpMaxColsPerThread][kEpTok];
 #pragma unroll
-        for (int c = 0; c < kEpMaxColsPerThread; ++c)
-#pragma unroll
-            for (int i = 0; i < kEpTok; ++i) acc[c][i] = 0.f;
-#pragma unroll
-        for (int c = 0; c < kEpMaxColsPerThread; ++c) {
-            const int j = threadIdx.x + c * blockDim.x;
-            if (j < out_dim) {
-                for (int k = 0; k < dim; ++k) {
-                    const float w = __half2float(proj[(size_t)k * out_dim + j]);
-#pragma unroll
-                    for (int i = 0; i < kEpTok; ++i) acc[c][i] = fmaf(xs[i * dim + k], w, acc[c][i]);
-                }
-            }
-        }
-        for (int i = 0; i < n; ++i) {
-            float inv = 1.0f;
-            if (!pool_then_l2) {
-                float sq = 0.f;
-#pragma unroll
-                for (int c = 0; c < kEpMaxColsPerThread; ++c) sq += acc[c][i] * acc[c][i];
-                const float norm = sqrtf(block_sum(sq, red));
-                inv = norm != 0.f ? 1.0f / norm : 1.0f;
-            }
-#pragma unroll
-            for (int c = 0; c < kEpMaxColsPerThread; ++c)
-                pooled[c] += acc[c][i] * inv;
-        }
-        count += n;
-        __syncthreads();
+        for (int c = 0; c < kEpMaxColsPerThread; ++c) pooled[c] += acc[c][i] * inv;
     }
-    float scale = count > 0 ? 1.0f / (float)count : 0.f;
 #pragma unroll
-    for (int c = 0; c < kEpMaxColsPerThread; ++c) pooled[c] *= scale;
+    for (int c = 0; c < kEpMaxColsPerThread; ++c) {
+        const int j = threadIdx.x + c * blockDim.x;
+        if (j < out_dim) partial[((size_t)b * groups + g) * out_dim + j] = pooled[c];
+    }
+}
+
+// out[b,:] = (sum of the sequence's group sums, in group order) / valid tokens, then optionally L2.
+__global__ void __launch_bounds__(256)
+embed_pooled_finish_kernel(const float* __restrict__ partial, const int* __restrict__ counts, int groups, int out_dim,
+                           int pool_then_l2, float* __restrict__ out) {
+    __shared__ float red[32];
+    const int b = blockIdx.x;
+    const int count = counts[b];
+    const int used = (count + kEpTok - 1) / kEpTok;
+    float pooled[kEpMaxColsPerThread];
+#pragma unroll
+    for (int c = 0; c < kEpMaxColsPerThread; ++c) {
+        const int j = threadIdx.x + c * blockDim.x;
+        float v = 0.f;
+        if (j < out_dim)
+            for (int g = 0; g < used; ++g) v += partial[((size_t)b * groups + g) * out_dim + j];
+        pooled[c] = count > 0 ? v * (1.0f / (float)count) : 0.f;
+    }
     if (pool_then_l2) {
         float sq = 0.f;
 #pragma unroll
@@ -1093,11 +1122,12 @@ void launch_compact_pool(const __half* hidden_states, const SeqLayout& lay, int 
 }
 
 void launch_embed_pooled(const int32_t* tokens, const int32_t* mask, int batch, int tlen, const __half* table,
-                         int vocab, int dim, const __half* projection, int out_dim, int pool_then_l2, float* out,
-                         int* status, cudaStream_t stream) {
-    embed_pooled_kernel<<<batch, 256, kEpTok * dim * sizeof(float), stream>>>(tokens, mask, tlen, table, vocab, dim,
-                                                                              projection, out_dim, pool_then_l2, out,
-                                                                              status);
+                         int vocab, int dim, const __half* projection, int out_dim, int pool_then_l2,
+                         float* partial, int* counts, float* out, int* status, cudaStream_t stream) {
+    const int groups = (tlen + kEpTok - 1) / kEpTok;
+    embed_pooled_group_kernel<<<dim3(groups, batch), 256, kEpTok * dim * sizeof(float), stream>>>(
+        tokens, mask, tlen, groups, table, vocab, dim, projection, out_dim, pool_then_l2, partial, counts, status);
+    embed_pooled_finish_kernel<<<batch, 256, 0, stream>>>(partial, counts, groups, out_dim, pool_then_l2, out);
 }
 
 }  // namespace eosb

@@ -56,10 +56,12 @@ void launch_token_normalize(__half* x, const SeqLayout& lay, int dim, int m_allo
 void launch_compact_pool(const __half* hidden_states, const SeqLayout& lay, int batch, int tokens, int dim, int normalize,
                          float* out, cudaStream_t stream);
 
-// Compiled pipeline gather -> matmul -> per-token normalize -> masked mean_pool in one launch.
-// table [vocab, dim] f16, projection [dim, out_dim] f16 (in-major), out [B, out_dim] fp32.
+// Compiled pipeline gather -> matmul -> per-token normalize -> masked mean_pool: one launch over groups of 8
+// valid tokens (partial sums) and one that adds a sequence's groups in order.
+// table [vocab, dim] f16, projection [dim, out_dim] f16 (in-major), out [B, out_dim] fp32;
+// partial [B, ceil(tlen / 8), out_dim] fp32 and counts [B] are scratch.
 void launch_embed_pooled(const int32_t* tokens, const int32_t* mask, int batch, int tlen, const __half* table,
-                         int vocab, int dim, const __half* projection, int out_dim, int pool_then_l2, float* out,
-                         int* status, cudaStream_t stream);
+                         int vocab, int dim, const __half* projection, int out_dim, int pool_then_l2,
+                         float* partial, int* counts, float* out, int* status, cudaStream_t stream);
 
 }  // namespace eosb

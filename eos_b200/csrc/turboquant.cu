@@ -82,16 +82,25 @@ tq_pack_kernel(const float* __restrict__ x, long long n, TqSpec s, uint8_t* __re
     const long long cb = ((long long)s.dim * s.bits + 7) / 8;
     for (long long v = (long long)blockIdx.x * warps + warp; v < n; v += (long long)gridDim.x * warps) {
         const float* xv = x + v * s.dim;
-        // sequential float sum of squares (the order the reference's one-thread-per-vector kernel uses)
+        // the vector moves to shared memory with coalesced loads (rot serves as the staging buffer: the rotation
+        // reads all of it before it writes any of it); the sum of squares stays a sequential float sum in index
+        // order, the order the reference's one-thread-per-vector kernel uses, so the norm bits are the same
+        if ((s.dim & 3) == 0 && (reinterpret_cast<uintptr_t>(xv) & 15u) == 0) {
+            for (int i = lane; i < (s.dim >> 2); i += 32)
+                reinterpret_cast<float4*>(rot)[i] = __ldg(reinterpret_cast<const float4*>(xv) + i);
+        } else {
+            for (int i = lane; i < s.dim; i += 32) rot[i] = __ldg(xv + i);
+        }
+        __syncwarp();
         float norm = 0.f;
         if (lane == 0) {
             float sq = 0.f;
-            for (int c = 0; c < s.dim; ++c) sq = __fadd_rn(sq, __fmul_rn(xv[c], xv[c]));
+            for (int c = 0; c < s.dim; ++c) sq = __fadd_rn(sq, __fmul_rn(rot[c], rot[c]));
             norm = __fsqrt_rn(sq);
         }
         norm = __shfl_sync(0xffffffffu, norm, 0);
         const float scale = norm > 1.0e-12f ? __fdiv_rn(1.0f, norm) : 1.0f;
-        warp_rotate(xv, scale, s, work, rot, lane);
+        warp_rotate(rot, scale, s, work, rot, lane);
         uint8_t* cv = codes + v * cb;
         for (long long byte = lane; byte < cb; byte += 32) {
             unsigned out = 0;
@@ -1129,10 +1138,13 @@ parent_key_kernel(const float* __restrict__ agg, int rows, const int* __restrict
 
 }  // namespace
 
+// SMs of the current device (set by tq_scan_init; grids of the grid-stride kernels are multiples of it)
+static int g_sm_count = 148;
+
 void launch_parent_keys(const float* scores, long long stride, int rows, const int* child_order, const int* offsets,
                         int parents, int top_n, double penalty, float* agg_scratch, uint64_t* keys,
                         cudaStream_t stream) {
-    parent_agg_kernel<<<148 * 8, 256, 0, stream>>>(scores, stride, rows, child_order, offsets, parents, top_n, penalty,
+    parent_agg_kernel<<<g_sm_count * 8, 256, 0, stream>>>(scores, stride, rows, child_order, offsets, parents, top_n, penalty,
                                                    agg_scratch);
     parent_key_kernel<<<(parents + 255) / 256, 256, 0, stream>>>(agg_scratch, rows, offsets, parents,
                                                                  reinterpret_cast<u64*>(keys));
@@ -1141,16 +1153,18 @@ void launch_parent_keys(const float* scores, long long stride, int rows, const i
 void launch_tq_pack(const float* x, int64_t n, const TqSpec& spec, uint8_t* codes, float* norms,
                     cudaStream_t stream) {
     if (n <= 0) return;
-    const int warps = 4;
+    // 2 float rows per warp within the default 48 KB of dynamic shared memory: 8 warps up to dim 768
+    int warps = 6144 / spec.dim;
+    warps = warps > 8 ? 8 : (warps < 1 ? 1 : warps);
     const size_t smem = (size_t)warps * 2 * spec.dim * sizeof(float);
     long long blocks = (n + warps - 1) / warps;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > (long long)g_sm_count * 8) blocks = (long long)g_sm_count * 8;
     tq_pack_kernel<<<(int)blocks, warps * 32, smem, stream>>>(x, (long long)n, spec, codes, norms);
 }
 
 void launch_tq_transcode(const uint8_t* codes, int64_t n, int dim, int bits, uint8_t* tiles, cudaStream_t stream) {
     if (n <= 0) return;
-    tq_transcode_kernel<<<148 * 8, 256, 0, stream>>>(codes, (long long)n, dim, bits,
+    tq_transcode_kernel<<<g_sm_count * 8, 256, 0, stream>>>(codes, (long long)n, dim, bits,
                                                      reinterpret_cast<uint32_t*>(tiles));
 }
 
@@ -1161,9 +1175,22 @@ void launch_tq_prepare(const float* queries, int q, int q_fill, const TqSpec& sp
     const size_t smem = (size_t)warps * 3 * spec.dim * sizeof(float);
     const int q_padded = q_fill;
     int blocks = (q_padded + warps - 1) / warps;
-    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks > (long long)g_sm_count * 4) blocks = (long long)g_sm_count * 4;
     tq_prepare_kernel<<<blocks, warps * 32, smem, stream>>>(queries, q, q_fill, spec, tq_ksteps(spec.dim), bfrag,
                                                             rotated_out, qperm);
+}
+
+// Empty when every kernel of the scoring path can be launched for vectors of this dimension, else the reason:
+// the widest users of shared memory are the prepare kernel (3 float rows per warp) and the 32-query scan (the
+// query fragments of four tiles), both limited to the 200 KB the kernels ask for.
+std::string tq_check_dim(int dim) {
+    const size_t limit = 200 * 1024;
+    const size_t prepare = (size_t)4 * 3 * dim * sizeof(float);
+    const size_t scan = tq_scan_smem_bytes(4, dim);
+    if (prepare > limit || scan > limit || dim > 6144)
+        return "dim " + std::to_string(dim) + " is too wide for the scoring kernels (shared memory: prepare " +
+               std::to_string(prepare) + " B, scan " + std::to_string(scan) + " B, limit " + std::to_string(limit) + " B)";
+    return "";
 }
 
 size_t tq_scan_smem_bytes(int query_tiles, int dim) {
@@ -1174,6 +1201,12 @@ size_t tq_scan_smem_bytes(int query_tiles, int dim) {
 }
 
 cudaError_t tq_scan_init() {
+    {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+            g_sm_count = sms;
+    }
     const int max_smem = 200 * 1024;
     cudaError_t e = cudaFuncSetAttribute(tq_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e == cudaSuccess)

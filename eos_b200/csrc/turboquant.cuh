@@ -79,6 +79,7 @@ struct TqScanArgs {
 };
 // Returns the dynamic shared memory the configuration needs (0 = unsupported).
 size_t tq_scan_smem_bytes(int query_tiles, int dim);
+std::string tq_check_dim(int dim);
 cudaError_t tq_scan_init();
 void launch_tq_scan(const TqScanArgs& a, cudaStream_t stream);
 
