@@ -40,9 +40,10 @@ __device__ void warp_fwht_blocks(float* work, int dim, int lane) {
     while (remaining > 0) {
         const int size = highest_pow2_le(remaining);
         float* v = work + offset;
-        for (int step = 1; step < size; step <<= 1) {
+        int lg = 0;
+        for (int step = 1; step < size; step <<= 1, ++lg) {
             for (int p = lane; p < (size >> 1); p += 32) {
-                const int j = ((p / step) * (step << 1)) + (p % step);
+                const int j = ((p >> lg) << (lg + 1)) + (p & (step - 1));   // step is a power of two
                 const float a = v[j], b = v[j + step];
                 v[j] = __fadd_rn(a, b);
                 v[j + step] = __fsub_rn(a, b);
