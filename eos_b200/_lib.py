@@ -123,6 +123,9 @@ SYMBOLS = {
     "eos_b200_comm_destroy": (None, [_P]),
     "eos_b200_score_topk_sharded": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P, C.POINTER(Stats),
                                               _ERR]),
+    "eos_b200_maxsim_topk_device": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, _P, _P,
+                                              C.POINTER(Stats), _ERR]),
+    "eos_b200_comm_merge_keys": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, _ERR]),
     "eos_b200_score_all": (C.c_int, [_P, _P, C.c_int, _P, _ERR]),
     "eos_b200_parent_topk": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, C.c_int, C.c_double, C.c_int, _P, _P,
                                        C.POINTER(Stats), _ERR]),

@@ -1433,6 +1433,51 @@ int enqueue_tc_passes(EosB200Corpus* c, int plan, int64_t n_docs, int q_count, i
     return launches;
 }
 
+// Late-interaction launches (plan 0: 128 query vectors per launch = 128 / group queries): every launch walks the whole
+// shard, keeps per-query candidate lists of parent keys and is followed by the merge of its queries' lists.
+int enqueue_maxsim_passes(EosB200Corpus* c, int q_vectors, int group, int children, int k, int64_t* d_ids, float* d_scores,
+                          uint64_t* d_keys, cudaStream_t s) {
+    EosB200Quantizer* qz = c->qz;
+    EosB200Corpus::TcPlan& p = c->tcp[0];
+    const int64_t tiles = (c->n + p.tile_docs - 1) / p.tile_docs;
+    const int grid = (int)(tiles < p.grid ? tiles : p.grid);
+    const int n_segs = p.segs_per_cta * grid;
+    int launches = 0;
+    for (int q0 = 0; q0 < q_vectors; q0 += p.queries) {
+        const int q_here = (q_vectors - q0) < p.queries ? (q_vectors - q0) : p.queries;
+        TqTcArgs a{};
+        a.tiles = c->tiles;
+        a.norms = c->norms;
+        a.n_docs = c->n;
+        a.id_base = (uint32_t)c->id_base;
+        a.dim = qz->dim;
+        a.q_row0 = q0;
+        a.q_valid = q_here;
+        a.k = k;
+        a.mag_hi[0] = qz->mag_hi[0];
+        a.mag_hi[1] = qz->mag_hi[1];
+        a.mag_lo[0] = qz->mag_lo[0];
+        a.mag_lo[1] = qz->mag_lo[1];
+        a.cand_keys = p.cand;
+        a.cand_count = p.count;
+        a.shared_tau = c->shared_tau + q0 / group;
+        a.seed_scores = nullptr;
+        a.seed_stride = 0;
+        a.qperm = c->qperm;
+        a.status = qz->rt->d_status;
+        a.maxsim_children = children;
+        a.maxsim_group = group;
+        c->prof.launch(kClsScan, s, [&] { launch_tq_score_tc(p.tm, a, p.q_in_tmem, grid, s); });
+        const int queries_here = q_here / group;
+        const size_t out0 = (size_t)(q0 / group) * k;
+        launch_tq_merge_lists(p.cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, p.count, queries_here, k,
+                              d_ids != nullptr ? d_ids + out0 : nullptr, d_scores != nullptr ? d_scores + out0 : nullptr,
+                              d_keys != nullptr ? d_keys + out0 : nullptr, s);
+        launches += 2;
+    }
+    return launches;
+}
+
 // The batch paths.  Thresholds are seeded from the first grid * 256 rows (every score written out, k-th best per
 // query); on a large shard a second sample of 1/32 of the rows, scored with those thresholds and merged like the real
 // pass, tightens them further, so that the lists of the full pass stay short (no list is cut, and the merge gathers a
@@ -2026,6 +2071,71 @@ int eos_b200_score_topk_sharded(EosB200Corpus* c, EosB200Comm* comm, const float
         stats->kernel_launches = launches;
     }
     return EOS_B200_OK;
+}
+
+int eos_b200_maxsim_topk_device(EosB200Corpus* c, const float* d_queries, int q_vectors, int query_group,
+                                int children_per_parent, int k, int64_t* d_ids, float* d_scores, uint64_t* d_keys,
+                                void* stream, EosB200Stats* stats, char** err) {
+    if (c == nullptr || d_queries == nullptr) return fail(err, "maxsim_topk: null argument");
+    if ((d_ids == nullptr) != (d_scores == nullptr))
+        return fail(err, "maxsim_topk: d_ids and d_scores must be given together or both be null");
+    if (d_ids == nullptr && d_keys == nullptr) return fail(err, "maxsim_topk: no output requested");
+    if (query_group < 1 || query_group > 32 || (query_group & (query_group - 1)) != 0)
+        return fail(err, "maxsim_topk: query_group must be a power of two in [1, 32]");
+    if (children_per_parent != 16 && children_per_parent != 32 && children_per_parent != 64 && children_per_parent != 128)
+        return fail(err, "maxsim_topk: children_per_parent must be 16, 32, 64 or 128");
+    if (q_vectors <= 0 || q_vectors % query_group != 0)
+        return fail(err, "maxsim_topk: the number of query vectors must be a positive multiple of query_group");
+    if (k <= 0 || k > kTqMaxK) return fail(err, "maxsim_topk: k must be in [1, 128]");
+    if (c->n <= 0 || c->n % children_per_parent != 0 || c->id_base % children_per_parent != 0)
+        return fail(err, "maxsim_topk: corpus rows and id_base must be multiples of children_per_parent");
+    if (c->n + c->id_base > 0xffffffffLL || c->id_base < 0) return fail(err, "maxsim_topk: child ids must fit 32 bits");
+    EosB200Runtime* rt = c->qz->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    int rc = ensure_score_workspace(c, q_vectors, err);
+    if (rc == EOS_B200_OK) rc = ensure_tc_workspace(c, 0, err);
+    if (rc != EOS_B200_OK) return rc;
+    cudaStream_t s = pick_stream(rt, stream);
+    const EosB200Corpus::TcPlan& p = c->tcp[0];
+    const int q_pad = (q_vectors + p.queries - 1) / p.queries * p.queries;
+    launch_tq_prepare(d_queries, q_vectors, q_pad, c->qz->spec(), nullptr, nullptr, c->qperm, s);
+    CUDA_TRY(cudaMemsetAsync(c->shared_tau, 0, (size_t)q_pad * sizeof(unsigned long long), s));
+    const int launches = 1 + enqueue_maxsim_passes(c, q_vectors, query_group, children_per_parent, k, d_ids, d_scores, d_keys, s);
+    CUDA_TRY(cudaGetLastError());
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+    }
+    return EOS_B200_OK;
+}
+
+int eos_b200_comm_merge_keys(EosB200Comm* comm, const uint64_t* d_keys, int q_count, int k, int64_t* d_ids, float* d_scores,
+                             void* stream, char** err) {
+    if (comm == nullptr || d_keys == nullptr || d_ids == nullptr || d_scores == nullptr)
+        return fail(err, "comm_merge_keys: null argument");
+    if (q_count <= 0 || k <= 0 || k > kTqMaxK) return fail(err, "comm_merge_keys: bad sizes");
+    EosB200Runtime* rt = comm->rt;
+    NcclApi* api = nccl_api();
+    CUDA_TRY(cudaSetDevice(rt->device));
+    cudaStream_t s = pick_stream(rt, stream);
+    if ((size_t)q_count * k > (size_t)comm->cap_queries * comm->cap_k) {
+        CUDA_TRY(cudaStreamSynchronize(s));
+        dev_free(comm->keys_all);
+        dev_free(comm->keys);
+        dev_free(comm->tau_local);
+        dev_free(comm->tau_all);
+        comm->cap_queries = comm->cap_k = 0;
+        const size_t slice_cap = (size_t)((q_count + kTqTc256Queries - 1) / kTqTc256Queries * kTqTc256Queries + kTqTc256Queries);
+        CUDA_TRY(dev_alloc(&comm->tau_local, slice_cap));
+        CUDA_TRY(dev_alloc(&comm->tau_all, slice_cap * comm->world));
+        CUDA_TRY(dev_alloc(&comm->keys, (size_t)q_count * k));
+        CUDA_TRY(dev_alloc(&comm->keys_all, (size_t)q_count * k * comm->world));
+        comm->cap_queries = q_count;
+        comm->cap_k = k;
+    }
+    const int r = api->AllGather(d_keys, comm->keys_all, (size_t)q_count * k * sizeof(uint64_t), kNcclChar, comm->comm, s);
+    if (r != 0) return fail(err, std::string("ncclAllGather(keys): ") + api->GetErrorString(r));
+    return eos_b200_topk_merge_device(rt, comm->keys_all, comm->world, q_count, k, d_ids, d_scores, s, err);
 }
 
 }  // extern "C"

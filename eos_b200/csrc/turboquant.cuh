@@ -107,6 +107,13 @@ struct TqTcArgs {
     int64_t seed_stride;   // no list is kept
     const __half* qperm;   // the permuted f16 query matrix itself (variant with the queries in tensor memory)
     int* status;
+    // late-interaction (MaxSim) mode when maxsim_children > 0: rows of the corpus are child vectors, every
+    // maxsim_children (16, 32, 64 or 128) consecutive rows belong to one parent, every maxsim_group (a power of two
+    // <= 32) consecutive query vectors to one query; the score of (query, parent) is the sum over the query's
+    // vectors of the best child score.  Candidate keys carry parent ids ((id_base + row) / maxsim_children); lists,
+    // counts and thresholds are indexed by query (query vector / maxsim_group), not by query vector.
+    int maxsim_children;
+    int maxsim_group;
 };
 cudaError_t tq_tc_init();
 // Tensor map of the permuted query matrix [rows][padded_dim] f16 (rows a multiple of kTqTcQueries).

@@ -297,11 +297,16 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
         const int seg = (int)blockIdx.x * 2 + epart;
         const int n_segs = (int)gridDim.x * 2;
         u64* const cand = reinterpret_cast<u64*>(a.cand_keys);
-        u64* my_list = cand + ((size_t)qrow * n_segs + seg) * kTqTcSegLen;
+        // MaxSim mode: the first thread of every group of maxsim_group query vectors owns the query's list
+        const bool maxsim = a.maxsim_children > 0;
+        const int group = maxsim ? a.maxsim_group : 1;
+        const bool owner = (lane & (group - 1)) == 0;
+        const int qlist = maxsim ? qrow / group : qrow;     // list / count / threshold index of this thread
+        u64* my_list = cand + ((size_t)qlist * n_segs + seg) * kTqTcSegLen;
         u64* sortbuf = reinterpret_cast<u64*>(sm + kOffSort) + ew * kSortCap;
         float* norm_s = reinterpret_cast<float*>(sm + kOffNorm);
         volatile u64* shared_tau = a.shared_tau;
-        const bool q_live = qrow < a.q_valid;
+        const bool q_live = qrow < a.q_valid && owner;
         u64 tau_key = q_live ? 0ull : ~0ull;
         float tau_f = q_live ? -INFINITY : INFINITY;
         int cnt = 0;
@@ -327,13 +332,13 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
             named_bar_sync(1, kEpiWarps * 32);
             if (*epi_stop != 0) break;
             // thresholds other CTAs published; lists that the coming tile could overflow are cut to their k best
-            if (q_live) raise_tau(shared_tau[qrow]);
+            if (q_live) raise_tau(shared_tau[qlist]);
             unsigned need = __ballot_sync(0xffffffffu, cnt > kCutAbove);
             while (need != 0) {
                 const int src = __ffs(need) - 1;
                 need &= need - 1;
                 const int n = __shfl_sync(0xffffffffu, cnt, src);
-                u64* lst = cand + ((size_t)(quarter * 32 + src) * n_segs + seg) * kTqTcSegLen;
+                u64* lst = cand + ((size_t)((quarter * 32 + src) / group) * n_segs + seg) * kTqTcSegLen;
                 __syncwarp();
                 for (int i = lane; i < n; i += 32) sortbuf[i] = lst[i];
                 warp_sort_desc(sortbuf, n, lane);
@@ -343,7 +348,7 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
                 if (lane == src) {
                     cnt = a.k;
                     raise_tau(kth);
-                    atomicMax(const_cast<u64*>(a.shared_tau) + qrow, kth);
+                    atomicMax(const_cast<u64*>(a.shared_tau) + qlist, kth);
                 }
             }
             if (!__all_sync(0xffffffffu, mbar_wait(acc_full(ab), aph, abort_flag))) {
@@ -358,6 +363,7 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
             float* seed_row = a.seed_scores != nullptr
                                   ? a.seed_scores + (size_t)qrow * a.seed_stride + (size_t)tile * TD + epart * (TD / 2)
                                   : nullptr;
+            float child_max = -INFINITY;   // MaxSim: best child score of the current parent for this query vector
             auto chunk = [&](const uint32_t (&r)[16], const int c0) {
                 float sc[16];
                 bool any = false;
@@ -370,7 +376,23 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
                     sc[j + 3] = __uint_as_float(r[j + 3]) * nv.w;
                     any |= (sc[j] >= tau_f) | (sc[j + 1] >= tau_f) | (sc[j + 2] >= tau_f) | (sc[j + 3] >= tau_f);
                 }
-                if (seed_row != nullptr) {
+                if (maxsim) {
+                    // a missing child has a NaN norm: fmaxf ignores it
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) child_max = fmaxf(child_max, sc[j]);
+                    if (((c0 + 16) & (a.maxsim_children - 1)) == 0) {
+                        // the parent's last columns: sum the best child scores over the query's vectors (lanes of one
+                        // group), the group's first lane keeps the candidate
+                        float v = child_max;
+                        for (int o = 1; o < group; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                        child_max = -INFINITY;
+                        if (v >= tau_f) {   // false for NaN / -inf (a parent without children) and for non-owners
+                            const uint32_t parent = (doc0 + (uint32_t)(c0 + 16 - a.maxsim_children)) / (uint32_t)a.maxsim_children;
+                            const u64 key = make_key(v, parent);
+                            if (key > tau_key) my_list[cnt++] = key;
+                        }
+                    }
+                } else if (seed_row != nullptr) {
                     // seed mode: the thread's 16 scores are 64 contiguous bytes of its query's row
                     uint32_t lo8[8], hi8[8];
 #pragma unroll
@@ -410,7 +432,7 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty(ab));
         }
-        a.cand_count[(size_t)qrow * n_segs + seg] = cnt;
+        if (!maxsim || owner) a.cand_count[(size_t)qlist * n_segs + seg] = cnt;
     }
 
     // ---------------------------------------------------------------- teardown

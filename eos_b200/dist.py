@@ -76,6 +76,10 @@ class Comm:
         _lib.call("eos_b200_comm_init", runtime.handle, self.rank, self.world, buf, C.byref(self.handle))
         runtime._adopt(self)
 
+    def merge_keys(self, d_keys: int, q_count: int, k: int, d_ids: int, d_scores: int, stream: Optional[int] = None) -> None:
+        """Collective: all-gather of every rank's key lists [q_count, k] and the merge into the global top-k."""
+        _lib.call("eos_b200_comm_merge_keys", self.handle, d_keys, int(q_count), int(k), d_ids, d_scores, stream)
+
     def close(self) -> None:
         if self.handle:
             _lib.lib().eos_b200_comm_destroy(self.handle)

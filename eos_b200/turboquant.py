@@ -204,6 +204,17 @@ class Corpus:
                   int(queries_per_pass), d_ids, d_scores, stream, C.byref(st))
         return st.kernel_launches
 
+    def maxsim_topk_device(self, d_queries: int, q_vectors: int, query_group: int, children_per_parent: int, k: int,
+                           d_ids: Optional[int], d_scores: Optional[int], d_keys: Optional[int] = None,
+                           stream: Optional[int] = None) -> int:
+        """Late interaction over fixed-size parents (rows = child vectors, children_per_parent consecutive rows per
+        parent): per query (query_group consecutive query vectors) the sum of the best child scores, exact top-k
+        over parents.  Results [q_vectors / query_group, k]."""
+        st = Stats()
+        _lib.call("eos_b200_maxsim_topk_device", self.handle, d_queries, int(q_vectors), int(query_group),
+                  int(children_per_parent), int(k), d_ids, d_scores, d_keys, stream, C.byref(st))
+        return st.kernel_launches
+
     def score_topk_noalloc(self, d_queries: int, q_count: int, k: int, queries_per_pass: int, d_ids: int,
                            d_scores: int, stream: Optional[int] = None) -> None:
         """score_topk_device for callers that may not allocate device memory while serving (a fixed memory

@@ -365,6 +365,24 @@ EOS_B200_API void eos_b200_comm_destroy(EosB200Comm* comm);
 EOS_B200_API int eos_b200_score_topk_sharded(EosB200Corpus* corpus, EosB200Comm* comm, const float* d_queries, int q_count,
                                              int k, int queries_per_pass, int64_t* d_ids, float* d_scores, void* stream,
                                              EosB200Stats* stats, char** err);
+/* Late interaction (MaxSim) over a corpus of child vectors with a fixed number of children per parent
+ * (the long-context multi-vector layout: a document is a run of children_per_parent consecutive rows; rows of
+ * a document that do not exist are bound with a norm of NaN and score nothing).  Extension of
+ * topTurboQuantMultiVectorParentScores (runtime/retrieval_multivector_turboquant.go:746-810, "max" aggregation):
+ * for each query (query_group consecutive query vectors, a power of two <= 32) and each parent,
+ *     score = sum over the query's vectors of max over the parent's children of norm * <R q, centroids[codes]>,
+ * exact top-k over parents, score descending then parent id ascending; parent id = (id_base + row) /
+ * children_per_parent.  d_queries [q_vectors, dim] fp32 on the device; results [q_vectors / query_group, k].
+ * One tensor-core pass over the shard per 128 query vectors; children_per_parent in {16, 32, 64, 128}.
+ * The general layout (any parent_of_child map, top-n mean, penalty) stays with eos_b200_parent_topk. */
+EOS_B200_API int eos_b200_maxsim_topk_device(EosB200Corpus* corpus, const float* d_queries, int q_vectors, int query_group,
+                                             int children_per_parent, int k, int64_t* d_ids, float* d_scores,
+                                             uint64_t* d_keys, void* stream, EosB200Stats* stats, char** err);
+/* Collective: all-gather of every rank's key lists [q_count, k] (as eos_b200_*_device calls emit them in d_keys)
+ * and the merge into the global top-k, for results sharded in any other way than eos_b200_score_topk_sharded's
+ * (for instance eos_b200_maxsim_topk_device over parents sharded across GPUs). */
+EOS_B200_API int eos_b200_comm_merge_keys(EosB200Comm* comm, const uint64_t* d_keys, int q_count, int k, int64_t* d_ids,
+                                          float* d_scores, void* stream, char** err);
 /* Dense scores of a few queries against every row (no top-k), for parity checks and rerank
  * candidates: h_scores [q_count, n]. */
 EOS_B200_API int eos_b200_score_all(EosB200Corpus* corpus, const float* h_queries, int q_count, float* h_scores, char** err);

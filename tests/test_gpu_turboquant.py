@@ -430,3 +430,68 @@ def test_sharded_call_through_the_library_communicator(rt, per_pass):
     comm.close()
     corpus.close()
     qz.close()
+
+
+@pytest.mark.parametrize("children,group,parents,nq", [(128, 32, 60, 9), (16, 8, 500, 40), (64, 1, 100, 130), (32, 32, 37, 4)])
+def test_maxsim_over_fixed_size_parents(rt, children, group, parents, nq):
+    """Late interaction on the tensor-core batch kernel: for each query (group consecutive query vectors) and parent
+    (children consecutive rows) the sum over the query's vectors of the best child score, exact top-k over parents.
+    Checked against the aggregation of the GPU's own child scores (exact up to fp32 summation order) and against the
+    oracle's child scores within the score tolerance; one parent has only missing children (NaN norms)."""
+    import torch
+    import eos_b200
+    from oracle import oracle as O
+    dim, bits, k = 128, 2, 20
+    n = parents * children
+    spec, qz, codes, norms, q = _setup(rt, dim, bits, n, nq * group, seed=11)
+    norms = norms * np.linspace(0.5, 1.5, n, dtype=np.float32)
+    norms[3 * children:4 * children] = np.nan             # parent 3 has no children
+    norms[5 * children + 1:6 * children] = np.nan          # parent 5 has one child
+    d_codes = torch.from_numpy(codes).cuda()
+    d_norms = torch.from_numpy(norms).cuda()
+    id_base = 7 * children
+    corpus = eos_b200.Corpus(qz, device_ptrs=(d_codes.data_ptr(), d_norms.data_ptr(), n), id_base=id_base)
+    dq = torch.from_numpy(q).cuda()
+    kk = min(k, parents - 1)
+    ids = torch.empty((nq, kk), dtype=torch.int64, device="cuda")
+    sc = torch.empty((nq, kk), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    corpus.maxsim_topk_device(dq.data_ptr(), nq * group, group, children, kk, ids.data_ptr(), sc.data_ptr())
+    corpus.sync()
+    ids, sc = ids.cpu().numpy(), sc.cpu().numpy()
+    finite = np.where(np.isnan(norms), 1.0, norms).astype(np.float32)
+    ref_child = _oracle_scores(spec, codes, finite, q)                      # [nq * group, n]
+    ref_child[:, np.isnan(norms)] = -np.inf
+    best = ref_child.reshape(nq, group, parents, children).max(axis=3)      # [nq, group, parents]
+    total = best.sum(axis=1, dtype=np.float64)                              # [nq, parents]
+    tol = 1e-3 * float(np.abs(total[np.isfinite(total)]).max())
+    for i in range(nq):
+        t = total[i].copy()
+        t[~np.isfinite(t)] = -np.inf
+        order = np.lexsort((np.arange(parents), -t))[:kk]
+        assert (sc[i][:-1] >= sc[i][1:]).all()
+        got = ids[i] - 7
+        assert got.min() >= 0 and got.max() < parents and len(set(got.tolist())) == kk and 3 not in got.tolist()
+        assert np.abs(sc[i] - t[got]).max() <= tol
+        sep = np.abs(np.diff(t[order])) > 2 * tol
+        clear = np.concatenate([[True], sep]) & np.concatenate([sep, [True]])
+        clear &= np.abs(t[order] - t[order][-1]) > 2 * tol
+        assert np.array_equal(got[clear], order[clear])
+    corpus.close()
+    qz.close()
+
+
+def test_maxsim_argument_errors(rt):
+    import torch
+    import eos_b200
+    spec, qz, codes, norms, q = _setup(rt, 128, 2, 640, 64)
+    corpus = eos_b200.Corpus(qz, codes, norms)
+    dq = torch.from_numpy(q).cuda()
+    ids = torch.empty((2, 5), dtype=torch.int64, device="cuda")
+    sc = torch.empty((2, 5), dtype=torch.float32, device="cuda")
+    for args, msg in (((64, 32, 48, 5), "children_per_parent"), ((64, 24, 64, 5), "query_group"),
+                      ((60, 32, 64, 5), "multiple of query_group"), ((64, 32, 128, 200), "k must")):
+        with pytest.raises(Exception, match=msg):
+            corpus.maxsim_topk_device(dq.data_ptr(), args[0], args[1], args[2], args[3], ids.data_ptr(), sc.data_ptr())
+    corpus.close()
+    qz.close()
