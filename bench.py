@@ -399,10 +399,25 @@ def run_ours(args, rank: int, world: int, local: int):
     torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ TurboQuant scoring
+    # N > 1: the library's own communicator (NCCL inside the C ABI); torch.distributed only carries the 128-byte id
+    comm = None
+    if world > 1:
+        from eos_b200 import dist as edist
+        id_t = torch.zeros((edist.NCCL_ID_BYTES,), dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            id_t.copy_(torch.frombuffer(bytearray(edist.new_comm_id()), dtype=torch.uint8))
+        dist.broadcast(id_t, src=0)
+        comm = edist.Comm(rt, rank, world, bytes(id_t.cpu().numpy().tobytes()))
     tq_out = None
     if not args.skip_turboquant:
-        tq_out = run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks)
+        tq_out = run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks, comm)
         launches += tq_out.pop("_launches", 0)
+    lc_out = None
+    if not args.skip_long_context:
+        lc_out = run_long_context(args, rt, rank, world, stream, peaks, barrier, max_over_ranks, comm)
+        launches += lc_out.pop("_launches", 0)
+    if comm is not None:
+        comm.close()
 
     if rank == 0:
         line = {
@@ -425,6 +440,8 @@ def run_ours(args, rank: int, world: int, local: int):
             line["cpu_baseline"] = cpu
         if tq_out is not None:
             line["turboquant"] = tq_out
+        if lc_out is not None:
+            line["long_context_multivector"] = lc_out
         print(json.dumps(line), flush=True)
     rt.close()
     if world > 1:
@@ -493,7 +510,159 @@ def run_small_configs(rt, stream, peaks, steps):
     return out
 
 
-def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks):
+LC = dict(layers=6, hidden=512, heads=8, inter=2048, vocab=30522, max_pos=8192, tokens=8192, window=512, batch=16,
+          token_dim=128, bits=2, docs=100_000, children=128, queries=256, query_tokens=32, k=100)
+
+
+def run_long_context(args, rt, rank, world, stream, peaks, barrier, max_over_ranks, comm):
+    """Configuration 5.  (a) Document side: 6-layer q8 encoder D=512 / 8 heads / FFN 2048 with a 512-token local
+    window over 16 sequences of 8192 tokens -> 128-d L2-normalised per-token vectors -> 2-bit TurboQuant packing,
+    per GPU (every rank encodes its own batch of 16: weak scaling, like the headline).  (b) Query side: late
+    interaction of 256 queries x 32 token vectors against 100k documents x 128 packed vectors, documents sharded
+    over the GPUs, per-shard parent lists merged through the library's communicator."""
+    import torch
+
+    import eos_b200
+    from eos_b200 import synth
+    from eos_b200 import turboquant as tq
+    c = LC
+    launches = 0
+    # ---- (a) documents -> per-token vectors -> packed codes
+    w = synth.make_q8_encoder(c["layers"], c["hidden"], c["heads"], c["inter"], vocab=c["vocab"], max_pos=c["max_pos"],
+                              seed=501)
+    enc = eos_b200.BertEmbedder(rt, attention_window=c["window"], **w)
+    rng = np.random.default_rng(502)
+    enc.set_token_head(synth.f16_round(rng.standard_normal((c["hidden"], c["token_dim"]), dtype=np.float32) * np.float32(0.05)))
+    B, T = c["batch"], c["tokens"]
+    ids = torch.from_numpy(rng.integers(0, c["vocab"], size=(B, T), dtype=np.int32)).cuda()
+    mask = torch.ones((B, T), dtype=torch.int32, device="cuda")
+    vec = torch.empty((B * T, c["token_dim"]), dtype=torch.float32, device="cuda")
+    spec = eos_b200.make_rotation_spec(c["token_dim"], c["bits"], seed=402)
+    qz = eos_b200.Quantizer(rt, spec)
+    dcodes = torch.empty((B * T, spec.code_bytes), dtype=torch.uint8, device="cuda")
+    dnorms = torch.empty((B * T,), dtype=torch.float32, device="cuda")
+
+    def encode_step():
+        n = enc.token_vectors_device(ids.data_ptr(), mask.data_ptr(), None, B, T, vec.data_ptr(), None, stream)
+        qz.quantize_device(vec.data_ptr(), B * T, dcodes.data_ptr(), dnorms.data_ptr(), stream)
+        return n + 1
+
+    for _ in range(3):
+        encode_step()
+    enc.sync(stream)
+    steps = max(1, min(args.steps, 10))
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        launches += encode_step()
+    e1.record()
+    barrier()
+    enc.sync(stream)
+    enc_ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+    D, F, L, W = c["hidden"], c["inter"], c["layers"], c["window"]
+    flops_seq = T * L * (2.0 * (4 * D * D + 2 * D * F) + 4.0 * W * D) + 2.0 * T * D * c["token_dim"]
+    enc_out = {"ms_per_batch": enc_ms, "sequences_per_s": B * world / (enc_ms / 1e3),
+               "tokens_per_s": B * T * world / (enc_ms / 1e3), "tflops": B * flops_seq / (enc_ms / 1e3) / 1e12,
+               "frac_of_sustained_tensor_peak": B * flops_seq / (enc_ms / 1e3) / 1e12 / peaks["tflops"],
+               "algorithmic_gflop_per_sequence": flops_seq / 1e9, "per_gpu_batch": B, "steps": steps,
+               "includes": "per-token head, L2 normalisation and 2-bit packing of 131072 vectors"}
+    vnorm = float(torch.linalg.norm(vec[:64], dim=1).mean().item())
+    assert abs(vnorm - 1.0) < 1e-2, vnorm
+    enc.close()
+    del vec, dcodes, dnorms, ids, mask
+    torch.cuda.empty_cache()
+    # ---- (b) late interaction over the sharded document set (synthetic unit-Gaussian child vectors)
+    docs, ch = c["docs"], c["children"]
+    shard = (docs + world - 1) // world
+    lo = min(docs, rank * shard)
+    n_docs = max(0, min(docs, lo + shard) - lo)
+    n_child = n_docs * ch
+    codes = torch.empty((max(1, n_child), spec.code_bytes), dtype=torch.uint8, device="cuda")
+    norms = torch.empty((max(1, n_child),), dtype=torch.float32, device="cuda")
+    chunk = 2_000_000
+    xbuf = torch.empty((min(chunk, max(1, n_child)), c["token_dim"]), dtype=torch.float32, device="cuda")
+    for c0 in range(0, n_child, chunk):
+        c1 = min(n_child, c0 + chunk)
+        tq.synth_gaussian_device(rt, 503, lo * ch + c0, c1 - c0, c["token_dim"], True, xbuf.data_ptr(), stream)
+        qz.quantize_device(xbuf.data_ptr(), c1 - c0, codes[c0:].data_ptr(), norms[c0:].data_ptr(), stream)
+    torch.cuda.synchronize()
+    corpus = eos_b200.Corpus(qz, device_ptrs=(codes.data_ptr(), norms.data_ptr(), n_child), id_base=lo * ch)
+    del xbuf
+    nq, qt, k = c["queries"], c["query_tokens"], c["k"]
+    queries = torch.empty((nq * qt, c["token_dim"]), dtype=torch.float32, device="cuda")
+    tq.synth_gaussian_device(rt, 504, 0, nq * qt, c["token_dim"], True, queries.data_ptr(), stream)
+    queries = queries.half().float().contiguous()
+    out_ids = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+    out_sc = torch.empty((nq, k), dtype=torch.float32, device="cuda")
+    keys = torch.empty((nq, k), dtype=torch.int64, device="cuda")
+
+    def score_step():
+        if world == 1:
+            return corpus.maxsim_topk_device(queries.data_ptr(), nq * qt, qt, ch, k, out_ids.data_ptr(), out_sc.data_ptr(),
+                                             None, stream)
+        n = corpus.maxsim_topk_device(queries.data_ptr(), nq * qt, qt, ch, k, None, None, keys.data_ptr(), stream)
+        comm.merge_keys(keys.data_ptr(), nq, k, out_ids.data_ptr(), out_sc.data_ptr(), stream)
+        return n + 1
+
+    for _ in range(2):
+        score_step()
+    corpus.sync(stream)
+    barrier()
+    corpus.profile_begin(steps * (nq * qt // 128) + 8)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        launches += score_step()
+    e1.record()
+    barrier()
+    k_ms, k_launches = corpus.profile_end(stream)
+    ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+    flops = 2.0 * nq * qt * docs * ch * c["token_dim"]
+    dimp = (c["token_dim"] + 127) // 128 * 128
+    k_flops = 2.0 * 128 * n_child * dimp
+    k_avg = k_ms / max(1, k_launches)
+    res = {"document_encoder": enc_out,
+           "maxsim": {"ms_per_step": ms, "query_doc_pairs_per_s": nq * docs / (ms / 1e3), "tflops": flops / (ms / 1e3) / 1e12,
+                      "scaling": "strong", "steps": steps,
+                      "config": {"workload": f"{nq} queries x {qt} token vectors vs {docs} documents x {ch} vectors of "
+                                             f"{c['token_dim']} dims at {c['bits']} bits, top-{k}; documents sharded over "
+                                             f"{world} GPU(s)",
+                                 "bytes_per_vector": spec.vector_bytes,
+                                 "merge": "none" if world == 1 else "NCCL all-gather of per-shard parent lists + merge kernel "
+                                                                    "(eos_b200_comm_merge_keys)"},
+                      "roofline": {"bound": "tensor", "kernel": "tq_score_tc_kernel (late-interaction epilogue)",
+                                   "achieved": k_flops / (k_avg / 1e3) / 1e12 if k_avg > 0 else None, "peak": peaks["tflops"],
+                                   "unit": "TFLOP/s", "avg_launch_ms": k_avg, "launches_per_step": k_launches // max(1, steps),
+                                   "algorithmic_flops_per_launch": k_flops,
+                                   "frac": k_flops / (k_avg / 1e3) / 1e12 / peaks["tflops"] if k_avg > 0 else None,
+                                   "traffic": None}},
+           "_launches": launches}
+    assert bool((out_ids[:, 0] >= 0).all().item()) and bool(torch.isfinite(out_sc).all().item())
+    # outside the timed region: the fused kernel against the general parent aggregation (every child score written
+    # out, then grouped by parent) on the first 2000 documents of this rank's shard, 4 queries
+    if n_docs >= 2000:
+        sub_docs, cq = 2000, 4
+        sub = eos_b200.Corpus(qz, device_ptrs=(codes.data_ptr(), norms.data_ptr(), sub_docs * ch), id_base=0)
+        s_ids = torch.empty((cq, k), dtype=torch.int64, device="cuda")
+        s_sc = torch.empty((cq, k), dtype=torch.float32, device="cuda")
+        sub.maxsim_topk_device(queries.data_ptr(), cq * qt, qt, ch, k, s_ids.data_ptr(), s_sc.data_ptr(), None, stream)
+        sub.sync(stream)
+        g_ids, g_sc = sub.parent_topk(np.repeat(np.arange(sub_docs, dtype=np.int32), ch), sub_docs,
+                                      queries[:cq * qt].cpu().numpy(), k, query_group=qt)
+        same = float((s_ids.cpu().numpy() == g_ids).mean())
+        err = float(np.abs(s_sc.cpu().numpy() - g_sc).max() / np.abs(g_sc).max())
+        assert same >= 0.98 and err <= 1e-4, f"late-interaction kernel and general aggregation disagree: {same}, {err}"
+        res["maxsim"]["self_check"] = {"documents": sub_docs, "queries": cq, "ids_equal_fraction": same,
+                                       "max_rel_score_diff": err, "against": "eos_b200_parent_topk (all child scores)"}
+        sub.close()
+    del codes
+    corpus.close()
+    qz.close()
+    return res
+
+
+def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks, comm):
     import torch
     import torch.distributed as dist
 
@@ -542,16 +711,6 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
     queries = queries.half().float().contiguous()  # the configuration's queries are f16
     ids = torch.empty((nq, k), dtype=torch.int64, device="cuda")
     scores = torch.empty((nq, k), dtype=torch.float32, device="cuda")
-    # N > 1: the library's own communicator (NCCL inside the C ABI); torch.distributed only carries the 128-byte id
-    comm = None
-    if world > 1:
-        from eos_b200 import dist as edist
-        id_t = torch.zeros((edist.NCCL_ID_BYTES,), dtype=torch.uint8, device="cuda")
-        if rank == 0:
-            id_t.copy_(torch.frombuffer(bytearray(edist.new_comm_id()), dtype=torch.uint8))
-        dist.broadcast(id_t, src=0)
-        comm = edist.Comm(rt, rank, world, bytes(id_t.cpu().numpy().tobytes()))
-
     def measure(per_pass, steps, with_e2e):
         launches = 0
 
@@ -666,8 +825,6 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
         out["_launches"] += st["_launches"]
     if rank == 0 and world == 1 and not args.skip_cpu:
         out["cpu_baseline"] = time_oracle_scoring(spec, rt, qz)
-    if comm is not None:
-        comm.close()
     corpus.close()
     qz.close()
     return out
@@ -708,6 +865,7 @@ def main():
                     help="how the projection kernel receives the 8-bit weights (results are bit-identical)")
     ap.add_argument("--skip-other-mode", action="store_true", help="do not also time the other weight mode")
     ap.add_argument("--skip-small-configs", action="store_true", help="do not also time configurations 1 and 2")
+    ap.add_argument("--skip-long-context", action="store_true", help="do not also time configuration 5")
     ap.add_argument("--tq-steps", type=int, default=10)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -407,6 +407,11 @@ struct EosB200Encoder {
     float2* rope_cs = nullptr;   // [rope_tokens, hidden / 2] (cos, sin), workspace
     int rope_tokens = 0;
     GemmPlan outp_plan{};
+    // per-token output head (long-context multi-vector documents): [token_dim, hidden] dense, no bias
+    DenseW tokp;
+    int token_dim = 0;
+    __half* tok_f16 = nullptr;   // [m_alloc, token_dim] workspace
+    GemmPlan tokp_plan{};
 };
 
 namespace {
@@ -432,6 +437,7 @@ void free_workspace(EosB200Encoder* e) {
     dev_free(e->ffn);
     dev_free(e->pooled);
     dev_free(e->d_out);
+    dev_free(e->tok_f16);
     e->plans.clear();
     e->cap_batch = 0;
     e->cap_elems = 0;
@@ -537,6 +543,22 @@ int ensure_workspace(EosB200Encoder* e, int batch, int tokens, char** err) {
             if (!ge.empty()) return fail(err, "encoder layer " + std::to_string(l) + ": " + ge);
         }
     }
+    if (e->token_dim > 0) {
+        CUDA_TRY(dev_alloc(&e->tok_f16, (size_t)m * e->token_dim));
+        GemmParams p{};
+        p.m_ptr = e->lay.total_rows;
+        p.m_alloc = m;
+        p.n = e->tokp.n;
+        p.k = e->tokp.k;
+        p.scale = e->tokp.scale;
+        p.bias = nullptr;
+        p.out = e->tok_f16;
+        p.ldo = e->token_dim;
+        p.mode = kEpiBias;
+        p.status = e->rt->d_status;
+        std::string ge = gemm_make_plan(&e->tokp_plan, e->h0, D, e->tokp.w, e->tokp.ldw, e->tokp.int8, p, e->rt->sm_count);
+        if (!ge.empty()) return fail(err, "token head: " + ge);
+    }
     if (e->compact) {
         if (e->outp.w != nullptr) {
             GemmParams p{};
@@ -558,6 +580,7 @@ int ensure_workspace(EosB200Encoder* e, int batch, int tokens, char** err) {
 }
 
 // Enqueues the whole forward on `s`; returns the number of kernels launched.
+// d_out == nullptr: stop after the last layer (the final hidden states stay in e->h0).
 int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_mask, const int32_t* d_types, int batch,
                     int tokens, float* d_out, cudaStream_t s) {
     EosB200Runtime* rt = e->rt;
@@ -596,6 +619,10 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
             launch_layernorm(e->pre, w.g2, w.b2, e->eps, D, e->m_alloc, e->lay.total_rows, e->h0, rt->sm_count, s);
         });
         launches += 7;
+    }
+    if (d_out == nullptr) {
+        e->launches_per_forward = launches;
+        return launches;
     }
     if (e->compact) {
         if (e->outp.w != nullptr) {
@@ -636,6 +663,7 @@ void eos_b200_encoder_destroy(EosB200Encoder* enc) {
     dev_free(enc->role);
     dev_free(enc->rope_cs);
     free_dense(enc->outp);
+    free_dense(enc->tokp);
     for (auto& w : enc->lw) {
         free_dense(w.qkv);
         free_dense(w.ao);
@@ -866,6 +894,57 @@ int eos_b200_encoder_run_device(EosB200Encoder* enc, const int32_t* d_ids, const
     cudaStream_t s = pick_stream(enc->rt, stream);
     CUDA_TRY(cudaMemsetAsync(enc->rt->d_status, 0, sizeof(int), s));
     const int launches = enqueue_forward(enc, d_ids, d_mask, d_types, batch, tokens, d_out, s);
+    CUDA_TRY(cudaGetLastError());
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+    }
+    return EOS_B200_OK;
+}
+
+int eos_b200_encoder_set_token_head(EosB200Encoder* enc, const float* h_weights, int token_dim, char** err) {
+    if (enc == nullptr || h_weights == nullptr) return fail(err, "encoder_set_token_head: null argument");
+    if (token_dim <= 0 || token_dim % 8 != 0 || token_dim > 1024)
+        return fail(err, "encoder_set_token_head: token_dim must be a multiple of 8 in [8, 1024]");
+    CUDA_TRY(cudaSetDevice(enc->rt->device));
+    CUDA_TRY(cudaStreamSynchronize(enc->rt->stream));
+    const int D = enc->hidden;
+    // [hidden, token_dim] in-major (as a projection head is stored) -> [token_dim, hidden] for the projection kernel
+    std::vector<float> wt((size_t)token_dim * D);
+    for (int i = 0; i < D; ++i)
+        for (int j = 0; j < token_dim; ++j) wt[(size_t)j * D + i] = h_weights[(size_t)i * token_dim + j];
+    EosB200Matrix m{};
+    m.rows = token_dim;
+    m.cols = D;
+    m.dense = wt.data();
+    free_dense(enc->tokp);
+    std::string msg = upload_dense({&m}, {nullptr}, EOS_B200_WEIGHTS_F16_RESIDENT, &enc->tokp);
+    if (!msg.empty()) return fail(err, "encoder_set_token_head: " + msg);
+    enc->token_dim = token_dim;
+    free_workspace(enc);   // the next run re-plans with the head's buffers
+    return EOS_B200_OK;
+}
+
+int eos_b200_encoder_token_vectors_device(EosB200Encoder* enc, const int32_t* d_ids, const int32_t* d_mask,
+                                          const int32_t* d_types, int batch, int tokens, float* d_vectors,
+                                          int32_t* d_row_count, void* stream, EosB200Stats* stats, char** err) {
+    if (enc == nullptr || d_ids == nullptr || d_mask == nullptr || d_vectors == nullptr)
+        return fail(err, "encoder_token_vectors: null argument");
+    if (enc->token_dim <= 0) return fail(err, "encoder_token_vectors: no token head set (eos_b200_encoder_set_token_head)");
+    if (enc->compact) return fail(err, "encoder_token_vectors: not available for the compact profile");
+    if (batch <= 0 || tokens <= 0) return fail(err, "bert_embedder input_ids must be a non-empty [B,T] tensor");
+    if (tokens > enc->max_pos) return fail(err, "bert_embeddings position_ids value out of range (tokens > max_positions)");
+    CUDA_TRY(cudaSetDevice(enc->rt->device));
+    int rc = ensure_workspace(enc, batch, tokens, err);
+    if (rc != EOS_B200_OK) return rc;
+    cudaStream_t s = pick_stream(enc->rt, stream);
+    CUDA_TRY(cudaMemsetAsync(enc->rt->d_status, 0, sizeof(int), s));
+    int launches = enqueue_forward(enc, d_ids, d_mask, d_types, batch, tokens, nullptr, s);
+    gemm_launch(enc->tokp_plan, s);
+    launch_rows_normalize_f32(enc->tok_f16, enc->lay, enc->token_dim, enc->m_alloc, d_vectors, enc->rt->sm_count, s);
+    launches += 2;
+    if (d_row_count != nullptr)
+        CUDA_TRY(cudaMemcpyAsync(d_row_count, enc->lay.total_rows, sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
     CUDA_TRY(cudaGetLastError());
     if (stats != nullptr) {
         std::memset(stats, 0, sizeof(*stats));

@@ -1039,6 +1039,29 @@ void dispatch_chunks(int dim, F&& f) {
     else f(std::integral_constant<int, 8>());
 }
 
+// out[r,:] (fp32) = x[r,:] (f16) / ||x[r,:]|| for the packed rows r < *total_rows (a zero row stays zero);
+// one warp per row, norm accumulated in fp32.
+__global__ void __launch_bounds__(256)
+rows_normalize_f32_kernel(const __half* __restrict__ x, int dim, int m_alloc, const int* __restrict__ total_rows,
+                          float* __restrict__ out) {
+    int rows = *total_rows;
+    rows = rows < m_alloc ? rows : m_alloc;
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const __half* xr = x + (size_t)r * dim;
+        float sq = 0.f;
+        for (int c = lane; c < dim; c += 32) {
+            const float v = __half2float(xr[c]);
+            sq = fmaf(v, v, sq);
+        }
+        sq = warp_sum(sq);
+        const float inv = sq > 0.f ? rsqrtf(sq) : 0.f;
+        float* o = out + (size_t)r * dim;
+        for (int c = lane; c < dim; c += 32) o[c] = __half2float(xr[c]) * inv;
+    }
+}
+
 }  // namespace
 
 void launch_seq_layout(const int32_t* mask, int batch, int tokens, int cls_pooling, int window, const SeqLayout& lay,
@@ -1106,6 +1129,11 @@ void launch_embed_rope(const int32_t* ids, const int32_t* roles, const SeqLayout
                                                                      vocab, role_tab, role_vocab, rope_cs, rope_tokens,
                                                                      dim, m_alloc, out, status);
     });
+}
+
+void launch_rows_normalize_f32(const __half* x, const SeqLayout& lay, int dim, int m_alloc, float* out, int sm_count,
+                                cudaStream_t stream) {
+    rows_normalize_f32_kernel<<<sm_count * 8, 256, 0, stream>>>(x, dim, m_alloc, lay.total_rows, out);
 }
 
 void launch_token_normalize(__half* x, const SeqLayout& lay, int dim, int m_alloc, int sm_count, cudaStream_t stream) {

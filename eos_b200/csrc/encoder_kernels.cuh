@@ -50,6 +50,9 @@ void launch_pool_head(const __half* hidden_states, const SeqLayout& lay, int bat
 void launch_embed_rope(const int32_t* ids, const int32_t* roles, const SeqLayout& lay, int tokens, const __half* tok,
                        int vocab, const __half* role_tab, int role_vocab, const float2* rope_cs, int rope_tokens, int dim,
                        int m_alloc, __half* out, int* status, int sm_count, cudaStream_t stream);
+// out [rows, dim] fp32 = the packed f16 rows, each divided by its L2 norm (zero rows stay zero).
+void launch_rows_normalize_f32(const __half* x, const SeqLayout& lay, int dim, int m_alloc, float* out, int sm_count,
+                                cudaStream_t stream);
 // In place per-row L2 normalisation of the packed rows (zero rows untouched).
 void launch_token_normalize(__half* x, const SeqLayout& lay, int dim, int m_alloc, int sm_count, cudaStream_t stream);
 // out [B, dim] fp32 = mean over each sequence's valid tokens of the (optionally L2-normalised) rows.

@@ -214,6 +214,23 @@ class BertEmbedder:
                   stream, C.byref(st))
         return st.kernel_launches
 
+    def set_token_head(self, weights) -> None:
+        """Per-token output head [hidden, token_dim] (in-major, no bias): enables token_vectors_device."""
+        w = _f32(weights)
+        if w.ndim != 2:
+            raise ValueError("token head weights must be [hidden, token_dim]")
+        _lib.call("eos_b200_encoder_set_token_head", self.handle, _ptr(w), int(w.shape[1]))
+        self.token_dim = int(w.shape[1])
+
+    def token_vectors_device(self, d_ids: int, d_mask: int, d_types: Optional[int], batch: int, tokens: int,
+                             d_vectors: int, d_row_count: Optional[int] = None, stream: Optional[int] = None) -> int:
+        """L2-normalised per-token vectors of the valid tokens (sequence after sequence, token order) into
+        d_vectors [rows, token_dim] fp32 on the device; returns kernels launched."""
+        st = Stats()
+        _lib.call("eos_b200_encoder_token_vectors_device", self.handle, d_ids, d_mask, d_types, int(batch), int(tokens),
+                  d_vectors, d_row_count, stream, C.byref(st))
+        return st.kernel_launches
+
     def sync(self, stream: Optional[int] = None) -> None:
         _lib.call("eos_b200_encoder_sync", self.handle, stream)
 

@@ -199,6 +199,18 @@ EOS_B200_API int eos_b200_compact_encoder_bind(EosB200Runtime* rt, const EosB200
 EOS_B200_API int eos_b200_encoder_run_device(EosB200Encoder* enc, const int32_t* d_ids, const int32_t* d_mask,
                                 const int32_t* d_types, int batch, int tokens, float* d_out, void* stream,
                                 EosB200Stats* stats, char** err);
+/* Per-token output vectors (the long-context multi-vector document path; no single counterpart in Eos, whose
+ * multi-vector documents come from span pooling, runtime/sparse_token_pool_vector_export.go): a projection
+ * [hidden, token_dim] (in-major, no bias, as a projection head is stored) applied to every valid token's final
+ * hidden row, then L2 normalisation.  set_token_head is called once after bind (the CLS-pooling row layout is
+ * not supported together with it).  token_vectors_device runs the forward on `stream` and writes the vectors of
+ * the valid tokens, sequence after sequence in token order, to d_vectors [rows, token_dim] fp32 (rows <=
+ * batch * tokens; the count is written to d_row_count when non-null); they are the input of
+ * eos_b200_quantize_device. */
+EOS_B200_API int eos_b200_encoder_set_token_head(EosB200Encoder* enc, const float* h_weights, int token_dim, char** err);
+EOS_B200_API int eos_b200_encoder_token_vectors_device(EosB200Encoder* enc, const int32_t* d_ids, const int32_t* d_mask,
+                                                       const int32_t* d_types, int batch, int tokens, float* d_vectors,
+                                                       int32_t* d_row_count, void* stream, EosB200Stats* stats, char** err);
 /* Per-kernel-class device time of the forwards enqueued between profile_begin and profile_end,
  * taken with CUDA events recorded around every launch on the launching stream.  The reference
  * keeps the same kind of evidence as CUDA-event phase pairs (native_linux.go:285-498,

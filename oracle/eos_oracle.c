@@ -556,6 +556,54 @@ EOS_ORACLE_API int eos_oracle_bert_embedder(const int32_t *input_ids, const int3
     return 0;
 }
 
+/* Per-token output vectors (long-context multi-vector documents): the same embeddings and layers, then for every
+ * token with mask != 0 the final hidden row times token_w [hidden, token_dim] (in-major, no bias, double accumulate
+ * like the projection head of runtime/pretrained_bert_projection_head.go:84-100) and normalizeRetrievalVector
+ * (runtime/retrieval_eval.go:1040-1054).  out is [batch, tokens, token_dim]; rows of masked tokens are zero. */
+EOS_ORACLE_API int eos_oracle_bert_token_vectors(const int32_t *input_ids, const int32_t *mask, const int32_t *type_ids,
+                                                 int batch, int tokens, const float *tok, int vocab, const float *pos,
+                                                 int max_pos, const float *typ, int type_vocab, const float *emb_gamma,
+                                                 const float *emb_beta, const float *const *layer_weights, int layers,
+                                                 int hidden, int inter, int heads, double eps, const float *token_w,
+                                                 int token_dim, int window, float *out, int workers) {
+    int64_t rows = (int64_t)batch * tokens;
+    int32_t *pos_ids = (int32_t *)malloc(sizeof(int32_t) * (size_t)rows);
+    for (int b = 0; b < batch; b++)
+        for (int t = 0; t < tokens; t++) pos_ids[(int64_t)b * tokens + t] = t;
+    float *hs = (float *)malloc(sizeof(float) * (size_t)(rows * hidden));
+    int rc = eos_oracle_bert_embeddings(tok, vocab, pos, max_pos, typ, type_vocab, emb_gamma, emb_beta, input_ids,
+                                        pos_ids, type_ids, rows, hidden, eps, hs);
+    free(pos_ids);
+    if (rc != 0) {
+        free(hs);
+        return rc;
+    }
+    for (int l = 0; l < layers; l++)
+        bert_layer_impl(hs, mask, batch, tokens, hidden, inter, heads, layer_weights + (size_t)l * 16, eps, window,
+                        workers);
+    for (int64_t r = 0; r < rows; r++) {
+        float *o = out + r * token_dim;
+        if (mask[r] == 0) {
+            memset(o, 0, sizeof(float) * (size_t)token_dim);
+            continue;
+        }
+        const float *vec = hs + r * hidden;
+        double sq = 0.0;
+        for (int j = 0; j < token_dim; j++) {
+            double sum = 0.0;
+            for (int i = 0; i < hidden; i++) sum += (double)vec[i] * (double)token_w[(int64_t)i * token_dim + j];
+            o[j] = (float)sum;
+        }
+        for (int j = 0; j < token_dim; j++) sq += (double)o[j] * (double)o[j];
+        if (sq != 0.0) {
+            float sc = (float)(1.0 / sqrt(sq));
+            for (int j = 0; j < token_dim; j++) o[j] *= sc;
+        }
+    }
+    free(hs);
+    return 0;
+}
+
 /* ------------------------------------------------------------------------------------ */
 /* TurboQuant, Hadamard/MSE variant (PARITY UNPINNED, see header).                        */
 /* Structure follows Eos's device restatement runtime/backends/cuda/native_linux.go:      */

@@ -239,6 +239,29 @@ def bert_embedder(input_ids, mask, type_ids, tok, pos, typ, emb_gamma, emb_beta,
     return out
 
 
+def bert_token_vectors(input_ids, mask, type_ids, tok, pos, typ, emb_gamma, emb_beta, layer_weights: Sequence[np.ndarray],
+                       heads: int, token_w, eps=1e-12, workers: int = 1, window: int = 0):
+    """[B, T, token_dim] per-token vectors: final hidden rows times token_w [hidden, token_dim], L2-normalised;
+    masked tokens give zero rows."""
+    ids, m, tids = map(_i32, (input_ids, mask, type_ids))
+    tok, pos, typ, eg, eb = map(_f32, (tok, pos, typ, emb_gamma, emb_beta))
+    ws = [_f32(w) for w in layer_weights]
+    layers = len(ws) // 16
+    b, t = ids.shape
+    hidden = tok.shape[1]
+    inter = ws[10].shape[0]
+    tw = _f32(token_w)
+    out = np.empty((b, t, tw.shape[1]), dtype=np.float32)
+    rc = lib().eos_oracle_bert_token_vectors(_p(ids), _p(m), _p(tids), C.c_int(b), C.c_int(t), _p(tok), C.c_int(tok.shape[0]),
+                                             _p(pos), C.c_int(pos.shape[0]), _p(typ), C.c_int(typ.shape[0]), _p(eg), _p(eb),
+                                             _ptr_array(ws), C.c_int(layers), C.c_int(hidden), C.c_int(inter),
+                                             C.c_int(heads), C.c_double(eps), _p(tw), C.c_int(tw.shape[1]),
+                                             C.c_int(window), _p(out), C.c_int(workers))
+    if rc:
+        raise IndexError(["", "input_ids", "position_ids", "token_type_ids"][rc] + " value out of range")
+    return out
+
+
 # --------------------------------------------------------------------------------- TurboQuant
 def tq_code_bytes(dim: int, bits: int) -> int:
     return int(lib().eos_oracle_tq_code_bytes(C.c_int(dim), C.c_int(bits)))

@@ -190,3 +190,53 @@ def test_c4_path_large_shard(rt):
     sub.close()
     corpus.close()
     qz.close()
+
+
+def test_per_token_vectors_long_context(rt):
+    """The document side of the long-context multi-vector configuration at reduced depth: 2 layers, D = 512, 8 heads,
+    T = 1536 with a 512-token window, a 512 -> 128 per-token head; the GPU's per-token vectors against the oracle's,
+    and their 2-bit packing bit-exact against the oracle's packing of the GPU vectors."""
+    import torch
+    import eos_b200
+    from eos_b200 import synth
+    from oracle import oracle as O
+    T, D, heads, window, tdim = 1536, 512, 8, 512, 128
+    args = synth.make_q8_encoder(2, D, heads, 2048, vocab=2000, max_pos=T, seed=55)
+    rng = np.random.default_rng(56)
+    tw = synth.f16_round(rng.standard_normal((D, tdim), dtype=np.float32) * np.float32(0.05))
+    ids = rng.integers(0, 2000, size=(3, T), dtype=np.int32)
+    lengths = np.array([T, 700, 130])
+    mask = (np.arange(T)[None, :] < lengths[:, None]).astype(np.int32)
+    enc = eos_b200.BertEmbedder(rt, attention_window=window, **args)
+    enc.set_token_head(tw)
+    d_ids, d_mask = torch.from_numpy(ids).cuda(), torch.from_numpy(mask).cuda()
+    rows = int(mask.sum())
+    d_vec = torch.zeros((3 * T, tdim), dtype=torch.float32, device="cuda")
+    d_rows = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    enc.token_vectors_device(d_ids.data_ptr(), d_mask.data_ptr(), None, 3, T, d_vec.data_ptr(), d_rows.data_ptr())
+    enc.sync()
+    assert int(d_rows.item()) == rows
+    got = d_vec[:rows].cpu().numpy()
+    ref = O.bert_token_vectors(ids, mask, np.zeros_like(ids), args["token_embeddings"], args["position_embeddings"],
+                               args["token_type_embeddings"], args["embedding_ln_weight"], args["embedding_ln_bias"],
+                               synth.dequantized_layer_weights(args["layer_weights"]), heads, tw, window=window,
+                               workers=O.default_workers())
+    ref = ref[mask.astype(bool)]
+    assert np.isfinite(got).all()
+    assert np.abs(np.linalg.norm(got, axis=1) - 1).max() < 1e-3
+    assert np.abs(got - ref).max() <= 3e-3           # per-token rows are 128-d unit vectors: entries ~0.09
+    assert cosine_rows(got, ref).min() >= 0.9995
+    # the pooled embedding of the same handle still works, and packing the vectors is bit-exact
+    spec = eos_b200.make_rotation_spec(tdim, 2, seed=402)
+    qz = eos_b200.Quantizer(rt, spec)
+    codes = torch.empty((rows, tdim // 4), dtype=torch.uint8, device="cuda")
+    norms = torch.empty((rows,), dtype=torch.float32, device="cuda")
+    qz.quantize_device(d_vec.data_ptr(), rows, codes.data_ptr(), norms.data_ptr())
+    torch.cuda.synchronize()
+    rc, rn = O.tq_encode(got, 2, spec.perm, spec.signs1, spec.signs2, spec.boundaries)
+    assert np.array_equal(codes.cpu().numpy(), rc) and np.array_equal(norms.cpu().numpy(), rn)
+    pooled = enc.run(ids, mask)
+    assert np.isfinite(pooled).all() and np.abs(np.linalg.norm(pooled[0]) - 1) < 1e-3
+    qz.close()
+    enc.close()
