@@ -136,6 +136,10 @@ SYMBOLS = {
     "eos_b200_dense_destroy": (None, [_P]),
     "eos_b200_dense_score_topk": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_dense_rerank": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
+    "eos_b200_sparse_attention": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                            C.c_int, _P, C.POINTER(Stats), _ERR]),
+    "eos_b200_turbo_sparse_attention": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                  C.c_int, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_synth_gaussian_device": (C.c_int, [_P, C.c_uint64, C.c_int64, C.c_int64, C.c_int, C.c_int, _P, _P,
                                                  _ERR]),
 }

@@ -18,6 +18,7 @@
 #include "attention_tc.cuh"
 #include "encoder_kernels.cuh"
 #include "gemm_tc.cuh"
+#include "sparse_attention.cuh"
 #include "turboquant.cuh"
 
 using namespace eosb;
@@ -162,6 +163,7 @@ int eos_b200_runtime_create(int device, EosB200Runtime** out, char** err) {
         if (se == cudaSuccess && (se = tq_tc_init()) != cudaSuccess) ge = std::string("tq_tc_init: ") + cudaGetErrorString(se);
         if (se == cudaSuccess && (se = tq_tc256_init()) != cudaSuccess) ge = std::string("tq_tc256_init: ") + cudaGetErrorString(se);
         if (se == cudaSuccess && (se = tq_merge_init()) != cudaSuccess) ge = std::string("tq_merge_init: ") + cudaGetErrorString(se);
+        if (se == cudaSuccess && (se = sparse_attention_init()) != cudaSuccess) ge = std::string("sparse_attention_init: ") + cudaGetErrorString(se);
     }
     if (!ge.empty()) {
         eos_b200_runtime_destroy(rt);
@@ -1513,7 +1515,8 @@ int enqueue_tc_passes(EosB200Corpus* c, int plan, int64_t n_docs, int q_count, i
 }
 
 // Late-interaction launches (plan 0: 128 query vectors per launch = 128 / group queries): every launch walks the whole
-// shard, keeps per-query candidate lists of parent keys and is followed by the merge of its queries' lists.
+// shard and keeps per-query candidate lists of parent keys; the lists of up to 128 queries (several launches) are
+// merged by one launch.
 int enqueue_maxsim_passes(EosB200Corpus* c, int q_vectors, int group, int children, int k, int64_t* d_ids, float* d_scores,
                           uint64_t* d_keys, cudaStream_t s) {
     EosB200Quantizer* qz = c->qz;
@@ -1521,9 +1524,23 @@ int enqueue_maxsim_passes(EosB200Corpus* c, int q_vectors, int group, int childr
     const int64_t tiles = (c->n + p.tile_docs - 1) / p.tile_docs;
     const int grid = (int)(tiles < p.grid ? tiles : p.grid);
     const int n_segs = p.segs_per_cta * grid;
+    const int per_launch = p.queries / group;   // queries of one launch
     int launches = 0;
+    int pending = 0;        // queries whose lists wait for the merge
+    int first_pending = 0;  // index of the first of them
+    auto merge = [&] {
+        if (pending == 0) return;
+        const size_t out0 = (size_t)first_pending * k;
+        launch_tq_merge_lists(p.cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, p.count, pending, k,
+                              d_ids != nullptr ? d_ids + out0 : nullptr, d_scores != nullptr ? d_scores + out0 : nullptr,
+                              d_keys != nullptr ? d_keys + out0 : nullptr, s);
+        ++launches;
+        first_pending += pending;
+        pending = 0;
+    };
     for (int q0 = 0; q0 < q_vectors; q0 += p.queries) {
         const int q_here = (q_vectors - q0) < p.queries ? (q_vectors - q0) : p.queries;
+        if (pending + per_launch > p.queries) merge();
         TqTcArgs a{};
         a.tiles = c->tiles;
         a.norms = c->norms;
@@ -1546,14 +1563,12 @@ int enqueue_maxsim_passes(EosB200Corpus* c, int q_vectors, int group, int childr
         a.status = qz->rt->d_status;
         a.maxsim_children = children;
         a.maxsim_group = group;
+        a.maxsim_list_base = pending;
         c->prof.launch(kClsScan, s, [&] { launch_tq_score_tc(p.tm, a, p.q_in_tmem, grid, s); });
-        const int queries_here = q_here / group;
-        const size_t out0 = (size_t)(q0 / group) * k;
-        launch_tq_merge_lists(p.cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, p.count, queries_here, k,
-                              d_ids != nullptr ? d_ids + out0 : nullptr, d_scores != nullptr ? d_scores + out0 : nullptr,
-                              d_keys != nullptr ? d_keys + out0 : nullptr, s);
-        launches += 2;
+        ++launches;
+        pending += q_here / group;
     }
+    merge();
     return launches;
 }
 
@@ -2672,6 +2687,170 @@ int eos_b200_dense_rerank(EosB200DenseIndex* ix, const float* h_queries, int q_c
     dev_free(d_cand);
     dev_free(d_keys);
     return rc;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// sparse attention
+// ------------------------------------------------------------------------------------------------
+namespace {
+// sparseAttentionBudget / normalizeSparseAttentionRoute, runtime/backend/attention_ops.go:445-460, 503-516
+int sparse_budget(int top_k, int key_len) {
+    if (key_len <= 0) return 0;
+    int budget = top_k;
+    if (budget <= 0) budget = (int)std::ceil(std::sqrt((double)key_len));
+    if (budget < 1) budget = 1;
+    if (budget > key_len) budget = key_len;
+    return budget;
+}
+void sparse_route(int key_len, int block_size, int top_blocks, int* bs, int* tb) {
+    *bs = *tb = 0;
+    if (key_len <= 0 || block_size <= 0 || top_blocks <= 0) return;
+    if (block_size > key_len) block_size = key_len;
+    const int block_count = (key_len + block_size - 1) / block_size;
+    if (top_blocks > block_count) top_blocks = block_count;
+    *bs = block_size;
+    *tb = top_blocks;
+}
+
+std::string sparse_check(int batches, int q_len, int k_len, int dim, int vdim, int top_k, int rbs, int rtb, int* budget,
+                         int* bs, int* tb) {
+    if (batches <= 0 || q_len <= 0 || dim <= 0 || vdim <= 0 || k_len < 0) return "sparse_attention: sizes must be positive";
+    if (dim > 4096) return "sparse_attention: query dim above 4096 is not supported";
+    *budget = sparse_budget(top_k, k_len);
+    sparse_route(k_len, rbs, rtb, bs, tb);
+    if (*budget > kSaMaxBudget) return "sparse_attention: top_k above 128 is not supported";
+    if (*tb > kSaMaxBudget) return "sparse_attention: route_top_blocks above 128 is not supported";
+    return "";
+}
+}  // namespace
+
+extern "C" {
+
+int eos_b200_sparse_attention(EosB200Runtime* rt, const float* h_query, const float* h_key, const float* h_value, int batches,
+                              int q_len, int k_len, int dim, int value_dim, int top_k, int route_block_size,
+                              int route_top_blocks, float* h_out, EosB200Stats* stats, char** err) {
+    if (rt == nullptr || h_query == nullptr || h_out == nullptr || (k_len > 0 && (h_key == nullptr || h_value == nullptr)))
+        return fail(err, "sparse_attention expects query, key, and value");
+    int budget = 0, bs = 0, tb = 0;
+    std::string m = sparse_check(batches, q_len, k_len, dim, value_dim, top_k, route_block_size, route_top_blocks, &budget,
+                                 &bs, &tb);
+    if (!m.empty()) return fail(err, m);
+    const size_t nq = (size_t)batches * q_len * dim, nk = (size_t)batches * k_len * dim, nv = (size_t)batches * k_len * value_dim;
+    const size_t no = (size_t)batches * q_len * value_dim;
+    if (k_len == 0) {
+        std::memset(h_out, 0, no * sizeof(float));
+        if (stats != nullptr) std::memset(stats, 0, sizeof(*stats));
+        return EOS_B200_OK;
+    }
+    CUDA_TRY(cudaSetDevice(rt->device));
+    float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
+    cudaStream_t s = rt->stream;
+    cudaError_t e = dev_alloc(&dq, nq);
+    if (e == cudaSuccess) e = dev_alloc(&dk, nk);
+    if (e == cudaSuccess) e = dev_alloc(&dv, nv);
+    if (e == cudaSuccess) e = dev_alloc(&dout, no);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev0, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dq, h_query, nq * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dk, h_key, nk * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dv, h_value, nv * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) {
+        launch_sparse_attention(dq, dk, dv, batches, q_len, k_len, dim, value_dim, budget, bs, tb, dout, rt->sm_count, s);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_out, dout, no * 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev1, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess && stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = 1;
+        stats->uploaded_bytes = (int64_t)(nq + nk + nv) * 4;
+        stats->downloaded_bytes = (int64_t)no * 4;
+        cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+    }
+    dev_free(dq);
+    dev_free(dk);
+    dev_free(dv);
+    dev_free(dout);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(err, std::string("sparse_attention: ") + cudaGetErrorString(e));
+    }
+    return EOS_B200_OK;
+}
+
+int eos_b200_turbo_sparse_attention(EosB200Quantizer* key_qz, EosB200Quantizer* value_qz, const float* h_query,
+                                    const uint8_t* h_key_codes, const uint8_t* h_key_norm_codes,
+                                    const uint8_t* h_value_codes, const uint8_t* h_value_norm_codes, int batches, int q_len,
+                                    int k_len, int top_k, int route_block_size, int route_top_blocks, float* h_out,
+                                    EosB200Stats* stats, char** err) {
+    if (key_qz == nullptr || value_qz == nullptr || h_query == nullptr || h_out == nullptr)
+        return fail(err, "turbo_sparse_attention expects query");
+    if (k_len > 0 && (h_key_codes == nullptr || h_key_norm_codes == nullptr || h_value_codes == nullptr ||
+                      h_value_norm_codes == nullptr))
+        return fail(err, "turbo_sparse_attention: missing compressed key / value tensors");
+    if (key_qz->rt != value_qz->rt) return fail(err, "turbo_sparse_attention: quantizers belong to different runtimes");
+    EosB200Runtime* rt = key_qz->rt;
+    const int dim = key_qz->dim, vdim = value_qz->dim;
+    int budget = 0, bs = 0, tb = 0;
+    std::string m = sparse_check(batches, q_len, k_len, dim, vdim, top_k, route_block_size, route_top_blocks, &budget, &bs, &tb);
+    if (!m.empty()) return fail(err, m);
+    const size_t nq = (size_t)batches * q_len * dim, rows = (size_t)batches * k_len;
+    const size_t no = (size_t)batches * q_len * vdim;
+    if (k_len == 0) {
+        std::memset(h_out, 0, no * sizeof(float));
+        if (stats != nullptr) std::memset(stats, 0, sizeof(*stats));
+        return EOS_B200_OK;
+    }
+    CUDA_TRY(cudaSetDevice(rt->device));
+    float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
+    uint8_t *ck = nullptr, *cv = nullptr, *nk = nullptr, *nv = nullptr;
+    cudaStream_t s = rt->stream;
+    cudaError_t e = dev_alloc(&dq, nq);
+    if (e == cudaSuccess) e = dev_alloc(&dk, rows * dim);
+    if (e == cudaSuccess) e = dev_alloc(&dv, rows * vdim);
+    if (e == cudaSuccess) e = dev_alloc(&dout, no);
+    if (e == cudaSuccess) e = dev_alloc(&ck, rows * dim);
+    if (e == cudaSuccess) e = dev_alloc(&cv, rows * vdim);
+    if (e == cudaSuccess) e = dev_alloc(&nk, rows);
+    if (e == cudaSuccess) e = dev_alloc(&nv, rows);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev0, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dq, h_query, nq * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(ck, h_key_codes, rows * dim, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(cv, h_value_codes, rows * vdim, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(nk, h_key_norm_codes, rows, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(nv, h_value_norm_codes, rows, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) {
+        // the compressed K / V are decoded on the device (the reference decodes them on the host), then attended to
+        launch_tq_decode_rows(ck, nk, (int64_t)rows, key_qz->spec(), dk, rt->sm_count, s);
+        launch_tq_decode_rows(cv, nv, (int64_t)rows, value_qz->spec(), dv, rt->sm_count, s);
+        launch_sparse_attention(dq, dk, dv, batches, q_len, k_len, dim, vdim, budget, bs, tb, dout, rt->sm_count, s);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_out, dout, no * 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev1, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess && stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = 3;
+        stats->uploaded_bytes = (int64_t)nq * 4 + (int64_t)rows * (dim + vdim + 2);
+        stats->downloaded_bytes = (int64_t)no * 4;
+        cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+    }
+    dev_free(dq);
+    dev_free(dk);
+    dev_free(dv);
+    dev_free(dout);
+    dev_free(ck);
+    dev_free(cv);
+    dev_free(nk);
+    dev_free(nv);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(err, std::string("turbo_sparse_attention: ") + cudaGetErrorString(e));
+    }
+    return EOS_B200_OK;
 }
 
 }  // extern "C"

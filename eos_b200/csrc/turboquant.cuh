@@ -114,6 +114,7 @@ struct TqTcArgs {
     // counts and thresholds are indexed by query (query vector / maxsim_group), not by query vector.
     int maxsim_children;
     int maxsim_group;
+    int maxsim_list_base;   // index of this launch's first query among the candidate lists (several launches share one merge)
 };
 cudaError_t tq_tc_init();
 // Tensor map of the permuted query matrix [rows][padded_dim] f16 (rows a multiple of kTqTcQueries).

@@ -134,4 +134,39 @@ __device__ __forceinline__ void dequant8(uint32_t w, uint32_t hi_a, uint32_t hi_
 }
 
 
+// ---------------------------------------------------------------- blocked Hadamard transform (packing, decoding)
+__device__ __forceinline__ int highest_pow2_le(int v) {
+    int p = 1;
+    while ((p << 1) <= v) p <<= 1;
+    return p;
+}
+
+// In-place blocked normalised FWHT of `work` (shared memory) by one warp.  Butterflies are
+// a+b / a-b in float exactly as the sequential form; their order inside a stage is irrelevant.
+__device__ __forceinline__ void warp_fwht_blocks(float* work, int dim, int lane) {
+    int offset = 0, remaining = dim;
+    while (remaining > 0) {
+        const int size = highest_pow2_le(remaining);
+        float* v = work + offset;
+        int lg = 0;
+        for (int step = 1; step < size; step <<= 1, ++lg) {
+            for (int p = lane; p < (size >> 1); p += 32) {
+                const int j = ((p >> lg) << (lg + 1)) + (p & (step - 1));   // step is a power of two
+                const float a = v[j], b = v[j + step];
+                v[j] = __fadd_rn(a, b);
+                v[j + step] = __fsub_rn(a, b);
+            }
+            __syncwarp();
+        }
+        if (size > 1) {
+            const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)size));
+            for (int i = lane; i < size; i += 32) v[i] = __fmul_rn(v[i], scale);
+            __syncwarp();
+        }
+        offset += size;
+        remaining -= size;
+    }
+}
+
+
 }  // namespace eosb

@@ -301,7 +301,8 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
         const bool maxsim = a.maxsim_children > 0;
         const int group = maxsim ? a.maxsim_group : 1;
         const bool owner = (lane & (group - 1)) == 0;
-        const int qlist = maxsim ? qrow / group : qrow;     // list / count / threshold index of this thread
+        const int qtau = maxsim ? qrow / group : qrow;                      // threshold index of this thread
+        const int qlist = maxsim ? a.maxsim_list_base + qtau : qrow;       // list / count index of this thread
         u64* my_list = cand + ((size_t)qlist * n_segs + seg) * kTqTcSegLen;
         u64* sortbuf = reinterpret_cast<u64*>(sm + kOffSort) + ew * kSortCap;
         float* norm_s = reinterpret_cast<float*>(sm + kOffNorm);
@@ -332,13 +333,13 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
             named_bar_sync(1, kEpiWarps * 32);
             if (*epi_stop != 0) break;
             // thresholds other CTAs published; lists that the coming tile could overflow are cut to their k best
-            if (q_live) raise_tau(shared_tau[qlist]);
+            if (q_live) raise_tau(shared_tau[qtau]);
             unsigned need = __ballot_sync(0xffffffffu, cnt > kCutAbove);
             while (need != 0) {
                 const int src = __ffs(need) - 1;
                 need &= need - 1;
                 const int n = __shfl_sync(0xffffffffu, cnt, src);
-                u64* lst = cand + ((size_t)((quarter * 32 + src) / group) * n_segs + seg) * kTqTcSegLen;
+                u64* lst = cand + ((size_t)((maxsim ? a.maxsim_list_base : 0) + (quarter * 32 + src) / group) * n_segs + seg) * kTqTcSegLen;
                 __syncwarp();
                 for (int i = lane; i < n; i += 32) sortbuf[i] = lst[i];
                 warp_sort_desc(sortbuf, n, lane);
@@ -348,7 +349,7 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
                 if (lane == src) {
                     cnt = a.k;
                     raise_tau(kth);
-                    atomicMax(const_cast<u64*>(a.shared_tau) + qlist, kth);
+                    atomicMax(const_cast<u64*>(a.shared_tau) + qtau, kth);
                 }
             }
             if (!__all_sync(0xffffffffu, mbar_wait(acc_full(ab), aph, abort_flag))) {

@@ -433,6 +433,30 @@ EOS_B200_API int eos_b200_parent_topk(EosB200Corpus* corpus, const int32_t* h_pa
                          int q_count, int query_group, int top_n, double penalty, int k, int64_t* h_ids,
                          float* h_scores, EosB200Stats* stats, char** err);
 
+/* ---- sparse attention ---------------------------------------------------------------------------
+ * Replaces sparseAttentionTensor (runtime/backend/attention_ops.go:218-276; device twin
+ * sparseAttentionKernelSource, runtime/backends/cuda/native_linux.go:2044-2339).  h_query [batches, q_len, dim],
+ * h_key [batches, k_len, dim], h_value [batches, k_len, value_dim], h_out [batches, q_len, value_dim], fp32; a
+ * rank-2 call passes batches = 1.  Per query row: scores q.k in fp32 (no 1/sqrt(d)); the best keys by score
+ * descending then index ascending, as many as top_k (<= 0: ceil(sqrt(k_len))), clamped to [1, k_len];
+ * route_block_size, route_top_blocks > 0 first keep the route_top_blocks key blocks whose middle key scores best
+ * (block_anchor routing, :462-497); softmax over the selected scores; their values mixed in selection order.
+ * k_len = 0 gives zeros.  Limits: the key budget and route_top_blocks at most 128 (EOS_SPARSE_ATTENTION_MAX_TOPK). */
+EOS_B200_API int eos_b200_sparse_attention(EosB200Runtime* rt, const float* h_query, const float* h_key, const float* h_value,
+                                           int batches, int q_len, int k_len, int dim, int value_dim, int top_k,
+                                           int route_block_size, int route_top_blocks, float* h_out, EosB200Stats* stats,
+                                           char** err);
+/* Replaces turboSparseAttentionTensor (attention_ops.go:278-300): the keys and values arrive TurboQuant-compressed
+ * -- codes [batches, k_len, dim] one byte per coordinate (the reference's coords tensor [B, D, T, 1] in sequence
+ * order) and 8-bit log-scale norm codes [batches, k_len] (native_linux.go:1879-1904) -- and are decoded on the
+ * device (manta_turboq_decode, :1959-2003) before the same attention.  key_qz / value_qz carry the rotation
+ * specs of the key and value widths (the same handle when both widths are equal). */
+EOS_B200_API int eos_b200_turbo_sparse_attention(EosB200Quantizer* key_qz, EosB200Quantizer* value_qz, const float* h_query,
+                                                 const uint8_t* h_key_codes, const uint8_t* h_key_norm_codes,
+                                                 const uint8_t* h_value_codes, const uint8_t* h_value_norm_codes,
+                                                 int batches, int q_len, int k_len, int top_k, int route_block_size,
+                                                 int route_top_blocks, float* h_out, EosB200Stats* stats, char** err);
+
 /* Seeded synthetic data on the device (bench / tests): n rows of dim N(0,1) values, optionally
  * L2-normalised, row r generated from (seed, row_offset + r) only. */
 EOS_B200_API int eos_b200_synth_gaussian_device(EosB200Runtime* rt, uint64_t seed, int64_t row_offset, int64_t n, int dim,

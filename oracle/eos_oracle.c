@@ -605,7 +605,128 @@ EOS_ORACLE_API int eos_oracle_bert_token_vectors(const int32_t *input_ids, const
 }
 
 /* ------------------------------------------------------------------------------------ */
-/* TurboQuant, Hadamard/MSE variant (PARITY UNPINNED, see header).                        */
+/* Sparse attention: sparseAttentionTensor, runtime/backend/attention_ops.go:218-276        */
+/* (device twin: sparseAttentionKernelSource, runtime/backends/cuda/native_linux.go:2044).  */
+/* Per query row: scores q.k (float accumulate in d order, no 1/sqrt(d)), top-`budget` keys */
+/* by score descending then index ascending (:518-531), optionally routed through the        */
+/* `route_top_blocks` blocks whose anchor key (the block's middle) scores best (:462-497);   */
+/* softmax over the selected scores with exp in double (:533-560); out += float(w/denom) * v */
+/* accumulated in float in selection order.                                                  */
+/* ------------------------------------------------------------------------------------ */
+typedef struct {
+    int index;
+    float score;
+} sparse_cand;
+
+static int sparse_cand_cmp(const void *a, const void *b) {
+    const sparse_cand *x = (const sparse_cand *)a, *y = (const sparse_cand *)b;
+    if (x->score == y->score) return (x->index > y->index) - (x->index < y->index);
+    return x->score > y->score ? -1 : 1;
+}
+
+/* budget: top_k attribute, else ceil(sqrt(key_len)), clamped to [1, key_len] (:445-460) */
+EOS_ORACLE_API int eos_oracle_sparse_attention_budget(int top_k, int key_len) {
+    if (key_len <= 0) return 0;
+    int budget = top_k;
+    if (budget <= 0) budget = (int)ceil(sqrt((double)key_len));
+    if (budget < 1) budget = 1;
+    if (budget > key_len) budget = key_len;
+    return budget;
+}
+
+/* (block size, top blocks) after normalizeSparseAttentionRoute (:503-516); 0, 0 = no routing */
+EOS_ORACLE_API void eos_oracle_sparse_attention_route(int key_len, int block_size, int top_blocks, int *out_block,
+                                                      int *out_top) {
+    *out_block = 0;
+    *out_top = 0;
+    if (key_len <= 0 || block_size <= 0 || top_blocks <= 0) return;
+    if (block_size > key_len) block_size = key_len;
+    int block_count = (key_len + block_size - 1) / block_size;
+    if (top_blocks > block_count) top_blocks = block_count;
+    *out_block = block_size;
+    *out_top = top_blocks;
+}
+
+static float sparse_score(const float *q, const float *k, int dim) {
+    float sum = 0.0f;
+    for (int d = 0; d < dim; d++) sum += q[d] * k[d];
+    return sum;
+}
+
+/* query [batches, q_len, dim], key [batches, k_len, dim], value [batches, k_len, vdim] -> out [batches, q_len, vdim] */
+EOS_ORACLE_API void eos_oracle_sparse_attention(const float *query, const float *key, const float *value, int batches,
+                                                int q_len, int k_len, int dim, int vdim, int top_k, int route_block_size,
+                                                int route_top_blocks, float *out) {
+    memset(out, 0, sizeof(float) * (size_t)batches * q_len * vdim);
+    if (k_len <= 0) return;
+    int budget = eos_oracle_sparse_attention_budget(top_k, k_len);
+    int bs, tb;
+    eos_oracle_sparse_attention_route(k_len, route_block_size, route_top_blocks, &bs, &tb);
+    sparse_cand *cand = (sparse_cand *)malloc(sizeof(sparse_cand) * (size_t)k_len);
+    sparse_cand *blocks = (sparse_cand *)malloc(sizeof(sparse_cand) * (size_t)k_len);
+    double *weights = (double *)malloc(sizeof(double) * (size_t)k_len);
+    for (int b = 0; b < batches; b++) {
+        const float *kb = key + (int64_t)b * k_len * dim;
+        const float *vb = value + (int64_t)b * k_len * vdim;
+        for (int q = 0; q < q_len; q++) {
+            const float *qv = query + ((int64_t)b * q_len + q) * dim;
+            int n = 0;
+            if (bs <= 0 || tb <= 0) {
+                for (int k = 0; k < k_len; k++) {
+                    cand[n].index = k;
+                    cand[n].score = sparse_score(qv, kb + (int64_t)k * dim, dim);
+                    n++;
+                }
+            } else {
+                int block_count = (k_len + bs - 1) / bs;
+                for (int blk = 0; blk < block_count; blk++) {
+                    int start = blk * bs, end = start + bs;
+                    if (end > k_len) end = k_len;
+                    int anchor = start + (end - start) / 2;
+                    blocks[blk].index = blk;
+                    blocks[blk].score = sparse_score(qv, kb + (int64_t)anchor * dim, dim);
+                }
+                qsort(blocks, (size_t)block_count, sizeof(sparse_cand), sparse_cand_cmp);
+                int nb = tb < block_count ? tb : block_count;
+                for (int i = 0; i < nb; i++) {
+                    int start = blocks[i].index * bs, end = start + bs;
+                    if (end > k_len) end = k_len;
+                    for (int k = start; k < end; k++) {
+                        cand[n].index = k;
+                        cand[n].score = sparse_score(qv, kb + (int64_t)k * dim, dim);
+                        n++;
+                    }
+                }
+            }
+            /* (score desc, index asc) is a total order, so qsort gives the stable sort's result */
+            qsort(cand, (size_t)n, sizeof(sparse_cand), sparse_cand_cmp);
+            if (budget < n) n = budget;
+            if (n == 0) continue;
+            float max_score = cand[0].score;
+            for (int i = 1; i < n; i++)
+                if (cand[i].score > max_score) max_score = cand[i].score;
+            double denom = 0.0;
+            for (int i = 0; i < n; i++) {
+                weights[i] = exp((double)(cand[i].score - max_score));
+                denom += weights[i];
+            }
+            if (denom == 0.0 || isnan(denom)) continue;
+            float *row = out + ((int64_t)b * q_len + q) * vdim;
+            for (int i = 0; i < n; i++) {
+                float scale = (float)(weights[i] / denom);
+                const float *vv = vb + (int64_t)cand[i].index * vdim;
+                for (int d = 0; d < vdim; d++) row[d] += scale * vv[d];
+            }
+        }
+    }
+    free(cand);
+    free(blocks);
+    free(weights);
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* TurboQuant, Hadamard/MSE variant (encode / decode pinned to the reference's device     */
+/* source compiled for the host, see header).                                             */
 /* Structure follows Eos's device restatement runtime/backends/cuda/native_linux.go:      */
 /*   blocked normalised FWHT over greedy power-of-two blocks  :1822-1851                  */
 /*   nearest centroid = first boundary greater than the value :1865-1877                  */

@@ -262,6 +262,32 @@ def bert_token_vectors(input_ids, mask, type_ids, tok, pos, typ, emb_gamma, emb_
     return out
 
 
+def sparse_attention_budget(top_k: int, key_len: int) -> int:
+    return int(lib().eos_oracle_sparse_attention_budget(C.c_int(top_k), C.c_int(key_len)))
+
+
+def sparse_attention_route(key_len: int, block_size: int, top_blocks: int):
+    bs, tb = C.c_int(), C.c_int()
+    lib().eos_oracle_sparse_attention_route(C.c_int(key_len), C.c_int(block_size), C.c_int(top_blocks), C.byref(bs),
+                                            C.byref(tb))
+    return bs.value, tb.value
+
+
+def sparse_attention(query, key, value, top_k: int = 0, route_block_size: int = 0, route_top_blocks: int = 0):
+    """sparseAttentionTensor (runtime/backend/attention_ops.go:218-276) for rank-2 or rank-3 q / k / v."""
+    q, k, v = map(_f32, (query, key, value))
+    squeeze = q.ndim == 2
+    if squeeze:
+        q, k, v = q[None], k[None], v[None]
+    b, ql, dim = q.shape
+    kl, vdim = k.shape[1], v.shape[2]
+    out = np.zeros((b, ql, vdim), dtype=np.float32)
+    lib().eos_oracle_sparse_attention(_p(q), _p(k), _p(v), C.c_int(b), C.c_int(ql), C.c_int(kl), C.c_int(dim),
+                                      C.c_int(vdim), C.c_int(top_k), C.c_int(route_block_size), C.c_int(route_top_blocks),
+                                      _p(out))
+    return out[0] if squeeze else out
+
+
 # --------------------------------------------------------------------------------- TurboQuant
 def tq_code_bytes(dim: int, bits: int) -> int:
     return int(lib().eos_oracle_tq_code_bytes(C.c_int(dim), C.c_int(bits)))

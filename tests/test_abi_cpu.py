@@ -105,3 +105,14 @@ def test_oracle_turboquant_round_trip_properties():
     ids, ps = O.parent_topk(sc, parent, 7, 7)
     for i, p in zip(ids, ps):
         assert p == sc[parent == i].max()
+
+
+def test_sparse_attention_plan_matches_oracle_knobs():
+    """PlanSparseAttention (runtime/backend/attention_ops.go:78-141): the host mirror normalises the knobs like the
+    oracle's restatement of sparseAttentionBudget / normalizeSparseAttentionRoute."""
+    from eos_b200.attention import plan_sparse_attention
+    from oracle import oracle as O
+    for kl, tk, bs, tb in [(50, 0, 0, 0), (1000, 32, 64, 4), (1000, 0, 37, 128), (3, 10, 0, 0), (0, 5, 4, 4)]:
+        plan = plan_sparse_attention(8, kl, tk, bs, tb)
+        assert plan.top_k == (O.sparse_attention_budget(tk, kl) if kl > 0 else tk)
+        assert (plan.route_block_size, plan.route_top_blocks) == O.sparse_attention_route(kl, bs, tb)

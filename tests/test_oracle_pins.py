@@ -268,3 +268,27 @@ def test_tq_encode_decode_match_the_reference_device_code(dim, bits, n):
     assert np.array_equal(O.tq_norm_value(norm_codes.astype(np.uint8)), norm8)
     out = O.tq_decode(codes, norm8, dim, bits, spec.perm, spec.signs1, spec.signs2, spec.centroids)
     assert np.array_equal(out.view(np.uint32), out_ref.view(np.uint32))   # bit-exact reconstruction
+
+
+# ---- sparse attention: known answers of runtime/backend/tensor_ops_test.go:898-1001 --------------------------------
+def test_sparse_attention_known_answers():
+    # TestSparseAttentionReferenceSelectsTopKValues
+    q = np.array([[1, 0], [0, 1]], np.float32)
+    k = np.array([[1, 0], [0, 1], [-1, 0]], np.float32)
+    v = np.array([[10, 0], [0, 20], [-10, 0]], np.float32)
+    np.testing.assert_allclose(O.sparse_attention(q, k, v, top_k=1), [[10, 0], [0, 20]], atol=1e-6)
+    # TestSparseAttentionReferenceRoutesThroughSelectedBlocks: anchors are keys 1, 3, 5 -> block 1 wins, key 2 in it
+    q = np.array([[1, 0]], np.float32)
+    k = np.array([[0, 10], [0, 0], [3, 0], [2, 0], [10, 0], [0, 0]], np.float32)
+    v = np.array([[10], [20], [30], [40], [50], [60]], np.float32)
+    np.testing.assert_allclose(O.sparse_attention(q, k, v, top_k=1, route_block_size=2, route_top_blocks=1), [[30]],
+                               atol=1e-6)
+    # budget / route normalisation (PlanSparseAttention, TestSparseAttentionPlanTracksRoutedBudget)
+    assert O.sparse_attention_budget(0, 64) == 8 and O.sparse_attention_budget(4, 64) == 4
+    assert O.sparse_attention_budget(100, 64) == 64 and O.sparse_attention_budget(0, 0) == 0
+    assert O.sparse_attention_route(64, 8, 2) == (8, 2) and O.sparse_attention_route(64, 100, 5) == (64, 1)
+    assert O.sparse_attention_route(64, 0, 2) == (0, 0)
+    # softmax over the selected keys only: two equal best scores share the weight
+    k2 = np.array([[1, 0], [1, 0], [0, 1]], np.float32)
+    v2 = np.array([[2, 0], [4, 0], [100, 100]], np.float32)
+    np.testing.assert_allclose(O.sparse_attention(np.array([[1, 0]], np.float32), k2, v2, top_k=2), [[3, 0]], atol=1e-6)
