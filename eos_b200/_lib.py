@@ -136,6 +136,14 @@ SYMBOLS = {
     "eos_b200_dense_destroy": (None, [_P]),
     "eos_b200_dense_score_topk": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_dense_rerank": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
+    "eos_b200_ip_corpus_bind": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, _P, _P, _P, _P, C.c_int64, C.c_int64, C.c_int,
+                                          C.POINTER(C.c_void_p), _ERR]),
+    "eos_b200_ip_corpus_destroy": (None, [_P]),
+    "eos_b200_ip_corpus_vector_bytes": (C.c_int64, [C.c_int, C.c_int]),
+    "eos_b200_norm_encode_log8": (None, [_P, C.c_int64, _P]),
+    "eos_b200_norm_decode_log8": (None, [_P, C.c_int64, _P]),
+    "eos_b200_embed_pooled_set_matmul_scale": (C.c_int, [_P, C.c_float, _ERR]),
+    "eos_b200_ip_score_topk": (C.c_int, [_P, _P, _P, C.c_float, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_sparse_attention": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                             C.c_int, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_turbo_sparse_attention": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

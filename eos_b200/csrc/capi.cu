@@ -163,6 +163,7 @@ int eos_b200_runtime_create(int device, EosB200Runtime** out, char** err) {
         if (se == cudaSuccess && (se = tq_tc_init()) != cudaSuccess) ge = std::string("tq_tc_init: ") + cudaGetErrorString(se);
         if (se == cudaSuccess && (se = tq_tc256_init()) != cudaSuccess) ge = std::string("tq_tc256_init: ") + cudaGetErrorString(se);
         if (se == cudaSuccess && (se = tq_merge_init()) != cudaSuccess) ge = std::string("tq_merge_init: ") + cudaGetErrorString(se);
+        if (se == cudaSuccess && (se = tq_ip_init()) != cudaSuccess) ge = std::string("tq_ip_init: ") + cudaGetErrorString(se);
         if (se == cudaSuccess && (se = sparse_attention_init()) != cudaSuccess) ge = std::string("sparse_attention_init: ") + cudaGetErrorString(se);
     }
     if (!ge.empty()) {
@@ -1143,9 +1144,17 @@ struct EosB200EmbedPooled {
     int* d_counts = nullptr;      // [batch] valid tokens
     long long cap_elems = 0;
     int cap_batch = 0;
+    float matmul_scale = 1.0f;    // the matmul step's `scale` attribute, resolved to a number by the caller
 };
 
 extern "C" {
+
+int eos_b200_embed_pooled_set_matmul_scale(EosB200EmbedPooled* ep, float scale, char** err) {
+    if (ep == nullptr) return fail(err, "embed_pooled_set_matmul_scale: null pipeline");
+    if (std::isnan(scale) || std::isinf(scale)) return fail(err, "matmul scale must be finite");
+    ep->matmul_scale = scale;
+    return EOS_B200_OK;
+}
 
 void eos_b200_embed_pooled_destroy(EosB200EmbedPooled* ep) {
     if (ep == nullptr) return;
@@ -1213,7 +1222,7 @@ int eos_b200_embed_pooled_run(EosB200EmbedPooled* ep, const int32_t* h_tokens, c
     CUDA_TRY(cudaMemcpyAsync(ep->d_tokens, h_tokens, (size_t)n * 4, cudaMemcpyHostToDevice, s));
     CUDA_TRY(cudaMemcpyAsync(ep->d_mask, h_mask, (size_t)n * 4, cudaMemcpyHostToDevice, s));
     launch_embed_pooled(ep->d_tokens, ep->d_mask, batch, tokens, ep->table, ep->vocab, ep->dim, ep->proj, ep->out_dim,
-                        pool_then_l2 ? 1 : 0, ep->d_partial, ep->d_counts, ep->d_out, rt->d_status, s);
+                        ep->matmul_scale, pool_then_l2 ? 1 : 0, ep->d_partial, ep->d_counts, ep->d_out, rt->d_status, s);
     CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaMemcpyAsync(h_out, ep->d_out, (size_t)batch * ep->out_dim * 4, cudaMemcpyDeviceToHost, s));
     CUDA_TRY(cudaEventRecord(rt->ev1, s));
@@ -1636,9 +1645,13 @@ int resolve_per_pass(int per_pass, int q_count) {
     return q_count <= kTqTcQueries ? kTqTcQueries : kTqTc256Queries;
 }
 
+int wide_topk(EosB200Corpus* c, const struct ::EosB200IpCorpus* ip, const float* h_queries, const float* h_sketch,
+              float qjl_scale, int q_count, int k, int64_t* h_ids, float* h_scores, EosB200Stats* stats, const char* what,
+              char** err);
+
 std::string check_score_args(const EosB200Corpus* c, int q_count, int k, int per_pass) {
     if (q_count <= 0) return "score_topk: no queries";
-    if (k <= 0 || k > kTqMaxK) return "score_topk: k must be in [1, 128]";
+    if (k <= 0 || k > kTqMaxK) return "score_topk: k must be in [1, 128] (the host call eos_b200_score_topk takes up to 256)";
     if (per_pass != 8 && per_pass != 16 && per_pass != 32 && per_pass != kTqTcQueries && per_pass != kTqTc256Queries)
         return "score_topk: queries_per_pass must be 0 (automatic), 8, 16, 32, 128 or 256";
     if (c->n + c->id_base > 0xffffffffLL || c->id_base < 0) return "score_topk: document ids must fit 32 bits";
@@ -1950,7 +1963,8 @@ int eos_b200_score_topk(EosB200Corpus* c, const float* h_queries, int q_count, i
     if (c == nullptr || h_queries == nullptr || h_ids == nullptr || h_scores == nullptr)
         return fail(err, "score_topk: null argument");
     per_pass = resolve_per_pass(per_pass, q_count);
-    std::string m = check_score_args(c, q_count, k, per_pass);
+    const bool wide = k > kTqMaxK && k <= kTqWideK;   // over-fetch sizes: all scores of a query chunk, then one select
+    std::string m = check_score_args(c, q_count, wide ? kTqMaxK : k, per_pass);
     if (!m.empty()) return fail(err, m);
     if (c->n == 0) {  // topK > len(docs): nothing to return (runtime/retrieval_turboquant.go:1854-1860)
         for (size_t i = 0; i < (size_t)q_count * k; ++i) {
@@ -1962,6 +1976,7 @@ int eos_b200_score_topk(EosB200Corpus* c, const float* h_queries, int q_count, i
     }
     EosB200Runtime* rt = c->qz->rt;
     CUDA_TRY(cudaSetDevice(rt->device));
+    if (wide) return wide_topk(c, nullptr, h_queries, nullptr, 0.f, q_count, k, h_ids, h_scores, stats, "score_topk", err);
     int rc = ensure_score_workspace(c, q_count, err);
     if (rc == EOS_B200_OK && (per_pass == kTqTcQueries || per_pass == kTqTc256Queries))
         rc = ensure_tc_workspace(c, per_pass == kTqTc256Queries ? 1 : 0, err);
@@ -1990,6 +2005,250 @@ int eos_b200_corpus_sync(EosB200Corpus* c, void* stream, char** err) {
     if (c == nullptr) return fail(err, "corpus_sync: null corpus");
     CUDA_TRY(cudaSetDevice(c->qz->rt->device));
     return read_status(c->qz->rt, pick_stream(c->qz->rt, stream), err);
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// wide path: all scores of a chunk of queries, optional sign stage, keys, one select per query
+// ------------------------------------------------------------------------------------------------
+struct EosB200IpCorpus {
+    EosB200Quantizer* qz = nullptr;   // 4-bit view of the MSE stage (owned)
+    EosB200Corpus* base = nullptr;    // MSE codes as scan tiles + norms (owned)
+    uint32_t* signs = nullptr;        // [n][ceil(dim / 32)]
+    float* resnorms = nullptr;        // [n]
+    int levels = 0;                   // levels of the MSE stage
+};
+
+namespace {
+constexpr int kWideSegLen = 4096;   // keys per merge segment (one warp each)
+
+// Exact top-k (k <= kTqWideK) of q_count host queries over the whole corpus.  ip == nullptr: the Hadamard/MSE score.
+int wide_topk(EosB200Corpus* c, const EosB200IpCorpus* ip, const float* h_queries, const float* h_sketch, float qjl_scale,
+              int q_count, int k, int64_t* h_ids, float* h_scores, EosB200Stats* stats, const char* what, char** err) {
+    EosB200Runtime* rt = c->qz->rt;
+    const int dim = c->qz->dim;
+    const int64_t n = c->n;
+    const int64_t n_pad = (n + kWideSegLen - 1) / kWideSegLen * kWideSegLen;
+    const int64_t n_segs = n_pad / kWideSegLen;
+    if (n_segs > 0x7fffffffLL) return fail(err, std::string(what) + ": too many rows");
+    // queries per chunk: 12 bytes (score + key) per (query, row), about 3 GB at most, a multiple of 8
+    int chunk = (int)std::min<int64_t>(q_count, std::max<int64_t>(8, (int64_t)3e9 / (12 * n_pad)));
+    chunk = (chunk + 7) / 8 * 8;
+    int rc = ensure_score_workspace(c, chunk, err);
+    if (rc != EOS_B200_OK) return rc;
+    cudaStream_t s = rt->stream;
+    float *d_all = nullptr, *d_sketch = nullptr, *d_scores = nullptr;
+    uint64_t* d_keys = nullptr;
+    int64_t* d_ids = nullptr;
+    cudaError_t e = dev_alloc(&d_all, (size_t)chunk * n);
+    if (e == cudaSuccess) e = dev_alloc(&d_keys, (size_t)chunk * n_pad);
+    if (e == cudaSuccess) e = dev_alloc(&d_ids, (size_t)chunk * k);
+    if (e == cudaSuccess) e = dev_alloc(&d_scores, (size_t)chunk * k);
+    if (e == cudaSuccess && ip != nullptr) e = dev_alloc(&d_sketch, (size_t)chunk * dim);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev0, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(rt->d_status, 0, sizeof(int), s);
+    const int ksteps = tq_ksteps(dim);
+    int launches = 0;
+    for (int q0 = 0; q0 < q_count && e == cudaSuccess; q0 += chunk) {
+        const int qn = std::min(chunk, q_count - q0);
+        const int q_pad = (qn + 7) / 8 * 8;
+        e = cudaMemcpyAsync(c->d_queries, h_queries + (size_t)q0 * dim, (size_t)qn * dim * 4, cudaMemcpyHostToDevice, s);
+        if (e != cudaSuccess) break;
+        launch_tq_prepare(c->d_queries, qn, q_pad, c->qz->spec(), c->bfrag, nullptr, nullptr, s);
+        for (int t = 0; t < q_pad / 8; ++t) {
+            TqScanArgs a{};
+            a.tiles = c->tiles;
+            a.norms = c->norms;
+            a.n_docs = n;
+            a.id_base = 0;
+            a.dim = dim;
+            a.bfrag = c->bfrag + (size_t)t * ksteps * 32;
+            a.query_tiles = 1;
+            a.k = 1;
+            a.mag_hi[0] = c->qz->mag_hi[0];
+            a.mag_hi[1] = c->qz->mag_hi[1];
+            a.mag_lo[0] = c->qz->mag_lo[0];
+            a.mag_lo[1] = c->qz->mag_lo[1];
+            a.cand_keys = c->cand;
+            a.cand_count = c->cand_count;
+            a.grid = c->grid;
+            a.all_scores = d_all + (size_t)t * 8 * n;
+            a.all_stride = n;
+            a.status = rt->d_status;
+            launch_tq_scan(a, s);
+        }
+        launches += 1 + q_pad / 8;
+        if (ip != nullptr) {
+            e = cudaMemcpyAsync(d_sketch, h_sketch + (size_t)q0 * dim, (size_t)qn * dim * 4, cudaMemcpyHostToDevice, s);
+            if (e != cudaSuccess) break;
+            launch_tq_ip_sign_stage(ip->signs, ip->resnorms, c->norms, n, d_sketch, qn, dim, qjl_scale, d_all, n,
+                                    rt->sm_count, s);
+            ++launches;
+        }
+        launch_tq_score_keys(d_all, n, qn, n, n_pad, d_keys, rt->sm_count, s);
+        launch_tq_merge(d_keys, n_pad, kWideSegLen, (int)n_segs, kWideSegLen, nullptr, qn, k, c->id_base, d_ids, d_scores,
+                        nullptr, s);
+        launches += 2;
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaMemcpyAsync(h_ids + (size_t)q0 * k, d_ids, (size_t)qn * k * 8, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(h_scores + (size_t)q0 * k, d_scores, (size_t)qn * k * 4, cudaMemcpyDeviceToHost, s);
+        // the next chunk reuses the buffers the copies read
+        if (e == cudaSuccess && q0 + chunk < q_count) e = cudaStreamSynchronize(s);
+    }
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev1, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    dev_free(d_all);
+    dev_free(d_keys);
+    dev_free(d_ids);
+    dev_free(d_scores);
+    dev_free(d_sketch);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(err, std::string(what) + ": " + cudaGetErrorString(e));
+    }
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+        stats->uploaded_bytes = (int64_t)q_count * dim * 4 * (ip != nullptr ? 2 : 1);
+        stats->downloaded_bytes = (int64_t)q_count * k * 12;
+        cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+    }
+    return read_status(rt, s, err);
+}
+}  // namespace
+
+extern "C" {
+
+void eos_b200_ip_corpus_destroy(EosB200IpCorpus* ip) {
+    if (ip == nullptr) return;
+    if (ip->base != nullptr) eos_b200_corpus_destroy(ip->base);
+    dev_free(ip->signs);
+    dev_free(ip->resnorms);
+    if (ip->qz != nullptr) eos_b200_quantizer_destroy(ip->qz);
+    delete ip;
+}
+
+int eos_b200_ip_corpus_bind(EosB200Runtime* rt, int dim, int mse_levels, const int32_t* perm, const float* signs1,
+                            const float* signs2, const float* centroids, const uint8_t* h_mse_indices,
+                            const uint8_t* h_signs, const float* h_resnorms, const float* h_norms, int64_t n,
+                            int64_t id_base, int allow_zero_norm, EosB200IpCorpus** out, char** err) {
+    if (rt == nullptr || perm == nullptr || signs1 == nullptr || signs2 == nullptr || centroids == nullptr || out == nullptr ||
+        (n > 0 && (h_mse_indices == nullptr || h_signs == nullptr || h_resnorms == nullptr || h_norms == nullptr)))
+        return fail(err, "ip_corpus_bind: null argument");
+    *out = nullptr;
+    if (mse_levels != 2 && mse_levels != 4 && mse_levels != 8 && mse_levels != 16)
+        return fail(err, "ip_corpus_bind: the MSE stage must have 2, 4, 8 or 16 levels");
+    if (n < 0 || dim <= 0) return fail(err, "ip_corpus_bind: bad sizes");
+    for (int64_t i = 0; i < n; ++i) {
+        const float r = h_resnorms[i];
+        if (std::isnan(r) || std::isinf(r) || r < 0)
+            return fail(err, "ip_corpus_bind: residual norm must be finite and non-negative (row " + std::to_string(i) + ")");
+    }
+    // The scan kernels read 4-bit codes as sign + magnitude of a symmetric 16-level table: level i of the L-level table
+    // becomes code 8 - L/2 + i, and the magnitudes the codes never use are filled with larger dummies.
+    const int half = mse_levels / 2;
+    float c16[16], b15[15];
+    for (int m = 0; m < 8; ++m) {
+        const float v = m < half ? centroids[half + m] : centroids[mse_levels - 1] + (float)(m - half + 1);
+        c16[8 + m] = v;
+        c16[7 - m] = m < half ? centroids[half - 1 - m] : -v;
+    }
+    for (int i = 0; i < 15; ++i) b15[i] = 0.5f * (c16[i] + c16[i + 1]);
+    auto* ip = new EosB200IpCorpus();
+    ip->levels = mse_levels;
+    int rc = eos_b200_quantizer_create(rt, dim, 4, perm, signs1, signs2, c16, b15, &ip->qz, err);
+    if (rc != EOS_B200_OK) {
+        eos_b200_ip_corpus_destroy(ip);
+        return rc;
+    }
+    const size_t cb = ((size_t)dim + 1) / 2;
+    const int words = (dim + 31) / 32;
+    std::vector<uint8_t> packed((size_t)(n > 0 ? n : 1) * cb, 0);
+    std::vector<uint32_t> sw((size_t)(n > 0 ? n : 1) * words, 0u);
+    const size_t sign_bytes = ((size_t)dim + 7) / 8;
+    for (int64_t r = 0; r < n; ++r) {
+        const uint8_t* src = h_mse_indices + (size_t)r * dim;
+        uint8_t* dst = packed.data() + (size_t)r * cb;
+        for (int cidx = 0; cidx < dim; ++cidx) {
+            if (src[cidx] >= mse_levels) {
+                eos_b200_ip_corpus_destroy(ip);
+                return fail(err, "ip_corpus_bind: MSE index out of range (row " + std::to_string(r) + ")");
+            }
+            const uint8_t code = (uint8_t)(8 - half + src[cidx]);
+            dst[cidx >> 1] |= (uint8_t)(code << ((cidx & 1) * 4));
+        }
+        const uint8_t* sb = h_signs + (size_t)r * sign_bytes;
+        for (size_t j = 0; j < sign_bytes; ++j) sw[(size_t)r * words + j / 4] |= (uint32_t)sb[j] << (8 * (j % 4));
+        if (dim % 8 != 0) sw[(size_t)r * words + (dim >> 5)] &= (dim & 31) ? ((1u << (dim & 31)) - 1u) : 0xffffffffu;
+    }
+    rc = eos_b200_corpus_bind(ip->qz, packed.data(), h_norms, n, id_base, allow_zero_norm, &ip->base, err);
+    if (rc != EOS_B200_OK) {
+        eos_b200_ip_corpus_destroy(ip);
+        return rc;
+    }
+    cudaError_t e = dev_alloc(&ip->signs, sw.size());
+    if (e == cudaSuccess) e = dev_alloc(&ip->resnorms, (size_t)(n > 0 ? n : 1));
+    if (e == cudaSuccess) e = cudaMemcpy(ip->signs, sw.data(), sw.size() * 4, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && n > 0) e = cudaMemcpy(ip->resnorms, h_resnorms, (size_t)n * 4, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        eos_b200_ip_corpus_destroy(ip);
+        return fail(err, std::string("ip_corpus_bind: ") + cudaGetErrorString(e));
+    }
+    *out = ip;
+    return EOS_B200_OK;
+}
+
+// 8-bit log-scale norm side-car of the reference's device encode (manta_tq_quantize_norm / manta_tq_dequantize_norm,
+// runtime/backends/cuda/native_linux.go:1879-1904).  Host arithmetic: a caller holding that side-car turns it into
+// the fp32 norms eos_b200_corpus_bind takes, or produces it from the norms eos_b200_quantize returns.
+void eos_b200_norm_encode_log8(const float* norms, int64_t n, uint8_t* codes) {
+    for (int64_t i = 0; i < n; ++i) {
+        const float norm = norms[i];
+        int code;
+        if (norm <= 0.0f || std::isnan(norm)) {
+            code = 0;
+        } else if (std::isinf(norm)) {
+            code = 255;
+        } else {
+            const float t = (logf(norm) + 16.0f) / 32.0f;
+            code = t <= 0.0f ? 0 : (t >= 1.0f ? 255 : (int)roundf(t * 255.0f));
+        }
+        codes[i] = (uint8_t)code;
+    }
+}
+
+void eos_b200_norm_decode_log8(const uint8_t* codes, int64_t n, float* norms) {
+    for (int64_t i = 0; i < n; ++i) norms[i] = expf(-16.0f + ((float)codes[i] / 255.0f) * 32.0f);
+}
+
+int64_t eos_b200_ip_corpus_vector_bytes(int dim, int bit_width) {
+    // turboquantVectorBytes (runtime/turboquant_bytes.go:22-25): MSE payload at bit_width - 1 bits, one sign bit per
+    // coordinate, two fp32 norm fields
+    if (dim <= 0 || bit_width < 2) return 0;
+    return ((int64_t)dim * (bit_width - 1) + 7) / 8 + ((int64_t)dim + 7) / 8 + 8;
+}
+
+int eos_b200_ip_score_topk(EosB200IpCorpus* ip, const float* h_queries, const float* h_query_sketch, float qjl_scale,
+                           int q_count, int k, int64_t* h_ids, float* h_scores, EosB200Stats* stats, char** err) {
+    if (ip == nullptr || h_queries == nullptr || h_query_sketch == nullptr || h_ids == nullptr || h_scores == nullptr)
+        return fail(err, "ip_score_topk: null argument");
+    if (q_count <= 0) return fail(err, "ip_score_topk: no queries");
+    if (k <= 0 || k > kTqWideK) return fail(err, "ip_score_topk: k must be in [1, 256]");
+    EosB200Corpus* c = ip->base;
+    if (c->n == 0) {
+        for (size_t i = 0; i < (size_t)q_count * k; ++i) {
+            h_ids[i] = -1;
+            h_scores[i] = -INFINITY;
+        }
+        if (stats != nullptr) std::memset(stats, 0, sizeof(*stats));
+        return EOS_B200_OK;
+    }
+    if (tq_ip_sign_stage_smem(c->qz->dim) > 100 * 1024) return fail(err, "ip_score_topk: dim is too wide for the sign stage");
+    CUDA_TRY(cudaSetDevice(c->qz->rt->device));
+    return wide_topk(c, ip, h_queries, h_query_sketch, qjl_scale, q_count, k, h_ids, h_scores, stats, "ip_score_topk", err);
 }
 
 }  // extern "C"
@@ -2624,7 +2883,7 @@ int eos_b200_dense_score_topk(EosB200DenseIndex* ix, const float* h_queries, int
         return fail(err, "dense_score_topk: null argument");
     if (q_count <= 0) return fail(err, "dense_score_topk: empty input");
     if (metric != EOS_B200_METRIC_DOT && metric != EOS_B200_METRIC_COSINE) return fail(err, "dense_score_topk: unknown metric");
-    if (k <= 0 || k > kTqMaxK || k > ix->n) return fail(err, "dense_score_topk: k must be in [1, min(128, rows)]");
+    if (k <= 0 || k > kTqWideK || k > ix->n) return fail(err, "dense_score_topk: k must be in [1, min(256, rows)]");
     EosB200Runtime* rt = ix->rt;
     CUDA_TRY(cudaSetDevice(rt->device));
     cudaStream_t s = rt->stream;
@@ -2657,7 +2916,7 @@ int eos_b200_dense_rerank(EosB200DenseIndex* ix, const float* h_queries, int q_c
         return fail(err, "dense_rerank: null argument");
     if (q_count <= 0 || cand <= 0) return fail(err, "dense_rerank: empty input");
     if (k <= 0 || k > cand) k = cand;  // the reference clamps topK to the candidate count
-    if (k > kTqMaxK) return fail(err, "dense_rerank: k must be at most 128");
+    if (k > kTqWideK) return fail(err, "dense_rerank: k must be at most 256");
     EosB200Runtime* rt = ix->rt;
     CUDA_TRY(cudaSetDevice(rt->device));
     cudaStream_t s = rt->stream;

@@ -915,8 +915,8 @@ constexpr int kEpMaxColsPerThread = 4;
 __global__ void __launch_bounds__(256)
 embed_pooled_group_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ mask, int tlen, int groups,
                           const __half* __restrict__ table, int vocab, int dim, const __half* __restrict__ proj,
-                          int out_dim, int pool_then_l2, float* __restrict__ partial, int* __restrict__ counts,
-                          int* status) {
+                          int out_dim, float matmul_scale, int pool_then_l2, float* __restrict__ partial,
+                          int* __restrict__ counts, int* status) {
     extern __shared__ float xs[];  // [kEpTok][dim]
     __shared__ float red[32];
     __shared__ int tok_ids[kEpTok];
@@ -970,6 +970,12 @@ embed_pooled_group_kernel(const int32_t* __restrict__ tokens, const int32_t* __r
                 const float w = __half2float(proj[(size_t)k * out_dim + j]);
 #pragma unroll
                 for (int i = 0; i < kEpTok; ++i) acc[c][i] = fmaf(xs[i * dim + k], w, acc[c][i]);
+            }
+            // the matmul step's `scale` attribute multiplies the finished products (ApplyMatMulAttributes,
+            // runtime/backend/tensor_ops.go:1261-1274)
+            if (matmul_scale != 1.0f) {
+#pragma unroll
+                for (int i = 0; i < kEpTok; ++i) acc[c][i] *= matmul_scale;
             }
         }
     }
@@ -1150,11 +1156,12 @@ void launch_compact_pool(const __half* hidden_states, const SeqLayout& lay, int 
 }
 
 void launch_embed_pooled(const int32_t* tokens, const int32_t* mask, int batch, int tlen, const __half* table,
-                         int vocab, int dim, const __half* projection, int out_dim, int pool_then_l2,
+                         int vocab, int dim, const __half* projection, int out_dim, float matmul_scale, int pool_then_l2,
                          float* partial, int* counts, float* out, int* status, cudaStream_t stream) {
     const int groups = (tlen + kEpTok - 1) / kEpTok;
     embed_pooled_group_kernel<<<dim3(groups, batch), 256, kEpTok * dim * sizeof(float), stream>>>(
-        tokens, mask, tlen, groups, table, vocab, dim, projection, out_dim, pool_then_l2, partial, counts, status);
+        tokens, mask, tlen, groups, table, vocab, dim, projection, out_dim, matmul_scale, pool_then_l2, partial, counts,
+        status);
     embed_pooled_finish_kernel<<<batch, 256, 0, stream>>>(partial, counts, groups, out_dim, pool_then_l2, out);
 }
 

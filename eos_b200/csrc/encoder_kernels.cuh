@@ -62,9 +62,9 @@ void launch_compact_pool(const __half* hidden_states, const SeqLayout& lay, int 
 // Compiled pipeline gather -> matmul -> per-token normalize -> masked mean_pool: one launch over groups of 8
 // valid tokens (partial sums) and one that adds a sequence's groups in order.
 // table [vocab, dim] f16, projection [dim, out_dim] f16 (in-major), out [B, out_dim] fp32;
-// partial [B, ceil(tlen / 8), out_dim] fp32 and counts [B] are scratch.
+// partial [B, ceil(tlen / 8), out_dim] fp32 and counts [B] are scratch.  matmul_scale multiplies the projected rows.
 void launch_embed_pooled(const int32_t* tokens, const int32_t* mask, int batch, int tlen, const __half* table,
-                         int vocab, int dim, const __half* projection, int out_dim, int pool_then_l2,
+                         int vocab, int dim, const __half* projection, int out_dim, float matmul_scale, int pool_then_l2,
                          float* partial, int* counts, float* out, int* status, cudaStream_t stream);
 
 }  // namespace eosb

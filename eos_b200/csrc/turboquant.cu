@@ -950,7 +950,7 @@ tq_merge_kernel(const u64* __restrict__ cand, long long query_stride, long long 
     __shared__ u64 s_prefix, s_mask;
     __shared__ unsigned s_want;
     __shared__ int s_total, s_fill;
-    __shared__ u64 sel[kTqMaxK];
+    __shared__ u64 sel[kTqWideK];
     const int qi = blockIdx.x;
     const u64* base = cand + (long long)qi * query_stride;
     const int* cnts = counts != nullptr ? counts + (long long)qi * n_segs : nullptr;
@@ -971,7 +971,7 @@ tq_merge_kernel(const u64* __restrict__ cand, long long query_stride, long long 
         s_total = 0;
         s_fill = 0;
     }
-    for (int i = threadIdx.x; i < kTqMaxK; i += blockDim.x) sel[i] = 0;
+    for (int i = threadIdx.x; i < kTqWideK; i += blockDim.x) sel[i] = 0;
     __syncthreads();
     int local = 0;
     for_each_key([&](u64 key) { local += key != 0; });
@@ -1013,15 +1013,15 @@ tq_merge_kernel(const u64* __restrict__ cand, long long query_stride, long long 
     for_each_key([&](u64 key) {
         if (key != 0 && key >= thr) {
             const int pos = atomicAdd(&s_fill, 1);
-            if (pos < kTqMaxK) sel[pos] = key;
+            if (pos < kTqWideK) sel[pos] = key;
         }
     });
     __syncthreads();
     if (warp == 0) {
-        // bitonic sort of 128 keys, descending; empty slots (0) sink to the end
-        for (int size = 2; size <= kTqMaxK; size <<= 1) {
+        // bitonic sort of the selected keys, descending; empty slots (0) sink to the end
+        for (int size = 2; size <= kTqWideK; size <<= 1) {
             for (int stride = size >> 1; stride > 0; stride >>= 1) {
-                for (int tt = lane; tt < kTqMaxK / 2; tt += 32) {
+                for (int tt = lane; tt < kTqWideK / 2; tt += 32) {
                     const int i = 2 * tt - (tt & (stride - 1));
                     const int j = i + stride;
                     const bool desc = (i & size) == 0;
@@ -1108,6 +1108,82 @@ parent_key_kernel(const float* __restrict__ agg, int rows, const int* __restrict
 
 // SMs of the current device (set by tq_scan_init; grids of the grid-stride kernels are multiples of it)
 static int g_sm_count = 148;
+
+// ------------------------------------------------------------------------------------------
+// wide path: every score of a query chunk is materialised (scan kernels with all_scores), optionally corrected by
+// the sign stage of the inner-product quantiser, turned into sortable keys and selected by tq_merge_kernel.  It
+// serves k in (128, 256] (over-fetch before a rerank, runtime/retrieval_turboquant.go:1610-1662) and the rows bound
+// as turboquant.IPQuantized{MSE, Signs, ResNorm, Norm} (runtime/turboquant_quantized_vector.go:43-49).
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+tq_score_keys_kernel(const float* __restrict__ scores, long long score_stride, int queries, long long n,
+                     long long key_stride, u64* __restrict__ keys) {
+    const long long total = (long long)queries * key_stride;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long q = i / key_stride, r = i - q * key_stride;
+        keys[i] = r < n ? make_key(scores[q * score_stride + r], (uint32_t)r) : 0ull;
+    }
+}
+
+constexpr int kIpQueryGroup = 4;
+
+// scores[q, row] += norm[row] * resnorm[row] * qjl_scale * sum_i sketch[q, i] * (sign bit i of row ? +1 : -1).
+// One warp per row; the sketches of kIpQueryGroup queries sit in shared memory bit-major ([q][bit][word]) so that the
+// 32 lanes, one sign word each, read consecutive addresses.  sum = 2 * (sum over set bits) - (sum of the sketch).
+__global__ void __launch_bounds__(256)
+tq_ip_sign_stage_kernel(const uint32_t* __restrict__ signs, int words, const float* __restrict__ resnorms,
+                        const float* __restrict__ norms, long long n, const float* __restrict__ sketch, int queries,
+                        int dim, float qjl_scale, float* __restrict__ scores, long long score_stride) {
+    extern __shared__ float ip_smem[];
+    float* sq = ip_smem;                                       // [kIpQueryGroup][32][words]
+    float* tot = ip_smem + (size_t)kIpQueryGroup * 32 * words;  // [kIpQueryGroup]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int q0 = 0; q0 < queries; q0 += kIpQueryGroup) {
+        const int qn = min(kIpQueryGroup, queries - q0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < kIpQueryGroup * 32 * words; i += blockDim.x) {
+            const int q = i / (32 * words), rem = i - q * 32 * words;
+            const int coord = rem;                              // coordinate = word * 32 + bit
+            const int w = coord >> 5, b = coord & 31;
+            sq[((size_t)q * 32 + b) * words + w] = (q < qn && coord < dim) ? sketch[(size_t)(q0 + q) * dim + coord] : 0.f;
+        }
+        __syncthreads();
+        if (warp < kIpQueryGroup) {
+            float t = 0.f;
+            for (int i = lane; i < 32 * words; i += 32) t += sq[(size_t)warp * 32 * words + i];
+            t = warp_sum(t);
+            if (lane == 0) tot[warp] = t;
+        }
+        __syncthreads();
+        for (long long row = (long long)blockIdx.x * 8 + warp; row < n; row += (long long)gridDim.x * 8) {
+            float acc[kIpQueryGroup];
+#pragma unroll
+            for (int q = 0; q < kIpQueryGroup; ++q) acc[q] = 0.f;
+            for (int w = lane; w < words; w += 32) {
+                const uint32_t bits = __ldg(signs + row * words + w);
+#pragma unroll 8
+                for (int b = 0; b < 32; ++b) {
+                    const bool on = (bits >> b) & 1u;
+#pragma unroll
+                    for (int q = 0; q < kIpQueryGroup; ++q) {
+                        const float v = sq[((size_t)q * 32 + b) * words + w];
+                        acc[q] += on ? v : 0.f;
+                    }
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < kIpQueryGroup; ++q) acc[q] = warp_sum(acc[q]);
+            const float scale = __ldg(norms + row) * __ldg(resnorms + row) * qjl_scale;
+            if (lane < qn) {
+                float mine = acc[0];
+#pragma unroll
+                for (int q = 1; q < kIpQueryGroup; ++q) mine = lane == q ? acc[q] : mine;
+                float* dst = scores + (long long)(q0 + lane) * score_stride + row;
+                *dst = *dst + scale * (2.f * mine - tot[lane]);
+            }
+        }
+    }
+}
 
 void launch_parent_keys(const float* scores, long long stride, int rows, const int* child_order, const int* offsets,
                         int parents, int top_n, double penalty, float* agg_scratch, uint64_t* keys,
@@ -1264,6 +1340,33 @@ void launch_dense_keys(const void* docs, bool docs_f16, int64_t n_rows, int dim,
         dense_keys_kernel<false><<<grid, 256, 0, stream>>>(docs, (long long)n_rows, dim, queries, nq,
                                                            reinterpret_cast<const long long*>(cand_ids), (long long)cand,
                                                            metric, reinterpret_cast<u64*>(keys));
+}
+
+void launch_tq_score_keys(const float* scores, int64_t score_stride, int queries, int64_t n, int64_t key_stride,
+                          uint64_t* keys, int sm_count, cudaStream_t stream) {
+    if (queries <= 0 || key_stride <= 0) return;
+    tq_score_keys_kernel<<<sm_count * 8, 256, 0, stream>>>(scores, (long long)score_stride, queries, (long long)n,
+                                                          (long long)key_stride, reinterpret_cast<u64*>(keys));
+}
+
+size_t tq_ip_sign_stage_smem(int dim) {
+    const int words = (dim + 31) / 32;
+    return ((size_t)kIpQueryGroup * 32 * words + kIpQueryGroup) * sizeof(float);
+}
+
+cudaError_t tq_ip_init() {
+    return cudaFuncSetAttribute(tq_ip_sign_stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+}
+
+void launch_tq_ip_sign_stage(const uint32_t* signs, const float* resnorms, const float* norms, int64_t n,
+                             const float* sketch, int queries, int dim, float qjl_scale, float* scores,
+                             int64_t score_stride, int sm_count, cudaStream_t stream) {
+    if (n <= 0 || queries <= 0) return;
+    const int words = (dim + 31) / 32;
+    long long blocks = (n + 7) / 8;
+    if (blocks > (long long)sm_count * 4) blocks = (long long)sm_count * 4;
+    tq_ip_sign_stage_kernel<<<(int)blocks, 256, tq_ip_sign_stage_smem(dim), stream>>>(
+        signs, words, resnorms, norms, (long long)n, sketch, queries, dim, qjl_scale, scores, (long long)score_stride);
 }
 
 }  // namespace eosb

@@ -25,6 +25,7 @@ struct TqSpec {
 constexpr int kTqDocsPerTile = 16;   // documents per scan tile (one m16 MMA row block)
 constexpr int kTqChunkCoords = 128;  // coordinates per 16-byte code chunk group (8 k-steps of 16)
 constexpr int kTqMaxK = 128;         // largest k of the fused top-k
+constexpr int kTqWideK = 256;        // largest k of the merge kernel (the wide path: all scores, then one select)
 constexpr int kTqScanWarps = 16;
 
 // bytes of one scan tile: 16 documents x padded_dim/2 bytes
@@ -159,5 +160,18 @@ void launch_tq_seed_tau_scores(const float* scores, int64_t query_stride, int to
 void launch_dense_keys(const void* docs, bool docs_f16, int64_t n_rows, int dim, const float* queries, int nq,
                        const int64_t* cand_ids, int64_t cand, int metric, uint64_t* keys, int sm_count,
                        cudaStream_t stream);
+
+// Wide path helpers.  keys[q * key_stride + r] = sortable key (scores[q * score_stride + r], r) for r < n, 0 (empty) for
+// n <= r < key_stride: feed them to launch_tq_merge in segments for k up to kTqWideK.
+void launch_tq_score_keys(const float* scores, int64_t score_stride, int queries, int64_t n, int64_t key_stride,
+                          uint64_t* keys, int sm_count, cudaStream_t stream);
+// Sign stage of the inner-product quantiser: scores[q, row] += norms[row] * resnorms[row] * qjl_scale *
+// sum_i sketch[q, i] * (bit i of signs[row] ? +1 : -1).  signs is [n][ceil(dim / 32)] 32-bit words, bit i of a row at
+// word i / 32, bit i % 32; sketch is [queries, dim] fp32.
+cudaError_t tq_ip_init();
+size_t tq_ip_sign_stage_smem(int dim);
+void launch_tq_ip_sign_stage(const uint32_t* signs, const float* resnorms, const float* norms, int64_t n,
+                             const float* sketch, int queries, int dim, float qjl_scale, float* scores,
+                             int64_t score_stride, int sm_count, cudaStream_t stream);
 
 }  // namespace eosb

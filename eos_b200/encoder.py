@@ -301,15 +301,31 @@ class CompactEmbedder(BertEmbedder):
 class EmbedPooledPipeline:
     """gather -> matmul -> normalize -> masked mean_pool (examples/embed_masked_pooled.eos:11-16)."""
 
-    def __init__(self, rt: Runtime, token_embedding, projection):
+    def __init__(self, rt: Runtime, token_embedding, projection, matmul_scale="none"):
+        """matmul_scale: the matmul step's `scale` attribute -- "none", "rsqrt_rhs_rows" (1 / sqrt of the projection's
+        row count) or a number (matmulScale, runtime/backend/tensor_ops.go:1291-1315)."""
         table, proj = _f32(token_embedding), _f32(projection)
         if table.ndim != 2 or proj.ndim != 2 or proj.shape[0] != table.shape[1]:
             raise ValueError(f"matmul mismatch {table.shape} x {proj.shape}")
+        if matmul_scale in (None, "", "none"):
+            scale = 1.0
+        elif matmul_scale == "rsqrt_rhs_rows":
+            scale = float(np.float32(1.0 / np.sqrt(float(proj.shape[0]))))
+        else:
+            try:
+                scale = float(np.float32(float(matmul_scale)))
+            except (TypeError, ValueError):
+                raise ValueError(f"unsupported matmul scale {matmul_scale!r}") from None
+            if not np.isfinite(scale):
+                raise ValueError(f"matmul scale must be finite, got {matmul_scale!r}")
         self.rt = rt
         self.out_dim = proj.shape[1]
+        self.matmul_scale = scale
         self.handle = C.c_void_p()
         _lib.call("eos_b200_embed_pooled_bind", rt.handle, _ptr(table), table.shape[0], table.shape[1], _ptr(proj),
                   proj.shape[1], C.byref(self.handle))
+        if scale != 1.0:
+            _lib.call("eos_b200_embed_pooled_set_matmul_scale", self.handle, C.c_float(scale))
         rt._adopt(self)
         self.last_stats = Stats()
 

@@ -276,6 +276,65 @@ class Corpus:
 METRIC_DOT, METRIC_COSINE = 0, 1
 
 
+def norm_encode_log8(norms) -> np.ndarray:
+    """fp32 norms -> the 8-bit log-scale side-car of the reference's device encode (native_linux.go:1879-1893)."""
+    a = _f32(norms).reshape(-1)
+    out = np.empty(a.size, dtype=np.uint8)
+    _lib.lib().eos_b200_norm_encode_log8(_ptr(a), a.size, _ptr(out))
+    return out
+
+
+def norm_decode_log8(codes) -> np.ndarray:
+    """8-bit log-scale norm codes -> fp32 norms (native_linux.go:1895-1904)."""
+    c = np.ascontiguousarray(codes, dtype=np.uint8).reshape(-1)
+    out = np.empty(c.size, dtype=np.float32)
+    _lib.lib().eos_b200_norm_decode_log8(_ptr(c), c.size, _ptr(out))
+    return out
+
+
+class IpCorpus:
+    """Rows quantised by the inner-product quantiser -- turboquant.IPQuantized{MSE, Signs, ResNorm, Norm}
+    (runtime/turboquant_quantized_vector.go:43-49) -- resident on one GPU.  The fields come from a host that holds the
+    quantiser module; the score is Norm * (<R q, centroids[MSE]> + ResNorm * qjl_scale * <sketch_q, +-1 signs>)."""
+
+    def __init__(self, rt: Runtime, dim: int, perm, signs1, signs2, mse_centroids, mse_indices, signs, resnorms, norms,
+                 id_base: int = 0, allow_zero_norm: bool = False):
+        self.rt, self.dim = rt, int(dim)
+        cent = _f32(mse_centroids).reshape(-1)
+        idx = np.ascontiguousarray(mse_indices, dtype=np.uint8)
+        sg = np.ascontiguousarray(signs, dtype=np.uint8)
+        rn, nr = _f32(resnorms).reshape(-1), _f32(norms).reshape(-1)
+        if idx.ndim != 2 or idx.shape[1] != dim or sg.shape != (idx.shape[0], (dim + 7) // 8) or \
+                rn.size != idx.shape[0] or nr.size != idx.shape[0]:
+            raise ValueError("ip corpus fields do not match dim / row count")
+        self.n = idx.shape[0]
+        self.handle = C.c_void_p()
+        _lib.call("eos_b200_ip_corpus_bind", rt.handle, int(dim), int(cent.size), _ptr(_i32(perm)), _ptr(_f32(signs1)),
+                  _ptr(_f32(signs2)), _ptr(cent), _ptr(idx), _ptr(sg), _ptr(rn), _ptr(nr), self.n, int(id_base),
+                  1 if allow_zero_norm else 0, C.byref(self.handle))
+        self.last_stats = Stats()
+
+    @staticmethod
+    def vector_bytes(dim: int, bit_width: int) -> int:
+        """turboquantVectorBytes (runtime/turboquant_bytes.go:22-25)."""
+        return int(_lib.lib().eos_b200_ip_corpus_vector_bytes(int(dim), int(bit_width)))
+
+    def score_topk(self, queries, query_sketch, qjl_scale: float, k: int) -> Tuple[np.ndarray, np.ndarray]:
+        q, sk = _f32(queries), _f32(query_sketch)
+        if q.ndim != 2 or q.shape[1] != self.dim or q.shape[0] == 0 or sk.shape != q.shape:
+            raise ValueError(f"ip score_topk expects non-empty [Q, {self.dim}] queries and sketches")
+        ids = np.empty((q.shape[0], k), dtype=np.int64)
+        scores = np.empty((q.shape[0], k), dtype=np.float32)
+        _lib.call("eos_b200_ip_score_topk", self.handle, _ptr(q), _ptr(sk), float(qjl_scale), q.shape[0], int(k),
+                  _ptr(ids), _ptr(scores), C.byref(self.last_stats))
+        return ids, scores
+
+    def close(self) -> None:
+        if self.handle:
+            _lib.lib().eos_b200_ip_corpus_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+
 class DenseIndex:
     """Uncompressed document vectors on one GPU: the dense scoring operators (dotRows / cosineRows + topKTensor,
     runtime/backend/tensor_ops.go:1967-2057, 2124-2193) and the rerank stage after a TurboQuant top-k

@@ -41,6 +41,7 @@ typedef struct EosB200Encoder EosB200Encoder;
 typedef struct EosB200EmbedPooled EosB200EmbedPooled;
 typedef struct EosB200Quantizer EosB200Quantizer;
 typedef struct EosB200Corpus EosB200Corpus;
+typedef struct EosB200IpCorpus EosB200IpCorpus;
 
 /* Accounting of one call; mirrors the fields of backend.ExecutionAccounting that the reference
  * fills per run (runtime/backend/backend.go:1364-1400): launches, bytes moved, device time. */
@@ -244,6 +245,10 @@ EOS_B200_API int eos_b200_linear(EosB200Runtime* rt, const float* h_x, int64_t r
 EOS_B200_API int eos_b200_embed_pooled_bind(EosB200Runtime* rt, const float* h_table, int vocab, int dim,
                                const float* h_projection, int out_dim, EosB200EmbedPooled** out, char** err);
 EOS_B200_API void eos_b200_embed_pooled_destroy(EosB200EmbedPooled* ep);
+/* The matmul step's `scale` attribute (matmulScale / ApplyMatMulAttributes, runtime/backend/tensor_ops.go:1259-1315):
+ * the caller resolves "rsqrt_rhs_rows" (1 / sqrt(dim)) or the literal to a number; the projected rows are multiplied by
+ * it in fp32 before the normalisation.  Default 1. */
+EOS_B200_API int eos_b200_embed_pooled_set_matmul_scale(EosB200EmbedPooled* ep, float scale, char** err);
 /* pool_then_l2 = 0: the pipeline's order (normalize each token, then mean);
  * 1: mean of the projected rows, then one L2 normalisation. h_out [batch, out_dim] fp32. */
 EOS_B200_API int eos_b200_embed_pooled_run(EosB200EmbedPooled* ep, const int32_t* h_tokens, const int32_t* h_mask, int batch,
@@ -288,7 +293,7 @@ EOS_B200_API int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* corpus);
  * (runtime/retrieval_turboquant.go:1324-1325, 1853-1887) for the Hadamard/MSE stage of the quantiser only:
  * exact top-k of norm * <R q, centroids[codes]> over the corpus, for q_count queries [q_count, dim] fp32.
  * The reference's IPQuantizer adds a QJL sign stage (Signs, ResNorm) on top of the MSE codes; those two
- * operands are not accepted here, so for bit widths where the reference uses that stage its rankings differ.
+ * operands are not accepted here (rows that carry them bind with eos_b200_ip_corpus_bind below).
  * queries_per_pass selects how many queries share one pass over the codes, and with it the kernel:
  *   0        automatic: 8 up to 16 queries, 128 up to 128 queries, 256 above;
  *   8        streaming scan (codes expanded in registers, mma.sync): the choice for a few queries;
@@ -298,7 +303,9 @@ EOS_B200_API int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* corpus);
  *            q_count exceeds 128); q_count need not be a multiple.
  * The result is the same exact top-k for every value.
  * Results [q_count, k]: ids (int64, -1 when the corpus has fewer than k rows) and scores, ordered
- * score descending then id ascending.  k <= 128. */
+ * score descending then id ascending.  k <= 128 on the fused kernels; this host call also takes k in (128, 256]
+ * (the over-fetch before a rerank, runtime/retrieval_turboquant.go:1610-1662: 200 candidates for a top-100), served
+ * by materialising the scores of a chunk of queries and selecting once per query. */
 EOS_B200_API int eos_b200_score_topk(EosB200Corpus* corpus, const float* h_queries, int q_count, int k, int queries_per_pass,
                         int64_t* h_ids, float* h_scores, EosB200Stats* stats, char** err);
 /* Device-resident variant, enqueued on `stream`.  d_keys (nullable, [q_count, k] uint64) receives
@@ -432,6 +439,36 @@ EOS_B200_API int eos_b200_dense_rerank(EosB200DenseIndex* index, const float* h_
 EOS_B200_API int eos_b200_parent_topk(EosB200Corpus* corpus, const int32_t* h_parent_of_child, int parents, const float* h_queries,
                          int q_count, int query_group, int top_n, double penalty, int k, int64_t* h_ids,
                          float* h_scores, EosB200Stats* stats, char** err);
+
+/* ---- rows quantised by the inner-product quantiser ---------------------------------------------
+ * turboquant.IPQuantized{MSE, Signs, ResNorm, Norm} (runtime/turboquant_quantized_vector.go:43-49; scored by
+ * IPQuantizer.InnerProductPrepared at runtime/retrieval_turboquant.go:1874): an MSE stage of bit_width - 1 bits, one
+ * QJL sign bit per coordinate of the projected residual, the residual's norm and the input's norm.  The module that
+ * produces them (m31labs.dev/turboquant) is not part of the reference tree, so this library takes the fields from a
+ * host that has it and scores
+ *     Norm * ( <R q, centroids[MSE]>  +  ResNorm * qjl_scale * sum_i sketch_q[i] * (Signs bit i ? +1 : -1) )
+ * where R q is the rotation of the query by (perm, signs1, signs2), and sketch_q (the query under the module's sign
+ * projection) and qjl_scale (sqrt(pi / 2) / dim in the published algorithm) come from the caller per query batch.
+ * h_mse_indices [n, dim]: one level index per byte, < mse_levels (2, 4, 8 or 16; centroids ascending and symmetric);
+ * h_signs [n, ceil(dim / 8)]: bit i of a row at byte i / 8, bit i % 8; h_resnorms, h_norms [n].
+ * Norm rule as eos_b200_corpus_bind (validateEosQuantizedVectorNorm, :26-34).  eos_b200_ip_corpus_vector_bytes is
+ * turboquantVectorBytes (runtime/turboquant_bytes.go:22-25): 392 at dim 768, bit width 4. */
+EOS_B200_API int eos_b200_ip_corpus_bind(EosB200Runtime* rt, int dim, int mse_levels, const int32_t* perm, const float* signs1,
+                                         const float* signs2, const float* centroids, const uint8_t* h_mse_indices,
+                                         const uint8_t* h_signs, const float* h_resnorms, const float* h_norms, int64_t n,
+                                         int64_t id_base, int allow_zero_norm, EosB200IpCorpus** out, char** err);
+EOS_B200_API void eos_b200_ip_corpus_destroy(EosB200IpCorpus* corpus);
+EOS_B200_API int64_t eos_b200_ip_corpus_vector_bytes(int dim, int bit_width);
+/* The 8-bit log-scale norm side-car of the reference's device encode (manta_tq_quantize_norm /
+ * manta_tq_dequantize_norm, runtime/backends/cuda/native_linux.go:1879-1904): code = round(255 (ln norm + 16) / 32)
+ * clamped to [0, 255], norm = exp(-16 + 32 code / 255).  Host arithmetic; eos_b200_corpus_bind takes the decoded
+ * norms, eos_b200_turbo_sparse_attention takes the codes. */
+EOS_B200_API void eos_b200_norm_encode_log8(const float* norms, int64_t n, uint8_t* codes);
+EOS_B200_API void eos_b200_norm_decode_log8(const uint8_t* codes, int64_t n, float* norms);
+/* Exact top-k (k <= 256) of the score above for q_count queries; results as eos_b200_score_topk. */
+EOS_B200_API int eos_b200_ip_score_topk(EosB200IpCorpus* corpus, const float* h_queries, const float* h_query_sketch,
+                                        float qjl_scale, int q_count, int k, int64_t* h_ids, float* h_scores,
+                                        EosB200Stats* stats, char** err);
 
 /* ---- sparse attention ---------------------------------------------------------------------------
  * Replaces sparseAttentionTensor (runtime/backend/attention_ops.go:218-276; device twin

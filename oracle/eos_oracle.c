@@ -262,13 +262,13 @@ EOS_ORACLE_API void eos_oracle_cls_pool(const float *in, int batches, int rows, 
  * Returns 1 on an out-of-range token id. */
 EOS_ORACLE_API int eos_oracle_embed_pooled(const float *table, int vocab, int dim, const float *projection, int out_dim,
                                            const int32_t *tokens, const int32_t *mask, int batch, int tlen,
-                                           int pool_then_l2, float *out) {
+                                           int pool_then_l2, float matmul_scale, float *out) {
     int64_t rows = (int64_t)batch * tlen;
     float *hidden = (float *)malloc(sizeof(float) * (size_t)(rows * dim));
     float *proj = (float *)malloc(sizeof(float) * (size_t)(rows * out_dim));
     int rc = eos_oracle_gather(table, vocab, dim, tokens, rows, hidden);
     if (rc == 0) {
-        eos_oracle_matmul(hidden, rows, dim, projection, out_dim, 1.0f, proj);
+        eos_oracle_matmul(hidden, rows, dim, projection, out_dim, matmul_scale, proj);
         if (!pool_then_l2) {
             float *norm = (float *)malloc(sizeof(float) * (size_t)(rows * out_dim));
             eos_oracle_normalize_rows(proj, rows, out_dim, norm);
@@ -882,6 +882,28 @@ EOS_ORACLE_API void eos_oracle_tq_decode(const uint8_t *codes, const float *norm
 EOS_ORACLE_API void eos_oracle_tq_prepare_query(const float *q, int dim, const int32_t *perm, const float *signs1,
                                                 const float *signs2, float *prepared) {
     eos_oracle_tq_rotate(q, dim, perm, signs1, signs2, 1.0f, prepared);
+}
+
+/* Score of rows quantised by the inner-product quantiser, turboquant.IPQuantized{MSE, Signs, ResNorm, Norm}
+ * (runtime/turboquant_quantized_vector.go:43-49; call site of IPQuantizer.InnerProductPrepared:
+ * runtime/retrieval_turboquant.go:1874).  The module (m31labs.dev/turboquant v0.2.0, go.mod:9) is not in the
+ * reference tree, so this restates the published two-stage estimator -- MSE stage plus the QJL sign stage on the
+ * residual, the whole estimate multiplied by Norm (turboquant_quantized_vector.go:9-13) -- with the sign projection
+ * of the query (sketch) and its scale supplied by the caller.  PARITY UNPINNED for this function.
+ * mse_idx [n, dim] one level index per byte; signs [n, ceil(dim/8)], bit i at byte i/8, bit i%8. */
+EOS_ORACLE_API void eos_oracle_tq_ip_score(const uint8_t *mse_idx, const uint8_t *signs, const float *resnorms,
+                                           const float *norms, int64_t n, int dim, const float *centroids,
+                                           const float *prepared, const float *sketch, float qjl_scale, float *scores) {
+    int sb = (dim + 7) / 8;
+    for (int64_t v = 0; v < n; v++) {
+        float a = 0.0f, b = 0.0f;
+        for (int c = 0; c < dim; c++) a += prepared[c] * centroids[mse_idx[v * dim + c]];
+        for (int i = 0; i < dim; i++) {
+            int on = (signs[v * sb + i / 8] >> (i % 8)) & 1;
+            b += on ? sketch[i] : -sketch[i];
+        }
+        scores[v] = norms[v] * (a + resnorms[v] * qjl_scale * b);
+    }
 }
 
 /* scores[v] = norm[v] * sum_c prepared[c]*centroids[code[v,c]], float accumulate in

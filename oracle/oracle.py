@@ -129,7 +129,7 @@ def mean_pool_masked(x, mask):
     return out
 
 
-def embed_pooled(table, projection, tokens, mask, pool_then_l2: bool = False):
+def embed_pooled(table, projection, tokens, mask, pool_then_l2: bool = False, matmul_scale: float = 1.0):
     t = _f32(table)
     pr = _f32(projection)
     tok = _i32(tokens)
@@ -138,7 +138,7 @@ def embed_pooled(table, projection, tokens, mask, pool_then_l2: bool = False):
     out = np.empty((b, pr.shape[1]), dtype=np.float32)
     rc = lib().eos_oracle_embed_pooled(_p(t), C.c_int(t.shape[0]), C.c_int(t.shape[1]), _p(pr), C.c_int(pr.shape[1]),
                                        _p(tok), _p(m), C.c_int(b), C.c_int(tl), C.c_int(1 if pool_then_l2 else 0),
-                                       _p(out))
+                                       C.c_float(matmul_scale), _p(out))
     if rc:
         raise IndexError("gather index out of range")
     return out
@@ -351,6 +351,17 @@ def tq_score(codes, norms, dim, bits, centroids, prepared):
     out = np.empty(c.shape[0], dtype=np.float32)
     lib().eos_oracle_tq_score(_p(c), _p(nr), C.c_int64(c.shape[0]), C.c_int(dim), C.c_int(bits), _p(_f32(centroids)),
                               _p(_f32(prepared)), _p(out))
+    return out
+
+
+def tq_ip_score(mse_idx, signs, resnorms, norms, centroids, prepared, sketch, qjl_scale: float):
+    """Score of IP-quantised rows (MSE stage + QJL sign stage); the module is absent: parity unpinned."""
+    idx = np.ascontiguousarray(mse_idx, dtype=np.uint8)
+    sg = np.ascontiguousarray(signs, dtype=np.uint8)
+    n, dim = idx.shape
+    out = np.empty(n, dtype=np.float32)
+    lib().eos_oracle_tq_ip_score(_p(idx), _p(sg), _p(_f32(resnorms)), _p(_f32(norms)), C.c_int64(n), C.c_int(dim),
+                                 _p(_f32(centroids)), _p(_f32(prepared)), _p(_f32(sketch)), C.c_float(qjl_scale), _p(out))
     return out
 
 

@@ -116,3 +116,18 @@ def test_sparse_attention_plan_matches_oracle_knobs():
         plan = plan_sparse_attention(8, kl, tk, bs, tb)
         assert plan.top_k == (O.sparse_attention_budget(tk, kl) if kl > 0 else tk)
         assert (plan.route_block_size, plan.route_top_blocks) == O.sparse_attention_route(kl, bs, tb)
+
+
+def test_log8_norm_sidecar_matches_the_oracle():
+    """Host arithmetic of the C ABI (no device): the 8-bit log-scale norm codes of the reference's encode
+    (runtime/backends/cuda/native_linux.go:1879-1904) against the oracle's restatement, edge values included."""
+    from eos_b200.turboquant import norm_decode_log8, norm_encode_log8
+    from oracle import oracle as O
+    rng = np.random.default_rng(3)
+    norms = np.concatenate([np.exp(rng.uniform(-20, 20, 5000)).astype(np.float32),
+                            np.array([0.0, -1.0, np.inf, np.nan, 1.0, 1e-7, 8886110.0, 1e7], np.float32)])
+    codes = norm_encode_log8(norms)
+    assert np.array_equal(codes, O.tq_norm_code(norms))
+    allc = np.arange(256, dtype=np.uint8)
+    assert np.array_equal(norm_decode_log8(allc).view(np.uint32), O.tq_norm_value(allc).view(np.uint32))
+    assert codes[-8] == 0 and codes[-7] == 0 and codes[-6] == 255 and codes[-5] == 0

@@ -56,3 +56,25 @@ def test_edges(rt):
     with pytest.raises(ValueError):
         pipe.run(ids[:0], mask[:0])
     pipe.close()
+
+
+@pytest.mark.parametrize("scale", ["rsqrt_rhs_rows", -0.5, 0.0, "none"])
+def test_matmul_scale_attribute(rt, scale):
+    """The matmul step's `scale` attribute (runtime/backend/tensor_ops.go:1259-1315): a positive factor cancels under
+    the normalisation up to rounding, a negative one flips the embedding, zero leaves nothing to normalise."""
+    import eos_b200
+    from oracle import oracle as O
+    table, proj, ids, mask = _config(211, 64, 48, 6, 33, 3, seed=55)
+    value = {"rsqrt_rhs_rows": float(np.float32(1.0 / np.sqrt(64.0))), "none": 1.0}.get(scale, scale)
+    for pool_then_l2 in (False, True):
+        pipe = eos_b200.EmbedPooledPipeline(rt, table, proj, matmul_scale=scale)
+        out = pipe.run(ids, mask, pool_then_l2=pool_then_l2)
+        ref = O.embed_pooled(table, proj, ids, mask, pool_then_l2=pool_then_l2, matmul_scale=float(value))
+        assert np.abs(out - ref).max() <= 2e-5
+        if value == 0.0:
+            assert not out.any()
+        pipe.close()
+    with pytest.raises(ValueError):
+        eos_b200.EmbedPooledPipeline(rt, table, proj, matmul_scale="sqrt")
+    with pytest.raises(ValueError):
+        eos_b200.EmbedPooledPipeline(rt, table, proj, matmul_scale=float("inf"))

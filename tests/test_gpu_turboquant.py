@@ -247,7 +247,7 @@ def test_argument_validation(rt):
     ids, scores = c.score_topk(q, 5)
     assert np.isfinite(scores).all()
     with pytest.raises(eos_b200.EosB200Error):
-        c.score_topk(q, 129)
+        c.score_topk(q, 257)                      # the host call takes k up to 256
     with pytest.raises(eos_b200.EosB200Error):
         c.score_topk(q, 5, queries_per_pass=12)
     c.close()
@@ -493,5 +493,84 @@ def test_maxsim_argument_errors(rt):
                       ((60, 32, 64, 5), "multiple of query_group"), ((64, 32, 128, 200), "k must")):
         with pytest.raises(Exception, match=msg):
             corpus.maxsim_topk_device(dq.data_ptr(), args[0], args[1], args[2], args[3], ids.data_ptr(), sc.data_ptr())
+    corpus.close()
+    qz.close()
+
+
+def _ip_quantise(x, spec3, proj_seed):
+    """Test-side producer of IPQuantized fields by the published two-stage scheme: MSE stage (spec3), then the signs
+    of a seeded Gaussian projection of the residual in the rotated space and the residual's norm."""
+    from oracle import oracle as O
+    dim = x.shape[1]
+    norms = np.linalg.norm(x, axis=1).astype(np.float32)
+    unit = (x / np.maximum(norms, 1e-30)[:, None]).astype(np.float32)
+    rot = np.stack([O.tq_rotate(u, spec3.perm, spec3.signs1, spec3.signs2) for u in unit])
+    idx = np.searchsorted(spec3.boundaries, rot).astype(np.uint8)
+    resid = rot - spec3.centroids[idx]
+    proj = np.random.default_rng(proj_seed).standard_normal((dim, dim)).astype(np.float32)
+    signs = np.packbits((resid @ proj.T) >= 0, axis=1, bitorder="little")
+    return idx, signs, np.linalg.norm(resid, axis=1).astype(np.float32), norms, proj
+
+
+@pytest.mark.parametrize("dim,levels,n,nq,k", [(768, 8, 3000, 11, 100), (128, 4, 5000, 5, 200), (96, 2, 700, 3, 256)])
+def test_ip_quantised_rows(rt, dim, levels, n, nq, k):
+    """Rows carrying MSE codes + QJL signs + ResNorm + Norm: GPU scores and top-k vs the oracle's restatement of the
+    two-stage estimator.  392 bytes per vector at dim 768, bit width 4, as the reference accounts them."""
+    import math
+    import eos_b200
+    from eos_b200.turboquant import IpCorpus, RotationSpec, lloyd_max_gaussian
+    from oracle import oracle as O
+    base = eos_b200.make_rotation_spec(dim, 2, seed=402)
+    cent, bound = lloyd_max_gaussian(levels, 1.0 / math.sqrt(dim))
+    spec = RotationSpec(dim, int(math.log2(levels)), base.perm, base.signs1, base.signs2, cent, bound)
+    rng = np.random.default_rng(5)
+    x = _unit_rows(n, dim, 31) * rng.uniform(0.5, 2.0, (n, 1)).astype(np.float32)
+    q = _unit_rows(nq, dim, 32).astype(np.float16).astype(np.float32)
+    idx, signs, resn, norms, proj = _ip_quantise(x, spec, 77)
+    prepared = np.stack([O.tq_prepare_query(qi, spec.perm, spec.signs1, spec.signs2) for qi in q])
+    sketch = (prepared @ proj.T).astype(np.float32)
+    qjl = math.sqrt(math.pi / 2.0) / dim
+    ref = np.stack([O.tq_ip_score(idx, signs, resn, norms, cent, prepared[i], sketch[i], qjl) for i in range(nq)])
+    assert IpCorpus.vector_bytes(768, 4) == 392
+    corpus = IpCorpus(rt, dim, spec.perm, spec.signs1, spec.signs2, cent, idx, signs, resn, norms, id_base=1000)
+    ids, scores = corpus.score_topk(q, sketch, qjl, k)
+    tol = 1e-3 * float(np.abs(ref).max())
+    for i in range(nq):
+        _check_topk(ids[i], scores[i], ref[i], k, 1000, tol)
+    # what the sign stage buys is an unbiased estimate: the MSE stage alone shrinks inner products (slope < 1 against
+    # the true values), the two-stage estimate does not
+    true = q @ x.T
+    mse_only = np.stack([O.tq_ip_score(idx, signs, resn * 0, norms, cent, prepared[i], sketch[i], qjl) for i in range(nq)])
+    slope_ip = float((ref * true).sum() / (true * true).sum())
+    slope_mse = float((mse_only * true).sum() / (true * true).sum())
+    assert abs(slope_ip - 1.0) < 0.1 and abs(slope_ip - 1.0) <= abs(slope_mse - 1.0) + 0.02, (slope_ip, slope_mse)
+    with pytest.raises(RuntimeError, match="256"):
+        corpus.score_topk(q, sketch, qjl, 257)
+    corpus.close()
+    bad = idx.copy()
+    bad[0, 0] = levels
+    with pytest.raises(RuntimeError, match="out of range"):
+        IpCorpus(rt, dim, spec.perm, spec.signs1, spec.signs2, cent, bad, signs, resn, norms)
+
+
+def test_wide_k_overfetch(rt):
+    """k = 200 (the over-fetch before a rerank to 100, runtime/retrieval_turboquant.go:1610-1662) through the host
+    call, against the oracle's scores; the first 100 of it equal the fused kernels' top-100."""
+    spec, qz, codes, norms, q = _setup(rt, 768, 4, 9000, 19, seed=61)
+    import eos_b200
+    corpus = eos_b200.Corpus(qz, codes, norms, id_base=5)
+    ref = _oracle_scores(spec, codes, norms, q)
+    tol = 1e-3 * float(np.abs(ref).max())
+    ids, scores = corpus.score_topk(q, 200)
+    for i in range(q.shape[0]):
+        _check_topk(ids[i], scores[i], ref[i], 200, 5, tol)
+    ids100, _ = corpus.score_topk(q, 100)
+    # two kernels, two summation orders: rows whose scores differ in the last bits may swap places
+    assert np.mean([len(set(ids[i, :100]) & set(ids100[i])) for i in range(q.shape[0])]) >= 99.0
+    ids256, scores256 = corpus.score_topk(q[:3], 256)
+    for i in range(3):
+        _check_topk(ids256[i], scores256[i], ref[i], 256, 5, tol)
+    with pytest.raises(RuntimeError):
+        corpus.score_topk(q, 257)
     corpus.close()
     qz.close()
