@@ -307,11 +307,14 @@ class IpCorpus:
         if idx.ndim != 2 or idx.shape[1] != dim or sg.shape != (idx.shape[0], (dim + 7) // 8) or \
                 rn.size != idx.shape[0] or nr.size != idx.shape[0]:
             raise ValueError("ip corpus fields do not match dim / row count")
+        pm, s1, s2 = _i32(perm), _f32(signs1), _f32(signs2)   # named, so that they outlive the call
+        if pm.size != dim or s1.size != dim or s2.size != dim:
+            raise ValueError("rotation arrays do not match dim")
         self.n = idx.shape[0]
         self.handle = C.c_void_p()
-        _lib.call("eos_b200_ip_corpus_bind", rt.handle, int(dim), int(cent.size), _ptr(_i32(perm)), _ptr(_f32(signs1)),
-                  _ptr(_f32(signs2)), _ptr(cent), _ptr(idx), _ptr(sg), _ptr(rn), _ptr(nr), self.n, int(id_base),
-                  1 if allow_zero_norm else 0, C.byref(self.handle))
+        _lib.call("eos_b200_ip_corpus_bind", rt.handle, int(dim), int(cent.size), _ptr(pm), _ptr(s1), _ptr(s2), _ptr(cent),
+                  _ptr(idx), _ptr(sg), _ptr(rn), _ptr(nr), self.n, int(id_base), 1 if allow_zero_norm else 0,
+                  C.byref(self.handle))
         self.last_stats = Stats()
 
     @staticmethod

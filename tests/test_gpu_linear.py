@@ -88,6 +88,21 @@ def test_linear_per_tensor_scale_and_dense_weights(rt):
     assert (np.abs(y - ref2) <= 1.5e-3 * np.abs(ref2) + 1e-3).all()
 
 
+def test_linear_from_packed_q8_payload(rt):
+    """A packed q8 tensor payload + its tensor_scales entry (runtime/mll_export.go:902-949) binds as it is: the
+    projection equals the one over the payload's decoded values."""
+    import eos_b200
+    from eos_b200 import formats
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((130, 96)).astype(np.float32)
+    wf = (rng.standard_normal((40, 96)) * 0.07).astype(np.float32)
+    raw, scale = formats.pack_quantized_tensor(wf, 8)
+    weight = formats.q8_weight_from_payload(raw, wf.shape, scale)
+    y = eos_b200.linear(rt, x, weight, None)
+    ref = _reference(x, formats.decode_tensor_payload("q8", raw, wf.shape, scale), None, 0, None)
+    assert (np.abs(y - ref) <= 1.5e-3 * np.abs(ref) + 1e-3).all()
+
+
 def test_linear_rejects_bad_arguments(rt):
     import eos_b200
     x = np.zeros((4, 24), np.float32)
