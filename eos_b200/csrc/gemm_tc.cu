@@ -28,9 +28,10 @@
 // leader's MMA thread issues tcgen05.mma.cta_group::2 (M = 256) reading both CTAs' shared memory, and
 // each CTA's epilogue drains its own 128 rows from its own tensor memory.  TMA completions of both
 // CTAs count on the leader's full barrier; the MMA commits release both CTAs' ring stages; both
-// epilogues arrive on the leader's accumulator-empty barrier.  Measured on the encoder's shapes it is
-// not faster than one CTA per tile (both are bound by shared-memory bandwidth and, at K = 768, by the
-// epilogue), so it is opt-in: environment EOS_B200_GEMM_CTA_PAIR=1.
+// epilogues arrive on the leader's accumulator-empty barrier.  Measured on the encoder's shapes it wins where the
+// main loop dominates (K = 3072: 6 % faster, the operand feed per CTA drops by a third) and loses at K = 768, so
+// it serves projections with K >= 2048; environment EOS_B200_GEMM_CTA_PAIR=1 forces it for every f16 projection,
+// =0 turns it off.
 // Every mbarrier wait is bounded (common.cuh: mbar_wait); on a timeout the kernel raises a CTA-wide
 // abort flag, all roles leave their loops, TMEM is freed and the status word is set.
 #include "gemm_tc.cuh"
@@ -91,7 +92,7 @@ struct Cfg {
     static constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;  // + alignment slack
 };
 
-// kMode >= 0 fixes the epilogue at compile time (the one-CTA f16 kernel, which serves the encoder: the residual
+// kMode >= 0 fixes the epilogue at compile time (the one-CTA kernels, which serve the encoder: the residual
 // registers and the activation code of the other modes disappear); kMode < 0 reads it from the parameters.
 template <bool kBInt8, bool kPair, int kMode>
 __global__ void __launch_bounds__(Cfg<kBInt8, kPair>::kThreads, 1)
@@ -465,9 +466,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         v[j] = fmaf(__uint_as_float(r[j]), f.x, f.y);
                         v[j + 1] = fmaf(__uint_as_float(r[j + 1]), f.z, f.w);
                     }
-                    if (mode == kEpiBiasGeluErf) {
+                    // the erf GELU is evaluated on f16 pairs (the output is f16 anyway)
+                    const bool kHalfGelu = mode == kEpiBiasGeluErf;
+                    uint32_t hv[8];
+                    if (kHalfGelu) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = gelu_erf_fast(v[j]);
+                        for (int j = 0; j < 8; ++j) {
+                            const __half2 g = gelu_erf_h2(__floats2half2_rn(v[2 * j], v[2 * j + 1]));
+                            hv[j] = *reinterpret_cast<const uint32_t*>(&g);
+                        }
                     } else if (mode == kEpiBiasGeluTanh) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
@@ -488,6 +495,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                         for (int q = 0; q < 2; ++q) {
                             uint4 o;
+                            if (kHalfGelu) {
+                                *reinterpret_cast<uint4*>(slab + lane * 64 + (((ch * 2 + q) ^ ((lane >> 1) & 3)) << 4)) =
+                                    make_uint4(hv[q * 4], hv[q * 4 + 1], hv[q * 4 + 2], hv[q * 4 + 3]);
+                                continue;
+                            }
                             __half2 h0 = __floats2half2_rn(v[q * 8 + 0], v[q * 8 + 1]);
                             __half2 h1 = __floats2half2_rn(v[q * 8 + 2], v[q * 8 + 3]);
                             __half2 h2 = __floats2half2_rn(v[q * 8 + 4], v[q * 8 + 5]);
@@ -505,6 +517,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         for (int j = 0; j < 16; ++j) {
                             if (nc + j < p.n) {
                                 float x = v[j];
+                                if (kHalfGelu) {
+                                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hv[j >> 1]));
+                                    x = (j & 1) ? f.y : f.x;
+                                }
                                 if (residual) x += __half2float(res_row[nc + j]);
                                 out_row[nc + j] = __float2half_rn(x);
                             }
@@ -579,6 +595,7 @@ extern "C" __attribute__((visibility("default"))) int eos_b200_debug_gemm_timing
 
 namespace {
 int g_pair_clusters = -1;  // CTA pairs that can be resident at once; 0 = pair mode unavailable
+int g_pair_min_k = 2048;   // pair mode serves projections at least this deep (EOS_B200_GEMM_CTA_PAIR=1: all, =0: none)
 
 cudaLaunchConfig_t pair_launch_config(int grid, cudaStream_t stream, cudaLaunchAttribute* attr) {
     attr->id = cudaLaunchAttributeClusterDimension;
@@ -597,8 +614,17 @@ cudaLaunchConfig_t pair_launch_config(int grid, cudaStream_t stream, cudaLaunchA
 }  // namespace
 
 std::string gemm_global_init() {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true, false, -1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<true, false, kEpiBias>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg<true, false>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<true, false, kEpiBiasGeluErf>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<true, false>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<true, false, kEpiBiasResidual>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<true, false>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<true, false, kEpiBiasGeluTanh>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<true, false>::kSmemBytes);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(gemm_tc_kernel<false, false, kEpiBias>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg<false, false>::kSmemBytes);
@@ -618,7 +644,9 @@ std::string gemm_global_init() {
     if (g_pair_clusters < 0) {
         g_pair_clusters = 0;
         const char* on = getenv("EOS_B200_GEMM_CTA_PAIR");
-        if (on != nullptr && on[0] != '\0' && on[0] != '0') {
+        const bool off = on != nullptr && on[0] == '0';
+        if (on != nullptr && on[0] != '\0' && !off) g_pair_min_k = 0;
+        if (!off) {
             int dev = 0, sms = 0, clusters = 0;
             cudaLaunchAttribute attr;
             if (cudaGetDevice(&dev) == cudaSuccess &&
@@ -641,7 +669,7 @@ std::string gemm_make_plan(GemmPlan* plan, const __half* a, int lda, const void*
     if (params.ldo % 8 != 0) return "gemm: output row stride must be a multiple of 8 elements";
     if (params.mode == kEpiBiasResidual && (params.residual == nullptr || params.ldr % 8 != 0))
         return "gemm: residual epilogue needs a residual pointer with a row stride that is a multiple of 8";
-    const bool pair = !b_int8 && g_pair_clusters > 0;
+    const bool pair = !b_int8 && g_pair_clusters > 0 && params.k >= g_pair_min_k;
     std::string err = encode_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)params.k,
                                 (uint64_t)params.m_alloc, (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!err.empty()) return "gemm A: " + err;
@@ -674,8 +702,22 @@ void gemm_launch(const GemmPlan& plan, cudaStream_t stream) {
         cudaLaunchConfig_t cfg = pair_launch_config(plan.grid, stream, &attr);
         cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, -1>, plan.tm_a, plan.tm_b, plan.p);
     } else if (plan.b_int8) {
-        gemm_tc_kernel<true, false, -1><<<plan.grid, Cfg<true, false>::kThreads, Cfg<true, false>::kSmemBytes, stream>>>(
-            plan.tm_a, plan.tm_b, plan.p);
+        constexpr int kT = Cfg<true, false>::kThreads;
+        constexpr uint32_t kS = Cfg<true, false>::kSmemBytes;
+        switch (plan.p.mode) {
+            case kEpiBiasGeluErf:
+                gemm_tc_kernel<true, false, kEpiBiasGeluErf><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                break;
+            case kEpiBiasResidual:
+                gemm_tc_kernel<true, false, kEpiBiasResidual><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                break;
+            case kEpiBiasGeluTanh:
+                gemm_tc_kernel<true, false, kEpiBiasGeluTanh><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                break;
+            default:
+                gemm_tc_kernel<true, false, kEpiBias><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                break;
+        }
     } else {
         constexpr int kT = Cfg<false, false>::kThreads;
         constexpr uint32_t kS = Cfg<false, false>::kSmemBytes;
