@@ -1764,7 +1764,7 @@ int eos_b200_quantize(EosB200Quantizer* qz, const float* h_x, int64_t n, uint8_t
     if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
     if (e == cudaSuccess && stats != nullptr) {
         std::memset(stats, 0, sizeof(*stats));
-        stats->kernel_launches = 1;
+        stats->kernel_launches = 2;
         stats->uploaded_bytes = (int64_t)n * qz->dim * 4;
         stats->downloaded_bytes = (int64_t)n * (cb + 4);
         cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);

@@ -31,6 +31,21 @@ __constant__ float c_norm_of_code[256];
 // q . k with separate multiply and add, d ascending (the reference's float loop)
 __device__ __forceinline__ float dot_in_order(const float* __restrict__ q, const float* __restrict__ k, int dim) {
     float sum = 0.f;
+    if ((dim & 3) == 0 && ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(q)) & 15u) == 0) {
+        // 16-byte loads, the same adds in the same order
+        const float4* k4 = reinterpret_cast<const float4*>(k);
+        const float4* q4 = reinterpret_cast<const float4*>(q);
+#pragma unroll 4
+        for (int d = 0; d < (dim >> 2); ++d) {
+            const float4 kv = __ldg(k4 + d);
+            const float4 qv = q4[d];
+            sum = __fadd_rn(sum, __fmul_rn(qv.x, kv.x));
+            sum = __fadd_rn(sum, __fmul_rn(qv.y, kv.y));
+            sum = __fadd_rn(sum, __fmul_rn(qv.z, kv.z));
+            sum = __fadd_rn(sum, __fmul_rn(qv.w, kv.w));
+        }
+        return sum;
+    }
     for (int d = 0; d < dim; ++d) sum = __fadd_rn(sum, __fmul_rn(q[d], __ldg(k + d)));
     return sum;
 }

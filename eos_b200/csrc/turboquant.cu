@@ -37,9 +37,40 @@ __device__ void warp_rotate(const float* x, float prescale, const TqSpec& s, flo
     __syncwarp();
 }
 
+// norms[v] = sqrt of the sequential float sum of squares of vector v, in index order: the order of the reference's
+// one-thread-per-vector kernel (manta_turboq_encode, runtime/backends/cuda/native_linux.go:1906-1957), so the bits
+// are the same.  A sequential sum cannot be split over lanes, so each lane sums a vector of its own: 32 vectors per
+// warp advance together (a lane's 16-byte loads walk its own row; a 32-byte sector serves two of them from L1).
+__global__ void __launch_bounds__(256)
+tq_norms_kernel(const float* __restrict__ x, long long n, int dim, float* __restrict__ norms) {
+    const long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= n) return;
+    const float* xv = x + v * dim;
+    float sq = 0.f;
+    if ((dim & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+        const float4* x4 = reinterpret_cast<const float4*>(xv);
+#pragma unroll 4
+        for (int c = 0; c < (dim >> 2); ++c) {
+            const float4 f = __ldg(x4 + c);
+            sq = __fadd_rn(sq, __fmul_rn(f.x, f.x));
+            sq = __fadd_rn(sq, __fmul_rn(f.y, f.y));
+            sq = __fadd_rn(sq, __fmul_rn(f.z, f.z));
+            sq = __fadd_rn(sq, __fmul_rn(f.w, f.w));
+        }
+    } else {
+        for (int c = 0; c < dim; ++c) {
+            const float f = __ldg(xv + c);
+            sq = __fadd_rn(sq, __fmul_rn(f, f));
+        }
+    }
+    norms[v] = __fsqrt_rn(sq);
+}
+
+// One warp per vector: unit-normalise (norm from tq_norms_kernel), rotate, nearest centroid per coordinate by
+// bisection over the boundaries, pack.
 __global__ void __launch_bounds__(256)
 tq_pack_kernel(const float* __restrict__ x, long long n, TqSpec s, uint8_t* __restrict__ codes,
-               float* __restrict__ norms) {
+               const float* __restrict__ norms) {
     extern __shared__ float sm_f[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warps = blockDim.x >> 5;
@@ -51,22 +82,15 @@ tq_pack_kernel(const float* __restrict__ x, long long n, TqSpec s, uint8_t* __re
     for (long long v = (long long)blockIdx.x * warps + warp; v < n; v += (long long)gridDim.x * warps) {
         const float* xv = x + v * s.dim;
         // the vector moves to shared memory with coalesced loads (rot serves as the staging buffer: the rotation
-        // reads all of it before it writes any of it); the sum of squares stays a sequential float sum in index
-        // order, the order the reference's one-thread-per-vector kernel uses, so the norm bits are the same
+        // reads all of it before it writes any of it)
         if ((s.dim & 3) == 0 && (reinterpret_cast<uintptr_t>(xv) & 15u) == 0) {
             for (int i = lane; i < (s.dim >> 2); i += 32)
                 reinterpret_cast<float4*>(rot)[i] = __ldg(reinterpret_cast<const float4*>(xv) + i);
         } else {
             for (int i = lane; i < s.dim; i += 32) rot[i] = __ldg(xv + i);
         }
+        const float norm = __ldg(norms + v);
         __syncwarp();
-        float norm = 0.f;
-        if (lane == 0) {
-            float sq = 0.f;
-            for (int c = 0; c < s.dim; ++c) sq = __fadd_rn(sq, __fmul_rn(rot[c], rot[c]));
-            norm = __fsqrt_rn(sq);
-        }
-        norm = __shfl_sync(0xffffffffu, norm, 0);
         const float scale = norm > 1.0e-12f ? __fdiv_rn(1.0f, norm) : 1.0f;
         warp_rotate(rot, scale, s, work, rot, lane);
         uint8_t* cv = codes + v * cb;
@@ -86,7 +110,6 @@ tq_pack_kernel(const float* __restrict__ x, long long n, TqSpec s, uint8_t* __re
             }
             cv[byte] = (uint8_t)out;
         }
-        if (lane == 0) norms[v] = norm;
         __syncwarp();
     }
 }
@@ -1203,6 +1226,7 @@ void launch_tq_pack(const float* x, int64_t n, const TqSpec& spec, uint8_t* code
     const size_t smem = (size_t)warps * 2 * spec.dim * sizeof(float);
     long long blocks = (n + warps - 1) / warps;
     if (blocks > (long long)g_sm_count * 8) blocks = (long long)g_sm_count * 8;
+    tq_norms_kernel<<<(int)((n + 255) / 256), 256, 0, stream>>>(x, (long long)n, spec.dim, norms);
     tq_pack_kernel<<<(int)blocks, warps * 32, smem, stream>>>(x, (long long)n, spec, codes, norms);
 }
 

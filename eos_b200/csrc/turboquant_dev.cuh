@@ -141,28 +141,72 @@ __device__ __forceinline__ int highest_pow2_le(int v) {
     return p;
 }
 
-// In-place blocked normalised FWHT of `work` (shared memory) by one warp.  Butterflies are
-// a+b / a-b in float exactly as the sequential form; their order inside a stage is irrelevant.
+// G consecutive butterfly stages (the first has distance 2^lg) of a block of `size` floats in shared memory, by one
+// warp: a lane takes the 2^G elements that these stages combine among themselves, runs the stages in registers and
+// writes them back, scaled by `scale` (1 except after the last stage).  Every butterfly is the a + b / a - b of the
+// sequential form on the same pair, so the result is that form's bit for bit.
+template <int G>
+__device__ __forceinline__ void warp_fwht_stages(float* v, int size, int lg, float scale, int lane) {
+    constexpr int E = 1 << G;
+    const int stride = 1 << lg;
+    const bool wide = G == 3 && lg == 0 && (reinterpret_cast<uintptr_t>(v) & 15u) == 0;   // 8 neighbours: two 16-byte accesses
+    for (int p = lane; p < (size >> G); p += 32) {
+        const int low = p & (stride - 1), high = p >> lg;
+        float* b = v + ((high << (lg + G)) | low);
+        float e[E];
+        if (wide) {
+            const float4 lo4 = reinterpret_cast<const float4*>(b)[0], hi4 = reinterpret_cast<const float4*>(b)[E > 4 ? 1 : 0];
+            e[0] = lo4.x, e[1] = lo4.y;
+            if (E > 2) e[2] = lo4.z, e[3] = lo4.w;
+            if (E > 4) e[4] = hi4.x, e[5] = hi4.y, e[6] = hi4.z, e[7] = hi4.w;
+        } else {
+#pragma unroll
+            for (int k = 0; k < E; ++k) e[k] = b[k * stride];
+        }
+#pragma unroll
+        for (int st = 0; st < G; ++st) {
+#pragma unroll
+            for (int k = 0; k < E; ++k) {
+                if ((k & (1 << st)) == 0) {
+                    const float a = e[k], c = e[k | (1 << st)];
+                    e[k] = __fadd_rn(a, c);
+                    e[k | (1 << st)] = __fsub_rn(a, c);
+                }
+            }
+        }
+        if (scale != 1.0f) {
+#pragma unroll
+            for (int k = 0; k < E; ++k) e[k] = __fmul_rn(e[k], scale);
+        }
+        if (wide) {
+            reinterpret_cast<float4*>(b)[0] = make_float4(e[0], e[1], e[E > 2 ? 2 : 0], e[E > 2 ? 3 : 0]);
+            if (E > 4) reinterpret_cast<float4*>(b)[1] = make_float4(e[E > 4 ? 4 : 0], e[E > 4 ? 5 : 0], e[E > 4 ? 6 : 0], e[E > 4 ? 7 : 0]);
+        } else {
+#pragma unroll
+            for (int k = 0; k < E; ++k) b[k * stride] = e[k];
+        }
+    }
+    __syncwarp();
+}
+
+// In-place blocked normalised FWHT of `work` (shared memory) by one warp: blocks of the largest power of two that
+// still fits, each transformed and multiplied by 1 / sqrt(size) (the reference's apply_blocks).  Stages run three at
+// a time in registers; the scaling rides on the last group.
 __device__ __forceinline__ void warp_fwht_blocks(float* work, int dim, int lane) {
     int offset = 0, remaining = dim;
     while (remaining > 0) {
         const int size = highest_pow2_le(remaining);
         float* v = work + offset;
+        const int stages = 31 - __clz(size);
+        const float scale = size > 1 ? __fdiv_rn(1.0f, __fsqrt_rn((float)size)) : 1.0f;
         int lg = 0;
-        for (int step = 1; step < size; step <<= 1, ++lg) {
-            for (int p = lane; p < (size >> 1); p += 32) {
-                const int j = ((p >> lg) << (lg + 1)) + (p & (step - 1));   // step is a power of two
-                const float a = v[j], b = v[j + step];
-                v[j] = __fadd_rn(a, b);
-                v[j + step] = __fsub_rn(a, b);
-            }
-            __syncwarp();
+        while (stages - lg > 3) {
+            warp_fwht_stages<3>(v, size, lg, 1.0f, lane);
+            lg += 3;
         }
-        if (size > 1) {
-            const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)size));
-            for (int i = lane; i < size; i += 32) v[i] = __fmul_rn(v[i], scale);
-            __syncwarp();
-        }
+        if (stages - lg == 3) warp_fwht_stages<3>(v, size, lg, scale, lane);
+        else if (stages - lg == 2) warp_fwht_stages<2>(v, size, lg, scale, lane);
+        else if (stages - lg == 1) warp_fwht_stages<1>(v, size, lg, scale, lane);
         offset += size;
         remaining -= size;
     }

@@ -129,9 +129,93 @@ def case_attention() -> None:
     rt.close()
 
 
+def case_maxsim(docs: int = 20000, children: int = 128, dim: int = 128, bits: int = 2, nq: int = 16, qt: int = 32) -> None:
+    """Late interaction: nq queries x qt token vectors against docs x children packed vectors, top-100 documents."""
+    import torch
+    import eos_b200
+    from eos_b200 import turboquant as tq
+    rt = eos_b200.Runtime(0)
+    ts = torch.cuda.Stream()
+    stream = ts.cuda_stream
+    spec = eos_b200.make_rotation_spec(dim, bits, seed=402)
+    qz = eos_b200.Quantizer(rt, spec)
+    n = docs * children
+    with torch.cuda.stream(ts):
+        x = torch.empty((n, dim), dtype=torch.float32, device="cuda")
+        codes = torch.empty((n, spec.code_bytes), dtype=torch.uint8, device="cuda")
+        norms = torch.empty((n,), dtype=torch.float32, device="cuda")
+        queries = torch.empty((nq * qt, dim), dtype=torch.float32, device="cuda")
+        ids = torch.empty((nq, 100), dtype=torch.int64, device="cuda")
+        scores = torch.empty((nq, 100), dtype=torch.float32, device="cuda")
+    tq.synth_gaussian_device(rt, 503, 0, n, dim, True, x.data_ptr(), stream)
+    tq.synth_gaussian_device(rt, 504, 0, nq * qt, dim, True, queries.data_ptr(), stream)
+    qz.quantize_device(x.data_ptr(), n, codes.data_ptr(), norms.data_ptr(), stream)
+    torch.cuda.synchronize()
+    corpus = eos_b200.Corpus(qz, device_ptrs=(codes.data_ptr(), norms.data_ptr(), n))
+    for _ in range(2):
+        corpus.maxsim_topk_device(queries.data_ptr(), nq * qt, qt, children, 100, ids.data_ptr(), scores.data_ptr(), None, stream)
+    corpus.sync(stream)
+    corpus.profile_begin(64)
+    corpus.maxsim_topk_device(queries.data_ptr(), nq * qt, qt, children, 100, ids.data_ptr(), scores.data_ptr(), None, stream)
+    ms, launches = corpus.profile_end(stream)
+    print(f"maxsim {docs} docs x {children} x {dim}d {bits}-bit, {nq} x {qt} query vectors: {ms / launches:.3f} ms per main "
+          f"launch ({launches} launches), {2.0 * 128 * n * dim / (ms / launches) / 1e9:.0f} TFLOP/s")
+    corpus.close()
+    qz.close()
+    rt.close()
+
+
+def case_pack(n: int = 1_000_000, dim: int = 768, bits: int = 4) -> None:
+    import torch
+    import eos_b200
+    from eos_b200 import turboquant as tq
+    rt = eos_b200.Runtime(0)
+    ts = torch.cuda.Stream()
+    stream = ts.cuda_stream
+    spec = eos_b200.make_rotation_spec(dim, bits, seed=402)
+    qz = eos_b200.Quantizer(rt, spec)
+    with torch.cuda.stream(ts):
+        x = torch.empty((n, dim), dtype=torch.float32, device="cuda")
+        codes = torch.empty((n, spec.code_bytes), dtype=torch.uint8, device="cuda")
+        norms = torch.empty((n,), dtype=torch.float32, device="cuda")
+    tq.synth_gaussian_device(rt, 503, 0, n, dim, True, x.data_ptr(), stream)
+    for _ in range(2):
+        qz.quantize_device(x.data_ptr(), n, codes.data_ptr(), norms.data_ptr(), stream)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ts)
+    qz.quantize_device(x.data_ptr(), n, codes.data_ptr(), norms.data_ptr(), stream)
+    e1.record(ts)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    print(f"pack {n} x {dim} at {bits} bits: {ms:.3f} ms, {n / ms / 1e3:.1f} M vectors/s, "
+          f"{n * (dim * 4 + spec.vector_bytes) / ms / 1e6:.0f} GB/s")
+    qz.close()
+    rt.close()
+
+
+def case_sparse_attention(batches: int = 8, q_len: int = 2048, k_len: int = 8192, dim: int = 64, top_k: int = 64,
+                          block: int = 64, top_blocks: int = 16) -> None:
+    import numpy as np
+    import eos_b200
+    from eos_b200.attention import sparse_attention
+    rt = eos_b200.Runtime(0)
+    rng = np.random.default_rng(1)
+    q = rng.standard_normal((batches, q_len, dim)).astype(np.float32)
+    k = rng.standard_normal((batches, k_len, dim)).astype(np.float32)
+    v = rng.standard_normal((batches, k_len, dim)).astype(np.float32)
+    for rbs, rtb, name in ((0, 0, "exact"), (block, top_blocks, "block_anchor")):
+        st = eos_b200.Stats()
+        sparse_attention(rt, q, k, v, top_k, rbs, rtb)
+        sparse_attention(rt, q, k, v, top_k, rbs, rtb, stats=st)
+        print(f"sparse attention {name}: {batches} x {q_len} queries x {k_len} keys x {dim}d, top {top_k}: "
+              f"{st.device_ms:.3f} ms incl. copies")
+    rt.close()
+
+
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": case_gemm, "gemm_res": lambda: case_gemm(True), "scan": case_scan, "score_tc": case_score_tc, "score_tc256": lambda: case_score_tc(per_pass=256), "attention": case_attention,
+     "maxsim": case_maxsim, "pack": case_pack, "sparse_attention": case_sparse_attention,
      "gemm_f16w": lambda: case_gemm(False, 1), "gemm_res_f16w": lambda: case_gemm(True, 1),
      "gemm_big": lambda: case_gemm(False, 0, 131072), "gemm_res_big": lambda: case_gemm(True, 0, 131072),
      "gemm_big_f16w": lambda: case_gemm(False, 1, 131072),
