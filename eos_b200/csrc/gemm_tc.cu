@@ -29,9 +29,9 @@
 // each CTA's epilogue drains its own 128 rows from its own tensor memory.  TMA completions of both
 // CTAs count on the leader's full barrier; the MMA commits release both CTAs' ring stages; both
 // epilogues arrive on the leader's accumulator-empty barrier.  Measured on the encoder's shapes it wins where the
-// main loop dominates (K = 3072: 6 % faster, the operand feed per CTA drops by a third) and loses at K = 768, so
-// it serves projections with K >= 2048; environment EOS_B200_GEMM_CTA_PAIR=1 forces it for every f16 projection,
-// =0 turns it off.
+// main loop dominates (K = 3072: 6 % faster, the operand feed per CTA drops by a third) and on wide outputs
+// (N = 2304: 5 %), and loses on the K = N = 768 projection, so it serves K >= 2048 and N >= 2048 with K >= 768;
+// environment EOS_B200_GEMM_CTA_PAIR=1 forces it for every f16 projection, =0 turns it off.
 // Every mbarrier wait is bounded (common.cuh: mbar_wait); on a timeout the kernel raises a CTA-wide
 // abort flag, all roles leave their loops, TMEM is freed and the status word is set.
 #include "gemm_tc.cuh"
@@ -595,7 +595,11 @@ extern "C" __attribute__((visibility("default"))) int eos_b200_debug_gemm_timing
 
 namespace {
 int g_pair_clusters = -1;  // CTA pairs that can be resident at once; 0 = pair mode unavailable
-int g_pair_min_k = 2048;   // pair mode serves projections at least this deep (EOS_B200_GEMM_CTA_PAIR=1: all, =0: none)
+bool g_pair_all = false;   // EOS_B200_GEMM_CTA_PAIR=1: every f16-weight projection runs on CTA pairs
+// Shapes the pair kernel serves by default: deep projections (the operand feed per CTA drops by a third) and wide ones
+// of at least the encoder's depth; measured per step at D = 768: FFN down 12.6 -> 11.8 ms, fused QKV 10.9 -> 10.4 ms,
+// FFN up unchanged, attention output (K = N = 768) 4.8 -> 4.9 ms and therefore left on one CTA per tile.
+bool pair_serves(int k, int n) { return g_pair_all || k >= 2048 || (n >= 2048 && k >= 768); }
 
 cudaLaunchConfig_t pair_launch_config(int grid, cudaStream_t stream, cudaLaunchAttribute* attr) {
     attr->id = cudaLaunchAttributeClusterDimension;
@@ -638,21 +642,30 @@ std::string gemm_global_init() {
         e = cudaFuncSetAttribute(gemm_tc_kernel<false, false, kEpiBiasGeluTanh>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg<false, false>::kSmemBytes);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_tc_kernel<false, true, -1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, true, kEpiBias>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<false, true>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, true, kEpiBiasGeluErf>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<false, true>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, true, kEpiBiasResidual>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<false, true>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_tc_kernel<false, true, kEpiBiasGeluTanh>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg<false, true>::kSmemBytes);
     if (e != cudaSuccess) return std::string("cudaFuncSetAttribute(gemm_tc_kernel): ") + cudaGetErrorString(e);
     if (g_pair_clusters < 0) {
         g_pair_clusters = 0;
         const char* on = getenv("EOS_B200_GEMM_CTA_PAIR");
         const bool off = on != nullptr && on[0] == '0';
-        if (on != nullptr && on[0] != '\0' && !off) g_pair_min_k = 0;
+        if (on != nullptr && on[0] != '\0' && !off) g_pair_all = true;
         if (!off) {
             int dev = 0, sms = 0, clusters = 0;
             cudaLaunchAttribute attr;
             if (cudaGetDevice(&dev) == cudaSuccess &&
                 cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms >= 2) {
                 cudaLaunchConfig_t cfg = pair_launch_config(sms & ~1, nullptr, &attr);
-                if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<false, true, -1>, &cfg) == cudaSuccess)
+                if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<false, true, kEpiBiasResidual>, &cfg) == cudaSuccess)
                     g_pair_clusters = clusters;
                 else
                     (void)cudaGetLastError();
@@ -669,7 +682,7 @@ std::string gemm_make_plan(GemmPlan* plan, const __half* a, int lda, const void*
     if (params.ldo % 8 != 0) return "gemm: output row stride must be a multiple of 8 elements";
     if (params.mode == kEpiBiasResidual && (params.residual == nullptr || params.ldr % 8 != 0))
         return "gemm: residual epilogue needs a residual pointer with a row stride that is a multiple of 8";
-    const bool pair = !b_int8 && g_pair_clusters > 0 && params.k >= g_pair_min_k;
+    const bool pair = !b_int8 && g_pair_clusters > 0 && pair_serves(params.k, params.n);
     std::string err = encode_2d(&plan->tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, (uint64_t)params.k,
                                 (uint64_t)params.m_alloc, (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!err.empty()) return "gemm A: " + err;
@@ -700,7 +713,20 @@ void gemm_launch(const GemmPlan& plan, cudaStream_t stream) {
     if (plan.pair) {
         cudaLaunchAttribute attr;
         cudaLaunchConfig_t cfg = pair_launch_config(plan.grid, stream, &attr);
-        cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, -1>, plan.tm_a, plan.tm_b, plan.p);
+        switch (plan.p.mode) {
+            case kEpiBiasGeluErf:
+                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBiasGeluErf>, plan.tm_a, plan.tm_b, plan.p);
+                break;
+            case kEpiBiasResidual:
+                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBiasResidual>, plan.tm_a, plan.tm_b, plan.p);
+                break;
+            case kEpiBiasGeluTanh:
+                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBiasGeluTanh>, plan.tm_a, plan.tm_b, plan.p);
+                break;
+            default:
+                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBias>, plan.tm_a, plan.tm_b, plan.p);
+                break;
+        }
     } else if (plan.b_int8) {
         constexpr int kT = Cfg<true, false>::kThreads;
         constexpr uint32_t kS = Cfg<true, false>::kSmemBytes;

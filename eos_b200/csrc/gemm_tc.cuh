@@ -51,8 +51,8 @@ std::string gemm_make_plan(GemmPlan* plan, const __half* a, int lda, const void*
 void gemm_launch(const GemmPlan& plan, cudaStream_t stream);
 
 // One-time per process: raises the dynamic shared memory limit of the kernels and asks the driver how
-// many CTA pairs fit on the device for the CTA-pair kernel, which serves f16-weight projections with K >= 2048
-// (environment EOS_B200_GEMM_CTA_PAIR=1: every f16-weight projection, =0: none).
+// many CTA pairs fit on the device for the CTA-pair kernel, which serves deep or wide f16-weight projections
+// (K >= 2048, or N >= 2048 with K >= 768; environment EOS_B200_GEMM_CTA_PAIR=1: every f16-weight projection, =0: none).
 std::string gemm_global_init();
 
 }  // namespace eosb

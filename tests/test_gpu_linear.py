@@ -136,7 +136,7 @@ rt.close()
 
 def test_linear_cta_pair_mode_is_bit_identical():
     """The CTA-pair kernel (two CTAs of a cluster per 256 x 256 tile, tcgen05.mma.cta_group::2; by default it serves
-    K >= 2048, EOS_B200_GEMM_CTA_PAIR=1 makes it serve every f16-weight projection) must give exactly the bits of the
+    deep or wide projections, EOS_B200_GEMM_CTA_PAIR=1 makes it serve every f16-weight projection) must give exactly the bits of the
     one-CTA kernel: same products, same fp32
     accumulation order along K, same epilogue.  Runs in a child process because the mode is read once per process."""
     import os
