@@ -28,6 +28,14 @@ class Stats(C.Structure):
                 ("reserved2", C.c_float)]
 
 
+class TokenPoolDesc(C.Structure):
+    _fields_ = [("vocab", C.c_int32), ("dim", C.c_int32), ("hidden", C.c_int32), ("encoder_repeats", C.c_int32),
+                ("attention_residual", C.c_int32), ("attention_layer_norm", C.c_int32), ("ffn_residual", C.c_int32),
+                ("ffn_layer_norm", C.c_int32), ("token_embedding", C.c_void_p), ("attention_query", C.c_void_p),
+                ("attention_key", C.c_void_p), ("attention_value", C.c_void_p), ("attention_output", C.c_void_p),
+                ("hidden_projection", C.c_void_p), ("projection", C.c_void_p)]
+
+
 class EncoderTimes(C.Structure):
     _fields_ = [("steps", C.c_int32), ("gemm_launches", C.c_int32), ("attention_launches", C.c_int32),
                 ("layernorm_launches", C.c_int32), ("other_launches", C.c_int32), ("gemm_ms", C.c_float),
@@ -144,6 +152,11 @@ SYMBOLS = {
     "eos_b200_norm_decode_log8": (None, [_P, C.c_int64, _P]),
     "eos_b200_embed_pooled_set_matmul_scale": (C.c_int, [_P, C.c_float, _ERR]),
     "eos_b200_ip_score_topk": (C.c_int, [_P, _P, _P, C.c_float, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
+    "eos_b200_token_pool_bind": (C.c_int, [_P, C.POINTER(TokenPoolDesc), C.POINTER(C.c_void_p), _ERR]),
+    "eos_b200_token_pool_destroy": (None, [_P]),
+    "eos_b200_token_pool_encode": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int,
+                                             C.c_int, C.c_int, _P, _P, _P, C.c_int, C.POINTER(C.c_int), C.POINTER(Stats),
+                                             _ERR]),
     "eos_b200_sparse_attention": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                             C.c_int, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_turbo_sparse_attention": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libeos_b200.so")
-SOURCES = ["gemm_tc.cu", "attention_tc.cu", "encoder_kernels.cu", "turboquant.cu", "turboquant_tc.cu", "turboquant_tc256.cu", "sparse_attention.cu", "capi.cu"]
+SOURCES = ["gemm_tc.cu", "attention_tc.cu", "encoder_kernels.cu", "turboquant.cu", "turboquant_tc.cu", "turboquant_tc256.cu", "sparse_attention.cu", "token_pool.cu", "capi.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

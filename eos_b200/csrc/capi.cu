@@ -19,6 +19,7 @@
 #include "encoder_kernels.cuh"
 #include "gemm_tc.cuh"
 #include "sparse_attention.cuh"
+#include "token_pool.cuh"
 #include "turboquant.cuh"
 
 using namespace eosb;
@@ -3109,6 +3110,279 @@ int eos_b200_turbo_sparse_attention(EosB200Quantizer* key_qz, EosB200Quantizer* 
         cudaGetLastError();
         return fail(err, std::string("turbo_sparse_attention: ") + cudaGetErrorString(e));
     }
+    return EOS_B200_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// token-pool encoder: fp32 single-head layers -> per-token rows -> span-pooled child vectors
+// ------------------------------------------------------------------------------------------------
+struct EosB200TokenPool {
+    EosB200Runtime* rt = nullptr;
+    EosB200TokenPoolDesc d{};
+    float *table = nullptr, *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *w1 = nullptr, *w2 = nullptr;
+};
+
+namespace {
+// sparseTokenPoolTokenSpans, runtime/sparse_token_pool_vector_export.go:1561-1595
+void token_spans(int token_count, int span_tokens, int overlap, int min_tokens, std::vector<int>* starts,
+                 std::vector<int>* ends) {
+    starts->clear();
+    ends->clear();
+    if (token_count <= 0 || span_tokens <= 0) return;
+    if (min_tokens <= 0) min_tokens = 1;
+    if (token_count <= span_tokens) {
+        if (token_count < min_tokens) return;
+        starts->push_back(0);
+        ends->push_back(token_count);
+        return;
+    }
+    const int step = span_tokens - overlap;
+    if (step <= 0) return;
+    for (int start = 0; start < token_count; start += step) {
+        int end = start + span_tokens;
+        if (end > token_count) end = token_count;
+        if (end - start < min_tokens) break;
+        starts->push_back(start);
+        ends->push_back(end);
+        if (end >= token_count) break;
+    }
+}
+}  // namespace
+
+extern "C" {
+
+void eos_b200_token_pool_destroy(EosB200TokenPool* tp) {
+    if (tp == nullptr) return;
+    cudaSetDevice(tp->rt->device);
+    dev_free(tp->table);
+    dev_free(tp->wq);
+    dev_free(tp->wk);
+    dev_free(tp->wv);
+    dev_free(tp->wo);
+    dev_free(tp->w1);
+    dev_free(tp->w2);
+    delete tp;
+}
+
+int eos_b200_token_pool_bind(EosB200Runtime* rt, const EosB200TokenPoolDesc* desc, EosB200TokenPool** out, char** err) {
+    if (rt == nullptr || desc == nullptr || out == nullptr) return fail(err, "token_pool_bind: null argument");
+    *out = nullptr;
+    const EosB200TokenPoolDesc& d = *desc;
+    if (d.vocab <= 0 || d.dim <= 0 || d.hidden <= 0 || d.encoder_repeats < 0)
+        return fail(err, "token_pool_bind: sizes must be positive");
+    if (d.token_embedding == nullptr || d.attention_query == nullptr || d.attention_key == nullptr ||
+        d.attention_value == nullptr || d.attention_output == nullptr || d.hidden_projection == nullptr ||
+        d.projection == nullptr)
+        return fail(err, "token_pool_bind: the full encoder needs all seven weight tensors");
+    CUDA_TRY(cudaSetDevice(rt->device));
+    auto* tp = new EosB200TokenPool();
+    tp->rt = rt;
+    tp->d = d;
+    const size_t dd = (size_t)d.dim * d.dim, dh = (size_t)d.dim * d.hidden;
+    std::string msg = upload_f32(d.token_embedding, (size_t)d.vocab * d.dim, &tp->table);
+    if (msg.empty()) msg = upload_f32(d.attention_query, dd, &tp->wq);
+    if (msg.empty()) msg = upload_f32(d.attention_key, dd, &tp->wk);
+    if (msg.empty()) msg = upload_f32(d.attention_value, dd, &tp->wv);
+    if (msg.empty()) msg = upload_f32(d.attention_output, dd, &tp->wo);
+    if (msg.empty()) msg = upload_f32(d.hidden_projection, dh, &tp->w1);
+    if (msg.empty()) msg = upload_f32(d.projection, dh, &tp->w2);
+    tp->d.token_embedding = tp->d.attention_query = tp->d.attention_key = tp->d.attention_value = nullptr;
+    tp->d.attention_output = tp->d.hidden_projection = tp->d.projection = nullptr;
+    if (!msg.empty()) {
+        eos_b200_token_pool_destroy(tp);
+        return fail(err, "token_pool_bind: " + msg);
+    }
+    *out = tp;
+    return EOS_B200_OK;
+}
+
+int eos_b200_token_pool_encode(EosB200TokenPool* tp, const int32_t* h_tokens, const int32_t* h_mask, int seq_len,
+                               int attention_mode, EosB200Quantizer* key_qz, EosB200Quantizer* value_qz, int top_k,
+                               int route_block_size, int route_top_blocks, int span_tokens, int span_overlap,
+                               int span_min_tokens, float* h_rows, float* h_pooled, float* h_children, int max_children,
+                               int* n_children, EosB200Stats* stats, char** err) {
+    if (tp == nullptr || h_tokens == nullptr) return fail(err, "token_pool_encode: null argument");
+    if (seq_len <= 0) return fail(err, "token_pool_encode: empty sequence");
+    if (attention_mode != EOS_B200_TOKEN_POOL_DENSE && attention_mode != EOS_B200_TOKEN_POOL_TURBO_SPARSE)
+        return fail(err, "token_pool_encode: unsupported attention mode");
+    if ((h_pooled != nullptr || h_children != nullptr) && h_mask == nullptr)
+        return fail(err, "token_pool_encode: pooling needs the attention mask");
+    if (h_children != nullptr && n_children == nullptr) return fail(err, "token_pool_encode: n_children is required");
+    EosB200Runtime* rt = tp->rt;
+    const int D = tp->d.dim, H = tp->d.hidden, T = seq_len;
+    int budget = 0, bs = 0, tb = 0;
+    if (attention_mode == EOS_B200_TOKEN_POOL_TURBO_SPARSE) {
+        if (key_qz == nullptr || value_qz == nullptr || key_qz->dim != D || value_qz->dim != D || key_qz->rt != rt ||
+            value_qz->rt != rt)
+            return fail(err, "token_pool_encode: the turbo-sparse mode needs key and value quantizers of the model width");
+        std::string m = sparse_check(1, T, T, D, D, top_k, route_block_size, route_top_blocks, &budget, &bs, &tb);
+        if (!m.empty()) return fail(err, m);
+    }
+    std::vector<int> starts, ends;
+    if (h_children != nullptr) {
+        token_spans(T, span_tokens, span_overlap, span_min_tokens, &starts, &ends);
+        if (starts.empty()) return fail(err, "token_pool_encode: token-span mode selected no spans");
+        if ((int)starts.size() > max_children) return fail(err, "token_pool_encode: more spans than max_children");
+    }
+    CUDA_TRY(cudaSetDevice(rt->device));
+    cudaStream_t s = rt->stream;
+    const size_t td = (size_t)T * D;
+    int32_t *d_tok = nullptr, *d_mask = nullptr;
+    float *cur = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *hid = nullptr, *ffn = nullptr, *tmp = nullptr;
+    float *scores = nullptr, *pooled = nullptr, *children = nullptr;
+    uint8_t *kc = nullptr, *vc = nullptr, *ku = nullptr, *vu = nullptr, *kn = nullptr, *vn = nullptr;
+    float *knf = nullptr, *vnf = nullptr;
+    int *d_spans = nullptr, *d_flags = nullptr;
+    const bool turbo = attention_mode == EOS_B200_TOKEN_POOL_TURBO_SPARSE;
+    const int n_spans = (int)starts.size();
+    cudaError_t e = dev_alloc(&d_tok, (size_t)T);
+    if (e == cudaSuccess) e = dev_alloc(&d_mask, (size_t)T);
+    for (float** p : {&cur, &q, &k, &v, &att, &hid, &tmp})
+        if (e == cudaSuccess) e = dev_alloc(p, td);
+    if (e == cudaSuccess) e = dev_alloc(&ffn, (size_t)T * H);
+    if (e == cudaSuccess && !turbo) e = dev_alloc(&scores, (size_t)T * T);
+    if (e == cudaSuccess) e = dev_alloc(&pooled, (size_t)D);
+    if (e == cudaSuccess) e = dev_alloc(&children, (size_t)(n_spans > 0 ? n_spans : 1) * D);
+    if (e == cudaSuccess) e = dev_alloc(&d_spans, (size_t)2 * (n_spans + 1));
+    if (e == cudaSuccess) e = dev_alloc(&d_flags, (size_t)(n_spans + 1));
+    size_t kcb = 0, vcb = 0;
+    if (turbo) {
+        kcb = ((size_t)D * key_qz->bits + 7) / 8;
+        vcb = ((size_t)D * value_qz->bits + 7) / 8;
+        if (e == cudaSuccess) e = dev_alloc(&kc, (size_t)T * kcb);
+        if (e == cudaSuccess) e = dev_alloc(&vc, (size_t)T * vcb);
+        if (e == cudaSuccess) e = dev_alloc(&ku, td);
+        if (e == cudaSuccess) e = dev_alloc(&vu, td);
+        if (e == cudaSuccess) e = dev_alloc(&kn, (size_t)T);
+        if (e == cudaSuccess) e = dev_alloc(&vn, (size_t)T);
+        if (e == cudaSuccess) e = dev_alloc(&knf, (size_t)T);
+        if (e == cudaSuccess) e = dev_alloc(&vnf, (size_t)T);
+    }
+    int launches = 0;
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev0, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_tok, h_tokens, (size_t)T * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess && h_mask != nullptr) e = cudaMemcpyAsync(d_mask, h_mask, (size_t)T * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) {
+        launch_tp_gather(tp->table, tp->d.vocab, D, d_tok, T, cur, s);
+        ++launches;
+    }
+    std::vector<float> h_norms((size_t)T);
+    std::vector<uint8_t> h_codes((size_t)T);
+    for (int layer = 0; layer < tp->d.encoder_repeats && e == cudaSuccess; ++layer) {
+        launch_tp_matmul(cur, T, D, tp->wq, D, 0, q, s);
+        launch_tp_matmul(cur, T, D, tp->wk, D, 0, k, s);
+        launch_tp_matmul(cur, T, D, tp->wv, D, 0, v, s);
+        launches += 3;
+        if (!turbo) {
+            launch_tp_dense_attention(q, k, v, T, D, scores, att, rt->sm_count, s);
+            ++launches;
+        } else {
+            // TurboQuantEncodeReference on the key and value rows (codes + 8-bit log norm), then the compressed
+            // sparse attention; the norm codes are formed on the host so that they are the host library's logf
+            launch_tq_pack(k, T, key_qz->spec(), kc, knf, s);
+            launch_tq_pack(v, T, value_qz->spec(), vc, vnf, s);
+            launches += 4;
+            for (int side = 0; side < 2 && e == cudaSuccess; ++side) {
+                e = cudaMemcpyAsync(h_norms.data(), side == 0 ? knf : vnf, (size_t)T * 4, cudaMemcpyDeviceToHost, s);
+                if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+                if (e != cudaSuccess) break;
+                eos_b200_norm_encode_log8(h_norms.data(), T, h_codes.data());
+                e = cudaMemcpyAsync(side == 0 ? kn : vn, h_codes.data(), (size_t)T, cudaMemcpyHostToDevice, s);
+                if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+            }
+            if (e != cudaSuccess) break;
+            launch_tp_unpack_codes(kc, T, D, key_qz->bits, ku, s);
+            launch_tp_unpack_codes(vc, T, D, value_qz->bits, vu, s);
+            launch_tq_decode_rows(ku, kn, T, key_qz->spec(), k, rt->sm_count, s);
+            launch_tq_decode_rows(vu, vn, T, value_qz->spec(), v, rt->sm_count, s);
+            launch_sparse_attention(q, k, v, 1, T, T, D, D, budget, bs, tb, att, rt->sm_count, s);
+            launches += 5;
+        }
+        launch_tp_matmul(att, T, D, tp->wo, D, 0, hid, s);
+        ++launches;
+        if (tp->d.attention_residual) {
+            launch_tp_add(hid, cur, (long long)td, hid, s);
+            ++launches;
+        }
+        if (tp->d.attention_layer_norm) {
+            launch_tp_layernorm(hid, T, D, tmp, s);
+            std::swap(hid, tmp);
+            ++launches;
+        }
+        launch_tp_matmul(hid, T, D, tp->w1, H, 1, ffn, s);
+        launch_tp_matmul(ffn, T, H, tp->w2, D, 0, tmp, s);
+        launches += 2;
+        if (tp->d.ffn_residual) {
+            launch_tp_add(tmp, hid, (long long)td, tmp, s);
+            ++launches;
+        }
+        if (tp->d.ffn_layer_norm) {
+            launch_tp_layernorm(tmp, T, D, cur, s);
+            ++launches;
+        } else {
+            std::swap(cur, tmp);
+        }
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) {
+        launch_tp_normalize(cur, T, D, s);
+        ++launches;
+        e = cudaGetLastError();
+    }
+    std::vector<int> h_flags((size_t)n_spans + 1, 0);
+    if (e == cudaSuccess && h_rows != nullptr) e = cudaMemcpyAsync(h_rows, cur, td * 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess && h_pooled != nullptr) {
+        const int span01[2] = {0, T};
+        e = cudaMemcpyAsync(d_spans, span01, sizeof(span01), cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) {
+            launch_tp_span_pool(cur, d_mask, d_spans, d_spans + 1, 1, D, 1, pooled, nullptr, s);
+            ++launches;
+            e = cudaMemcpyAsync(h_pooled, pooled, (size_t)D * 4, cudaMemcpyDeviceToHost, s);
+        }
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);   // span01 and d_spans are reused below
+    }
+    if (e == cudaSuccess && h_children != nullptr) {
+        std::vector<int> se((size_t)2 * n_spans);
+        for (int i = 0; i < n_spans; ++i) {
+            se[i] = starts[i];
+            se[n_spans + i] = ends[i];
+        }
+        e = cudaMemcpyAsync(d_spans, se.data(), se.size() * 4, cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) {
+            launch_tp_span_pool(cur, d_mask, d_spans, d_spans + n_spans, n_spans, D, 0, children, d_flags, s);
+            ++launches;
+            e = cudaMemcpyAsync(h_children, children, (size_t)n_spans * D * 4, cudaMemcpyDeviceToHost, s);
+        }
+        if (e == cudaSuccess) e = cudaMemcpyAsync(h_flags.data(), d_flags, (size_t)n_spans * 4, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    }
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev1, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess && stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = launches;
+        stats->uploaded_bytes = (int64_t)T * 8;
+        stats->downloaded_bytes = (int64_t)((h_rows != nullptr ? td : 0) + (h_pooled != nullptr ? D : 0) + (size_t)n_spans * D) * 4;
+        stats->valid_tokens = T;
+        cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
+    }
+    dev_free(d_tok);
+    dev_free(d_mask);
+    for (float** p : {&cur, &q, &k, &v, &att, &hid, &tmp, &ffn, &scores, &pooled, &children, &knf, &vnf}) dev_free(*p);
+    for (uint8_t** p : {&kc, &vc, &ku, &vu, &kn, &vn}) dev_free(*p);
+    dev_free(d_spans);
+    dev_free(d_flags);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(err, std::string("token_pool_encode: ") + cudaGetErrorString(e));
+    }
+    if (n_children != nullptr) *n_children = n_spans;
+    for (int i = 0; i < n_spans; ++i)
+        if (h_flags[i] != 0)
+            return fail(err, "token_pool_encode: span [" + std::to_string(starts[i]) + "," + std::to_string(ends[i]) +
+                                 ") has no active tokens");
     return EOS_B200_OK;
 }
 

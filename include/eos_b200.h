@@ -42,6 +42,7 @@ typedef struct EosB200EmbedPooled EosB200EmbedPooled;
 typedef struct EosB200Quantizer EosB200Quantizer;
 typedef struct EosB200Corpus EosB200Corpus;
 typedef struct EosB200IpCorpus EosB200IpCorpus;
+typedef struct EosB200TokenPool EosB200TokenPool;
 
 /* Accounting of one call; mirrors the fields of backend.ExecutionAccounting that the reference
  * fills per run (runtime/backend/backend.go:1364-1400): launches, bytes moved, device time. */
@@ -493,6 +494,44 @@ EOS_B200_API int eos_b200_turbo_sparse_attention(EosB200Quantizer* key_qz, EosB2
                                                  const uint8_t* h_value_codes, const uint8_t* h_value_norm_codes,
                                                  int batches, int q_len, int k_len, int top_k, int route_block_size,
                                                  int route_top_blocks, float* h_out, EosB200Stats* stats, char** err);
+
+/* ---- token-pool encoder and token-span child vectors --------------------------------------------
+ * Replaces sparseTokenPoolEncoder.embedTextFullEncoderRows / embedTextFullEncoder and the span pooling of
+ * writeSparseTokenPoolTokenSpanChildVectorCache (runtime/sparse_token_pool_vector_export.go:1290-1335, 802-890):
+ * gather -> encoder_repeats x [single-head Q/K/V projections over the whole width, attention, output projection,
+ * optional residual + non-affine LayerNorm, tanh-GELU FFN, optional residual + LayerNorm] with ONE set of weights
+ * shared by all repeats -> per-token L2-normalised rows.  All tensors fp32, projections in [in, out] layout
+ * (matmulRowsRight, :1620-1633); arithmetic is float in the reference's summation orders.
+ * attention_mode: DENSE = denseSoftmaxAttentionRows (:1430-1465, no 1/sqrt(d)); TURBO_SPARSE = the key and value rows
+ * are TurboQuant-encoded (key_qz / value_qz carry the rotation specs, codes + 8-bit log norms as
+ * TurboQuantEncodeReference, runtime/backend/image_ops.go:212-249) and attended to with
+ * eos_b200_turbo_sparse_attention's kernels (top_k, route_block_size, route_top_blocks as there).
+ * Outputs, each optional (null = skip): h_rows [seq_len, dim]; h_pooled [dim] = maskedMeanPoolNormalized (:1534-1559);
+ * h_children [n, dim] = one unit vector per token span (sparseTokenPoolTokenSpans :1561-1595 with span_tokens,
+ * span_overlap, span_min_tokens; poolSparseTokenRowsRange :1597-1618), n returned in *n_children (<= max_children).
+ * A span without an active token is an error, as in the reference. */
+typedef struct {
+    int32_t vocab, dim, hidden, encoder_repeats;
+    int32_t attention_residual, attention_layer_norm, ffn_residual, ffn_layer_norm;   /* manifest flags */
+    const float* token_embedding;    /* [vocab, dim] */
+    const float* attention_query;    /* [dim, dim] */
+    const float* attention_key;
+    const float* attention_value;
+    const float* attention_output;
+    const float* hidden_projection;  /* [dim, hidden] */
+    const float* projection;         /* [hidden, dim] */
+} EosB200TokenPoolDesc;
+#define EOS_B200_TOKEN_POOL_DENSE 0
+#define EOS_B200_TOKEN_POOL_TURBO_SPARSE 1
+EOS_B200_API int eos_b200_token_pool_bind(EosB200Runtime* rt, const EosB200TokenPoolDesc* desc, EosB200TokenPool** out,
+                                          char** err);
+EOS_B200_API void eos_b200_token_pool_destroy(EosB200TokenPool* tp);
+EOS_B200_API int eos_b200_token_pool_encode(EosB200TokenPool* tp, const int32_t* h_tokens, const int32_t* h_mask, int seq_len,
+                                            int attention_mode, EosB200Quantizer* key_qz, EosB200Quantizer* value_qz,
+                                            int top_k, int route_block_size, int route_top_blocks, int span_tokens,
+                                            int span_overlap, int span_min_tokens, float* h_rows, float* h_pooled,
+                                            float* h_children, int max_children, int* n_children, EosB200Stats* stats,
+                                            char** err);
 
 /* Seeded synthetic data on the device (bench / tests): n rows of dim N(0,1) values, optionally
  * L2-normalised, row r generated from (seed, row_offset + r) only. */

@@ -1185,3 +1185,220 @@ EOS_ORACLE_API void eos_oracle_gelu_tanh_rows(const float *in, int64_t n, float 
         out[i] = 0.5f * x * (1.0f + (float)tanh((double)inner));
     }
 }
+
+/* ------------------------------------------------------------------------------------ */
+/* Token-pool encoder and token-span child vectors                                       */
+/* ------------------------------------------------------------------------------------ */
+
+/* geluForward: runtime/embedding_trainer.go:13471-13475 (float arithmetic, tanh in double) */
+static float tp_gelu(float x) {
+    float cubic = x * x * x;
+    float inner = 0.7978845608f * (x + 0.044715f * cubic);
+    return 0.5f * x * (1.0f + (float)tanh((double)inner));
+}
+
+/* matmulRowsRight: runtime/sparse_token_pool_vector_export.go:1620-1633 (weight [in, out], float sum in i order) */
+static void tp_matmul(const float *rows, int row_count, int in_dim, const float *w, int out_dim, float *out) {
+    for (int r = 0; r < row_count; r++)
+        for (int o = 0; o < out_dim; o++) {
+            float sum = 0.0f;
+            for (int i = 0; i < in_dim; i++) sum += rows[(int64_t)r * in_dim + i] * w[(int64_t)i * out_dim + o];
+            out[(int64_t)r * out_dim + o] = sum;
+        }
+}
+
+/* layerNormRow: runtime/embedding_trainer.go:13005-13024 */
+static void tp_layernorm_rows(const float *rows, int row_count, int dim, float *out) {
+    for (int r = 0; r < row_count; r++) {
+        const float *src = rows + (int64_t)r * dim;
+        float *dst = out + (int64_t)r * dim;
+        float mean = 0.0f;
+        for (int i = 0; i < dim; i++) mean += src[i];
+        mean /= (float)dim;
+        float variance = 0.0f;
+        for (int i = 0; i < dim; i++) {
+            float centered = src[i] - mean;
+            variance += centered * centered;
+        }
+        variance /= (float)dim;
+        float inv_std = (float)(1.0 / sqrt((double)variance + 1e-5));
+        for (int i = 0; i < dim; i++) dst[i] = (src[i] - mean) * inv_std;
+    }
+}
+
+/* normalizeRetrievalVector: runtime/retrieval_eval.go:1040-1054 */
+static void tp_normalize(float *v, int dim) {
+    double sum = 0.0;
+    for (int i = 0; i < dim; i++) sum += (double)v[i] * (double)v[i];
+    if (sum == 0.0) return;
+    float scale = (float)(1.0 / sqrt(sum));
+    for (int i = 0; i < dim; i++) v[i] *= scale;
+}
+
+/* denseSoftmaxAttentionRows: runtime/sparse_token_pool_vector_export.go:1430-1465 */
+static void tp_dense_attention(const float *q, const float *k, const float *v, int seq_len, int dim, float *out) {
+    float *scores = (float *)malloc(sizeof(float) * (size_t)seq_len);
+    memset(out, 0, sizeof(float) * (size_t)seq_len * dim);
+    for (int row = 0; row < seq_len; row++) {
+        float max_score = -INFINITY;
+        for (int col = 0; col < seq_len; col++) {
+            float score = 0.0f;
+            for (int d = 0; d < dim; d++) score += q[(int64_t)row * dim + d] * k[(int64_t)col * dim + d];
+            scores[col] = score;
+            if (score > max_score) max_score = score;
+        }
+        float sum = 0.0f;
+        for (int col = 0; col < seq_len; col++) {
+            float prob = (float)exp((double)(scores[col] - max_score));
+            scores[col] = prob;
+            sum += prob;
+        }
+        if (sum == 0.0f) continue;
+        for (int col = 0; col < seq_len; col++) {
+            float prob = scores[col] / sum;
+            for (int d = 0; d < dim; d++) out[(int64_t)row * dim + d] += prob * v[(int64_t)col * dim + d];
+        }
+    }
+    free(scores);
+}
+
+/* sparseTokenPoolEncoder.embedTextFullEncoderRows: runtime/sparse_token_pool_vector_export.go:1301-1335.
+ * weights: token_embedding [vocab, dim], attention q / k / v / output [dim, dim], hidden_projection [dim, hidden],
+ * projection [hidden, dim]; flags = {attention_residual, attention_layer_norm, ffn_residual, ffn_layer_norm}.
+ * mode 0: dense attention; mode 1: key / value rows TurboQuant-encoded (codes + 8-bit log norm, :1369-1401 with
+ * runtime/backend/image_ops.go:212-249), decoded, sparse attention with top_k / route knobs.  kspec / vspec =
+ * {perm, signs1, signs2, centroids, boundaries} of the key / value quantisers (the module that derives them from a
+ * seed is not in the reference tree; the caller supplies them). */
+EOS_ORACLE_API void eos_oracle_token_pool_rows(const float *token_embedding, int vocab, int dim, int hidden,
+                                               const float *wq, const float *wk, const float *wv, const float *wo,
+                                               const float *w1, const float *w2, int repeats, const int32_t *flags,
+                                               const int32_t *tokens, int seq_len, int mode, int key_bits,
+                                               const int32_t *kperm, const float *ks1, const float *ks2,
+                                               const float *kcent, const float *kbound, int value_bits,
+                                               const int32_t *vperm, const float *vs1, const float *vs2,
+                                               const float *vcent, const float *vbound, int top_k,
+                                               int route_block_size, int route_top_blocks, float *rows_out) {
+    size_t td = (size_t)seq_len * dim;
+    float *cur = (float *)calloc(td, sizeof(float));
+    float *q = (float *)malloc(sizeof(float) * td), *k = (float *)malloc(sizeof(float) * td);
+    float *v = (float *)malloc(sizeof(float) * td), *att = (float *)malloc(sizeof(float) * td);
+    float *hid = (float *)malloc(sizeof(float) * td), *tmp = (float *)malloc(sizeof(float) * td);
+    float *ffn = (float *)malloc(sizeof(float) * (size_t)seq_len * hidden);
+    for (int i = 0; i < seq_len; i++) {   /* gatherTokenRows :1337-1349: rows of unknown ids stay zero */
+        int tok = tokens[i];
+        if (tok >= 0 && tok < vocab) memcpy(cur + (size_t)i * dim, token_embedding + (size_t)tok * dim, sizeof(float) * dim);
+    }
+    for (int layer = 0; layer < repeats; layer++) {
+        tp_matmul(cur, seq_len, dim, wq, dim, q);
+        tp_matmul(cur, seq_len, dim, wk, dim, k);
+        tp_matmul(cur, seq_len, dim, wv, dim, v);
+        if (mode == 0) {
+            tp_dense_attention(q, k, v, seq_len, dim, att);
+        } else {
+            for (int side = 0; side < 2; side++) {
+                int bits = side == 0 ? key_bits : value_bits;
+                float *rowsf = side == 0 ? k : v;
+                int64_t cb = eos_oracle_tq_code_bytes(dim, bits);
+                uint8_t *codes = (uint8_t *)malloc((size_t)seq_len * cb);
+                float *norms = (float *)malloc(sizeof(float) * (size_t)seq_len);
+                uint8_t *ncodes = (uint8_t *)malloc((size_t)seq_len);
+                eos_oracle_tq_encode(rowsf, seq_len, dim, bits, side == 0 ? kperm : vperm, side == 0 ? ks1 : vs1,
+                                     side == 0 ? ks2 : vs2, side == 0 ? kbound : vbound, codes, norms);
+                eos_oracle_tq_norm_code(norms, seq_len, ncodes);
+                eos_oracle_tq_norm_value(ncodes, seq_len, norms);
+                eos_oracle_tq_decode(codes, norms, seq_len, dim, bits, side == 0 ? kperm : vperm, side == 0 ? ks1 : vs1,
+                                     side == 0 ? ks2 : vs2, side == 0 ? kcent : vcent, rowsf);
+                free(codes);
+                free(norms);
+                free(ncodes);
+            }
+            eos_oracle_sparse_attention(q, k, v, 1, seq_len, seq_len, dim, dim, top_k, route_block_size, route_top_blocks,
+                                        att);
+        }
+        tp_matmul(att, seq_len, dim, wo, dim, hid);
+        if (flags[0])
+            for (size_t i = 0; i < td; i++) hid[i] = hid[i] + cur[i];
+        if (flags[1]) {
+            tp_layernorm_rows(hid, seq_len, dim, tmp);
+            float *t = hid;
+            hid = tmp;
+            tmp = t;
+        }
+        tp_matmul(hid, seq_len, dim, w1, hidden, ffn);
+        for (size_t i = 0; i < (size_t)seq_len * hidden; i++) ffn[i] = tp_gelu(ffn[i]);
+        tp_matmul(ffn, seq_len, hidden, w2, dim, tmp);
+        if (flags[2])
+            for (size_t i = 0; i < td; i++) tmp[i] = tmp[i] + hid[i];
+        if (flags[3]) {
+            tp_layernorm_rows(tmp, seq_len, dim, cur);
+        } else {
+            float *t = cur;
+            cur = tmp;
+            tmp = t;
+        }
+    }
+    for (int r = 0; r < seq_len; r++) tp_normalize(cur + (size_t)r * dim, dim);
+    memcpy(rows_out, cur, sizeof(float) * td);
+    free(cur);
+    free(q);
+    free(k);
+    free(v);
+    free(att);
+    free(hid);
+    free(tmp);
+    free(ffn);
+}
+
+/* poolSparseTokenRowsRange (:1597-1618) when fallback_all == 0, maskedMeanPoolNormalized (:1534-1559) otherwise.
+ * Returns the number of active rows (0 with fallback_all == 0: no vector is produced). */
+EOS_ORACLE_API int eos_oracle_token_span_pool(const float *rows, const int32_t *mask, int start, int end, int dim,
+                                              int fallback_all, float *out) {
+    int active = 0;
+    for (int d = 0; d < dim; d++) out[d] = 0.0f;
+    for (int r = start; r < end; r++) {
+        if (mask[r] == 0) continue;
+        active++;
+        for (int d = 0; d < dim; d++) out[d] += rows[(int64_t)r * dim + d];
+    }
+    if (active == 0) {
+        if (!fallback_all) return 0;
+        active = end - start;
+        for (int r = start; r < end; r++)
+            for (int d = 0; d < dim; d++) out[d] += rows[(int64_t)r * dim + d];
+    }
+    float scale = (float)(1.0 / (double)active);
+    for (int d = 0; d < dim; d++) out[d] *= scale;
+    tp_normalize(out, dim);
+    return active;
+}
+
+/* sparseTokenPoolTokenSpans: runtime/sparse_token_pool_vector_export.go:1561-1595.  Returns the span count;
+ * starts / ends hold at most cap entries. */
+EOS_ORACLE_API int eos_oracle_token_spans(int token_count, int span_tokens, int overlap, int min_tokens, int32_t *starts,
+                                          int32_t *ends, int cap) {
+    int n = 0;
+    if (token_count <= 0 || span_tokens <= 0) return 0;
+    if (min_tokens <= 0) min_tokens = 1;
+    if (token_count <= span_tokens) {
+        if (token_count < min_tokens) return 0;
+        if (cap > 0) {
+            starts[0] = 0;
+            ends[0] = token_count;
+        }
+        return 1;
+    }
+    int step = span_tokens - overlap;
+    if (step <= 0) return 0;
+    for (int start = 0; start < token_count; start += step) {
+        int end = start + span_tokens;
+        if (end > token_count) end = token_count;
+        if (end - start < min_tokens) break;
+        if (n < cap) {
+            starts[n] = start;
+            ends[n] = end;
+        }
+        n++;
+        if (end >= token_count) break;
+    }
+    return n;
+}

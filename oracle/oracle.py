@@ -469,3 +469,52 @@ def compact_encoder(tokens, mask, role_ids, token_embedding, role_embedding, lay
     if output_projection is not None:
         normalized = matmul(normalized, output_projection)
     return mean_pool_masked(normalized, mask)
+
+
+# ------------------------------------------------------------------------------ token-pool encoder
+def token_pool_rows(weights: dict, tokens, mode: int = 0, key_spec=None, value_spec=None, top_k: int = 0,
+                    route_block_size: int = 0, route_top_blocks: int = 0):
+    """embedTextFullEncoderRows (runtime/sparse_token_pool_vector_export.go:1301-1335).  weights: token_embedding,
+    attention_query / key / value / output, hidden_projection, projection (fp32), encoder_repeats and the four
+    manifest flags; key_spec / value_spec: objects with bits, perm, signs1, signs2, centroids, boundaries."""
+    te = _f32(weights["token_embedding"])
+    w = [_f32(weights[n]) for n in ("attention_query", "attention_key", "attention_value", "attention_output",
+                                    "hidden_projection", "projection")]
+    tok = _i32(tokens).reshape(-1)
+    dim, hidden = te.shape[1], w[4].shape[1]
+    flags = _i32([int(bool(weights.get(n, False))) for n in ("attention_residual", "attention_layer_norm",
+                                                                "ffn_residual", "ffn_layer_norm")])
+    out = np.empty((tok.size, dim), dtype=np.float32)
+
+    def spec_args(sp):
+        if sp is None:
+            return [C.c_int(0), None, None, None, None, None], []
+        keep = [_i32(sp.perm), _f32(sp.signs1), _f32(sp.signs2), _f32(sp.centroids), _f32(sp.boundaries)]
+        return [C.c_int(sp.bits)] + [_p(a) for a in keep], keep
+
+    ka, kkeep = spec_args(key_spec)
+    va, vkeep = spec_args(value_spec)
+    lib().eos_oracle_token_pool_rows(_p(te), C.c_int(te.shape[0]), C.c_int(dim), C.c_int(hidden), *[_p(a) for a in w],
+                                     C.c_int(int(weights["encoder_repeats"])), _p(flags), _p(tok), C.c_int(tok.size),
+                                     C.c_int(mode), *ka, *va, C.c_int(top_k), C.c_int(route_block_size),
+                                     C.c_int(route_top_blocks), _p(out))
+    del kkeep, vkeep
+    return out
+
+
+def token_spans(token_count: int, span_tokens: int, overlap: int, min_tokens: int):
+    cap = max(1, token_count)
+    starts, ends = np.zeros(cap, np.int32), np.zeros(cap, np.int32)
+    n = lib().eos_oracle_token_spans(C.c_int(token_count), C.c_int(span_tokens), C.c_int(overlap), C.c_int(min_tokens),
+                                     _p(starts), _p(ends), C.c_int(cap))
+    return [(int(starts[i]), int(ends[i])) for i in range(n)]
+
+
+def token_span_pool(rows, mask, start: int, end: int, fallback_all: bool = False):
+    """(vector, active rows): poolSparseTokenRowsRange / maskedMeanPoolNormalized."""
+    r = _f32(rows)
+    m = _i32(mask).reshape(-1)
+    out = np.empty(r.shape[1], dtype=np.float32)
+    active = lib().eos_oracle_token_span_pool(_p(r), _p(m), C.c_int(start), C.c_int(end), C.c_int(r.shape[1]),
+                                              C.c_int(1 if fallback_all else 0), _p(out))
+    return out, int(active)

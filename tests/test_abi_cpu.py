@@ -131,3 +131,12 @@ def test_log8_norm_sidecar_matches_the_oracle():
     allc = np.arange(256, dtype=np.uint8)
     assert np.array_equal(norm_decode_log8(allc).view(np.uint32), O.tq_norm_value(allc).view(np.uint32))
     assert codes[-8] == 0 and codes[-7] == 0 and codes[-6] == 255 and codes[-5] == 0
+
+
+def test_token_spans_follow_the_oracle():
+    """sparseTokenPoolTokenSpans (runtime/sparse_token_pool_vector_export.go:1561-1595): host mirror vs the oracle."""
+    from eos_b200.token_pool import token_spans
+    from oracle import oracle as O
+    for args in [(10, 4, 1, 2), (3, 4, 1, 2), (3, 4, 1, 5), (10, 4, 4, 1), (0, 4, 0, 1), (100, 16, 4, 3), (17, 16, 0, 2),
+                 (33, 16, 0, 0), (64, 64, 8, 1)]:
+        assert token_spans(*args) == O.token_spans(*args), args

@@ -192,29 +192,32 @@ def test_c4_path_large_shard(rt):
     qz.close()
 
 
-def test_per_token_vectors_long_context(rt):
-    """The document side of the long-context multi-vector configuration at reduced depth: 2 layers, D = 512, 8 heads,
-    T = 1536 with a 512-token window, a 512 -> 128 per-token head; the GPU's per-token vectors against the oracle's,
-    and their 2-bit packing bit-exact against the oracle's packing of the GPU vectors."""
+@pytest.mark.parametrize("T,layers,lengths", [(1536, 2, (1536, 700, 130)), (8192, 6, (8192, 3000, 257))])
+def test_per_token_vectors_long_context(rt, T, layers, lengths):
+    """The document side of the long-context multi-vector configuration: D = 512, 8 heads, FFN 2048, a 512-token
+    window, a 512 -> 128 per-token head; at reduced depth and length, and at the configuration's own 6 layers and
+    T = 8192 (64 key tiles per sequence, 5 of them per query tile under the window).  The GPU's per-token vectors
+    against the oracle's, and their 2-bit packing bit-exact against the oracle's packing of the GPU vectors."""
     import torch
     import eos_b200
     from eos_b200 import synth
     from oracle import oracle as O
-    T, D, heads, window, tdim = 1536, 512, 8, 512, 128
-    args = synth.make_q8_encoder(2, D, heads, 2048, vocab=2000, max_pos=T, seed=55)
+    D, heads, window, tdim = 512, 8, 512, 128
+    args = synth.make_q8_encoder(layers, D, heads, 2048, vocab=2000, max_pos=T, seed=55)
     rng = np.random.default_rng(56)
     tw = synth.f16_round(rng.standard_normal((D, tdim), dtype=np.float32) * np.float32(0.05))
-    ids = rng.integers(0, 2000, size=(3, T), dtype=np.int32)
-    lengths = np.array([T, 700, 130])
+    lengths = np.array(lengths)
+    B = len(lengths)
+    ids = rng.integers(0, 2000, size=(B, T), dtype=np.int32)
     mask = (np.arange(T)[None, :] < lengths[:, None]).astype(np.int32)
     enc = eos_b200.BertEmbedder(rt, attention_window=window, **args)
     enc.set_token_head(tw)
     d_ids, d_mask = torch.from_numpy(ids).cuda(), torch.from_numpy(mask).cuda()
     rows = int(mask.sum())
-    d_vec = torch.zeros((3 * T, tdim), dtype=torch.float32, device="cuda")
+    d_vec = torch.zeros((B * T, tdim), dtype=torch.float32, device="cuda")
     d_rows = torch.zeros((1,), dtype=torch.int32, device="cuda")
     torch.cuda.synchronize()
-    enc.token_vectors_device(d_ids.data_ptr(), d_mask.data_ptr(), None, 3, T, d_vec.data_ptr(), d_rows.data_ptr())
+    enc.token_vectors_device(d_ids.data_ptr(), d_mask.data_ptr(), None, B, T, d_vec.data_ptr(), d_rows.data_ptr())
     enc.sync()
     assert int(d_rows.item()) == rows
     got = d_vec[:rows].cpu().numpy()
