@@ -8,21 +8,25 @@
 // first key_count rows of the sequence.  With a local window key j is visible to query i only if
 // 2 |pos_i - pos_j| < window (positions are the tokens' original positions).
 //
-// One CTA per SM holds two independent pipelines ("streams"), each with 256 columns of tensor memory, its own
+// One CTA per SM holds two independent pipelines ("streams"), each with 256 columns of tensor memory (S 128, O 64,
+// P 64), its own
 // shared-memory rings and its own warps, walking work items (sequence, 128-query tile, head); while one stream's
 // softmax threads work the other stream's MMAs run, so neither pipe waits for the other.  Per stream:
 //   4 warps      softmax, one thread per query row (thread = TMEM lane, so a row's maximum needs no exchange
 //                between threads; the whole row of a tile is held in registers, which the other warps make room
-//                for with setmaxnreg): per key tile read the row of S (fp32), update the row maximum, write
-//                P = exp2(s - m) as packed f16 back over the first columns of S; after the item's last key tile
-//                O / l -> f16 -> global (one 128-byte row segment per thread).  The running maximum only moves
-//                when a tile's maximum exceeds it by more than kRescaleThreshold (then O is rescaled in place);
-//                otherwise the stale maximum is kept, which cancels in O / l.
-//   1 warp       TMA producer: Q tile (ring of 2), then K_j, V_j tiles (128 rows x 64, 128B swizzle, ring of 4).
-//   1 warp       MMA issuer: S = Q K_j^T (M128 x N<=128 x K64), then O += P V_j with P read from tensor memory as
-//                the A operand and [V_j | ones] as the B operand (N = 80): column 64 of O is the row sum l of
-//                exactly the f16 probabilities that multiply V.  S(j+1) is issued right behind P V(j); the tensor
-//                pipe executes a thread's MMAs in issue order, so it cannot overwrite P(j) before it was read.
+//                for with setmaxnreg): per key tile read the row of S (fp32) and release S at once, update the row
+//                maximum, write P = exp2(s - m) as packed f16 into P's own columns and add the row sum of exactly
+//                those f16 values; after the item's last key tile O / l -> f16 -> global (one 128-byte row segment
+//                per thread).  The running maximum only moves when a tile's maximum exceeds it by more than
+//                kRescaleThreshold (then O and l are rescaled in place); otherwise the stale maximum is kept, which
+//                cancels in O / l.  Three exponentials of four run on the MUFU unit (ex2.approx.f16x2), the fourth
+//                on the FMA pipe.
+//   1 warp       TMA producer: Q tile (ring of 2), then K_j and V_j tiles (128 rows x 64, 128B swizzle) into a ring
+//                of 2 each.
+//   1 warp       MMA issuer: S = Q K_j^T (M128 x N<=128 x K64) and O += P V_j (N = 64) with P read from tensor memory
+//                as the A operand.  S(j+1) is issued as soon as the softmax threads hold S(j) in registers, ahead of
+//                P V(j), which has to wait for the probabilities: the softmax of tile j + 1 never waits for a
+//                tensor-pipe round trip.
 // The last key tile of a sequence only pays for its visible keys: N of the first MMA, the K extent of the second
 // and the softmax's column chunks are cut to the keys that exist (rounded to 16 / 32).
 // All mbarrier waits are bounded (abort flag + status word); there are no named barriers, so a role that gives
@@ -55,19 +59,21 @@ constexpr int kFirstOtherWarp = kStreams * kSoftmaxWarps;   // then per stream: 
 constexpr int kAtThreads = (kStreams * kSoftmaxWarps + 2 * kStreams) * 32;   // 384
 constexpr int kRegsSoftmax = 224, kRegsOther = 56;  // 8 x 224 + 4 x 56 = 12 x 168: the launch's allocation, redistributed
 constexpr int kQStages = 2;
-constexpr int kKvStages = 4;
+constexpr int kKStages = 2;    // the K and the V tiles ride separate rings: the first MMA of tile j + 1 is issued
+constexpr int kVStages = 2;    // before the second MMA of tile j, so the two are consumed out of step
 constexpr uint32_t kTileBytes = 128 * 64 * 2;   // 16 KB: Q, K_j or V_j
 constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffKv = kOffQ + kQStages * kTileBytes;
-constexpr uint32_t kOffOnes = kOffKv + kKvStages * kTileBytes;  // 16 x 64 f16 of 1.0: second MN block of the P V B operand
-constexpr uint32_t kOffBars = kOffOnes + 2048;
-constexpr uint32_t kNumBars = 2 * kQStages + 2 * kKvStages + 3;
+constexpr uint32_t kOffK = kOffQ + kQStages * kTileBytes;
+constexpr uint32_t kOffV = kOffK + kKStages * kTileBytes;
+constexpr uint32_t kOffBars = kOffV + kVStages * kTileBytes;
+constexpr uint32_t kNumBars = 2 * kQStages + 2 * kKStages + 2 * kVStages + 5;
 constexpr uint32_t kStreamBytes = (kOffBars + kNumBars * 8 + 1023u) & ~1023u;   // shared memory of one stream
 constexpr uint32_t kOffMisc = kStreams * kStreamBytes;
 constexpr uint32_t kAtSmemBytes = kOffMisc + 16 + 1024;
 constexpr uint32_t kTmemCols = 256;   // per stream
-constexpr uint32_t kColS = 0;         // S: 128 fp32 columns; P (packed f16 pairs) overwrites its first 64
-constexpr uint32_t kColO = 128;       // O: 64 fp32 columns, then 16 columns of row sums (column kColO + 64 is read)
+constexpr uint32_t kColS = 0;         // S: 128 fp32 columns
+constexpr uint32_t kColO = 128;       // O: 64 fp32 columns
+constexpr uint32_t kColP = 192;       // P: 128 probabilities as packed f16 pairs in 64 columns
 constexpr float kRescaleThreshold = 1.0f;  // in log2 units: probabilities stay below 2
 
 struct Item {
@@ -153,6 +159,31 @@ __device__ __forceinline__ uint32_t ex2_f16x2(float x0, float x1) {
     return px;
 }
 
+// The same on the FMA pipe (the MUFU unit serves one ex2.approx.f16x2 per 16 cycles and scheduler, which two softmax
+// warps per scheduler saturate): x = n + f with n the nearest integer (magic-number rounding), 2^f by a cubic on
+// [-0.5, 0.5] (relative error 7.7e-5, a third of an f16 half-ulp), n added to the exponent field.  x <= 1 here; values
+// below -125 (masked scores are -inf) give a number that rounds to 0 in f16.
+#ifndef EOSB_ATTN_POLY_EVERY
+#define EOSB_ATTN_POLY_EVERY 4   // every n-th pair of a row takes this path (0 = none); measured per step at 12 layers,
+                                 // 1024 x 64..512 tokens: none 15.5 ms, every 4th 14.75, every 3rd 14.8, every 2nd 15.9
+#endif
+__device__ __forceinline__ uint32_t ex2_poly_f16x2(float x0, float x1) {
+    const float magic = 12582912.0f;   // 1.5 * 2^23
+    x0 = fmaxf(x0, -125.0f);
+    x1 = fmaxf(x1, -125.0f);
+    const float t0 = x0 + magic, t1 = x1 + magic;
+    const float f0 = x0 - (t0 - magic), f1 = x1 - (t1 - magic);
+    float p0 = fmaf(0.05508868f, f0, 0.24260405f), p1 = fmaf(0.05508868f, f1, 0.24260405f);
+    p0 = fmaf(p0, f0, 0.69327624f);
+    p1 = fmaf(p1, f1, 0.69327624f);
+    p0 = fmaf(p0, f0, 0.99992894f);
+    p1 = fmaf(p1, f1, 0.99992894f);
+    const uint32_t r0 = __float_as_uint(p0) + (__float_as_uint(t0) << 23);
+    const uint32_t r1 = __float_as_uint(p1) + (__float_as_uint(t1) << 23);
+    __half2 h = __floats2half2_rn(__uint_as_float(r0), __uint_as_float(r1));
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
 __global__ void __launch_bounds__(kAtThreads, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict__ cu_qtiles,
                const int4* __restrict__ qtile_info, const int4* __restrict__ qtile_win,
@@ -171,17 +202,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
     const bool is_mma = warp >= kFirstOtherWarp && ((warp - kFirstOtherWarp) & 1) == 1;
     const int quarter = warp & 3;                     // softmax warps: the TMEM lane quarter they may access
     const uint32_t base = base_cta + stream * kStreamBytes;
-    uint8_t* sm = sm_cta + stream * kStreamBytes;
     const int vcta = blockIdx.x * kStreams + stream, vgrid = gridDim.x * kStreams;
 
     const uint32_t bar0 = base + kOffBars;
     auto q_full = [&](int s) { return bar0 + 8u * s; };
     auto q_empty = [&](int s) { return bar0 + 8u * (kQStages + s); };
-    auto kv_full = [&](int s) { return bar0 + 8u * (2 * kQStages + s); };
-    auto kv_empty = [&](int s) { return bar0 + 8u * (2 * kQStages + kKvStages + s); };
-    const uint32_t s_full = bar0 + 8u * (2 * kQStages + 2 * kKvStages);  // S of the next key tile is in tensor memory
-    const uint32_t p_full = s_full + 8u;                                 // its probabilities are (4 warps arrive)
-    const uint32_t o_full = s_full + 16u;                                // the item's O is complete
+    auto k_full = [&](int s) { return bar0 + 8u * (2 * kQStages + s); };
+    auto k_empty = [&](int s) { return bar0 + 8u * (2 * kQStages + kKStages + s); };
+    auto v_full = [&](int s) { return bar0 + 8u * (2 * kQStages + 2 * kKStages + s); };
+    auto v_empty = [&](int s) { return bar0 + 8u * (2 * kQStages + 2 * kKStages + kVStages + s); };
+    const uint32_t s_full = bar0 + 8u * (2 * kQStages + 2 * kKStages + 2 * kVStages);  // S of a key tile is in tensor memory
+    const uint32_t s_free = s_full + 8u;    // its rows are in the softmax threads' registers (4 warps arrive): S may be overwritten
+    const uint32_t p_full = s_full + 16u;   // its probabilities are in tensor memory (4 warps arrive)
+    const uint32_t pv_done = s_full + 24u;  // its P V product is complete: P may be overwritten, O touched
+    const uint32_t o_full = s_full + 32u;   // the item's O is complete
 
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm_cta + kOffMisc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sm_cta + kOffMisc + 4);
@@ -194,12 +228,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
             mbar_init(q_full(s), 1);
             mbar_init(q_empty(s), 1);
         }
-        for (int s = 0; s < kKvStages; ++s) {
-            mbar_init(kv_full(s), 1);
-            mbar_init(kv_empty(s), 1);
+        for (int s = 0; s < kKStages; ++s) {
+            mbar_init(k_full(s), 1);
+            mbar_init(k_empty(s), 1);
+        }
+        for (int s = 0; s < kVStages; ++s) {
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), 1);
         }
         mbar_init(s_full, 1);
+        mbar_init(s_free, kSoftmaxWarps);
         mbar_init(p_full, kSoftmaxWarps);
+        mbar_init(pv_done, 1);
         mbar_init(o_full, 1);
         mbar_fence_init();
         tma_prefetch_desc(&tm_qkv);
@@ -207,10 +247,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
     if (warp == kFirstOtherWarp + 1) {   // one warp allocates (and frees) the whole CTA's tensor memory
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kStreams * kTmemCols);
         tmem_relinquish();
-    }
-    if (is_producer) {
-        for (int i = lane; i < 2048 / 4; i += 32) reinterpret_cast<uint32_t*>(sm + kOffOnes)[i] = 0x3c003c00u;
-        fence_proxy_async_smem();
     }
     tc_fence_before();
     __syncthreads();
@@ -223,7 +259,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         if (lane == 0) {
             ItemWalker wk;
             wk.init(vcta, vgrid, total_items, heads, qtile_info, qtile_win);
-            uint32_t qn = 0, kvc = 0;
+            uint32_t qn = 0, kc = 0, vc = 0;
             bool ok = true;
             TDECL;
             for (; ok && wk.valid(); wk.next()) {
@@ -236,19 +272,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                 mbar_arrive_expect_tx(q_full(qs), kTileBytes);
                 tma_load_2d(base + kOffQ + qs * kTileBytes, &tm_qkv, it.head * 64, it.row0 + it.q0, q_full(qs));
                 ++qn;
-                // ring order = order of consumption: K(j), V(j), K(j+1), V(j+1), ...
                 for (int kt = it.kt_begin; ok && kt < it.kt_end; ++kt) {
-                    for (int part = 1; part <= 2; ++part, ++kvc) {
-                        const int s = kvc % kKvStages;
+                    {
+                        const int s = kc % kKStages;
                         TMARK(0);
-                        if (!mbar_wait(kv_empty(s), ((kvc / kKvStages) & 1u) ^ 1u, abort_flag)) {
+                        if (!mbar_wait(k_empty(s), ((kc / kKStages) & 1u) ^ 1u, abort_flag)) {
                             ok = false;
                             break;
                         }
                         TMARK(2);
-                        mbar_arrive_expect_tx(kv_full(s), kTileBytes);
-                        tma_load_2d(base + kOffKv + s * kTileBytes, &tm_qkv, part * hidden + it.head * 64,
-                                    it.row0 + kt * 128, kv_full(s));
+                        mbar_arrive_expect_tx(k_full(s), kTileBytes);
+                        tma_load_2d(base + kOffK + s * kTileBytes, &tm_qkv, hidden + it.head * 64, it.row0 + kt * 128,
+                                    k_full(s));
+                        ++kc;
+                    }
+                    {
+                        const int s = vc % kVStages;
+                        TMARK(0);
+                        if (!mbar_wait(v_empty(s), ((vc / kVStages) & 1u) ^ 1u, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        TMARK(2);
+                        mbar_arrive_expect_tx(v_full(s), kTileBytes);
+                        tma_load_2d(base + kOffV + s * kTileBytes, &tm_qkv, 2 * hidden + it.head * 64,
+                                    it.row0 + kt * 128, v_full(s));
+                        ++vc;
                     }
                 }
             }
@@ -259,76 +308,98 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         // ------------------------------------------------------------ MMA issuer
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
         if (lane == 0) {
-            // B = [V | ones]: 64 columns of V (MN-major, as TMA delivered it) and, as a second MN block, 16
-            // columns of 1.0, so that columns 64..79 of the accumulator are the row sums of P
-            constexpr uint32_t idesc_o = umma_idesc_f16(128, 80) | (1u << 16);
-            ItemWalker wk;
-            wk.init(vcta, vgrid, total_items, heads, qtile_info, qtile_win);
-            uint32_t qn = 0, kvc = 0, pn = 0;
+            // O += P V: P (f16) from tensor memory as the A operand, V (MN-major, as TMA delivered it) as B, N = 64
+            constexpr uint32_t idesc_o = umma_idesc_f16(128, 64) | (1u << 16);
+            // Two cursors over the same sequence of key tiles: the first MMA (S = Q K^T) of tile n + 1 is issued as
+            // soon as the softmax threads hold S(n) in registers, i.e. before the second MMA (O += P V) of tile n,
+            // which has to wait for the probabilities; the softmax of tile n + 1 then starts without waiting for a
+            // tensor-pipe round trip.
+            ItemWalker wq, wp;
+            wq.init(vcta, vgrid, total_items, heads, qtile_info, qtile_win);
+            wp.init(vcta, vgrid, total_items, heads, qtile_info, qtile_win);
+            while (wq.valid() && wq.it.kt_end <= wq.it.kt_begin) wq.next();
+            while (wp.valid() && wp.it.kt_end <= wp.it.kt_begin) wp.next();
+            int kt_q = wq.valid() ? wq.it.kt_begin : 0, kt_p = wp.valid() ? wp.it.kt_begin : 0;
+            uint32_t qn_q = 0, qn_p = 0, kc = 0, vc = 0, nqk = 0, npv = 0;
             bool ok = true;
             TDECL;
-            const uint32_t tmem_s = tmem_base + kColS, tmem_o = tmem_base + kColO;
-            auto issue_qk = [&](const Item& it, int kt, int qs) -> bool {
-                const int s = kvc % kKvStages;
+            const uint32_t tmem_s = tmem_base + kColS, tmem_o = tmem_base + kColO, tmem_p = tmem_base + kColP;
+            auto issue_qk = [&]() -> bool {
+                const Item& it = wq.it;
+                const int qs = qn_q % kQStages;
+                if (kt_q == it.kt_begin) {
+                    TMARK(0);
+                    if (!mbar_wait(q_full(qs), (qn_q / kQStages) & 1u, abort_flag)) return false;
+                    TMARK(3);
+                }
+                if (nqk > 0) {   // S still holds the previous tile until its rows are in registers
+                    TMARK(0);
+                    if (!mbar_wait(s_free, (nqk - 1) & 1u, abort_flag)) return false;
+                    TMARK(7);
+                }
+                const int s = kc % kKStages;
                 TMARK(0);
-                if (!mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag)) return false;
+                if (!mbar_wait(k_full(s), (kc / kKStages) & 1u, abort_flag)) return false;
                 TMARK(1);
-                ++kvc;
+                ++kc;
                 tc_fence_after();
-                const int n16 = (visible_in_tile(it, kt) + 15) & ~15;
+                const int n16 = (visible_in_tile(it, kt_q) + 15) & ~15;
                 const uint32_t idesc_s = umma_idesc_f16(128, n16);
                 const uint32_t q_lo = umma_desc_sw128_lo(base + kOffQ + qs * kTileBytes);
-                const uint32_t k_lo = umma_desc_sw128_lo(base + kOffKv + s * kTileBytes);
+                const uint32_t k_lo = umma_desc_sw128_lo(base + kOffK + s * kTileBytes);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)  // 32 bytes along K per step = 2 in descriptor units
                     umma_f16_split(tmem_s, q_lo + kk * 2, kDescSw128Hi, k_lo + kk * 2, kDescSw128Hi, idesc_s,
                                    kk > 0 ? 1u : 0u);
-                umma_commit(kv_empty(s));
+                umma_commit(k_empty(s));
                 umma_commit(s_full);
                 TMARK(2);
+                ++nqk;
+                if (++kt_q >= it.kt_end) {
+                    ++qn_q;
+                    do wq.next(); while (wq.valid() && wq.it.kt_end <= wq.it.kt_begin);
+                    if (wq.valid()) kt_q = wq.it.kt_begin;
+                }
                 return true;
             };
-            for (; ok && wk.valid(); wk.next()) {
-                const Item& it = wk.it;
-                if (it.kt_end <= it.kt_begin) continue;
-                const int qs = qn % kQStages;
+            if (wq.valid()) ok = issue_qk();
+            while (ok && wp.valid()) {
+                if (wq.valid()) {
+                    ok = issue_qk();
+                    if (!ok) break;
+                }
+                const Item& it = wp.it;
                 TMARK(0);
-                if (!mbar_wait(q_full(qs), (qn / kQStages) & 1u, abort_flag)) break;
-                TMARK(3);
-                ++qn;
-                ok = issue_qk(it, it.kt_begin, qs);
-                for (int kt = it.kt_begin; ok && kt < it.kt_end; ++kt) {
-                    TMARK(0);
-                    if (!mbar_wait(p_full, pn & 1u, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                    TMARK(4);
-                    ++pn;
-                    const int s = kvc % kKvStages;
-                    if (!mbar_wait(kv_full(s), (kvc / kKvStages) & 1u, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                    TMARK(5);
-                    ++kvc;
-                    tc_fence_after();
-                    const int ksteps = (visible_in_tile(it, kt) + 15) >> 4;
-                    const uint32_t v_addr = base + kOffKv + s * kTileBytes;
-                    // MN-major V: start address and the leading offset (distance to the block of ones) both
-                    // move by one 16-key slab (2048 bytes = 128 units) per step, in opposite directions
-                    const uint32_t v_lo = ((v_addr >> 4) & 0x3fffu) | (((base + kOffOnes - v_addr) >> 4) << 16);
-                    for (int kk = 0; kk < ksteps; ++kk)
-                        umma_f16_tmem_a(tmem_o, tmem_s + kk * 8, v_lo + kk * 128u - ((kk * 128u) << 16), kDescSw128Hi,
-                                        idesc_o, (kt > it.kt_begin || kk > 0) ? 1u : 0u);
-                    umma_commit(kv_empty(s));
-                    TMARK(6);
-                    if (kt + 1 < it.kt_end) {
-                        ok = issue_qk(it, kt + 1, qs);
-                    } else {
-                        umma_commit(q_empty(qs));
-                        umma_commit(o_full);
-                    }
+                if (!mbar_wait(p_full, npv & 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                TMARK(4);
+                const int s = vc % kVStages;
+                if (!mbar_wait(v_full(s), (vc / kVStages) & 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                TMARK(5);
+                ++vc;
+                tc_fence_after();
+                const int ksteps = (visible_in_tile(it, kt_p) + 15) >> 4;
+                const uint32_t v_addr = base + kOffV + s * kTileBytes;
+                // MN-major V: the start address moves by one 16-key slab (2048 bytes = 128 units) per step
+                const uint32_t v_lo = (v_addr >> 4) & 0x3fffu;
+                for (int kk = 0; kk < ksteps; ++kk)
+                    umma_f16_tmem_a(tmem_o, tmem_p + kk * 8, v_lo + kk * 128u, kDescSw128Hi, idesc_o,
+                                    (kt_p > it.kt_begin || kk > 0) ? 1u : 0u);
+                umma_commit(v_empty(s));
+                umma_commit(pv_done);
+                TMARK(6);
+                ++npv;
+                if (++kt_p >= it.kt_end) {
+                    umma_commit(q_empty(qn_p % kQStages));
+                    umma_commit(o_full);
+                    ++qn_p;
+                    do wp.next(); while (wp.valid() && wp.it.kt_end <= wp.it.kt_begin);
+                    if (wp.valid()) kt_p = wp.it.kt_begin;
                 }
             }
             TFLUSH(8, stream == 0);
@@ -341,6 +412,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const uint32_t t_s = tmem_base + lane_addr + kColS;
         const uint32_t t_o = tmem_base + lane_addr + kColO;
+        const uint32_t t_p = tmem_base + lane_addr + kColP;
         const float sl2 = 0.125f * 1.4426950408889634f;        // 1/sqrt(64) * log2(e)
         ItemWalker wk;
         wk.init(vcta, vgrid, total_items, heads, qtile_info, qtile_win);
@@ -366,25 +438,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
             // positions enter only as differences inside one sequence, so the flat index b * tokens + t serves
             const int qpos = (window > 0 && row_valid) ? __ldg(row_src + it.row0 + qrow) : 0;
             float m_used = -INFINITY;   // the maximum the probabilities of this row are currently scaled by
+            float l_run = 0.f;          // the row sum of the f16 probabilities written so far, in that scaling
             for (int kt = it.kt_begin; kt < it.kt_end; ++kt, ++sn) {
                 TMARK(0);
                 ok = __all_sync(0xffffffffu, mbar_wait(s_full, sn & 1u, abort_flag));
                 if (!ok) break;
                 TMARK(1);
                 tc_fence_after();
+                const int nvis = visible_in_tile(it, kt);
+                const int nch = (nvis + 31) >> 5;          // 32-column chunks that hold visible keys
+                const bool masked = nvis < nch * 32;
+                const bool edge = kt < it.full_begin || kt >= it.full_end;   // window mask needed
+                // the row's scores of this tile, all in registers (one wait for up to four loads)
+                uint32_t v[4][32];
                 if (live) {
-                    const int nvis = visible_in_tile(it, kt);
-                    const int nch = (nvis + 31) >> 5;          // 32-column chunks that hold visible keys
-                    const bool masked = nvis < nch * 32;
-                    const bool edge = kt < it.full_begin || kt >= it.full_end;   // window mask needed
-                    // the row's scores of this tile, all in registers (one wait for up to four loads)
-                    uint32_t v[4][32];
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
                         if (c < nch) tmem_ld_32x32(t_s + c * 32, v[c]);
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
                         if (c < nch) tmem_ld_wait32(v[c]);
+                }
+                // the row is in registers: the first MMA of the next tile may overwrite S
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_free);
+                if (live) {
                     if (masked) {
                         // the sequence's last, partial tile: scores of keys that do not exist become -inf
                         // (probability 0); only the last chunk can hold any
@@ -431,13 +510,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                         mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
                     }
                     const float mxs = mx * sl2;
+                    // P and O belong to the second MMA of the previous tile until it is complete
+                    if (sn > 0 && !mbar_wait(pv_done, (sn - 1) & 1u, abort_flag)) ok = false;
+                    tc_fence_after();
                     if (kt == it.kt_begin) {
                         m_used = mxs;
                     } else {
                         const bool need = mxs > m_used + kRescaleThreshold;
                         if (__any_sync(0xffffffffu, need)) {
-                            // O (and the row sum) of the rows whose maximum moved are rescaled in place; the P V
-                            // MMAs of the tiles before this one are complete (s_full was committed after them)
+                            // O and the row sum of the rows whose maximum moved are rescaled in place
                             float f = 1.0f;
                             if (need && m_used != -INFINITY) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(f) : "f"(m_used - mxs));
                             uint32_t o[16];
@@ -449,17 +530,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                                 for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
                                 tmem_st_32x16(t_o + h * 16, o);
                             }
-                            uint32_t l1[1];
-                            tmem_ld_32x1(t_o + 64, l1);
-                            tmem_ld_wait1(l1);
-                            tmem_st_32x1(t_o + 64, __float_as_uint(__uint_as_float(l1[0]) * f));
+                            l_run *= f;
                             if (need) m_used = mxs;
                         }
                     }
                     TMARK(3);
                     const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
-                    // probabilities: chunk c of P (16 columns of packed pairs) lands on columns of S that chunks
-                    // <= c held, all of which are in registers by now
+                    // probabilities as packed f16 pairs into the P columns; the row sum adds exactly the values that
+                    // multiply V (two pairs are added in f16 first: sums below 4, then in fp32)
+                    float l0 = 0.f, l1 = 0.f;
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
                         if (c < nch) {
@@ -468,13 +547,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
                             for (int e = 0; e < 32; e += 2) {
                                 float x0, x1;
                                 ffma2(x0, x1, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]), sl2, neg_m);
-                                p[e >> 1] = ex2_f16x2(x0, x1);
+                                if (EOSB_ATTN_POLY_EVERY > 0 && ((e >> 1) % (EOSB_ATTN_POLY_EVERY > 0 ? EOSB_ATTN_POLY_EVERY : 1)) ==
+                                                                    (EOSB_ATTN_POLY_EVERY > 0 ? EOSB_ATTN_POLY_EVERY : 1) - 1)
+                                    p[e >> 1] = ex2_poly_f16x2(x0, x1);
+                                else
+                                    p[e >> 1] = ex2_f16x2(x0, x1);
                             }
-                            tmem_st_32x16(t_s + c * 16, p);
+#pragma unroll
+                            for (int e = 0; e < 16; e += 2) {
+                                const __half2 hs = __hadd2(*reinterpret_cast<const __half2*>(&p[e]),
+                                                           *reinterpret_cast<const __half2*>(&p[e + 1]));
+                                const float2 fs = __half22float2(hs);
+                                l0 += fs.x;
+                                l1 += fs.y;
+                            }
+                            tmem_st_32x16(t_p + c * 16, p);
                         }
+                    l_run += l0 + l1;
                     TMARK(4);
                     tmem_st_wait();
+                } else if (sn > 0) {
+                    if (!mbar_wait(pv_done, (sn - 1) & 1u, abort_flag)) ok = false;
                 }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full);
@@ -488,15 +584,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int* __restrict
             ++on;
             tc_fence_after();
             if (live) {
-                uint32_t oa[32], ob[32], l1[1];
+                uint32_t oa[32], ob[32];
                 tmem_ld_32x32(t_o, oa);
                 tmem_ld_32x32(t_o + 32, ob);
-                tmem_ld_32x1(t_o + 64, l1);
                 tmem_ld_wait32(oa);
                 tmem_ld_wait32(ob);
-                tmem_ld_wait1(l1);
                 tc_fence_before();
-                const float l = __uint_as_float(l1[0]);
+                const float l = l_run;
                 const float inv = l > 0.f ? __frcp_rn(l) : 0.f;
                 if (row_valid) {
 #pragma unroll
