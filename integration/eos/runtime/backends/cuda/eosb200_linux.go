@@ -322,8 +322,49 @@ func (e *executor) dispatchStepB200(step eosartifact.Step, outputType eosartifac
 			return backend.StepDispatchResult{}, true, err
 		}
 		return backend.StepDispatchResult{Outputs: []*backend.Tensor{out}, VariantEntry: "eos_b200_linear"}, true, nil
+	case eosartifact.StepSparseAttention:
+		// cuda.go:565-577: query, key, value [T, D] or [B, T, D] fp32; top_k / route_* attributes
+		if len(inputs) != 3 {
+			return backend.StepDispatchResult{}, false, nil
+		}
+		out, err := e.b200.sparseAttention(inputs[0], inputs[1], inputs[2], attrInt(step, "top_k", 0),
+			attrInt(step, "route_block_size", 0), attrInt(step, "route_top_blocks", 0))
+		if err != nil {
+			return backend.StepDispatchResult{}, true, err
+		}
+		return backend.StepDispatchResult{Outputs: []*backend.Tensor{out}, VariantEntry: "eos_b200_sparse_attention"}, true, nil
 	}
 	return backend.StepDispatchResult{}, false, nil
+}
+
+// sparseAttention maps sparseAttentionTensor (runtime/backend/attention_ops.go:218-276).  Budgets above 128 keys or
+// route blocks are outside the library's limit (EOS_SPARSE_ATTENTION_MAX_TOPK): the error falls through to the host.
+func (rt *b200Runtime) sparseAttention(q, k, v *backend.Tensor, topK, routeBlock, routeTop int) (*backend.Tensor, error) {
+	rank := len(q.Shape)
+	if rank != len(k.Shape) || rank != len(v.Shape) || (rank != 2 && rank != 3) {
+		return nil, errors.New("sparse_attention expects rank-2 or rank-3 query/key/value tensors")
+	}
+	batches := 1
+	if rank == 3 {
+		batches = q.Shape[0]
+	}
+	qLen, dim := q.Shape[rank-2], q.Shape[rank-1]
+	kLen, vDim := k.Shape[rank-2], v.Shape[rank-1]
+	out := make([]float32, batches*qLen*vDim)
+	var st C.EosB200Stats
+	var cerr *C.char
+	var kp, vp *C.float
+	if kLen > 0 {
+		kp, vp = (*C.float)(unsafe.Pointer(&k.F32[0])), (*C.float)(unsafe.Pointer(&v.F32[0]))
+	}
+	rc := C.eos_b200_sparse_attention(rt.h, (*C.float)(unsafe.Pointer(&q.F32[0])), kp, vp, C.int(batches), C.int(qLen),
+		C.int(kLen), C.int(dim), C.int(vDim), C.int(topK), C.int(routeBlock), C.int(routeTop),
+		(*C.float)(unsafe.Pointer(&out[0])), &st, &cerr)
+	if err := b200Error(rc, cerr); err != nil {
+		return nil, err
+	}
+	shape := append(append([]int(nil), q.Shape[:rank-1]...), vDim)
+	return backend.NewTensorF16(shape, out), nil
 }
 
 // linear maps a single dense projection (MatMulAccelerator, backend.go:785-795): x [rows, k] times rhs [k, n]
@@ -366,6 +407,13 @@ func (rt *b200Runtime) bindEmbedPooled(table, projection *backend.Tensor) (*b200
 		return nil, err
 	}
 	return &b200EmbedPooled{h: h}, nil
+}
+
+// setMatMulScale forwards the matmul step's `scale` attribute, already resolved to a number by matmulScale
+// (runtime/backend/tensor_ops.go:1291-1315).
+func (p *b200EmbedPooled) setMatMulScale(scale float32) error {
+	var cerr *C.char
+	return b200Error(C.eos_b200_embed_pooled_set_matmul_scale(p.h, C.float(scale), &cerr), cerr)
 }
 
 func (p *b200EmbedPooled) run(tokens, mask *backend.Tensor, outDim int) (*backend.Tensor, error) {
