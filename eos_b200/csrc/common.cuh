@@ -90,6 +90,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tmap,
         : "memory");
 }
 
+// TMA store of a tile from shared memory (x = innermost coordinate, x * element size a multiple of 16 bytes; rows and
+// columns outside the tensor are clipped).  The writes to shared memory that produced the tile must be made visible
+// to the async proxy (fence_proxy_async_smem) before; the tile may be reused after tma_store_wait_read.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(tmap), "r"(smem_src), "r"(x), "r"(y)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // Asks L2 to fetch a tile ahead of the TMA load that will bring it into shared memory.
 // Asks the L2 for `bytes` (a multiple of 16) of global memory starting at a 16-byte aligned address; no data reaches
 // the SM and nothing has to be waited for.

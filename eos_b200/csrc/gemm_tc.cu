@@ -18,9 +18,9 @@
 //               sum_k a_k (s_n q_kn) = s_n sum_k a_k q_kn).
 //   last 8      epilogue warps, two per TMEM lane quarter, each owning 128 of the tile's 256 columns:
 //               tcgen05.ld (thread = row, software-pipelined 16 columns at a time), scale, bias, GELU or
-//               residual add, f16.  Output (and the residual) move between registers and global memory
-//               through a per-warp swizzled staging slab of 32 rows x 32 columns, so that every global
-//               access instruction covers 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
+//               residual add, f16.  A finished 32-row x 32-column slab leaves through a per-warp staging slab in the
+//               64-byte TMA swizzle as one TMA store; the residual comes in through the same slab with coalesced
+//               loads (8 rows x 64 contiguous bytes per instruction).
 // Two accumulators (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
 //
 // CTA-pair mode (f16 weights): two CTAs of a cluster share one 256x256 output tile.  Each loads its
@@ -96,7 +96,8 @@ struct Cfg {
 // registers and the activation code of the other modes disappear); kMode < 0 reads it from the parameters.
 template <bool kBInt8, bool kPair, int kMode>
 __global__ void __launch_bounds__(Cfg<kBInt8, kPair>::kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+               const __grid_constant__ CUtensorMap tm_out, GemmParams p) {
     using C = Cfg<kBInt8, kPair>;
     const int mode = kMode >= 0 ? kMode : p.mode;
     constexpr int kStagesAB = C::kStagesAB;
@@ -160,6 +161,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         mbar_fence_init();
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
+        tma_prefetch_desc(&tm_out);
     }
     if (warp == 2) {
         if (kPair) {
@@ -440,6 +442,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
                 const bool fast = (ncol0 + kSlabCols <= p.n);
                 uint4 res_own[4];
+                // the slab of the previous iteration may still be read by its TMA store
+                if (lane == 0) tma_store_wait_read();
+                __syncwarp();
                 if (fast && residual) {
                     // residual slab: coalesced registers -> staging -> this thread's own row
 #pragma unroll
@@ -542,15 +547,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 if (tm__) GMARK(6);
 #endif
                 if (fast) {
+                    // the slab (32 rows x 64 bytes, 16-byte chunk c of row r at c ^ ((r >> 1) & 3): the 64-byte TMA
+                    // swizzle) leaves as one TMA store; rows past the end of the allocation are clipped, rows between
+                    // the valid count and the allocation receive values nobody reads
+                    fence_proxy_async_smem();
                     __syncwarp();
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int rr = 8 * i + crow;
-                        const uint4 o = *reinterpret_cast<const uint4*>(slab + rr * 64 + ((cchunk ^ ((rr >> 1) & 3)) << 4));
-                        if (rr < rows_here)
-                            *reinterpret_cast<uint4*>(p.out + (size_t)(m0 + wrow0 + rr) * p.ldo + ncol0 + cchunk * 8) = o;
-                    }
-                    __syncwarp();
+                    if (lane == 0 && m0 + wrow0 < p.m_alloc) tma_store_2d(&tm_out, smem_u32(slab), ncol0, m0 + wrow0);
                 }
 #ifdef EOSB_GEMM_TIMING
                 if (tm__) GMARK(7);
@@ -565,6 +567,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 if (kPair) mbar_arrive_cluster(ab ? acc_empty_leader1 : acc_empty_leader0); else mbar_arrive(acc_empty(ab));
             }
         }
+        if (lane == 0) tma_store_wait_all();
+        __syncwarp();
 #ifdef EOSB_GEMM_TIMING
         GFLUSH(4);
 #endif
@@ -693,6 +697,9 @@ std::string gemm_make_plan(GemmPlan* plan, const __half* a, int lda, const void*
         err = encode_2d(&plan->tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w, (uint64_t)params.k, (uint64_t)params.n,
                         (uint64_t)ldw * 2, BK, pair ? BN / 2 : BN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!err.empty()) return "gemm W: " + err;
+    err = encode_2d(&plan->tm_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, params.out, (uint64_t)params.n, (uint64_t)params.m_alloc,
+                    (uint64_t)params.ldo * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (!err.empty()) return "gemm out: " + err;
     plan->p = params;
     plan->b_int8 = b_int8;
     plan->pair = pair;
@@ -715,16 +722,16 @@ void gemm_launch(const GemmPlan& plan, cudaStream_t stream) {
         cudaLaunchConfig_t cfg = pair_launch_config(plan.grid, stream, &attr);
         switch (plan.p.mode) {
             case kEpiBiasGeluErf:
-                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBiasGeluErf>, plan.tm_a, plan.tm_b, plan.p);
+                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBiasGeluErf>, plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
             case kEpiBiasResidual:
-                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBiasResidual>, plan.tm_a, plan.tm_b, plan.p);
+                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBiasResidual>, plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
             case kEpiBiasGeluTanh:
-                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBiasGeluTanh>, plan.tm_a, plan.tm_b, plan.p);
+                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBiasGeluTanh>, plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
             default:
-                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBias>, plan.tm_a, plan.tm_b, plan.p);
+                cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false, true, kEpiBias>, plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
         }
     } else if (plan.b_int8) {
@@ -732,16 +739,16 @@ void gemm_launch(const GemmPlan& plan, cudaStream_t stream) {
         constexpr uint32_t kS = Cfg<true, false>::kSmemBytes;
         switch (plan.p.mode) {
             case kEpiBiasGeluErf:
-                gemm_tc_kernel<true, false, kEpiBiasGeluErf><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                gemm_tc_kernel<true, false, kEpiBiasGeluErf><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
             case kEpiBiasResidual:
-                gemm_tc_kernel<true, false, kEpiBiasResidual><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                gemm_tc_kernel<true, false, kEpiBiasResidual><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
             case kEpiBiasGeluTanh:
-                gemm_tc_kernel<true, false, kEpiBiasGeluTanh><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                gemm_tc_kernel<true, false, kEpiBiasGeluTanh><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
             default:
-                gemm_tc_kernel<true, false, kEpiBias><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                gemm_tc_kernel<true, false, kEpiBias><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
         }
     } else {
@@ -749,16 +756,16 @@ void gemm_launch(const GemmPlan& plan, cudaStream_t stream) {
         constexpr uint32_t kS = Cfg<false, false>::kSmemBytes;
         switch (plan.p.mode) {
             case kEpiBiasGeluErf:
-                gemm_tc_kernel<false, false, kEpiBiasGeluErf><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                gemm_tc_kernel<false, false, kEpiBiasGeluErf><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
             case kEpiBiasResidual:
-                gemm_tc_kernel<false, false, kEpiBiasResidual><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                gemm_tc_kernel<false, false, kEpiBiasResidual><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
             case kEpiBiasGeluTanh:
-                gemm_tc_kernel<false, false, kEpiBiasGeluTanh><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                gemm_tc_kernel<false, false, kEpiBiasGeluTanh><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
             default:
-                gemm_tc_kernel<false, false, kEpiBias><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.p);
+                gemm_tc_kernel<false, false, kEpiBias><<<plan.grid, kT, kS, stream>>>(plan.tm_a, plan.tm_b, plan.tm_out, plan.p);
                 break;
         }
     }

@@ -35,6 +35,7 @@ struct GemmParams {
 struct GemmPlan {
     CUtensorMap tm_a;
     CUtensorMap tm_b;
+    CUtensorMap tm_out;   // output rows, boxes of 32 rows x 32 columns (the epilogue's staging slabs, 64-byte swizzle)
     GemmParams p;
     int grid;
     bool b_int8;
