@@ -33,8 +33,8 @@ ENC_BATCH, ENC_TOKENS, ENC_MIN_LEN = 1024, 512, 64
 TQ = dict(dim=768, bits=4, corpus=10_000_000, queries=4096, k=100)
 # DRAM traffic measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum of one launch) on the small
 # cases of eos_b200/profile_cases.py, per row of the launch; the summaries are under profiles/.
-NCU_GEMM_DRAM_BYTES_PER_ROW = {"qkv": 152.35e6 / 32768, "attn_out": 124.88e6 / 32768, "ffn_up": 207.08e6 / 32768,
-                               "ffn_down": 291.77e6 / 32768}
+NCU_GEMM_DRAM_BYTES_PER_ROW = {"qkv": 157.73e6 / 32768, "attn_out": 122.71e6 / 32768, "ffn_up": 203.39e6 / 32768,
+                               "ffn_down": 297.53e6 / 32768}
 NCU_SCAN_DRAM_BYTES_PER_ROW = 780.13e6 / 2_000_000
 NCU_TC_DRAM_BYTES_PER_ROW = {128: 493.16e6 / 1_250_000, 256: 494.45e6 / 1_250_000}  # profiles/tq_score_tc*_kernel_*.md
 
