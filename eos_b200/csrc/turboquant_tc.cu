@@ -112,6 +112,8 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
 
     const int chunks = (a.dim + kTqChunkCoords - 1) / kTqChunkCoords;
     const int num_kb = chunks * 2;
+    // up to 256 coordinates the launch's queries fit the query ring and are loaded once instead of once per tile
+    const bool q_resident = !kQInTmem && num_kb <= kStQ;
     const long long n_tiles = (a.n_docs + TD - 1) / TD;
     const long long n_tiles16 = (a.n_docs + kTqDocsPerTile - 1) / kTqDocsPerTile;
 
@@ -172,6 +174,16 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
         if (!kQInTmem && lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            if (q_resident) {
+                // the whole query block fits the ring: it is loaded once and stays (stage = k-block)
+                if ((long long)blockIdx.x < n_tiles) {
+                    for (int kb = 0; kb < num_kb; ++kb) {
+                        mbar_arrive_expect_tx(full_q(kb), kBytesQ);
+                        tma_load_2d(base + kOffQ + kb * kBytesQ, &tm_q, kb * TK, a.q_row0, full_q(kb));
+                    }
+                }
+                ok = false;
+            }
             for (long long tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % kStQ;
@@ -199,9 +211,9 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ab * TD;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % kStQ;
+                    const int s = q_resident ? kb : (int)(it % kStQ);
                     const int c = it % kStD;
-                    if ((!kQInTmem && !mbar_wait(full_q(s), (it / kStQ) & 1u, abort_flag)) ||
+                    if ((!kQInTmem && !mbar_wait(full_q(s), q_resident ? 0u : ((it / kStQ) & 1u), abort_flag)) ||
                         !mbar_wait(full_d(c), (it / kStD) & 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -218,7 +230,7 @@ __global__ void __launch_bounds__(Cfg<kQInTmem>::kThreads, 1) tq_score_tc_kernel
                             umma_f16_split(d_tmem, q_lo + k * 2, kDescSw128Hi, d_lo + k * 2, kDescSw128Hi, idesc,
                                            (kb > 0 || k > 0) ? 1u : 0u);
                     }
-                    if (!kQInTmem) umma_commit(empty_q(s));
+                    if (!kQInTmem && !q_resident) umma_commit(empty_q(s));
                     umma_commit(empty_d(c));
                 }
                 if (ok) umma_commit(acc_full(ab));
