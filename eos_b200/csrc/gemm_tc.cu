@@ -442,9 +442,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
                 const bool fast = (ncol0 + kSlabCols <= p.n);
                 uint4 res_own[4];
-                // the slab of the previous iteration may still be read by its TMA store
-                if (lane == 0) tma_store_wait_read();
-                __syncwarp();
+                // the slab of the previous iteration may still be read by its TMA store: the residual path needs the
+                // slab now, the others only when the first chunk's results are written (see chunk below)
+                if (residual) {
+                    if (lane == 0) tma_store_wait_read();
+                    __syncwarp();
+                }
                 if (fast && residual) {
                     // residual slab: coalesced registers -> staging -> this thread's own row
 #pragma unroll
@@ -483,6 +486,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     } else if (mode == kEpiBiasGeluTanh) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
+                    }
+                    if (!residual && ch == 0) {
+                        if (lane == 0) tma_store_wait_read();
+                        __syncwarp();
                     }
                     if (fast) {
                         if (residual) {
