@@ -1612,6 +1612,81 @@ int enqueue_score_tc(EosB200Corpus* c, int plan, const float* d_queries, int q_c
     return launches;
 }
 
+// valid[q] = 1 when the lists of query q hold its exact top-k for a k above the kernel's own list size: no CTA cut a
+// list (the shared threshold still is the seeded one: a cut always publishes a higher one), no list ran over, and at
+// least k candidates exist, i.e. every document above the seeded threshold is in a list and the k-th best is among them.
+__global__ void wide_check_kernel(const int* __restrict__ counts, int n_segs, int seg_len, const unsigned long long* __restrict__ tau_now,
+                                  const unsigned long long* __restrict__ tau_seed, int q_count, int k, int* __restrict__ valid) {
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= q_count) return;
+    long long total = 0;
+    bool over = false;
+    for (int i = 0; i < n_segs; ++i) {
+        const int cnt = counts[(size_t)q * n_segs + i];
+        over |= cnt > seg_len;
+        total += cnt;
+    }
+    valid[q] = (!over && tau_now[q] == tau_seed[q] && total >= k) ? 1 : 0;
+}
+
+// The 256-query batch kernel for k above its list size (128 < k <= 256): one pass with the kernel's own k = 128, then
+// a merge of the per-CTA lists for the caller's k and a validity flag per query (wide_check_kernel).  Queries whose
+// flag is 0 have to be answered by the all-scores path.
+int enqueue_score_tc_wide(EosB200Corpus* c, const float* d_queries, int q_count, int k, int64_t* d_ids, float* d_scores,
+                          int* d_valid, cudaStream_t s) {
+    const int plan = 1;
+    EosB200Corpus::TcPlan& p = c->tcp[plan];
+    EosB200Quantizer* qz = c->qz;
+    const int q_pad = (q_count + p.queries - 1) / p.queries * p.queries;
+    int launches = 1;
+    launch_tq_prepare(d_queries, q_count, q_pad, qz->spec(), nullptr, nullptr, c->qperm, s);
+    cudaMemsetAsync(c->shared_tau, 0, (size_t)q_pad * sizeof(unsigned long long), s);
+    const int64_t seed_docs = (int64_t)p.grid * 256;
+    launches += enqueue_tc_passes(c, plan, seed_docs, q_count, kTqMaxK, true, false, nullptr, nullptr, nullptr, s);
+    if (c->n >= 64 * seed_docs) {
+        const int64_t second = c->n / 32 / 256 * 256;
+        launches += enqueue_tc_passes(c, plan, second, q_count, kTqMaxK, false, false, nullptr, nullptr, c->seed_keys, s);
+        seed_tau_kernel<<<(q_count + 255) / 256, 256, 0, s>>>(c->seed_keys, q_count, kTqMaxK, c->shared_tau);
+        launches++;
+    }
+    // the seeded thresholds, kept for the check (seed_keys is free once the thresholds are made)
+    unsigned long long* tau_seed = reinterpret_cast<unsigned long long*>(c->seed_keys);
+    cudaMemcpyAsync(tau_seed, c->shared_tau, (size_t)q_pad * sizeof(unsigned long long), cudaMemcpyDeviceToDevice, s);
+    const int64_t tiles = (c->n + p.tile_docs - 1) / p.tile_docs;
+    const int grid = (int)(tiles < p.grid ? tiles : p.grid);
+    const int n_segs = p.segs_per_cta * grid;
+    for (int q0 = 0; q0 < q_count; q0 += p.queries) {
+        const int q_here = (q_count - q0) < p.queries ? (q_count - q0) : p.queries;
+        TqTcArgs a{};
+        a.tiles = c->tiles;
+        a.norms = c->norms;
+        a.n_docs = c->n;
+        a.id_base = (uint32_t)c->id_base;
+        a.dim = qz->dim;
+        a.q_row0 = q0;
+        a.q_valid = q_here;
+        a.k = kTqMaxK;
+        a.mag_hi[0] = qz->mag_hi[0];
+        a.mag_hi[1] = qz->mag_hi[1];
+        a.mag_lo[0] = qz->mag_lo[0];
+        a.mag_lo[1] = qz->mag_lo[1];
+        a.cand_keys = p.cand;
+        a.cand_count = p.count;
+        a.shared_tau = c->shared_tau + q0;
+        a.seed_scores = nullptr;
+        a.seed_stride = c->n;
+        a.qperm = c->qperm;
+        a.status = qz->rt->d_status;
+        launch_tq_score_tc256(p.tm, a, grid, s);
+        wide_check_kernel<<<(q_here + 255) / 256, 256, 0, s>>>(p.count, n_segs, kTqTcSegLen, c->shared_tau + q0, tau_seed + q0,
+                                                               q_here, k, d_valid + q0);
+        launch_tq_merge(p.cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, p.count, q_here, k, 0,
+                        d_ids + (size_t)q0 * k, d_scores + (size_t)q0 * k, nullptr, s);
+        launches += 3;
+    }
+    return launches;
+}
+
 // Enqueues prepare + scan passes + merges; returns launches (or -1 with *err set).
 int enqueue_score(EosB200Corpus* c, const float* d_queries, int q_count, int k, int per_pass, int64_t* d_ids,
                   float* d_scores, uint64_t* d_keys, cudaStream_t s) {
@@ -1977,7 +2052,77 @@ int eos_b200_score_topk(EosB200Corpus* c, const float* h_queries, int q_count, i
     }
     EosB200Runtime* rt = c->qz->rt;
     CUDA_TRY(cudaSetDevice(rt->device));
-    if (wide) return wide_topk(c, nullptr, h_queries, nullptr, 0.f, q_count, k, h_ids, h_scores, stats, "score_topk", err);
+    if (wide) {
+        // One pass of the 256-query batch kernel answers k up to 256 whenever its lists were never cut (the usual
+        // case on a seeded corpus: a few thousand candidates per query spread over the CTAs' lists); the queries for
+        // which that cannot be shown (flag 0) are answered by the all-scores path.
+        int rc = ensure_score_workspace(c, q_count, err);
+        if (rc == EOS_B200_OK) rc = ensure_tc_workspace(c, 1, err);
+        if (rc != EOS_B200_OK) return rc;
+        if (c->n < 8 * (int64_t)c->tcp[1].grid * 256)
+            return wide_topk(c, nullptr, h_queries, nullptr, 0.f, q_count, k, h_ids, h_scores, stats, "score_topk", err);
+        cudaStream_t s = rt->stream;
+        int64_t* d_ids = nullptr;
+        float* d_scores = nullptr;
+        int* d_valid = nullptr;
+        cudaError_t e = dev_alloc(&d_ids, (size_t)q_count * k);
+        if (e == cudaSuccess) e = dev_alloc(&d_scores, (size_t)q_count * k);
+        if (e == cudaSuccess) e = dev_alloc(&d_valid, (size_t)q_count);
+        std::vector<int> valid((size_t)q_count, 0);
+        int launches = 0;
+        if (e == cudaSuccess) e = cudaEventRecord(rt->ev0, s);
+        if (e == cudaSuccess) e = cudaMemsetAsync(rt->d_status, 0, sizeof(int), s);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_queries, h_queries, (size_t)q_count * c->qz->dim * 4, cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) {
+            launches = enqueue_score_tc_wide(c, c->d_queries, q_count, k, d_ids, d_scores, d_valid, s);
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess) e = cudaMemcpyAsync(h_ids, d_ids, (size_t)q_count * k * 8, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(h_scores, d_scores, (size_t)q_count * k * 4, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(valid.data(), d_valid, (size_t)q_count * 4, cudaMemcpyDeviceToHost, s);
+        if (e == cudaSuccess) e = cudaEventRecord(rt->ev1, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        dev_free(d_ids);
+        dev_free(d_scores);
+        dev_free(d_valid);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(err, std::string("score_topk: ") + cudaGetErrorString(e));
+        }
+        rc = read_status(rt, s, err);
+        if (rc != EOS_B200_OK) return rc;
+        float device_ms = 0.f;
+        cudaEventElapsedTime(&device_ms, rt->ev0, rt->ev1);
+        std::vector<int> redo;
+        for (int q = 0; q < q_count; ++q)
+            if (!valid[q]) redo.push_back(q);
+        if (!redo.empty()) {
+            const int dim = c->qz->dim;
+            std::vector<float> rq(redo.size() * (size_t)dim);
+            std::vector<int64_t> rid(redo.size() * (size_t)k);
+            std::vector<float> rsc(redo.size() * (size_t)k);
+            for (size_t i = 0; i < redo.size(); ++i)
+                std::memcpy(rq.data() + i * dim, h_queries + (size_t)redo[i] * dim, (size_t)dim * 4);
+            EosB200Stats st2{};
+            rc = wide_topk(c, nullptr, rq.data(), nullptr, 0.f, (int)redo.size(), k, rid.data(), rsc.data(), &st2, "score_topk", err);
+            if (rc != EOS_B200_OK) return rc;
+            for (size_t i = 0; i < redo.size(); ++i) {
+                std::memcpy(h_ids + (size_t)redo[i] * k, rid.data() + i * k, (size_t)k * 8);
+                std::memcpy(h_scores + (size_t)redo[i] * k, rsc.data() + i * k, (size_t)k * 4);
+            }
+            launches += st2.kernel_launches;
+            device_ms += st2.device_ms;
+        }
+        if (stats != nullptr) {
+            std::memset(stats, 0, sizeof(*stats));
+            stats->kernel_launches = launches;
+            stats->uploaded_bytes = (int64_t)q_count * c->qz->dim * 4;
+            stats->downloaded_bytes = (int64_t)q_count * k * 12;
+            stats->reserved = (int32_t)redo.size();   // queries answered by the all-scores path
+            stats->device_ms = device_ms;
+        }
+        return EOS_B200_OK;
+    }
     int rc = ensure_score_workspace(c, q_count, err);
     if (rc == EOS_B200_OK && (per_pass == kTqTcQueries || per_pass == kTqTc256Queries))
         rc = ensure_tc_workspace(c, per_pass == kTqTc256Queries ? 1 : 0, err);

@@ -305,8 +305,10 @@ EOS_B200_API int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* corpus);
  * The result is the same exact top-k for every value.
  * Results [q_count, k]: ids (int64, -1 when the corpus has fewer than k rows) and scores, ordered
  * score descending then id ascending.  k <= 128 on the fused kernels; this host call also takes k in (128, 256]
- * (the over-fetch before a rerank, runtime/retrieval_turboquant.go:1610-1662: 200 candidates for a top-100), served
- * by materialising the scores of a chunk of queries and selecting once per query. */
+ * (the over-fetch before a rerank, runtime/retrieval_turboquant.go:1610-1662: 200 candidates for a top-100): on a
+ * corpus large enough for seeded thresholds one pass of the 256-query kernel answers every query whose candidate
+ * lists were never cut; the others (stats->reserved counts them) and small corpora are answered by materialising the
+ * scores of a chunk of queries and selecting once per query. */
 EOS_B200_API int eos_b200_score_topk(EosB200Corpus* corpus, const float* h_queries, int q_count, int k, int queries_per_pass,
                         int64_t* h_ids, float* h_scores, EosB200Stats* stats, char** err);
 /* Device-resident variant, enqueued on `stream`.  d_keys (nullable, [q_count, k] uint64) receives

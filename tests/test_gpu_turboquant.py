@@ -574,3 +574,33 @@ def test_wide_k_overfetch(rt):
         corpus.score_topk(q, 257)
     corpus.close()
     qz.close()
+
+
+def test_wide_k_single_pass_and_fallback(rt):
+    """k in (128, 256] on a corpus large enough for seeded thresholds: one pass of the 256-query batch kernel answers
+    every query whose candidate lists were never cut (random data: all of them, `reserved` = 0 fallbacks); on data
+    built to cut every list (scores ascending with the row index) every query falls back to the all-scores path and
+    the answer is the same exact top-k."""
+    import eos_b200
+    spec, qz, codes, norms, q = _setup(rt, 96, 4, 320000, 7, seed=71)
+    corpus = eos_b200.Corpus(qz, codes, norms, id_base=11)
+    ref = _oracle_scores(spec, codes, norms, q)
+    tol = 1e-3 * float(np.abs(ref).max())
+    for k in (200, 256, 129):
+        ids, scores = corpus.score_topk(q, k)
+        assert corpus.last_stats.reserved == 0, corpus.last_stats.reserved
+        for i in range(q.shape[0]):
+            _check_topk(ids[i], scores[i], ref[i], k, 11, tol)
+    corpus.close()
+    n = 320000
+    codes1 = np.tile(codes[:1], (n, 1))
+    norms1 = np.linspace(0.5, 2.0, n, dtype=np.float32)
+    corpus = eos_b200.Corpus(qz, codes1, norms1)
+    ref = _oracle_scores(spec, codes1[:1], np.ones(1, np.float32), q)[:, 0:1] * norms1[None, :]
+    tol = 1e-3 * float(np.abs(ref).max())
+    ids, scores = corpus.score_topk(q, 200)
+    assert corpus.last_stats.reserved > 0
+    for i in range(q.shape[0]):
+        _check_topk(ids[i], scores[i], ref[i], 200, 0, tol)
+    corpus.close()
+    qz.close()
