@@ -433,6 +433,8 @@ void free_workspace(EosB200Encoder* e) {
     dev_free(e->lay.cu_qtiles);
     dev_free(e->lay.qtile_info);
     dev_free(e->lay.qtile_win);
+    dev_free(e->lay.qtile_info_seq);
+    dev_free(e->lay.qtile_win_seq);
     dev_free(e->h0);
     dev_free(e->h1);
     dev_free(e->qkv);
@@ -487,6 +489,8 @@ int ensure_workspace(EosB200Encoder* e, int batch, int tokens, char** err) {
     CUDA_TRY(dev_alloc(&e->lay.cu_qtiles, (size_t)nb + 1));
     CUDA_TRY(dev_alloc(&e->lay.qtile_info, (size_t)(m / 128 + nb + 1)));
     CUDA_TRY(dev_alloc(&e->lay.qtile_win, (size_t)(m / 128 + nb + 1)));
+    CUDA_TRY(dev_alloc(&e->lay.qtile_info_seq, (size_t)(m / 128 + nb + 1)));
+    CUDA_TRY(dev_alloc(&e->lay.qtile_win_seq, (size_t)(m / 128 + nb + 1)));
     CUDA_TRY(dev_alloc(&e->h0, (size_t)m * D));
     CUDA_TRY(dev_alloc(&e->h1, (size_t)m * D));
     CUDA_TRY(dev_alloc(&e->qkv, (size_t)m * 3 * D));
@@ -593,7 +597,7 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
     int launches = 0;
     Profiler& pf = e->prof;
     pf.launch(kClsLayout, s, [&] { launch_seq_layout(d_mask, batch, tokens, cls, e->window, e->lay, s); });
-    launches += 4;
+    launches += 5;
     pf.launch(kClsEmbed, s, [&] {
         if (e->compact)
             launch_embed_rope(d_ids, d_types, e->lay, tokens, e->tok, e->vocab, e->role, e->role_vocab, e->rope_cs,
@@ -988,7 +992,7 @@ int eos_b200_encoder_profile_end(EosB200Encoder* enc, void* stream, EosB200Encod
             case kClsLayerNorm: out->layernorm_ms += ms; out->layernorm_launches++; break;
             case kClsEmbed: out->embed_ms += ms; out->other_launches++; break;
             case kClsPool: out->pool_ms += ms; out->other_launches += enc->head_w != nullptr ? 2 : 1; break;
-            default: out->layout_ms += ms; out->other_launches += 4; break;
+            default: out->layout_ms += ms; out->other_launches += 5; break;
         }
     }
     enc->prof.reset();

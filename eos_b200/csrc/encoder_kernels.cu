@@ -154,6 +154,37 @@ __global__ void seq_fill_kernel(const int32_t* __restrict__ mask, int tokens, in
     }
 }
 
+// Orders the 128-query tiles by the number of key tiles each visits, most first (a counting sort in one block).
+// The attention kernel deals tiles out round-robin over its workers; in sequence order the workers' sums differ by
+// several percent (the slowest one sets the kernel's time), in this order by at most a tile or two.  Tiles of equal
+// cost land in no particular order: every tile's result is independent of where it runs.
+constexpr int kQtileCostBins = 66;   // costs 0 .. 64 key tiles, anything above shares the top bin
+__global__ void qtile_sort_kernel(const int* __restrict__ cu_qtiles, int batch, const int4* __restrict__ info_seq,
+                                  const int4* __restrict__ win_seq, int4* __restrict__ info, int4* __restrict__ win) {
+    __shared__ int count[kQtileCostBins];
+    __shared__ int start[kQtileCostBins];
+    const int total = cu_qtiles[batch];
+    for (int i = threadIdx.x; i < kQtileCostBins; i += blockDim.x) count[i] = 0;
+    __syncthreads();
+    auto bin_of = [](const int4& w) { return max(0, min(w.y - w.x, kQtileCostBins - 1)); };
+    for (int i = threadIdx.x; i < total; i += blockDim.x) atomicAdd(&count[bin_of(win_seq[i])], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int b = kQtileCostBins - 1; b >= 0; --b) {
+            start[b] = run;
+            run += count[b];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int4 w = win_seq[i];
+        const int at = atomicAdd(&start[bin_of(w)], 1);
+        win[at] = w;
+        info[at] = info_seq[i];
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // row-wise kernels: one warp per row, 8 f16 per 16-byte access, kChunks accesses per lane
 // ------------------------------------------------------------------------------------------
@@ -1076,7 +1107,9 @@ void launch_seq_layout(const int32_t* mask, int batch, int tokens, int cls_pooli
     seq_scan_kernel<<<1, 1024, 0, stream>>>(lay.row_count, batch, 1, lay.cu_rows, lay.total_rows);
     seq_scan_kernel<<<1, 1024, 0, stream>>>(lay.row_count, batch, 128, lay.cu_qtiles, nullptr);
     seq_fill_kernel<<<batch, 256, 0, stream>>>(mask, tokens, cls_pooling, lay.cu_rows, lay.key_count, lay.cu_qtiles,
-                                               window, lay.row_src, lay.cls_row, lay.qtile_info, lay.qtile_win);
+                                               window, lay.row_src, lay.cls_row, lay.qtile_info_seq, lay.qtile_win_seq);
+    qtile_sort_kernel<<<1, 1024, 0, stream>>>(lay.cu_qtiles, batch, lay.qtile_info_seq, lay.qtile_win_seq, lay.qtile_info,
+                                              lay.qtile_win);
 }
 
 void launch_embed_ln(const int32_t* ids, const int32_t* types, const SeqLayout& lay, int tokens, const __half* tok,

@@ -18,6 +18,10 @@ struct SeqLayout {
     int* cu_qtiles;   // [B+1] exclusive prefix sum of ceil(row_count / 128): 128-query tiles per sequence
     int4* qtile_info; // [sum of q-tiles] per 128-query tile: {first row of the sequence, its rows, its keys, tile's first query}
     int4* qtile_win;  // [sum of q-tiles] key tiles of 128 the tile attends to: {first, end, first fully visible, end of those}
+                      // both lists are ordered by the number of key tiles a tile visits, most first, so that a kernel
+                      // that deals the tiles out round-robin gives every worker the same amount of work
+    int4* qtile_info_seq;  // the same two lists in sequence order (what the fill kernel writes; scratch)
+    int4* qtile_win_seq;
 };
 
 // window: local attention window of the model (<= 0: none); it only shapes qtile_win.

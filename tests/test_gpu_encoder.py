@@ -152,7 +152,7 @@ def test_device_resident_run_matches_host_run(rt):
     stream = ts.cuda_stream  # non-null: the library launches on this stream
     launches = enc.run_device(d_ids.data_ptr(), d_mask.data_ptr(), None, 16, 128, d_out.data_ptr(), stream)
     enc.sync(stream)
-    assert launches == 4 + 1 + 7 * 2 + 1
+    assert launches == 5 + 1 + 7 * 2 + 1
     assert np.array_equal(d_out.cpu().numpy(), ref)
     enc.close()
 
