@@ -64,7 +64,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu)], stdout=open(self.path, "w"),
+                                          "-lms", "50", "-i", str(self.gpu)], stdout=open(self.path, "w"),
                                          stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -421,6 +421,8 @@ def run_ours(args, rank: int, world: int, local: int):
         comm.close()
 
     if rank == 0:
+        if clocks.get("sm_mhz"):   # time x clock: comparable between boxes whose power-capped clocks differ
+            clocks["ms_per_step_x_sm_ghz"] = ms_step * clocks["sm_mhz"] / 1e3
         line = {
             "metric": "q8_encoder_embeddings_per_s_T512", "value": value, "unit": "embeddings/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -802,6 +804,8 @@ def run_turboquant(args, rt, rank, world, stream, peaks, barrier, max_over_ranks
     out["pack"] = pack
     if rank == 0:
         out["clocks"] = sampler.stop()  # warm-up, timed steps and the end-to-end calls of the batch kernel
+        if out["clocks"].get("sm_mhz"):   # time x clock: comparable between boxes whose power-capped clocks differ
+            out["clocks"]["ms_per_step_x_sm_ghz"] = out["ms_per_step"] * out["clocks"]["sm_mhz"] / 1e3
     # outside the timed region: the job's result for the first 16 queries (ids / scores hold the last step's output,
     # merged over all shards) against the streaming scan of the same shards, merged the same way
     chk_q = 16
