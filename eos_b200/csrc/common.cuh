@@ -374,11 +374,17 @@ __device__ __forceinline__ __half2 gelu_erf_h2(__half2 x) {
     const __half2 hx = __hmul2(x, __float2half2_rn(0.5f));
     return __hfma2(hx, *reinterpret_cast<const __half2*>(&th), hx);
 }
-// tanh-form GELU of the compact encoder profile.
-__device__ __forceinline__ float gelu_tanh(float x) {
-    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+// tanh-form GELU on an f16 pair: x/2 (1 + tanh(x (c0 + c1 x^2))), c0 = sqrt(2/pi), c1 = 0.044715 c0; x^2 is clamped
+// at 36 (the tanh is saturated from |x| = 4.5 on), one tanh.approx.f16x2 per pair, the same error picture as above.
+__device__ __forceinline__ __half2 gelu_tanh_h2(__half2 x) {
+    const __half2 t = __hmin2(__hmul2(x, x), __float2half2_rn(36.0f));
+    const __half2 p = __hfma2(__float2half2_rn(0.035677408f), t, __float2half2_rn(0.7978845608f));
+    const __half2 z = __hmul2(x, p);
+    uint32_t th;
+    asm("tanh.approx.f16x2 %0, %1;" : "=r"(th) : "r"(*reinterpret_cast<const uint32_t*>(&z)));
+    const __half2 hx = __hmul2(x, __float2half2_rn(0.5f));
+    return __hfma2(hx, *reinterpret_cast<const __half2*>(&th), hx);
 }
-
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

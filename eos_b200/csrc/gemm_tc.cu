@@ -474,18 +474,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         v[j] = fmaf(__uint_as_float(r[j]), f.x, f.y);
                         v[j + 1] = fmaf(__uint_as_float(r[j + 1]), f.z, f.w);
                     }
-                    // the erf GELU is evaluated on f16 pairs (the output is f16 anyway)
-                    const bool kHalfGelu = mode == kEpiBiasGeluErf;
+                    // both GELU forms are evaluated on f16 pairs (the output is f16 anyway)
+                    const bool kHalfGelu = mode == kEpiBiasGeluErf || mode == kEpiBiasGeluTanh;
                     uint32_t hv[8];
                     if (kHalfGelu) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const __half2 g = gelu_erf_h2(__floats2half2_rn(v[2 * j], v[2 * j + 1]));
+                            const __half2 x2 = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                            const __half2 g = mode == kEpiBiasGeluErf ? gelu_erf_h2(x2) : gelu_tanh_h2(x2);
                             hv[j] = *reinterpret_cast<const uint32_t*>(&g);
                         }
-                    } else if (mode == kEpiBiasGeluTanh) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
                     }
                     if (!residual && ch == 0) {
                         if (lane == 0) tma_store_wait_read();
