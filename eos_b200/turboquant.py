@@ -159,7 +159,7 @@ class Corpus:
 
     def score_topk(self, queries, k: int, queries_per_pass: int = 0) -> Tuple[np.ndarray, np.ndarray]:
         """Exact top-k per query: (ids int64 [Q,k], scores fp32 [Q,k]); score desc, then id asc.
-        queries_per_pass: 0 = automatic (streaming scan up to 16 queries, tensor-core batch kernels above),
+        queries_per_pass: 0 = automatic (streaming scan up to 8 queries, tensor-core batch kernels above),
         or 8 / 16 / 32 (streaming scan), 128 / 256 (batch kernels)."""
         q = _f32(queries)
         if q.ndim != 2 or q.shape[1] != self.qz.spec.dim or q.shape[0] == 0:

@@ -296,13 +296,14 @@ EOS_B200_API int64_t eos_b200_corpus_vector_bytes(const EosB200Corpus* corpus);
  * The reference's IPQuantizer adds a QJL sign stage (Signs, ResNorm) on top of the MSE codes; those two
  * operands are not accepted here (rows that carry them bind with eos_b200_ip_corpus_bind below).
  * queries_per_pass selects how many queries share one pass over the codes, and with it the kernel:
- *   0        automatic: 8 up to 16 queries, 128 up to 128 queries, 256 above;
+ *   0        automatic: 8 up to 8 queries, 128 up to 128 queries, 256 above;
  *   8        streaming scan (codes expanded in registers, mma.sync): the choice for a few queries;
  *   16, 32   the same scan with more query fragments per pass;
  *   128, 256 batch kernels on the tensor cores (codes expanded once per 128 / 256 queries into a
  *            tcgen05 operand tile): the choice for hundreds of queries (256 is the faster one once
  *            q_count exceeds 128); q_count need not be a multiple.
- * The result is the same exact top-k for every value.
+ * Every value gives the exact top-k of the scores its kernel computes; the kernels round differently (their scores
+ * agree to about 1e-6 relative), so neighbours whose scores are closer than that may come out in either order.
  * Results [q_count, k]: ids (int64, -1 when the corpus has fewer than k rows) and scores, ordered
  * score descending then id ascending.  k <= 128 on the fused kernels; this host call also takes k in (128, 256]
  * (the over-fetch before a rerank, runtime/retrieval_turboquant.go:1610-1662: 200 candidates for a top-100): on a
