@@ -98,6 +98,8 @@ SYMBOLS = {
     "eos_b200_encoder_destroy": (None, [_P]),
     "eos_b200_encoder_reserve": (C.c_int, [_P, C.c_int, C.c_int, _ERR]),
     "eos_b200_encoder_run": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P, C.POINTER(Stats), _ERR]),
+    "eos_b200_encoder_submit": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P, _ERR]),
+    "eos_b200_encoder_wait": (C.c_int, [_P, C.POINTER(Stats), _ERR]),
     "eos_b200_encoder_run_device": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P, _P, C.POINTER(Stats), _ERR]),
     "eos_b200_encoder_set_token_head": (C.c_int, [_P, _P, C.c_int, _ERR]),
     "eos_b200_encoder_token_vectors_device": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P, _P, _P, C.POINTER(Stats),

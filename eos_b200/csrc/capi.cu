@@ -402,6 +402,8 @@ struct EosB200Encoder {
     bool attn_tc = false;        // tensor-memory attention kernel usable (head_dim 64)
     Profiler prof;
     int launches_per_forward = 0;
+    int submitted_launches = 0;          // of the batches submitted since the last wait
+    int64_t submitted_up = 0, submitted_down = 0;
     // compact profile (models/default_embedding.go:461-505): role table instead of position / type tables,
     // rotary positions, no biases, non-affine LayerNorm, per-token normalize + masked mean at the end
     bool compact = false;
@@ -1041,6 +1043,55 @@ int eos_b200_encoder_run(EosB200Encoder* enc, const int32_t* h_ids, const int32_
         stats->valid_tokens = rows;
         cudaEventElapsedTime(&stats->device_ms, rt->ev0, rt->ev1);
     }
+    return rc;
+}
+
+int eos_b200_encoder_submit(EosB200Encoder* enc, const int32_t* h_ids, const int32_t* h_mask, const int32_t* h_types,
+                            int batch, int tokens, float* h_out, char** err) {
+    if (enc == nullptr || h_ids == nullptr || h_mask == nullptr || h_out == nullptr)
+        return fail(err, "bert_embedder expects non-nil input_ids, attention_mask and output");
+    if (batch <= 0 || tokens <= 0) return fail(err, "bert_embedder input_ids must be a non-empty [B,T] tensor");
+    if (!enc->compact && tokens > enc->max_pos)
+        return fail(err, "bert_embeddings position_ids value out of range (tokens > max_positions)");
+    EosB200Runtime* rt = enc->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    // growing the workspace frees the buffers batches in flight still use: they are waited for first
+    const long long elems = (long long)batch * tokens;
+    if (batch > enc->cap_batch || elems > enc->cap_elems) CUDA_TRY(cudaStreamSynchronize(rt->stream));
+    int rc = ensure_workspace(enc, batch, tokens, err);
+    if (rc != EOS_B200_OK) return rc;
+    cudaStream_t s = rt->stream;
+    const size_t n = (size_t)batch * tokens;
+    const int E = enc->head_out > 0 ? enc->head_out : enc->hidden;
+    // stream order does the rest: this batch's uploads follow the previous batch's kernels, its kernels the previous
+    // batch's download.  The status word is not reset here: an error of any batch in flight stays until the wait.
+    CUDA_TRY(cudaMemcpyAsync(enc->d_ids, h_ids, n * 4, cudaMemcpyHostToDevice, s));
+    CUDA_TRY(cudaMemcpyAsync(enc->d_mask, h_mask, n * 4, cudaMemcpyHostToDevice, s));
+    if (h_types != nullptr) CUDA_TRY(cudaMemcpyAsync(enc->d_types, h_types, n * 4, cudaMemcpyHostToDevice, s));
+    const int launches =
+        enqueue_forward(enc, enc->d_ids, enc->d_mask, h_types != nullptr ? enc->d_types : nullptr, batch, tokens,
+                        enc->d_out, s);
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaMemcpyAsync(h_out, enc->d_out, (size_t)batch * E * 4, cudaMemcpyDeviceToHost, s));
+    enc->submitted_launches += launches;
+    enc->submitted_up += (int64_t)n * 4 * (h_types != nullptr ? 3 : 2);
+    enc->submitted_down += (int64_t)batch * E * 4;
+    return EOS_B200_OK;
+}
+
+int eos_b200_encoder_wait(EosB200Encoder* enc, EosB200Stats* stats, char** err) {
+    if (enc == nullptr) return fail(err, "encoder_wait: null encoder");
+    EosB200Runtime* rt = enc->rt;
+    CUDA_TRY(cudaSetDevice(rt->device));
+    const int rc = read_status(rt, rt->stream, err);   // synchronises the stream
+    if (stats != nullptr) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->kernel_launches = enc->submitted_launches;
+        stats->uploaded_bytes = enc->submitted_up;
+        stats->downloaded_bytes = enc->submitted_down;
+    }
+    enc->submitted_launches = 0;
+    enc->submitted_up = enc->submitted_down = 0;
     return rc;
 }
 

@@ -187,6 +187,7 @@ class BertEmbedder:
         rt._adopt(self)
         self.hidden, self.layers, self.heads, self.intermediate = d.hidden, layers, d.heads, d.intermediate
         self.last_stats = Stats()
+        self._in_flight: list = []
 
     def reserve(self, batch: int, tokens: int) -> None:
         _lib.call("eos_b200_encoder_reserve", self.handle, int(batch), int(tokens))
@@ -205,6 +206,32 @@ class BertEmbedder:
         _lib.call("eos_b200_encoder_run", self.handle, _ptr(ids), _ptr(mask), _ptr(types), ids.shape[0], ids.shape[1],
                   _ptr(out), C.byref(self.last_stats))
         return out
+
+    def submit(self, input_ids, attention_mask, out: np.ndarray, token_type_ids=None) -> None:
+        """Enqueues one batch (uploads, forward, download into `out` [B, E] fp32) and returns without waiting; `wait`
+        completes every batch submitted since the last wait.  The arrays must be C-contiguous int32 / float32 (they are
+        not copied), stay untouched until the wait, and be page-locked for the copies to overlap."""
+        ids, mask = np.asarray(input_ids), np.asarray(attention_mask)
+        types = None if token_type_ids is None else np.asarray(token_type_ids)
+        for name, a in (("input_ids", ids), ("attention_mask", mask), ("token_type_ids", types)):
+            if a is not None and (a.dtype != np.int32 or not a.flags.c_contiguous):
+                raise ValueError(f"submit: {name} must be a C-contiguous int32 array (it is used in place)")
+        if ids.ndim != 2 or mask.shape != ids.shape or (types is not None and types.shape != ids.shape):
+            raise ValueError("submit: input_ids, attention_mask and token_type_ids must be [B,T] arrays of one shape")
+        if out.dtype != np.float32 or not out.flags.c_contiguous or out.shape != (ids.shape[0], self.out_dim):
+            raise ValueError(f"submit: out must be a C-contiguous float32 array [{ids.shape[0]}, {self.out_dim}]")
+        _lib.call("eos_b200_encoder_submit", self.handle, _ptr(ids), _ptr(mask), _ptr(types), ids.shape[0], ids.shape[1],
+                  _ptr(out))
+        if not hasattr(self, "_in_flight"):
+            self._in_flight = []
+        self._in_flight.append((ids, mask, types, out))   # keeps the buffers alive until the wait
+
+    def wait(self) -> None:
+        try:
+            _lib.call("eos_b200_encoder_wait", self.handle, C.byref(self.last_stats))
+        finally:
+            if hasattr(self, "_in_flight"):
+                self._in_flight.clear()
 
     def run_device(self, d_ids: int, d_mask: int, d_types: Optional[int], batch: int, tokens: int, d_out: int,
                    stream: Optional[int] = None) -> int:

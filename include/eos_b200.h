@@ -163,6 +163,17 @@ EOS_B200_API int eos_b200_encoder_reserve(EosB200Encoder* enc, int batch, int to
  * (tensor_ops.go:1479-1487); an all-masked sequence yields a zero vector. */
 EOS_B200_API int eos_b200_encoder_run(EosB200Encoder* enc, const int32_t* h_ids, const int32_t* h_mask, const int32_t* h_types,
                          int batch, int tokens, float* h_out, EosB200Stats* stats, char** err);
+/* The same forward without waiting for it: the uploads, the kernels and the download of h_out are enqueued on the
+ * runtime's stream and the call returns; eos_b200_encoder_wait blocks until every submitted batch is complete and
+ * reports the first device status raised by any of them.  A host that has the next batch ready keeps the GPU busy
+ * across the copies this way (EmbedBatch callers that loop over batches, runtime/embedding_model.go:664-700).
+ * h_ids / h_mask / h_types must not be modified and h_out not read before the wait; buffers of different batches in
+ * flight must be distinct; for the copies to overlap the host buffers have to be page-locked.  stats of the wait:
+ * launches and bytes of all the batches waited for. */
+EOS_B200_API int eos_b200_encoder_submit(EosB200Encoder* enc, const int32_t* h_ids, const int32_t* h_mask,
+                                         const int32_t* h_types, int batch, int tokens, float* h_out, char** err);
+EOS_B200_API int eos_b200_encoder_wait(EosB200Encoder* enc, EosB200Stats* stats, char** err);
+
 /* ---- compact encoder profile ----------------------------------------------------------------
  * The native q8 encoder graph of models/default_embedding.go:461-505 (pipeline embed_pooled_batch):
  * gather(token_embedding) + gather(role_embedding) -> rope (runtime/backend/tensor_ops.go:1936-1965)

@@ -194,3 +194,33 @@ def test_local_window_attention_extension(rt):
         # a window wider than the sequence is full attention (different kernels: tensor-memory vs mma.sync)
         assert np.abs(outs[0] - outs[1000]).max() <= 1e-4
         assert np.abs(outs[0][:3] - outs[16][:3]).max() > 5e-3  # and a narrow one is a different function
+
+
+def test_submit_wait_reproduces_run(rt):
+    """Batches submitted without waiting in between (eos_b200_encoder_submit / _wait) give the bits of the synchronous
+    call, each in its own output buffer, in submission order; a bad token id in one of them surfaces at the wait and
+    leaves the handle usable."""
+    import eos_b200
+    from eos_b200 import synth
+    w = synth.make_q8_encoder(2, 128, 4, 256, vocab=500, max_pos=64, seed=77)
+    enc = eos_b200.BertEmbedder(rt, **w)
+    batches = [synth.make_batch(b, t, 500, 3, t, seed=90 + i)[:2] for i, (b, t) in enumerate(((5, 40), (9, 64), (2, 17)))]
+    want = [enc.run(ids, mask) for ids, mask in batches]
+    per_forward = enc.last_stats.kernel_launches
+    outs = [np.full((ids.shape[0], enc.out_dim), np.nan, np.float32) for ids, _ in batches]
+    for (ids, mask), out in zip(batches, outs):
+        enc.submit(np.ascontiguousarray(ids, np.int32), np.ascontiguousarray(mask, np.int32), out)
+    enc.wait()
+    for got, ref in zip(outs, want):
+        assert np.array_equal(got, ref)
+    assert enc.last_stats.kernel_launches == 3 * per_forward
+    bad = np.ascontiguousarray(batches[0][0], np.int32).copy()
+    bad[0, 0] = 500
+    enc.submit(bad, np.ascontiguousarray(batches[0][1], np.int32), outs[0])
+    enc.submit(np.ascontiguousarray(batches[1][0], np.int32), np.ascontiguousarray(batches[1][1], np.int32), outs[1])
+    with pytest.raises(eos_b200.EosB200DeviceStatusError):
+        enc.wait()
+    assert np.array_equal(enc.run(*batches[2]), want[2])
+    with pytest.raises(ValueError):
+        enc.submit(batches[0][0].astype(np.int64), batches[0][1], outs[0])
+    enc.close()
