@@ -402,6 +402,15 @@ struct EosB200Encoder {
     bool attn_tc = false;        // tensor-memory attention kernel usable (head_dim 64)
     Profiler prof;
     int launches_per_forward = 0;
+    // forwards of the host-buffer calls, captured once per [batch, tokens] shape and replayed as one graph launch
+    struct ForwardGraph {
+        int batch, tokens;
+        bool types;
+        int launches;
+        cudaGraphExec_t exec;
+    };
+    std::vector<ForwardGraph> graphs;
+    bool graphs_off = false;
     int submitted_launches = 0;          // of the batches submitted since the last wait
     int64_t submitted_up = 0, submitted_down = 0;
     // compact profile (models/default_embedding.go:461-505): role table instead of position / type tables,
@@ -423,6 +432,11 @@ struct EosB200Encoder {
 namespace {
 
 void free_workspace(EosB200Encoder* e) {
+    if (!e->graphs.empty()) {   // they hold the workspace's pointers; none may be in flight when it goes
+        cudaStreamSynchronize(e->rt->stream);
+        for (auto& g : e->graphs) cudaGraphExecDestroy(g.exec);
+        e->graphs.clear();
+    }
     dev_free(e->d_ids);
     dev_free(e->d_mask);
     dev_free(e->d_types);
@@ -651,6 +665,50 @@ int enqueue_forward(EosB200Encoder* e, const int32_t* d_ids, const int32_t* d_ma
         launches += e->head_w != nullptr ? 2 : 1;
     }
     e->launches_per_forward = launches;
+    return launches;
+}
+
+// The forward of a host-buffer call (inputs in e->d_ids / d_mask / d_types, result in e->d_out): captured into a CUDA
+// graph the first time a [batch, tokens] shape is seen and replayed afterwards.  A 12-layer forward is 92 launches;
+// for a single query or a small batch the host's launch calls, not the kernels, set the latency.  Every pointer and
+// size the kernels receive is fixed per shape (row counts are read from device memory), so a replay is the same work.
+// Falls back to plain launches while a profile is being recorded, when EOS_B200_NO_GRAPHS is set, or if a capture fails.
+int forward_host_call(EosB200Encoder* e, bool types, int batch, int tokens, cudaStream_t s) {
+    static const bool env_off = [] {
+        const char* v = getenv("EOS_B200_NO_GRAPHS");
+        return v != nullptr && v[0] != '\0' && v[0] != '0';
+    }();
+    const int32_t* d_types = types ? e->d_types : nullptr;
+    if (env_off || e->graphs_off || e->prof.on)
+        return enqueue_forward(e, e->d_ids, e->d_mask, d_types, batch, tokens, e->d_out, s);
+    for (const auto& g : e->graphs)
+        if (g.batch == batch && g.tokens == tokens && g.types == types) {
+            if (cudaGraphLaunch(g.exec, s) == cudaSuccess) return g.launches;
+            break;
+        }
+    if (e->graphs.size() >= 16) {   // a host cycling through many shapes: start over rather than grow without bound
+        cudaStreamSynchronize(s);
+        for (auto& g : e->graphs) cudaGraphExecDestroy(g.exec);
+        e->graphs.clear();
+    }
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int launches = 0;
+    bool ok = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+    if (ok) {
+        launches = enqueue_forward(e, e->d_ids, e->d_mask, d_types, batch, tokens, e->d_out, s);
+        ok = cudaStreamEndCapture(s, &graph) == cudaSuccess && graph != nullptr;
+    }
+    if (ok) ok = cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess;
+    if (graph != nullptr) cudaGraphDestroy(graph);
+    if (ok) ok = cudaGraphLaunch(exec, s) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();   // the failed capture's error is not this call's
+        if (exec != nullptr) cudaGraphExecDestroy(exec);
+        e->graphs_off = true;
+        return enqueue_forward(e, e->d_ids, e->d_mask, d_types, batch, tokens, e->d_out, s);
+    }
+    e->graphs.push_back({batch, tokens, types, launches, exec});
     return launches;
 }
 
@@ -1026,9 +1084,7 @@ int eos_b200_encoder_run(EosB200Encoder* enc, const int32_t* h_ids, const int32_
     CUDA_TRY(cudaMemcpyAsync(enc->d_ids, h_ids, n * 4, cudaMemcpyHostToDevice, s));
     CUDA_TRY(cudaMemcpyAsync(enc->d_mask, h_mask, n * 4, cudaMemcpyHostToDevice, s));
     if (h_types != nullptr) CUDA_TRY(cudaMemcpyAsync(enc->d_types, h_types, n * 4, cudaMemcpyHostToDevice, s));
-    const int launches =
-        enqueue_forward(enc, enc->d_ids, enc->d_mask, h_types != nullptr ? enc->d_types : nullptr, batch, tokens,
-                        enc->d_out, s);
+    const int launches = forward_host_call(enc, h_types != nullptr, batch, tokens, s);
     CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaMemcpyAsync(h_out, enc->d_out, (size_t)batch * E * 4, cudaMemcpyDeviceToHost, s));
     int rows = 0;
@@ -1068,9 +1124,7 @@ int eos_b200_encoder_submit(EosB200Encoder* enc, const int32_t* h_ids, const int
     CUDA_TRY(cudaMemcpyAsync(enc->d_ids, h_ids, n * 4, cudaMemcpyHostToDevice, s));
     CUDA_TRY(cudaMemcpyAsync(enc->d_mask, h_mask, n * 4, cudaMemcpyHostToDevice, s));
     if (h_types != nullptr) CUDA_TRY(cudaMemcpyAsync(enc->d_types, h_types, n * 4, cudaMemcpyHostToDevice, s));
-    const int launches =
-        enqueue_forward(enc, enc->d_ids, enc->d_mask, h_types != nullptr ? enc->d_types : nullptr, batch, tokens,
-                        enc->d_out, s);
+    const int launches = forward_host_call(enc, h_types != nullptr, batch, tokens, s);
     CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaMemcpyAsync(h_out, enc->d_out, (size_t)batch * E * 4, cudaMemcpyDeviceToHost, s));
     enc->submitted_launches += launches;

@@ -160,7 +160,9 @@ EOS_B200_API int eos_b200_encoder_reserve(EosB200Encoder* enc, int batch, int to
  * (runtime/backend/bert_embedder_ops.go:101-197) [+ PretrainedBERTProjectionHead.Apply].
  * h_ids/h_mask/h_types are [batch, tokens] int32 (h_types may be NULL = all zero); h_out is
  * [batch, E] fp32, E = head_out or hidden.  Out-of-range ids return EOS_B200_DEVICE_STATUS
- * (tensor_ops.go:1479-1487); an all-masked sequence yields a zero vector. */
+ * (tensor_ops.go:1479-1487); an all-masked sequence yields a zero vector.
+ * The forward is captured into a CUDA graph the first time a [batch, tokens] shape is seen and replayed afterwards
+ * (one launch call instead of 92 for 12 layers; EOS_B200_NO_GRAPHS=1 turns this off). */
 EOS_B200_API int eos_b200_encoder_run(EosB200Encoder* enc, const int32_t* h_ids, const int32_t* h_mask, const int32_t* h_types,
                          int batch, int tokens, float* h_out, EosB200Stats* stats, char** err);
 /* The same forward without waiting for it: the uploads, the kernels and the download of h_out are enqueued on the
