@@ -1386,8 +1386,9 @@ struct EosB200Corpus {
         int grid = 0;
         bool q_in_tmem = false;   // plan 0 only: opt-in variant with the queries resident in tensor memory
         int map_queries = 0;      // query rows the tensor map covers (0 = not built)
-        uint64_t* cand = nullptr;     // [queries][segs_per_cta * grid][kTqTcSegLen]
-        int* count = nullptr;         // [queries][segs_per_cta * grid]
+        int slots = 1;            // launches whose candidate lists are held before one merge launch
+        uint64_t* cand = nullptr;     // [slots][queries][segs_per_cta * grid][kTqTcSegLen]
+        int* count = nullptr;         // [slots][queries][segs_per_cta * grid]
         float* seed_scores = nullptr; // [queries][grid * 256] scores of the sample that seeds the thresholds
         CUtensorMap tm;
     } tcp[2];
@@ -1398,6 +1399,7 @@ struct EosB200Corpus {
 
 namespace {
 constexpr int kTqGroupQueries = 256;  // queries whose per-CTA candidates are held before one merge launch
+constexpr int kTqTcMergeSlots = 16;   // launches of the 256-query batch kernel whose lists one launch merges
 
 __global__ void synth_gaussian_kernel(unsigned long long seed, long long row_offset, long long n, int dim, int normalize,
                                       float* __restrict__ out) {
@@ -1515,8 +1517,11 @@ int ensure_tc_workspace(EosB200Corpus* c, int plan, char** err) {
         p.segs_per_cta = plan == 1 ? 1 : 2;
         const int64_t tiles = (c->n + p.tile_docs - 1) / p.tile_docs;
         const int grid = (int)(tiles < c->qz->rt->sm_count ? (tiles > 0 ? tiles : 1) : c->qz->rt->sm_count);
-        CUDA_TRY(dev_alloc(&p.cand, (size_t)p.queries * p.segs_per_cta * grid * kTqTcSegLen));
-        CUDA_TRY(dev_alloc(&p.count, (size_t)p.queries * p.segs_per_cta * grid));
+        // the 256-query plan keeps the lists of up to 16 launches (16 x 77.6 MB on a full grid) and merges them with
+        // one launch: a merge of 256 queries is a 40 us launch of 256 blocks, one of 4096 queries fills the GPU
+        p.slots = plan == 1 ? kTqTcMergeSlots : 1;
+        CUDA_TRY(dev_alloc(&p.cand, (size_t)p.slots * p.queries * p.segs_per_cta * grid * kTqTcSegLen));
+        CUDA_TRY(dev_alloc(&p.count, (size_t)p.slots * p.queries * p.segs_per_cta * grid));
         CUDA_TRY(dev_alloc(&p.seed_scores, (size_t)p.queries * grid * 256));
         p.grid = grid;
     }
@@ -1593,6 +1598,21 @@ int enqueue_tc_passes(EosB200Corpus* c, int plan, int64_t n_docs, int q_count, i
     const int grid = (int)(tiles < p.grid ? tiles : p.grid);
     const int n_segs = p.segs_per_cta * grid;
     int launches = 0;
+    // lists of the launches since the last merge: launch i of them writes slot i of the workspace; the lists of all
+    // their queries are then contiguous ([slot][query][list]) and one merge launch serves them all
+    const size_t slot_lists = (size_t)p.queries * n_segs;
+    int pending = 0, pending_q0 = 0, slot = 0;
+    auto merge = [&] {
+        if (pending == 0) return;
+        launch_tq_merge_lists(p.cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, p.count, pending, k,
+                              d_ids != nullptr ? d_ids + (size_t)pending_q0 * k : nullptr,
+                              d_scores != nullptr ? d_scores + (size_t)pending_q0 * k : nullptr,
+                              d_keys != nullptr ? d_keys + (size_t)pending_q0 * k : nullptr, s);
+        ++launches;
+        pending_q0 += pending;
+        pending = 0;
+        slot = 0;
+    };
     for (int q0 = 0; q0 < q_count; q0 += p.queries) {
         const int q_here = (q_count - q0) < p.queries ? (q_count - q0) : p.queries;
         TqTcArgs a{};
@@ -1608,8 +1628,8 @@ int enqueue_tc_passes(EosB200Corpus* c, int plan, int64_t n_docs, int q_count, i
         a.mag_hi[1] = qz->mag_hi[1];
         a.mag_lo[0] = qz->mag_lo[0];
         a.mag_lo[1] = qz->mag_lo[1];
-        a.cand_keys = p.cand;
-        a.cand_count = p.count;
+        a.cand_keys = p.cand + (seed ? 0 : (size_t)slot * slot_lists * kTqTcSegLen);
+        a.cand_count = p.count + (seed ? 0 : (size_t)slot * slot_lists);
         a.shared_tau = c->shared_tau + q0;
         a.seed_scores = seed ? p.seed_scores : nullptr;
         a.seed_stride = n_docs;  // seed mode: n_docs = grid * 256 scores per query, a multiple of the tile
@@ -1621,15 +1641,16 @@ int enqueue_tc_passes(EosB200Corpus* c, int plan, int64_t n_docs, int q_count, i
         };
         if (profile) c->prof.launch(kClsScan, s, launch);
         else launch();
-        if (seed)
+        ++launches;
+        if (seed) {
             launch_tq_seed_tau_scores(p.seed_scores, n_docs, (int)n_docs, q_here, k, c->shared_tau + q0, s);
-        else
-            launch_tq_merge_lists(p.cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, p.count, q_here, k,
-                                  d_ids != nullptr ? d_ids + (size_t)q0 * k : nullptr,
-                                  d_scores != nullptr ? d_scores + (size_t)q0 * k : nullptr,
-                                  d_keys != nullptr ? d_keys + (size_t)q0 * k : nullptr, s);
-        launches += 2;
+            ++launches;
+        } else {
+            pending += q_here;
+            if (++slot == p.slots) merge();
+        }
     }
+    merge();
     return launches;
 }
 
