@@ -2,6 +2,7 @@
 
     python -m eos_b200.profile_cases gemm        # projection kernel, 32768 x 768 -> 3072, erf-GELU epilogue
     python -m eos_b200.profile_cases gemm_res    # 32768 x 3072 -> 768 with residual epilogue
+    python -m eos_b200.profile_cases layernorm   # two-layer forward over 512 sequences (capture layernorm_kernel)
     python -m eos_b200.profile_cases gemm_f16w / gemm_res_f16w / gemm_qkv_f16w / gemm_attn_out_f16w
                                                  # the four projections of a layer, weights resident as f16
     python -m eos_b200.profile_cases scan        # TurboQuant scan, 2,000,000 x 768 4-bit codes (776 MB), 8 / 16 / 32 queries per pass
@@ -111,12 +112,12 @@ def case_score_tc(n: int = 1_250_000, nq: int = 512, per_pass: int = 128) -> Non
     rt.close()
 
 
-def case_attention() -> None:
+def case_attention(sequences: int = 128) -> None:
     import eos_b200
     from eos_b200 import synth
     rt = eos_b200.Runtime(0)
     args = synth.make_q8_encoder(2, 768, 12, 3072, vocab=30522, max_pos=512, seed=301)
-    ids, mask, lengths = synth.make_batch(128, 512, 30522, 64, 512, seed=303)
+    ids, mask, lengths = synth.make_batch(sequences, 512, 30522, 64, 512, seed=303)
     enc = eos_b200.BertEmbedder(rt, **args)
     for _ in range(2):
         enc.run(ids, mask)
@@ -215,6 +216,7 @@ def case_sparse_attention(batches: int = 8, q_len: int = 2048, k_len: int = 8192
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": case_gemm, "gemm_res": lambda: case_gemm(True), "scan": case_scan, "score_tc": case_score_tc, "score_tc256": lambda: case_score_tc(per_pass=256), "attention": case_attention,
+     "layernorm": lambda: case_attention(512),   # the same two-layer forward at 512 sequences: rows larger than L2
      "maxsim": case_maxsim, "pack": case_pack, "sparse_attention": case_sparse_attention,
      "gemm_f16w": lambda: case_gemm(False, 1), "gemm_res_f16w": lambda: case_gemm(True, 1),
      "gemm_big": lambda: case_gemm(False, 0, 131072), "gemm_res_big": lambda: case_gemm(True, 0, 131072),
