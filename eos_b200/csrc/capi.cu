@@ -1712,6 +1712,23 @@ int enqueue_maxsim_passes(EosB200Corpus* c, int q_vectors, int group, int childr
     return launches;
 }
 
+// Rows of the second threshold sample (0 = none).  A threshold that is the k-th best score of s rows lets about
+// k n / s of a shard's n rows into each query's candidate lists, and handling those costs the batch kernel about 42 ns
+// per candidate and query of a launch (measured at 768 dimensions: 0.14 ms per launch of 256 queries at 3300
+// candidates each, whatever the shard's size).  Scoring a sample of f n rows costs f of a launch per group of
+// queries a rank seeds; with `sharing` ranks splitting the seeding of a batch, total time is least at
+// f = sqrt(sharing * 108 k (768 / padded dim) / n): 1/30 for one GPU at 10 M rows, 1/4 for eight GPUs at 1.25 M each.
+// A sample under four times the first one (grid * 256 rows) tightens too little to pay for its launches.
+int64_t second_sample_rows(const EosB200Corpus* c, int64_t seed_docs, int k, int sharing) {
+    if (c->n <= 0) return 0;
+    const double dimp = (double)tq_ksteps(c->qz->dim) * 16.0;
+    double f = std::sqrt((double)(sharing > 0 ? sharing : 1) * 108.0 * (double)k * (768.0 / dimp) / (double)c->n);
+    if (f < 1.0 / 32.0) f = 1.0 / 32.0;
+    if (f > 0.5) f = 0.5;
+    const int64_t rows = (int64_t)(f * (double)c->n) / 256 * 256;
+    return rows >= 4 * seed_docs ? rows : 0;
+}
+
 // The batch paths.  Thresholds are seeded from the first grid * 256 rows (every score written out, k-th best per
 // query); on a large shard a second sample of 1/32 of the rows, scored with those thresholds and merged like the real
 // pass, tightens them further, so that the lists of the full pass stay short (no list is cut, and the merge gathers a
@@ -1731,8 +1748,8 @@ int enqueue_score_tc(EosB200Corpus* c, int plan, const float* d_queries, int q_c
         cudaMemcpyAsync(c->shared_tau, d_tau_in, (size_t)q_count * sizeof(unsigned long long), cudaMemcpyDeviceToDevice, s);
     } else if (c->n >= 8 * seed_docs && k <= seed_docs) {
         launches += enqueue_tc_passes(c, plan, seed_docs, q_count, k, true, false, nullptr, nullptr, nullptr, s);
-        if (c->n >= 64 * seed_docs) {
-            const int64_t second = c->n / 32 / 256 * 256;
+        const int64_t second = second_sample_rows(c, seed_docs, k, 1);
+        if (second > 0) {
             launches += enqueue_tc_passes(c, plan, second, q_count, k, false, false, nullptr, nullptr, c->seed_keys, s);
             seed_tau_kernel<<<(q_count + 255) / 256, 256, 0, s>>>(c->seed_keys, q_count, k, c->shared_tau);
             launches++;
@@ -2107,13 +2124,17 @@ int eos_b200_score_topk_device(EosB200Corpus* c, const float* d_queries, int q_c
     return EOS_B200_OK;
 }
 
-int eos_b200_score_seed_device(EosB200Corpus* c, const float* d_queries, int q_count, int k, uint64_t* d_tau_out,
-                               void* stream, char** err) {
+// Thresholds of q_count queries from samples of this shard.  sharing = ranks that split the seeding of one batch
+// between them (each calls this for its slice): the more they are, the larger the second sample that pays.
+static int score_seed_shared(EosB200Corpus* c, const float* d_queries, int q_count, int k, uint64_t* d_tau_out, int sharing,
+                      void* stream, int* launches_out, char** err) {
     if (c == nullptr || d_queries == nullptr || d_tau_out == nullptr) return fail(err, "score_seed: null argument");
     std::string m = check_score_args(c, q_count, k, kTqTc256Queries);
     if (!m.empty()) return fail(err, m);
     CUDA_TRY(cudaSetDevice(c->qz->rt->device));
     cudaStream_t s = pick_stream(c->qz->rt, stream);
+    int launches = 0;
+    if (launches_out != nullptr) *launches_out = 0;
     if (c->n == 0) {
         CUDA_TRY(cudaMemsetAsync(d_tau_out, 0, (size_t)q_count * sizeof(uint64_t), s));
         return EOS_B200_OK;
@@ -2124,20 +2145,27 @@ int eos_b200_score_seed_device(EosB200Corpus* c, const float* d_queries, int q_c
     const EosB200Corpus::TcPlan& p = c->tcp[1];
     const int q_pad = (q_count + p.queries - 1) / p.queries * p.queries;
     launch_tq_prepare(d_queries, q_count, q_pad, c->qz->spec(), nullptr, nullptr, c->qperm, s);
+    launches++;
     CUDA_TRY(cudaMemsetAsync(c->shared_tau, 0, (size_t)q_pad * sizeof(unsigned long long), s));
     const int64_t seed_docs = (int64_t)p.grid * 256;
     if (c->n >= seed_docs && k <= seed_docs) {
-        enqueue_tc_passes(c, 1, seed_docs, q_count, k, true, false, nullptr, nullptr, nullptr, s);
-        if (c->n >= 64 * seed_docs) {
-            // a large shard: tighten the thresholds with a second sample of 1/32 of the rows, as the unsharded call does
-            const int64_t second = c->n / 32 / 256 * 256;
-            enqueue_tc_passes(c, 1, second, q_count, k, false, false, nullptr, nullptr, c->seed_keys, s);
+        launches += enqueue_tc_passes(c, 1, seed_docs, q_count, k, true, false, nullptr, nullptr, nullptr, s);
+        const int64_t second = second_sample_rows(c, seed_docs, k, sharing);
+        if (second > 0) {
+            launches += enqueue_tc_passes(c, 1, second, q_count, k, false, false, nullptr, nullptr, c->seed_keys, s);
             seed_tau_kernel<<<(q_count + 255) / 256, 256, 0, s>>>(c->seed_keys, q_count, k, c->shared_tau);
+            launches++;
         }
     }
     CUDA_TRY(cudaMemcpyAsync(d_tau_out, c->shared_tau, (size_t)q_count * sizeof(uint64_t), cudaMemcpyDeviceToDevice, s));
     CUDA_TRY(cudaGetLastError());
+    if (launches_out != nullptr) *launches_out = launches;
     return EOS_B200_OK;
+}
+
+int eos_b200_score_seed_device(EosB200Corpus* c, const float* d_queries, int q_count, int k, uint64_t* d_tau_out,
+                               void* stream, char** err) {
+    return score_seed_shared(c, d_queries, q_count, k, d_tau_out, 1, stream, nullptr, err);
 }
 
 int eos_b200_score_topk_seeded_device(EosB200Corpus* c, const float* d_queries, int q_count, int k, const uint64_t* d_tau,
@@ -2670,9 +2698,11 @@ int eos_b200_score_topk_sharded(EosB200Corpus* c, EosB200Comm* comm, const float
         const int q_n = std::min(q_count, q_lo + slice) - q_lo;
         CUDA_TRY(cudaMemsetAsync(comm->tau_local, 0, (size_t)slice * sizeof(uint64_t), s));
         if (q_n > 0 && c->n > 0) {
-            rc = eos_b200_score_seed_device(c, d_queries + (size_t)q_lo * c->qz->dim, q_n, k, comm->tau_local, s, err);
+            int seed_launches = 0;
+            rc = score_seed_shared(c, d_queries + (size_t)q_lo * c->qz->dim, q_n, k, comm->tau_local, world, s, &seed_launches,
+                                   err);
             if (rc != EOS_B200_OK) return rc;
-            launches += 2 * ((q_n + kTqTc256Queries - 1) / kTqTc256Queries) + 1;
+            launches += seed_launches;
         }
         nccl_try(api->AllGather(comm->tau_local, comm->tau_all, (size_t)slice * sizeof(uint64_t), kNcclChar, comm->comm, s),
                  "ncclAllGather(thresholds)");
