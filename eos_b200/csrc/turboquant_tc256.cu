@@ -49,11 +49,18 @@ constexpr uint32_t kOffD = kOffQ + kStQ * kBytesQ;
 constexpr uint32_t kOffSort = kOffD + kStD * kBytesD;                 // 8 warps x 256 keys
 constexpr uint32_t kOffTauKey = kOffSort + kEpiWarps * kSortCap * 8;  // [256] u64
 constexpr uint32_t kOffTauF = kOffTauKey + TQ * 8;                    // [256] float
-constexpr uint32_t kOffCnt = kOffTauF + TQ * 4;                       // [256] int
+constexpr uint32_t kOffTauLo = kOffTauF + TQ * 4;                     // [256] float: the threshold one ulp lower
+constexpr uint32_t kOffCnt = kOffTauLo + TQ * 4;                      // [256] int
 constexpr uint32_t kOffBars = kOffCnt + TQ * 4;
 constexpr uint32_t kNumBars = 2 * kStQ + 2 * kStD + 4;
 constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;
 constexpr uint32_t kSmemBytes = kOffMisc + 16 + 1024;
+
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 
 static_assert(TD / kTqDocsPerTile == kExpWarps, "one 16-document group per expander warp");
 static_assert(kTqTcSegLen == kSortCap && kTqTcSegLen >= kCutAbove + TD && kTqMaxK <= kCutAbove, "list capacity");
@@ -227,12 +234,21 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc256_kernel(const __gri
         u64* const cand = reinterpret_cast<u64*>(a.cand_keys);
         u64* tau_key_s = reinterpret_cast<u64*>(sm + kOffTauKey);
         float* tau_f_s = reinterpret_cast<float*>(sm + kOffTauF);
+        // The screening test of a tile is one fused multiply-add per score, accumulator x norm - threshold, and a
+        // running maximum: its sign is the sign of the exact difference, while the score that is kept is the rounded
+        // product.  A product that rounds up onto the threshold would be missed, so the screen uses the threshold one
+        // ulp lower; what it lets through is tested again on the rounded score.
+        float* tau_lo_s = reinterpret_cast<float*>(sm + kOffTauLo);
+        auto set_tau_f = [&](int q, float t) {
+            tau_f_s[q] = t;
+            tau_lo_s[q] = (t == -INFINITY || t == INFINITY) ? t : nextafterf(t, -INFINITY);
+        };
         int* cnt_s = reinterpret_cast<int*>(sm + kOffCnt);
         u64* sortbuf = reinterpret_cast<u64*>(sm + kOffSort) + ew * kSortCap;
         volatile u64* shared_tau = a.shared_tau;
         const bool q_live = etid < a.q_valid;
         tau_key_s[etid] = q_live ? 0ull : ~0ull;
-        tau_f_s[etid] = q_live ? -INFINITY : INFINITY;
+        set_tau_f(etid, q_live ? -INFINITY : INFINITY);
         cnt_s[etid] = 0;
         const float kNoDoc = __int_as_float(0x7fc00000);  // NaN: a missing document never passes a comparison
         auto fetch_norm = [&](long long tile) {
@@ -258,7 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc256_kernel(const __gri
                 const u64 pub = shared_tau[etid];
                 if (pub > tau_key_s[etid]) {
                     tau_key_s[etid] = pub;
-                    tau_f_s[etid] = ordered_to_float((uint32_t)(pub >> 32));
+                    set_tau_f(etid, ordered_to_float((uint32_t)(pub >> 32)));
                 }
             }
             const int my_cnt = cnt_s[etid];
@@ -278,7 +294,7 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc256_kernel(const __gri
                     cnt_s[etid] = a.k;
                     if (kth > tau_key_s[etid]) {
                         tau_key_s[etid] = kth;
-                        tau_f_s[etid] = ordered_to_float((uint32_t)(kth >> 32));
+                        set_tau_f(etid, ordered_to_float((uint32_t)(kth >> 32)));
                     }
                     atomicMax(const_cast<u64*>(a.shared_tau) + etid, kth);
                 }
@@ -295,33 +311,38 @@ __global__ void __launch_bounds__(kThreads, 1) tq_score_tc256_kernel(const __gri
             const uint32_t doc_id = a.id_base + (uint32_t)row;
             const int q0 = epart * (TQ / 2);
             auto chunk = [&](const uint32_t (&r)[16], const int c0) {
-                float sc[16], tf[16];
-                bool any = false;
-#pragma unroll
-                for (int j = 0; j < 16; j += 4) {
-                    const float4 tv = *reinterpret_cast<const float4*>(tau_f_s + q0 + c0 + j);
-                    tf[j] = tv.x;
-                    tf[j + 1] = tv.y;
-                    tf[j + 2] = tv.z;
-                    tf[j + 3] = tv.w;
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    sc[j] = __uint_as_float(r[j]) * norm;
-                    any |= sc[j] >= tf[j];
-                }
                 if (a.seed_scores != nullptr) {
                     // seed mode: for one query the 32 lanes hold 32 consecutive rows
                     if (row < a.n_docs) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) a.seed_scores[(size_t)(q0 + c0 + j) * a.seed_stride + row] = sc[j];
+                        for (int j = 0; j < 16; ++j)
+                            a.seed_scores[(size_t)(q0 + c0 + j) * a.seed_stride + row] = __uint_as_float(r[j]) * norm;
                     }
-                } else if (any) {
+                    return;
+                }
+                float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                    const float4 tl = *reinterpret_cast<const float4*>(tau_lo_s + q0 + c0 + j);
+                    m0 = max3f(m0, fmaf(__uint_as_float(r[j]), norm, -tl.x), fmaf(__uint_as_float(r[j + 1]), norm, -tl.y));
+                    m1 = max3f(m1, fmaf(__uint_as_float(r[j + 2]), norm, -tl.z), fmaf(__uint_as_float(r[j + 3]), norm, -tl.w));
+                }
+                if (fmaxf(m0, m1) >= 0.0f) {   // a missing document's NaN never gets here: max ignores it
+                    float tf[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        const float4 tv = *reinterpret_cast<const float4*>(tau_f_s + q0 + c0 + j);
+                        tf[j] = tv.x;
+                        tf[j + 1] = tv.y;
+                        tf[j + 2] = tv.z;
+                        tf[j + 3] = tv.w;
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        if (sc[j] >= tf[j]) {
-                            const int q = q0 + c0 + j;
-                            const u64 key = make_key(sc[j], doc_id);
+                        const float sc = __uint_as_float(r[j]) * norm;
+                        const int q = q0 + c0 + j;
+                        if (sc >= tf[j]) {
+                            const u64 key = make_key(sc, doc_id);
                             if (key > tau_key_s[q]) {
                                 const int pos = atomicAdd(&cnt_s[q], 1);  // <= 128 before the tile, <= 128 + TD after
                                 cand[((size_t)q * n_segs + blockIdx.x) * kTqTcSegLen + pos] = key;
