@@ -684,7 +684,9 @@ int forward_host_call(EosB200Encoder* e, bool types, int batch, int tokens, cuda
     for (const auto& g : e->graphs)
         if (g.batch == batch && g.tokens == tokens && g.types == types) {
             if (cudaGraphLaunch(g.exec, s) == cudaSuccess) return g.launches;
-            break;
+            cudaGetLastError();   // a replay that cannot be launched: plain launches from here on
+            e->graphs_off = true;
+            return enqueue_forward(e, e->d_ids, e->d_mask, d_types, batch, tokens, e->d_out, s);
         }
     if (e->graphs.size() >= 16) {   // a host cycling through many shapes: start over rather than grow without bound
         cudaStreamSynchronize(s);
