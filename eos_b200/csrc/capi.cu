@@ -1391,7 +1391,7 @@ struct EosB200Corpus {
         int slots = 1;            // launches whose candidate lists are held before one merge launch
         uint64_t* cand = nullptr;     // [slots][queries][segs_per_cta * grid][kTqTcSegLen]
         int* count = nullptr;         // [slots][queries][segs_per_cta * grid]
-        float* seed_scores = nullptr; // [queries][grid * 256] scores of the sample that seeds the thresholds
+        float* seed_scores = nullptr; // [slots][queries][grid * 256] scores of the sample that seeds the thresholds
         CUtensorMap tm;
     } tcp[2];
     int qperm_queries = 0;
@@ -1524,7 +1524,7 @@ int ensure_tc_workspace(EosB200Corpus* c, int plan, char** err) {
         p.slots = plan == 1 ? kTqTcMergeSlots : 1;
         CUDA_TRY(dev_alloc(&p.cand, (size_t)p.slots * p.queries * p.segs_per_cta * grid * kTqTcSegLen));
         CUDA_TRY(dev_alloc(&p.count, (size_t)p.slots * p.queries * p.segs_per_cta * grid));
-        CUDA_TRY(dev_alloc(&p.seed_scores, (size_t)p.queries * grid * 256));
+        CUDA_TRY(dev_alloc(&p.seed_scores, (size_t)p.slots * p.queries * grid * 256));
         p.grid = grid;
     }
     if (p.map_queries != c->cap_queries) {
@@ -1600,16 +1600,20 @@ int enqueue_tc_passes(EosB200Corpus* c, int plan, int64_t n_docs, int q_count, i
     const int grid = (int)(tiles < p.grid ? tiles : p.grid);
     const int n_segs = p.segs_per_cta * grid;
     int launches = 0;
-    // lists of the launches since the last merge: launch i of them writes slot i of the workspace; the lists of all
-    // their queries are then contiguous ([slot][query][list]) and one merge launch serves them all
+    // lists (or, in seed mode, sample scores) of the launches since the last merge: launch i of them writes slot i of
+    // the workspace; what belongs to all their queries is then contiguous ([slot][query][...]) and one launch -- the
+    // list merge, or the threshold select of the seed mode -- serves them all
     const size_t slot_lists = (size_t)p.queries * n_segs;
     int pending = 0, pending_q0 = 0, slot = 0;
     auto merge = [&] {
         if (pending == 0) return;
-        launch_tq_merge_lists(p.cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, p.count, pending, k,
-                              d_ids != nullptr ? d_ids + (size_t)pending_q0 * k : nullptr,
-                              d_scores != nullptr ? d_scores + (size_t)pending_q0 * k : nullptr,
-                              d_keys != nullptr ? d_keys + (size_t)pending_q0 * k : nullptr, s);
+        if (seed)   // the sample's scores of all pending queries -> their thresholds
+            launch_tq_seed_tau_scores(p.seed_scores, n_docs, (int)n_docs, pending, k, c->shared_tau + pending_q0, s);
+        else
+            launch_tq_merge_lists(p.cand, (int64_t)n_segs * kTqTcSegLen, kTqTcSegLen, n_segs, kTqTcSegLen, p.count, pending,
+                                  k, d_ids != nullptr ? d_ids + (size_t)pending_q0 * k : nullptr,
+                                  d_scores != nullptr ? d_scores + (size_t)pending_q0 * k : nullptr,
+                                  d_keys != nullptr ? d_keys + (size_t)pending_q0 * k : nullptr, s);
         ++launches;
         pending_q0 += pending;
         pending = 0;
@@ -1633,8 +1637,9 @@ int enqueue_tc_passes(EosB200Corpus* c, int plan, int64_t n_docs, int q_count, i
         a.cand_keys = p.cand + (seed ? 0 : (size_t)slot * slot_lists * kTqTcSegLen);
         a.cand_count = p.count + (seed ? 0 : (size_t)slot * slot_lists);
         a.shared_tau = c->shared_tau + q0;
-        a.seed_scores = seed ? p.seed_scores : nullptr;
-        a.seed_stride = n_docs;  // seed mode: n_docs = grid * 256 scores per query, a multiple of the tile
+        // seed mode: n_docs = grid * 256 scores per query, a multiple of the tile; slot i holds launch i's queries
+        a.seed_scores = seed ? p.seed_scores + (size_t)slot * p.queries * n_docs : nullptr;
+        a.seed_stride = n_docs;
         a.qperm = c->qperm;
         a.status = qz->rt->d_status;
         auto launch = [&] {
@@ -1644,13 +1649,8 @@ int enqueue_tc_passes(EosB200Corpus* c, int plan, int64_t n_docs, int q_count, i
         if (profile) c->prof.launch(kClsScan, s, launch);
         else launch();
         ++launches;
-        if (seed) {
-            launch_tq_seed_tau_scores(p.seed_scores, n_docs, (int)n_docs, q_here, k, c->shared_tau + q0, s);
-            ++launches;
-        } else {
-            pending += q_here;
-            if (++slot == p.slots) merge();
-        }
+        pending += q_here;
+        if (++slot == p.slots) merge();
     }
     merge();
     return launches;
