@@ -758,12 +758,14 @@ pool_l2_kernel(const __half* __restrict__ hs, const int* __restrict__ cu_rows, c
 
 // Projection head: out[b,:] = l2norm(pooled[b,:] x W), W [dim, out_dim] in-major, fp32 accumulate in input order
 // (PretrainedBERTProjectionHead.Apply, runtime/pretrained_bert_projection_head.go:84-100).  A CTA serves kHeadRows
-// batch rows so that every weight it reads is used kHeadRows times.
+// batch rows and a thread kHeadCols output columns at a time, so that every weight it reads is used kHeadRows times
+// and every 16-byte read of the rows' values in shared memory kHeadCols x 4 times.
 constexpr int kHeadRows = 8;
+constexpr int kHeadCols = 3;
 __global__ void __launch_bounds__(256)
 head_l2_kernel(const float* __restrict__ pooled, int batch, int dim, const float* __restrict__ w, int out_dim,
                float* __restrict__ out) {
-    extern __shared__ float vec[];  // [kHeadRows][dim]
+    extern __shared__ __align__(16) float vec[];  // [kHeadRows][dim]
     __shared__ float red[32];
     const int b0 = blockIdx.x * kHeadRows;
     const int nb = batch - b0 < kHeadRows ? batch - b0 : kHeadRows;
@@ -775,31 +777,51 @@ head_l2_kernel(const float* __restrict__ pooled, int batch, int dim, const float
     float sq[kHeadRows];
 #pragma unroll
     for (int r = 0; r < kHeadRows; ++r) sq[r] = 0.f;
-    for (int j = threadIdx.x; j < out_dim; j += blockDim.x) {
-        float acc[kHeadRows];
+    const int dim4 = (dim & 3) == 0 ? dim : 0;   // the 16-byte reads need rows that start on 16 bytes
+    for (int j0 = threadIdx.x; j0 < out_dim; j0 += blockDim.x * kHeadCols) {
+        float acc[kHeadCols][kHeadRows];
+        int jc[kHeadCols];
 #pragma unroll
-        for (int r = 0; r < kHeadRows; ++r) acc[r] = 0.f;
-        // eight weight loads in flight per thread (the loop is bound by their L2 latency otherwise)
+        for (int c = 0; c < kHeadCols; ++c) {
+            jc[c] = j0 + c * blockDim.x < out_dim ? j0 + c * blockDim.x : j0;   // a column past the end recomputes j0
+#pragma unroll
+            for (int r = 0; r < kHeadRows; ++r) acc[c][r] = 0.f;
+        }
         int i = 0;
-        for (; i + 8 <= dim; i += 8) {
-            float wv[8];
+        for (; i + 4 <= dim4; i += 4) {
+            float wv[kHeadCols][4];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) wv[u] = __ldg(w + (size_t)(i + u) * out_dim + j);
+            for (int c = 0; c < kHeadCols; ++c)
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < 4; ++u) wv[c][u] = __ldg(w + (size_t)(i + u) * out_dim + jc[c]);
 #pragma unroll
-                for (int r = 0; r < kHeadRows; ++r) acc[r] = fmaf(vec[r * dim + i + u], wv[u], acc[r]);
+            for (int r = 0; r < kHeadRows; ++r) {
+                const float4 v = *reinterpret_cast<const float4*>(vec + r * dim + i);
+#pragma unroll
+                for (int c = 0; c < kHeadCols; ++c) {   // every accumulator takes its terms in input order
+                    acc[c][r] = fmaf(v.x, wv[c][0], acc[c][r]);
+                    acc[c][r] = fmaf(v.y, wv[c][1], acc[c][r]);
+                    acc[c][r] = fmaf(v.z, wv[c][2], acc[c][r]);
+                    acc[c][r] = fmaf(v.w, wv[c][3], acc[c][r]);
+                }
             }
         }
         for (; i < dim; ++i) {
-            const float wv = __ldg(w + (size_t)i * out_dim + j);
 #pragma unroll
-            for (int r = 0; r < kHeadRows; ++r) acc[r] = fmaf(vec[r * dim + i], wv, acc[r]);
+            for (int c = 0; c < kHeadCols; ++c) {
+                const float wv = __ldg(w + (size_t)i * out_dim + jc[c]);
+#pragma unroll
+                for (int r = 0; r < kHeadRows; ++r) acc[c][r] = fmaf(vec[r * dim + i], wv, acc[c][r]);
+            }
         }
 #pragma unroll
-        for (int r = 0; r < kHeadRows; ++r) {
-            if (r < nb) out[(size_t)(b0 + r) * out_dim + j] = acc[r];
-            sq[r] += acc[r] * acc[r];
+        for (int c = 0; c < kHeadCols; ++c) {
+            if (j0 + c * blockDim.x >= out_dim) continue;
+#pragma unroll
+            for (int r = 0; r < kHeadRows; ++r) {
+                if (r < nb) out[(size_t)(b0 + r) * out_dim + jc[c]] = acc[c][r];
+                sq[r] += acc[c][r] * acc[c][r];
+            }
         }
     }
 #pragma unroll
