@@ -240,9 +240,12 @@ __device__ __forceinline__ void row_mean_inv(const float (&v)[kChunks][8], int d
     *inv_out = 1.0f / sqrtf(var + eps);
 }
 
+// gb: optional shared-memory copy of the scale and shift, [chunk][gamma lo, gamma hi, beta lo, beta hi][lane] (the
+// layout of layernorm_kernel); nullptr reads them from global memory.
 template <int kChunks>
 __device__ __forceinline__ void row_layernorm_store(float (&v)[kChunks][8], int dim, int lane, const float* gamma,
-                                                    const float* beta, float eps, __half* out_row) {
+                                                    const float* beta, float eps, __half* out_row,
+                                                    const float4 (*gb)[4][32] = nullptr) {
     float sum = 0.f;
 #pragma unroll
     for (int c = 0; c < kChunks; ++c) {
@@ -272,10 +275,10 @@ __device__ __forceinline__ void row_layernorm_store(float (&v)[kChunks][8], int 
         const int col = (c * 32 + lane) * 8;
         if (col < dim) {
             float o[8];
-            const float4 g0 = *reinterpret_cast<const float4*>(gamma + col);
-            const float4 g1 = *reinterpret_cast<const float4*>(gamma + col + 4);
-            const float4 b0 = *reinterpret_cast<const float4*>(beta + col);
-            const float4 b1 = *reinterpret_cast<const float4*>(beta + col + 4);
+            const float4 g0 = gb != nullptr ? gb[c][0][lane] : *reinterpret_cast<const float4*>(gamma + col);
+            const float4 g1 = gb != nullptr ? gb[c][1][lane] : *reinterpret_cast<const float4*>(gamma + col + 4);
+            const float4 b0 = gb != nullptr ? gb[c][2][lane] : *reinterpret_cast<const float4*>(beta + col);
+            const float4 b1 = gb != nullptr ? gb[c][3][lane] : *reinterpret_cast<const float4*>(beta + col + 4);
             const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
             const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
@@ -292,10 +295,26 @@ embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ typ
                 const __half* __restrict__ pos, int max_pos, const __half* __restrict__ typ, int type_vocab,
                 const float* __restrict__ gamma, const float* __restrict__ beta, float eps, int dim, int m_alloc,
                 __half* __restrict__ out, int* status) {
+    __shared__ float4 gb_s[kChunks][4][32];
     const int lane = threadIdx.x & 31;
     const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
     int rows = *total_rows;
     if (rows > m_alloc) rows = m_alloc;
+    for (int i = threadIdx.x; i < kChunks * 32; i += blockDim.x) {
+        const int c = i >> 5, l = i & 31;
+        const int col = (c * 32 + l) * 8;
+        float g[8], b[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            g[j] = col < dim ? gamma[col + j] : 0.f;
+            b[j] = col < dim ? beta[col + j] : 0.f;
+        }
+        gb_s[c][0][l] = make_float4(g[0], g[1], g[2], g[3]);
+        gb_s[c][1][l] = make_float4(g[4], g[5], g[6], g[7]);
+        gb_s[c][2][l] = make_float4(b[0], b[1], b[2], b[3]);
+        gb_s[c][3][l] = make_float4(b[4], b[5], b[6], b[7]);
+    }
+    __syncthreads();
     for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps_per_grid) {
         const int src = row_src[r];
         const int t = src % tokens;
@@ -325,7 +344,7 @@ embed_ln_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ typ
                 for (int i = 0; i < 8; ++i) v[c][i] = (fa[i] + fp[i]) + fq[i];
             }
         }
-        row_layernorm_store<kChunks>(v, dim, lane, gamma, beta, eps, out + (size_t)r * dim);
+        row_layernorm_store<kChunks>(v, dim, lane, gamma, beta, eps, out + (size_t)r * dim, gb_s);
     }
 }
 
