@@ -299,6 +299,59 @@ func (rt *b200Runtime) runB200Embedder(e *b200Encoder, ids, mask, types *backend
 	}, nil
 }
 
+// runB200EmbedderBatches embeds several [B,T] batches back to back (the loop of EmbedBatch,
+// runtime/embedding_model.go:664-700) without a host stall between them: every batch is submitted with
+// eos_b200_encoder_submit and one eos_b200_encoder_wait completes them all.  C keeps the host pointers until the wait,
+// so the inputs and outputs of the batches in flight live in C memory (cgo pointer-passing rule) and are copied out
+// after the wait.  ids[i], mask[i] are [B_i, T_i] int32 tensors; types may be nil.
+func (rt *b200Runtime) runB200EmbedderBatches(e *b200Encoder, ids, mask, types []*backend.Tensor) ([]*backend.Tensor, error) {
+	var arena cArena
+	defer arena.free()
+	i32 := func(v []int32) *C.int32_t {
+		n := C.size_t(len(v)) * 4
+		p := C.malloc(n)
+		C.memcpy(p, unsafe.Pointer(&v[0]), n)
+		arena.ptrs = append(arena.ptrs, p)
+		return (*C.int32_t)(p)
+	}
+	outs := make([]unsafe.Pointer, len(ids))
+	var cerr *C.char
+	for i := range ids {
+		if len(ids[i].Shape) != 2 || len(ids[i].I32) == 0 || len(mask[i].I32) != len(ids[i].I32) {
+			return nil, fmt.Errorf("bert_embedder input_ids / attention_mask must be non-empty [B,T] tensors of one shape")
+		}
+		b, t := ids[i].Shape[0], ids[i].Shape[1]
+		var typesPtr *C.int32_t
+		if types != nil && types[i] != nil && len(types[i].I32) == b*t {
+			typesPtr = i32(types[i].I32)
+		}
+		outs[i] = C.malloc(C.size_t(b*e.outDim) * 4)
+		arena.ptrs = append(arena.ptrs, outs[i])
+		rc := C.eos_b200_encoder_submit(e.h, i32(ids[i].I32), i32(mask[i].I32), typesPtr, C.int(b), C.int(t),
+			(*C.float)(outs[i]), &cerr)
+		if err := b200Error(rc, cerr); err != nil {
+			var werr *C.char
+			C.eos_b200_encoder_wait(e.h, nil, &werr) // nothing may stay in flight over buffers about to be freed
+			if werr != nil {
+				C.eos_b200_free_cstring(werr)
+			}
+			return nil, err
+		}
+	}
+	var st C.EosB200Stats
+	if err := b200Error(C.eos_b200_encoder_wait(e.h, &st, &cerr), cerr); err != nil {
+		return nil, err
+	}
+	res := make([]*backend.Tensor, len(ids))
+	for i := range ids {
+		b := ids[i].Shape[0]
+		out := make([]float32, b*e.outDim)
+		C.memcpy(unsafe.Pointer(&out[0]), outs[i], C.size_t(len(out))*4)
+		res[i] = backend.NewTensorF32([]int{b, e.outDim}, out)
+	}
+	return res, nil
+}
+
 // dispatchStepB200 is what executor.dispatchStep calls first when the build tag is set; (result, handled, error)
 // as in cuda.go:394.
 func (e *executor) dispatchStepB200(step eosartifact.Step, outputType eosartifact.ValueType, inputs []*backend.Tensor) (backend.StepDispatchResult, bool, error) {
